@@ -1,0 +1,1 @@
+from functools import cached_property  # noqa: F401

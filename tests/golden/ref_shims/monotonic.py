@@ -1,0 +1,1 @@
+from time import monotonic  # noqa: F401
