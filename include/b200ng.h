@@ -1,0 +1,155 @@
+/*
+ * b200ng -- C ABI of the B200 backend for nGraph-Python graphs.
+ *
+ * Every entry point has C linkage, takes plain pointers and sizes, and returns an int status:
+ * 0 on success, a negative B2_ERR_* code on failure (b2_last_error() then returns a
+ * description owned by the library, valid until the next failing call on the same thread).
+ * Device pointers are raw CUDA device addresses; `stream` is a cudaStream_t passed as void*.
+ * Unless stated otherwise an entry point allocates no device memory: the caller owns every
+ * buffer, including scratch.
+ *
+ * The reference drives its GPU through pycuda and has no C ABI of its own; each group below
+ * names the reference interface (file:line in NervanaSystems/ngraph-python) whose job it takes
+ * over.
+ */
+#ifndef B200NG_H
+#define B200NG_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_OK 0
+#define B2_ERR_INVALID (-1)     /* bad argument / unsupported program */
+#define B2_ERR_CUDA (-2)        /* a CUDA runtime call failed */
+#define B2_ERR_COMPILE (-3)     /* run-time kernel compilation failed */
+#define B2_ERR_UNAVAILABLE (-4) /* a required system library could not be loaded */
+#define B2_ERR_TIMEOUT (-5)     /* a bounded device-side wait ran out */
+#define B2_ERR_COMM (-6)        /* NCCL reported an error */
+
+const char* b2_last_error(void);
+/* library version: major * 10000 + minor * 100 + patch */
+int b2_version(void);
+/* number of visible CUDA devices, or a negative error */
+int b2_device_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused elementwise + reduction kernels.
+ * Replaces: ElementWiseKernel / CudaSourceFile / _get_compound_kernel / _generate_kernel_args
+ * (ngraph/transformers/gputransform.py:86-345, ngraph/transformers/gpu/float_ew2.py:553-1653).
+ * A program is a straight-line list of fp32 ops over up to 12 input tensors, with elementwise
+ * outputs and at most one family of reductions, over an iteration space [A, B, C] (C innermost).
+ * ------------------------------------------------------------------------------------------ */
+#define B2_EW_MAX_IN 12
+#define B2_EW_MAX_OUT 6   /* elementwise + reduction outputs together */
+#define B2_EW_MAX_CONST 16
+#define B2_EW_MAX_OPS 96
+
+enum b2_dtype { B2_F32 = 0, B2_FLEX16 = 1 };
+
+/* op codes: one per template of float_ew2.py:31-68 */
+enum b2_ew_opcode {
+    B2_OP_ASSIGN = 0, B2_OP_NEG, B2_OP_ABS, B2_OP_SQRT, B2_OP_SQR, B2_OP_EXP, B2_OP_LOG,
+    B2_OP_RCP, B2_OP_EXP2, B2_OP_LOG2, B2_OP_SIG, B2_OP_TANH, B2_OP_SAFELOG, B2_OP_SGN,
+    B2_OP_SIN, B2_OP_COS,
+    B2_OP_ADD = 32, B2_OP_SUB, B2_OP_MUL, B2_OP_DIV, B2_OP_INT_DIV, B2_OP_MOD, B2_OP_EQ,
+    B2_OP_NE, B2_OP_LT, B2_OP_LE, B2_OP_GT, B2_OP_GE, B2_OP_POW, B2_OP_MINIMUM, B2_OP_MAXIMUM,
+    B2_OP_ONEHOT  /* (index along the reduction-free axis B) == x */
+};
+
+/* reduction codes: float_ew2.py:70-90 */
+enum b2_ew_redop {
+    B2_RED_SUM = 0, B2_RED_PROD, B2_RED_MAX, B2_RED_MIN, B2_RED_ARGMAX, B2_RED_ARGMIN
+};
+
+enum b2_ew_reduce_mode {
+    B2_REDUCE_NONE = 0, /* elementwise only */
+    B2_REDUCE_C = 1,    /* reduce the innermost axis: results have shape [A, B] */
+    B2_REDUCE_B = 2     /* reduce the middle axis: results have shape [A, C] */
+};
+
+typedef struct b2_ew_tensor {
+    int32_t dtype;       /* enum b2_dtype */
+    int32_t flex_slot;   /* row of the flex table / stats array; -1 for fp32 */
+    int64_t sa, sb, sc;  /* element strides along A, B, C; 0 broadcasts */
+} b2_ew_tensor;
+
+/* registers: 0..n_in-1 inputs, n_in..n_in+n_const-1 constants, then one per op in order */
+typedef struct b2_ew_op {
+    int32_t opcode;
+    int32_t a, b;        /* source registers (b ignored by unary ops) */
+} b2_ew_op;
+
+typedef struct b2_ew_result {
+    int32_t reg;         /* register stored (elementwise) or reduced */
+    int32_t redop;       /* enum b2_ew_redop; ignored for elementwise outputs */
+    b2_ew_tensor t;      /* strides of the destination; the reduced axis has stride 0 */
+} b2_ew_result;
+
+typedef struct b2_ew_program {
+    int64_t A, B, C;
+    int32_t reduce_mode; /* enum b2_ew_reduce_mode */
+    int32_t n_in, n_const, n_ops, n_out, n_red;
+    b2_ew_tensor in[B2_EW_MAX_IN];
+    b2_ew_op ops[B2_EW_MAX_OPS];
+    b2_ew_result out[B2_EW_MAX_OUT]; /* n_out elementwise outputs, then n_red reductions */
+} b2_ew_program;
+
+typedef struct b2_flex_scale {
+    float scale;      /* 2^-dec : readers multiply mantissas by it */
+    float inv_scale;  /* 2^dec  : writers multiply values by it before rounding */
+} b2_flex_scale;
+
+typedef struct b2_ew_kernel b2_ew_kernel;
+
+/* Compiles (or fetches from the in-process cache) the kernel for a program.
+ * replaces CudaSourceFile.add_kernel + compile (float_ew2.py:1553-1623). */
+int b2_ew_compile(const b2_ew_program* prog, b2_ew_kernel** out_kernel);
+/* Generates and compiles the program for sm_100a without loading it (needs no GPU): the
+ * build-time check of a program.  `vec` asks for the 128-bit variant where the program allows
+ * it; the generated source is copied to `source` when given. */
+int b2_ew_check(const b2_ew_program* prog, int vec, int probe, char* source, size_t source_cap);
+/* Bytes of caller-provided scratch a launch needs (0 for most programs; reductions of a few
+ * very long rows are split across CTAs and combined from scratch). */
+int b2_ew_scratch_bytes(const b2_ew_kernel* k, size_t* bytes);
+/* Launches.  `out` holds the n_out elementwise destinations followed by the n_red reduction
+ * destinations.  `probe` != 0 runs the measuring variant used on a tensor's first write: nothing
+ * is stored, and flex_stats[slot] receives the bit pattern of the largest |fp32 value| each
+ * flex output would have been given (fmaxf order == integer order for non-negative floats).
+ * `status` (device int32, may be NULL) is set to 1 if a bounded device-side wait ran out, in
+ * which case the results of that launch are undefined.
+ * replaces ElementWiseKernel.execute / bind_flex_scales (gputransform.py:277-345,
+ * flexgputransform.py:56-64). */
+int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const* out, const float* consts,
+                 const b2_flex_scale* flex_table, int32_t* flex_stats, void* scratch,
+                 size_t scratch_bytes, int32_t* status, int probe, void* stream);
+/* Generated CUDA source of a compiled kernel (for inspection / tests). */
+const char* b2_ew_source(const b2_ew_kernel* k);
+/* Number of kernel launches one b2_ew_launch issues (1, or 2 for split reductions). */
+int b2_ew_launch_count(const b2_ew_kernel* k);
+/* Directory searched first for libnvrtc.so.12 (optional; NULL keeps the default search). */
+int b2_set_nvrtc_path(const char* path);
+
+/* ------------------------------------------------------------------------------------------
+ * Flex16 host<->device conversions, done on the device.
+ * Replaces: FlexGPUDeviceTensor.get / __setitem__ (ngraph/transformers/flexgputransform.py:
+ * 178-208), which convert on the host with numpy.
+ * ------------------------------------------------------------------------------------------ */
+/* dst[i] = (int16) trunc(clip(src[i] * table[slot].inv_scale, -32768, 32767));
+ * stats[slot] = max(stats[slot], max |dst|). */
+int b2_flex_host_quantize(const float* src, int16_t* dst, int64_t n, const b2_flex_scale* table,
+                          int32_t slot, int32_t* stats, void* stream);
+/* dst[i] = table[slot].scale * (float) src[i] */
+int b2_flex_dequantize(const int16_t* src, float* dst, int64_t n, const b2_flex_scale* table,
+                       int32_t slot, void* stream);
+/* *out = max(*out, bit pattern of max |src[i]|) (NaN counts as 0); used to pick a first exponent
+ * for data arriving from the host. */
+int b2_absmax_bits_f32(const float* src, int64_t n, int32_t* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200NG_H */
