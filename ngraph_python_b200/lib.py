@@ -174,3 +174,18 @@ class EwKernel(object):
             self._consts[i] = c
         check(_lib.b2_ew_launch(self.handle, ins, outs, self._consts, flex_table, flex_stats,
                                 scratch, scratch_bytes, status, int(probe), stream))
+
+
+class PlannedKernel(object):
+    """Generated and compiled for sm_100a, but not loaded (no device needed)."""
+
+    def __init__(self, prog, flex=False):
+        self.prog = prog
+        self._source = ew_check(prog, vec=True, probe=False, want_source=True)
+        if flex:
+            ew_check(prog, vec=True, probe=True)
+        self.scratch_bytes = 0
+        self.launches = 2 if "b2_ew_finalize" in self._source else 1
+
+    def source(self):
+        return self._source

@@ -1,0 +1,849 @@
+"""The `b200` transformer: compiles an op graph into a list of CUDA launches and runs it.
+
+Mirrors the reference's transformer API (ngraph/transformers/base.py): a registry of transformer
+classes keyed by `transformer_name` (:265-279), `make_transformer`, `set_transformer_factory`,
+`make_transformer_factory`, `transformer_choices` (:807-847), `Transformer.computation`
+(:420-433) and `Computation.__call__` (:94-136).  What the reference's GPU backend does with
+pycuda, NVRTC'd per-op kernels and maxas SASS (ngraph/transformers/gputransform.py:348-1148,
+flexgputransform.py:67-371) is done here by hand-written sm_100a kernels behind the C ABI of
+libb200ng.so; PyTorch only provides device memory, streams and pinned host buffers.
+
+There is no CPU path: constructing the transformer without the shared library or without a CUDA
+device raises.
+"""
+import collections
+import numbers
+
+import numpy as np
+
+from . import flex as flexmod
+from . import fusion
+from . import lib
+from .op_graph import (AssignableTensorOp, AssignOp, Axes, BroadcastOp, ConvolutionOp, DotOp,
+                       ElementWiseOp, Op, PoolingOp, ReductionOp, ReorderAxes, SequentialOp,
+                       ViewOp, as_op, make_axes)
+
+
+class UnsupportedTransformerException(Exception):
+    """ngraph/transformers/base.py:37"""
+
+
+# ---------------------------------------------------------------------------------------------
+# storage
+# ---------------------------------------------------------------------------------------------
+class Buffer(object):
+    """One device allocation; dense in `axes` order."""
+
+    def __init__(self, name, axes, flex, persistent=False):
+        self.name = name
+        self.axes = make_axes(axes)
+        self.size = self.axes.size
+        self.flex = flex
+        self.persistent = persistent
+        self.tensor = None          # torch tensor, flat
+        self.staging = None         # fp32 staging for flex host writes
+        self.entry = None           # FlexEntry
+        self.slot = -1              # flex table row of the data currently stored
+        self.slot_write = -1        # row used by in-place writers (persistent tensors)
+        self.init_array = None
+        # planning state (per computation build)
+        self.last_write_step = -1
+        self.last_read_step = -1
+
+    def ptr(self):
+        return self.tensor.data_ptr()
+
+
+class View(object):
+    """A strided window on a buffer, described per named axis."""
+
+    def __init__(self, buffer, axes, strides, offset=0):
+        self.buffer = buffer
+        self.axes = make_axes(axes)
+        self.strides = tuple(int(s) for s in strides)
+        self.offset = int(offset)
+
+    @staticmethod
+    def dense(buffer):
+        strides, acc = [], 1
+        for n in reversed(buffer.axes.lengths):
+            strides.append(acc)
+            acc *= n
+        return View(buffer, buffer.axes, tuple(reversed(strides)))
+
+    def stride_of(self, axis):
+        for a, s in zip(self.axes, self.strides):
+            if a == axis:
+                return s
+        return 0
+
+    def key(self):
+        return (id(self.buffer), tuple((a.name, s) for a, s in zip(self.axes, self.strides)
+                                       if s != 0 and a.length != 1), self.offset)
+
+    def is_dense(self):
+        d = View.dense(self.buffer)
+        return self.offset == 0 and self.axes == d.axes and self.strides == d.strides
+
+
+# ---------------------------------------------------------------------------------------------
+# steps (what the executor launches, in order)
+# ---------------------------------------------------------------------------------------------
+class EwStep(object):
+    kind = "ew"
+
+    def __init__(self, group):
+        self.group = group
+        self.index = group.index
+        self.kernel = None
+        self.in_views = []
+        self.out_views = []      # elementwise outputs then reduction outputs
+        self.consts = []
+        self.scratch = None
+
+    def output_buffers(self):
+        return [v.buffer for v in self.out_views]
+
+
+# ---------------------------------------------------------------------------------------------
+class Computation(object):
+    """A callable compiled from (returns, *parameters) (ngraph/transformers/base.py:44-136)."""
+
+    def __init__(self, transformer, returns, parameters):
+        self.transformer = transformer
+        if isinstance(returns, (list, tuple)):
+            self.returns_kind = type(returns)
+            self.returns = [as_op(r) for r in returns]
+        elif isinstance(returns, dict):
+            raise ValueError("dict returns are not supported")
+        elif returns is None:
+            self.returns_kind = None
+            self.returns = []
+        else:
+            self.returns_kind = Op
+            self.returns = [as_op(returns)]
+        self.parameters = [as_op(p) for p in parameters]
+        for p in self.parameters:
+            if not (isinstance(p, AssignableTensorOp) and p.is_input):
+                raise ValueError("computation parameters must be placeholders or variables, "
+                                 "got %r" % (p,))
+        self.steps = None
+        self.executor = None
+        self.launches_per_call = 0
+
+    # ---- compile -------------------------------------------------------------------------
+    def _ordered_ops(self):
+        order, seen = [], set()
+
+        def visit(op):
+            if op in seen:
+                return
+            seen.add(op)
+            for a in op.all_deps:
+                visit(a)
+            order.append(op)
+        for r in self.returns:
+            visit(r)
+        return order
+
+    def build(self):
+        t = self.transformer
+        planner = _Planner(t, self)
+        self.steps, self.return_views = planner.plan(self._ordered_ops(), self.returns)
+        for s in self.steps:
+            planner.finalize_step(s)
+        t._allocate()
+        self.launches_per_call = builtin_sum(s.kernel.launches for s in self.steps)
+        self.written = planner.written_buffers
+        self.executor = self._run_steps
+
+    # ---- run -----------------------------------------------------------------------------
+    def __call__(self, *args, **kwargs):
+        t = self.transformer
+        if self.steps is None:
+            t.initialize()
+        if t.plan_only:
+            raise lib.B200Error("a plan_only transformer cannot run computations")
+        feed = kwargs.pop("feed_dict", None)
+        if feed is not None:
+            args = [feed[p] for p in self.parameters]
+        if len(args) != len(self.parameters):
+            raise ValueError("Computation was expecting %d arguments, but was called with %d" %
+                             (len(self.parameters), len(args)))
+        t._begin_call(self)
+        for p, value in zip(self.parameters, args):
+            t._host_to_device(t._view_of(p), value)
+        self.executor()
+        results = [t._device_to_host(v) for v in self.return_views]
+        t._end_call(self)
+        if self.returns_kind is Op:
+            return results[0]
+        if self.returns_kind is None:
+            return None
+        return tuple(results)
+
+    def _run_steps(self):
+        t = self.transformer
+        for s in self.steps:
+            t._launch_step(s)
+
+
+builtin_sum = sum
+
+
+# ---------------------------------------------------------------------------------------------
+class _Planner(object):
+    """Builds the step list of one computation: views, fusion groups, programs."""
+
+    def __init__(self, transformer, computation):
+        self.t = transformer
+        self.comp = computation
+        self.steps = []
+        self.producer = {}        # op -> step index that produces its value
+        self.group_of = {}        # EW/reduction op -> EwGroup
+        self.consumers = collections.defaultdict(list)
+        self.written_buffers = []
+
+    # -- helpers ------------------------------------------------------------------------------
+    def _resolve(self, op):
+        """Follows SequentialOp to the op that carries the value."""
+        while isinstance(op, SequentialOp):
+            op = op.value_tensor
+        return op
+
+    def _is_scalar_const(self, op):
+        return isinstance(op, AssignableTensorOp) and op.is_scalar_constant
+
+    def _base_tensor(self, op):
+        """(source op, view transform chain) for an argument: strips views."""
+        op = self._resolve(op)
+        chain = []
+        while isinstance(op, ViewOp):
+            chain.append(op)
+            op = self._resolve(op.args[0])
+        return op, chain
+
+    def _new_step_index(self):
+        return len(self.steps)
+
+    # -- planning -----------------------------------------------------------------------------
+    def plan(self, ordered, returns):
+        for op in ordered:
+            for a in op.args:
+                self.consumers[self._base_tensor(a)[0]].append(op)
+        returned = set(self._base_tensor(r)[0] for r in returns)
+        self.returned = returned
+        for buf in self.t._buffers.values():
+            buf.last_write_step = -1
+            buf.last_read_step = -1
+        for op in ordered:
+            if isinstance(op, (ElementWiseOp, ReductionOp, AssignOp)):
+                self._place_ew(op)
+            elif isinstance(op, (AssignableTensorOp, ViewOp, SequentialOp)):
+                continue
+            else:
+                self._place_other(op)
+        # decide what each group materialises
+        for step in self.steps:
+            if step.kind == "ew":
+                self._collect_outputs(step)
+        steps = [s for s in self.steps if s.kind != "ew" or s.out_ops]
+        return_views = [self.t._view_of(self._resolve(r)) for r in returns]
+        return steps, return_views
+
+    def _place_ew(self, op):
+        is_assign = isinstance(op, AssignOp)
+        is_red = isinstance(op, ReductionOp)
+        if is_assign:
+            target = op.args[0]
+            value_args = [op.args[1]]
+            iter_axes = target.axes
+            tbuf = self.t._buffer_of(target)
+        else:
+            value_args = list(op.args)
+            iter_axes = op.args[0].axes if is_red else op.axes
+        lower = -1
+        for a in value_args:
+            base, chain = self._base_tensor(a)
+            if isinstance(base, AssignableTensorOp):
+                if not base.is_scalar_constant:
+                    lws = self.t._buffer_of(base).last_write_step
+                    if lws >= 0:
+                        lower = max(lower, lws + 1)    # must see the in-place write
+            elif base in self.producer:
+                direct = not chain and not isinstance(base, ReductionOp) and base in self.group_of
+                lower = max(lower, self.producer[base] + (0 if direct else 1))
+        if is_assign:
+            lower = max(lower, tbuf.last_write_step, tbuf.last_read_step)
+        # candidate groups: the latest open groups that run late enough for every dependency;
+        # independent chains over the same iteration space end up in one kernel this way
+        group = None
+        tried = 0
+        for step in reversed(self.steps if self.t.fuse else []):
+            if step.index < lower or tried >= 6:
+                break
+            if step.kind != "ew":
+                continue
+            tried += 1
+            cand = step.group
+            if not self._can_join(cand, op, iter_axes, is_red):
+                continue
+            if is_assign and tbuf.last_read_step == cand.index:
+                # the group already reads the target: in-place is safe only element for element
+                tv = self.t._view_of(target)
+                if any(v.buffer is tbuf and v.key() != tv.key() for v in cand.ext_inputs):
+                    continue
+            group = cand
+            break
+        if group is None:
+            group = fusion.EwGroup(self._new_step_index(), iter_axes)
+            step = EwStep(group)
+            step.out_ops = []
+            self.steps.append(step)
+        group.add(op)
+        if is_red or is_assign or op in self.returned:
+            group.stored.add(op)
+        if is_red:
+            group.red_axes = op.reduction_axes
+        self.group_of[op] = group
+        self.producer[op] = group.index
+        # external loads of this op
+        for a in value_args:
+            base, chain = self._base_tensor(a)
+            if self._is_scalar_const(base):
+                group.n_consts += 1
+                continue
+            if group.has(base) and not chain and not isinstance(base, ReductionOp):
+                continue
+            if base in self.group_of:
+                self.group_of[base].stored.add(base)     # consumed outside its own kernel
+            v = self.t._view_of(self._resolve(a))
+            if not any(v.key() == w.key() for w in group.ext_inputs):
+                group.ext_inputs.append(v)
+                # a persistent tensor read after an in-place write of this computation carries
+                # the exponent chosen for that write
+                group.after_write[v.key()] = isinstance(base, AssignableTensorOp) and \
+                    self.t._buffer_of(base).last_write_step >= 0
+            if isinstance(base, AssignableTensorOp):
+                b = self.t._buffer_of(base)
+                b.last_read_step = max(b.last_read_step, group.index)
+        if is_assign:
+            tbuf.last_write_step = group.index
+
+    def _can_join(self, g, op, iter_axes, is_red):
+        if g.iter_axes != iter_axes:
+            return False
+        if is_red:
+            if g.red_axes is not None and g.red_axes != op.reduction_axes:
+                return False
+        new_inputs = 0
+        for a in (op.args[1:] if isinstance(op, AssignOp) else op.args):
+            base, chain = self._base_tensor(a)
+            if g.has(base) and isinstance(base, ReductionOp):
+                return False     # needs a value that exists only after the whole reduction
+            if self._is_scalar_const(base) or (g.has(base) and not chain):
+                continue
+            new_inputs += 1
+        if len(g.ext_inputs) + new_inputs > fusion.MAX_IN:
+            return False
+        # the iteration space must still fold onto the kernel's three axes
+        views = list(g.ext_inputs)
+        for a in (op.args[1:] if isinstance(op, AssignOp) else op.args):
+            base, chain = self._base_tensor(a)
+            if self._is_scalar_const(base) or (g.has(base) and not chain):
+                continue
+            views.append(self.t._view_of(self._resolve(a)))
+        red_axes = op.reduction_axes if is_red else (g.red_axes or Axes())
+        strides = [[v.stride_of(a) for a in iter_axes] for v in views]
+        dense, acc = [], 1
+        for n in reversed(iter_axes.lengths):
+            dense.append(acc)
+            acc *= n
+        strides.append(list(reversed(dense)))
+        try:
+            cl, cs, cr = fusion.collapse_dims(list(iter_axes.lengths), strides,
+                                              [a in red_axes for a in iter_axes])
+            fusion.map_to_abc(cl, cs, cr)
+        except ValueError:
+            return False
+        if len(g.members) + 1 > fusion.MAX_OPS or g.n_consts + 2 > fusion.MAX_CONST:
+            return False
+        if len(g.stored) + 1 > fusion.MAX_OUT - 1:      # one spare for a later outside consumer
+            return False
+        return True
+
+    def _place_other(self, op):
+        raise ValueError("Unhandled op: {}".format(op))
+
+    def _collect_outputs(self, step):
+        """Which values of the group must be stored: those used by another step or returned."""
+        g = step.group
+        outs = []
+        for m in g.members:
+            if isinstance(m, AssignOp):
+                outs.append(m)
+                continue
+            needed = m in self.returned or isinstance(m, ReductionOp)
+            if not needed:
+                for c in self.consumers.get(m, ()):
+                    cg = self.group_of.get(c)
+                    direct = any(self._base_tensor(a)[0] is m and not self._base_tensor(a)[1]
+                                 for a in c.args)
+                    if cg is not g or not direct:
+                        needed = True
+                        break
+            if needed:
+                outs.append(m)
+        if len(outs) > fusion.MAX_OUT:
+            raise ValueError("Unhandled op: fused kernel with %d outputs" % len(outs))
+        step.out_ops = outs
+        for m in outs:
+            if not isinstance(m, AssignOp):
+                self.t._view_of(m)       # creates the buffer
+
+    # -- program construction -------------------------------------------------------------------
+    def finalize_step(self, step):
+        if step.kind == "ew":
+            self._finalize_ew(step)
+
+    def _finalize_ew(self, step):
+        t = self.t
+        g = step.group
+        iter_axes = g.iter_axes
+        red_axes = g.red_axes if g.red_axes is not None else Axes()
+        lengths = list(iter_axes.lengths)
+        reduced = [a in red_axes for a in iter_axes]
+        in_views = list(g.ext_inputs)
+        ew_outs = [m for m in step.out_ops if not isinstance(m, ReductionOp)]
+        red_outs = [m for m in step.out_ops if isinstance(m, ReductionOp)]
+        out_views = []
+        for m in ew_outs + red_outs:
+            out_views.append(t._view_of(m.args[0]) if isinstance(m, AssignOp) else t._view_of(m))
+        strides_list = [[v.stride_of(a) for a in iter_axes] for v in in_views + out_views]
+        clen, cstr, cred = fusion.collapse_dims(lengths, strides_list, reduced)
+        dims, abc, mode = fusion.map_to_abc(clen, cstr, cred)
+        # registers
+        reg = {}
+        consts = []
+        const_reg = {}
+        ops = []
+        n_in = len(in_views)
+
+        def input_index(view):
+            for i, w in enumerate(in_views):
+                if w.key() == view.key():
+                    return i
+            raise KeyError(view)
+
+        pending = []     # (dst op, opname, [arg descriptors])
+        for m in g.members:
+            if isinstance(m, ReductionOp):
+                continue
+            args = [m.args[1]] if isinstance(m, AssignOp) else list(m.args)
+            descs = []
+            for a in args:
+                base, chain = self._base_tensor(a)
+                if self._is_scalar_const(base):
+                    val = float(np.asarray(base.initial_value))
+                    if val not in const_reg:
+                        const_reg[val] = len(consts)
+                        consts.append(val)
+                    descs.append(("c", const_reg[val]))
+                elif g.has(base) and not chain and not isinstance(base, ReductionOp):
+                    descs.append(("r", base))
+                else:
+                    descs.append(("i", input_index(t._view_of(self._resolve(a)))))
+            pending.append((m, "assign" if isinstance(m, AssignOp) else m.opname, descs))
+        n_const = len(consts)
+
+        def resolve(d):
+            if d[0] == "c":
+                return n_in + d[1]
+            if d[0] == "i":
+                return d[1]
+            return reg[d[1]]
+        for m, name, descs in pending:
+            a = resolve(descs[0])
+            b = resolve(descs[1]) if len(descs) > 1 else None
+            ops.append((name, a, b))
+            reg[m] = n_in + n_const + len(ops) - 1
+
+        if t.flex:
+            ops = _fuse_sigmoid(ops, n_in, consts)
+
+        def tdesc(view, st):
+            fx = view.buffer.flex
+            return dict(dtype=lib.FLEX16 if fx else lib.F32, strides=st)
+        inputs = []
+        for v, st in zip(in_views, abc[:n_in]):
+            d = tdesc(v, st)
+            d["slot"] = -1
+            if v.buffer.flex:
+                d["slot"] = v.buffer.slot_write if g.after_write.get(v.key()) else v.buffer.slot
+            inputs.append(d)
+        outs, reds = [], []
+        for k, (m, v) in enumerate(zip(ew_outs + red_outs, out_views)):
+            d = tdesc(v, abc[n_in + k])
+            d["slot"] = t._write_slot(v.buffer) if v.buffer.flex else -1
+            if isinstance(m, ReductionOp):
+                src = m.args[0]
+                base, chain = self._base_tensor(src)
+                if g.has(base) and not chain:
+                    d["reg"] = reg[base]
+                else:
+                    d["reg"] = input_index(t._view_of(self._resolve(src)))
+                d["redop"] = m.redop
+                reds.append(d)
+            else:
+                d["reg"] = reg[m]
+                outs.append(d)
+        prog = lib.make_program(dims, inputs, consts, ops, outs, reds, mode)
+        step.kernel = lib.PlannedKernel(prog, self.t.flex) if self.t.plan_only else lib.EwKernel(prog)
+        step.in_views = in_views
+        step.out_views = out_views
+        step.consts = consts
+        step.scratch_bytes = step.kernel.scratch_bytes
+        t._need_scratch(step.scratch_bytes)
+        for v in out_views:
+            if v.buffer not in self.written_buffers:
+                self.written_buffers.append(v.buffer)
+
+
+def _fuse_sigmoid(ops, n_in, consts):
+    """reciprocal(exp(-x) + 1) -> sig(x) inside a fused flex program: the reference's flex
+    transformer does the same rewrite on the graph (FlexFusion,
+    ngraph/transformers/passes/flexfusion.py: sigmoid -> SigmoidAtomicOp).  The intermediate
+    registers stay defined; the compiler drops them when nothing else reads them."""
+    base = n_in + len(consts)
+
+    def producer(r):
+        return ops[r - base] if r >= base else None
+
+    def is_one(r):
+        return n_in <= r < base and consts[r - n_in] == 1.0
+    out = list(ops)
+    for i, (name, a, b) in enumerate(ops):
+        if name != "rcp":
+            continue
+        add = producer(a)
+        if not add or add[0] != "add":
+            continue
+        e = add[1] if is_one(add[2]) else add[2] if is_one(add[1]) else None
+        ex = producer(e) if e is not None else None
+        if not ex or ex[0] != "exp":
+            continue
+        ng_ = producer(ex[1])
+        if not ng_ or ng_[0] != "neg":
+            continue
+        out[i] = ("sig", ng_[1], None)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+class B200Transformer(object):
+    """Transformer for one B200 (ngraph/transformers/gputransform.py:1034-1148 and
+    flexgputransform.py:67-157 are the reference classes whose job this takes)."""
+
+    transformer_name = "b200"
+    default_rtol = 1e-05
+    default_atol = 1e-08
+
+    def __init__(self, device_id=0, flex=False, fixed_point=False, flex_verbose=False,
+                 plan_only=False, fuse=True, **kwargs):
+        """plan_only=True builds and compiles the kernels of every computation (NVRTC needs no
+        GPU) but allocates nothing and cannot run: it exists so that the planning logic can be
+        inspected and tested on a machine without a device."""
+        self.plan_only = bool(plan_only)
+        # fuse=False launches one kernel per op, as the reference does; in flex mode that also
+        # reproduces the reference's per-op re-quantisation of every intermediate tensor
+        self.fuse = bool(fuse)
+        self.flex = bool(flex)
+        self.fixed_point = bool(fixed_point)
+        self.flex_manager = flexmod.FlexManager(fixed_point=fixed_point, verbose=flex_verbose)
+        self.computations = []
+        self._buffers = collections.OrderedDict()   # op -> Buffer
+        self._views = {}
+        self.finalized = False
+        self.closed = False
+        self._scratch_bytes = 0
+        self.kernel_launches = 0
+        if self.plan_only:
+            return
+        try:
+            import torch
+        except ImportError as e:    # pragma: no cover
+            raise UnsupportedTransformerException("the b200 transformer needs torch: %s" % e)
+        if not torch.cuda.is_available():
+            raise UnsupportedTransformerException(
+                "the b200 transformer needs a CUDA device; there is no CPU path")
+        self.torch = torch
+        self.device_id = int(device_id)
+        self.device = torch.device("cuda", self.device_id)
+        torch.cuda.set_device(self.device)
+        self._scratch = None
+        self._status = None
+        self._table = None
+        self._stats = None
+        self.stream = torch.cuda.current_stream(self.device)
+
+    # ---- tolerances (ngraph/transformers/flexgputransform.py:80-103) ----------------------------
+    def get_default_tolerance(self, desired):
+        if self.flex:
+            scale = flexmod.flex16.get_scale(float(np.max(np.abs(desired))))
+            return scale * 8, 1e-2
+        return self.default_atol, self.default_rtol
+
+    # ---- public API ----------------------------------------------------------------------------
+    def computation(self, returns, *parameters):
+        if self.finalized:
+            raise ValueError("Cannot create computations from a finalized transformer")
+        c = Computation(self, returns, parameters)
+        self.computations.append(c)
+        return c
+
+    def initialize(self):
+        if self.finalized:
+            return
+        self.finalized = True
+        for c in self.computations:
+            c.build()
+
+    def close(self):
+        if self.closed:
+            return
+        self.closed = True
+        self._buffers.clear()
+        self._views.clear()
+        self._scratch = self._table = self._stats = self._status = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    # ---- storage -----------------------------------------------------------------------------
+    def _buffer_of(self, op):
+        b = self._buffers.get(op)
+        if b is None:
+            persistent = isinstance(op, AssignableTensorOp)
+            b = Buffer(op.name, op.axes, self.flex, persistent)
+            if persistent:
+                b.init_array = op.initial_array()
+            if self.flex:
+                b.entry = self.flex_manager.make_flex_entry(op.name)
+                b.slot = self.flex_manager.new_slot()
+                b.slot_write = b.slot
+            self._buffers[op] = b
+        return b
+
+    def _view_of(self, op):
+        while isinstance(op, SequentialOp):
+            op = op.value_tensor
+        v = self._views.get(op)
+        if v is not None:
+            return v
+        if isinstance(op, (BroadcastOp, ReorderAxes)):
+            src = self._view_of(op.args[0])
+            v = View(src.buffer, op.axes, [src.stride_of(a) for a in op.axes], src.offset)
+        elif isinstance(op, AssignOp):
+            v = self._view_of(op.args[0])
+        else:
+            v = View.dense(self._buffer_of(op))
+        self._views[op] = v
+        return v
+
+    def _write_slot(self, buf):
+        if buf.persistent and buf.slot_write == buf.slot:
+            buf.slot_write = self.flex_manager.new_slot()
+        if buf.persistent:
+            return buf.slot_write
+        return buf.slot
+
+    def _need_scratch(self, nbytes):
+        self._scratch_bytes = max(self._scratch_bytes, int(nbytes))
+
+    def _allocate(self):
+        if self.plan_only:
+            return
+        torch = self.torch
+        for op, b in self._buffers.items():
+            if b.tensor is None:
+                dt = torch.int16 if b.flex else torch.float32
+                b.tensor = torch.zeros((max(b.size, 1),), dtype=dt, device=self.device)
+        if self._status is None:
+            self._status = torch.zeros((1,), dtype=torch.int32, device=self.device)
+        if self.flex:
+            n = max(self.flex_manager.n_slots + 64, 64)
+            if self._table is None or self._table.shape[0] < n:
+                self._table = torch.zeros((n, 2), dtype=torch.float32, device=self.device)
+                self._stats = torch.zeros((n,), dtype=torch.int32, device=self.device)
+                self._table_host = torch.zeros((n, 2), dtype=torch.float32).pin_memory()
+                self._stats_host = torch.zeros((n,), dtype=torch.int32).pin_memory()
+        for op, b in self._buffers.items():
+            if b.init_array is not None and not getattr(b, "initialised", False):
+                b.initialised = True
+                self._host_to_device(View.dense(b), b.init_array, init=True)
+
+    def _ensure_scratch(self):
+        if self._scratch is None or self._scratch.numel() < self._scratch_bytes:
+            self._scratch = self.torch.empty((max(self._scratch_bytes, 16),), dtype=self.torch.uint8,
+                                             device=self.device)
+
+    # ---- host <-> device -----------------------------------------------------------------------
+    def _host_to_device(self, view, value, init=False):
+        """DeviceTensor.__setitem__ (ngraph/transformers/gputransform.py:806-854); flex:
+        FlexGPUDeviceTensor.__setitem__ (flexgputransform.py:183-208)."""
+        torch = self.torch
+        buf = view.buffer
+        arr = np.asarray(value, dtype=np.float32)
+        if arr.shape not in ((), view.axes.lengths) and arr.size != buf.size:
+            raise ValueError("value shape %s does not match tensor axes %s" % (arr.shape, view.axes))
+        if not view.is_dense():
+            raise ValueError("host writes need a dense tensor")
+        arr = np.ascontiguousarray(np.broadcast_to(arr, view.axes.lengths)
+                                   if arr.shape == () else arr.reshape(view.axes.lengths))
+        src = torch.from_numpy(np.array(arr.reshape(-1), copy=not arr.flags.writeable))
+        if not buf.flex:
+            buf.tensor.copy_(src, non_blocking=False)
+            return
+        if buf.staging is None:
+            buf.staging = torch.empty((max(buf.size, 1),), dtype=torch.float32, device=self.device)
+        buf.staging.copy_(src, non_blocking=False)
+        e = buf.entry
+        raw = lib.raw()
+        if not e.initialized:
+            bits = self._stats[-1:]
+            bits.zero_()
+            lib.check(raw.b2_absmax_bits_f32(buf.staging.data_ptr(), buf.size, bits.data_ptr(),
+                                            self.stream.cuda_stream))
+            maxabs = float(bits.cpu().numpy().view(np.float32)[0])
+            e.initialize_from_range(maxabs)
+        else:
+            e.begin_write()
+        self._set_table_row(buf.slot, e.dec)
+        self._set_table_row(buf.slot_write, e.dec)
+        self._stats[buf.slot:buf.slot + 1].zero_()
+        lib.check(raw.b2_flex_host_quantize(buf.staging.data_ptr(), buf.ptr(), buf.size,
+                                            self._table.data_ptr(), buf.slot,
+                                            self._stats.data_ptr(), self.stream.cuda_stream))
+        self.kernel_launches += 1
+        e.end_write(int(self._stats[buf.slot].item()))
+
+    def _device_to_host(self, view):
+        """DeviceTensor.get (gputransform.py:710-744); flex: int16 * scale
+        (flexgputransform.py:178-181)."""
+        buf = view.buffer
+        flat = buf.tensor
+        if view.is_dense():
+            host = flat.cpu().numpy().reshape(view.axes.lengths)
+        else:
+            t = self.torch.as_strided(flat, view.axes.lengths, view.strides, view.offset)
+            host = t.cpu().numpy()
+        if buf.flex:
+            return host.astype(np.float64) * buf.entry.scale
+        if host.shape == ():
+            return host[()]
+        return host
+
+    # ---- flex bookkeeping ------------------------------------------------------------------------
+    def _set_table_row(self, slot, dec):
+        self._table_host[slot, 0] = 2.0 ** -dec
+        self._table_host[slot, 1] = 2.0 ** dec
+        self._table[slot].copy_(self._table_host[slot])
+
+    def _begin_call(self, comp):
+        self._ensure_scratch()
+        if not self.flex:
+            return
+        self.flex_manager.autoflex_count += 1
+        written = set(id(b) for b in comp.written)
+        for b in self._buffers.values():
+            e = b.entry
+            dec_stored = e.dec
+            # tensors this call overwrites adopt the exponent chosen after their previous write
+            dec_w = e.begin_write() if (id(b) in written and e.initialized) else e.dec
+            self._table_host[b.slot_write, 0] = 2.0 ** -dec_w
+            self._table_host[b.slot_write, 1] = 2.0 ** dec_w
+            if b.slot != b.slot_write:
+                self._table_host[b.slot, 0] = 2.0 ** -dec_stored
+                self._table_host[b.slot, 1] = 2.0 ** dec_stored
+        self._table.copy_(self._table_host, non_blocking=False)
+        self._stats.zero_()
+
+    def _end_call(self, comp):
+        if int(self._status.item()) != 0:
+            self._status.zero_()
+            raise lib.B200Error("a device-side wait ran out during the computation")
+        if not self.flex:
+            return
+        self._stats_host.copy_(self._stats, non_blocking=False)
+        stats = self._stats_host.numpy()
+        for b in comp.written:
+            b.entry.end_write(int(stats[b.slot_write]))
+
+    # ---- launching -------------------------------------------------------------------------------
+    def _launch_step(self, step):
+        if step.kind == "ew":
+            self._launch_ew(step)
+        else:
+            step.launch(self)
+
+    def _launch_ew(self, step):
+        ins = [v.buffer.ptr() + v.offset * (2 if v.buffer.flex else 4) for v in step.in_views]
+        outs = [v.buffer.ptr() + v.offset * (2 if v.buffer.flex else 4) for v in step.out_views]
+        common = dict(consts=step.consts, scratch=self._scratch.data_ptr(),
+                      scratch_bytes=self._scratch.numel(), status=self._status.data_ptr(),
+                      stream=self.stream.cuda_stream)
+        if self.flex:
+            common.update(flex_table=self._table.data_ptr(), flex_stats=self._stats.data_ptr())
+            fresh = [b for b in step.output_buffers() if not b.entry.initialized]
+            if fresh:
+                # first write of these tensors: measure the unsaturated range, then pick exponents
+                step.kernel.launch(ins, outs, probe=True, **common)
+                self.kernel_launches += step.kernel.launches
+                self._stats_host.copy_(self._stats, non_blocking=False)
+                bits = self._stats_host.numpy()
+                for b in fresh:
+                    maxabs = float(bits[b.slot_write:b.slot_write + 1].view(np.float32)[0])
+                    dec = b.entry.initialize_from_range(maxabs)
+                    self._set_table_row(b.slot_write, dec)
+                    self._stats[b.slot_write:b.slot_write + 1].zero_()
+        step.kernel.launch(ins, outs, **common)
+        self.kernel_launches += step.kernel.launches
+
+
+# ---------------------------------------------------------------------------------------------
+# registry / factories (ngraph/transformers/base.py:265-279, 807-847)
+# ---------------------------------------------------------------------------------------------
+_transformers = {B200Transformer.transformer_name: B200Transformer}
+_factory = None
+
+
+def transformer_choices():
+    return sorted(_transformers.keys())
+
+
+def allocate_transformer(name, **kwargs):
+    try:
+        cls = _transformers[name]
+    except KeyError:
+        raise ValueError("The given transformer name ({}) is invalid/unsupported.".format(name))
+    return cls(**kwargs)
+
+
+def make_transformer_factory(name, **kwargs):
+    def factory():
+        return allocate_transformer(name, **kwargs)
+    factory.name = name
+    return factory
+
+
+def set_transformer_factory(factory):
+    global _factory
+    _factory = factory
+
+
+def make_transformer():
+    f = _factory or make_transformer_factory("b200")
+    return f()

@@ -1,0 +1,43 @@
+"""Generates tests/golden/fixtures/<case>.npz by running each case of cases.py on the
+reference's own CPU transformer.  Run in a container that has the reference tree:
+
+    python tests/golden/make_fixtures.py /path/to/ngraph-python
+
+The reference is imported unmodified through the small compatibility shims in ref_shims/.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "ref_shims"))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+
+def main(ref_root, only=None):
+    import ref_bootstrap
+    ref_bootstrap.install(ref_root)
+    import ngraph as ng
+    import ngraph.transformers as ngt
+    from tests.golden import cases
+    out_dir = os.path.join(HERE, "fixtures")
+    os.makedirs(out_dir, exist_ok=True)
+    for name, build in sorted(cases.CASES.items()):
+        if only and name not in only:
+            continue
+        outs, params, vals = build(ng)
+        t = ngt.make_transformer_factory("cpu")()
+        comp = t.computation(outs, *params)
+        data = {}      # inputs are not stored: cases.py regenerates them from its seeds
+        for rep in range(cases.REPEAT.get(name, 1)):
+            res = comp(*vals)
+            for k, r in enumerate(res):
+                data["out%d_%d" % (rep, k)] = np.array(r, copy=True)
+        t.close()
+        np.savez_compressed(os.path.join(out_dir, name + ".npz"), **data)
+        print(name, {k: v.shape for k, v in data.items() if k.startswith("out")})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", set(sys.argv[2:]))

