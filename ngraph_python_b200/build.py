@@ -1,4 +1,4 @@
-"""Builds libb200ng.so (sm_100a) in-tree with nvcc.  `python -m ngraph_python_b200.build`."""
+"""Builds libb200ng.so (sm_100a) in-tree with nvcc.  `python ngraph_python_b200/build.py`."""
 import os
 import subprocess
 import sys
