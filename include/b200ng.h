@@ -126,6 +126,19 @@ int b2_ew_scratch_bytes(const b2_ew_kernel* k, size_t* bytes);
 int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const* out, const float* consts,
                  const b2_flex_scale* flex_table, int32_t* flex_stats, void* scratch,
                  size_t scratch_bytes, int32_t* status, int probe, void* stream);
+/* The same launch for callers that cannot allocate (no counterpart in the reference, which
+ * always allocates through pycuda).  Meant for hosts that gave the whole device to their own
+ * arena at start-up, and for execution loops that must never reach cudaMalloc because it
+ * synchronises the device.  Scratch for split reductions comes from an array inside the library
+ * (B2_EW_BUILTIN_SCRATCH_BYTES per device, held until the process exits); a launch that needs more
+ * fails with B2_ERR_INVALID.  Calls no cudaMalloc/cudaFree and never compiles or loads a kernel:
+ * the variant must already exist (b2_ew_compile builds the one for 16-byte-aligned pointers,
+ * probe == 0).  The first call on a device resolves the array's address -- make it before any
+ * stream capture.  All calls share the array: launches that overlap on the GPU race. */
+#define B2_EW_BUILTIN_SCRATCH_BYTES (1 << 20)
+int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* in, void* const* out,
+                                 const float* consts, const b2_flex_scale* flex_table,
+                                 int32_t* flex_stats, int32_t* status, int probe, void* stream);
 /* Generated CUDA source of a compiled kernel (for inspection / tests). */
 const char* b2_ew_source(const b2_ew_kernel* k);
 /* Number of kernel launches one b2_ew_launch issues (1, or 2 for split reductions). */

@@ -1068,3 +1068,121 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
     }
     return B2_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Launch with the library's own scratch: an entry point that allocates nothing.
+//
+// Who needs it: a host that cannot (or must not) call cudaMalloc when it discovers that a kernel
+// wants scratch.  Two such hosts exist for this library: an embedding runtime that took the whole
+// device for its own arena when it started, so that a later cudaMalloc fails or has to wait for
+// that arena to give memory back; and a steady-state execution loop that was promised "no
+// allocator calls", because cudaMalloc/cudaFree synchronise the device and would stall every
+// stream in flight.  The only kernels here that use scratch are the split row reductions (a few
+// very long rows shared by many CTAs, fp32 partials combined by b2_ew_finalize); this variant
+// gives them a fixed array that lives in the library's device image instead of a caller buffer.
+//
+// Limits and rules:
+//   * the array is B2_EW_BUILTIN_SCRATCH_BYTES (1 MiB) per device, held by every GPU that loads
+//     the library until the process exits; a launch that needs more is refused with an error;
+//   * the first call on a device looks the array's device address up (cudaGetSymbolAddress, with
+//     that device current) and remembers it; make that first call outside any stream capture;
+//   * all calls share the array and it keeps whatever the previous call left.  The split
+//     reduction writes every partial before b2_ew_finalize reads it, so nothing has to be cleared
+//     first -- but two such launches that overlap on the GPU (different streams) would overwrite
+//     each other's partials: run them on one stream, or serialise them;
+//   * no kernel is compiled or loaded here: the variant (aligned / unaligned pointers, probe) must
+//     already exist, which b2_ew_compile guarantees for aligned pointers and probe == 0.
+// ------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_builtin_scratch[B2_EW_BUILTIN_SCRATCH_BYTES];
+
+namespace {
+const int kMaxDevices = 64;
+void* g_builtin_scratch_ptr[kMaxDevices] = {nullptr};
+std::mutex g_builtin_mutex;
+
+// In host code `g_builtin_scratch` is only a handle for the symbol, not a device address: the
+// address a kernel can use has to be asked for, per device.
+int builtin_scratch_for_current_device(void** out) {
+    int dev = -1;
+    B2_CUDA(cudaGetDevice(&dev));
+    B2_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_builtin_mutex);
+    if (!g_builtin_scratch_ptr[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_builtin_scratch);
+        if (e != cudaSuccess || !p)
+            return b2::fail(B2_ERR_CUDA, "cudaGetSymbolAddress(built-in scratch) failed: %s",
+                            cudaGetErrorString(e));
+        g_builtin_scratch_ptr[dev] = p;
+    }
+    *out = g_builtin_scratch_ptr[dev];
+    return B2_OK;
+}
+}  // namespace
+
+extern "C" int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* in,
+                                            void* const* out, const float* consts,
+                                            const b2_flex_scale* flex_table, int32_t* flex_stats,
+                                            int32_t* status, int probe, void* stream) {
+    B2_REQUIRE(k && (in || k->prog.n_in == 0) && out, "null argument");
+    const b2_ew_program& p = k->prog;
+    const int nres = p.n_out + p.n_red;
+    bool any_flex = false;
+    int vec = k->can_vec ? 1 : 0;
+    for (int i = 0; i < p.n_in; ++i) {
+        B2_REQUIRE(in[i], "input %d is null", i);
+        any_flex |= p.in[i].dtype == B2_FLEX16;
+        if (vec && p.in[i].sc == 1 && !aligned16(in[i])) vec = 0;
+    }
+    for (int q = 0; q < nres; ++q) {
+        B2_REQUIRE(out[q], "result %d is null", q);
+        any_flex |= p.out[q].t.dtype == B2_FLEX16;
+        if (vec && q < p.n_out && !aligned16(out[q])) vec = 0;
+    }
+    if (any_flex) B2_REQUIRE(flex_table && flex_stats, "flex tensors need a scale table and stats");
+    B2_REQUIRE(p.n_const == 0 || consts, "constants missing");
+    probe = probe ? 1 : 0;
+    Module* m = k->mod[vec][probe];
+    B2_REQUIRE(m != nullptr,
+               "this kernel variant (vector=%d, probe=%d) has not been compiled yet; the "
+               "no-allocation launch never compiles or loads code -- run b2_ew_launch once with "
+               "the same kind of pointers first", vec, probe);
+    const Plan& pl = k->plan[vec];
+    const size_t need = pl.nsplit > 1
+        ? (size_t)pl.nsplit * (size_t)(p.A * p.B) * (size_t)p.n_red * sizeof(float) : 0;
+    B2_REQUIRE(need <= (size_t)B2_EW_BUILTIN_SCRATCH_BYTES,
+               "this launch needs %zu bytes of scratch but the built-in scratch holds %zu; use "
+               "b2_ew_launch with a caller buffer", need, (size_t)B2_EW_BUILTIN_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    int rc = builtin_scratch_for_current_device(&scratch);
+    if (rc) return rc;
+    EwArgs a;
+    memset(&a, 0, sizeof(a));
+    a.A = p.A; a.B = p.B; a.C = p.C;
+    for (int i = 0; i < p.n_in; ++i) {
+        a.in[i] = in[i];
+        a.in_sa[i] = p.in[i].sa; a.in_sb[i] = p.in[i].sb; a.in_sc[i] = p.in[i].sc;
+        a.in_slot[i] = p.in[i].flex_slot;
+    }
+    for (int q = 0; q < nres; ++q) {
+        a.out[q] = out[q];
+        a.out_sa[q] = p.out[q].t.sa; a.out_sb[q] = p.out[q].t.sb; a.out_sc[q] = p.out[q].t.sc;
+        a.out_slot[q] = p.out[q].t.flex_slot;
+    }
+    for (int i = 0; i < p.n_const; ++i) a.consts[i] = consts[i];
+    a.flex_table = flex_table;
+    a.flex_stats = flex_stats;
+    a.scratch = static_cast<float*>(scratch);
+    a.status = status;
+    a.nsplit = pl.nsplit;
+    void* params[] = {&a};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t dyn = pl.staged ? (size_t)pl.stages * pl.stage_bytes : 0;
+    B2_CUDA(cudaLaunchKernel((const void*)m->main, pl.grid, dim3(kThreads), params, dyn, st));
+    if (pl.nsplit > 1) {
+        const long long rows = p.A * p.B;
+        dim3 g((unsigned)((rows + kThreads - 1) / kThreads));
+        B2_CUDA(cudaLaunchKernel((const void*)m->finalize, g, dim3(kThreads), params, 0, st));
+    }
+    return B2_OK;
+}

@@ -57,7 +57,7 @@ class FlexScale(C.Structure):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            "%s is missing: build it with `python -m ngraph_python_b200.build` "
+            "%s is missing: build it with `python ngraph_python_b200/build.py` "
             "(needs nvcc; there is no CPU fallback)" % LIB_PATH)
     lib = C.CDLL(LIB_PATH)
     vp, i32, i64, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
@@ -71,6 +71,8 @@ def _load():
         "b2_ew_scratch_bytes": (C.c_int, [vp, C.POINTER(sz)]),
         "b2_ew_launch": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(C.c_float), vp, vp,
                                    vp, sz, vp, C.c_int, vp]),
+        "b2_ew_launch_builtin_scratch": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp),
+                                                   C.POINTER(C.c_float), vp, vp, vp, C.c_int, vp]),
         "b2_ew_source": (C.c_char_p, [vp]),
         "b2_ew_launch_count": (C.c_int, [vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
@@ -174,6 +176,17 @@ class EwKernel(object):
             self._consts[i] = c
         check(_lib.b2_ew_launch(self.handle, ins, outs, self._consts, flex_table, flex_stats,
                                 scratch, scratch_bytes, status, int(probe), stream))
+
+    def launch_builtin_scratch(self, in_ptrs, out_ptrs, consts=(), flex_table=0, flex_stats=0,
+                               status=0, probe=False, stream=0):
+        """Same launch through the entry point that allocates nothing: split reductions use the
+        1 MiB scratch array that lives inside the library instead of a caller buffer."""
+        ins = (C.c_void_p * max(1, len(in_ptrs)))(*in_ptrs)
+        outs = (C.c_void_p * max(1, len(out_ptrs)))(*out_ptrs)
+        for i, c in enumerate(consts):
+            self._consts[i] = c
+        check(_lib.b2_ew_launch_builtin_scratch(self.handle, ins, outs, self._consts, flex_table,
+                                                flex_stats, status, int(probe), stream))
 
 
 class PlannedKernel(object):
