@@ -38,7 +38,7 @@ C2_ROWS, C2_COLS = 8192, 16384
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per full-size launch, scaled from the ncu capture
 # of a quarter-size launch (2048 rows): see profiles/ew_c2_flex16.md and profiles/ew_c2_fp32.md
-NCU_TRAFFIC_BYTES = {"c2_flex16": None, "c2_fp32": None}
+NCU_TRAFFIC_BYTES = {"c2_flex16": 4 * (268457728 + 39549952), "c2_fp32": 4 * (536940544 + 107399680)}
 
 
 def peaks():
