@@ -162,6 +162,32 @@ int b2_flex_dequantize(const int16_t* src, float* dst, int64_t n, const b2_flex_
  * for data arriving from the host. */
 int b2_absmax_bits_f32(const float* src, int64_t n, int32_t* out, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Dense GEMM on tcgen05 tensor cores: C[M,N] = op(A)[M,K] * op(B)[K,N], C row-major (ldc).
+ * Replaces: GEMMKernel and the sgemm / fgemm SASS kernels (ngraph/transformers/gpu/gemm.py:26-263,
+ * gpu/kernels/sass/fgemm_common_128x128.sass).  op() is given by element strides, as the
+ * reference derives nn/nt/tn from strides (gemm.py:95-110): element (m,k) of op(A) is
+ * A[m*a_row_stride + k*a_k_stride], element (k,n) of op(B) is B[k*b_k_stride + n*b_col_stride];
+ * one stride of each pair must be 1.  `scratch` (1024-byte aligned, b2_gemm_scratch_bytes) holds
+ * the K-major operand planes the kernel streams with TMA.
+ * ------------------------------------------------------------------------------------------ */
+int b2_gemm_scratch_bytes(int32_t flex, int32_t M, int32_t N, int32_t K, size_t* bytes);
+/* fp32 via 3xTF32 (relative error ~2^-21). */
+int b2_gemm_f32(const float* A, int64_t a_row_stride, int64_t a_k_stride, const float* B,
+                int64_t b_k_stride, int64_t b_col_stride, float* C, int64_t ldc, int32_t M,
+                int32_t N, int32_t K, void* scratch, size_t scratch_bytes, int32_t* status,
+                void* stream);
+/* flex16: exact integer products (int8 hi/lo split, int32 accumulation), output rescaled by
+ * 2^(decC - decA - decB) with round-to-nearest-even, saturated to int16; stats[slotC] receives
+ * max |mantissa| (fgemm epilogue, fgemm_common_128x128.sass:29-97,331-420).  K <= 32768.
+ * probe != 0: nothing is stored; *probe_out receives max |exact integer sum| (the caller
+ * multiplies by 2^-(decA+decB) to get the unsaturated range of the result). */
+int b2_gemm_flex16(const int16_t* A, int64_t a_row_stride, int64_t a_k_stride, const int16_t* B,
+                   int64_t b_k_stride, int64_t b_col_stride, int16_t* C, int64_t ldc, int32_t M,
+                   int32_t N, int32_t K, const b2_flex_scale* table, int32_t slotA, int32_t slotB,
+                   int32_t slotC, int32_t* stats, void* scratch, size_t scratch_bytes,
+                   uint64_t* probe_out, int32_t* status, int32_t probe, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

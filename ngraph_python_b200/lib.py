@@ -75,6 +75,11 @@ def _load():
                                                    C.POINTER(C.c_float), vp, vp, vp, C.c_int, vp]),
         "b2_ew_source": (C.c_char_p, [vp]),
         "b2_ew_launch_count": (C.c_int, [vp]),
+        "b2_gemm_scratch_bytes": (C.c_int, [i32, i32, i32, i32, C.POINTER(sz)]),
+        "b2_gemm_f32": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, vp, sz, vp,
+                                  vp]),
+        "b2_gemm_flex16": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, vp, i32,
+                                     i32, i32, vp, vp, sz, vp, vp, i32, vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),
@@ -202,3 +207,9 @@ class PlannedKernel(object):
 
     def source(self):
         return self._source
+
+
+def gemm_scratch_bytes(flex, M, N, K):
+    n = C.c_size_t()
+    check(_lib.b2_gemm_scratch_bytes(int(bool(flex)), M, N, K, C.byref(n)))
+    return n.value

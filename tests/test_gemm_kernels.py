@@ -1,0 +1,112 @@
+"""GPU parity of the tcgen05 GEMM kernels through the C ABI.
+
+flex16: the exact integer product sum is computed by the oracle in int64; the kernel's mantissas
+must be within +-1 of round(sum * 2^(decC-decA-decB)) (the bar for flex contractions), and are in
+fact expected to be identical because both sides are exact.  fp32: rtol 1e-4 / atol 1e-5 scaled
+by sqrt(K) against a float64 product."""
+import numpy as np
+import pytest
+
+from oracle import flex_oracle as fx
+
+pytestmark = pytest.mark.gpu
+
+
+def _scratch(torch, nbytes):
+    t = torch.empty((nbytes + 1024,), dtype=torch.uint8, device="cuda")
+    off = (-t.data_ptr()) % 1024
+    return t, t.data_ptr() + off
+
+
+SHAPES = [(128, 128, 128), (256, 384, 512), (100, 72, 200), (1, 10, 64), (512, 128, 1024),
+          (130, 257, 96)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+def test_gemm_f32(M, N, K, layout):
+    import torch
+    from ngraph_python_b200 import lib
+    rng = np.random.RandomState(M + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    a_store = A.T.copy() if layout == "tn" else A
+    b_store = B.T.copy() if layout == "nt" else B
+    a_str = (1, M) if layout == "tn" else (K, 1)
+    b_str = (1, K) if layout == "nt" else (N, 1)
+    dA, dB = torch.from_numpy(a_store).cuda(), torch.from_numpy(b_store).cuda()
+    dC = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    nbytes = lib.gemm_scratch_bytes(False, M, N, K)
+    keep, sp = _scratch(torch, nbytes)
+    lib.check(lib.raw().b2_gemm_f32(dA.data_ptr(), a_str[0], a_str[1], dB.data_ptr(), b_str[0],
+                                    b_str[1], dC.data_ptr(), N, M, N, K, sp, nbytes,
+                                    status.data_ptr(), 0))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    expect = A.astype(np.float64) @ B.astype(np.float64)
+    np.testing.assert_allclose(dC.cpu().numpy(), expect, rtol=1e-4, atol=1e-5 * np.sqrt(K) * 4)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+def test_gemm_flex16(M, N, K, layout):
+    import torch
+    from ngraph_python_b200 import lib
+    rng = np.random.RandomState(M * 3 + N + K)
+    A = rng.randint(-32767, 32768, (M, K)).astype(np.int16)
+    B = rng.randint(-32767, 32768, (K, N)).astype(np.int16)
+    A[0, 0] = -32768
+    B[0, 0] = -32768
+    dec_a, dec_b = 15, 12
+    exact = A.astype(np.int64) @ B.astype(np.int64)
+    real_max = float(np.abs(exact).max()) * 2.0 ** -(dec_a + dec_b)
+    dec_c = fx.fit_dec(real_max)
+    a_store = A.T.copy() if layout == "tn" else A
+    b_store = B.T.copy() if layout == "nt" else B
+    a_str = (1, M) if layout == "tn" else (K, 1)
+    b_str = (1, K) if layout == "nt" else (N, 1)
+    dA, dB = torch.from_numpy(a_store).cuda(), torch.from_numpy(b_store).cuda()
+    dC = torch.zeros((M, N), dtype=torch.int16, device="cuda")
+    table = torch.tensor([[2.0 ** -dec_a, 2.0 ** dec_a], [2.0 ** -dec_b, 2.0 ** dec_b],
+                          [2.0 ** -dec_c, 2.0 ** dec_c]], dtype=torch.float32, device="cuda")
+    stats = torch.zeros((3,), dtype=torch.int32, device="cuda")
+    probe = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    nbytes = lib.gemm_scratch_bytes(True, M, N, K)
+    keep, sp = _scratch(torch, nbytes)
+
+    def call(probe_flag):
+        lib.check(lib.raw().b2_gemm_flex16(
+            dA.data_ptr(), a_str[0], a_str[1], dB.data_ptr(), b_str[0], b_str[1], dC.data_ptr(), N,
+            M, N, K, table.data_ptr(), 0, 1, 2, stats.data_ptr(), sp, nbytes, probe.data_ptr(),
+            status.data_ptr(), probe_flag, 0))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+    call(1)
+    assert int(probe.item()) == int(np.abs(exact).max())
+    call(0)
+    sh = dec_a + dec_b - dec_c
+    # round-to-nearest-even of exact / 2^sh in exact integer arithmetic
+    if sh > 0:
+        half = 1 << (sh - 1)
+        expect = (exact + half - 1 + ((exact >> sh) & 1)) >> sh
+    else:
+        expect = exact << (-sh)
+    expect = np.clip(expect, -32768, 32767)
+    got = dC.cpu().numpy().astype(np.int64)
+    assert np.array_equal(got, expect)
+    assert int(stats[2].item()) == int(np.abs(got).max())
+    # and with a deliberately too-fine output exponent everything saturates cleanly
+    table[2, 0] = 2.0 ** -(dec_c + 6)
+    table[2, 1] = 2.0 ** (dec_c + 6)
+    stats.zero_()
+    call(0)
+    sh2 = sh - 6
+    if sh2 > 0:
+        half = 1 << (sh2 - 1)
+        e2 = (exact + half - 1 + ((exact >> sh2) & 1)) >> sh2
+    else:
+        e2 = exact << (-sh2)
+    e2 = np.clip(e2, -32768, 32767)
+    assert np.array_equal(dC.cpu().numpy().astype(np.int64), e2)
