@@ -36,14 +36,19 @@
 
 namespace {
 
-constexpr int kBlockM = 128, kBlockN = 128;
+constexpr int kBlockM = 128;          // UMMA M; the N tile (16/32/64/128) is a template parameter
 constexpr int kKBytes = 128;            // bytes of K per k-block row: one 128B swizzle atom
 constexpr int kPlaneBytes = 128 * kKBytes;   // 16 KB: 128 rows x 128 B
-constexpr int kStageBytes = 4 * kPlaneBytes; // A0 A1 B0 B1
+__host__ __device__ constexpr int stage_bytes(int bn) { return 2 * kPlaneBytes + 2 * bn * kKBytes; }  // A0 A1 B0 B1
 constexpr int kStages = 3;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+__host__ __device__ constexpr int smem_bytes(int bn) { return kStages * stage_bytes(bn) + 1024 /*alignment*/ + 256 /*barriers*/; }
+// tensor-memory columns: a power of two >= 32 that holds the accumulators (3 x BN or BN)
+__host__ __device__ constexpr int tmem_cols(int mode, int bn) {
+    int need = (mode == 0 ? 3 : 1) * bn, c = 32;
+    while (c < need) c *= 2;
+    return c;
+}
 
 enum { MODE_FLEX16 = 0, MODE_F32X3 = 1 };
 
@@ -140,8 +145,9 @@ __device__ __forceinline__ unsigned long long make_smem_desc(const void* p) {
 }
 // Instruction descriptor: D format [4,6), A format [7,10), B format [10,13), K-major both,
 // N>>3 [17,23), M>>4 [24,29).
-__host__ __device__ constexpr unsigned make_idesc(unsigned dfmt, unsigned afmt, unsigned bfmt) {
-    return (dfmt << 4) | (afmt << 7) | (bfmt << 10) | ((unsigned)(kBlockN >> 3) << 17) |
+__host__ __device__ constexpr unsigned make_idesc(unsigned dfmt, unsigned afmt, unsigned bfmt,
+                                                  unsigned bn) {
+    return (dfmt << 4) | (afmt << 7) | (bfmt << 10) | ((bn >> 3) << 17) |
            ((unsigned)(kBlockM >> 4) << 24);
 }
 
@@ -155,6 +161,7 @@ struct GemmParams {
     unsigned long long* probe_out;   // probe: max |exact integer product sum|
     int* status;
     int probe;
+    int c_colmajor;                  // 0: C[row*ldc + col]; 1: C[col*ldc + row]
 };
 
 // round-to-nearest-even of v / 2^sh (sh > 0), or v * 2^-sh (sh <= 0), saturated to int16
@@ -177,13 +184,16 @@ __device__ __forceinline__ int rescale_i64(long long v, int sh) {
     return (int)q;
 }
 
-template <int MODE>
+template <int MODE, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
             const __grid_constant__ CUtensorMap mapB0, const __grid_constant__ CUtensorMap mapB1,
             const GemmParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int kStageBytes = stage_bytes(BN);
+    constexpr int kBPlane = BN * kKBytes;
+    constexpr int kTmemCols = tmem_cols(MODE, BN);
     unsigned long long* full_bar = (unsigned long long*)(smem + kStages * kStageBytes);
     unsigned long long* empty_bar = full_bar + kStages;
     unsigned long long* tmem_full = empty_bar + kStages;
@@ -191,7 +201,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
     int* fail_flag = (int*)(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * kBlockM, n0 = blockIdx.x * kBlockN;
+    const int m0 = blockIdx.y * kBlockM, n0 = blockIdx.x * BN;
     const int kElems = MODE == MODE_FLEX16 ? kKBytes : kKBytes / 4;   // elements of K per k-block
 
     if (threadIdx.x == 0) {
@@ -220,15 +230,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 tma_load_2d(st + 0 * kPlaneBytes, &mapA0, kx, m0, &full_bar[s]);
                 tma_load_2d(st + 1 * kPlaneBytes, &mapA1, kx, m0, &full_bar[s]);
                 tma_load_2d(st + 2 * kPlaneBytes, &mapB0, kx, n0, &full_bar[s]);
-                tma_load_2d(st + 3 * kPlaneBytes, &mapB1, kx, n0, &full_bar[s]);
+                tma_load_2d(st + 2 * kPlaneBytes + kBPlane, &mapB1, kx, n0, &full_bar[s]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // flex16: planes are (hi = signed, lo = unsigned) bytes; accumulators HH | X | LL
-            const unsigned id_ss = make_idesc(2, 1, 1), id_su = make_idesc(2, 1, 0),
-                           id_us = make_idesc(2, 0, 1), id_uu = make_idesc(2, 0, 0);
-            const unsigned id_tf = make_idesc(1, 2, 2);
+            const unsigned id_ss = make_idesc(2, 1, 1, BN), id_su = make_idesc(2, 1, 0, BN),
+                           id_us = make_idesc(2, 0, 1, BN), id_uu = make_idesc(2, 0, 0, BN);
+            const unsigned id_tf = make_idesc(1, 2, 2, BN);
             bool ok = true;
             for (int kb = 0; kb < p.num_kb && ok; ++kb) {
                 const int s = kb % kStages;
@@ -238,16 +248,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 const unsigned long long dA0 = make_smem_desc(st + 0 * kPlaneBytes);
                 const unsigned long long dA1 = make_smem_desc(st + 1 * kPlaneBytes);
                 const unsigned long long dB0 = make_smem_desc(st + 2 * kPlaneBytes);
-                const unsigned long long dB1 = make_smem_desc(st + 3 * kPlaneBytes);
+                const unsigned long long dB1 = make_smem_desc(st + 2 * kPlaneBytes + kBPlane);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * 32) >> 4);
                     const unsigned acc = (kb > 0 || k > 0) ? 1u : 0u;
                     if (MODE == MODE_FLEX16) {
                         tc_mma<MODE>(tmem_base + 0, dA0 + adv, dB0 + adv, id_ss, acc);      // HH
-                        tc_mma<MODE>(tmem_base + 128, dA0 + adv, dB1 + adv, id_su, acc);    // X += ah*bl
-                        tc_mma<MODE>(tmem_base + 128, dA1 + adv, dB0 + adv, id_us, 1u);     // X += al*bh
-                        tc_mma<MODE>(tmem_base + 256, dA1 + adv, dB1 + adv, id_uu, acc);    // LL
+                        tc_mma<MODE>(tmem_base + BN, dA0 + adv, dB1 + adv, id_su, acc);     // X += ah*bl
+                        tc_mma<MODE>(tmem_base + BN, dA1 + adv, dB0 + adv, id_us, 1u);      // X += al*bh
+                        tc_mma<MODE>(tmem_base + 2 * BN, dA1 + adv, dB1 + adv, id_uu, acc); // LL
                     } else {
                         tc_mma<MODE>(tmem_base, dA0 + adv, dB0 + adv, id_tf, acc);          // hi*hi
                         tc_mma<MODE>(tmem_base, dA0 + adv, dB1 + adv, id_tf, 1u);           // hi*lo
@@ -273,11 +283,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             int stat = 0;
             unsigned long long pmax = 0;
             short* crow = (short*)p.C + (long long)row * p.ldc;
-            for (int c0 = 0; c0 < kBlockN; c0 += 16) {
+            for (int c0 = 0; c0 < BN; c0 += 16) {
                 unsigned hh[16], xx[16], ll[16];
                 tmem_ld16(lane_addr + c0, hh);
-                tmem_ld16(lane_addr + 128 + c0, xx);
-                tmem_ld16(lane_addr + 256 + c0, ll);
+                tmem_ld16(lane_addr + BN + c0, xx);
+                tmem_ld16(lane_addr + 2 * BN + c0, ll);
                 tmem_ld_wait();
                 if (!ok || row >= p.M) continue;
                 int q[16];
@@ -296,7 +306,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 }
                 if (!p.probe) {
                     const int col = n0 + c0;
-                    if (col + 16 <= p.N && ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+                    if (p.c_colmajor) {
+                        // lanes hold consecutive rows: each column is a coalesced 64-byte store
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (col + j < p.N)
+                                ((short*)p.C)[(long long)(col + j) * p.ldc + row] = (short)q[j];
+                    } else if (col + 16 <= p.N && ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0)) {
                         int4 w0, w1;
                         w0.x = (q[0] & 0xffff) | (q[1] << 16); w0.y = (q[2] & 0xffff) | (q[3] << 16);
                         w0.z = (q[4] & 0xffff) | (q[5] << 16); w0.w = (q[6] & 0xffff) | (q[7] << 16);
@@ -326,13 +342,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             }
         } else {
             float* crow = (float*)p.C + (long long)row * p.ldc;
-            for (int c0 = 0; c0 < kBlockN; c0 += 16) {
+            for (int c0 = 0; c0 < BN; c0 += 16) {
                 unsigned acc[16];
                 tmem_ld16(lane_addr + c0, acc);
                 tmem_ld_wait();
                 if (!ok || row >= p.M) continue;
                 const int col = n0 + c0;
-                if (col + 16 <= p.N && ((p.ldc & 3) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+                if (p.c_colmajor) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (col + j < p.N)
+                            ((float*)p.C)[(long long)(col + j) * p.ldc + row] = __uint_as_float(acc[j]);
+                } else if (col + 16 <= p.N && ((p.ldc & 3) == 0) && (((uintptr_t)p.C & 15) == 0)) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
                         *reinterpret_cast<float4*>(crow + col + j) =
@@ -418,10 +439,10 @@ int get_encode() {
 }
 
 // plane: [rows_p][kp] elements of `esize` bytes, K contiguous; box = 128 rows x 128 bytes
-int make_map(CUtensorMap* map, void* base, int rows_p, int kp, int esize) {
+int make_map(CUtensorMap* map, void* base, int rows_p, int kp, int esize, int box_rows) {
     cuuint64_t dims[2] = {(cuuint64_t)kp, (cuuint64_t)rows_p};
     cuuint64_t strides[1] = {(cuuint64_t)kp * esize};
-    cuuint32_t box[2] = {(cuuint32_t)(kKBytes / esize), 128};
+    cuuint32_t box[2] = {(cuuint32_t)(kKBytes / esize), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(map, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                           2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -433,16 +454,58 @@ int make_map(CUtensorMap* map, void* base, int rows_p, int kp, int esize) {
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-struct Shapes { int Mp, Np, Kp, esize; size_t bytes; };
+struct Shapes { int Mp, Np, Kp, esize, bn; size_t bytes, a_bytes; };
+
+inline int pick_bn(int N) { return N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : 128; }
 
 Shapes shapes_for(int mode, int M, int N, int K) {
     Shapes s;
     s.esize = mode == MODE_FLEX16 ? 1 : 4;
+    s.bn = pick_bn(N);
     s.Mp = round_up(M, kBlockM);
-    s.Np = round_up(N, kBlockN);
+    s.Np = round_up(N, s.bn);
     s.Kp = round_up(K, kKBytes / s.esize);
-    s.bytes = 2ull * ((size_t)s.Mp + s.Np) * s.Kp * s.esize;
+    s.a_bytes = 2ull * (size_t)s.Mp * s.Kp * s.esize;
+    s.bytes = s.a_bytes + 2ull * (size_t)s.Np * s.Kp * s.esize;
     return s;
+}
+
+template <int MODE, int BN>
+int launch_tile(const CUtensorMap& mA0, const CUtensorMap& mA1, const CUtensorMap& mB0,
+                const CUtensorMap& mB1, const GemmParams& p, const Shapes& s, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        B2_CUDA(cudaFuncSetAttribute(gemm_kernel<MODE, BN>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
+        attr_set = true;
+    }
+    dim3 grid(s.Np / BN, s.Mp / kBlockM);
+    gemm_kernel<MODE, BN><<<grid, kThreads, smem_bytes(BN), st>>>(mA0, mA1, mB0, mB1, p);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+// Launches the tile kernel on operand planes that are already in scratch:
+// A planes at `base`, B planes behind them.
+template <int MODE>
+int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStream_t st) {
+    int rc = get_encode();
+    if (rc) return rc;
+    const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
+    void* A0 = base; void* A1 = base + a_plane;
+    void* B0 = base + 2 * a_plane; void* B1 = base + 2 * a_plane + b_plane;
+    CUtensorMap mA0, mA1, mB0, mB1;
+    if ((rc = make_map(&mA0, A0, s.Mp, s.Kp, s.esize, 128))) return rc;
+    if ((rc = make_map(&mA1, A1, s.Mp, s.Kp, s.esize, 128))) return rc;
+    if ((rc = make_map(&mB0, B0, s.Np, s.Kp, s.esize, s.bn))) return rc;
+    if ((rc = make_map(&mB1, B1, s.Np, s.Kp, s.esize, s.bn))) return rc;
+    p.num_kb = s.Kp / (kKBytes / s.esize);
+    switch (s.bn) {
+        case 16: return launch_tile<MODE, 16>(mA0, mA1, mB0, mB1, p, s, st);
+        case 32: return launch_tile<MODE, 32>(mA0, mA1, mB0, mB1, p, s, st);
+        case 64: return launch_tile<MODE, 64>(mA0, mA1, mB0, mB1, p, s, st);
+        default: return launch_tile<MODE, 128>(mA0, mA1, mB0, mB1, p, s, st);
+    }
 }
 
 template <typename T, int MODE>
@@ -454,8 +517,6 @@ int run_gemm(const T* A, long long a_rs, long long a_cs, const T* B, long long b
     B2_REQUIRE(a_rs == 1 || a_cs == 1, "A must be contiguous along M or K");
     B2_REQUIRE(b_ks == 1 || b_ns == 1, "B must be contiguous along K or N");
     if (MODE == MODE_FLEX16) B2_REQUIRE(K <= 32768, "flex16 GEMM keeps exact int32 sums for K <= 32768");
-    int rc = get_encode();
-    if (rc) return rc;
     const Shapes s = shapes_for(MODE, M, N, K);
     B2_REQUIRE(scratch && scratch_bytes >= s.bytes && ((uintptr_t)scratch & 1023) == 0,
                "GEMM needs %zu bytes of 1024-byte aligned scratch, got %zu", s.bytes, scratch_bytes);
@@ -471,25 +532,12 @@ int run_gemm(const T* A, long long a_rs, long long a_cs, const T* B, long long b
         split_planes_kernel<T, MODE><<<g2, 256, 0, st>>>(B, b_ns, b_ks, N, K, s.Np, s.Kp, B0, B1);
         B2_CUDA(cudaGetLastError());
     }
-    CUtensorMap mA0, mA1, mB0, mB1;
-    if ((rc = make_map(&mA0, A0, s.Mp, s.Kp, s.esize))) return rc;
-    if ((rc = make_map(&mA1, A1, s.Mp, s.Kp, s.esize))) return rc;
-    if ((rc = make_map(&mB0, B0, s.Np, s.Kp, s.esize))) return rc;
-    if ((rc = make_map(&mB1, B1, s.Np, s.Kp, s.esize))) return rc;
     GemmParams p;
-    p.M = M; p.N = N; p.num_kb = s.Kp / (kKBytes / s.esize);
+    p.M = M; p.N = N; p.num_kb = 0;
     p.ldc = ldc; p.C = C; p.table = table; p.slotA = slotA; p.slotB = slotB; p.slotC = slotC;
     p.stats = stats; p.probe_out = probe_out; p.status = status; p.probe = probe;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[MODE]) {
-        B2_CUDA(cudaFuncSetAttribute(gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kSmemBytes));
-        attr_set[MODE] = true;
-    }
-    dim3 grid(s.Np / kBlockN, s.Mp / kBlockM);
-    gemm_kernel<MODE><<<grid, kThreads, kSmemBytes, st>>>(mA0, mA1, mB0, mB1, p);
-    B2_CUDA(cudaGetLastError());
-    return B2_OK;
+    p.c_colmajor = 0;
+    return launch_on_planes<MODE>(base, s, p, st);
 }
 
 }  // namespace
