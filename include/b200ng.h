@@ -188,6 +188,36 @@ int b2_gemm_flex16(const int16_t* A, int64_t a_row_stride, int64_t a_k_stride, c
                    int32_t slotC, int32_t* stats, void* scratch, size_t scratch_bytes,
                    uint64_t* probe_out, int32_t* status, int32_t probe, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Convolution forward and average pooling on C,D,H,W,N tensors (filters C,T,R,S,K, outputs
+ * K,M,P,Q,N), the reference's layouts.
+ * Replaces: ConvFpropKernel / FlexConvFpropKernel (ngraph/transformers/gpu/conv.py:24-100,
+ * gpu/flex_conv.py:49-200) and PoolFpropKernel avg (gpu/pool.py:27-220).
+ * The dims struct has the fields of the reference's conv_params plus the tensor extents
+ * (ngraph/op_graph/convolution.py; ngraph/testing/conv_utils.py:ConvParams).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b2_conv_dims {
+    int32_t C, D, H, W, N;        /* input */
+    int32_t K, T, R, S;           /* filter */
+    int32_t M, P, Q;              /* output */
+    int32_t pad_d, pad_h, pad_w, str_d, str_h, str_w, dil_d, dil_h, dil_w;
+} b2_conv_dims;
+int b2_conv_fprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, size_t* bytes);
+/* fp32 (3xTF32 on the tensor cores). */
+int b2_conv_fprop_f32(const float* I, const float* F, float* O, const b2_conv_dims* d,
+                      void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+/* flex16: exact integer sums, rescale/saturate/statistic as b2_gemm_flex16; probe as there. */
+int b2_conv_fprop_flex16(const int16_t* I, const int16_t* F, int16_t* O, const b2_conv_dims* d,
+                         const b2_flex_scale* table, int32_t slotI, int32_t slotF, int32_t slotO,
+                         int32_t* stats, void* scratch, size_t scratch_bytes, uint64_t* probe_out,
+                         int32_t* status, int32_t probe, void* stream);
+/* Average pooling over H,W windows.  flex != 0: int16 in and out sharing one exponent
+ * (ngraph/transformers/passes/flexpass.py:40-48); *stats_slot = max(*stats_slot, max |out|). */
+int b2_pool_avg_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H, int32_t W,
+                      int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S, int32_t pad_h,
+                      int32_t pad_w, int32_t str_h, int32_t str_w, int32_t* stats_slot,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

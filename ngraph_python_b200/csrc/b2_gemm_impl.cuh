@@ -1,0 +1,547 @@
+// Dense GEMM on the 5th-generation tensor cores: C[M,N] = op(A)[M,K] * op(B)[K,N]
+//
+// Takes the place of the reference's GEMMKernel and its maxas SASS kernels
+// (ngraph/transformers/gpu/gemm.py:26-263, gpu/kernels/sass/sgemm_*.sass, fgemm_*.sass).
+//
+//   flex16: operands are int16 mantissas.  Each is split exactly into a signed high byte and an
+//           unsigned low byte, a = 256*ah + al, and the product is formed from four int8 tensor-core
+//           products with int32 accumulation in tensor memory:
+//               sum a*b = 65536*sum(ah*bh) + 256*(sum(ah*bl) + sum(al*bh)) + sum(al*bl)
+//           Three accumulators (HH, cross, LL) stay exact in int32 for K <= 32768; the epilogue
+//           recombines them in int64, applies the power-of-two rescale 2^(decC-decA-decB) with
+//           round-to-nearest-even in integer arithmetic, saturates to int16 and folds max|mantissa|.
+//           (The reference accumulates int16 products in fp32 FFMA, fgemm_common_128x128.sass:
+//           188-228, which is inexact above 2^24; this path is exact.)
+//   fp32:   3xTF32: a = a_hi + a_lo with a_hi rounded to tf32, and
+//               a*b ~= a_hi*b_hi + a_hi*b_lo + a_lo*b_hi        (relative error ~2^-21)
+//           three kind::tf32 products into one fp32 accumulator.
+//
+// Structure of the main kernel (one CTA per 128x128 output tile, 192 threads):
+//   warp 0   : TMA producer -- 2-D tiled bulk tensor copies of the four operand planes of a
+//              k-block (4 x 16 KB, 128-byte swizzle) into a 3-stage shared-memory ring;
+//   warp 1   : allocates tensor memory, one lane issues tcgen05.mma (12 or 16 per k-block) and
+//              commits each stage back to the producer;
+//   warps 2-5: epilogue -- tcgen05.ld of the accumulators (each warp owns 32 lanes = 32 rows),
+//              recombination / rescale / store.
+// A pre-pass writes the operand planes K-major (and transposes when the source is not), zero
+// padded to tile multiples, into caller-provided scratch.
+//
+// Every mbarrier wait is bounded; when one runs out the kernel records it in `status` and
+// finishes without hanging.  No cluster multicast is used anywhere.
+#ifndef B2_GEMM_IMPL_CUH
+#define B2_GEMM_IMPL_CUH
+#include <cuda.h>
+
+#include <mutex>
+
+#include "b2_common.h"
+
+namespace {
+
+constexpr int kBlockM = 128;          // UMMA M; the N tile (16/32/64/128) is a template parameter
+constexpr int kKBytes = 128;            // bytes of K per k-block row: one 128B swizzle atom
+constexpr int kPlaneBytes = 128 * kKBytes;   // 16 KB: 128 rows x 128 B
+__host__ __device__ constexpr int stage_bytes(int bn) { return 2 * kPlaneBytes + 2 * bn * kKBytes; }  // A0 A1 B0 B1
+constexpr int kStages = 3;
+constexpr int kThreads = 192;
+__host__ __device__ constexpr int smem_bytes(int bn) { return kStages * stage_bytes(bn) + 1024 /*alignment*/ + 256 /*barriers*/; }
+// tensor-memory columns: a power of two >= 32 that holds the accumulators (3 x BN or BN)
+__host__ __device__ constexpr int tmem_cols(int mode, int bn) {
+    int need = (mode == 0 ? 3 : 1) * bn, c = 32;
+    while (c < need) c *= 2;
+    return c;
+}
+
+enum { MODE_FLEX16 = 0, MODE_F32X3 = 1 };
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: gives up after ~1M polls (each poll suspends up to a hardware time limit)
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    for (int i = 0; i < (1 << 20); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned* holder, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(holder)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+template <int MODE>
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc,
+                                       unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+    if (MODE == MODE_FLEX16) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 B stored
+// consecutively (8-row groups 1024 B apart).  Fields: start>>4 [0,14), LBO>>4 [16,30) (=1 for
+// swizzled K-major), SBO>>4 [32,46) (=64), version [46,48) = 1, layout type [61,64) = 2.
+__device__ __forceinline__ unsigned long long make_smem_desc(const void* p) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(p) >> 4) & 0x3FFF);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// Instruction descriptor: D format [4,6), A format [7,10), B format [10,13), K-major both,
+// N>>3 [17,23), M>>4 [24,29).
+__host__ __device__ constexpr unsigned make_idesc(unsigned dfmt, unsigned afmt, unsigned bfmt,
+                                                  unsigned bn) {
+    return (dfmt << 4) | (afmt << 7) | (bfmt << 10) | ((bn >> 3) << 17) |
+           ((unsigned)(kBlockM >> 4) << 24);
+}
+
+struct GemmParams {
+    int M, N, num_kb;
+    long long ldc;
+    void* C;
+    const b2_flex_scale* table;
+    int slotA, slotB, slotC;
+    int* stats;
+    unsigned long long* probe_out;   // probe: max |exact integer product sum|
+    int* status;
+    int probe;
+    int c_colmajor;                  // 0: C[row*ldc + col]; 1: C[col*ldc + row]
+};
+
+// round-to-nearest-even of v / 2^sh (sh > 0), or v * 2^-sh (sh <= 0), saturated to int16
+__device__ __forceinline__ int rescale_i64(long long v, int sh) {
+    long long q;
+    if (sh <= 0) {
+        // scale up: anything with |v| >= 2^16 saturates for every left shift
+        const int l = -sh;
+        const long long a = v < 0 ? -v : v;
+        if (a >= 65536 || (l >= 16 && a != 0)) q = v > 0 ? 32767 : -32768;
+        else q = v << l;
+    } else if (sh >= 62) {
+        q = 0;
+    } else {
+        const long long half = 1LL << (sh - 1);
+        const long long lsb = (v >> sh) & 1;
+        q = (v + half - 1 + lsb) >> sh;
+    }
+    q = q > 32767 ? 32767 : (q < -32768 ? -32768 : q);
+    return (int)q;
+}
+
+template <int MODE, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
+            const __grid_constant__ CUtensorMap mapB0, const __grid_constant__ CUtensorMap mapB1,
+            const GemmParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int kStageBytes = stage_bytes(BN);
+    constexpr int kBPlane = BN * kKBytes;
+    constexpr int kTmemCols = tmem_cols(MODE, BN);
+    unsigned long long* full_bar = (unsigned long long*)(smem + kStages * kStageBytes);
+    unsigned long long* empty_bar = full_bar + kStages;
+    unsigned long long* tmem_full = empty_bar + kStages;
+    unsigned* tmem_holder = (unsigned*)(tmem_full + 1);
+    int* fail_flag = (int*)(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * kBlockM, n0 = blockIdx.x * BN;
+    const int kElems = MODE == MODE_FLEX16 ? kKBytes : kKBytes / 4;   // elements of K per k-block
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(tmem_full, 1);
+        *fail_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < p.num_kb; ++kb) {
+                const int s = kb % kStages;
+                if (kb >= kStages && !mbar_wait(&empty_bar[s], ((kb / kStages) - 1) & 1)) {
+                    atomicExch(fail_flag, 1);
+                    break;
+                }
+                unsigned char* st = smem + s * kStageBytes;
+                mbar_expect_tx(&full_bar[s], kStageBytes);
+                const int kx = kb * kElems;
+                tma_load_2d(st + 0 * kPlaneBytes, &mapA0, kx, m0, &full_bar[s]);
+                tma_load_2d(st + 1 * kPlaneBytes, &mapA1, kx, m0, &full_bar[s]);
+                tma_load_2d(st + 2 * kPlaneBytes, &mapB0, kx, n0, &full_bar[s]);
+                tma_load_2d(st + 2 * kPlaneBytes + kBPlane, &mapB1, kx, n0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // flex16: planes are (hi = signed, lo = unsigned) bytes; accumulators HH | X | LL
+            const unsigned id_ss = make_idesc(2, 1, 1, BN), id_su = make_idesc(2, 1, 0, BN),
+                           id_us = make_idesc(2, 0, 1, BN), id_uu = make_idesc(2, 0, 0, BN);
+            const unsigned id_tf = make_idesc(1, 2, 2, BN);
+            bool ok = true;
+            for (int kb = 0; kb < p.num_kb && ok; ++kb) {
+                const int s = kb % kStages;
+                if (!mbar_wait(&full_bar[s], (kb / kStages) & 1)) { atomicExch(fail_flag, 1); ok = false; break; }
+                tc_fence_after();
+                unsigned char* st = smem + s * kStageBytes;
+                const unsigned long long dA0 = make_smem_desc(st + 0 * kPlaneBytes);
+                const unsigned long long dA1 = make_smem_desc(st + 1 * kPlaneBytes);
+                const unsigned long long dB0 = make_smem_desc(st + 2 * kPlaneBytes);
+                const unsigned long long dB1 = make_smem_desc(st + 2 * kPlaneBytes + kBPlane);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const unsigned long long adv = (unsigned long long)((k * 32) >> 4);
+                    const unsigned acc = (kb > 0 || k > 0) ? 1u : 0u;
+                    if (MODE == MODE_FLEX16) {
+                        tc_mma<MODE>(tmem_base + 0, dA0 + adv, dB0 + adv, id_ss, acc);      // HH
+                        tc_mma<MODE>(tmem_base + BN, dA0 + adv, dB1 + adv, id_su, acc);     // X += ah*bl
+                        tc_mma<MODE>(tmem_base + BN, dA1 + adv, dB0 + adv, id_us, 1u);      // X += al*bh
+                        tc_mma<MODE>(tmem_base + 2 * BN, dA1 + adv, dB1 + adv, id_uu, acc); // LL
+                    } else {
+                        tc_mma<MODE>(tmem_base, dA0 + adv, dB0 + adv, id_tf, acc);          // hi*hi
+                        tc_mma<MODE>(tmem_base, dA0 + adv, dB1 + adv, id_tf, 1u);           // hi*lo
+                        tc_mma<MODE>(tmem_base, dA1 + adv, dB0 + adv, id_tf, 1u);           // lo*hi
+                    }
+                }
+                tc_commit(&empty_bar[s]);       // stage reusable once these MMAs have read it
+            }
+            tc_commit(tmem_full);               // accumulators complete
+        }
+    } else {
+        // epilogue warps 2..5: TMEM lane quarter = warp % 4
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        bool ok = mbar_wait(tmem_full, 0);
+        if (!ok) atomicExch(fail_flag, 1);
+        tc_fence_after();
+        const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
+        if (MODE == MODE_FLEX16) {
+            const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
+                            (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
+            const int sh = -ilogbf(f);          // f = 2^-sh exactly
+            int stat = 0;
+            unsigned long long pmax = 0;
+            short* crow = (short*)p.C + (long long)row * p.ldc;
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                unsigned hh[16], xx[16], ll[16];
+                tmem_ld16(lane_addr + c0, hh);
+                tmem_ld16(lane_addr + BN + c0, xx);
+                tmem_ld16(lane_addr + 2 * BN + c0, ll);
+                tmem_ld_wait();
+                if (!ok || row >= p.M) continue;
+                int q[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const long long v = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
+                                        (long long)(int)ll[j];
+                    if (p.probe) {
+                        const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
+                        pmax = a > pmax ? a : pmax;
+                    } else {
+                        q[j] = rescale_i64(v, sh);
+                        const int a = q[j] < 0 ? -q[j] : q[j];
+                        stat = a > stat ? a : stat;
+                    }
+                }
+                if (!p.probe) {
+                    const int col = n0 + c0;
+                    if (p.c_colmajor) {
+                        // lanes hold consecutive rows: each column is a coalesced 64-byte store
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (col + j < p.N)
+                                ((short*)p.C)[(long long)(col + j) * p.ldc + row] = (short)q[j];
+                    } else if (col + 16 <= p.N && ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+                        int4 w0, w1;
+                        w0.x = (q[0] & 0xffff) | (q[1] << 16); w0.y = (q[2] & 0xffff) | (q[3] << 16);
+                        w0.z = (q[4] & 0xffff) | (q[5] << 16); w0.w = (q[6] & 0xffff) | (q[7] << 16);
+                        w1.x = (q[8] & 0xffff) | (q[9] << 16); w1.y = (q[10] & 0xffff) | (q[11] << 16);
+                        w1.z = (q[12] & 0xffff) | (q[13] << 16); w1.w = (q[14] & 0xffff) | (q[15] << 16);
+                        *reinterpret_cast<int4*>(crow + col) = w0;
+                        *reinterpret_cast<int4*>(crow + col + 8) = w1;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (col + j < p.N) crow[col + j] = (short)q[j];
+                    }
+                }
+            }
+            if (p.probe) {
+                for (int o = 16; o > 0; o >>= 1) {
+                    const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
+                    pmax = t > pmax ? t : pmax;
+                }
+                if (lane == 0 && pmax) atomicMax(p.probe_out, pmax);
+            } else {
+                for (int o = 16; o > 0; o >>= 1) {
+                    const int t = __shfl_xor_sync(0xffffffffu, stat, o);
+                    stat = t > stat ? t : stat;
+                }
+                if (lane == 0 && stat) atomicMax(p.stats + p.slotC, stat);
+            }
+        } else {
+            float* crow = (float*)p.C + (long long)row * p.ldc;
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                unsigned acc[16];
+                tmem_ld16(lane_addr + c0, acc);
+                tmem_ld_wait();
+                if (!ok || row >= p.M) continue;
+                const int col = n0 + c0;
+                if (p.c_colmajor) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (col + j < p.N)
+                            ((float*)p.C)[(long long)(col + j) * p.ldc + row] = __uint_as_float(acc[j]);
+                } else if (col + 16 <= p.N && ((p.ldc & 3) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        *reinterpret_cast<float4*>(crow + col + j) =
+                            make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]),
+                                        __uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (col + j < p.N) crow[col + j] = __uint_as_float(acc[j]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *fail_flag && p.status) atomicExch(p.status, 1);
+}
+
+// ---- pre-pass: operand planes, K-major, zero padded ---------------------------------------------
+// src element (r, k) of op(X) is src[r * rs + k * cs]; planes are [rows_p][kp] with kp contiguous.
+// 32x32 tiles through shared memory so that both the read and the write are coalesced whichever of
+// rs / cs is 1.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+split_planes_kernel(const T* __restrict__ src, long long rs, long long cs, int rows, int k,
+                    int rows_p, int kp, void* __restrict__ plane0, void* __restrict__ plane1) {
+    __shared__ T tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 x 8
+    const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+    const bool k_contig = (cs == 1);
+    for (int i = ty; i < 32; i += 8) {
+        // read so that the contiguous source direction runs along tx
+        const int r = k_contig ? r0 + i : r0 + tx;
+        const int kk = k_contig ? k0 + tx : k0 + i;
+        T v = 0;
+        if (r < rows && kk < k) v = src[(long long)r * rs + (long long)kk * cs];
+        if (k_contig) tile[i][tx] = v; else tile[tx][i] = v;
+    }
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8) {
+        const int r = r0 + i, kk = k0 + tx;
+        if (r >= rows_p || kk >= kp) continue;
+        const T v = tile[i][tx];
+        const long long o = (long long)r * kp + kk;
+        if (MODE == MODE_FLEX16) {
+            const int m = (int)v;
+            const int lo = m & 0xff;                 // unsigned low byte
+            const int hi = (m - lo) >> 8;            // signed high byte: m = 256*hi + lo
+            ((signed char*)plane0)[o] = (signed char)hi;
+            ((unsigned char*)plane1)[o] = (unsigned char)lo;
+        } else {
+            const float a = (float)v;
+            unsigned hb;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(a));
+            const float hi = __uint_as_float(hb);
+            ((float*)plane0)[o] = hi;
+            ((float*)plane1)[o] = a - hi;
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_gemm_mutex;
+
+int get_encode() {
+    std::lock_guard<std::mutex> lock(g_gemm_mutex);
+    if (g_encode) return B2_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    B2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess)
+        return b2::fail(B2_ERR_UNAVAILABLE, "driver lacks cuTensorMapEncodeTiled");
+    g_encode = (EncodeTiledFn)fn;
+    return B2_OK;
+}
+
+// plane: [rows_p][kp] elements of `esize` bytes, K contiguous; box = 128 rows x 128 bytes
+int make_map(CUtensorMap* map, void* base, int rows_p, int kp, int esize, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)kp, (cuuint64_t)rows_p};
+    cuuint64_t strides[1] = {(cuuint64_t)kp * esize};
+    cuuint32_t box[2] = {(cuuint32_t)(kKBytes / esize), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                          2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return b2::fail(B2_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return B2_OK;
+}
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+struct Shapes { int Mp, Np, Kp, esize, bn; size_t bytes, a_bytes; };
+
+inline int pick_bn(int N) { return N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : 128; }
+
+Shapes shapes_for(int mode, int M, int N, int K) {
+    Shapes s;
+    s.esize = mode == MODE_FLEX16 ? 1 : 4;
+    s.bn = pick_bn(N);
+    s.Mp = round_up(M, kBlockM);
+    s.Np = round_up(N, s.bn);
+    s.Kp = round_up(K, kKBytes / s.esize);
+    s.a_bytes = 2ull * (size_t)s.Mp * s.Kp * s.esize;
+    s.bytes = s.a_bytes + 2ull * (size_t)s.Np * s.Kp * s.esize;
+    return s;
+}
+
+template <int MODE, int BN>
+int launch_tile(const CUtensorMap& mA0, const CUtensorMap& mA1, const CUtensorMap& mB0,
+                const CUtensorMap& mB1, const GemmParams& p, const Shapes& s, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        B2_CUDA(cudaFuncSetAttribute(gemm_kernel<MODE, BN>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
+        attr_set = true;
+    }
+    dim3 grid(s.Np / BN, s.Mp / kBlockM);
+    gemm_kernel<MODE, BN><<<grid, kThreads, smem_bytes(BN), st>>>(mA0, mA1, mB0, mB1, p);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+// Launches the tile kernel on operand planes that are already in scratch:
+// A planes at `base`, B planes behind them.
+template <int MODE>
+int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStream_t st) {
+    int rc = get_encode();
+    if (rc) return rc;
+    const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
+    void* A0 = base; void* A1 = base + a_plane;
+    void* B0 = base + 2 * a_plane; void* B1 = base + 2 * a_plane + b_plane;
+    CUtensorMap mA0, mA1, mB0, mB1;
+    if ((rc = make_map(&mA0, A0, s.Mp, s.Kp, s.esize, 128))) return rc;
+    if ((rc = make_map(&mA1, A1, s.Mp, s.Kp, s.esize, 128))) return rc;
+    if ((rc = make_map(&mB0, B0, s.Np, s.Kp, s.esize, s.bn))) return rc;
+    if ((rc = make_map(&mB1, B1, s.Np, s.Kp, s.esize, s.bn))) return rc;
+    p.num_kb = s.Kp / (kKBytes / s.esize);
+    switch (s.bn) {
+        case 16: return launch_tile<MODE, 16>(mA0, mA1, mB0, mB1, p, s, st);
+        case 32: return launch_tile<MODE, 32>(mA0, mA1, mB0, mB1, p, s, st);
+        case 64: return launch_tile<MODE, 64>(mA0, mA1, mB0, mB1, p, s, st);
+        default: return launch_tile<MODE, 128>(mA0, mA1, mB0, mB1, p, s, st);
+    }
+}
+
+template <typename T, int MODE>
+int run_gemm(const T* A, long long a_rs, long long a_cs, const T* B, long long b_ks, long long b_ns,
+             void* C, long long ldc, int M, int N, int K, const b2_flex_scale* table, int slotA,
+             int slotB, int slotC, int* stats, void* scratch, size_t scratch_bytes,
+             unsigned long long* probe_out, int* status, int probe, cudaStream_t st) {
+    B2_REQUIRE(A && B && C && M > 0 && N > 0 && K > 0, "bad GEMM argument");
+    B2_REQUIRE(a_rs == 1 || a_cs == 1, "A must be contiguous along M or K");
+    B2_REQUIRE(b_ks == 1 || b_ns == 1, "B must be contiguous along K or N");
+    if (MODE == MODE_FLEX16) B2_REQUIRE(K <= 32768, "flex16 GEMM keeps exact int32 sums for K <= 32768");
+    const Shapes s = shapes_for(MODE, M, N, K);
+    B2_REQUIRE(scratch && scratch_bytes >= s.bytes && ((uintptr_t)scratch & 1023) == 0,
+               "GEMM needs %zu bytes of 1024-byte aligned scratch, got %zu", s.bytes, scratch_bytes);
+    unsigned char* base = (unsigned char*)scratch;
+    const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
+    void* A0 = base; void* A1 = base + a_plane;
+    void* B0 = base + 2 * a_plane; void* B1 = base + 2 * a_plane + b_plane;
+    {
+        dim3 g((s.Kp + 31) / 32, (s.Mp + 31) / 32);
+        split_planes_kernel<T, MODE><<<g, 256, 0, st>>>(A, a_rs, a_cs, M, K, s.Mp, s.Kp, A0, A1);
+        dim3 g2((s.Kp + 31) / 32, (s.Np + 31) / 32);
+        // op(B)^T: rows = N, element (n, k) = B[k * b_ks + n * b_ns]
+        split_planes_kernel<T, MODE><<<g2, 256, 0, st>>>(B, b_ns, b_ks, N, K, s.Np, s.Kp, B0, B1);
+        B2_CUDA(cudaGetLastError());
+    }
+    GemmParams p;
+    p.M = M; p.N = N; p.num_kb = 0;
+    p.ldc = ldc; p.C = C; p.table = table; p.slotA = slotA; p.slotB = slotB; p.slotC = slotC;
+    p.stats = stats; p.probe_out = probe_out; p.status = status; p.probe = probe;
+    p.c_colmajor = 0;
+    return launch_on_planes<MODE>(base, s, p, st);
+}
+
+}  // namespace
+
+#endif  // B2_GEMM_IMPL_CUH

@@ -1,0 +1,220 @@
+"""Executor steps for the dense contractions and pooling: each wraps one C-ABI entry point.
+
+Takes the place of the reference's per-op kernel objects GEMMKernel (ngraph/transformers/gpu/
+gemm.py:26-263), ConvFpropKernel / FlexConvFpropKernel (gpu/conv.py:24-100, gpu/flex_conv.py:
+49-200) and PoolFpropKernel / FlexPoolFpropKernel (gpu/pool.py:27-220, gpu/flex_pool.py): bind
+buffers once, then launch per call; in flex mode the first write of an output runs the measuring
+("probe") variant so that the exponent fits the true range of the result.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import lib
+
+
+def _merge(view, axes):
+    """(extent, element stride) of `axes` walked as one dimension of `view`, or None."""
+    axes = [a for a in axes if a.length != 1]
+    if not axes:
+        return 1, 0
+    size, stride = 1, None
+    for a in reversed(list(axes)):
+        s = view.stride_of(a)
+        if stride is None:
+            stride = s
+        elif s != stride * size:
+            return None
+        size *= a.length
+    return size, stride
+
+
+class _Step(object):
+    launches = 0
+    scratch_bytes = 0
+
+    def __init__(self, index, op):
+        self.index = index
+        self.op = op
+        self.out_views = []
+        self.in_views = []
+
+    def output_buffers(self):
+        return [v.buffer for v in self.out_views]
+
+    def _ptr(self, v):
+        return v.buffer.ptr() + v.offset * (2 if v.buffer.flex else 4)
+
+    # flex first-write protocol shared by GEMM and conv -------------------------------------------
+    def _flex_probe_then(self, t, out_buf, in_bufs, call):
+        """call(probe) launches; on the first write of out_buf a probe launch measures the exact
+        integer maximum, from which the output exponent is chosen."""
+        e = out_buf.entry
+        if not e.initialized:
+            t._probe64.zero_()
+            call(1)
+            t.kernel_launches += self.launches
+            imax = int(t._probe64.item())
+            real = float(imax) * in_bufs[0].entry.scale * in_bufs[1].entry.scale
+            dec = e.initialize_from_range(real)
+            t._set_table_row(out_buf.slot_write, dec)
+            t._stats[out_buf.slot_write:out_buf.slot_write + 1].zero_()
+        call(0)
+        t.kernel_launches += self.launches
+
+
+class GemmStep(_Step):
+    """C[M,N] = op(A)[M,K] * op(B)[K,N] for a DotOp."""
+    kind = "gemm"
+    launches = 3          # two operand-plane kernels + the tensor-core kernel
+
+    def __init__(self, index, op, t):
+        super(GemmStep, self).__init__(index, op)
+        x, y = op.args
+        xv, yv = t._view_of(x), t._view_of(y)
+        red = [a for a in xv.axes if a in op.reduction_axes]
+        am, ak = _merge(xv, op.x_out_axes), _merge(xv, red)
+        bk, bn = _merge(yv, red), _merge(yv, op.y_out_axes)
+        if None in (am, ak, bk, bn):
+            raise ValueError("Unhandled op: dot operands must be 2-d collapsible: {}".format(op))
+        self.M, self.K, self.N = am[0], ak[0], bn[0]
+        if bk[0] != self.K:
+            raise ValueError("Unhandled op: reduction axes of the dot operands disagree")
+        # extents of 1 carry no stride of their own: describe them as row-major
+        a_cs = ak[1] if self.K > 1 else 1
+        a_rs = am[1] if self.M > 1 else (self.K if a_cs == 1 else 1)
+        b_ns = bn[1] if self.N > 1 else 1
+        b_ks = bk[1] if self.K > 1 else (self.N if b_ns == 1 else 1)
+        self.a_str = (a_rs, a_cs)
+        self.b_str = (b_ks, b_ns)
+        if 1 not in self.a_str or 1 not in self.b_str:
+            raise ValueError("Unhandled op: dot operand is not contiguous along M/K or K/N")
+        self.in_views = [xv, yv]
+        self.out_views = [t._view_of(op)]
+        self.flex = t.flex
+        self.scratch_bytes = lib.gemm_scratch_bytes(self.flex, self.M, self.N, self.K) + 1024
+
+    def launch(self, t):
+        xv, yv = self.in_views
+        ov = self.out_views[0]
+        raw = lib.raw()
+        sp, sb = t._scratch_aligned()
+        st = t.stream.cuda_stream
+        if not self.flex:
+            lib.check(raw.b2_gemm_f32(self._ptr(xv), self.a_str[0], self.a_str[1], self._ptr(yv),
+                                      self.b_str[0], self.b_str[1], self._ptr(ov), self.N, self.M,
+                                      self.N, self.K, sp, sb, t._status.data_ptr(), st))
+            t.kernel_launches += self.launches
+            return
+        slots = (t._slot_for_read(xv.buffer, self), t._slot_for_read(yv.buffer, self),
+                 ov.buffer.slot_write)
+
+        def call(probe):
+            lib.check(raw.b2_gemm_flex16(
+                self._ptr(xv), self.a_str[0], self.a_str[1], self._ptr(yv), self.b_str[0],
+                self.b_str[1], self._ptr(ov), self.N, self.M, self.N, self.K, t._table.data_ptr(),
+                slots[0], slots[1], slots[2], t._stats.data_ptr(), sp, sb, t._probe64.data_ptr(),
+                t._status.data_ptr(), probe, st))
+        self._flex_probe_then(t, ov.buffer, [xv.buffer, yv.buffer], call)
+
+
+class ConvStep(_Step):
+    """Convolution forward on C,D,H,W,N / C,T,R,S,K / K,M,P,Q,N tensors."""
+    kind = "conv"
+    launches = 3
+
+    def __init__(self, index, op, t):
+        super(ConvStep, self).__init__(index, op)
+        inputs, filters = op.args
+        iv, fv, ov = t._view_of(inputs), t._view_of(filters), t._view_of(op)
+        for v, what in ((iv, "input"), (fv, "filter")):
+            if not v.is_dense():
+                raise ValueError("Unhandled op: convolution %s must be a dense tensor" % what)
+        cp = op.conv_params
+        Cc, D, H, W, N = iv.axes.lengths
+        C2, T, R, S, K = fv.axes.lengths
+        K2, M, P, Q, N2 = ov.axes.lengths
+        if K2 != K or N2 != N:
+            raise ValueError("convolution output axes do not match filter/input axes")
+        d = lib.ConvDims()
+        d.C, d.D, d.H, d.W, d.N = Cc, D, H, W, N
+        d.K, d.T, d.R, d.S = K, T, R, S
+        d.M, d.P, d.Q = M, P, Q
+        for k in ("pad_d", "pad_h", "pad_w"):
+            setattr(d, k, int(cp.get(k, 0)))
+        for k in ("str_d", "str_h", "str_w", "dil_d", "dil_h", "dil_w"):
+            setattr(d, k, int(cp.get(k, 1)))
+        # the output extents must be what the parameters imply (reference: output_dim,
+        # ngraph/frontends/neon/utils.py / conv_utils.py)
+        for (x, f, pad, st, dil, o, nm) in ((H, R, d.pad_h, d.str_h, d.dil_h, P, "H"),
+                                            (W, S, d.pad_w, d.str_w, d.dil_w, Q, "W")):
+            expect = (x + 2 * pad - dil * (f - 1) - 1) // st + 1
+            if expect != o:
+                raise ValueError("convolution output extent along %s is %d, parameters imply %d"
+                                 % (nm, o, expect))
+        self.dims = d
+        self.in_views = [iv, fv]
+        self.out_views = [ov]
+        self.flex = t.flex
+        self.scratch_bytes = lib.conv_fprop_scratch_bytes(self.flex, d) + 1024
+
+    def launch(self, t):
+        iv, fv = self.in_views
+        ov = self.out_views[0]
+        raw = lib.raw()
+        sp, sb = t._scratch_aligned()
+        st = t.stream.cuda_stream
+        if not self.flex:
+            lib.check(raw.b2_conv_fprop_f32(self._ptr(iv), self._ptr(fv), self._ptr(ov),
+                                            C.byref(self.dims), sp, sb, t._status.data_ptr(), st))
+            t.kernel_launches += self.launches
+            return
+        slots = (t._slot_for_read(iv.buffer, self), t._slot_for_read(fv.buffer, self),
+                 ov.buffer.slot_write)
+
+        def call(probe):
+            lib.check(raw.b2_conv_fprop_flex16(
+                self._ptr(iv), self._ptr(fv), self._ptr(ov), C.byref(self.dims),
+                t._table.data_ptr(), slots[0], slots[1], slots[2], t._stats.data_ptr(), sp, sb,
+                t._probe64.data_ptr(), t._status.data_ptr(), probe, st))
+        self._flex_probe_then(t, ov.buffer, [iv.buffer, fv.buffer], call)
+
+
+class PoolStep(_Step):
+    """Average pooling forward; a flex output keeps its input's exponent
+    (ngraph/transformers/passes/flexpass.py:40-48)."""
+    kind = "pool"
+    launches = 1
+
+    def __init__(self, index, op, t):
+        super(PoolStep, self).__init__(index, op)
+        pp = op.pool_params
+        if pp["op"] != "avg":
+            raise ValueError("Unhandled op: only average pooling is implemented: {}".format(op))
+        iv = t._view_of(op.args[0])
+        if not iv.is_dense():
+            raise ValueError("Unhandled op: pooling input must be a dense tensor")
+        if int(pp.get("J", 1)) != 1 or int(pp.get("T", 1)) != 1:
+            raise ValueError("Unhandled op: pooling over channels or depth")
+        ov = t._view_of(op)
+        if t.flex:
+            t._share_entry(ov.buffer, iv.buffer)
+        Cc, D, H, W, N = iv.axes.lengths
+        K, M, P, Q, N2 = ov.axes.lengths
+        self.args = (Cc, H, W, N, P, Q, int(pp["R"]), int(pp["S"]), int(pp.get("pad_h", 0)),
+                     int(pp.get("pad_w", 0)), int(pp.get("str_h", 1)), int(pp.get("str_w", 1)))
+        self.in_views = [iv]
+        self.out_views = [ov]
+        self.flex = t.flex
+
+    def output_buffers(self):
+        return []          # no exponent of its own to manage
+
+    def launch(self, t):
+        iv, ov = self.in_views[0], self.out_views[0]
+        stats = 0
+        if self.flex:
+            stats = t._stats.data_ptr() + 4 * (t._stats.numel() - 2)    # discarded
+        lib.check(lib.raw().b2_pool_avg_fprop(self._ptr(iv), self._ptr(ov), int(self.flex),
+                                              *(self.args + (stats, t.stream.cuda_stream))))
+        t.kernel_launches += 1

@@ -50,6 +50,12 @@ class EwProgram(C.Structure):
                 ("out", EwResult * EW_MAX_OUT)]
 
 
+class ConvDims(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("C", "D", "H", "W", "N", "K", "T", "R", "S", "M", "P", "Q", "pad_d", "pad_h",
+                 "pad_w", "str_d", "str_h", "str_w", "dil_d", "dil_h", "dil_w")]
+
+
 class FlexScale(C.Structure):
     _fields_ = [("scale", C.c_float), ("inv_scale", C.c_float)]
 
@@ -80,6 +86,12 @@ def _load():
                                   vp]),
         "b2_gemm_flex16": (C.c_int, [vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, vp, i32,
                                      i32, i32, vp, vp, sz, vp, vp, i32, vp]),
+        "b2_conv_fprop_scratch_bytes": (C.c_int, [i32, C.POINTER(ConvDims), C.POINTER(sz)]),
+        "b2_conv_fprop_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
+        "b2_conv_fprop_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,
+                                           vp, sz, vp, vp, i32, vp]),
+        "b2_pool_avg_fprop": (C.c_int, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32,
+                                        i32, i32, i32, vp, vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),
@@ -212,4 +224,10 @@ class PlannedKernel(object):
 def gemm_scratch_bytes(flex, M, N, K):
     n = C.c_size_t()
     check(_lib.b2_gemm_scratch_bytes(int(bool(flex)), M, N, K, C.byref(n)))
+    return n.value
+
+
+def conv_fprop_scratch_bytes(flex, dims):
+    n = C.c_size_t()
+    check(_lib.b2_conv_fprop_scratch_bytes(int(bool(flex)), C.byref(dims), C.byref(n)))
     return n.value

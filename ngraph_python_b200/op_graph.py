@@ -324,6 +324,26 @@ class ReorderAxes(ViewOp):
         super(ReorderAxes, self).__init__((x,), axes, **kw)
 
 
+class AxesCastOp(ViewOp):
+    """Same storage, new axes position by position (ngraph/op_graph/op_graph.py: AxesCastOp)."""
+
+    def __init__(self, x, axes, **kw):
+        x = as_op(x)
+        axes = make_axes(axes)
+        if x.axes.lengths != axes.lengths:
+            raise ValueError("casting axes {} must have the same length as original axes {}"
+                             .format(axes, x.axes))
+        super(AxesCastOp, self).__init__((x,), axes, **kw)
+
+
+def cast_axes(tensor, axes):
+    tensor = as_op(tensor)
+    axes = make_axes(axes)
+    if tensor.axes == axes:
+        return tensor
+    return AxesCastOp(tensor, axes)
+
+
 def broadcast(x, axes):
     x = as_op(x)
     axes = make_axes(axes)

@@ -18,8 +18,9 @@ import numpy as np
 
 from . import flex as flexmod
 from . import fusion
+from . import kernels
 from . import lib
-from .op_graph import (AssignableTensorOp, AssignOp, Axes, BroadcastOp, ConvolutionOp, DotOp,
+from .op_graph import (AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp, ConvolutionOp, DotOp,
                        ElementWiseOp, Op, PoolingOp, ReductionOp, ReorderAxes, SequentialOp,
                        ViewOp, as_op, make_axes)
 
@@ -104,6 +105,10 @@ class EwStep(object):
     def output_buffers(self):
         return [v.buffer for v in self.out_views]
 
+    @property
+    def launches(self):
+        return self.kernel.launches
+
 
 # ---------------------------------------------------------------------------------------------
 class Computation(object):
@@ -153,7 +158,7 @@ class Computation(object):
         for s in self.steps:
             planner.finalize_step(s)
         t._allocate()
-        self.launches_per_call = builtin_sum(s.kernel.launches for s in self.steps)
+        self.launches_per_call = builtin_sum(s.launches for s in self.steps)
         self.written = planner.written_buffers
         self.executor = self._run_steps
 
@@ -373,7 +378,34 @@ class _Planner(object):
         return True
 
     def _place_other(self, op):
-        raise ValueError("Unhandled op: {}".format(op))
+        """Dense contractions and pooling: one step each, never fused with neighbours."""
+        index = self._new_step_index()
+        if isinstance(op, DotOp):
+            step = kernels.GemmStep(index, op, self.t)
+        elif isinstance(op, ConvolutionOp):
+            step = kernels.ConvStep(index, op, self.t)
+        elif isinstance(op, PoolingOp):
+            step = kernels.PoolStep(index, op, self.t)
+        else:
+            raise ValueError("Unhandled op: {}".format(op))
+        # the step must come after everything its arguments depend on; steps are appended in
+        # dependency order, so only in-place writes of persistent tensors need recording
+        for a in op.args:
+            base, _ = self._base_tensor(a)
+            if base in self.group_of:
+                self.group_of[base].stored.add(base)
+            if isinstance(base, AssignableTensorOp) and not base.is_scalar_constant:
+                b = self.t._buffer_of(base)
+                b.last_read_step = max(b.last_read_step, index)
+                step.reads_after_write = getattr(step, "reads_after_write", set())
+                if b.last_write_step >= 0:
+                    step.reads_after_write.add(id(b))
+        self.steps.append(step)
+        self.producer[op] = index
+        self.t._need_scratch(step.scratch_bytes)
+        for b in step.output_buffers():
+            if b not in self.written_buffers:
+                self.written_buffers.append(b)
 
     def _collect_outputs(self, step):
         """Which values of the group must be stored: those used by another step or returned."""
@@ -614,7 +646,7 @@ class B200Transformer(object):
         self.closed = True
         self._buffers.clear()
         self._views.clear()
-        self._scratch = self._table = self._stats = self._status = None
+        self._scratch = self._table = self._stats = self._status = self._probe64 = None
 
     def __enter__(self):
         return self
@@ -646,6 +678,9 @@ class B200Transformer(object):
         if isinstance(op, (BroadcastOp, ReorderAxes)):
             src = self._view_of(op.args[0])
             v = View(src.buffer, op.axes, [src.stride_of(a) for a in op.axes], src.offset)
+        elif isinstance(op, AxesCastOp):
+            src = self._view_of(op.args[0])
+            v = View(src.buffer, op.axes, src.strides, src.offset)
         elif isinstance(op, AssignOp):
             v = self._view_of(op.args[0])
         else:
@@ -663,6 +698,25 @@ class B200Transformer(object):
     def _need_scratch(self, nbytes):
         self._scratch_bytes = max(self._scratch_bytes, int(nbytes))
 
+    def _scratch_aligned(self):
+        """(pointer, bytes) of the scratch arena rounded up to a 1024-byte boundary (the tensor
+        core kernels place TMA-swizzled operand planes in it)."""
+        base = self._scratch.data_ptr()
+        off = (-base) % 1024
+        return base + off, self._scratch.numel() - off
+
+    def _slot_for_read(self, buf, step):
+        if id(buf) in getattr(step, "reads_after_write", ()):
+            return buf.slot_write
+        return buf.slot
+
+    def _share_entry(self, buf, src):
+        """buf's values are stored with src's exponent (pooling / dimshuffle outputs)."""
+        buf.entry = src.entry
+        buf.slot = src.slot
+        buf.slot_write = src.slot_write
+        buf.shares_entry = True
+
     def _allocate(self):
         if self.plan_only:
             return
@@ -673,6 +727,7 @@ class B200Transformer(object):
                 b.tensor = torch.zeros((max(b.size, 1),), dtype=dt, device=self.device)
         if self._status is None:
             self._status = torch.zeros((1,), dtype=torch.int32, device=self.device)
+            self._probe64 = torch.zeros((1,), dtype=torch.int64, device=self.device)
         if self.flex:
             n = max(self.flex_manager.n_slots + 64, 64)
             if self._table is None or self._table.shape[0] < n:
@@ -687,8 +742,8 @@ class B200Transformer(object):
 
     def _ensure_scratch(self):
         if self._scratch is None or self._scratch.numel() < self._scratch_bytes:
-            self._scratch = self.torch.empty((max(self._scratch_bytes, 16),), dtype=self.torch.uint8,
-                                             device=self.device)
+            self._scratch = self.torch.empty((max(self._scratch_bytes, 16) + 1024,),
+                                             dtype=self.torch.uint8, device=self.device)
 
     # ---- host <-> device -----------------------------------------------------------------------
     def _host_to_device(self, view, value, init=False):
@@ -759,6 +814,8 @@ class B200Transformer(object):
         self.flex_manager.autoflex_count += 1
         written = set(id(b) for b in comp.written)
         for b in self._buffers.values():
+            if getattr(b, "shares_entry", False):
+                continue
             e = b.entry
             dec_stored = e.dec
             # tensors this call overwrites adopt the exponent chosen after their previous write

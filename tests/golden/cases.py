@@ -132,7 +132,132 @@ def assign_sequence(ng):
     return [upd], [g], vals
 
 
+def _conv_params(pad, stride):
+    return dict(pad_d=0, pad_h=pad, pad_w=pad, str_d=1, str_h=stride, str_w=stride,
+                dil_d=1, dil_h=1, dil_w=1)
+
+
+def conv_basic(ng, C=16, K=32, H=12, W=10, N=32, R=3, S=3, pad=1, stride=1):
+    """One convolution forward, C,D,H,W,N * C,T,R,S,K -> K,M,P,Q,N
+    (tests/transformer_dependent/test_conv.py:55-89)."""
+    P = (H + 2 * pad - R) // stride + 1
+    Q = (W + 2 * pad - S) // stride + 1
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    ax_i = [ax(C, "C"), ax(1, "D"), ax(H, "H"), ax(W, "W"), ax(N, "N")]
+    ax_f = [ax_i[0], ax(1, "T"), ax(R, "R"), ax(S, "S"), ax(K, "K")]
+    ax_o = [ax_f[4], ax(1, "M"), ax(P, "P"), ax(Q, "Q"), ax_i[4]]
+    inputs = ng.placeholder(ax_i)
+    filters = ng.placeholder(ax_f)
+    out = ng.convolution(_conv_params(pad, stride), inputs, filters, axes=ax_o)
+    r = _rng(10)
+    vals = [r.standard_normal((C, 1, H, W, N)).astype(np.float32),
+            (r.standard_normal((C, 1, R, S, K)) * 0.2).astype(np.float32)]
+    return [out], [inputs, filters], vals
+
+
+def conv_stride2_1x1(ng):
+    return conv_basic(ng, C=32, K=64, H=16, W=16, N=32, R=1, S=1, pad=0, stride=2)
+
+
+def conv_stride2_3x3(ng):
+    return conv_basic(ng, C=3, K=16, H=9, W=11, N=32, R=3, S=3, pad=1, stride=2)
+
+
+def mlp_forward(ng):
+    """Forward pass of BASELINE config 1: 784 -> 512 ReLU -> 512 ReLU -> 10 softmax, batch 128."""
+    r = _rng(0)
+    N = ng.make_axis(128, name="N")
+    F = ng.make_axis(784, name="F")
+    H1 = ng.make_axis(512, name="H1")
+    H2 = ng.make_axis(512, name="H2")
+    Y = ng.make_axis(10, name="Y")
+    x = ng.placeholder([F, N])
+
+    def dense(inp, out_ax, in_ax):
+        w = ng.variable([out_ax, in_ax], initial_value=(
+            r.standard_normal((out_ax.length, in_ax.length)) *
+            np.sqrt(2.0 / in_ax.length)).astype(np.float32))
+        b = ng.variable([out_ax], initial_value=np.zeros(out_ax.length, np.float32))
+        return ng.dot(w, inp) + b
+    h1 = ng.maximum(dense(x, H1, F), 0.0)
+    h2 = ng.maximum(dense(h1, H2, H1), 0.0)
+    logits = dense(h2, Y, H2)
+    e = ng.exp(logits - ng.max(logits, reduction_axes=[Y]))
+    p = e / ng.sum(e, reduction_axes=[Y])
+    vals = [_rng(1).uniform(0, 1, (784, 128)).astype(np.float32)]
+    return [p, logits], [x], vals
+
+
+def resnet20(ng, n=32, hw=32, widths=(16, 32, 64), blocks=3):
+    """ResNet-20 inference (BASELINE config 4): 3 stages of 3 basic blocks, 3x3 convolutions,
+    batch norm folded into per-channel biases, a 1x1 projection on the first block of every stage,
+    8x8 average pool, 10-way linear, softmax.  22 convolutions, He-initialised from seed 0."""
+    r = _rng(0)
+    ax = lambda nlen, nm: ng.make_axis(nlen, name=nm)   # noqa: E731
+    N = ax(n, "N")
+    D = ax(1, "D")
+    T = ax(1, "T")
+    C3 = ax(3, "C3")
+    x = ng.placeholder([C3, D, ax(hw, "H0"), ax(hw, "W0"), N])
+    counter = [0]
+
+    def conv(inp, cout_axis, k, stride, out_sp):
+        """inp axes (Cin, D, H, W, N) -> (cout_axis, D, H', W', N) with bias."""
+        i = counter[0]
+        counter[0] += 1
+        cin = inp.axes[0]
+        Kt = ax(cout_axis.length, "K%d" % i)
+        fan_in = cin.length * k * k
+        f = ng.variable([cin, T, ax(k, "R%d" % i), ax(k, "S%d" % i), Kt],
+                        initial_value=(r.standard_normal((cin.length, 1, k, k, Kt.length)) *
+                                       np.sqrt(2.0 / fan_in)).astype(np.float32))
+        b = ng.variable([cout_axis], initial_value=(r.standard_normal(cout_axis.length) *
+                                                    0.05).astype(np.float32))
+        o = ng.convolution(_conv_params(k // 2, stride), inp, f,
+                           axes=[Kt, ax(1, "M%d" % i), out_sp[0], out_sp[1], N])
+        o = ng.cast_axes(o, [cout_axis, D, out_sp[0], out_sp[1], N])
+        return o + b
+
+    size = hw
+    sp = (ax(size, "H%d" % size), ax(size, "W%d" % size))
+    cur = ng.maximum(conv(x, ax(widths[0], "C%d" % widths[0]), 3, 1, sp), 0.0)
+    for s, width in enumerate(widths):
+        c_axis = ax(width, "C%d" % width)
+        for b in range(blocks):
+            stride = 2 if (b == 0 and s > 0) else 1
+            if stride == 2:
+                size //= 2
+                sp = (ax(size, "H%d" % size), ax(size, "W%d" % size))
+            y = ng.maximum(conv(cur, c_axis, 3, stride, sp), 0.0)
+            y = conv(y, c_axis, 3, 1, sp)
+            shortcut = conv(cur, c_axis, 1, stride, sp) if b == 0 else cur
+            cur = ng.maximum(y + shortcut, 0.0)
+    pool = dict(op="avg", J=1, T=1, R=size, S=size, pad_c=0, pad_d=0, pad_h=0, pad_w=0,
+                str_c=1, str_d=1, str_h=1, str_w=1)
+    pooled = ng.pooling(pool, cur, axes=[cur.axes[0], D, ax(1, "PP"), ax(1, "QQ"), N])
+    Y = ax(10, "Y")
+    w = ng.variable([Y, cur.axes[0]], initial_value=(
+        r.standard_normal((10, widths[-1])) * np.sqrt(2.0 / widths[-1])).astype(np.float32))
+    by = ng.variable([Y], initial_value=np.zeros(10, np.float32))
+    logits = ng.dot(w, pooled) + by
+    e = ng.exp(logits - ng.max(logits, reduction_axes=[Y]))
+    p = e / ng.sum(e, reduction_axes=[Y])
+    vals = [_rng(1).standard_normal((3, 1, hw, hw, n)).astype(np.float32)]
+    return [p, logits], [x], vals
+
+
+def resnet8_small(ng):
+    """A one-block-per-stage cut of the same network on 16x16 images (fast fixture)."""
+    return resnet20(ng, n=32, hw=16, blocks=1)
+
+
 CASES = {
+    "conv_basic": conv_basic,
+    "conv_stride2_1x1": conv_stride2_1x1,
+    "conv_stride2_3x3": conv_stride2_3x3,
+    "mlp_forward": mlp_forward,
+    "resnet20": resnet20,
+    "resnet8_small": resnet8_small,
     "c2_fused": c2_fused,
     "ew_4d": ew_4d,
     "reduce_4d_axis1": reduce_4d_axis1,

@@ -22,7 +22,10 @@ def test_every_case_plans_and_compiles(name, flex):
     t, comp = _plan(name, flex)
     assert len(comp.steps) >= 1
     for s in comp.steps:
-        assert "b2_ew_main" in s.kernel.source()
+        if s.kind == "ew":
+            assert "b2_ew_main" in s.kernel.source()
+        else:
+            assert s.kind in ("gemm", "conv", "pool") and s.launches >= 1
 
 
 def test_c2_is_one_kernel():
@@ -83,3 +86,14 @@ def test_no_cpu_fallback():
         pytest.skip("device present")
     with pytest.raises(ng.UnsupportedTransformerException):
         ng.transformers.make_transformer()
+
+
+def test_resnet20_plan_shape():
+    """22 convolutions, one pooling, one dot; everything between them fused."""
+    t, comp = _plan("resnet20")
+    kinds = [s.kind for s in comp.steps]
+    assert kinds.count("conv") == 22
+    assert kinds.count("pool") == 1
+    assert kinds.count("gemm") == 1
+    # bias/ReLU/residual chains collapse: far fewer elementwise kernels than the 60+ ops
+    assert kinds.count("ew") <= 26
