@@ -6,6 +6,11 @@
 One step = one pass of the workload's computation over one batch of seeded synthetic input.
 Rank 0 prints ONE JSON line.  Workloads:
 
+  resnet20_flex16 / resnet20_fp32 (default: resnet20_flex16)
+                        ResNet-20 inference, 3x32x32 images ~N(0,1) in C,H,W,N layout, batch 256
+                        per GPU, He-initialised weights from seed 0, batch norm folded into
+                        biases.  Metric: images per second.  Each GPU runs a full replica on its
+                        own batch; nothing is exchanged.
   c2_flex16 / c2_fp32   fused elementwise + reduction microbenchmark
                         y = tanh(a*x+b)*sigmoid(c), s = sum(y, axis 1), m = max|y| over axis 1,
                         x,a,b,c of shape (8192, 16384); y is stored (into a variable), s and m are
@@ -123,6 +128,232 @@ def build_c2(ng, flex, rows, cols):
     return [out, m], ph
 
 
+# ---------------------------------------------------------------------------------------------
+# ResNet-20 (BASELINE config 4): described once as a layer list, built either as a graph for the
+# b200 transformer or evaluated with the numpy restatement for the CPU baseline.
+RESNET_WIDTHS = (16, 32, 64)
+RESNET_N = 256
+# algorithmic figures per 256-image batch: 21.03 GFLOP; minimal layer I/O of the 22 convolutions
+# (inputs 58 458 112 + outputs 55 574 528 + filters 270 512 elements)
+RESNET_FLOP_PER_IMG = 82.1e6
+RESNET_CONV_ELEMS_PER_256 = 58458112 + 55574528 + 270512
+
+
+def resnet_weights(seed=0):
+    """He-initialised filters (C,R,S,K) and biases for the 22 convolutions + the linear layer."""
+    r = np.random.RandomState(seed)
+    convs = []
+
+    def add(cin, cout, k):
+        convs.append(((r.standard_normal((cin, k, k, cout)) * np.sqrt(2.0 / (cin * k * k)))
+                      .astype(np.float32), (r.standard_normal(cout) * 0.05).astype(np.float32)))
+    add(3, 16, 3)
+    cin = 16
+    for s, w in enumerate(RESNET_WIDTHS):
+        for b in range(3):
+            add(cin, w, 3)
+            add(w, w, 3)
+            if b == 0:
+                add(cin, w, 1)
+            cin = w
+    lin = ((r.standard_normal((10, 64)) * np.sqrt(2.0 / 64)).astype(np.float32),
+           np.zeros(10, np.float32))
+    return convs, lin
+
+
+def build_resnet20(ng, n, weights):
+    convs, lin = weights
+    ax = lambda ln, nm: ng.make_axis(ln, name=nm)   # noqa: E731
+    N, D, T = ax(n, "N"), ax(1, "D"), ax(1, "T")
+    x = ng.placeholder([ax(3, "C3"), D, ax(32, "H0"), ax(32, "W0"), N])
+    it = iter(range(len(convs)))
+
+    def conv(inp, c_axis, stride, sp):
+        i = next(it)
+        f_np, b_np = convs[i]
+        cin, k = f_np.shape[0], f_np.shape[1]
+        Kt = ax(f_np.shape[3], "K%d" % i)
+        f = ng.variable([inp.axes[0], T, ax(k, "R%d" % i), ax(k, "S%d" % i), Kt],
+                        initial_value=f_np.reshape(cin, 1, k, k, -1))
+        b = ng.variable([c_axis], initial_value=b_np)
+        cp = dict(pad_d=0, pad_h=k // 2, pad_w=k // 2, str_d=1, str_h=stride, str_w=stride,
+                  dil_d=1, dil_h=1, dil_w=1)
+        o = ng.convolution(cp, inp, f, axes=[Kt, ax(1, "M%d" % i), sp[0], sp[1], N])
+        return ng.cast_axes(o, [c_axis, D, sp[0], sp[1], N]) + b
+    size = 32
+    sp = (ax(size, "H32"), ax(size, "W32"))
+    cur = ng.maximum(conv(x, ax(16, "C16"), 1, sp), 0.0)
+    for s, w in enumerate(RESNET_WIDTHS):
+        c_axis = ax(w, "C%d" % w)
+        for b in range(3):
+            stride = 2 if (b == 0 and s > 0) else 1
+            if stride == 2:
+                size //= 2
+                sp = (ax(size, "H%d" % size), ax(size, "W%d" % size))
+            y = ng.maximum(conv(cur, c_axis, stride, sp), 0.0)
+            y = conv(y, c_axis, 1, sp)
+            shortcut = conv(cur, c_axis, stride, sp) if b == 0 else cur
+            cur = ng.maximum(y + shortcut, 0.0)
+    pool = dict(op="avg", J=1, T=1, R=size, S=size, pad_c=0, pad_d=0, pad_h=0, pad_w=0,
+                str_c=1, str_d=1, str_h=1, str_w=1)
+    pooled = ng.pooling(pool, cur, axes=[cur.axes[0], D, ax(1, "PP"), ax(1, "QQ"), N])
+    Y = ax(10, "Y")
+    w = ng.variable([Y, cur.axes[0]], initial_value=lin[0])
+    by = ng.variable([Y], initial_value=lin[1])
+    logits = ng.dot(w, pooled) + by
+    e = ng.exp(logits - ng.max(logits, reduction_axes=[Y]))
+    return [e / ng.sum(e, reduction_axes=[Y])], [x]
+
+
+def resnet20_numpy(x, weights):
+    """The same network with the numpy restatement (oracle/conv_oracle.py); x: (3, 32, 32, n)."""
+    from oracle import conv_oracle as co
+    convs, lin = weights
+    it = iter(convs)
+
+    def conv(inp, stride):
+        f, b = next(it)
+        k = f.shape[1]
+        return co.conv_fprop(inp, f, (k // 2, k // 2), (stride, stride)) + b[:, None, None, None]
+    cur = np.maximum(conv(x, 1), 0)
+    for s in range(3):
+        for b in range(3):
+            stride = 2 if (b == 0 and s > 0) else 1
+            y = np.maximum(conv(cur, stride), 0)
+            y = conv(y, 1)
+            shortcut = conv(cur, stride) if b == 0 else cur
+            cur = np.maximum(y + shortcut, 0)
+    pooled = co.pool_avg_fprop(cur, cur.shape[1:3])[:, 0, 0, :]
+    logits = lin[0] @ pooled + lin[1][:, None]
+    e = np.exp(logits - logits.max(axis=0))
+    return e / e.sum(axis=0)
+
+
+def run_resnet(args, rank, world, torch, dist, local):
+    import ngraph_python_b200 as ng
+    flex = args.workload == "resnet20_flex16"
+    n = args.batch
+    weights = resnet_weights(0)
+    t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex)
+    outs, params = build_resnet20(ng, n, weights)
+    comp = t.computation(outs, *params)
+    pinned = torch.empty((3, 1, 32, 32, n), dtype=torch.float32).pin_memory()
+    host = pinned.numpy()
+    host[...] = np.random.RandomState(100 + rank).standard_normal(host.shape).astype(np.float32)
+    first = comp(host)[0]
+    comp(host)
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    launches0 = t.kernel_launches
+    for _ in range(args.warmup):
+        comp.executor()
+    launches_per_step = (t.kernel_launches - launches0) // max(args.warmup, 1)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        comp.executor()
+    ev1.record(stream)
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    # per-kind device time: events between the steps of a few instrumented passes
+    kinds = {}
+    passes = 5
+    for _ in range(passes):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(comp.steps) + 1)]
+        evs[0].record(stream)
+        for i, s in enumerate(comp.steps):
+            t._launch_step(s)
+            evs[i + 1].record(stream)
+        torch.cuda.synchronize()
+        for i, s in enumerate(comp.steps):
+            k = kinds.setdefault(s.kind, [0.0, 0])
+            k[0] += evs[i].elapsed_time(evs[i + 1])
+            k[1] += 1
+    # end to end
+    for _ in range(2):
+        comp(host)
+    e2e_steps = max(1, min(args.steps, args.e2e_steps * 4))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        res = comp(host)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop()
+    if dist is not None:
+        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
+    if rank != 0:
+        return None
+    ms_step = dev_ms / args.steps
+    peak, which = peaks()
+    item = 2 if flex else 4
+    conv_ms = kinds["conv"][0] / passes                     # all 22 convolutions of one pass
+    conv_bytes = RESNET_CONV_ELEMS_PER_256 * item * n / 256.0
+    conv_gbs = conv_bytes / (conv_ms * 1e-3) / 1e9
+    line = {
+        "metric": "ResNet-20 %s inference img/s" % ("flex16" if flex else "fp32"),
+        "value": round(world * n / (ms_step * 1e-3), 1), "unit": "img/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "flex16 (i16 mantissas, int8 hi/lo tensor-core products, i32 accumulation)"
+                 if flex else "f32 (3xTF32 tensor-core products)",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": n, "image": [3, 32, 32],
+                   "layout": "C,H,W,N", "convolutions": 22, "replicas": world,
+                   "l2": "L2 flushed by the run itself: each pass streams >126 MB of "
+                         "activations and operand planes",
+                   "steps_per_pass": len(comp.steps)},
+        "clocks": clocks,
+        "e2e": {"value": round(world * n / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "img/s",
+                "h2d_bytes_per_step": int(host.nbytes), "d2h_bytes_per_step": int(10 * n * item),
+                "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 3)},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "convolution steps (gather/split + tcgen05 tile "
+                     "kernel), all 22 per pass", "achieved": round(conv_gbs, 1), "peak": peak,
+                     "unit": "GB/s", "frac": round(conv_gbs / peak, 4), "traffic": None,
+                     "peak_source": which, "algorithmic_bytes_per_launch": int(conv_bytes),
+                     "ms": round(conv_ms, 4)},
+        "step_time_ms_by_kind": {k: round(v[0] / passes, 4) for k, v in kinds.items()},
+        "tensor_TOPS_algorithmic": round(RESNET_FLOP_PER_IMG * n * (4 if flex else 3)
+                                         / (conv_ms * 1e-3) / 1e12, 2),
+        "softmax_checksum": float(np.asarray(first).sum()),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = resnet_cpu_baseline(budget_s=12.0)
+    return line
+
+
+def resnet_cpu_baseline(budget_s=12.0, steps=None):
+    cores = os.cpu_count() or 1
+    weights = resnet_weights(0)
+    n = 32
+    x = np.random.RandomState(100).standard_normal((3, 32, 32, n)).astype(np.float32)
+    resnet20_numpy(x, weights)
+    t0 = time.perf_counter()
+    resnet20_numpy(x, weights)
+    dt = time.perf_counter() - t0
+    reps = steps or int(max(1, min(50, budget_s / max(dt, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        resnet20_numpy(x, weights)
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": round(n / dt, 1), "unit": "img/s", "cores": cores, "kind": "port",
+            "sample": "%d passes of a %d-image batch through the numpy restatement of the "
+                      "network (oracle/conv_oracle.py; numpy BLAS threads = all %d cores)"
+                      % (reps, n, cores), "ms_per_step": round(dt * 1e3, 2)}
+
+
 def run_b200(args, rank, world):
     import torch
     import ngraph_python_b200 as ng
@@ -132,6 +363,11 @@ def run_b200(args, rank, world):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.workload.startswith("resnet20"):
+        line = run_resnet(args, rank, world, torch, dist, local)
+        if dist is not None:
+            dist.destroy_process_group()
+        return line
     flex = args.workload == "c2_flex16"
     rows, cols = args.rows, C2_COLS
     t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex)
@@ -274,6 +510,22 @@ def cpu_baseline(workload, budget_s=12.0):
 def run_reference(args, rank, world):
     if rank != 0:
         return None
+    if args.workload.startswith("resnet20"):
+        flex = args.workload == "resnet20_flex16"
+        b = resnet_cpu_baseline(steps=max(1, args.steps))
+        return {
+            "impl": "reference",
+            "metric": "ResNet-20 %s inference img/s" % ("flex16" if flex else "fp32"),
+            "value": b["value"], "unit": "img/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": b["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 (numpy)", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": RESNET_N, "image": [3, 32, 32],
+                       "layout": "C,H,W,N", "convolutions": 22, "replicas": world},
+            "cpu_baseline": b,
+            "e2e": {"value": b["value"], "unit": "img/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
     rows = 256
     gbs, dt, cores = cpu_reference_run(args.workload, rows, max(1, args.steps), max(0, args.warmup))
     flex = args.workload == "c2_flex16"
@@ -301,7 +553,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2_flex16", choices=["c2_flex16", "c2_fp32"])
+    ap.add_argument("--workload", default="resnet20_flex16",
+                    choices=["resnet20_flex16", "resnet20_fp32", "c2_flex16", "c2_fp32"])
+    ap.add_argument("--batch", type=int, default=RESNET_N, help="images per GPU (ResNet-20)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=C2_ROWS,
                     help="rows of the microbenchmark (smaller values are for profiler captures)")

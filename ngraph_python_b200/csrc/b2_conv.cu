@@ -39,51 +39,86 @@ int geom_from(const b2_conv_dims* d, ConvGeom* g) {
 }
 
 // Gather + split.  Rows of the planes: r = (p*Q + q)*N + n ; columns: kidx = (c*R + r_)*S + s_.
-// A block handles 32 rows x 32 columns through shared memory: reads run along n (contiguous in
-// the input), writes along kidx (contiguous in the planes).
+// A block owns 32 consecutive rows (32 images of one output pixel when N is a multiple of 32) and
+// walks the columns in chunks of 128 bytes of plane row.  Per chunk the tap decomposition of each
+// column is computed once into shared memory; loads run along n (contiguous in the input), the
+// write phase emits one 16-byte vector per thread and plane (contiguous along the plane row).
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int rows_p, int kp,
                      void* __restrict__ plane0, void* __restrict__ plane1) {
-    __shared__ T tile[32][33];
+    constexpr int CK = MODE == MODE_FLEX16 ? 128 : 32;
+    __shared__ T tile[CK][33];
+    __shared__ int tab_c[CK], tab_h[CK], tab_w[CK];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
-    const int RS = g.R * g.S;
-    for (int i = ty; i < 32; i += 8) {
-        const int kidx = k0 + i;           // one filter tap / channel per i
-        const int r = r0 + tx;             // consecutive rows = consecutive n
-        T v = 0;
-        if (kidx < kg && r < rows) {
-            const int c = kidx / RS, rs = kidx - c * RS;
-            const int fr = rs / g.S, fs = rs - fr * g.S;
-            const int n = r % g.N, pq = r / g.N;
-            const int q = pq % g.Q, pp = pq / g.Q;
-            const int h = pp * g.str_h - g.pad_h + fr * g.dil_h;
-            const int w = q * g.str_w - g.pad_w + fs * g.dil_w;
-            if (h >= 0 && h < g.H && w >= 0 && w < g.W)
-                v = I[(((long long)c * g.H + h) * g.W + w) * g.N + n];
-        }
-        tile[tx][i] = v;
+    const int r0 = blockIdx.x * 32;
+    const int r = r0 + tx;
+    const bool rvalid = r < rows;
+    int n = 0, h0 = 0, w0 = 0;
+    if (rvalid) {
+        n = r % g.N;
+        const int pq = r / g.N;
+        const int q = pq % g.Q, pp = pq / g.Q;
+        h0 = pp * g.str_h - g.pad_h;
+        w0 = q * g.str_w - g.pad_w;
     }
-    __syncthreads();
-    for (int i = ty; i < 32; i += 8) {
-        const int r = r0 + i, kk = k0 + tx;
-        if (r >= rows_p || kk >= kp) continue;
-        const T v = tile[i][tx];
-        const long long o = (long long)r * kp + kk;
-        if (MODE == MODE_FLEX16) {
-            const int m = (int)v;
-            const int lo = m & 0xff;
-            const int hi = (m - lo) >> 8;
-            ((signed char*)plane0)[o] = (signed char)hi;
-            ((unsigned char*)plane1)[o] = (unsigned char)lo;
-        } else {
-            const float a = (float)v;
-            unsigned hb;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(a));
-            const float hi = __uint_as_float(hb);
-            ((float*)plane0)[o] = hi;
-            ((float*)plane1)[o] = a - hi;
+    const int RS = g.R * g.S;
+    const int wr = threadIdx.x >> 3, vec = threadIdx.x & 7;
+    const int orow = r0 + wr;
+    for (int kc = 0; kc < kp; kc += CK) {
+        __syncthreads();
+        if (threadIdx.x < CK) {
+            const int kidx = kc + threadIdx.x;
+            if (kidx < kg) {
+                const int c = kidx / RS, rs = kidx - c * RS;
+                const int fr = rs / g.S, fs = rs - fr * g.S;
+                tab_c[threadIdx.x] = c * g.H * g.W * g.N;
+                tab_h[threadIdx.x] = fr * g.dil_h;
+                tab_w[threadIdx.x] = fs * g.dil_w;
+            } else {
+                tab_c[threadIdx.x] = -1;
+            }
+        }
+        __syncthreads();
+        for (int i = ty; i < CK; i += 8) {
+            T v = 0;
+            const int tc = tab_c[i];
+            if (tc >= 0 && rvalid) {
+                const int h = h0 + tab_h[i], w = w0 + tab_w[i];
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W)
+                    v = I[(long long)tc + ((long long)h * g.W + w) * g.N + n];
+            }
+            tile[i][tx] = v;
+        }
+        __syncthreads();
+        if (orow < rows_p) {
+            if (MODE == MODE_FLEX16) {
+                unsigned hi[4] = {0, 0, 0, 0}, lo[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = (int)tile[vec * 16 + j][wr];
+                    const int l = m & 0xff;
+                    const int h8 = ((m - l) >> 8) & 0xff;
+                    hi[j >> 2] |= (unsigned)h8 << (8 * (j & 3));
+                    lo[j >> 2] |= (unsigned)l << (8 * (j & 3));
+                }
+                const long long o = (long long)orow * kp + kc + vec * 16;
+                *reinterpret_cast<uint4*>((unsigned char*)plane0 + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>((unsigned char*)plane1 + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            } else {
+                float hi[4], lo[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float a = (float)tile[vec * 4 + j][wr];
+                    unsigned hb;
+                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(a));
+                    hi[j] = __uint_as_float(hb);
+                    lo[j] = a - hi[j];
+                }
+                const long long o = (long long)orow * kp + kc + vec * 4;
+                *reinterpret_cast<float4*>((float*)plane0 + o) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<float4*>((float*)plane1 + o) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+            }
         }
     }
 }
@@ -107,8 +142,8 @@ int run_fprop(const T* I, const T* F, void* O, const b2_conv_dims* d, const b2_f
     unsigned char* base = (unsigned char*)scratch;
     const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
     {
-        dim3 ga((s.Kp + 31) / 32, (s.Mp + 31) / 32);
-        im2col_planes_kernel<T, MODE><<<ga, 256, 0, st>>>(I, g, rows, kg, s.Mp, s.Kp, base,
+        B2_REQUIRE((long long)g.C * g.H * g.W * g.N < (1LL << 31), "input tensor too large");
+        im2col_planes_kernel<T, MODE><<<s.Mp / 32, 256, 0, st>>>(I, g, rows, kg, s.Mp, s.Kp, base,
                                                          base + a_plane);
         // filters: element (n = k_out, k = kidx) = F[kidx * K + k_out]
         dim3 gb((s.Kp + 31) / 32, (s.Np + 31) / 32);

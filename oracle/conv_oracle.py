@@ -1,0 +1,50 @@
+"""CPU restatement of the reference's convolution / pooling forward for C,D,H,W,N tensors.
+
+TEST INFRASTRUCTURE ONLY (tests, smoke check, CPU-baseline legs of the bench).  Follows the numpy
+fallbacks of the reference's CPU engine (ngraph/transformers/cpu/cpuengine.py:234-283 fprop_conv:
+for every output position, dot of the clipped filter slice with the clipped input slice; :285-305
+fprop_pool avg: mean of the clipped window) and ngraph/testing/conv_utils.py:66-102
+(reference_conv).  Written tap-wise instead of position-wise: for every filter tap (r, s) one
+tensordot over channels, which is the same sum in a different order.
+Pinned against the reference CPU transformer's outputs in tests/golden/fixtures (conv_basic,
+conv_stride2_*, resnet*).
+"""
+import numpy as np
+
+
+def conv_fprop(I, F, pad=(0, 0), stride=(1, 1), dtype=np.float32):
+    """I: (C, H, W, N); F: (C, R, S, K) -> O: (K, P, Q, N).  dtype np.int64 gives the exact
+    integer sums used for flex16 mantissas."""
+    C, H, W, N = I.shape
+    C2, R, S, K = F.shape
+    assert C == C2
+    ph, pw = pad
+    sh, sw = stride
+    P = (H + 2 * ph - R) // sh + 1
+    Q = (W + 2 * pw - S) // sw + 1
+    Ip = np.zeros((C, H + 2 * ph, W + 2 * pw, N), dtype=dtype)
+    Ip[:, ph:ph + H, pw:pw + W, :] = I
+    O = np.zeros((K, P, Q, N), dtype=dtype)
+    Ft = F.astype(dtype)
+    for r in range(R):
+        for s in range(S):
+            win = Ip[:, r:r + (P - 1) * sh + 1:sh, s:s + (Q - 1) * sw + 1:sw, :]
+            O += np.tensordot(Ft[:, r, s, :].T, win, axes=([1], [0]))
+    return O
+
+
+def pool_avg_fprop(I, window, pad=(0, 0), stride=(1, 1)):
+    """I: (C, H, W, N) -> (C, P, Q, N): mean over the part of each window inside the image."""
+    C, H, W, N = I.shape
+    R, S = window
+    ph, pw = pad
+    sh, sw = stride
+    P = (H + 2 * ph - R) // sh + 1
+    Q = (W + 2 * pw - S) // sw + 1
+    O = np.zeros((C, P, Q, N), dtype=np.float32)
+    for p in range(P):
+        for q in range(Q):
+            h0, h1 = max(p * sh - ph, 0), min(p * sh - ph + R, H)
+            w0, w1 = max(q * sw - pw, 0), min(q * sw - pw + S, W)
+            O[:, p, q, :] = I[:, h0:h1, w0:w1, :].reshape(C, -1, N).mean(axis=1)
+    return O

@@ -1,0 +1,125 @@
+"""GPU parity of the convolution / pooling entry points through the C ABI.
+
+flex16 with small integer data must equal the exact integer convolution (the reference's own
+flex convolution test asserts np.array_equal on integer inputs in [-4, 4):
+tests/flex_tests/test_flexconv.py:60-70); full-range mantissas are checked against the int64
+oracle with the exact round-to-nearest-even rescale."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import conv_oracle as co
+
+pytestmark = pytest.mark.gpu
+
+# (C, H, W, N, K, R, S, pad, stride): shapes of the reference's flex conv tests plus ResNet-20's
+SHAPES = [(16, 7, 7, 32, 8, 3, 3, 0, 1), (16, 9, 11, 32, 8, 3, 3, 1, 1), (3, 32, 32, 32, 16, 3, 3, 1, 1),
+          (16, 16, 16, 64, 32, 3, 3, 1, 2), (32, 16, 16, 32, 64, 1, 1, 0, 2), (64, 8, 8, 32, 64, 3, 3, 1, 1),
+          (5, 6, 5, 24, 10, 2, 3, 1, 1)]
+
+
+def _dims(lib, Cc, H, W, N, K, R, S, pad, stride):
+    d = lib.ConvDims()
+    P = (H + 2 * pad - R) // stride + 1
+    Q = (W + 2 * pad - S) // stride + 1
+    d.C, d.D, d.H, d.W, d.N = Cc, 1, H, W, N
+    d.K, d.T, d.R, d.S = K, 1, R, S
+    d.M, d.P, d.Q = 1, P, Q
+    d.pad_d, d.pad_h, d.pad_w = 0, pad, pad
+    d.str_d, d.str_h, d.str_w = 1, stride, stride
+    d.dil_d = d.dil_h = d.dil_w = 1
+    return d, P, Q
+
+
+def _scratch(torch, nbytes):
+    t = torch.empty((nbytes + 1024,), dtype=torch.uint8, device="cuda")
+    return t, t.data_ptr() + (-t.data_ptr()) % 1024
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_conv_fprop_f32(shape):
+    import torch
+    from ngraph_python_b200 import lib
+    Cc, H, W, N, K, R, S, pad, stride = shape
+    d, P, Q = _dims(lib, *shape)
+    rng = np.random.RandomState(sum(shape))
+    I = rng.standard_normal((Cc, H, W, N)).astype(np.float32)
+    F = rng.standard_normal((Cc, R, S, K)).astype(np.float32)
+    dI, dF = torch.from_numpy(I).cuda(), torch.from_numpy(F).cuda()
+    dO = torch.zeros((K, P, Q, N), dtype=torch.float32, device="cuda")
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    nb = lib.conv_fprop_scratch_bytes(False, d)
+    keep, sp = _scratch(torch, nb)
+    lib.check(lib.raw().b2_conv_fprop_f32(dI.data_ptr(), dF.data_ptr(), dO.data_ptr(), C.byref(d),
+                                          sp, nb, status.data_ptr(), 0))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    exp = co.conv_fprop(I, F, (pad, pad), (stride, stride), dtype=np.float64)
+    np.testing.assert_allclose(dO.cpu().numpy(), exp, rtol=1e-4, atol=1e-5 * np.sqrt(Cc * R * S) * 4)
+
+
+@pytest.mark.parametrize("small", [True, False])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_conv_fprop_flex16_exact(shape, small):
+    import torch
+    from ngraph_python_b200 import lib
+    Cc, H, W, N, K, R, S, pad, stride = shape
+    d, P, Q = _dims(lib, *shape)
+    rng = np.random.RandomState(sum(shape) + 1)
+    lim = 4 if small else 32767
+    I = rng.randint(-lim, lim, (Cc, H, W, N)).astype(np.int16)
+    F = rng.randint(-lim, lim, (Cc, R, S, K)).astype(np.int16)
+    exact = co.conv_fprop(I, F, (pad, pad), (stride, stride), dtype=np.int64)
+    # small integers: all exponents 0, the output mantissas ARE the integer convolution
+    dec_i = dec_f = 0
+    sh = 0 if small else max(0, int(np.ceil(np.log2(max(1, np.abs(exact).max()) / 32767.0))) + 1)
+    dec_o = dec_i + dec_f - sh
+    dI, dF = torch.from_numpy(I).cuda(), torch.from_numpy(F).cuda()
+    dO = torch.zeros((K, P, Q, N), dtype=torch.int16, device="cuda")
+    table = torch.tensor([[1.0, 1.0], [1.0, 1.0], [2.0 ** -dec_o, 2.0 ** dec_o]],
+                         dtype=torch.float32, device="cuda")
+    stats = torch.zeros((3,), dtype=torch.int32, device="cuda")
+    probe = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    nb = lib.conv_fprop_scratch_bytes(True, d)
+    keep, sp = _scratch(torch, nb)
+    for pr in (1, 0):
+        lib.check(lib.raw().b2_conv_fprop_flex16(
+            dI.data_ptr(), dF.data_ptr(), dO.data_ptr(), C.byref(d), table.data_ptr(), 0, 1, 2,
+            stats.data_ptr(), sp, nb, probe.data_ptr(), status.data_ptr(), pr, 0))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+    assert int(probe.item()) == int(np.abs(exact).max())
+    if sh > 0:
+        half = 1 << (sh - 1)
+        exp = (exact + half - 1 + ((exact >> sh) & 1)) >> sh
+    else:
+        exp = exact
+    exp = np.clip(exp, -32768, 32767)
+    got = dO.cpu().numpy().astype(np.int64)
+    assert np.array_equal(got, exp)
+    assert int(stats[2].item()) == int(np.abs(got).max())
+
+
+@pytest.mark.parametrize("flex", [0, 1])
+def test_pool_avg(flex):
+    import torch
+    from ngraph_python_b200 import lib
+    Cc, H, W, N = 64, 8, 8, 32
+    rng = np.random.RandomState(5)
+    if flex:
+        x = rng.randint(-30000, 30000, (Cc, H, W, N)).astype(np.int16)
+    else:
+        x = rng.standard_normal((Cc, H, W, N)).astype(np.float32)
+    dx = torch.from_numpy(x).cuda()
+    out = torch.zeros((Cc, 1, 1, N), dtype=dx.dtype, device="cuda")
+    stat = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    lib.check(lib.raw().b2_pool_avg_fprop(dx.data_ptr(), out.data_ptr(), flex, Cc, H, W, N, 1, 1,
+                                          8, 8, 0, 0, 1, 1, stat.data_ptr(), 0))
+    torch.cuda.synchronize()
+    exp = co.pool_avg_fprop(x.astype(np.float32), (8, 8))
+    if flex:
+        assert np.abs(out.cpu().numpy().astype(np.float64) - exp).max() <= 0.5 + 1e-3
+    else:
+        np.testing.assert_allclose(out.cpu().numpy(), exp, rtol=1e-5, atol=1e-5)
