@@ -1,0 +1,172 @@
+"""Gradient allreduce for data-parallel training: flat buckets over NCCL, overlapped with compute.
+
+Takes the place of hetr's GPU allreduce, CudaAllReduceKernel
+(ngraph/transformers/gpu/tensor_ops.py:428-618): per gradient tensor, a reduce-scatter by
+peer-to-peer memcpy into peer scratch, a float_accum kernel, an all-gather by peer-to-peer memcpy,
+three MPI barriers and host synchronisations, with no overlap with back-propagation.
+
+Here every tensor that goes through an allreduce lives inside one flat arena, cut into buckets of at
+most `bucket_bytes` (25 MB by default) in the order the tensors are produced.  When the last tensor
+of a bucket has been produced, ONE collective is started for the whole bucket on the communication
+stream (torch.distributed: NCCL over NVLink/NVSwitch on GPUs, gloo in CPU tests); the compute
+stream only waits for it right before the first consumer of a reduced tensor, so the exchange
+overlaps the remaining back-propagation.  `reduce_func` is 'sum' or 'mean' as in the reference's
+kernel (tensor_ops.py:95-108).
+
+One process per GPU; the process group is created by the caller (torchrun) and handed in.
+"""
+import numpy as np
+
+DEFAULT_BUCKET_BYTES = 25 * 1024 * 1024
+ALIGN_ELEMS = 64          # every tensor starts on a 256-byte boundary inside the arena
+
+
+class BucketPlan(object):
+    """Assigns tensors (given in production order as (key, n_elements)) to arena offsets and
+    buckets.  A tensor never straddles two buckets; a tensor larger than the limit gets a bucket
+    of its own."""
+
+    def __init__(self, sizes, bucket_bytes=DEFAULT_BUCKET_BYTES, itemsize=4):
+        self.offsets = {}
+        self.bucket_of = {}
+        self.buckets = []          # (start_elem, end_elem, [keys])
+        limit = max(1, int(bucket_bytes) // itemsize)
+        cur_start, cur_end, cur_keys = 0, 0, []
+        for key, n in sizes:
+            n_pad = -(-int(n) // ALIGN_ELEMS) * ALIGN_ELEMS
+            if cur_keys and (cur_end - cur_start) + n_pad > limit:
+                self.buckets.append((cur_start, cur_end, cur_keys))
+                cur_start, cur_keys = cur_end, []
+            self.offsets[key] = cur_end
+            self.bucket_of[key] = len(self.buckets)
+            cur_keys.append(key)
+            cur_end += n_pad
+        if cur_keys:
+            self.buckets.append((cur_start, cur_end, cur_keys))
+        self.total = cur_end
+
+
+class TorchDistComm(object):
+    """Thin wrapper over an initialised torch.distributed process group."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised: launch one process per GPU "
+                               "(torchrun) and call init_process_group first")
+        self.dist = dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+
+    def Get_rank(self):          # the reference passes an mpi4py-style comm (hetrtransform.py:38-57)
+        return self.rank
+
+    def Get_size(self):
+        return self.size
+
+    def all_reduce_async(self, flat, reduce_func="sum"):
+        """Starts an in-place allreduce of a flat tensor; returns a handle with .wait()."""
+        if reduce_func not in ("sum", "mean"):
+            raise ValueError("unsupported reduce_func %r" % (reduce_func,))
+        work = self.dist.all_reduce(flat, op=self.dist.ReduceOp.SUM, group=self.group,
+                                    async_op=True)
+        return _Pending(work, flat, self.size if reduce_func == "mean" else 1)
+
+
+class _Pending(object):
+    def __init__(self, work, flat, divisor):
+        self.work, self.flat, self.divisor = work, flat, divisor
+        self.done = False
+
+    def wait(self):
+        """Makes the current stream wait for the collective (does not block the host on GPUs)."""
+        if self.done:
+            return
+        self.work.wait()
+        if self.divisor != 1:
+            self.flat.div_(self.divisor)
+        self.done = True
+
+
+class SingleProcessComm(object):
+    """World of one: the allreduce is the identity.  Lets a graph with allreduce ops run
+    unchanged on a single GPU."""
+    rank, size = 0, 1
+
+    def Get_rank(self):
+        return 0
+
+    def Get_size(self):
+        return 1
+
+    def all_reduce_async(self, flat, reduce_func="sum"):
+        if reduce_func not in ("sum", "mean"):
+            raise ValueError("unsupported reduce_func %r" % (reduce_func,))
+        return _Done()
+
+
+class _Done(object):
+    def wait(self):
+        return
+
+
+class BucketedAllReduce(object):
+    """Run-time state of the bucketed exchange for one computation.
+
+    Tensors are produced in arena order.  A bucket's collective normally starts when its last
+    tensor has been produced; if a consumer needs a reduced tensor earlier (an optimizer update
+    whose result feeds the rest of back-propagation), the part of the bucket produced so far is
+    exchanged at that point and the remainder later.  Every replica runs the same step list, so
+    all of them issue the same sequence of collectives."""
+
+    def __init__(self, comm, plan, arena, reduce_funcs):
+        self.comm = comm
+        self.plan = plan
+        self.arena = arena                      # flat fp32 torch tensor of plan.total elements
+        self.reduce_funcs = reduce_funcs        # key -> 'sum' | 'mean'
+        self.sizes = {}
+        for start, end, keys in plan.buckets:
+            for i, k in enumerate(keys):
+                nxt = plan.offsets[keys[i + 1]] if i + 1 < len(keys) else end
+                self.sizes[k] = nxt - plan.offsets[k]
+        self.started = 0
+        self.begin_call()
+
+    def begin_call(self):
+        self.pending = [[] for _ in self.plan.buckets]          # (start, end, handle)
+        self.launched_upto = [b[0] for b in self.plan.buckets]
+        self.produced_upto = [b[0] for b in self.plan.buckets]
+        self.produced_keys = [[] for _ in self.plan.buckets]
+
+    def produced(self, key):
+        b = self.plan.bucket_of[key]
+        self.produced_upto[b] = self.plan.offsets[key] + self.sizes[key]
+        self.produced_keys[b].append(key)
+
+    def flush(self, b):
+        start, end = self.launched_upto[b], self.produced_upto[b]
+        if end <= start:
+            return
+        funcs = set(self.reduce_funcs[k] for k in self.produced_keys[b]
+                    if self.plan.offsets[k] >= start)
+        if len(funcs) != 1:
+            raise ValueError("tensors exchanged together must share a reduce_func")
+        self.pending[b].append((start, end,
+                                self.comm.all_reduce_async(self.arena[start:end], funcs.pop())))
+        self.launched_upto[b] = end
+        self.started += 1
+
+    def bucket_ready(self, index):
+        """All tensors of bucket `index` have been produced: exchange what is left of it."""
+        self.flush(index)
+
+    def wait_for(self, key):
+        """Called before the first consumer of the reduced tensor `key`."""
+        b = self.plan.bucket_of[key]
+        off = self.plan.offsets[key]
+        if off >= self.launched_upto[b]:
+            self.flush(b)
+        for start, end, handle in self.pending[b]:
+            if start <= off < end:
+                handle.wait()

@@ -218,3 +218,35 @@ class PoolStep(_Step):
         lib.check(lib.raw().b2_pool_avg_fprop(self._ptr(iv), self._ptr(ov), int(self.flex),
                                               *(self.args + (stats, t.stream.cuda_stream))))
         t.kernel_launches += 1
+
+
+class CommStep(_Step):
+    """One tensor's share of a bucketed allreduce (see comm.py).  The tensor lives inside the
+    flat fp32 arena; when this step is the last of its bucket the collective for the whole bucket
+    is started.  In flex mode the int16 gradient is first de-quantised into the arena."""
+    kind = "comm"
+    launches = 0
+
+    def __init__(self, index, op, t, src_view, arena_buffer):
+        super(CommStep, self).__init__(index, op)
+        self.key = id(arena_buffer)
+        self.src_view = src_view            # flex: the int16 tensor to de-quantise; else None
+        self.arena_buffer = arena_buffer    # fp32 Buffer placed in the arena
+        self.in_views = [src_view] if src_view is not None else []
+        self.out_views = []
+        self.closes_bucket = None           # set when the bucket plan is known
+        self.launches = 1 if src_view is not None else 0
+
+    def output_buffers(self):
+        return []
+
+    def launch(self, t):
+        if self.src_view is not None:
+            v = self.src_view
+            lib.check(lib.raw().b2_flex_dequantize(
+                self._ptr(v), self.arena_buffer.ptr(), v.buffer.size, t._table.data_ptr(),
+                t._slot_for_read(v.buffer, self), t.stream.cuda_stream))
+            t.kernel_launches += 1
+        t._allreduce.produced(self.key)
+        if self.closes_bucket is not None:
+            t._allreduce.bucket_ready(self.closes_bucket)

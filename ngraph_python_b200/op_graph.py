@@ -551,6 +551,25 @@ def pooling(pool_params, inputs, axes, **kw):
     return PoolingOp(pool_params, inputs, make_axes(axes), **kw)
 
 
+# ---- communication ----------------------------------------------------------------------------
+class AllReduceOp(Op):
+    """Sum (or mean) of a tensor over all data-parallel replicas; every replica gets the result
+    (ngraph/op_graph/comm_nodes.py:347-383 GPUCudaAllReduceOp; inserted by hetr wherever an
+    argument carries reduce_func and its consumer does not,
+    ngraph/factory/comm_node_factory.py:298-341)."""
+
+    def __init__(self, x, reduce_func="sum", **kw):
+        x = as_op(x)
+        if reduce_func not in ("sum", "mean"):
+            raise ValueError("unsupported reduce_func %r" % (reduce_func,))
+        super(AllReduceOp, self).__init__((x,), x.axes, **kw)
+        self.reduce_func = reduce_func
+
+
+def allreduce(x, reduce_func="sum"):
+    return AllReduceOp(x, reduce_func)
+
+
 # ---- state and control ------------------------------------------------------------------------
 class AssignOp(Op):
     """tensor <- value (ngraph/op_graph/op_graph.py: AssignOp)."""

@@ -20,7 +20,9 @@ from . import flex as flexmod
 from . import fusion
 from . import kernels
 from . import lib
-from .op_graph import (AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp, ConvolutionOp, DotOp,
+from . import comm as commmod
+from .op_graph import (AllReduceOp, AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp,
+                       ConvolutionOp, DotOp,
                        ElementWiseOp, Op, PoolingOp, ReductionOp, ReorderAxes, SequentialOp,
                        ViewOp, as_op, make_axes)
 
@@ -211,10 +213,14 @@ class _Planner(object):
 
     # -- helpers ------------------------------------------------------------------------------
     def _resolve(self, op):
-        """Follows SequentialOp to the op that carries the value."""
-        while isinstance(op, SequentialOp):
-            op = op.value_tensor
-        return op
+        """Follows SequentialOp (and planner-made replacements) to the op that carries the value."""
+        while True:
+            if isinstance(op, SequentialOp):
+                op = op.value_tensor
+            elif op in self.t._alias:
+                op = self.t._alias[op]
+            else:
+                return op
 
     def _is_scalar_const(self, op):
         return isinstance(op, AssignableTensorOp) and op.is_scalar_constant
@@ -244,10 +250,14 @@ class _Planner(object):
         for op in ordered:
             if isinstance(op, (ElementWiseOp, ReductionOp, AssignOp)):
                 self._place_ew(op)
+            elif isinstance(op, AllReduceOp):
+                self._place_allreduce(op)
             elif isinstance(op, (AssignableTensorOp, ViewOp, SequentialOp)):
                 continue
             else:
                 self._place_other(op)
+        # replacements made while placing (allreduce) change what the returns resolve to
+        self.returned = set(self._base_tensor(r)[0] for r in returns)
         # decide what each group materialises
         for step in self.steps:
             if step.kind == "ew":
@@ -376,6 +386,46 @@ class _Planner(object):
         if len(g.stored) + 1 > fusion.MAX_OUT - 1:      # one spare for a later outside consumer
             return False
         return True
+
+    def _place_allreduce(self, op):
+        """fp32: the producer's buffer is placed in the communication arena and reduced in
+        place.  flex16: the int16 gradient is de-quantised into an fp32 arena slot, reduced
+        there, and re-quantised by an ordinary fused kernel, so every replica derives the same
+        exponent from the same reduced values."""
+        t = self.t
+        src, chain = self._base_tensor(op.args[0])
+        if chain or isinstance(src, AssignableTensorOp):
+            raise ValueError("Unhandled op: allreduce of a view or of a variable: {}".format(op))
+        if src in self.group_of:
+            self.group_of[src].stored.add(src)
+        index = self._new_step_index()
+        src_view = t._view_of(src)
+        if not t.flex:
+            buf = src_view.buffer
+            buf.in_arena = True
+            buf.comm_key = id(buf)
+            step = kernels.CommStep(index, op, t, None, buf)
+            t._alias[op] = src                 # consumers read the same (now reduced) buffer
+            t._views[op] = src_view
+            self.producer[src] = max(self.producer.get(src, -1), index)
+        else:
+            from .op_graph import AssignableTensorOp as _A
+            staging = _A(op.axes, name=op.name + "_f32")
+            sbuf = Buffer(staging.name, op.axes, False, persistent=True)
+            sbuf.in_arena = True
+            sbuf.comm_key = id(sbuf)
+            sbuf.entry = None
+            t._buffers[staging] = sbuf
+            step = kernels.CommStep(index, op, t, src_view, sbuf)
+            sbuf.last_write_step = index
+            requant = ElementWiseOp("assign", (staging,))
+            t._alias[op] = requant
+        step.reduce_func = op.reduce_func
+        self.steps.append(step)
+        self.producer[op] = index
+        t._comm_steps.append(step)
+        if t.flex:
+            self._place_ew(requant)
 
     def _place_other(self, op):
         """Dense contractions and pooling: one step each, never fused with neighbours."""
@@ -593,6 +643,11 @@ class B200Transformer(object):
         self.fixed_point = bool(fixed_point)
         self.flex_manager = flexmod.FlexManager(fixed_point=fixed_point, verbose=flex_verbose)
         self.computations = []
+        self.comm = kwargs.pop("comm", None) or commmod.SingleProcessComm()
+        self.bucket_bytes = int(kwargs.pop("bucket_bytes", commmod.DEFAULT_BUCKET_BYTES))
+        self._alias = {}
+        self._comm_steps = []
+        self._allreduce = None
         self._buffers = collections.OrderedDict()   # op -> Buffer
         self._views = {}
         self.finalized = False
@@ -670,8 +725,8 @@ class B200Transformer(object):
         return b
 
     def _view_of(self, op):
-        while isinstance(op, SequentialOp):
-            op = op.value_tensor
+        while isinstance(op, SequentialOp) or op in self._alias:
+            op = op.value_tensor if isinstance(op, SequentialOp) else self._alias[op]
         v = self._views.get(op)
         if v is not None:
             return v
@@ -721,6 +776,23 @@ class B200Transformer(object):
         if self.plan_only:
             return
         torch = self.torch
+        if self._comm_steps and self._allreduce is None:
+            # every tensor that is exchanged lives in one flat fp32 arena, bucketed in the order
+            # the tensors are produced
+            steps = sorted(self._comm_steps, key=lambda s: s.index)
+            plan = commmod.BucketPlan([(s.key, s.arena_buffer.size) for s in steps],
+                                      self.bucket_bytes)
+            arena = torch.zeros((max(plan.total, 1),), dtype=torch.float32, device=self.device)
+            funcs = {}
+            last_of_bucket = {}
+            for s in steps:
+                off = plan.offsets[s.key]
+                s.arena_buffer.tensor = arena[off:off + max(s.arena_buffer.size, 1)]
+                funcs[s.key] = s.reduce_func
+                last_of_bucket[plan.bucket_of[s.key]] = s
+            for b_index, s in last_of_bucket.items():
+                s.closes_bucket = b_index
+            self._allreduce = commmod.BucketedAllReduce(self.comm, plan, arena, funcs)
         for op, b in self._buffers.items():
             if b.tensor is None:
                 dt = torch.int16 if b.flex else torch.float32
@@ -790,6 +862,8 @@ class B200Transformer(object):
         (flexgputransform.py:178-181)."""
         buf = view.buffer
         flat = buf.tensor
+        if self._allreduce is not None and getattr(buf, "comm_key", None) is not None:
+            self._allreduce.wait_for(buf.comm_key)
         if view.is_dense():
             host = flat.cpu().numpy().reshape(view.axes.lengths)
         else:
@@ -809,12 +883,14 @@ class B200Transformer(object):
 
     def _begin_call(self, comp):
         self._ensure_scratch()
+        if self._allreduce is not None:
+            self._allreduce.begin_call()
         if not self.flex:
             return
         self.flex_manager.autoflex_count += 1
         written = set(id(b) for b in comp.written)
         for b in self._buffers.values():
-            if getattr(b, "shares_entry", False):
+            if getattr(b, "shares_entry", False) or b.entry is None:
                 continue
             e = b.entry
             dec_stored = e.dec
@@ -841,6 +917,11 @@ class B200Transformer(object):
 
     # ---- launching -------------------------------------------------------------------------------
     def _launch_step(self, step):
+        if self._allreduce is not None:
+            for v in step.in_views:
+                key = getattr(v.buffer, "comm_key", None)
+                if key is not None and step.kind != "comm":
+                    self._allreduce.wait_for(key)      # first consumer of a reduced tensor
         if step.kind == "ew":
             self._launch_ew(step)
         else:

@@ -251,7 +251,68 @@ def resnet8_small(ng):
     return resnet20(ng, n=32, hw=16, blocks=1)
 
 
+def mlp_train_step(ng, global_n=128, shard=None, dims=(64, 48, 32, 10), lr=0.05):
+    """One data-parallel SGD step of a 3-layer MLP with softmax cross-entropy, gradients written
+    out by hand (BASELINE configs 1 and 5 in miniature).  Every replica sees `shard = (rank,
+    world)` of the global batch, scales its gradients by 1/global batch (the reference's optimizer
+    divides by the global batch size, ngraph/frontends/neon/optimizer.py:177-198) and sum-allreduces
+    them; with one replica the allreduce is the identity.  Returns the post-step weights and the
+    pre-step mean loss."""
+    allreduce = getattr(ng, "allreduce", None) or (lambda x, reduce_func="sum": x)
+    rank, world = shard or (0, 1)
+    local_n = global_n // world
+    r = _rng(0)
+    Fd, H1d, H2d, Yd = dims
+    N = ng.make_axis(local_n, name="N")
+    F, H1, H2, Y = [ng.make_axis(d, name=nm) for d, nm in zip(dims, ("F", "H1", "H2", "Y"))]
+    x = ng.placeholder([F, N])
+    t = ng.placeholder([Y, N])
+
+    def weights(out_ax, in_ax):
+        w = ng.variable([out_ax, in_ax], initial_value=(
+            r.standard_normal((out_ax.length, in_ax.length)) *
+            np.sqrt(2.0 / in_ax.length)).astype(np.float32))
+        b = ng.variable([out_ax], initial_value=(r.standard_normal(out_ax.length) *
+                                                 0.1).astype(np.float32))
+        return w, b
+    W1, b1 = weights(H1, F)
+    W2, b2 = weights(H2, H1)
+    W3, b3 = weights(Y, H2)
+    z1 = ng.dot(W1, x) + b1
+    a1 = ng.maximum(z1, 0.0)
+    z2 = ng.dot(W2, a1) + b2
+    a2 = ng.maximum(z2, 0.0)
+    z3 = ng.dot(W3, a2) + b3
+    e = ng.exp(z3 - ng.max(z3, reduction_axes=[Y]))
+    p = e / ng.sum(e, reduction_axes=[Y])
+    inv_n = 1.0 / global_n
+    loss = allreduce(ng.sum(ng.negative(ng.sum(t * ng.log(p), reduction_axes=[Y])),
+                            reduction_axes=[N]) * inv_n)
+    dz3 = (p - t) * inv_n
+    dW3 = ng.dot(dz3, a2)                      # [Y, H2], contracts N
+    db3 = ng.sum(dz3, reduction_axes=[N])
+    da2 = ng.dot(W3, dz3)                      # [H2, N], contracts Y
+    dz2 = da2 * ng.greater(z2, 0.0)
+    dW2 = ng.dot(dz2, a1)
+    db2 = ng.sum(dz2, reduction_axes=[N])
+    da1 = ng.dot(W2, dz2)
+    dz1 = da1 * ng.greater(z1, 0.0)
+    dW1 = ng.dot(dz1, x)
+    db1 = ng.sum(dz1, reduction_axes=[N])
+    updates = []
+    for w, g in ((W3, dW3), (b3, db3), (W2, dW2), (b2, db2), (W1, dW1), (b1, db1)):
+        updates.append(ng.assign(w, w - lr * allreduce(g)))
+    step = ng.sequential(updates + [loss])
+    outs = [step, W1, W2, W3, b3]
+    rng = _rng(3)
+    xs = rng.uniform(0, 1, (Fd, global_n)).astype(np.float32)
+    labels = np.eye(Yd, dtype=np.float32)[rng.randint(0, Yd, global_n)].T.copy()
+    lo, hi = rank * local_n, (rank + 1) * local_n
+    return outs, [x, t], [np.ascontiguousarray(xs[:, lo:hi]), np.ascontiguousarray(labels[:, lo:hi])]
+
+
 CASES = {
+    "mlp_train_step": mlp_train_step,
     "conv_basic": conv_basic,
     "conv_stride2_1x1": conv_stride2_1x1,
     "conv_stride2_3x3": conv_stride2_3x3,
@@ -269,4 +330,4 @@ CASES = {
     "assign_sequence": assign_sequence,
 }
 # cases evaluated twice in a row (state carried by variables)
-REPEAT = {"assign_sequence": 2}
+REPEAT = {"assign_sequence": 2, "mlp_train_step": 2}

@@ -1,0 +1,112 @@
+"""Data-parallel training step on GPUs: gradients exchanged by the bucketed NCCL allreduce must
+give the same post-step weights as the reference CPU transformer on the global batch
+(the reference asserts the same for hetr vs cpu, tests/hetr_tests/test_hetr_mnist.py:89-104).
+
+One GPU: the allreduce is the identity.  Two GPUs (skipped when only one is visible): one process
+per GPU, each sees half of the batch."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import ngraph_python_b200 as ng
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+FIX = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fixtures")
+
+
+def _check(results, fix, rtol=1e-4, atol=2e-5):
+    for rep, res in enumerate(results):
+        for k, got in enumerate(res):
+            np.testing.assert_allclose(got, fix["out%d_%d" % (rep, k)], rtol=rtol, atol=atol,
+                                       err_msg="output %d call %d" % (k, rep))
+
+
+def test_train_step_single_gpu_fp32():
+    fix = np.load(os.path.join(FIX, "mlp_train_step.npz"))
+    outs, params, vals = cases.mlp_train_step(ng)
+    t = ng.transformers.allocate_transformer("b200", bucket_bytes=8192)
+    comp = t.computation(outs, *params)
+    results = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
+    assert t._allreduce is not None and len(t._allreduce.plan.buckets) >= 2
+    _check(results, fix)
+    t.close()
+
+
+def test_train_step_single_gpu_flex16():
+    fix = np.load(os.path.join(FIX, "mlp_train_step.npz"))
+    outs, params, vals = cases.mlp_train_step(ng)
+    t = ng.transformers.allocate_transformer("b200", flex=True)
+    comp = t.computation(outs, *params)
+    results = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
+    # flex16 weights: 15-bit mantissas, so compare at the flex tolerance of each tensor
+    for rep, res in enumerate(results):
+        for k, got in enumerate(res):
+            exp = fix["out%d_%d" % (rep, k)]
+            scale = float(np.max(np.abs(exp))) * 2.0 ** -14
+            np.testing.assert_allclose(got, exp, rtol=2e-2, atol=16 * scale)
+    t.close()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, flex, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        from ngraph_python_b200.comm import TorchDistComm
+        outs, params, vals = cases.mlp_train_step(ng, shard=(rank, world))
+        t = ng.transformers.allocate_transformer("b200", device_id=rank, flex=flex,
+                                                 comm=TorchDistComm(), bucket_bytes=8192)
+        comp = t.computation(outs, *params)
+        results = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
+        q.put((rank, results))
+        dist.barrier()
+        t.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("flex", [False, True])
+def test_train_step_two_gpus(flex):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    fix = np.load(os.path.join(FIX, "mlp_train_step.npz"))
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, flex, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank in (0, 1):
+        if flex:
+            for rep, res in enumerate(got[rank]):
+                for k, g in enumerate(res):
+                    exp = fix["out%d_%d" % (rep, k)]
+                    scale = float(np.max(np.abs(exp))) * 2.0 ** -14
+                    np.testing.assert_allclose(g, exp, rtol=2e-2, atol=16 * scale)
+        else:
+            _check(got[rank], fix)
+    # replicas stay identical, bit for bit
+    for a, b in zip(got[0], got[1]):
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
