@@ -17,6 +17,8 @@
 // N (batch) is the GEMM-M direction (128 rows per tile), the output channels are the GEMM-N
 // direction with a 16/32/64/128-wide tile, so the small channel counts of ResNet-20 do not pad
 // the tensor-core tile to 128.
+#include <cstdlib>
+
 #include "b2_gemm_impl.cuh"
 
 namespace {
@@ -123,6 +125,426 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
     }
 }
 
+// ================================================================================================
+// Implicit GEMM: no unrolled copy of the input.
+//
+// For batches that are a multiple of 128 the tile kernel reads the activations straight from
+// their C,H,W,N layout.  A tile is one output pixel (p,q) x 128 images.  The reduction runs over
+// units of (filter tap, block of 32 channels); for every unit ONE 4-d TMA box
+// [32 channels][128 images] is fetched from the operand plane at (c0, h, w, n0) with
+// h = p*str - pad + r*dil (zero fill outside the image does the padding), and lands in shared
+// memory as an MN-major (images contiguous) swizzled operand.  The filter planes are K-major with
+// their columns in the same (tap, channel block, channel) order.  CTAs are persistent: each
+// walks many tiles, the producer warp runs ahead across tile boundaries, and the accumulators are
+// double-buffered in tensor memory so the epilogue of one tile overlaps the MMAs of the next.
+// The only pre-pass is an elementwise split of the activations into the two operand planes.
+// ================================================================================================
+struct ConvTileParams {
+    int P, Q, N, K, S;
+    int pad_h, pad_w, str_h, str_w, dil_h, dil_w;
+    int cchunks, units, stages_per_tile, num_tiles, nblk;
+    long long ldc;
+    void* O;
+    const b2_flex_scale* table;
+    int slotA, slotB, slotC;
+    int* stats;
+    unsigned long long* probe_out;
+    int* status;
+    int probe;
+};
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            int c2, int c3, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// MN-major operand, 128-byte swizzle: 8-row K groups `sbo` bytes apart, MN atoms `lbo` bytes apart
+__device__ __forceinline__ unsigned long long make_smem_desc_mn(const void* p, unsigned lbo,
+                                                                unsigned sbo) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(p) >> 4) & 0x3FFF);
+    d |= (unsigned long long)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (unsigned long long)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+
+template <int MODE, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
+                     const __grid_constant__ CUtensorMap mapI1,
+                     const __grid_constant__ CUtensorMap mapB0,
+                     const __grid_constant__ CUtensorMap mapB1, const ConvTileParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int kStageBytes = stage_bytes(BN);
+    constexpr int kBPlane = BN * kKBytes;
+    constexpr int kAcc = (MODE == MODE_FLEX16 ? 3 : 1) * BN;       // columns per accumulator set
+    constexpr int kNBuf = (2 * kAcc <= 512) ? 2 : 1;
+    constexpr int kCols = tmem_cols(MODE, BN) * kNBuf > 512 ? 512 : tmem_cols(MODE, BN) * kNBuf;
+    unsigned long long* full_bar = (unsigned long long*)(smem + kStages * kStageBytes);
+    unsigned long long* empty_bar = full_bar + kStages;
+    unsigned long long* tmem_full = empty_bar + kStages;      // [2]
+    unsigned long long* tmem_empty = tmem_full + 2;           // [2]
+    unsigned* tmem_holder = (unsigned*)(tmem_empty + 2);
+    int* fail_flag = (int*)(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ncol0 = blockIdx.y * BN;                        // first output channel of this CTA
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+        *fail_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, kCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                const int pq = tile / p.nblk, nb = tile - pq * p.nblk;
+                const int pp = pq / p.Q, q = pq - pp * p.Q;
+                const int n0 = nb * 128;
+                const int h0 = pp * p.str_h - p.pad_h, w0 = q * p.str_w - p.pad_w;
+                for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
+                    const int s = g % kStages;
+                    if (g >= kStages && !mbar_wait(&empty_bar[s], ((g / kStages) - 1) & 1)) {
+                        atomicExch(fail_flag, 1); ok = false; break;
+                    }
+                    unsigned char* sa = smem + s * kStageBytes;
+                    mbar_expect_tx(&full_bar[s], kStageBytes);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        // int8: four units of 32 channels per stage; tf32: one unit, four blocks
+                        // of 32 images
+                        int u = MODE == MODE_FLEX16 ? st * 4 + j : st;
+                        if (u >= p.units) u = 0;       // padding unit: its filter columns are zero
+                        const int tap = u / p.cchunks, cc = u - tap * p.cchunks;
+                        const int fr = tap / p.S, fs = tap - fr * p.S;
+                        const int h = h0 + fr * p.dil_h, w = w0 + fs * p.dil_w;
+                        const int nn = MODE == MODE_FLEX16 ? n0 : n0 + j * 32;
+                        tma_load_4d(sa + j * 4096, &mapI0, nn, w, h, cc * 32, &full_bar[s]);
+                        tma_load_4d(sa + kPlaneBytes + j * 4096, &mapI1, nn, w, h, cc * 32,
+                                    &full_bar[s]);
+                    }
+                    const int kx = st * (MODE == MODE_FLEX16 ? kKBytes : kKBytes / 4);
+                    tma_load_2d(sa + 2 * kPlaneBytes, &mapB0, kx, ncol0, &full_bar[s]);
+                    tma_load_2d(sa + 2 * kPlaneBytes + kBPlane, &mapB1, kx, ncol0, &full_bar[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // bit 15: A is MN-major
+            const unsigned mn = 1u << 15;
+            const unsigned id_ss = make_idesc(2, 1, 1, BN) | mn, id_su = make_idesc(2, 1, 0, BN) | mn,
+                           id_us = make_idesc(2, 0, 1, BN) | mn, id_uu = make_idesc(2, 0, 0, BN) | mn;
+            const unsigned id_tf = make_idesc(1, 2, 2, BN) | mn;
+            int g = 0, ti = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
+                const int buf = ti % kNBuf;
+                const unsigned acc_base = tmem_base + buf * kAcc;
+                if (ti >= kNBuf && !mbar_wait(&tmem_empty[buf], ((ti / kNBuf) - 1) & 1)) {
+                    atomicExch(fail_flag, 1); ok = false; break;
+                }
+                tc_fence_after();
+                for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
+                    const int s = g % kStages;
+                    if (!mbar_wait(&full_bar[s], (g / kStages) & 1)) {
+                        atomicExch(fail_flag, 1); ok = false; break;
+                    }
+                    tc_fence_after();
+                    unsigned char* sa = smem + s * kStageBytes;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const unsigned acc = (st > 0 || k > 0) ? 1u : 0u;
+                        const unsigned long long badv = (unsigned long long)((k * 32) >> 4);
+                        const unsigned long long dB0 = make_smem_desc(sa + 2 * kPlaneBytes) + badv;
+                        const unsigned long long dB1 =
+                            make_smem_desc(sa + 2 * kPlaneBytes + kBPlane) + badv;
+                        if (MODE == MODE_FLEX16) {
+                            const unsigned long long dA0 = make_smem_desc_mn(sa + k * 4096, 0, 1024);
+                            const unsigned long long dA1 =
+                                make_smem_desc_mn(sa + kPlaneBytes + k * 4096, 0, 1024);
+                            tc_mma<MODE>(acc_base + 0, dA0, dB0, id_ss, acc);
+                            tc_mma<MODE>(acc_base + BN, dA0, dB1, id_su, acc);
+                            tc_mma<MODE>(acc_base + BN, dA1, dB0, id_us, 1u);
+                            tc_mma<MODE>(acc_base + 2 * BN, dA1, dB1, id_uu, acc);
+                        } else {
+                            const unsigned long long dA0 = make_smem_desc_mn(sa + k * 1024, 4096, 1024);
+                            const unsigned long long dA1 =
+                                make_smem_desc_mn(sa + kPlaneBytes + k * 1024, 4096, 1024);
+                            tc_mma<MODE>(acc_base, dA0, dB0, id_tf, acc);
+                            tc_mma<MODE>(acc_base, dA0, dB1, id_tf, 1u);
+                            tc_mma<MODE>(acc_base, dA1, dB0, id_tf, 1u);
+                        }
+                    }
+                    tc_commit(&empty_bar[s]);
+                }
+                tc_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int stat = 0;
+        unsigned long long pmax = 0;
+        int sh = 0;
+        if (MODE == MODE_FLEX16) {
+            const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
+                            (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
+            sh = -ilogbf(f);
+        }
+        int ti = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++ti) {
+            const int buf = ti % kNBuf;
+            if (ok && !mbar_wait(&tmem_full[buf], (ti / kNBuf) & 1)) { atomicExch(fail_flag, 1); ok = false; }
+            tc_fence_after();
+            const long long row = (long long)tile * 128 + quarter * 32 + lane;   // (pq*N + n)
+            const unsigned lane_addr = tmem_base + buf * kAcc + ((unsigned)(quarter * 32) << 16);
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (MODE == MODE_FLEX16) {
+                    unsigned hh[16], xx[16], ll[16];
+                    tmem_ld16(lane_addr + c0, hh);
+                    tmem_ld16(lane_addr + BN + c0, xx);
+                    tmem_ld16(lane_addr + 2 * BN + c0, ll);
+                    tmem_ld_wait();
+                    if (!ok) continue;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int col = ncol0 + c0 + j;
+                        const long long v = ((long long)(int)hh[j] << 16) +
+                                            ((long long)(int)xx[j] << 8) + (long long)(int)ll[j];
+                        if (p.probe) {
+                            const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
+                            if (col < p.K) pmax = a > pmax ? a : pmax;
+                        } else if (col < p.K) {
+                            const int qv = rescale_i64(v, sh);
+                            const int a = qv < 0 ? -qv : qv;
+                            stat = a > stat ? a : stat;
+                            ((short*)p.O)[(long long)col * p.ldc + row] = (short)qv;
+                        }
+                    }
+                } else {
+                    unsigned acc[16];
+                    tmem_ld16(lane_addr + c0, acc);
+                    tmem_ld_wait();
+                    if (!ok) continue;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int col = ncol0 + c0 + j;
+                        if (col < p.K)
+                            ((float*)p.O)[(long long)col * p.ldc + row] = __uint_as_float(acc[j]);
+                    }
+                }
+            }
+            // this warp has read its part of the accumulator buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+        if (MODE == MODE_FLEX16) {
+            if (p.probe) {
+                for (int o = 16; o > 0; o >>= 1) {
+                    const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
+                    pmax = t > pmax ? t : pmax;
+                }
+                if (lane == 0 && pmax) atomicMax(p.probe_out, pmax);
+            } else {
+                for (int o = 16; o > 0; o >>= 1) {
+                    const int t = __shfl_xor_sync(0xffffffffu, stat, o);
+                    stat = t > stat ? t : stat;
+                }
+                if (lane == 0 && stat) atomicMax(p.stats + p.slotC, stat);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kCols);
+    }
+    if (threadIdx.x == 0 && *fail_flag && p.status) atomicExch(p.status, 1);
+}
+
+// activations -> two operand planes in the same C,H,W,N layout (elementwise)
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+split_same_layout_kernel(const T* __restrict__ src, long long n, void* __restrict__ plane0,
+                         void* __restrict__ plane1) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        if (MODE == MODE_FLEX16) {
+            const int m = (int)src[i];
+            const int lo = m & 0xff;
+            ((signed char*)plane0)[i] = (signed char)((m - lo) >> 8);
+            ((unsigned char*)plane1)[i] = (unsigned char)lo;
+        } else {
+            const float a = (float)src[i];
+            unsigned hb;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(a));
+            const float hi = __uint_as_float(hb);
+            ((float*)plane0)[i] = hi;
+            ((float*)plane1)[i] = a - hi;
+        }
+    }
+}
+
+// filters C,R,S,K -> planes [k_out][columns] with columns ordered (tap, channel block, channel)
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cchunks, int units,
+                     int rows_p, int kp, void* __restrict__ plane0, void* __restrict__ plane1) {
+    const long long total = (long long)rows_p * kp;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / kp), kc = (int)(i - (long long)row * kp);
+        const int u = kc >> 5, cl = kc & 31;
+        const int tap = u / cchunks, cc = u - tap * cchunks;
+        const int c = cc * 32 + cl;
+        T v = 0;
+        if (u < units && c < C && row < K) v = F[((long long)c * RS + tap) * K + row];
+        if (MODE == MODE_FLEX16) {
+            const int m = (int)v;
+            const int lo = m & 0xff;
+            ((signed char*)plane0)[i] = (signed char)((m - lo) >> 8);
+            ((unsigned char*)plane1)[i] = (unsigned char)lo;
+        } else {
+            const float a = (float)v;
+            unsigned hb;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(a));
+            const float hi = __uint_as_float(hb);
+            ((float*)plane0)[i] = hi;
+            ((float*)plane1)[i] = a - hi;
+        }
+    }
+}
+
+int make_map_4d(CUtensorMap* map, void* base, const ConvGeom& g, int esize) {
+    cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.C};
+    cuuint64_t strides[3] = {(cuuint64_t)g.N * esize, (cuuint64_t)g.W * g.N * esize,
+                             (cuuint64_t)g.H * g.W * g.N * esize};
+    cuuint32_t box[4] = {(cuuint32_t)(kKBytes / esize), 1, 1, 32};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = g_encode(map, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                          4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return b2::fail(B2_ERR_CUDA, "cuTensorMapEncodeTiled (4-d) failed (%d)", (int)r);
+    return B2_OK;
+}
+
+struct ImplicitShape {
+    int esize, bn, cchunks, units, stages, kp, np;
+    size_t act_plane, filt_plane, bytes;
+};
+
+ImplicitShape implicit_shape(int mode, const ConvGeom& g) {
+    ImplicitShape s;
+    s.esize = mode == MODE_FLEX16 ? 1 : 4;
+    s.bn = pick_bn(g.K);
+    s.cchunks = (g.C + 31) / 32;
+    s.units = g.R * g.S * s.cchunks;
+    const int ups = mode == MODE_FLEX16 ? 4 : 1;
+    s.stages = (s.units + ups - 1) / ups;
+    s.kp = s.stages * (kKBytes / s.esize);
+    s.np = round_up(g.K, s.bn);
+    s.act_plane = (((size_t)g.C * g.H * g.W * g.N * s.esize) + 1023) / 1024 * 1024;
+    s.filt_plane = (size_t)s.np * s.kp * s.esize;
+    s.bytes = 2 * s.act_plane + 2 * s.filt_plane;
+    return s;
+}
+
+// flex16 only: an MN-major tf32 operand needs the 32-byte-atom variant of the 128-byte swizzle
+// (both in the tensor map and in the matrix descriptor); with the plain 128-byte swizzle the
+// tensor core reads zeros.  fp32 convolutions therefore stay on the gather + K-major path.
+bool implicit_ok(int mode, const ConvGeom& g) {
+    return mode == MODE_FLEX16 && g.N % 128 == 0 &&
+           (long long)g.P * g.Q * (g.N / 128) < (1LL << 30);
+}
+
+template <int MODE, int BN>
+int launch_implicit(const CUtensorMap& mI0, const CUtensorMap& mI1, const CUtensorMap& mB0,
+                    const CUtensorMap& mB1, const ConvTileParams& p, int ntiles_n, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        B2_CUDA(cudaFuncSetAttribute(conv_implicit_kernel<MODE, BN>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
+        attr_set = true;
+    }
+    int ctas = p.num_tiles < 148 ? p.num_tiles : 148;
+    dim3 grid(ctas, ntiles_n);
+    conv_implicit_kernel<MODE, BN><<<grid, kThreads, smem_bytes(BN), st>>>(mI0, mI1, mB0, mB1, p);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+template <typename T, int MODE>
+int run_fprop_implicit(const T* I, const T* F, void* O, const ConvGeom& g,
+                       const b2_flex_scale* table, int slotI, int slotF, int slotO, int* stats,
+                       void* scratch, size_t scratch_bytes, unsigned long long* probe_out,
+                       int* status, int probe, cudaStream_t st) {
+    int rc = get_encode();
+    if (rc) return rc;
+    const ImplicitShape s = implicit_shape(MODE, g);
+    B2_REQUIRE(scratch && scratch_bytes >= s.bytes && ((uintptr_t)scratch & 1023) == 0,
+               "convolution needs %zu bytes of 1024-byte aligned scratch, got %zu", s.bytes,
+               scratch_bytes);
+    unsigned char* base = (unsigned char*)scratch;
+    void* A0 = base; void* A1 = base + s.act_plane;
+    void* B0 = base + 2 * s.act_plane; void* B1 = base + 2 * s.act_plane + s.filt_plane;
+    const long long n_act = (long long)g.C * g.H * g.W * g.N;
+    {
+        long long blocks = (n_act + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        split_same_layout_kernel<T, MODE><<<(unsigned)blocks, 256, 0, st>>>(I, n_act, A0, A1);
+        const long long n_f = (long long)s.np * s.kp;
+        long long fb = (n_f + 255) / 256;
+        if (fb > 148 * 8) fb = 148 * 8;
+        filter_planes_kernel<T, MODE><<<(unsigned)fb, 256, 0, st>>>(F, g.C, g.R * g.S, g.K, s.cchunks,
+                                                                   s.units, s.np, s.kp, B0, B1);
+        B2_CUDA(cudaGetLastError());
+    }
+    CUtensorMap mI0, mI1, mB0, mB1;
+    if ((rc = make_map_4d(&mI0, A0, g, s.esize))) return rc;
+    if ((rc = make_map_4d(&mI1, A1, g, s.esize))) return rc;
+    if ((rc = make_map(&mB0, B0, s.np, s.kp, s.esize, s.bn))) return rc;
+    if ((rc = make_map(&mB1, B1, s.np, s.kp, s.esize, s.bn))) return rc;
+    ConvTileParams p;
+    p.P = g.P; p.Q = g.Q; p.N = g.N; p.K = g.K; p.S = g.S;
+    p.pad_h = g.pad_h; p.pad_w = g.pad_w; p.str_h = g.str_h; p.str_w = g.str_w;
+    p.dil_h = g.dil_h; p.dil_w = g.dil_w;
+    p.cchunks = s.cchunks; p.units = s.units; p.stages_per_tile = s.stages;
+    p.nblk = g.N / 128;
+    p.num_tiles = g.P * g.Q * p.nblk;
+    p.ldc = (long long)g.P * g.Q * g.N;
+    p.O = O; p.table = table; p.slotA = slotI; p.slotB = slotF; p.slotC = slotO;
+    p.stats = stats; p.probe_out = probe_out; p.status = status; p.probe = probe;
+    const int ntn = s.np / s.bn;
+    switch (s.bn) {
+        case 16: return launch_implicit<MODE, 16>(mI0, mI1, mB0, mB1, p, ntn, st);
+        case 32: return launch_implicit<MODE, 32>(mI0, mI1, mB0, mB1, p, ntn, st);
+        case 64: return launch_implicit<MODE, 64>(mI0, mI1, mB0, mB1, p, ntn, st);
+        default: return launch_implicit<MODE, 128>(mI0, mI1, mB0, mB1, p, ntn, st);
+    }
+}
+
 template <typename T, int MODE>
 int run_fprop(const T* I, const T* F, void* O, const b2_conv_dims* d, const b2_flex_scale* table,
               int slotI, int slotF, int slotO, int* stats, void* scratch, size_t scratch_bytes,
@@ -131,6 +553,9 @@ int run_fprop(const T* I, const T* F, void* O, const b2_conv_dims* d, const b2_f
     int rc = geom_from(d, &g);
     if (rc) return rc;
     B2_REQUIRE(I && F && O, "null tensor");
+    if (implicit_ok(MODE, g) && !getenv("B2_CONV_IM2COL"))
+        return run_fprop_implicit<T, MODE>(I, F, O, g, table, slotI, slotF, slotO, stats, scratch,
+                                           scratch_bytes, probe_out, status, probe, st);
     const long long rows_ll = (long long)g.P * g.Q * g.N;
     B2_REQUIRE(rows_ll < (1LL << 31) - 256, "too many output positions");
     const int rows = (int)rows_ll, kg = g.C * g.R * g.S;
@@ -207,7 +632,13 @@ extern "C" int b2_conv_fprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, 
     int rc = geom_from(d, &g);
     if (rc) return rc;
     B2_REQUIRE(bytes, "null argument");
-    *bytes = shapes_for(flex ? MODE_FLEX16 : MODE_F32X3, g.P * g.Q * g.N, g.K, g.C * g.R * g.S).bytes;
+    const int mode = flex ? MODE_FLEX16 : MODE_F32X3;
+    size_t need = shapes_for(mode, g.P * g.Q * g.N, g.K, g.C * g.R * g.S).bytes;
+    if (implicit_ok(mode, g)) {
+        const size_t alt = implicit_shape(mode, g).bytes;
+        if (alt > need || !getenv("B2_CONV_IM2COL")) need = alt > need ? alt : need;
+    }
+    *bytes = need;
     return B2_OK;
 }
 

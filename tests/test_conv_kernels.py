@@ -16,7 +16,11 @@ pytestmark = pytest.mark.gpu
 # (C, H, W, N, K, R, S, pad, stride): shapes of the reference's flex conv tests plus ResNet-20's
 SHAPES = [(16, 7, 7, 32, 8, 3, 3, 0, 1), (16, 9, 11, 32, 8, 3, 3, 1, 1), (3, 32, 32, 32, 16, 3, 3, 1, 1),
           (16, 16, 16, 64, 32, 3, 3, 1, 2), (32, 16, 16, 32, 64, 1, 1, 0, 2), (64, 8, 8, 32, 64, 3, 3, 1, 1),
-          (5, 6, 5, 24, 10, 2, 3, 1, 1)]
+          (5, 6, 5, 24, 10, 2, 3, 1, 1),
+          # batches that are a multiple of 128 take the implicit-GEMM kernel
+          (16, 8, 8, 128, 16, 3, 3, 1, 1), (3, 10, 9, 128, 16, 3, 3, 1, 1), (16, 12, 12, 256, 32, 3, 3, 1, 2),
+          (32, 8, 8, 128, 64, 1, 1, 0, 2), (64, 6, 6, 128, 64, 3, 3, 1, 1), (40, 5, 7, 128, 24, 3, 2, 1, 1),
+          (16, 6, 6, 128, 144, 3, 3, 1, 1)]
 
 
 def _dims(lib, Cc, H, W, N, K, R, S, pad, stride):
