@@ -242,6 +242,8 @@ def run_resnet(args, rank, world, torch, dist, local):
     host[...] = np.random.RandomState(100 + rank).standard_normal(host.shape).astype(np.float32)
     first = comp(host)[0]
     comp(host)
+    if not args.no_graph:
+        comp.capture()          # the step list becomes one CUDA graph launch
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -313,7 +315,7 @@ def run_resnet(args, rank, world, torch, dist, local):
                    "layout": "C,H,W,N", "convolutions": 22, "replicas": world,
                    "l2": "L2 flushed by the run itself: each pass streams >126 MB of "
                          "activations and operand planes",
-                   "steps_per_pass": len(comp.steps)},
+                   "steps_per_pass": len(comp.steps), "cuda_graph": not args.no_graph},
         "clocks": clocks,
         "e2e": {"value": round(world * n / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "img/s",
                 "h2d_bytes_per_step": int(host.nbytes), "d2h_bytes_per_step": int(10 * n * item),
@@ -561,6 +563,8 @@ def main():
                     help="rows of the microbenchmark (smaller values are for profiler captures)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch kernel by kernel instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", 0))

@@ -142,6 +142,7 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
 struct ConvTileParams {
     int P, Q, N, K, S;
     int pad_h, pad_w, str_h, str_w, dil_h, dil_w;
+    int cu;                       // channels per unit: 16 when C <= 16, else 32
     int cchunks, units, stages_per_tile, num_tiles, nblk;
     long long ldc;
     void* O;
@@ -176,6 +177,15 @@ __device__ __forceinline__ unsigned long long make_smem_desc_mn(const void* p, u
     return d;
 }
 
+// deeper rings for the narrow tiles: the kernel is latency-bound, not capacity-bound
+__host__ __device__ constexpr int conv_stages(int bn) { return bn <= 32 ? 5 : bn <= 64 ? 4 : 3; }
+__host__ __device__ constexpr int conv_smem_bytes(int bn) {
+    return conv_stages(bn) * stage_bytes(bn) + 1024 + 256;
+}
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* m) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+}
+
 template <int MODE, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
@@ -184,14 +194,15 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                      const __grid_constant__ CUtensorMap mapB1, const ConvTileParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int kCS = conv_stages(BN);
     constexpr int kStageBytes = stage_bytes(BN);
     constexpr int kBPlane = BN * kKBytes;
     constexpr int kAcc = (MODE == MODE_FLEX16 ? 3 : 1) * BN;       // columns per accumulator set
     constexpr int kNBuf = (2 * kAcc <= 512) ? 2 : 1;
     constexpr int kCols = tmem_cols(MODE, BN) * kNBuf > 512 ? 512 : tmem_cols(MODE, BN) * kNBuf;
-    unsigned long long* full_bar = (unsigned long long*)(smem + kStages * kStageBytes);
-    unsigned long long* empty_bar = full_bar + kStages;
-    unsigned long long* tmem_full = empty_bar + kStages;      // [2]
+    unsigned long long* full_bar = (unsigned long long*)(smem + kCS * kStageBytes);
+    unsigned long long* empty_bar = full_bar + kCS;
+    unsigned long long* tmem_full = empty_bar + kCS;      // [2]
     unsigned long long* tmem_empty = tmem_full + 2;           // [2]
     unsigned* tmem_holder = (unsigned*)(tmem_empty + 2);
     int* fail_flag = (int*)(tmem_holder + 1);
@@ -200,7 +211,8 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     const int ncol0 = blockIdx.y * BN;                        // first output channel of this CTA
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapB0); prefetch_map(&mapB1);
+        for (int s = 0; s < kCS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
         *fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -221,25 +233,42 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 const int n0 = nb * 128;
                 const int h0 = pp * p.str_h - p.pad_h, w0 = q * p.str_w - p.pad_w;
                 for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
-                    const int s = g % kStages;
-                    if (g >= kStages && !mbar_wait(&empty_bar[s], ((g / kStages) - 1) & 1)) {
+                    const int s = g % kCS;
+                    if (g >= kCS && !mbar_wait(&empty_bar[s], ((g / kCS) - 1) & 1)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
                     unsigned char* sa = smem + s * kStageBytes;
-                    mbar_expect_tx(&full_bar[s], kStageBytes);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        // int8: four units of 32 channels per stage; tf32: one unit, four blocks
-                        // of 32 images
-                        int u = MODE == MODE_FLEX16 ? st * 4 + j : st;
-                        if (u >= p.units) u = 0;       // padding unit: its filter columns are zero
+                    if (MODE == MODE_FLEX16) {
+                        // units of `cu` channels; a 32-row MMA step takes 32/cu of them; the last
+                        // stage of a tile may be short
+                        const int ups = 128 / p.cu, per_step = 32 / p.cu;
+                        int nu = p.units - st * ups;
+                        if (nu > ups) nu = ups;
+                        const int loaded = ((nu + per_step - 1) / per_step) * per_step;
+                        const int ubytes = p.cu * 128;
+                        mbar_expect_tx(&full_bar[s], 2 * loaded * ubytes + 2 * kBPlane);
+                        for (int j = 0; j < loaded; ++j) {
+                            int u = st * ups + j;
+                            if (u >= p.units) u = 0;   // filler: its filter columns are zero
+                            const int tap = u / p.cchunks, cc = u - tap * p.cchunks;
+                            const int fr = tap / p.S, fs = tap - fr * p.S;
+                            const int h = h0 + fr * p.dil_h, w = w0 + fs * p.dil_w;
+                            tma_load_4d(sa + j * ubytes, &mapI0, n0, w, h, cc * p.cu, &full_bar[s]);
+                            tma_load_4d(sa + kPlaneBytes + j * ubytes, &mapI1, n0, w, h, cc * p.cu,
+                                        &full_bar[s]);
+                        }
+                    } else {
+                        mbar_expect_tx(&full_bar[s], kStageBytes);
+                        const int u = st;
                         const int tap = u / p.cchunks, cc = u - tap * p.cchunks;
                         const int fr = tap / p.S, fs = tap - fr * p.S;
                         const int h = h0 + fr * p.dil_h, w = w0 + fs * p.dil_w;
-                        const int nn = MODE == MODE_FLEX16 ? n0 : n0 + j * 32;
-                        tma_load_4d(sa + j * 4096, &mapI0, nn, w, h, cc * 32, &full_bar[s]);
-                        tma_load_4d(sa + kPlaneBytes + j * 4096, &mapI1, nn, w, h, cc * 32,
-                                    &full_bar[s]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            tma_load_4d(sa + j * 4096, &mapI0, n0 + j * 32, w, h, cc * 32, &full_bar[s]);
+                            tma_load_4d(sa + kPlaneBytes + j * 4096, &mapI1, n0 + j * 32, w, h,
+                                        cc * 32, &full_bar[s]);
+                        }
                     }
                     const int kx = st * (MODE == MODE_FLEX16 ? kKBytes : kKBytes / 4);
                     tma_load_2d(sa + 2 * kPlaneBytes, &mapB0, kx, ncol0, &full_bar[s]);
@@ -264,14 +293,20 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 }
                 tc_fence_after();
                 for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
-                    const int s = g % kStages;
-                    if (!mbar_wait(&full_bar[s], (g / kStages) & 1)) {
+                    const int s = g % kCS;
+                    if (!mbar_wait(&full_bar[s], (g / kCS) & 1)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
                     tc_fence_after();
                     unsigned char* sa = smem + s * kStageBytes;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
+                    int ksteps = 4;
+                    if (MODE == MODE_FLEX16) {
+                        const int ups = 128 / p.cu;
+                        int nu = p.units - st * ups;
+                        if (nu > ups) nu = ups;
+                        ksteps = (nu * p.cu + 31) / 32;
+                    }
+                    for (int k = 0; k < ksteps; ++k) {
                         const unsigned acc = (st > 0 || k > 0) ? 1u : 0u;
                         const unsigned long long badv = (unsigned long long)((k * 32) >> 4);
                         const unsigned long long dB0 = make_smem_desc(sa + 2 * kPlaneBytes) + badv;
@@ -389,6 +424,27 @@ __global__ void __launch_bounds__(256)
 split_same_layout_kernel(const T* __restrict__ src, long long n, void* __restrict__ plane0,
                          void* __restrict__ plane1) {
     const long long stride = (long long)gridDim.x * blockDim.x;
+    if (MODE == MODE_FLEX16 && (n & 7) == 0 && (((uintptr_t)src | (uintptr_t)plane0 |
+                                                  (uintptr_t)plane1) & 15) == 0) {
+        // eight mantissas per thread: one 16-byte load, two 8-byte stores
+        for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n / 8; v += stride) {
+            const int4 w = __ldcs(reinterpret_cast<const int4*>(src) + v);
+            const unsigned x[4] = {(unsigned)w.x, (unsigned)w.y, (unsigned)w.z, (unsigned)w.w};
+            unsigned hi[2] = {0, 0}, lo[2] = {0, 0};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // each word holds two int16: low byte of each -> lo plane; (m - lo) >> 8 is just
+                // the high byte of the two's-complement pattern
+                const unsigned l2 = __byte_perm(x[j], 0, 0x4420);   // bytes 0 and 2
+                const unsigned h2 = __byte_perm(x[j], 0, 0x4431);   // bytes 1 and 3
+                lo[j >> 1] |= (l2 & 0xffffu) << (16 * (j & 1));
+                hi[j >> 1] |= (h2 & 0xffffu) << (16 * (j & 1));
+            }
+            reinterpret_cast<uint2*>(plane0)[v] = make_uint2(hi[0], hi[1]);
+            reinterpret_cast<uint2*>(plane1)[v] = make_uint2(lo[0], lo[1]);
+        }
+        return;
+    }
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         if (MODE == MODE_FLEX16) {
             const int m = (int)src[i];
@@ -409,15 +465,15 @@ split_same_layout_kernel(const T* __restrict__ src, long long n, void* __restric
 // filters C,R,S,K -> planes [k_out][columns] with columns ordered (tap, channel block, channel)
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
-filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cchunks, int units,
+filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cu, int cchunks, int units,
                      int rows_p, int kp, void* __restrict__ plane0, void* __restrict__ plane1) {
     const long long total = (long long)rows_p * kp;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int row = (int)(i / kp), kc = (int)(i - (long long)row * kp);
-        const int u = kc >> 5, cl = kc & 31;
+        const int u = kc / cu, cl = kc - u * cu;
         const int tap = u / cchunks, cc = u - tap * cchunks;
-        const int c = cc * 32 + cl;
+        const int c = cc * cu + cl;
         T v = 0;
         if (u < units && c < C && row < K) v = F[((long long)c * RS + tap) * K + row];
         if (MODE == MODE_FLEX16) {
@@ -436,11 +492,11 @@ filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cchunks,
     }
 }
 
-int make_map_4d(CUtensorMap* map, void* base, const ConvGeom& g, int esize) {
+int make_map_4d(CUtensorMap* map, void* base, const ConvGeom& g, int esize, int cu) {
     cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.C};
     cuuint64_t strides[3] = {(cuuint64_t)g.N * esize, (cuuint64_t)g.W * g.N * esize,
                              (cuuint64_t)g.H * g.W * g.N * esize};
-    cuuint32_t box[4] = {(cuuint32_t)(kKBytes / esize), 1, 1, 32};
+    cuuint32_t box[4] = {(cuuint32_t)(kKBytes / esize), 1, 1, (cuuint32_t)cu};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = g_encode(map, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                           4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -451,7 +507,7 @@ int make_map_4d(CUtensorMap* map, void* base, const ConvGeom& g, int esize) {
 }
 
 struct ImplicitShape {
-    int esize, bn, cchunks, units, stages, kp, np;
+    int esize, bn, cu, cchunks, units, stages, kp, np;
     size_t act_plane, filt_plane, bytes;
 };
 
@@ -459,9 +515,10 @@ ImplicitShape implicit_shape(int mode, const ConvGeom& g) {
     ImplicitShape s;
     s.esize = mode == MODE_FLEX16 ? 1 : 4;
     s.bn = pick_bn(g.K);
-    s.cchunks = (g.C + 31) / 32;
+    s.cu = (mode == MODE_FLEX16 && g.C <= 16) ? 16 : 32;
+    s.cchunks = (g.C + s.cu - 1) / s.cu;
     s.units = g.R * g.S * s.cchunks;
-    const int ups = mode == MODE_FLEX16 ? 4 : 1;
+    const int ups = mode == MODE_FLEX16 ? 128 / s.cu : 1;
     s.stages = (s.units + ups - 1) / ups;
     s.kp = s.stages * (kKBytes / s.esize);
     s.np = round_up(g.K, s.bn);
@@ -485,12 +542,13 @@ int launch_implicit(const CUtensorMap& mI0, const CUtensorMap& mI1, const CUtens
     static bool attr_set = false;
     if (!attr_set) {
         B2_CUDA(cudaFuncSetAttribute(conv_implicit_kernel<MODE, BN>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     conv_smem_bytes(BN)));
         attr_set = true;
     }
     int ctas = p.num_tiles < 148 ? p.num_tiles : 148;
     dim3 grid(ctas, ntiles_n);
-    conv_implicit_kernel<MODE, BN><<<grid, kThreads, smem_bytes(BN), st>>>(mI0, mI1, mB0, mB1, p);
+    conv_implicit_kernel<MODE, BN><<<grid, kThreads, conv_smem_bytes(BN), st>>>(mI0, mI1, mB0, mB1, p);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }
@@ -517,20 +575,21 @@ int run_fprop_implicit(const T* I, const T* F, void* O, const ConvGeom& g,
         const long long n_f = (long long)s.np * s.kp;
         long long fb = (n_f + 255) / 256;
         if (fb > 148 * 8) fb = 148 * 8;
-        filter_planes_kernel<T, MODE><<<(unsigned)fb, 256, 0, st>>>(F, g.C, g.R * g.S, g.K, s.cchunks,
-                                                                   s.units, s.np, s.kp, B0, B1);
+        filter_planes_kernel<T, MODE><<<(unsigned)fb, 256, 0, st>>>(F, g.C, g.R * g.S, g.K, s.cu,
+                                                                   s.cchunks, s.units, s.np, s.kp,
+                                                                   B0, B1);
         B2_CUDA(cudaGetLastError());
     }
     CUtensorMap mI0, mI1, mB0, mB1;
-    if ((rc = make_map_4d(&mI0, A0, g, s.esize))) return rc;
-    if ((rc = make_map_4d(&mI1, A1, g, s.esize))) return rc;
+    if ((rc = make_map_4d(&mI0, A0, g, s.esize, s.cu))) return rc;
+    if ((rc = make_map_4d(&mI1, A1, g, s.esize, s.cu))) return rc;
     if ((rc = make_map(&mB0, B0, s.np, s.kp, s.esize, s.bn))) return rc;
     if ((rc = make_map(&mB1, B1, s.np, s.kp, s.esize, s.bn))) return rc;
     ConvTileParams p;
     p.P = g.P; p.Q = g.Q; p.N = g.N; p.K = g.K; p.S = g.S;
     p.pad_h = g.pad_h; p.pad_w = g.pad_w; p.str_h = g.str_h; p.str_w = g.str_w;
     p.dil_h = g.dil_h; p.dil_w = g.dil_w;
-    p.cchunks = s.cchunks; p.units = s.units; p.stages_per_tile = s.stages;
+    p.cu = s.cu; p.cchunks = s.cchunks; p.units = s.units; p.stages_per_tile = s.stages;
     p.nblk = g.N / 128;
     p.num_tiles = g.P * g.Q * p.nblk;
     p.ldc = (long long)g.P * g.Q * g.N;

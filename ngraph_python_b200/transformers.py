@@ -194,6 +194,34 @@ class Computation(object):
         for s in self.steps:
             t._launch_step(s)
 
+    def capture(self):
+        """Records the step list into a CUDA graph and replays it from now on: one graph launch
+        per call instead of one launch (plus tensor-map encoding) per kernel.  Call after the
+        computation has run at least once, so that flex exponents exist and every kernel variant is
+        compiled; flex scales live in a device table, so a replay picks up exponent changes.
+        Computations with collectives are not captured."""
+        t = self.transformer
+        if self.steps is None or t.plan_only:
+            raise lib.B200Error("run the computation once before capturing it")
+        if any(s.kind == "comm" for s in self.steps):
+            raise lib.B200Error("computations with collectives are not captured")
+        if t.flex and any(not b.entry.initialized for b in self.written):
+            raise lib.B200Error("run the computation once before capturing it")
+        torch = t.torch
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = t.kernel_launches
+        with torch.cuda.graph(graph):
+            self._run_steps()
+        per_call = t.kernel_launches - before
+        self._graph = graph
+
+        def replay():
+            graph.replay()
+            t.kernel_launches += per_call
+        self.executor = replay
+        return self
+
 
 builtin_sum = sum
 
@@ -671,7 +699,12 @@ class B200Transformer(object):
         self._status = None
         self._table = None
         self._stats = None
-        self.stream = torch.cuda.current_stream(self.device)
+
+    @property
+    def stream(self):
+        """Kernels go to torch's current stream (which is the capture stream while a CUDA graph
+        is being recorded)."""
+        return self.torch.cuda.current_stream(self.device)
 
     # ---- tolerances (ngraph/transformers/flexgputransform.py:80-103) ----------------------------
     def get_default_tolerance(self, desired):

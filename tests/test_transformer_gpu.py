@@ -74,3 +74,26 @@ def test_flex16_within_reference_tolerance(name, fuse):
             atol *= 4
             np.testing.assert_allclose(got, exp, rtol=rtol, atol=atol,
                                        err_msg="%s output %d call %d" % (name, k, rep))
+
+
+@pytest.mark.parametrize("flex", [False, True])
+def test_captured_graph_matches_stepwise(flex):
+    """Two transformers see the same sequence of calls; one of them switches to replaying a
+    captured CUDA graph half way.  Results must be identical call by call -- also in flex mode,
+    where exponents move between calls and the replay has to pick them up from the device table."""
+    def run(capture_after):
+        outs, params, vals = cases.CASES["resnet8_small"](ng)
+        seq = [vals, [v * 1.7 for v in vals], [v * 1.7 for v in vals], vals, [v * 0.3 for v in vals]]
+        t = ng.transformers.allocate_transformer("b200", flex=flex)
+        comp = t.computation(outs, *params)
+        got = []
+        for i, v in enumerate(seq):
+            if i == capture_after:
+                comp.capture()
+            got.append([np.array(r, copy=True) for r in comp(*v)])
+        t.close()
+        return got
+    stepwise, replayed = run(None), run(2)
+    for a, b in zip(stepwise, replayed):
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
