@@ -152,6 +152,7 @@ struct ConvTileParams {
     unsigned long long* probe_out;
     int* status;
     int probe;
+    long long* dbg;      // optional per-role cycle counters of CTA 0 (profiling aid), else null
 };
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1,
@@ -227,6 +228,8 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         if (lane == 0) {
             int g = 0;
             bool ok = true;
+            const long long t_start = clock64();
+            long long t_wait = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
                 const int pq = tile / p.nblk, nb = tile - pq * p.nblk;
                 const int pp = pq / p.Q, q = pq - pp * p.Q;
@@ -234,9 +237,11 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 const int h0 = pp * p.str_h - p.pad_h, w0 = q * p.str_w - p.pad_w;
                 for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
                     const int s = g % kCS;
+                    const long long tw = clock64();
                     if (g >= kCS && !mbar_wait(&empty_bar[s], ((g / kCS) - 1) & 1)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
+                    t_wait += clock64() - tw;
                     unsigned char* sa = smem + s * kStageBytes;
                     if (MODE == MODE_FLEX16) {
                         // units of `cu` channels; a 32-row MMA step takes 32/cu of them; the last
@@ -275,6 +280,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                     tma_load_2d(sa + 2 * kPlaneBytes + kBPlane, &mapB1, kx, ncol0, &full_bar[s]);
                 }
             }
+            if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) {
+                p.dbg[0] = clock64() - t_start; p.dbg[1] = t_wait;
+            }
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -285,18 +293,24 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const unsigned id_tf = make_idesc(1, 2, 2, BN) | mn;
             int g = 0, ti = 0;
             bool ok = true;
+            const long long t_start = clock64();
+            long long t_wait_e = 0, t_wait_f = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
                 const int buf = ti % kNBuf;
                 const unsigned acc_base = tmem_base + buf * kAcc;
+                const long long tw = clock64();
                 if (ti >= kNBuf && !mbar_wait(&tmem_empty[buf], ((ti / kNBuf) - 1) & 1)) {
                     atomicExch(fail_flag, 1); ok = false; break;
                 }
+                t_wait_e += clock64() - tw;
                 tc_fence_after();
                 for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
                     const int s = g % kCS;
+                    const long long tw2 = clock64();
                     if (!mbar_wait(&full_bar[s], (g / kCS) & 1)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
+                    t_wait_f += clock64() - tw2;
                     tc_fence_after();
                     unsigned char* sa = smem + s * kStageBytes;
                     int ksteps = 4;
@@ -333,6 +347,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 }
                 tc_commit(&tmem_full[buf]);
             }
+            if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) {
+                p.dbg[2] = clock64() - t_start; p.dbg[3] = t_wait_e; p.dbg[4] = t_wait_f;
+            }
         }
     } else {
         const int quarter = warp & 3;
@@ -346,9 +363,13 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         }
         int ti = 0;
         bool ok = true;
+        const long long t_start = clock64();
+        long long t_wait = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++ti) {
             const int buf = ti % kNBuf;
+            const long long tw = clock64();
             if (ok && !mbar_wait(&tmem_full[buf], (ti / kNBuf) & 1)) { atomicExch(fail_flag, 1); ok = false; }
+            t_wait += clock64() - tw;
             tc_fence_after();
             const long long row = (long long)tile * 128 + quarter * 32 + lane;   // (pq*N + n)
             const unsigned lane_addr = tmem_base + buf * kAcc + ((unsigned)(quarter * 32) << 16);
@@ -392,6 +413,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+        if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64) {
+            p.dbg[5] = clock64() - t_start; p.dbg[6] = t_wait; p.dbg[7] = ti;
         }
         if (MODE == MODE_FLEX16) {
             if (p.probe) {
@@ -595,6 +619,11 @@ int run_fprop_implicit(const T* I, const T* F, void* O, const ConvGeom& g,
     p.ldc = (long long)g.P * g.Q * g.N;
     p.O = O; p.table = table; p.slotA = slotI; p.slotB = slotF; p.slotC = slotO;
     p.stats = stats; p.probe_out = probe_out; p.status = status; p.probe = probe;
+    {
+        // profiling aid: B2_CONV_DBG=<device address> makes CTA 0 write 8 cycle counters there
+        const char* e = getenv("B2_CONV_DBG");
+        p.dbg = e ? (long long*)strtoull(e, nullptr, 0) : nullptr;
+    }
     const int ntn = s.np / s.bn;
     switch (s.bn) {
         case 16: return launch_implicit<MODE, 16>(mI0, mI1, mB0, mB1, p, ntn, st);

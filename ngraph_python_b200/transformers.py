@@ -12,6 +12,7 @@ There is no CPU path: constructing the transformer without the shared library or
 device raises.
 """
 import collections
+import math
 import numbers
 
 import numpy as np
@@ -162,6 +163,7 @@ class Computation(object):
         t._allocate()
         self.launches_per_call = builtin_sum(s.launches for s in self.steps)
         self.written = planner.written_buffers
+        self.param_buffers = [t._view_of(p).buffer for p in self.parameters]
         self.executor = self._run_steps
 
     # ---- run -----------------------------------------------------------------------------
@@ -179,10 +181,13 @@ class Computation(object):
                              (len(self.parameters), len(args)))
         t._begin_call(self)
         for p, value in zip(self.parameters, args):
-            t._host_to_device(t._view_of(p), value)
+            t._host_to_device(t._view_of(p), value, in_call=True)
         self.executor()
-        results = [t._device_to_host(v) for v in self.return_views]
+        # results, flex statistics and the status word come back with asynchronous copies and
+        # ONE stream synchronisation
+        pending = [t._device_to_host_async(v) for v in self.return_views]
         t._end_call(self)
+        results = [t._finish_host(p) for p in pending]
         if self.returns_kind is Op:
             return results[0]
         if self.returns_kind is None:
@@ -674,6 +679,8 @@ class B200Transformer(object):
         self.comm = kwargs.pop("comm", None) or commmod.SingleProcessComm()
         self.bucket_bytes = int(kwargs.pop("bucket_bytes", commmod.DEFAULT_BUCKET_BYTES))
         self._alias = {}
+        self._pinned = {}
+        self._inputs_written = []
         self._comm_steps = []
         self._allreduce = None
         self._buffers = collections.OrderedDict()   # op -> Buffer
@@ -832,6 +839,7 @@ class B200Transformer(object):
                 b.tensor = torch.zeros((max(b.size, 1),), dtype=dt, device=self.device)
         if self._status is None:
             self._status = torch.zeros((1,), dtype=torch.int32, device=self.device)
+            self._status_host = torch.zeros((1,), dtype=torch.int32).pin_memory()
             self._probe64 = torch.zeros((1,), dtype=torch.int64, device=self.device)
         if self.flex:
             n = max(self.flex_manager.n_slots + 64, 64)
@@ -840,6 +848,8 @@ class B200Transformer(object):
                 self._stats = torch.zeros((n,), dtype=torch.int32, device=self.device)
                 self._table_host = torch.zeros((n, 2), dtype=torch.float32).pin_memory()
                 self._stats_host = torch.zeros((n,), dtype=torch.int32).pin_memory()
+                self._table_np = self._table_host.numpy()
+                self._dec_uploaded = {}
         for op, b in self._buffers.items():
             if b.init_array is not None and not getattr(b, "initialised", False):
                 b.initialised = True
@@ -851,7 +861,7 @@ class B200Transformer(object):
                                              dtype=self.torch.uint8, device=self.device)
 
     # ---- host <-> device -----------------------------------------------------------------------
-    def _host_to_device(self, view, value, init=False):
+    def _host_to_device(self, view, value, init=False, in_call=False):
         """DeviceTensor.__setitem__ (ngraph/transformers/gputransform.py:806-854); flex:
         FlexGPUDeviceTensor.__setitem__ (flexgputransform.py:183-208)."""
         torch = self.torch
@@ -864,14 +874,24 @@ class B200Transformer(object):
         arr = np.ascontiguousarray(np.broadcast_to(arr, view.axes.lengths)
                                    if arr.shape == () else arr.reshape(view.axes.lengths))
         src = torch.from_numpy(np.array(arr.reshape(-1), copy=not arr.flags.writeable))
+        async_ok = src.is_pinned()
         if not buf.flex:
-            buf.tensor.copy_(src, non_blocking=False)
+            buf.tensor.copy_(src, non_blocking=async_ok)
             return
         if buf.staging is None:
             buf.staging = torch.empty((max(buf.size, 1),), dtype=torch.float32, device=self.device)
-        buf.staging.copy_(src, non_blocking=False)
+        buf.staging.copy_(src, non_blocking=async_ok)
         e = buf.entry
         raw = lib.raw()
+        if in_call and e.initialized:
+            # exponent adopted and table row uploaded by _begin_call; the statistic is read with
+            # everything else at the end of the call
+            lib.check(raw.b2_flex_host_quantize(buf.staging.data_ptr(), buf.ptr(), buf.size,
+                                                self._table.data_ptr(), buf.slot,
+                                                self._stats.data_ptr(), self.stream.cuda_stream))
+            self.kernel_launches += 1
+            self._inputs_written.append(buf)
+            return
         if not e.initialized:
             bits = self._stats[-1:]
             bits.zero_()
@@ -889,6 +909,36 @@ class B200Transformer(object):
                                             self._stats.data_ptr(), self.stream.cuda_stream))
         self.kernel_launches += 1
         e.end_write(int(self._stats[buf.slot].item()))
+
+    def _device_to_host_async(self, view):
+        """Starts the device->host copy of a result into a pinned buffer; see _finish_host."""
+        buf = view.buffer
+        if self._allreduce is not None and getattr(buf, "comm_key", None) is not None:
+            self._allreduce.wait_for(buf.comm_key)
+        key = (id(buf), view.key())
+        pinned = self._pinned.get(key)
+        if view.is_dense():
+            src = buf.tensor[:max(buf.size, 1)]
+        else:
+            src = self.torch.as_strided(buf.tensor, view.axes.lengths, view.strides, view.offset)
+        if pinned is None:
+            pinned = self.torch.empty(src.shape, dtype=src.dtype).pin_memory()
+            self._pinned[key] = pinned
+        pinned.copy_(src, non_blocking=True)
+        return pinned, view
+
+    def _finish_host(self, pending):
+        """After the stream has been synchronised: a caller-owned array from the pinned copy
+        (DeviceTensor.get, gputransform.py:710-744; flex: int16 * scale,
+        flexgputransform.py:178-181)."""
+        pinned, view = pending
+        host = pinned.numpy().reshape(view.axes.lengths)
+        if view.buffer.flex:
+            return host.astype(np.float64) * view.buffer.entry.scale
+        host = host.copy()
+        if host.shape == ():
+            return host[()]
+        return host
 
     def _device_to_host(self, view):
         """DeviceTensor.get (gputransform.py:710-744); flex: int16 * scale
@@ -910,8 +960,9 @@ class B200Transformer(object):
 
     # ---- flex bookkeeping ------------------------------------------------------------------------
     def _set_table_row(self, slot, dec):
-        self._table_host[slot, 0] = 2.0 ** -dec
-        self._table_host[slot, 1] = 2.0 ** dec
+        self._dec_uploaded[slot] = dec
+        self._table_np[slot, 0] = 2.0 ** -dec
+        self._table_np[slot, 1] = 2.0 ** dec
         self._table[slot].copy_(self._table_host[slot])
 
     def _begin_call(self, comp):
@@ -921,30 +972,43 @@ class B200Transformer(object):
         if not self.flex:
             return
         self.flex_manager.autoflex_count += 1
+        self._inputs_written = []
         written = set(id(b) for b in comp.written)
+        written.update(id(b) for b in comp.param_buffers)
+        tab = self._table_np
         for b in self._buffers.values():
-            if getattr(b, "shares_entry", False) or b.entry is None:
-                continue
             e = b.entry
+            if e is None or getattr(b, "shares_entry", False):
+                continue
             dec_stored = e.dec
             # tensors this call overwrites adopt the exponent chosen after their previous write
-            dec_w = e.begin_write() if (id(b) in written and e.initialized) else e.dec
-            self._table_host[b.slot_write, 0] = 2.0 ** -dec_w
-            self._table_host[b.slot_write, 1] = 2.0 ** dec_w
-            if b.slot != b.slot_write:
-                self._table_host[b.slot, 0] = 2.0 ** -dec_stored
-                self._table_host[b.slot, 1] = 2.0 ** dec_stored
+            dec_w = e.begin_write() if (e.initialized and id(b) in written) else dec_stored
+            if self._dec_uploaded.get(b.slot_write) != dec_w:
+                self._dec_uploaded[b.slot_write] = dec_w
+                tab[b.slot_write, 0] = math.ldexp(1.0, -dec_w)
+                tab[b.slot_write, 1] = math.ldexp(1.0, dec_w)
+            if b.slot != b.slot_write and self._dec_uploaded.get(b.slot) != dec_stored:
+                self._dec_uploaded[b.slot] = dec_stored
+                tab[b.slot, 0] = math.ldexp(1.0, -dec_stored)
+                tab[b.slot, 1] = math.ldexp(1.0, dec_stored)
         self._table.copy_(self._table_host, non_blocking=False)
         self._stats.zero_()
 
     def _end_call(self, comp):
-        if int(self._status.item()) != 0:
+        """One synchronisation per call: statistics and status come back together."""
+        torch = self.torch
+        self._status_host.copy_(self._status, non_blocking=True)
+        if self.flex:
+            self._stats_host.copy_(self._stats, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        if int(self._status_host[0]) != 0:
             self._status.zero_()
             raise lib.B200Error("a device-side wait ran out during the computation")
         if not self.flex:
             return
-        self._stats_host.copy_(self._stats, non_blocking=False)
         stats = self._stats_host.numpy()
+        for b in self._inputs_written:
+            b.entry.end_write(int(stats[b.slot]))
         for b in comp.written:
             b.entry.end_write(int(stats[b.slot_write]))
 
