@@ -1,0 +1,202 @@
+"""Plug-in that registers the b200 transformer INSIDE an nGraph-Python installation.
+
+    import ngraph_python_b200.ngraph_plugin          # registers transformer_name = 'b200'
+    import ngraph.transformers as ngt
+    t = ngt.make_transformer_factory('b200', flex=True)()
+    f = t.computation(outputs, *placeholders)         # ordinary ngraph ops
+    y = f(x)
+
+The reference registers every `Transformer` subclass that defines `transformer_name`
+(ngraph/transformers/base.py:265-279) and reaches it through make_transformer_factory /
+allocate_transformer (:834-847).  This class takes a ComputationOp (what
+`Transformer.computation` builds, base.py:420-433, op_graph.py:961-1033), translates the graph it
+returns into the op surface of this package (same op names and argument meaning, so the mapping
+is one line per op class) and hands it to the b200 planner.  The reference's own graph passes,
+CPU code generator and GPU back end are not involved.
+
+Only importable where `ngraph` itself imports.
+"""
+import collections
+
+import numpy as np
+
+import ngraph.op_graph.op_graph as ref
+from ngraph.op_graph.convolution import ConvolutionOp as RefConvolutionOp
+from ngraph.op_graph.pooling import PoolingOp as RefPoolingOp
+from ngraph.transformers.base import Transformer
+
+from . import op_graph as b2
+from . import transformers as b2t
+
+_UNARY = {
+    "NegativeOp": b2.negative, "AbsoluteOp": b2.absolute, "SinOp": b2.sin, "CosOp": b2.cos,
+    "TanhOp": b2.tanh, "ExpOp": b2.exp, "LogOp": b2.log, "ReciprocalOp": b2.reciprocal,
+    "SignOp": b2.sign, "SquareOp": b2.square, "SqrtOp": b2.sqrt,
+    "SigmoidAtomicOp": b2.sigmoidAtomic,
+}
+_BINARY = {
+    "Add": b2.add, "Subtract": b2.subtract, "Multiply": b2.multiply, "Divide": b2.divide,
+    "FloorDivide": b2.floordivide, "Mod": b2.mod, "Maximum": b2.maximum, "Minimum": b2.minimum,
+    "Power": b2.power, "Equal": b2.equal, "NotEqual": b2.not_equal, "Greater": b2.greater,
+    "Less": b2.less, "GreaterEqual": b2.greater_equal, "LessEqual": b2.less_equal,
+}
+_REDUCE = {"Sum": b2.sum, "Prod": b2.prod, "Max": b2.max, "Min": b2.min, "Argmax": b2.argmax,
+           "Argmin": b2.argmin}
+
+
+class GraphTranslator(object):
+    """reference Op -> ngraph_python_b200 Op, memoised."""
+
+    def __init__(self):
+        self.memo = {}
+        self.axis_memo = {}
+
+    def axis(self, a):
+        key = (a.name, a.length)
+        if key not in self.axis_memo:
+            self.axis_memo[key] = b2.make_axis(a.length, name=a.name)
+        return self.axis_memo[key]
+
+    def axes(self, axes):
+        return b2.make_axes([self.axis(a) for a in axes])
+
+    def __call__(self, op):
+        op = op.forwarded
+        if op in self.memo:
+            return self.memo[op]
+        out = self._translate(op)
+        self.memo[op] = out
+        return out
+
+    def _translate(self, op):
+        name = type(op).__name__
+        if isinstance(op, ref.AssignableTensorOp):
+            init = op.initial_value
+            if op.is_constant and init is None:
+                init = op.const
+            kw = dict(is_input=op.is_input, is_persistent=op.is_persistent,
+                      is_constant=op.is_constant, is_trainable=op.is_trainable,
+                      is_placeholder=op.is_placeholder, name=op.name)
+            if init is not None and not callable(init):
+                init = np.asarray(init, dtype=np.float32)
+            return b2.AssignableTensorOp(self.axes(op.axes), init, **kw)
+        if isinstance(op, ref.SequentialOp):
+            return b2.sequential([self(o) for o in op.ops])
+        if isinstance(op, ref.ValueOp):                 # sigmoid, softmax, mean, ... expand
+            return self(op.value_tensor)
+        if isinstance(op, ref.AssignOp):
+            return b2.assign(self(op.args[0]), self(op.args[1]))
+        args = [self(a) for a in op.args]
+        if name in _UNARY:
+            return _UNARY[name](args[0])
+        if name in _BINARY:
+            return _BINARY[name](args[0], args[1])
+        if name in _REDUCE:
+            return _REDUCE[name](args[0], reduction_axes=self.axes(op.reduction_axes))
+        if isinstance(op, ref.DotOp):
+            return b2.dot(args[0], args[1])
+        if isinstance(op, ref.BroadcastOp):
+            return b2.broadcast(args[0], self.axes(op.axes))
+        if isinstance(op, ref.ReorderAxes):
+            return b2.axes_with_order(args[0], self.axes(op.axes))
+        if isinstance(op, ref.AxesCastOp):
+            return b2.cast_axes(args[0], self.axes(op.axes))
+        if isinstance(op, ref.ExpandDims):
+            return b2.broadcast(args[0], self.axes(op.axes))
+        if isinstance(op, RefConvolutionOp):
+            return b2.convolution(dict(op.conv_params), args[0], args[1], self.axes(op.axes))
+        if isinstance(op, RefPoolingOp):
+            return b2.pooling(dict(op.pool_params), args[0], self.axes(op.axes))
+        if isinstance(op, ref.ContiguousOp):
+            return b2.value_of(args[0])
+        raise ValueError("Unhandled op: {}".format(op))
+
+
+class _PluginComputation(object):
+    """Callable with the calling conventions of ngraph.transformers.base.Computation
+    (base.py:73-136): positional arguments or feed_dict; scalar / tuple / dict results."""
+
+    def __init__(self, transformer, computation_op):
+        self.transformer = transformer
+        self.computation_op = computation_op
+        tr = transformer.translator
+        returns = computation_op.returns
+        self.dict_keys = None
+        if isinstance(returns, dict):
+            self.dict_keys = list(returns.keys())
+            outs = [tr(returns[k]) for k in self.dict_keys]
+        elif isinstance(returns, collections.abc.Container) and not isinstance(returns, ref.Op):
+            self.container = type(returns)
+            outs = [tr(r) for r in returns]
+        elif returns is None:
+            outs = None
+        else:
+            outs = tr(returns)
+        self.parameters = list(computation_op.parameters)
+        params = [tr(p.tensor) for p in self.parameters]
+        self.impl = transformer.impl.computation(outs, *params)
+        self.returns = returns
+
+    def __call__(self, *args, **kwargs):
+        feed = kwargs.pop("feed_dict", None)
+        if feed is not None:
+            args = [feed[p.tensor] if p.tensor in feed else feed[p] for p in self.parameters]
+        res = self.impl(*args)
+        if self.dict_keys is not None:
+            return dict(zip(self.dict_keys, res))
+        if isinstance(self.returns, ref.Op) or self.returns is None:
+            return res
+        return self.container(res) if self.container in (tuple, list) else tuple(res)
+
+
+class B200NgraphTransformer(Transformer):
+    """The b200 back end behind the reference's transformer API."""
+
+    transformer_name = "b200"
+    default_rtol = 1e-05
+    default_atol = 1e-08
+
+    def __init__(self, **kwargs):
+        # the reference base class expects no unknown keyword arguments
+        self.impl = b2t.B200Transformer(**kwargs)
+        self.translator = GraphTranslator()
+        self.computations = []
+        self.finalized = False
+
+    # -- the API callers use ---------------------------------------------------------------------
+    def computation(self, results, *parameters):
+        return self.add_computation(ref.computation(results, *parameters))
+
+    def add_computation(self, computation_op):
+        if self.impl.finalized:
+            raise ValueError("Cannot create computations from a finalized transformer")
+        c = _PluginComputation(self, computation_op)
+        self.computations.append(c)
+        return c
+
+    def initialize(self):
+        self.impl.initialize()
+        self.finalized = True
+
+    def close(self):
+        self.impl.close()
+
+    def get_default_tolerance(self, desired):
+        return self.impl.get_default_tolerance(desired)
+
+    # -- hooks of the abstract base that this back end does not route through -------------------
+    @property
+    def use_exop(self):
+        return False
+
+    def initialize_allocations(self):
+        pass
+
+    def get_tensor_view_value(self, op, host_tensor=None):
+        raise NotImplementedError("read tensors through a computation")
+
+    def host_to_device(self, computation, parameters, args):
+        pass
+
+    def device_to_host(self, computation, op, tensor=None):
+        pass
