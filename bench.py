@@ -11,6 +11,10 @@ Rank 0 prints ONE JSON line.  Workloads:
                         per GPU, He-initialised weights from seed 0, batch norm folded into
                         biases.  Metric: images per second.  Each GPU runs a full replica on its
                         own batch; nothing is exchanged.
+  gemm_flex16 / gemm_fp32  (BASELINE config 3) C = A.B with M = N = K = --size (default 8192);
+                        flex16: int16 mantissas uniform in [-32767, 32767], exponents -15 and -12,
+                        C re-quantised with the exponent chosen from its measured range.
+                        Metric: T(flex-)MAC-op/s = 2MNK / t; roofline on the tensor pipe.
   c2_flex16 / c2_fp32   fused elementwise + reduction microbenchmark
                         y = tanh(a*x+b)*sigmoid(c), s = sum(y, axis 1), m = max|y| over axis 1,
                         x,a,b,c of shape (8192, 16384); y is stored (into a variable), s and m are
@@ -356,6 +360,111 @@ def resnet_cpu_baseline(budget_s=12.0, steps=None):
                       % (reps, n, cores), "ms_per_step": round(dt * 1e3, 2)}
 
 
+def tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
+def run_gemm(args, rank, world, torch, dist, local):
+    import ngraph_python_b200 as ng
+    flex = args.workload == "gemm_flex16"
+    n = args.size
+    t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex)
+    M, K, N = ng.make_axis(n, name="M"), ng.make_axis(n, name="K"), ng.make_axis(n, name="N")
+    a, b = ng.placeholder([M, K]), ng.placeholder([K, N])
+    c = ng.dot(a, b)
+    cvar = ng.persistent_tensor([M, N])
+    # C stays on the device (assigned to a persistent tensor); its column maxima are returned
+    out = ng.sequential([ng.assign(cvar, c), ng.max(cvar, reduction_axes=[M])])
+    comp = t.computation(out, a, b)
+    rng = np.random.RandomState(rank)
+    host = []
+    for scale in ((2.0 ** -15, 2.0 ** -12) if flex else (1.0, 1.0)):
+        pinned = torch.empty((n, n), dtype=torch.float32).pin_memory()
+        arr = pinned.numpy()
+        if flex:
+            arr[...] = rng.randint(-32767, 32768, (n, n)).astype(np.float32) * scale
+        else:
+            arr[...] = rng.standard_normal((n, n)).astype(np.float32)
+        host.append(arr)
+    comp(*host)
+    comp(*host)
+    stream = torch.cuda.current_stream()
+    gemm_step = [s for s in comp.steps if s.kind == "gemm"][0]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        t._launch_step(gemm_step)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        t._launch_step(gemm_step)
+    ev1.record(stream)
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    comp(*host)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        res = comp(*host)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop()
+    if dist is not None:
+        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
+    if rank != 0:
+        return None
+    ms_step = dev_ms / args.steps
+    ops = 2.0 * n * n * n
+    bf16, which = tensor_peak()
+    # flex16: four int8 products per MAC; int8 peak is not measured on this pool, 2 x the
+    # measured bf16 figure stands in for it (datasheet: 4500 TOPS)
+    tensor_ops = (4 if flex else 3) * ops
+    peak = (2 * bf16) if flex else bf16 / 2
+    achieved = tensor_ops / (ms_step * 1e-3) / 1e12
+    line = {
+        "metric": "%s GEMM T%sMAC-op/s (2MNK/t), M=N=K=%d" % ("flex16" if flex else "fp32",
+                                                              "flex-" if flex else "", n),
+        "value": round(world * ops / (ms_step * 1e-3) / 1e12, 2), "unit": "Tops/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "flex16 (int8 hi/lo tensor-core products, i32 accumulation)" if flex
+                 else "f32 (3xTF32)",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "M": n, "N": n, "K": n, "replicas": world,
+                   "l2": "operand planes (%d MB) larger than L2" % (4 * n * n * (1 if flex else 4) >> 20)
+                         if n >= 8192 else "operands fit in L2 at this size",
+                   "includes": "operand split pre-pass + tensor-core kernel"},
+        "clocks": clocks,
+        "e2e": {"value": round(world * ops / (e2e_ms / e2e_steps * 1e-3) / 1e12, 3),
+                "unit": "Tops/s", "h2d_bytes_per_step": int(sum(h.nbytes for h in host)),
+                "d2h_bytes_per_step": int(n * (2 if flex else 4)), "steps": e2e_steps,
+                "ms_per_step": round(e2e_ms / e2e_steps, 3)},
+        "gpu_launches": gemm_step.launches * args.steps,
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1),
+                     "unit": "TOPS (int8)" if flex else "TFLOP/s (tf32)",
+                     "frac": round(achieved / peak, 4), "traffic": None,
+                     "peak_source": which + (" bf16 x2 as int8 stand-in" if flex
+                                             else " bf16 / 2 as tf32 stand-in"),
+                     "algorithmic_ops_per_launch": tensor_ops},
+    }
+    return line
+
+
 def run_b200(args, rank, world):
     import torch
     import ngraph_python_b200 as ng
@@ -365,6 +474,11 @@ def run_b200(args, rank, world):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.workload.startswith("gemm"):
+        line = run_gemm(args, rank, world, torch, dist, local)
+        if dist is not None:
+            dist.destroy_process_group()
+        return line
     if args.workload.startswith("resnet20"):
         line = run_resnet(args, rank, world, torch, dist, local)
         if dist is not None:
@@ -512,6 +626,29 @@ def cpu_baseline(workload, budget_s=12.0):
 def run_reference(args, rank, world):
     if rank != 0:
         return None
+    if args.workload.startswith("gemm"):
+        n = min(args.size, 2048)
+        rng = np.random.RandomState(0)
+        flex = args.workload == "gemm_flex16"
+        a = rng.randint(-32767, 32768, (n, n)).astype(np.float64 if flex else np.float32)
+        bm = rng.randint(-32767, 32768, (n, n)).astype(np.float64 if flex else np.float32)
+        a @ bm
+        t0 = time.perf_counter()
+        for _ in range(max(1, args.steps)):
+            a @ bm
+        dt = (time.perf_counter() - t0) / max(1, args.steps)
+        v = round(2.0 * n ** 3 / dt / 1e12, 4)
+        cores = os.cpu_count() or 1
+        return {"impl": "reference", "metric": "GEMM Tops/s (2MNK/t)", "value": v,
+                "unit": "Tops/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f64 (exact for int16 products)" if flex else "f32",
+                "data": "synthetic", "config": {"workload": args.workload, "M": n, "N": n, "K": n},
+                "cpu_baseline": {"value": v, "unit": "Tops/s", "cores": cores, "kind": "port",
+                                 "sample": "numpy matmul %d^3 (the reference CPU transformer's "
+                                           "Dot is np.dot), %d BLAS threads" % (n, cores)},
+                "e2e": {"value": v, "unit": "Tops/s", "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     if args.workload.startswith("resnet20"):
         flex = args.workload == "resnet20_flex16"
         b = resnet_cpu_baseline(steps=max(1, args.steps))
@@ -556,7 +693,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="resnet20_flex16",
-                    choices=["resnet20_flex16", "resnet20_fp32", "c2_flex16", "c2_fp32"])
+                    choices=["resnet20_flex16", "resnet20_fp32", "c2_flex16", "c2_fp32",
+                             "gemm_flex16", "gemm_fp32"])
+    ap.add_argument("--size", type=int, default=8192, help="M = N = K of the GEMM workloads")
     ap.add_argument("--batch", type=int, default=RESNET_N, help="images per GPU (ResNet-20)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=C2_ROWS,
