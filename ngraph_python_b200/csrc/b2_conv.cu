@@ -659,17 +659,17 @@ int run_fprop(const T* I, const T* F, void* O, const b2_conv_dims* d, const b2_f
         im2col_planes_kernel<T, MODE><<<s.Mp / 32, 256, 0, st>>>(I, g, rows, kg, s.Mp, s.Kp, base,
                                                          base + a_plane);
         // filters: element (n = k_out, k = kidx) = F[kidx * K + k_out]
-        dim3 gb((s.Kp + 31) / 32, (s.Np + 31) / 32);
-        split_planes_kernel<T, MODE><<<gb, 256, 0, st>>>(F, 1, g.K, g.K, kg, s.Np, s.Kp,
-                                                        base + 2 * a_plane,
-                                                        base + 2 * a_plane + b_plane);
         B2_CUDA(cudaGetLastError());
+        rc = split_operand<T, MODE>(F, 1, g.K, g.K, kg, s.Np, s.Kp, base + 2 * a_plane,
+                                    base + 2 * a_plane + b_plane, 0, nullptr, st);
+        if (rc) return rc;
     }
     GemmParams p;
     p.M = rows; p.N = g.K; p.num_kb = 0;
     p.ldc = rows; p.C = O; p.table = table; p.slotA = slotI; p.slotB = slotF; p.slotC = slotO;
     p.stats = stats; p.probe_out = probe_out; p.status = status; p.probe = probe;
     p.c_colmajor = 1;
+    p.rowsum = nullptr;
     return launch_on_planes<MODE>(base, s, p, st);
 }
 

@@ -12,6 +12,12 @@
 //           round-to-nearest-even in integer arithmetic, saturates to int16 and folds max|mantissa|.
 //           (The reference accumulates int16 products in fp32 FFMA, fgemm_common_128x128.sass:
 //           188-228, which is inexact above 2^24; this path is exact.)
+//           When the caller supplies row sums of A ("merged" form, used by the dense GEMM entry
+//           point) the low plane of B is stored as the signed byte bl - 128, so that both planes of
+//           B are signed and lie behind one another in shared memory as ONE 2*BN-row operand:
+//               A_hi x [B_hi | B_lo'] -> HH | X          A_lo x [B_hi | B_lo'] -> X | LL
+//           two N = 2*BN instructions per k-step instead of four of N = BN (a quarter less operand
+//           traffic from shared memory); the epilogue adds back 128 * sum_k a[m,k].
 //   fp32:   3xTF32: a = a_hi + a_lo with a_hi rounded to tf32, and
 //               a*b ~= a_hi*b_hi + a_hi*b_lo + a_lo*b_hi        (relative error ~2^-21)
 //           three kind::tf32 products into one fp32 accumulator.
@@ -19,7 +25,7 @@
 // Structure of the main kernel (one CTA per 128x128 output tile, 192 threads):
 //   warp 0   : TMA producer -- 2-D tiled bulk tensor copies of the four operand planes of a
 //              k-block (4 x 16 KB, 128-byte swizzle) into a 3-stage shared-memory ring;
-//   warp 1   : allocates tensor memory, one lane issues tcgen05.mma (12 or 16 per k-block) and
+//   warp 1   : allocates tensor memory, one lane issues tcgen05.mma (8, 12 or 16 per k-block) and
 //              commits each stage back to the producer;
 //   warps 2-5: epilogue -- tcgen05.ld of the accumulators (each warp owns 32 lanes = 32 rows),
 //              recombination / rescale / store.
@@ -164,6 +170,7 @@ struct GemmParams {
     int* status;
     int probe;
     int c_colmajor;                  // 0: C[row*ldc + col]; 1: C[col*ldc + row]
+    const int* rowsum;               // flex16 merged form: sum_k a[m,k] per row of A, else null
 };
 
 // round-to-nearest-even of v / 2^sh (sh > 0), or v * 2^-sh (sh <= 0), saturated to int16
@@ -241,6 +248,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             const unsigned id_ss = make_idesc(2, 1, 1, BN), id_su = make_idesc(2, 1, 0, BN),
                            id_us = make_idesc(2, 0, 1, BN), id_uu = make_idesc(2, 0, 0, BN);
             const unsigned id_tf = make_idesc(1, 2, 2, BN);
+            const unsigned id_ss2 = make_idesc(2, 1, 1, 2 * BN), id_us2 = make_idesc(2, 0, 1, 2 * BN);
+            const bool merged = MODE == MODE_FLEX16 && p.rowsum != nullptr;
             bool ok = true;
             for (int kb = 0; kb < p.num_kb && ok; ++kb) {
                 const int s = kb % kStages;
@@ -255,7 +264,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 for (int k = 0; k < 4; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * 32) >> 4);
                     const unsigned acc = (kb > 0 || k > 0) ? 1u : 0u;
-                    if (MODE == MODE_FLEX16) {
+                    if (merged && acc) {
+                        // B_hi and B_lo' are adjacent: one descriptor spans both
+                        tc_mma<MODE>(tmem_base + 0, dA0 + adv, dB0 + adv, id_ss2, 1u);      // HH | X
+                        tc_mma<MODE>(tmem_base + BN, dA1 + adv, dB0 + adv, id_us2, 1u);     // X | LL
+                    } else if (merged) {
+                        // first k-step: the three accumulators start from different instructions
+                        tc_mma<MODE>(tmem_base + 0, dA0 + adv, dB0 + adv, id_ss, 0u);
+                        tc_mma<MODE>(tmem_base + BN, dA0 + adv, dB1 + adv, id_ss, 0u);
+                        tc_mma<MODE>(tmem_base + BN, dA1 + adv, dB0 + adv, id_us, 1u);
+                        tc_mma<MODE>(tmem_base + 2 * BN, dA1 + adv, dB1 + adv, id_us, 0u);
+                    } else if (MODE == MODE_FLEX16) {
                         tc_mma<MODE>(tmem_base + 0, dA0 + adv, dB0 + adv, id_ss, acc);      // HH
                         tc_mma<MODE>(tmem_base + BN, dA0 + adv, dB1 + adv, id_su, acc);     // X += ah*bl
                         tc_mma<MODE>(tmem_base + BN, dA1 + adv, dB0 + adv, id_us, 1u);      // X += al*bh
@@ -285,6 +304,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             int stat = 0;
             unsigned long long pmax = 0;
             short* crow = (short*)p.C + (long long)row * p.ldc;
+            const long long fix = (p.rowsum && row < p.M) ? 128LL * (long long)p.rowsum[row] : 0LL;
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 unsigned hh[16], xx[16], ll[16];
                 tmem_ld16(lane_addr + c0, hh);
@@ -296,7 +316,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const long long v = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
-                                        (long long)(int)ll[j];
+                                        (long long)(int)ll[j] + fix;
                     if (p.probe) {
                         const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
                         pmax = a > pmax ? a : pmax;
@@ -380,12 +400,184 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
 
 // ---- pre-pass: operand planes, K-major, zero padded ---------------------------------------------
 // src element (r, k) of op(X) is src[r * rs + k * cs]; planes are [rows_p][kp] with kp contiguous.
-// 32x32 tiles through shared memory so that both the read and the write are coalesced whichever of
-// rs / cs is 1.
+//   flex16: plane0 = high byte (signed), plane1 = low byte XOR lo_xor (lo_xor = 0x80 stores the
+//           signed byte lo - 128); rowsum (optional) accumulates sum_k of the int16 values per row.
+//   fp32:   plane0 = value rounded to tf32, plane1 = remainder.
+// Three kernels: K contiguous with 16-byte aligned rows (vector loads, no staging), rows contiguous
+// with aligned columns (64x64 / 64x32 tiles transposed through shared memory, vector loads and
+// stores), and a 32x32-tile kernel without any alignment requirement.
+
+__device__ __forceinline__ void tf32_split(float a, float& hi, float& lo) {
+    unsigned hb;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(a));
+    hi = __uint_as_float(hb);
+    lo = a - hi;
+}
+
+__device__ __forceinline__ void add_rowsum(int* rowsum, int r, int rows, int v, int group) {
+    // lanes of a group (a power of two, aligned) hold partial sums of the same row
+    for (int o = group >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & (group - 1)) == 0 && r < rows && v != 0) atomicAdd(rowsum + r, v);
+}
+
+// K contiguous: one thread = 16 int16 (two 16-byte loads) or 4 floats of one row
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+split_rows_kernel(const T* __restrict__ src, long long rs, int rows, int k, int rows_p, int kp,
+                  void* __restrict__ plane0, void* __restrict__ plane1, unsigned lo_xor,
+                  int* __restrict__ rowsum) {
+    constexpr int kPer = MODE == MODE_FLEX16 ? 16 : 4;
+    const int upr = kp / kPer;                                   // units per row
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    const bool live = idx < (long long)rows_p * upr;
+    const int r = live ? (int)(idx / upr) : rows_p;
+    const int kk = live ? (int)(idx % upr) * kPer : 0;
+    const long long o = (long long)r * kp + kk;
+    if (MODE == MODE_FLEX16) {
+        unsigned w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (live && r < rows) {
+            const short* sp = (const short*)src + (long long)r * rs + kk;
+            if (kk + 16 <= k) {
+                const int4 a = __ldg((const int4*)sp), b = __ldg((const int4*)sp + 1);
+                w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+                w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+            } else {
+                for (int j = 0; j < 16 && kk + j < k; ++j)
+                    w[j >> 1] |= (unsigned)(unsigned short)sp[j] << ((j & 1) * 16);
+            }
+        }
+        int sum = 0;
+        unsigned hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            hi[j] = __byte_perm(w[2 * j], w[2 * j + 1], 0x7531);
+            lo[j] = __byte_perm(w[2 * j], w[2 * j + 1], 0x6420) ^ (lo_xor * 0x01010101u);
+            sum += ((int)(w[2 * j] << 16) >> 16) + ((int)w[2 * j] >> 16) +
+                   ((int)(w[2 * j + 1] << 16) >> 16) + ((int)w[2 * j + 1] >> 16);
+        }
+        if (live) {
+            *(int4*)((unsigned char*)plane0 + o) = make_int4(hi[0], hi[1], hi[2], hi[3]);
+            *(int4*)((unsigned char*)plane1 + o) = make_int4(lo[0], lo[1], lo[2], lo[3]);
+        }
+        if (rowsum) {
+            const int r0 = __shfl_sync(0xffffffffu, r, 0);
+            if (__all_sync(0xffffffffu, r == r0)) add_rowsum(rowsum, r, rows, sum, 32);
+            else if (r < rows && sum != 0) atomicAdd(rowsum + r, sum);
+        }
+    } else {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live && r < rows) {
+            const float* sp = (const float*)src + (long long)r * rs + kk;
+            if (kk + 4 <= k) v = __ldg((const float4*)sp);
+            else {
+                if (kk + 0 < k) v.x = sp[0];
+                if (kk + 1 < k) v.y = sp[1];
+                if (kk + 2 < k) v.z = sp[2];
+            }
+        }
+        float4 h, l;
+        tf32_split(v.x, h.x, l.x); tf32_split(v.y, h.y, l.y);
+        tf32_split(v.z, h.z, l.z); tf32_split(v.w, h.w, l.w);
+        if (live) {
+            *(float4*)((float*)plane0 + o) = h;
+            *(float4*)((float*)plane1 + o) = l;
+        }
+    }
+}
+
+// rows contiguous in the source (element (r, k) at src[k * cs + r]): tiles of 64 rows x 64 k
+// (flex16) or 64 rows x 32 k (fp32) are read with 16-byte loads along r, transposed through shared
+// memory and written with 16- / 32-byte stores along k.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+split_cols_kernel(const T* __restrict__ src, long long cs, int rows, int k, int rows_p, int kp,
+                  void* __restrict__ plane0, void* __restrict__ plane1, unsigned lo_xor,
+                  int* __restrict__ rowsum) {
+    constexpr int kTileK = MODE == MODE_FLEX16 ? 64 : 32;
+    constexpr int kPitch = MODE == MODE_FLEX16 ? 66 : 65;       // elements; odd word pitch
+    __shared__ T tile[kTileK * kPitch];
+    const int tid = threadIdx.x;
+    const int r0 = blockIdx.y * 64, k0 = blockIdx.x * kTileK;
+    if (MODE == MODE_FLEX16) {
+        // load: 8 rows per thread per k; 8 threads cover 64 rows, 32 k per pass
+        for (int i = 0; i < 2; ++i) {
+            const int kk = (tid >> 3) + 32 * i, r8 = (tid & 7) * 8;
+            unsigned w[4] = {0, 0, 0, 0};
+            if (k0 + kk < k) {
+                const short* sp = (const short*)src + (long long)(k0 + kk) * cs + r0 + r8;
+                if (r0 + r8 + 8 <= rows) {
+                    const int4 a = __ldg((const int4*)sp);
+                    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+                } else {
+                    for (int j = 0; j < 8 && r0 + r8 + j < rows; ++j)
+                        w[j >> 1] |= (unsigned)(unsigned short)sp[j] << ((j & 1) * 16);
+                }
+            }
+            unsigned* dst = (unsigned*)((short*)tile + kk * kPitch + r8);
+            dst[0] = w[0]; dst[1] = w[1]; dst[2] = w[2]; dst[3] = w[3];
+        }
+        __syncthreads();
+        const int r = tid >> 2, kc = (tid & 3) * 16;
+        unsigned hi[4], lo[4];
+        int sum = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            unsigned h = 0, l = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int m = ((short*)tile)[(kc + 4 * j + b) * kPitch + r];
+                sum += m;
+                l |= (unsigned)(m & 0xff) << (8 * b);
+                h |= (unsigned)((m >> 8) & 0xff) << (8 * b);
+            }
+            hi[j] = h;
+            lo[j] = l ^ (lo_xor * 0x01010101u);
+        }
+        if (r0 + r < rows_p && k0 + kc < kp) {
+            const long long o = (long long)(r0 + r) * kp + k0 + kc;
+            *(int4*)((unsigned char*)plane0 + o) = make_int4(hi[0], hi[1], hi[2], hi[3]);
+            *(int4*)((unsigned char*)plane1 + o) = make_int4(lo[0], lo[1], lo[2], lo[3]);
+        }
+        if (rowsum) add_rowsum(rowsum, r0 + r, rows, sum, 4);
+    } else {
+        // load: 4 rows per thread per k; 16 threads cover 64 rows, 16 k per pass
+        for (int i = 0; i < 2; ++i) {
+            const int kk = (tid >> 4) + 16 * i, r4 = (tid & 15) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k0 + kk < k) {
+                const float* sp = (const float*)src + (long long)(k0 + kk) * cs + r0 + r4;
+                if (r0 + r4 + 4 <= rows) v = __ldg((const float4*)sp);
+                else {
+                    if (r0 + r4 + 0 < rows) v.x = sp[0];
+                    if (r0 + r4 + 1 < rows) v.y = sp[1];
+                    if (r0 + r4 + 2 < rows) v.z = sp[2];
+                }
+            }
+            float* dst = (float*)tile + kk * kPitch + r4;
+            dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+        }
+        __syncthreads();
+        const int r = tid >> 2, kc = (tid & 3) * 8;
+        float h[8], l[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tf32_split(((float*)tile)[(kc + j) * kPitch + r], h[j], l[j]);
+        if (r0 + r < rows_p && k0 + kc < kp) {
+            const long long o = (long long)(r0 + r) * kp + k0 + kc;
+            *(float4*)((float*)plane0 + o) = make_float4(h[0], h[1], h[2], h[3]);
+            *(float4*)((float*)plane0 + o + 4) = make_float4(h[4], h[5], h[6], h[7]);
+            *(float4*)((float*)plane1 + o) = make_float4(l[0], l[1], l[2], l[3]);
+            *(float4*)((float*)plane1 + o + 4) = make_float4(l[4], l[5], l[6], l[7]);
+        }
+    }
+}
+
+// no alignment requirement: 32x32 tiles through shared memory so that both the read and the write
+// are coalesced whichever of rs / cs is 1.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 split_planes_kernel(const T* __restrict__ src, long long rs, long long cs, int rows, int k,
-                    int rows_p, int kp, void* __restrict__ plane0, void* __restrict__ plane1) {
+                    int rows_p, int kp, void* __restrict__ plane0, void* __restrict__ plane1,
+                    unsigned lo_xor, int* __restrict__ rowsum) {
     __shared__ T tile[32][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 x 8
     const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
@@ -401,24 +593,47 @@ split_planes_kernel(const T* __restrict__ src, long long rs, long long cs, int r
     __syncthreads();
     for (int i = ty; i < 32; i += 8) {
         const int r = r0 + i, kk = k0 + tx;
-        if (r >= rows_p || kk >= kp) continue;
         const T v = tile[i][tx];
+        if (MODE == MODE_FLEX16 && rowsum) add_rowsum(rowsum, r, rows, (int)v, 32);
+        if (r >= rows_p || kk >= kp) continue;
         const long long o = (long long)r * kp + kk;
         if (MODE == MODE_FLEX16) {
             const int m = (int)v;
             const int lo = m & 0xff;                 // unsigned low byte
             const int hi = (m - lo) >> 8;            // signed high byte: m = 256*hi + lo
             ((signed char*)plane0)[o] = (signed char)hi;
-            ((unsigned char*)plane1)[o] = (unsigned char)lo;
+            ((unsigned char*)plane1)[o] = (unsigned char)(lo ^ lo_xor);
         } else {
-            const float a = (float)v;
-            unsigned hb;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(a));
-            const float hi = __uint_as_float(hb);
+            float hi, lo;
+            tf32_split((float)v, hi, lo);
             ((float*)plane0)[o] = hi;
-            ((float*)plane1)[o] = a - hi;
+            ((float*)plane1)[o] = lo;
         }
     }
+}
+
+// Picks the pre-pass kernel for one operand.
+template <typename T, int MODE>
+int split_operand(const T* src, long long rs, long long cs, int rows, int k, int rows_p, int kp,
+                  void* plane0, void* plane1, unsigned lo_xor, int* rowsum, cudaStream_t st) {
+    const bool base16 = ((uintptr_t)src & 15) == 0;
+    const int vec = 16 / (int)sizeof(T);
+    if (cs == 1 && base16 && rs % vec == 0) {
+        const long long units = (long long)rows_p * (kp / (MODE == MODE_FLEX16 ? 16 : 4));
+        split_rows_kernel<T, MODE><<<(unsigned)((units + 255) / 256), 256, 0, st>>>(
+            src, rs, rows, k, rows_p, kp, plane0, plane1, lo_xor, rowsum);
+    } else if (rs == 1 && base16 && cs % vec == 0) {
+        const int tk = MODE == MODE_FLEX16 ? 64 : 32;
+        dim3 g((kp + tk - 1) / tk, (rows_p + 63) / 64);
+        split_cols_kernel<T, MODE><<<g, 256, 0, st>>>(src, cs, rows, k, rows_p, kp, plane0, plane1,
+                                                     lo_xor, rowsum);
+    } else {
+        dim3 g((kp + 31) / 32, (rows_p + 31) / 32);
+        split_planes_kernel<T, MODE><<<g, 256, 0, st>>>(src, rs, cs, rows, k, rows_p, kp, plane0,
+                                                       plane1, lo_xor, rowsum);
+    }
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -456,7 +671,7 @@ int make_map(CUtensorMap* map, void* base, int rows_p, int kp, int esize, int bo
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-struct Shapes { int Mp, Np, Kp, esize, bn; size_t bytes, a_bytes; };
+struct Shapes { int Mp, Np, Kp, esize, bn; size_t bytes, a_bytes, rowsum_off; };
 
 inline int pick_bn(int N) { return N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : 128; }
 
@@ -469,6 +684,8 @@ Shapes shapes_for(int mode, int M, int N, int K) {
     s.Kp = round_up(K, kKBytes / s.esize);
     s.a_bytes = 2ull * (size_t)s.Mp * s.Kp * s.esize;
     s.bytes = s.a_bytes + 2ull * (size_t)s.Np * s.Kp * s.esize;
+    s.rowsum_off = s.bytes;                  // int32 row sums of A (flex16 merged form)
+    if (mode == MODE_FLEX16) s.bytes += (size_t)s.Mp * sizeof(int);
     return s;
 }
 
@@ -526,19 +743,24 @@ int run_gemm(const T* A, long long a_rs, long long a_cs, const T* B, long long b
     const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
     void* A0 = base; void* A1 = base + a_plane;
     void* B0 = base + 2 * a_plane; void* B1 = base + 2 * a_plane + b_plane;
-    {
-        dim3 g((s.Kp + 31) / 32, (s.Mp + 31) / 32);
-        split_planes_kernel<T, MODE><<<g, 256, 0, st>>>(A, a_rs, a_cs, M, K, s.Mp, s.Kp, A0, A1);
-        dim3 g2((s.Kp + 31) / 32, (s.Np + 31) / 32);
-        // op(B)^T: rows = N, element (n, k) = B[k * b_ks + n * b_ns]
-        split_planes_kernel<T, MODE><<<g2, 256, 0, st>>>(B, b_ns, b_ks, N, K, s.Np, s.Kp, B0, B1);
-        B2_CUDA(cudaGetLastError());
+    int* rowsum = nullptr;
+    unsigned lo_xor = 0;
+    if (MODE == MODE_FLEX16) {
+        rowsum = (int*)(base + s.rowsum_off);
+        lo_xor = 0x80;
+        B2_CUDA(cudaMemsetAsync(rowsum, 0, (size_t)s.Mp * sizeof(int), st));
     }
+    int rc = split_operand<T, MODE>(A, a_rs, a_cs, M, K, s.Mp, s.Kp, A0, A1, 0, rowsum, st);
+    if (rc) return rc;
+    // op(B)^T: rows = N, element (n, k) = B[k * b_ks + n * b_ns]
+    rc = split_operand<T, MODE>(B, b_ns, b_ks, N, K, s.Np, s.Kp, B0, B1, lo_xor, nullptr, st);
+    if (rc) return rc;
     GemmParams p;
     p.M = M; p.N = N; p.num_kb = 0;
     p.ldc = ldc; p.C = C; p.table = table; p.slotA = slotA; p.slotB = slotB; p.slotC = slotC;
     p.stats = stats; p.probe_out = probe_out; p.status = status; p.probe = probe;
     p.c_colmajor = 0;
+    p.rowsum = rowsum;
     return launch_on_planes<MODE>(base, s, p, st);
 }
 
