@@ -179,7 +179,8 @@ int b2_gemm_f32(const float* A, int64_t a_row_stride, int64_t a_k_stride, const 
                 void* stream);
 /* flex16: exact integer products (int8 hi/lo split, int32 accumulation), output rescaled by
  * 2^(decC - decA - decB) with round-to-nearest-even, saturated to int16; stats[slotC] receives
- * max |mantissa| (fgemm epilogue, fgemm_common_128x128.sass:29-97,331-420).  K <= 32768.
+ * max |mantissa| (fgemm epilogue, fgemm_common_128x128.sass:29-97,331-420).  K above 32768 is
+ * cut into slices of exact int32 sums that are added in 64-bit.
  * probe != 0: nothing is stored; *probe_out receives max |exact integer sum| (the caller
  * multiplies by 2^-(decA+decB) to get the unsaturated range of the result). */
 int b2_gemm_flex16(const int16_t* A, int64_t a_row_stride, int64_t a_k_stride, const int16_t* B,
@@ -211,6 +212,29 @@ int b2_conv_fprop_flex16(const int16_t* I, const int16_t* F, int16_t* O, const b
                          const b2_flex_scale* table, int32_t slotI, int32_t slotF, int32_t slotO,
                          int32_t* stats, void* scratch, size_t scratch_bytes, uint64_t* probe_out,
                          int32_t* status, int32_t probe, void* stream);
+/* The two training contractions of a convolution whose forward pass has the dimensions `d`
+ * (d always describes the FORWARD convolution: I is C,D,H,W,N, F is C,T,R,S,K, E is K,M,P,Q,N).
+ * Replace ConvBpropKernel / ConvUpdateKernel (ngraph/transformers/gpu/conv.py:121-312) and
+ * FlexConvBpropKernel / FlexConvUpdateKernel (gpu/flex_conv.py:203-621); arithmetic as the
+ * reference's CPU engine states it (ngraph/transformers/cpu/cpuengine.py:256-271, 395-418).
+ *   bprop:  GI[C,D,H,W,N] = sum_{k,r,s} F[c,r,s,k] * E[k,p,q,n],  h = p*str - pad + r*dil
+ *   update: U[C,T,R,S,K]  = sum_{p,q,n} I[c,h,w,n] * E[k,p,q,n]   (sums added in a fixed order)
+ * flex16 variants: exact integer sums, rescale / saturate / statistic / probe as b2_gemm_flex16
+ * with (slot of first operand, slot of second operand, slot of the result). */
+int b2_conv_bprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, size_t* bytes);
+int b2_conv_bprop_f32(const float* E, const float* F, float* GI, const b2_conv_dims* d,
+                      void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+int b2_conv_bprop_flex16(const int16_t* E, const int16_t* F, int16_t* GI, const b2_conv_dims* d,
+                         const b2_flex_scale* table, int32_t slotE, int32_t slotF, int32_t slotGI,
+                         int32_t* stats, void* scratch, size_t scratch_bytes, uint64_t* probe_out,
+                         int32_t* status, int32_t probe, void* stream);
+int b2_conv_update_scratch_bytes(int32_t flex, const b2_conv_dims* d, size_t* bytes);
+int b2_conv_update_f32(const float* I, const float* E, float* U, const b2_conv_dims* d,
+                       void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+int b2_conv_update_flex16(const int16_t* I, const int16_t* E, int16_t* U, const b2_conv_dims* d,
+                          const b2_flex_scale* table, int32_t slotI, int32_t slotE, int32_t slotU,
+                          int32_t* stats, void* scratch, size_t scratch_bytes, uint64_t* probe_out,
+                          int32_t* status, int32_t probe, void* stream);
 /* Average pooling over H,W windows.  flex != 0: int16 in and out sharing one exponent
  * (ngraph/transformers/passes/flexpass.py:40-48); *stats_slot = max(*stats_slot, max |out|). */
 int b2_pool_avg_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H, int32_t W,

@@ -17,6 +17,17 @@
 // N (batch) is the GEMM-M direction (128 rows per tile), the output channels are the GEMM-N
 // direction with a 16/32/64/128-wide tile, so the small channel counts of ResNet-20 do not pad
 // the tensor-core tile to 128.
+//
+// The two training contractions (ConvBpropKernel / ConvUpdateKernel, gpu/conv.py:121-312,
+// FlexConvBpropKernel / FlexConvUpdateKernel, gpu/flex_conv.py:203-621; readable specification
+// ngraph/transformers/cpu/cpuengine.py:256-271 and :395-418) run on the same tile kernel:
+//   bprop:  gI^T[(h,w,n), c] = Ecol[(h,w,n),(k,r,s)] * F[(c,r,s),k] read as [(k,r,s)][c], where the
+//           gather takes E[k,p,q,n] with p = (h + pad - r*dil) / str when that division is exact
+//           and p lies inside the output, zero otherwise (the transposed, flipped convolution);
+//   update: U[(c,r,s), k] = Icol^T[(c,r,s),(p,q,n)] * E[k,(p,q,n)]: the contraction runs over all
+//           output positions and images (262144 for a 32x32 layer at batch 256), so it is cut
+//           into K slices spread over the SMs; the slices are added in a fixed order by a second
+//           kernel (deterministic, and exact for flex16: every slice is an exact integer).
 #include <cstdlib>
 
 #include "b2_gemm_impl.cuh"
@@ -45,7 +56,9 @@ int geom_from(const b2_conv_dims* d, ConvGeom* g) {
 // walks the columns in chunks of 128 bytes of plane row.  Per chunk the tap decomposition of each
 // column is computed once into shared memory; loads run along n (contiguous in the input), the
 // write phase emits one 16-byte vector per thread and plane (contiguous along the plane row).
-template <typename T, int MODE>
+// BPROP = true gathers the rows of Ecol instead: row = (h*W + w)*N + n of the INPUT gradient,
+// column = (k*R + r_)*S + s_, source E[k, p, q, n] (see the head of this file).
+template <typename T, int MODE, bool BPROP>
 __global__ void __launch_bounds__(256)
 im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int rows_p, int kp,
                      void* __restrict__ plane0, void* __restrict__ plane1) {
@@ -60,9 +73,14 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
     if (rvalid) {
         n = r % g.N;
         const int pq = r / g.N;
-        const int q = pq % g.Q, pp = pq / g.Q;
-        h0 = pp * g.str_h - g.pad_h;
-        w0 = q * g.str_w - g.pad_w;
+        if (BPROP) {
+            h0 = pq / g.W + g.pad_h;
+            w0 = pq % g.W + g.pad_w;
+        } else {
+            const int q = pq % g.Q, pp = pq / g.Q;
+            h0 = pp * g.str_h - g.pad_h;
+            w0 = q * g.str_w - g.pad_w;
+        }
     }
     const int RS = g.R * g.S;
     const int wr = threadIdx.x >> 3, vec = threadIdx.x & 7;
@@ -74,7 +92,7 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
             if (kidx < kg) {
                 const int c = kidx / RS, rs = kidx - c * RS;
                 const int fr = rs / g.S, fs = rs - fr * g.S;
-                tab_c[threadIdx.x] = c * g.H * g.W * g.N;
+                tab_c[threadIdx.x] = c * (BPROP ? g.P * g.Q : g.H * g.W) * g.N;
                 tab_h[threadIdx.x] = fr * g.dil_h;
                 tab_w[threadIdx.x] = fs * g.dil_w;
             } else {
@@ -86,9 +104,18 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
             T v = 0;
             const int tc = tab_c[i];
             if (tc >= 0 && rvalid) {
-                const int h = h0 + tab_h[i], w = w0 + tab_w[i];
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W)
-                    v = I[(long long)tc + ((long long)h * g.W + w) * g.N + n];
+                if (BPROP) {
+                    const int th = h0 - tab_h[i], tw = w0 - tab_w[i];
+                    if (th >= 0 && tw >= 0 && th % g.str_h == 0 && tw % g.str_w == 0) {
+                        const int pp = th / g.str_h, q = tw / g.str_w;
+                        if (pp < g.P && q < g.Q)
+                            v = I[(long long)tc + ((long long)pp * g.Q + q) * g.N + n];
+                    }
+                } else {
+                    const int h = h0 + tab_h[i], w = w0 + tab_w[i];
+                    if (h >= 0 && h < g.H && w >= 0 && w < g.W)
+                        v = I[(long long)tc + ((long long)h * g.W + w) * g.N + n];
+                }
             }
             tile[i][tx] = v;
         }
@@ -162,9 +189,6 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, i
         "[%0], [%1, {%2, %3, %4, %5}], [%6];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
         : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // MN-major operand, 128-byte swizzle: 8-row K groups `sbo` bytes apart, MN atoms `lbo` bytes apart
 __device__ __forceinline__ unsigned long long make_smem_desc_mn(const void* p, unsigned lbo,
@@ -656,8 +680,8 @@ int run_fprop(const T* I, const T* F, void* O, const b2_conv_dims* d, const b2_f
     const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
     {
         B2_REQUIRE((long long)g.C * g.H * g.W * g.N < (1LL << 31), "input tensor too large");
-        im2col_planes_kernel<T, MODE><<<s.Mp / 32, 256, 0, st>>>(I, g, rows, kg, s.Mp, s.Kp, base,
-                                                         base + a_plane);
+        im2col_planes_kernel<T, MODE, false><<<s.Mp / 32, 256, 0, st>>>(I, g, rows, kg, s.Mp, s.Kp,
+                                                                base, base + a_plane);
         // filters: element (n = k_out, k = kidx) = F[kidx * K + k_out]
         B2_CUDA(cudaGetLastError());
         rc = split_operand<T, MODE>(F, 1, g.K, g.K, kg, s.Np, s.Kp, base + 2 * a_plane,
@@ -671,6 +695,193 @@ int run_fprop(const T* I, const T* F, void* O, const b2_conv_dims* d, const b2_f
     p.c_colmajor = 1;
     p.rowsum = nullptr;
     return launch_on_planes<MODE>(base, s, p, st);
+}
+
+// ---- training contractions -------------------------------------------------------------------
+// filter planes for bprop: row = c, column = (k*R + r_)*S + s_, value F[((c*R + r_)*S + s_)*K + k]
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+filter_bprop_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int rows_p, int kp,
+                           void* __restrict__ plane0, void* __restrict__ plane1) {
+    const long long total = (long long)rows_p * kp;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total;
+         i += (long long)gridDim.x * 256) {
+        const int c = (int)(i / kp), kidx = (int)(i % kp);
+        T v = 0;
+        if (c < C && kidx < K * RS) {
+            const int k = kidx / RS, rs = kidx - k * RS;
+            v = F[((long long)c * RS + rs) * K + k];
+        }
+        if (MODE == MODE_FLEX16) {
+            const int m = (int)v, lo = m & 0xff;
+            ((signed char*)plane0)[i] = (signed char)((m - lo) >> 8);
+            ((unsigned char*)plane1)[i] = (unsigned char)lo;
+        } else {
+            float hi, lo;
+            tf32_split((float)v, hi, lo);
+            ((float*)plane0)[i] = hi;
+            ((float*)plane1)[i] = lo;
+        }
+    }
+}
+
+// A planes of the update contraction: row = (c*R + r_)*S + s_, column = (p*Q + q)*N + n, value
+// I[c, p*str - pad + r_*dil, q*str - pad + s_*dil, n] (zero outside the image).  One thread writes
+// 16 (flex16) or 4 (fp32) consecutive columns; they share (p, q) when N is a multiple of that.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+update_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int rows_p, int kp,
+                     void* __restrict__ plane0, void* __restrict__ plane1) {
+    constexpr int kPer = MODE == MODE_FLEX16 ? 16 : 4;
+    const int upr = kp / kPer;
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= (long long)rows_p * upr) return;
+    const int m = (int)(idx / upr), j0 = (int)(idx % upr) * kPer;
+    __align__(16) T v[kPer];
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) v[e] = 0;
+    if (m < rows && j0 < kg) {
+        const int RS = g.R * g.S;
+        const int c = m / RS, rs = m - c * RS, fr = rs / g.S, fs = rs - fr * g.S;
+        const T* plane = I + (long long)c * g.H * g.W * g.N;
+        const bool fast = (g.N % kPer == 0) && ((uintptr_t)I & 15) == 0;
+        if (fast) {
+            const int n0 = j0 % g.N, pq = j0 / g.N, q = pq % g.Q, pp = pq / g.Q;
+            const int h = pp * g.str_h - g.pad_h + fr * g.dil_h;
+            const int w = q * g.str_w - g.pad_w + fs * g.dil_w;
+            if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
+                const T* sp = plane + ((long long)h * g.W + w) * g.N + n0;
+                if (MODE == MODE_FLEX16) {
+                    const int4 a = __ldg((const int4*)sp), b = __ldg((const int4*)sp + 1);
+                    *(int4*)&v[0] = a;
+                    *(int4*)&v[8 % kPer] = b;
+                } else {
+                    *(float4*)&v[0] = __ldg((const float4*)sp);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                const int j = j0 + e;
+                if (j >= kg) break;
+                const int n = j % g.N, pq = j / g.N, q = pq % g.Q, pp = pq / g.Q;
+                const int h = pp * g.str_h - g.pad_h + fr * g.dil_h;
+                const int w = q * g.str_w - g.pad_w + fs * g.dil_w;
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W)
+                    v[e] = plane[((long long)h * g.W + w) * g.N + n];
+            }
+        }
+    }
+    const long long o = (long long)m * kp + j0;
+    if (MODE == MODE_FLEX16) {
+        unsigned hi[4] = {0, 0, 0, 0}, lo[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) {
+            const int mm = (int)v[e], l = mm & 0xff;
+            hi[e >> 2] |= (unsigned)(((mm - l) >> 8) & 0xff) << (8 * (e & 3));
+            lo[e >> 2] |= (unsigned)l << (8 * (e & 3));
+        }
+        *(uint4*)((unsigned char*)plane0 + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *(uint4*)((unsigned char*)plane1 + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    } else {
+        float hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) tf32_split((float)v[e % kPer], hi[e], lo[e]);
+        *(float4*)((float*)plane0 + o) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        *(float4*)((float*)plane1 + o) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+inline void fill_params(GemmParams* p, int M, int N, long long ldc, void* C, int colmajor,
+                        const b2_flex_scale* table, int slotA, int slotB, int slotC, int* stats,
+                        unsigned long long* probe_out, int* status, int probe) {
+    p->M = M; p->N = N; p->num_kb = 0; p->ldc = ldc; p->C = C; p->table = table;
+    p->slotA = slotA; p->slotB = slotB; p->slotC = slotC; p->stats = stats;
+    p->probe_out = probe_out; p->status = status; p->probe = probe; p->c_colmajor = colmajor;
+    p->rowsum = nullptr;
+}
+
+struct TrainShape { Shapes s; int splits; size_t bytes; };
+
+TrainShape bprop_shape(int mode, const ConvGeom& g) {
+    TrainShape t;
+    t.s = shapes_for(mode, g.H * g.W * g.N, g.C, g.K * g.R * g.S);
+    t.splits = pick_splits(mode, t.s, false);
+    t.bytes = align1k(t.s.bytes) + splitk_bytes(mode, t.s, t.splits);
+    return t;
+}
+
+TrainShape update_shape(int mode, const ConvGeom& g) {
+    TrainShape t;
+    t.s = shapes_for(mode, g.C * g.R * g.S, g.K, g.P * g.Q * g.N);
+    t.splits = pick_splits(mode, t.s, true);
+    t.bytes = align1k(t.s.bytes) + splitk_bytes(mode, t.s, t.splits);
+    return t;
+}
+
+template <typename T, int MODE>
+int run_bprop(const T* E, const T* F, void* GI, const b2_conv_dims* d, const b2_flex_scale* table,
+              int slotE, int slotF, int slotG, int* stats, void* scratch, size_t scratch_bytes,
+              unsigned long long* probe_out, int* status, int probe, cudaStream_t st) {
+    ConvGeom g;
+    int rc = geom_from(d, &g);
+    if (rc) return rc;
+    B2_REQUIRE(E && F && GI, "null tensor");
+    const long long rows_ll = (long long)g.H * g.W * g.N;
+    B2_REQUIRE(rows_ll < (1LL << 31) - 256 && (long long)g.K * g.P * g.Q * g.N < (1LL << 31),
+               "tensor too large");
+    const int rows = (int)rows_ll, kg = g.K * g.R * g.S;
+    const TrainShape t = bprop_shape(MODE, g);
+    const Shapes& s = t.s;
+    B2_REQUIRE(scratch && scratch_bytes >= t.bytes && ((uintptr_t)scratch & 1023) == 0,
+               "convolution bprop needs %zu bytes of 1024-byte aligned scratch, got %zu", t.bytes,
+               scratch_bytes);
+    unsigned char* base = (unsigned char*)scratch;
+    const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
+    im2col_planes_kernel<T, MODE, true><<<s.Mp / 32, 256, 0, st>>>(E, g, rows, kg, s.Mp, s.Kp, base,
+                                                                   base + a_plane);
+    long long blocks = ((long long)s.Np * s.Kp + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    filter_bprop_planes_kernel<T, MODE><<<(unsigned)blocks, 256, 0, st>>>(
+        F, g.C, g.R * g.S, g.K, s.Np, s.Kp, base + 2 * a_plane, base + 2 * a_plane + b_plane);
+    B2_CUDA(cudaGetLastError());
+    GemmParams p;
+    fill_params(&p, rows, g.C, rows, GI, 1, table, slotE, slotF, slotG, stats, probe_out, status,
+                probe);
+    return launch_on_planes<MODE>(base, s, p, st, t.splits, base + align1k(s.bytes));
+}
+
+template <typename T, int MODE>
+int run_update(const T* I, const T* E, void* U, const b2_conv_dims* d, const b2_flex_scale* table,
+               int slotI, int slotE, int slotU, int* stats, void* scratch, size_t scratch_bytes,
+               unsigned long long* probe_out, int* status, int probe, cudaStream_t st) {
+    ConvGeom g;
+    int rc = geom_from(d, &g);
+    if (rc) return rc;
+    B2_REQUIRE(I && E && U, "null tensor");
+    const long long kg_ll = (long long)g.P * g.Q * g.N;
+    B2_REQUIRE(kg_ll < (1LL << 31) - 256 && (long long)g.C * g.H * g.W * g.N < (1LL << 31),
+               "tensor too large");
+    const int rows = g.C * g.R * g.S, kg = (int)kg_ll;
+    const TrainShape t = update_shape(MODE, g);
+    const Shapes& s = t.s;
+    B2_REQUIRE(scratch && scratch_bytes >= t.bytes && ((uintptr_t)scratch & 1023) == 0,
+               "convolution update needs %zu bytes of 1024-byte aligned scratch, got %zu", t.bytes,
+               scratch_bytes);
+    unsigned char* base = (unsigned char*)scratch;
+    const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
+    const long long units = (long long)s.Mp * (s.Kp / (MODE == MODE_FLEX16 ? 16 : 4));
+    update_planes_kernel<T, MODE><<<(unsigned)((units + 255) / 256), 256, 0, st>>>(
+        I, g, rows, kg, s.Mp, s.Kp, base, base + a_plane);
+    B2_CUDA(cudaGetLastError());
+    // E is [K][(p,q,n)]: already the K-major B operand
+    rc = split_operand<T, MODE>(E, (long long)kg, 1, g.K, kg, s.Np, s.Kp, base + 2 * a_plane,
+                                base + 2 * a_plane + b_plane, 0, nullptr, st);
+    if (rc) return rc;
+    GemmParams p;
+    fill_params(&p, rows, g.K, g.K, U, 0, table, slotI, slotE, slotU, stats, probe_out, status,
+                probe);
+    return launch_on_planes<MODE>(base, s, p, st, t.splits, base + align1k(s.bytes));
 }
 
 // ---- average pooling over H, W windows (C and D windows of 1) ------------------------------------
@@ -747,6 +958,62 @@ extern "C" int b2_conv_fprop_flex16(const int16_t* I, const int16_t* F, int16_t*
     return run_fprop<short, MODE_FLEX16>(I, F, O, d, table, slotI, slotF, slotO, stats, scratch,
                                          scratch_bytes, (unsigned long long*)probe_out, status,
                                          probe ? 1 : 0, (cudaStream_t)stream);
+}
+
+extern "C" int b2_conv_bprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, size_t* bytes) {
+    ConvGeom g;
+    int rc = geom_from(d, &g);
+    if (rc) return rc;
+    B2_REQUIRE(bytes, "null argument");
+    *bytes = bprop_shape(flex ? MODE_FLEX16 : MODE_F32X3, g).bytes;
+    return B2_OK;
+}
+
+extern "C" int b2_conv_bprop_f32(const float* E, const float* F, float* GI, const b2_conv_dims* d,
+                                 void* scratch, size_t scratch_bytes, int32_t* status,
+                                 void* stream) {
+    return run_bprop<float, MODE_F32X3>(E, F, GI, d, nullptr, 0, 0, 0, nullptr, scratch,
+                                        scratch_bytes, nullptr, status, 0, (cudaStream_t)stream);
+}
+
+extern "C" int b2_conv_bprop_flex16(const int16_t* E, const int16_t* F, int16_t* GI,
+                                    const b2_conv_dims* d, const b2_flex_scale* table,
+                                    int32_t slotE, int32_t slotF, int32_t slotGI, int32_t* stats,
+                                    void* scratch, size_t scratch_bytes, uint64_t* probe_out,
+                                    int32_t* status, int32_t probe, void* stream) {
+    B2_REQUIRE(table && slotE >= 0 && slotF >= 0 && slotGI >= 0, "flex conv needs the scale table");
+    B2_REQUIRE(probe ? probe_out != nullptr : stats != nullptr, "missing statistics destination");
+    return run_bprop<short, MODE_FLEX16>(E, F, GI, d, table, slotE, slotF, slotGI, stats, scratch,
+                                         scratch_bytes, (unsigned long long*)probe_out, status,
+                                         probe ? 1 : 0, (cudaStream_t)stream);
+}
+
+extern "C" int b2_conv_update_scratch_bytes(int32_t flex, const b2_conv_dims* d, size_t* bytes) {
+    ConvGeom g;
+    int rc = geom_from(d, &g);
+    if (rc) return rc;
+    B2_REQUIRE(bytes, "null argument");
+    *bytes = update_shape(flex ? MODE_FLEX16 : MODE_F32X3, g).bytes;
+    return B2_OK;
+}
+
+extern "C" int b2_conv_update_f32(const float* I, const float* E, float* U, const b2_conv_dims* d,
+                                  void* scratch, size_t scratch_bytes, int32_t* status,
+                                  void* stream) {
+    return run_update<float, MODE_F32X3>(I, E, U, d, nullptr, 0, 0, 0, nullptr, scratch,
+                                         scratch_bytes, nullptr, status, 0, (cudaStream_t)stream);
+}
+
+extern "C" int b2_conv_update_flex16(const int16_t* I, const int16_t* E, int16_t* U,
+                                     const b2_conv_dims* d, const b2_flex_scale* table,
+                                     int32_t slotI, int32_t slotE, int32_t slotU, int32_t* stats,
+                                     void* scratch, size_t scratch_bytes, uint64_t* probe_out,
+                                     int32_t* status, int32_t probe, void* stream) {
+    B2_REQUIRE(table && slotI >= 0 && slotE >= 0 && slotU >= 0, "flex conv needs the scale table");
+    B2_REQUIRE(probe ? probe_out != nullptr : stats != nullptr, "missing statistics destination");
+    return run_update<short, MODE_FLEX16>(I, E, U, d, table, slotI, slotE, slotU, stats, scratch,
+                                          scratch_bytes, (unsigned long long*)probe_out, status,
+                                          probe ? 1 : 0, (cudaStream_t)stream);
 }
 
 extern "C" int b2_pool_avg_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H,

@@ -4,7 +4,8 @@
 
 extern "C" int b2_gemm_scratch_bytes(int32_t flex, int32_t M, int32_t N, int32_t K, size_t* bytes) {
     B2_REQUIRE(bytes && M > 0 && N > 0 && K > 0, "bad argument");
-    *bytes = shapes_for(flex ? MODE_FLEX16 : MODE_F32X3, M, N, K).bytes;
+    const int mode = flex ? MODE_FLEX16 : MODE_F32X3;
+    *bytes = gemm_scratch_need(mode, shapes_for(mode, M, N, K));
     return B2_OK;
 }
 

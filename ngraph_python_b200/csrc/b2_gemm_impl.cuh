@@ -20,7 +20,12 @@
 //           traffic from shared memory); the epilogue adds back 128 * sum_k a[m,k].
 //   fp32:   3xTF32: a = a_hi + a_lo with a_hi rounded to tf32, and
 //               a*b ~= a_hi*b_hi + a_hi*b_lo + a_lo*b_hi        (relative error ~2^-21)
-//           three kind::tf32 products into one fp32 accumulator.
+//           three kind::tf32 products into one fp32 accumulator.  The tensor core's fp32
+//           accumulation truncates, and the bias grows with the length of the accumulation
+//           chain (measured: 5e-4 relative at K = 40000), so the chain is cut every 16 k-blocks
+//           (512 elements): the MMA warp alternates between two accumulator buffers in tensor
+//           memory and the epilogue warps add each finished buffer into registers with ordinary
+//           round-to-nearest fp32 adds while the next chunk is being multiplied.
 //
 // Structure of the main kernel (one CTA per 128x128 output tile, 192 threads):
 //   warp 0   : TMA producer -- 2-D tiled bulk tensor copies of the four operand planes of a
@@ -57,6 +62,11 @@ __host__ __device__ constexpr int tmem_cols(int mode, int bn) {
     while (c < need) c *= 2;
     return c;
 }
+// the dense GEMM kernel keeps two fp32 accumulator buffers (see the head of this file)
+__host__ __device__ constexpr int gemm_tmem_cols(int mode, int bn) {
+    return mode == 0 ? tmem_cols(0, bn) : tmem_cols(1, 2 * bn);
+}
+constexpr int kChunkKb = 16;            // fp32: k-blocks per accumulation chain
 
 enum { MODE_FLEX16 = 0, MODE_F32X3 = 1 };
 
@@ -66,6 +76,9 @@ __device__ __forceinline__ unsigned smem_u32(const void* p) {
 }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -171,6 +184,10 @@ struct GemmParams {
     int probe;
     int c_colmajor;                  // 0: C[row*ldc + col]; 1: C[col*ldc + row]
     const int* rowsum;               // flex16 merged form: sum_k a[m,k] per row of A, else null
+    // split-K: grid.z slices of kb_per_split k-blocks each write raw sums (int64 for flex16, float
+    // for fp32) to partial[z][Mp][Np]; splitk_finish_kernel adds the slices in a fixed order
+    void* partial;
+    int kb_per_split, Mp, Np;
 };
 
 // round-to-nearest-even of v / 2^sh (sh > 0), or v * 2^-sh (sh <= 0), saturated to int16
@@ -202,20 +219,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int kStageBytes = stage_bytes(BN);
     constexpr int kBPlane = BN * kKBytes;
-    constexpr int kTmemCols = tmem_cols(MODE, BN);
+    constexpr int kTmemCols = gemm_tmem_cols(MODE, BN);
     unsigned long long* full_bar = (unsigned long long*)(smem + kStages * kStageBytes);
     unsigned long long* empty_bar = full_bar + kStages;
-    unsigned long long* tmem_full = empty_bar + kStages;
-    unsigned* tmem_holder = (unsigned*)(tmem_full + 1);
+    unsigned long long* tmem_full = empty_bar + kStages;        // [2]
+    unsigned long long* tmem_empty = tmem_full + 2;             // [2] (fp32 only)
+    unsigned* tmem_holder = (unsigned*)(tmem_empty + 2);
     int* fail_flag = (int*)(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * kBlockM, n0 = blockIdx.x * BN;
     const int kElems = MODE == MODE_FLEX16 ? kKBytes : kKBytes / 4;   // elements of K per k-block
+    const int kb0 = p.partial ? blockIdx.z * p.kb_per_split : 0;
+    const int nkb = p.partial ? min(p.kb_per_split, p.num_kb - kb0) : p.num_kb;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(tmem_full, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
         *fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -227,7 +247,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < p.num_kb; ++kb) {
+            for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % kStages;
                 if (kb >= kStages && !mbar_wait(&empty_bar[s], ((kb / kStages) - 1) & 1)) {
                     atomicExch(fail_flag, 1);
@@ -235,7 +255,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 }
                 unsigned char* st = smem + s * kStageBytes;
                 mbar_expect_tx(&full_bar[s], kStageBytes);
-                const int kx = kb * kElems;
+                const int kx = (kb0 + kb) * kElems;
                 tma_load_2d(st + 0 * kPlaneBytes, &mapA0, kx, m0, &full_bar[s]);
                 tma_load_2d(st + 1 * kPlaneBytes, &mapA1, kx, m0, &full_bar[s]);
                 tma_load_2d(st + 2 * kPlaneBytes, &mapB0, kx, n0, &full_bar[s]);
@@ -251,7 +271,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             const unsigned id_ss2 = make_idesc(2, 1, 1, 2 * BN), id_us2 = make_idesc(2, 0, 1, 2 * BN);
             const bool merged = MODE == MODE_FLEX16 && p.rowsum != nullptr;
             bool ok = true;
-            for (int kb = 0; kb < p.num_kb && ok; ++kb) {
+            for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % kStages;
                 if (!mbar_wait(&full_bar[s], (kb / kStages) & 1)) { atomicExch(fail_flag, 1); ok = false; break; }
                 tc_fence_after();
@@ -260,10 +280,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 const unsigned long long dA1 = make_smem_desc(st + 1 * kPlaneBytes);
                 const unsigned long long dB0 = make_smem_desc(st + 2 * kPlaneBytes);
                 const unsigned long long dB1 = make_smem_desc(st + 2 * kPlaneBytes + kBPlane);
+                // fp32: accumulation chains of kChunkKb k-blocks alternate between two buffers
+                const int chunk = MODE == MODE_F32X3 ? kb / kChunkKb : 0;
+                const int kin = MODE == MODE_F32X3 ? kb % kChunkKb : kb;
+                const unsigned tmem_acc = tmem_base + (MODE == MODE_F32X3 ? (chunk & 1) * BN : 0);
+                if (MODE == MODE_F32X3 && kin == 0 && chunk >= 2) {
+                    if (!mbar_wait(&tmem_empty[chunk & 1], ((chunk >> 1) - 1) & 1)) {
+                        atomicExch(fail_flag, 1); ok = false; break;
+                    }
+                    tc_fence_after();
+                }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * 32) >> 4);
-                    const unsigned acc = (kb > 0 || k > 0) ? 1u : 0u;
+                    const unsigned acc = (kin > 0 || k > 0) ? 1u : 0u;
                     if (merged && acc) {
                         // B_hi and B_lo' are adjacent: one descriptor spans both
                         tc_mma<MODE>(tmem_base + 0, dA0 + adv, dB0 + adv, id_ss2, 1u);      // HH | X
@@ -280,22 +310,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                         tc_mma<MODE>(tmem_base + BN, dA1 + adv, dB0 + adv, id_us, 1u);      // X += al*bh
                         tc_mma<MODE>(tmem_base + 2 * BN, dA1 + adv, dB1 + adv, id_uu, acc); // LL
                     } else {
-                        tc_mma<MODE>(tmem_base, dA0 + adv, dB0 + adv, id_tf, acc);          // hi*hi
-                        tc_mma<MODE>(tmem_base, dA0 + adv, dB1 + adv, id_tf, 1u);           // hi*lo
-                        tc_mma<MODE>(tmem_base, dA1 + adv, dB0 + adv, id_tf, 1u);           // lo*hi
+                        tc_mma<MODE>(tmem_acc, dA0 + adv, dB0 + adv, id_tf, acc);           // hi*hi
+                        tc_mma<MODE>(tmem_acc, dA0 + adv, dB1 + adv, id_tf, 1u);            // hi*lo
+                        tc_mma<MODE>(tmem_acc, dA1 + adv, dB0 + adv, id_tf, 1u);            // lo*hi
                     }
                 }
                 tc_commit(&empty_bar[s]);       // stage reusable once these MMAs have read it
+                if (MODE == MODE_F32X3 && (kin == kChunkKb - 1 || kb == nkb - 1))
+                    tc_commit(&tmem_full[chunk & 1]);      // this chain is complete
             }
-            tc_commit(tmem_full);               // accumulators complete
+            if (MODE == MODE_FLEX16) tc_commit(&tmem_full[0]);     // accumulators complete
         }
     } else {
         // epilogue warps 2..5: TMEM lane quarter = warp % 4
         const int quarter = warp & 3;
         const int row = m0 + quarter * 32 + lane;
-        bool ok = mbar_wait(tmem_full, 0);
-        if (!ok) atomicExch(fail_flag, 1);
-        tc_fence_after();
+        bool ok = true;
+        if (MODE == MODE_FLEX16) {
+            ok = mbar_wait(&tmem_full[0], 0);
+            if (!ok) atomicExch(fail_flag, 1);
+            tc_fence_after();
+        }
         const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
         if (MODE == MODE_FLEX16) {
             const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
@@ -304,7 +339,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             int stat = 0;
             unsigned long long pmax = 0;
             short* crow = (short*)p.C + (long long)row * p.ldc;
-            const long long fix = (p.rowsum && row < p.M) ? 128LL * (long long)p.rowsum[row] : 0LL;
+            // the row-sum term belongs to the whole contraction: slice 0 carries it
+            const long long fix = (p.rowsum && row < p.M && (!p.partial || blockIdx.z == 0))
+                                      ? 128LL * (long long)p.rowsum[row] : 0LL;
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 unsigned hh[16], xx[16], ll[16];
                 tmem_ld16(lane_addr + c0, hh);
@@ -312,6 +349,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 tmem_ld16(lane_addr + 2 * BN + c0, ll);
                 tmem_ld_wait();
                 if (!ok || row >= p.M) continue;
+                if (p.partial) {
+                    long long* dst = (long long*)p.partial +
+                                     ((long long)blockIdx.z * p.Mp + row) * p.Np + n0 + c0;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        dst[j] = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
+                                 (long long)(int)ll[j] + fix;
+                    continue;
+                }
                 int q[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -349,7 +395,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                     }
                 }
             }
-            if (p.probe) {
+            if (p.partial) {
+                // statistics are taken by the finishing kernel
+            } else if (p.probe) {
                 for (int o = 16; o > 0; o >>= 1) {
                     const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
                     pmax = t > pmax ? t : pmax;
@@ -363,28 +411,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 if (lane == 0 && stat) atomicMax(p.stats + p.slotC, stat);
             }
         } else {
+            // add every finished accumulation chain into registers (round-to-nearest adds)
+            float sum[BN];
+#pragma unroll
+            for (int j = 0; j < BN; ++j) sum[j] = 0.f;
+            const int nchunks = (nkb + kChunkKb - 1) / kChunkKb;
+            for (int chunk = 0; chunk < nchunks; ++chunk) {
+                const int b = chunk & 1;
+                if (ok && !mbar_wait(&tmem_full[b], (chunk >> 1) & 1)) {
+                    atomicExch(fail_flag, 1);
+                    ok = false;
+                }
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    unsigned acc[16];
+                    tmem_ld16(lane_addr + b * BN + c0, acc);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sum[c0 + j] += __uint_as_float(acc[j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[b]);
+            }
             float* crow = (float*)p.C + (long long)row * p.ldc;
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                unsigned acc[16];
-                tmem_ld16(lane_addr + c0, acc);
-                tmem_ld_wait();
-                if (!ok || row >= p.M) continue;
-                const int col = n0 + c0;
-                if (p.c_colmajor) {
+            if (ok && row < p.M) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (col + j < p.N)
-                            ((float*)p.C)[(long long)(col + j) * p.ldc + row] = __uint_as_float(acc[j]);
-                } else if (col + 16 <= p.N && ((p.ldc & 3) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    const int col = n0 + c0;
+                    if (p.partial) {
+                        float* dst = (float*)p.partial + ((long long)blockIdx.z * p.Mp + row) * p.Np + col;
 #pragma unroll
-                    for (int j = 0; j < 16; j += 4)
-                        *reinterpret_cast<float4*>(crow + col + j) =
-                            make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]),
-                                        __uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
-                } else {
+                        for (int j = 0; j < 16; j += 4)
+                            *reinterpret_cast<float4*>(dst + j) =
+                                make_float4(sum[c0 + j], sum[c0 + j + 1], sum[c0 + j + 2], sum[c0 + j + 3]);
+                    } else if (p.c_colmajor) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (col + j < p.N) crow[col + j] = __uint_as_float(acc[j]);
+                        for (int j = 0; j < 16; ++j)
+                            if (col + j < p.N)
+                                ((float*)p.C)[(long long)(col + j) * p.ldc + row] = sum[c0 + j];
+                    } else if (col + 16 <= p.N && ((p.ldc & 3) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            *reinterpret_cast<float4*>(crow + col + j) =
+                                make_float4(sum[c0 + j], sum[c0 + j + 1], sum[c0 + j + 2], sum[c0 + j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (col + j < p.N) crow[col + j] = sum[c0 + j];
+                    }
                 }
             }
         }
@@ -396,6 +472,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
         tmem_dealloc(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0 && *fail_flag && p.status) atomicExch(p.status, 1);
+}
+
+// ---- split-K second stage ----------------------------------------------------------------------
+// Adds the slices of one output element in slice order (deterministic), then finishes it like the
+// tile kernel's epilogue: flex16 rescale + saturate + statistics (or the probe maximum), fp32 store.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const GemmParams p, int splits) {
+    const long long total = (long long)p.M * p.N;
+    int stat = 0;
+    unsigned long long pmax = 0;
+    int sh = 0;
+    if (MODE == MODE_FLEX16) {
+        const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
+                        (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
+        sh = -ilogbf(f);
+    }
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total;
+         i += (long long)gridDim.x * 256) {
+        const int row = (int)(i / p.N), col = (int)(i % p.N);
+        const long long src = (long long)row * p.Np + col, slice = (long long)p.Mp * p.Np;
+        const long long dst = p.c_colmajor ? (long long)col * p.ldc + row : (long long)row * p.ldc + col;
+        if (MODE == MODE_FLEX16) {
+            long long v = 0;
+            for (int z = 0; z < splits; ++z) v += ((const long long*)p.partial)[z * slice + src];
+            if (p.probe) {
+                const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
+                pmax = a > pmax ? a : pmax;
+            } else {
+                const int q = rescale_i64(v, sh);
+                const int a = q < 0 ? -q : q;
+                stat = a > stat ? a : stat;
+                ((short*)p.C)[dst] = (short)q;
+            }
+        } else {
+            float v = 0.f;
+            for (int z = 0; z < splits; ++z) v += ((const float*)p.partial)[z * slice + src];
+            ((float*)p.C)[dst] = v;
+        }
+    }
+    if (MODE == MODE_FLEX16) {
+        if (p.probe) {
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
+                pmax = t > pmax ? t : pmax;
+            }
+            if ((threadIdx.x & 31) == 0 && pmax) atomicMax(p.probe_out, pmax);
+        } else {
+            for (int o = 16; o > 0; o >>= 1) {
+                const int t = __shfl_xor_sync(0xffffffffu, stat, o);
+                stat = t > stat ? t : stat;
+            }
+            if ((threadIdx.x & 31) == 0 && stat) atomicMax(p.stats + p.slotC, stat);
+        }
+    }
 }
 
 // ---- pre-pass: operand planes, K-major, zero padded ---------------------------------------------
@@ -670,6 +801,7 @@ int make_map(CUtensorMap* map, void* base, int rows_p, int kp, int esize, int bo
 }
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline size_t align1k(size_t v) { return (v + 1023) & ~(size_t)1023; }
 
 struct Shapes { int Mp, Np, Kp, esize, bn; size_t bytes, a_bytes, rowsum_off; };
 
@@ -691,23 +823,52 @@ Shapes shapes_for(int mode, int M, int N, int K) {
 
 template <int MODE, int BN>
 int launch_tile(const CUtensorMap& mA0, const CUtensorMap& mA1, const CUtensorMap& mB0,
-                const CUtensorMap& mB1, const GemmParams& p, const Shapes& s, cudaStream_t st) {
+                const CUtensorMap& mB1, const GemmParams& p, const Shapes& s, int splits,
+                cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
         B2_CUDA(cudaFuncSetAttribute(gemm_kernel<MODE, BN>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(BN)));
         attr_set = true;
     }
-    dim3 grid(s.Np / BN, s.Mp / kBlockM);
+    dim3 grid(s.Np / BN, s.Mp / kBlockM, splits);
     gemm_kernel<MODE, BN><<<grid, kThreads, smem_bytes(BN), st>>>(mA0, mA1, mB0, mB1, p);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }
 
+// bytes of split-K workspace for `splits` slices (0 when the GEMM runs in one slice)
+inline size_t splitk_bytes(int mode, const Shapes& s, int splits) {
+    return splits > 1 ? (size_t)splits * s.Mp * s.Np * (mode == MODE_FLEX16 ? 8 : 4) : 0;
+}
+
+// Number of K slices: at least enough that a flex16 slice keeps exact int32 sums (256 k-blocks =
+// 32768 elements), and, when `fill` is set, enough to give every SM a tile.
+inline int pick_splits(int mode, const Shapes& s, bool fill) {
+    const int num_kb = s.Kp / (kKBytes / s.esize);
+    int splits = 1;
+    if (mode == MODE_FLEX16) splits = (num_kb + 255) / 256;
+    if (fill) {
+        const int tiles = (s.Mp / kBlockM) * (s.Np / s.bn);
+        int want = (2 * 148 + tiles - 1) / tiles;
+        const int max_by_k = num_kb / 4 > 0 ? num_kb / 4 : 1;      // at least 4 k-blocks a slice
+        if (want > max_by_k) want = max_by_k;
+        if (want > splits) splits = want;
+    }
+    return splits;
+}
+
+// scratch of the dense GEMM entry points: operand planes (+ row sums), then the split-K slices
+inline size_t gemm_scratch_need(int mode, const Shapes& s) {
+    return align1k(s.bytes) + splitk_bytes(mode, s, pick_splits(mode, s, false));
+}
+
 // Launches the tile kernel on operand planes that are already in scratch:
-// A planes at `base`, B planes behind them.
+// A planes at `base`, B planes behind them.  With splits > 1, `workspace` (splitk_bytes) receives
+// the slices and a finishing kernel writes C.
 template <int MODE>
-int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStream_t st) {
+int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStream_t st,
+                     int splits = 1, void* workspace = nullptr) {
     int rc = get_encode();
     if (rc) return rc;
     const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
@@ -719,12 +880,26 @@ int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStr
     if ((rc = make_map(&mB0, B0, s.Np, s.Kp, s.esize, s.bn))) return rc;
     if ((rc = make_map(&mB1, B1, s.Np, s.Kp, s.esize, s.bn))) return rc;
     p.num_kb = s.Kp / (kKBytes / s.esize);
-    switch (s.bn) {
-        case 16: return launch_tile<MODE, 16>(mA0, mA1, mB0, mB1, p, s, st);
-        case 32: return launch_tile<MODE, 32>(mA0, mA1, mB0, mB1, p, s, st);
-        case 64: return launch_tile<MODE, 64>(mA0, mA1, mB0, mB1, p, s, st);
-        default: return launch_tile<MODE, 128>(mA0, mA1, mB0, mB1, p, s, st);
+    p.Mp = s.Mp; p.Np = s.Np;
+    p.partial = nullptr; p.kb_per_split = p.num_kb;
+    if (splits > 1) {
+        B2_REQUIRE(workspace, "split-K needs a workspace");
+        p.partial = workspace;
+        p.kb_per_split = (p.num_kb + splits - 1) / splits;
+        splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;      // no empty slice
     }
+    switch (s.bn) {
+        case 16: rc = launch_tile<MODE, 16>(mA0, mA1, mB0, mB1, p, s, splits, st); break;
+        case 32: rc = launch_tile<MODE, 32>(mA0, mA1, mB0, mB1, p, s, splits, st); break;
+        case 64: rc = launch_tile<MODE, 64>(mA0, mA1, mB0, mB1, p, s, splits, st); break;
+        default: rc = launch_tile<MODE, 128>(mA0, mA1, mB0, mB1, p, s, splits, st); break;
+    }
+    if (rc || !p.partial) return rc;
+    long long blocks = ((long long)p.M * p.N + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    splitk_finish_kernel<MODE><<<(unsigned)blocks, 256, 0, st>>>(p, splits);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
 }
 
 template <typename T, int MODE>
@@ -735,10 +910,11 @@ int run_gemm(const T* A, long long a_rs, long long a_cs, const T* B, long long b
     B2_REQUIRE(A && B && C && M > 0 && N > 0 && K > 0, "bad GEMM argument");
     B2_REQUIRE(a_rs == 1 || a_cs == 1, "A must be contiguous along M or K");
     B2_REQUIRE(b_ks == 1 || b_ns == 1, "B must be contiguous along K or N");
-    if (MODE == MODE_FLEX16) B2_REQUIRE(K <= 32768, "flex16 GEMM keeps exact int32 sums for K <= 32768");
     const Shapes s = shapes_for(MODE, M, N, K);
-    B2_REQUIRE(scratch && scratch_bytes >= s.bytes && ((uintptr_t)scratch & 1023) == 0,
-               "GEMM needs %zu bytes of 1024-byte aligned scratch, got %zu", s.bytes, scratch_bytes);
+    const int splits = pick_splits(MODE, s, false);     // > 1 only for flex16 with K > 32768
+    const size_t need = gemm_scratch_need(MODE, s);
+    B2_REQUIRE(scratch && scratch_bytes >= need && ((uintptr_t)scratch & 1023) == 0,
+               "GEMM needs %zu bytes of 1024-byte aligned scratch, got %zu", need, scratch_bytes);
     unsigned char* base = (unsigned char*)scratch;
     const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
     void* A0 = base; void* A1 = base + a_plane;
@@ -761,7 +937,7 @@ int run_gemm(const T* A, long long a_rs, long long a_cs, const T* B, long long b
     p.stats = stats; p.probe_out = probe_out; p.status = status; p.probe = probe;
     p.c_colmajor = 0;
     p.rowsum = rowsum;
-    return launch_on_planes<MODE>(base, s, p, st);
+    return launch_on_planes<MODE>(base, s, p, st, splits, base + align1k(s.bytes));
 }
 
 }  // namespace

@@ -180,6 +180,93 @@ class ConvStep(_Step):
         self._flex_probe_then(t, ov.buffer, [iv.buffer, fv.buffer], call)
 
 
+def _conv_dims_of(fprop, t):
+    """ConvDims of a forward ConvolutionOp (axes C,D,H,W,N / C,T,R,S,K / K,M,P,Q,N)."""
+    cp = fprop.conv_params
+    Cc, D, H, W, N = fprop.args[0].axes.lengths
+    C2, T, R, S, K = fprop.args[1].axes.lengths
+    K2, M, P, Q, N2 = fprop.axes.lengths
+    d = lib.ConvDims()
+    d.C, d.D, d.H, d.W, d.N = Cc, D, H, W, N
+    d.K, d.T, d.R, d.S = K, T, R, S
+    d.M, d.P, d.Q = M, P, Q
+    for k in ("pad_d", "pad_h", "pad_w"):
+        setattr(d, k, int(cp.get(k, 0)))
+    for k in ("str_d", "str_h", "str_w", "dil_d", "dil_h", "dil_w"):
+        setattr(d, k, int(cp.get(k, 1)))
+    return d
+
+
+class _ConvGradStep(_Step):
+    """Shared part of the two convolution gradients: two dense operands, one dense result, the
+    forward convolution's dimensions."""
+    launches = 3
+    what = None                     # "bprop" | "update"
+
+    def __init__(self, index, op, t):
+        super(_ConvGradStep, self).__init__(index, op)
+        av, bv, ov = t._view_of(op.args[0]), t._view_of(op.args[1]), t._view_of(op)
+        for v in (av, bv):
+            if not v.is_dense():
+                raise ValueError("Unhandled op: convolution %s operands must be dense tensors"
+                                 % self.what)
+        self.dims = _conv_dims_of(op.fprop, t)
+        d = self.dims
+        expect = {"bprop": ((d.K, d.M, d.P, d.Q, d.N), (d.C, d.T, d.R, d.S, d.K),
+                            (d.C, d.D, d.H, d.W, d.N)),
+                  "update": ((d.K, d.M, d.P, d.Q, d.N), (d.C, d.D, d.H, d.W, d.N),
+                             (d.C, d.T, d.R, d.S, d.K))}[self.what]
+        for v, shape in zip((av, bv, ov), expect):
+            if tuple(v.axes.lengths) != shape:
+                raise ValueError("convolution %s: tensor of shape %s where %s is expected"
+                                 % (self.what, tuple(v.axes.lengths), shape))
+        self.in_views = [av, bv]
+        self.out_views = [ov]
+        self.flex = t.flex
+        sizer = lib.conv_bprop_scratch_bytes if self.what == "bprop" else \
+            lib.conv_update_scratch_bytes
+        self.scratch_bytes = sizer(self.flex, d) + 1024
+
+    def launch(self, t):
+        av, bv = self.in_views           # (delta, filters) or (delta, inputs)
+        ov = self.out_views[0]
+        raw = lib.raw()
+        sp, sb = t._scratch_aligned()
+        st = t.stream.cuda_stream
+        if self.what == "bprop":
+            first, second = av, bv       # E, F
+            f32, f16 = raw.b2_conv_bprop_f32, raw.b2_conv_bprop_flex16
+        else:
+            first, second = bv, av       # I, E
+            f32, f16 = raw.b2_conv_update_f32, raw.b2_conv_update_flex16
+        if not self.flex:
+            lib.check(f32(self._ptr(first), self._ptr(second), self._ptr(ov), C.byref(self.dims),
+                          sp, sb, t._status.data_ptr(), st))
+            t.kernel_launches += self.launches
+            return
+        slots = (t._slot_for_read(first.buffer, self), t._slot_for_read(second.buffer, self),
+                 ov.buffer.slot_write)
+
+        def call(probe):
+            lib.check(f16(self._ptr(first), self._ptr(second), self._ptr(ov), C.byref(self.dims),
+                          t._table.data_ptr(), slots[0], slots[1], slots[2], t._stats.data_ptr(),
+                          sp, sb, t._probe64.data_ptr(), t._status.data_ptr(), probe, st))
+        self._flex_probe_then(t, ov.buffer, [first.buffer, second.buffer], call)
+
+
+class ConvBpropStep(_ConvGradStep):
+    """Input gradient of a convolution: args (delta K,M,P,Q,N ; filters C,T,R,S,K)."""
+    kind = "conv_bprop"
+    what = "bprop"
+
+
+class ConvUpdateStep(_ConvGradStep):
+    """Filter gradient of a convolution: args (delta K,M,P,Q,N ; inputs C,D,H,W,N)."""
+    kind = "conv_update"
+    what = "update"
+    launches = 4                    # two operand kernels, the tile kernel, the slice sum
+
+
 class PoolStep(_Step):
     """Average pooling forward; a flex output keeps its input's exponent
     (ngraph/transformers/passes/flexpass.py:40-48)."""

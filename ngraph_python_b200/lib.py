@@ -90,6 +90,14 @@ def _load():
         "b2_conv_fprop_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
         "b2_conv_fprop_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,
                                            vp, sz, vp, vp, i32, vp]),
+        "b2_conv_bprop_scratch_bytes": (C.c_int, [i32, C.POINTER(ConvDims), C.POINTER(sz)]),
+        "b2_conv_bprop_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
+        "b2_conv_bprop_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,
+                                           vp, sz, vp, vp, i32, vp]),
+        "b2_conv_update_scratch_bytes": (C.c_int, [i32, C.POINTER(ConvDims), C.POINTER(sz)]),
+        "b2_conv_update_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
+        "b2_conv_update_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,
+                                            vp, sz, vp, vp, i32, vp]),
         "b2_pool_avg_fprop": (C.c_int, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32,
                                         i32, i32, i32, vp, vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
@@ -230,4 +238,16 @@ def gemm_scratch_bytes(flex, M, N, K):
 def conv_fprop_scratch_bytes(flex, dims):
     n = C.c_size_t()
     check(_lib.b2_conv_fprop_scratch_bytes(int(bool(flex)), C.byref(dims), C.byref(n)))
+    return n.value
+
+
+def conv_bprop_scratch_bytes(flex, dims):
+    n = C.c_size_t()
+    check(_lib.b2_conv_bprop_scratch_bytes(int(bool(flex)), C.byref(dims), C.byref(n)))
+    return n.value
+
+
+def conv_update_scratch_bytes(flex, dims):
+    n = C.c_size_t()
+    check(_lib.b2_conv_update_scratch_bytes(int(bool(flex)), C.byref(dims), C.byref(n)))
     return n.value

@@ -22,6 +22,8 @@ import numpy as np
 
 import ngraph.op_graph.op_graph as ref
 from ngraph.op_graph.convolution import ConvolutionOp as RefConvolutionOp
+from ngraph.op_graph.convolution import bprop_conv as ref_bprop_conv
+from ngraph.op_graph.convolution import update_conv as ref_update_conv
 from ngraph.op_graph.pooling import PoolingOp as RefPoolingOp
 from ngraph.transformers.base import Transformer
 
@@ -105,6 +107,12 @@ class GraphTranslator(object):
             return b2.broadcast(args[0], self.axes(op.axes))
         if isinstance(op, RefConvolutionOp):
             return b2.convolution(dict(op.conv_params), args[0], args[1], self.axes(op.axes))
+        if isinstance(op, ref_bprop_conv):           # args (delta, filters)
+            fprop = self(op.fprop)
+            return b2.bprop_conv(args[0], fprop.args[0], args[1], fprop)
+        if isinstance(op, ref_update_conv):          # args (delta, inputs)
+            fprop = self(op.fprop)
+            return b2.update_conv(args[0], args[1], fprop.args[1], fprop)
         if isinstance(op, RefPoolingOp):
             return b2.pooling(dict(op.pool_params), args[0], self.axes(op.axes))
         if isinstance(op, ref.ContiguousOp):

@@ -532,6 +532,37 @@ def convolution(conv_params, inputs, filters, axes, **kw):
     return ConvolutionOp(conv_params, inputs, filters, make_axes(axes), **kw)
 
 
+class ConvDerivOp(Op):
+    """Common part of the two convolution gradients: they carry the forward op, whose
+    conv_params and tensor extents they share (ngraph/op_graph/convolution.py: ConvDerivOp)."""
+
+    def __init__(self, args, fprop, axes, **kw):
+        if not isinstance(fprop, ConvolutionOp):
+            raise ValueError("fprop must be the forward ConvolutionOp")
+        super(ConvDerivOp, self).__init__(args, axes, **kw)
+        self.fprop = fprop
+        self.conv_params = fprop.conv_params
+        self.add_control_dep(fprop)
+
+
+class update_conv(ConvDerivOp):
+    """Filter gradient U[C,T,R,S,K] = sum_{p,q,n} I * delta
+    (ngraph/op_graph/convolution.py: update_conv; args are (delta, inputs))."""
+
+    def __init__(self, delta, inputs, filters, fprop, **kw):
+        delta, inputs = as_op(delta), as_op(inputs)
+        super(update_conv, self).__init__((delta, inputs), fprop, as_op(filters).axes, **kw)
+
+
+class bprop_conv(ConvDerivOp):
+    """Input gradient gI[C,D,H,W,N] = sum_{k,r,s} F * delta
+    (ngraph/op_graph/convolution.py: bprop_conv; args are (delta, filters))."""
+
+    def __init__(self, delta, inputs, filters, fprop, **kw):
+        delta, filters = as_op(delta), as_op(filters)
+        super(bprop_conv, self).__init__((delta, filters), fprop, as_op(inputs).axes, **kw)
+
+
 class PoolingOp(Op):
     """ngraph/op_graph/pooling.py: PoolingOp; input C,D,H,W,N -> output C,M,P,Q,N."""
 

@@ -23,7 +23,7 @@ from . import kernels
 from . import lib
 from . import comm as commmod
 from .op_graph import (AllReduceOp, AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp,
-                       ConvolutionOp, DotOp,
+                       ConvolutionOp, DotOp, bprop_conv, update_conv,
                        ElementWiseOp, Op, PoolingOp, ReductionOp, ReorderAxes, SequentialOp,
                        ViewOp, as_op, make_axes)
 
@@ -467,6 +467,10 @@ class _Planner(object):
             step = kernels.GemmStep(index, op, self.t)
         elif isinstance(op, ConvolutionOp):
             step = kernels.ConvStep(index, op, self.t)
+        elif isinstance(op, bprop_conv):
+            step = kernels.ConvBpropStep(index, op, self.t)
+        elif isinstance(op, update_conv):
+            step = kernels.ConvUpdateStep(index, op, self.t)
         elif isinstance(op, PoolingOp):
             step = kernels.PoolStep(index, op, self.t)
         else:

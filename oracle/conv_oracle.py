@@ -1,4 +1,5 @@
-"""CPU restatement of the reference's convolution / pooling forward for C,D,H,W,N tensors.
+"""CPU restatement of the reference's convolution (forward and the two gradients) and average
+pooling for C,D,H,W,N tensors.
 
 TEST INFRASTRUCTURE ONLY (tests, smoke check, CPU-baseline legs of the bench).  Follows the numpy
 fallbacks of the reference's CPU engine (ngraph/transformers/cpu/cpuengine.py:234-283 fprop_conv:
@@ -6,8 +7,11 @@ for every output position, dot of the clipped filter slice with the clipped inpu
 fprop_pool avg: mean of the clipped window) and ngraph/testing/conv_utils.py:66-102
 (reference_conv).  Written tap-wise instead of position-wise: for every filter tap (r, s) one
 tensordot over channels, which is the same sum in a different order.
+The gradients follow ngraph/transformers/cpu/cpuengine.py:256-271 (bprop_conv: the same loop with
+the filter flipped and transposed over the "backward" slices) and :395-418 (update_conv: for every
+output position, outer product of the clipped input slice with the error column, accumulated).
 Pinned against the reference CPU transformer's outputs in tests/golden/fixtures (conv_basic,
-conv_stride2_*, resnet*).
+conv_stride2_*, conv_grads*, resnet*).
 """
 import numpy as np
 
@@ -31,6 +35,45 @@ def conv_fprop(I, F, pad=(0, 0), stride=(1, 1), dtype=np.float32):
             win = Ip[:, r:r + (P - 1) * sh + 1:sh, s:s + (Q - 1) * sw + 1:sw, :]
             O += np.tensordot(Ft[:, r, s, :].T, win, axes=([1], [0]))
     return O
+
+
+def conv_bprop(E, F, in_hw, pad=(0, 0), stride=(1, 1), dtype=np.float32):
+    """E: (K, P, Q, N); F: (C, R, S, K) -> gI: (C, H, W, N), the gradient of conv_fprop with
+    respect to its input.  Every tap scatters F[:, r, s, :] . E onto the input positions it read."""
+    K, P, Q, N = E.shape
+    C, R, S, K2 = F.shape
+    assert K == K2
+    H, W = in_hw
+    ph, pw = pad
+    sh, sw = stride
+    G = np.zeros((C, H + 2 * ph + R, W + 2 * pw + S, N), dtype=dtype)
+    Ft = F.astype(dtype)
+    Et = E.astype(dtype)
+    for r in range(R):
+        for s in range(S):
+            G[:, r:r + (P - 1) * sh + 1:sh, s:s + (Q - 1) * sw + 1:sw, :] += np.tensordot(
+                Ft[:, r, s, :], Et, axes=([1], [0]))
+    return np.ascontiguousarray(G[:, ph:ph + H, pw:pw + W, :])
+
+
+def conv_update(I, E, filter_hw, pad=(0, 0), stride=(1, 1), dtype=np.float32):
+    """I: (C, H, W, N); E: (K, P, Q, N) -> U: (C, R, S, K), the gradient of conv_fprop with
+    respect to its filters."""
+    C, H, W, N = I.shape
+    K, P, Q, N2 = E.shape
+    assert N == N2
+    R, S = filter_hw
+    ph, pw = pad
+    sh, sw = stride
+    Ip = np.zeros((C, H + 2 * ph + R, W + 2 * pw + S, N), dtype=dtype)
+    Ip[:, ph:ph + H, pw:pw + W, :] = I
+    Et = E.astype(dtype)
+    U = np.zeros((C, R, S, K), dtype=dtype)
+    for r in range(R):
+        for s in range(S):
+            win = Ip[:, r:r + (P - 1) * sh + 1:sh, s:s + (Q - 1) * sw + 1:sw, :]
+            U[:, r, s, :] = np.tensordot(win, Et, axes=([1, 2, 3], [1, 2, 3]))
+    return U
 
 
 def pool_avg_fprop(I, window, pad=(0, 0), stride=(1, 1)):

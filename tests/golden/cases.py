@@ -163,6 +163,42 @@ def conv_stride2_3x3(ng):
     return conv_basic(ng, C=3, K=16, H=9, W=11, N=32, R=3, S=3, pad=1, stride=2)
 
 
+def _conv_grad_ops(ng):
+    """bprop_conv / update_conv: the reference keeps them in ngraph.op_graph.convolution, outside
+    its ng namespace."""
+    if hasattr(ng, "bprop_conv"):
+        return ng.bprop_conv, ng.update_conv
+    from ngraph.op_graph.convolution import bprop_conv, update_conv
+    return bprop_conv, update_conv
+
+
+def conv_grads(ng, C=16, K=32, H=12, W=10, N=32, R=3, S=3, pad=1, stride=1):
+    """Forward convolution and its two gradients for a given error tensor
+    (tests/transformer_dependent/test_conv.py:55-89 checks the same three results)."""
+    P = (H + 2 * pad - R) // stride + 1
+    Q = (W + 2 * pad - S) // stride + 1
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    ax_i = [ax(C, "C"), ax(1, "D"), ax(H, "H"), ax(W, "W"), ax(N, "N")]
+    ax_f = [ax_i[0], ax(1, "T"), ax(R, "R"), ax(S, "S"), ax(K, "K")]
+    ax_o = [ax_f[4], ax(1, "M"), ax(P, "P"), ax(Q, "Q"), ax_i[4]]
+    inputs = ng.placeholder(ax_i)
+    filters = ng.placeholder(ax_f)
+    delta = ng.placeholder(ax_o)
+    bprop_conv, update_conv = _conv_grad_ops(ng)
+    out = ng.convolution(_conv_params(pad, stride), inputs, filters, axes=ax_o)
+    gi = bprop_conv(delta, inputs, filters, out)
+    gf = update_conv(delta, inputs, filters, out)
+    r = _rng(12)
+    vals = [r.standard_normal((C, 1, H, W, N)).astype(np.float32),
+            (r.standard_normal((C, 1, R, S, K)) * 0.2).astype(np.float32),
+            (r.standard_normal((K, 1, P, Q, N)) * 0.5).astype(np.float32)]
+    return [out, gi, gf], [inputs, filters, delta], vals
+
+
+def conv_grads_stride2(ng):
+    return conv_grads(ng, C=8, K=16, H=9, W=11, N=32, R=3, S=3, pad=1, stride=2)
+
+
 def mlp_forward(ng):
     """Forward pass of BASELINE config 1: 784 -> 512 ReLU -> 512 ReLU -> 10 softmax, batch 128."""
     r = _rng(0)
@@ -316,6 +352,8 @@ CASES = {
     "conv_basic": conv_basic,
     "conv_stride2_1x1": conv_stride2_1x1,
     "conv_stride2_3x3": conv_stride2_3x3,
+    "conv_grads": conv_grads,
+    "conv_grads_stride2": conv_grads_stride2,
     "mlp_forward": mlp_forward,
     "resnet20": resnet20,
     "resnet8_small": resnet8_small,

@@ -79,6 +79,18 @@ class Interp(object):
             out = co.conv_fprop(i[:, 0], f[:, 0], (cp["pad_h"], cp["pad_w"]),
                                 (cp["str_h"], cp["str_w"]))
             return out[:, None].reshape(op.axes.lengths)
+        if isinstance(op, g.bprop_conv):
+            e, f = [self.eval(a) for a in op.args]
+            cp = op.conv_params
+            out = co.conv_bprop(e[:, 0], f[:, 0], op.axes.lengths[2:4], (cp["pad_h"], cp["pad_w"]),
+                                (cp["str_h"], cp["str_w"]))
+            return out[:, None].reshape(op.axes.lengths)
+        if isinstance(op, g.update_conv):
+            e, i = [self.eval(a) for a in op.args]
+            cp = op.conv_params
+            out = co.conv_update(i[:, 0], e[:, 0], op.axes.lengths[2:4], (cp["pad_h"], cp["pad_w"]),
+                                 (cp["str_h"], cp["str_w"]))
+            return out[:, None].reshape(op.axes.lengths)
         if isinstance(op, g.PoolingOp):
             i = self.eval(op.args[0])
             pp = op.pool_params

@@ -127,3 +127,103 @@ def test_pool_avg(flex):
         assert np.abs(out.cpu().numpy().astype(np.float64) - exp).max() <= 0.5 + 1e-3
     else:
         np.testing.assert_allclose(out.cpu().numpy(), exp, rtol=1e-5, atol=1e-5)
+
+
+# ---- the two training contractions ------------------------------------------------------------
+# shapes of ResNet-20's layers (scaled down in H, W, N) plus ragged ones; the update contraction of
+# the larger ones runs in several K slices
+GRAD_SHAPES = [(16, 7, 7, 32, 8, 3, 3, 0, 1), (16, 9, 11, 32, 8, 3, 3, 1, 1), (3, 16, 16, 32, 16, 3, 3, 1, 1),
+               (16, 16, 16, 64, 32, 3, 3, 1, 2), (32, 16, 16, 32, 64, 1, 1, 0, 2), (64, 8, 8, 32, 64, 3, 3, 1, 1),
+               (5, 6, 5, 24, 10, 2, 3, 1, 1), (16, 12, 12, 256, 32, 3, 3, 1, 2), (16, 32, 32, 64, 16, 3, 3, 1, 1),
+               (4, 9, 7, 10, 6, 3, 3, 1, 2)]
+
+
+def _run_grad(torch, lib, which, flex, first, second, out, d, table=None):
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    sizer = lib.conv_bprop_scratch_bytes if which == "bprop" else lib.conv_update_scratch_bytes
+    nb = sizer(bool(flex), d)
+    keep, sp = _scratch(torch, nb)
+    raw = lib.raw()
+    if not flex:
+        fn = raw.b2_conv_bprop_f32 if which == "bprop" else raw.b2_conv_update_f32
+        lib.check(fn(first.data_ptr(), second.data_ptr(), out.data_ptr(), C.byref(d), sp, nb,
+                     status.data_ptr(), 0))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        return None
+    fn = raw.b2_conv_bprop_flex16 if which == "bprop" else raw.b2_conv_update_flex16
+    stats = torch.zeros((3,), dtype=torch.int32, device="cuda")
+    probe = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    for pr in (1, 0):
+        lib.check(fn(first.data_ptr(), second.data_ptr(), out.data_ptr(), C.byref(d),
+                     table.data_ptr(), 0, 1, 2, stats.data_ptr(), sp, nb, probe.data_ptr(),
+                     status.data_ptr(), pr, 0))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+    return int(probe.item()), int(stats[2].item())
+
+
+@pytest.mark.parametrize("which", ["bprop", "update"])
+@pytest.mark.parametrize("shape", GRAD_SHAPES)
+def test_conv_grad_f32(shape, which):
+    import torch
+    from ngraph_python_b200 import lib
+    Cc, H, W, N, K, R, S, pad, stride = shape
+    d, P, Q = _dims(lib, *shape)
+    rng = np.random.RandomState(sum(shape) + 7)
+    I = rng.standard_normal((Cc, H, W, N)).astype(np.float32)
+    F = rng.standard_normal((Cc, R, S, K)).astype(np.float32)
+    E = rng.standard_normal((K, P, Q, N)).astype(np.float32)
+    dI, dF, dE = [torch.from_numpy(a).cuda() for a in (I, F, E)]
+    if which == "bprop":
+        out = torch.zeros((Cc, H, W, N), dtype=torch.float32, device="cuda")
+        _run_grad(torch, lib, which, 0, dE, dF, out, d)
+        exp = co.conv_bprop(E, F, (H, W), (pad, pad), (stride, stride), dtype=np.float64)
+        terms = K * R * S
+    else:
+        out = torch.zeros((Cc, R, S, K), dtype=torch.float32, device="cuda")
+        _run_grad(torch, lib, which, 0, dI, dE, out, d)
+        exp = co.conv_update(I, E, (R, S), (pad, pad), (stride, stride), dtype=np.float64)
+        terms = P * Q * N
+    np.testing.assert_allclose(out.cpu().numpy(), exp, rtol=1e-4, atol=1e-5 * np.sqrt(terms) * 4)
+
+
+@pytest.mark.parametrize("which", ["bprop", "update"])
+@pytest.mark.parametrize("small", [True, False])
+@pytest.mark.parametrize("shape", GRAD_SHAPES)
+def test_conv_grad_flex16_exact(shape, small, which):
+    import torch
+    from ngraph_python_b200 import lib
+    Cc, H, W, N, K, R, S, pad, stride = shape
+    d, P, Q = _dims(lib, *shape)
+    rng = np.random.RandomState(sum(shape) + 11)
+    lim = 4 if small else 32767
+    I = rng.randint(-lim, lim, (Cc, H, W, N)).astype(np.int16)
+    F = rng.randint(-lim, lim, (Cc, R, S, K)).astype(np.int16)
+    E = rng.randint(-lim, lim, (K, P, Q, N)).astype(np.int16)
+    if which == "bprop":
+        exact = co.conv_bprop(E, F, (H, W), (pad, pad), (stride, stride), dtype=np.int64)
+        shape_o = (Cc, H, W, N)
+    else:
+        exact = co.conv_update(I, E, (R, S), (pad, pad), (stride, stride), dtype=np.int64)
+        shape_o = (Cc, R, S, K)
+    amax = int(np.abs(exact).max())
+    sh = 0 if amax <= 32767 else int(np.ceil(np.log2(amax / 32767.0))) + 1
+    table = torch.tensor([[1.0, 1.0], [1.0, 1.0], [2.0 ** sh, 2.0 ** -sh]], dtype=torch.float32,
+                         device="cuda")
+    dI, dF, dE = [torch.from_numpy(a).cuda() for a in (I, F, E)]
+    out = torch.zeros(shape_o, dtype=torch.int16, device="cuda")
+    if which == "bprop":
+        probe, stat = _run_grad(torch, lib, which, 1, dE, dF, out, d, table)
+    else:
+        probe, stat = _run_grad(torch, lib, which, 1, dI, dE, out, d, table)
+    assert probe == amax
+    if sh > 0:
+        half = 1 << (sh - 1)
+        exp = (exact + half - 1 + ((exact >> sh) & 1)) >> sh
+    else:
+        exp = exact
+    exp = np.clip(exp, -32768, 32767)
+    got = out.cpu().numpy().astype(np.int64)
+    assert np.array_equal(got, exp)
+    assert stat == int(np.abs(got).max())

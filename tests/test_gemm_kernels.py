@@ -19,7 +19,9 @@ def _scratch(torch, nbytes):
 
 
 SHAPES = [(128, 128, 128), (256, 384, 512), (100, 72, 200), (1, 10, 64), (512, 128, 1024),
-          (130, 257, 96)]
+          (130, 257, 96),
+          # K above 32768: the flex16 contraction runs in slices of exact int32 sums
+          (64, 48, 40000)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
