@@ -106,13 +106,15 @@ class FlexEntry(object):
             self.pending_dec = None
         return self.dec
 
-    def initialize_from_range(self, maxabs_real):
-        """First write: exponent from the true range of the values about to be stored."""
-        if not self.fixed_point:
-            d = largest_dec_holding(maxabs_real)
-            if d is not None:
-                self.dec = d
-        self.initialized = True
+    def initialize_from_range(self, maxabs_real, from_host=False):
+        """First write: exponent from the true range of the values about to be stored.  An
+        all-zero HOST write (the initial value of a freshly created optimizer state) says nothing
+        about the range: the default exponent is kept and the first write by a kernel measures
+        again."""
+        d = None if self.fixed_point else largest_dec_holding(maxabs_real)
+        if d is not None:
+            self.dec = d
+        self.initialized = self.fixed_point or d is not None or not from_host
         return self.dec
 
     def end_write(self, maxabs_mantissa):

@@ -86,8 +86,16 @@ class View(object):
                                        if s != 0 and a.length != 1), self.offset)
 
     def is_dense(self):
-        d = View.dense(self.buffer)
-        return self.offset == 0 and self.axes == d.axes and self.strides == d.strides
+        """The view walks the whole buffer in memory order (axes may have been renamed by a cast;
+        the stride of an axis of length 1 is immaterial)."""
+        if self.offset != 0:
+            return False
+        expect = 1
+        for a, s in reversed(list(zip(self.axes, self.strides))):
+            if a.length != 1 and s != expect:
+                return False
+            expect *= a.length
+        return expect == self.buffer.size
 
 
 # ---------------------------------------------------------------------------------------------
@@ -453,6 +461,9 @@ class _Planner(object):
             sbuf.last_write_step = index
             requant = ElementWiseOp("assign", (staging,))
             t._alias[op] = requant
+            # whoever consumes the allreduce consumes the re-quantised tensor: without this a
+            # consumer in a later kernel would find nothing stored
+            self.consumers[requant] = list(self.consumers.get(op, ()))
         step.reduce_func = op.reduce_func
         self.steps.append(step)
         self.producer[op] = index
@@ -611,6 +622,14 @@ class _Planner(object):
                     d["reg"] = reg[base]
                 else:
                     d["reg"] = input_index(t._view_of(self._resolve(src)))
+                if mode == lib.REDUCE_NONE:
+                    # every reduced axis has length 1: the reduction is a copy
+                    if m.redop in ("argmax", "argmin"):
+                        raise ValueError("Unhandled op: {} over axes of length 1".format(m.redop))
+                    ops.append(("assign", d["reg"], None))
+                    d["reg"] = n_in + n_const + len(ops) - 1
+                    outs.append(d)
+                    continue
                 d["redop"] = m.redop
                 reds.append(d)
             else:
@@ -902,7 +921,7 @@ class B200Transformer(object):
             lib.check(raw.b2_absmax_bits_f32(buf.staging.data_ptr(), buf.size, bits.data_ptr(),
                                             self.stream.cuda_stream))
             maxabs = float(bits.cpu().numpy().view(np.float32)[0])
-            e.initialize_from_range(maxabs)
+            e.initialize_from_range(maxabs, from_host=True)
         else:
             e.begin_write()
         self._set_table_row(buf.slot, e.dec)
@@ -1038,10 +1057,14 @@ class B200Transformer(object):
             common.update(flex_table=self._table.data_ptr(), flex_stats=self._stats.data_ptr())
             fresh = [b for b in step.output_buffers() if not b.entry.initialized]
             if fresh:
-                # first write of these tensors: measure the unsaturated range, then pick exponents
+                # first write of these tensors: measure the unsaturated range, then pick exponents.
+                # The measuring launch leaves float bits in the statistic of EVERY output of the
+                # kernel, so the statistics of the outputs that are not new are put back after it.
+                saved = self._stats.clone()
                 step.kernel.launch(ins, outs, probe=True, **common)
                 self.kernel_launches += step.kernel.launches
                 self._stats_host.copy_(self._stats, non_blocking=False)
+                self._stats.copy_(saved)
                 bits = self._stats_host.numpy()
                 for b in fresh:
                     maxabs = float(bits[b.slot_write:b.slot_write + 1].view(np.float32)[0])

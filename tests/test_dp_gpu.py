@@ -24,9 +24,13 @@ def _check(results, fix, rtol=1e-4, atol=2e-5):
                                        err_msg="output %d call %d" % (k, rep))
 
 
-def test_train_step_single_gpu_fp32():
-    fix = np.load(os.path.join(FIX, "mlp_train_step.npz"))
-    outs, params, vals = cases.mlp_train_step(ng)
+TRAIN_CASES = ["mlp_train_step", "resnet_train_step"]
+
+
+@pytest.mark.parametrize("case", TRAIN_CASES)
+def test_train_step_single_gpu_fp32(case):
+    fix = np.load(os.path.join(FIX, case + ".npz"))
+    outs, params, vals = cases.CASES[case](ng)
     t = ng.transformers.allocate_transformer("b200", bucket_bytes=8192)
     comp = t.computation(outs, *params)
     results = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
@@ -35,18 +39,33 @@ def test_train_step_single_gpu_fp32():
     t.close()
 
 
-def test_train_step_single_gpu_flex16():
-    fix = np.load(os.path.join(FIX, "mlp_train_step.npz"))
-    outs, params, vals = cases.mlp_train_step(ng)
-    t = ng.transformers.allocate_transformer("b200", flex=True)
-    comp = t.computation(outs, *params)
-    results = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
-    # flex16 weights: 15-bit mantissas, so compare at the flex tolerance of each tensor
+def _check_flex(results, fix, case):
+    # flex16 weights: 15-bit mantissas, so compare at the flex tolerance of each tensor.  In the
+    # convolutional network a pre-activation that is quantised across zero flips its ReLU mask,
+    # which moves single gradient elements by far more than a mantissa step; there the bar is on
+    # the tensor as a whole (relative L2 error) with a loose bound per element.
     for rep, res in enumerate(results):
         for k, got in enumerate(res):
             exp = fix["out%d_%d" % (rep, k)]
+            msg = "output %d call %d" % (k, rep)
+            if case == "resnet_train_step":
+                err = np.linalg.norm((got - exp).ravel()) / max(np.linalg.norm(exp.ravel()), 1e-30)
+                assert err <= 5e-3, "%s: relative L2 error %g" % (msg, err)
+                np.testing.assert_allclose(got, exp, rtol=0.1, atol=0.05 * float(np.max(np.abs(exp))),
+                                           err_msg=msg)
+                continue
             scale = float(np.max(np.abs(exp))) * 2.0 ** -14
-            np.testing.assert_allclose(got, exp, rtol=2e-2, atol=16 * scale)
+            np.testing.assert_allclose(got, exp, rtol=2e-2, atol=16 * scale, err_msg=msg)
+
+
+@pytest.mark.parametrize("case", TRAIN_CASES)
+def test_train_step_single_gpu_flex16(case):
+    fix = np.load(os.path.join(FIX, case + ".npz"))
+    outs, params, vals = cases.CASES[case](ng)
+    t = ng.transformers.allocate_transformer("b200", flex=True)
+    comp = t.computation(outs, *params)
+    results = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
+    _check_flex(results, fix, case)
     t.close()
 
 
@@ -58,7 +77,7 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, world, port, flex, q):
+def _rank_main(rank, world, port, flex, case, q):
     import torch
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -68,7 +87,7 @@ def _rank_main(rank, world, port, flex, q):
                             device_id=torch.device("cuda", rank))
     try:
         from ngraph_python_b200.comm import TorchDistComm
-        outs, params, vals = cases.mlp_train_step(ng, shard=(rank, world))
+        outs, params, vals = cases.CASES[case](ng, shard=(rank, world))
         t = ng.transformers.allocate_transformer("b200", device_id=rank, flex=flex,
                                                  comm=TorchDistComm(), bucket_bytes=8192)
         comp = t.computation(outs, *params)
@@ -80,17 +99,18 @@ def _rank_main(rank, world, port, flex, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("case", TRAIN_CASES)
 @pytest.mark.parametrize("flex", [False, True])
-def test_train_step_two_gpus(flex):
+def test_train_step_two_gpus(flex, case):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    fix = np.load(os.path.join(FIX, "mlp_train_step.npz"))
+    fix = np.load(os.path.join(FIX, case + ".npz"))
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, flex, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, flex, case, q)) for r in range(2)]
     for p in procs:
         p.start()
     got = dict(q.get(timeout=300) for _ in range(2))
@@ -99,11 +119,7 @@ def test_train_step_two_gpus(flex):
         assert p.exitcode == 0
     for rank in (0, 1):
         if flex:
-            for rep, res in enumerate(got[rank]):
-                for k, g in enumerate(res):
-                    exp = fix["out%d_%d" % (rep, k)]
-                    scale = float(np.max(np.abs(exp))) * 2.0 ** -14
-                    np.testing.assert_allclose(g, exp, rtol=2e-2, atol=16 * scale)
+            _check_flex(got[rank], fix, case)
         else:
             _check(got[rank], fix)
     # replicas stay identical, bit for bit
