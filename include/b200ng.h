@@ -48,7 +48,10 @@ int b2_device_count(void);
 #define B2_EW_MAX_CONST 16
 #define B2_EW_MAX_OPS 96
 
-enum b2_dtype { B2_F32 = 0, B2_FLEX16 = 1 };
+/* B2_FLEX16_PLANES (elementwise results only): the int16 mantissa is stored as two byte planes,
+ * high bytes at the destination pointer and low bytes plane_bytes further -- the operand format
+ * of the convolution entry points that take planes, so no separate split pass is needed. */
+enum b2_dtype { B2_F32 = 0, B2_FLEX16 = 1, B2_FLEX16_PLANES = 2 };
 
 /* op codes: one per template of float_ew2.py:31-68 */
 enum b2_ew_opcode {
@@ -75,6 +78,7 @@ typedef struct b2_ew_tensor {
     int32_t dtype;       /* enum b2_dtype */
     int32_t flex_slot;   /* row of the flex table / stats array; -1 for fp32 */
     int64_t sa, sb, sc;  /* element strides along A, B, C; 0 broadcasts */
+    int64_t plane_bytes; /* B2_FLEX16_PLANES: byte offset of the low plane (multiple of 8) */
 } b2_ew_tensor;
 
 /* registers: 0..n_in-1 inputs, n_in..n_in+n_const-1 constants, then one per op in order */
@@ -212,6 +216,22 @@ int b2_conv_fprop_flex16(const int16_t* I, const int16_t* F, int16_t* O, const b
                          const b2_flex_scale* table, int32_t slotI, int32_t slotF, int32_t slotO,
                          int32_t* stats, void* scratch, size_t scratch_bytes, uint64_t* probe_out,
                          int32_t* status, int32_t probe, void* stream);
+/* The flex16 forward convolution in parts, for callers that keep operand planes around: the
+ * tile kernel reads the activations and the filters as two byte planes each (high and low bytes
+ * of the int16 mantissas; activations in C,H,W,N order with the low plane act_plane_bytes after
+ * the high plane, both 1024-byte aligned).  A fused elementwise kernel can emit activation planes
+ * directly (B2_FLEX16_PLANES) and the filter planes of constant weights can be built once, which
+ * leaves ONE launch per convolution.  `supported` is 0 where the plane path does not apply (batch
+ * not a multiple of 128, dilation, very large windows); use b2_conv_fprop_flex16 there.
+ * No counterpart in the reference, whose kernels read int16 tensors directly. */
+int b2_conv_planes_info(const b2_conv_dims* d, int32_t* supported, size_t* act_plane_bytes,
+                        size_t* filter_planes_bytes);
+int b2_conv_split_activations(const int16_t* I, const b2_conv_dims* d, void* planes, void* stream);
+int b2_conv_filter_planes(const int16_t* F, const b2_conv_dims* d, void* planes, void* stream);
+int b2_conv_fprop_flex16_planes(const void* act_planes, const void* filter_planes, int16_t* O,
+                                const b2_conv_dims* d, const b2_flex_scale* table, int32_t slotI,
+                                int32_t slotF, int32_t slotO, int32_t* stats, uint64_t* probe_out,
+                                int32_t* status, int32_t probe, void* stream);
 /* The two training contractions of a convolution whose forward pass has the dimensions `d`
  * (d always describes the FORWARD convolution: I is C,D,H,W,N, F is C,T,R,S,K, E is K,M,P,Q,N).
  * Replace ConvBpropKernel / ConvUpdateKernel (ngraph/transformers/gpu/conv.py:121-312) and

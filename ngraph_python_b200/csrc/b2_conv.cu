@@ -153,24 +153,32 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
 }
 
 // ================================================================================================
-// Implicit GEMM: no unrolled copy of the input.
+// Implicit GEMM (flex16): no unrolled copy of the input.
 //
 // For batches that are a multiple of 128 the tile kernel reads the activations straight from
-// their C,H,W,N layout.  A tile is one output pixel (p,q) x 128 images.  The reduction runs over
-// units of (filter tap, block of 32 channels); for every unit ONE 4-d TMA box
-// [32 channels][128 images] is fetched from the operand plane at (c0, h, w, n0) with
-// h = p*str - pad + r*dil (zero fill outside the image does the padding), and lands in shared
-// memory as an MN-major (images contiguous) swizzled operand.  The filter planes are K-major with
-// their columns in the same (tap, channel block, channel) order.  CTAs are persistent: each
-// walks many tiles, the producer warp runs ahead across tile boundaries, and the accumulators are
-// double-buffered in tensor memory so the epilogue of one tile overlaps the MMAs of the next.
+// their C,H,W,N layout.  A tile is one output pixel (p,q) x 128 images; its reduction runs over
+// chunks of `cu` input channels.  For every chunk ONE 4-d TMA box [cu channels][R][S][128 images]
+// per operand plane is fetched at (n0, q*str - pad, p*str - pad, c0): the whole filter window of
+// those channels in a single copy, zero fill outside the image doing the padding.  It lands in
+// shared memory as an MN-major (images contiguous) 128-byte-swizzled operand whose K rows are in
+// (channel, r, s) order -- the natural order of the C,R,S,K filter tensor -- padded to a multiple
+// of 32 rows (one MMA step); the rows of the padding multiply filter columns that are zero.
+// The filter planes of the CTA's output channels are K-major, loaded ONCE per CTA and stay
+// resident in shared memory.  CTAs are persistent: each walks many tiles, the producer warp runs
+// ahead across tile boundaries through a ring of stages, and the accumulators are double-buffered
+// in tensor memory so that the epilogue of one tile (eight warps) overlaps the MMAs of the next.
 // The only pre-pass is an elementwise split of the activations into the two operand planes.
 // ================================================================================================
 struct ConvTileParams {
-    int P, Q, N, K, S;
-    int pad_h, pad_w, str_h, str_w, dil_h, dil_w;
-    int cu;                       // channels per unit: 16 when C <= 16, else 32
-    int cchunks, units, stages_per_tile, num_tiles, nblk;
+    int P, Q, N, K;
+    int pad_h, pad_w, str_h, str_w;
+    int cu;                       // channels per chunk
+    int cchunks;                  // chunks per tile = stages per tile
+    int kc_pad;                   // K rows per chunk, padded to a multiple of 32
+    int box_bytes;                // bytes one activation box delivers (cu*R*S*128)
+    int npanels;                  // 128-byte K panels of the resident filter planes
+    int nstages;                  // ring depth
+    int num_tiles, nblk;
     long long ldc;
     void* O;
     const b2_flex_scale* table;
@@ -201,35 +209,46 @@ __device__ __forceinline__ unsigned long long make_smem_desc_mn(const void* p, u
     d |= (unsigned long long)2 << 61;
     return d;
 }
-
-// deeper rings for the narrow tiles: the kernel is latency-bound, not capacity-bound
-__host__ __device__ constexpr int conv_stages(int bn) { return bn <= 32 ? 5 : bn <= 64 ? 4 : 3; }
-__host__ __device__ constexpr int conv_smem_bytes(int bn) {
-    return conv_stages(bn) * stage_bytes(bn) + 1024 + 256;
+// 8 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld8(unsigned taddr, unsigned* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7])
+        : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
 }
 
-template <int MODE, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+constexpr int kConvMaxStages = 8;
+constexpr int kConvThreads = 320;           // producer, MMA, eight epilogue warps
+constexpr int kConvSmemMax = 232448;        // 227 KB: the most one CTA can have
+constexpr int kConvSmemFixed = 1024 /*alignment*/ + 512 /*barriers*/;
+
+template <int BN>
+__global__ void __launch_bounds__(kConvThreads, 1)
 conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                      const __grid_constant__ CUtensorMap mapI1,
                      const __grid_constant__ CUtensorMap mapB0,
                      const __grid_constant__ CUtensorMap mapB1, const ConvTileParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    constexpr int kCS = conv_stages(BN);
-    constexpr int kStageBytes = stage_bytes(BN);
-    constexpr int kBPlane = BN * kKBytes;
-    constexpr int kAcc = (MODE == MODE_FLEX16 ? 3 : 1) * BN;       // columns per accumulator set
+    constexpr int kPanelBytes = BN * kKBytes;
+    constexpr int kAcc = 3 * BN;                               // columns per accumulator set
     constexpr int kNBuf = (2 * kAcc <= 512) ? 2 : 1;
-    constexpr int kCols = tmem_cols(MODE, BN) * kNBuf > 512 ? 512 : tmem_cols(MODE, BN) * kNBuf;
-    unsigned long long* full_bar = (unsigned long long*)(smem + kCS * kStageBytes);
-    unsigned long long* empty_bar = full_bar + kCS;
-    unsigned long long* tmem_full = empty_bar + kCS;      // [2]
-    unsigned long long* tmem_empty = tmem_full + 2;           // [2]
-    unsigned* tmem_holder = (unsigned*)(tmem_empty + 2);
+    constexpr int kCols = tmem_cols(MODE_FLEX16, BN) * kNBuf > 512 ? 512
+                                                                   : tmem_cols(MODE_FLEX16, BN) * kNBuf;
+    const int act_stage = p.kc_pad * 128;                      // bytes per plane per stage
+    unsigned char* filt = smem;                                // [2 planes][npanels][BN][128]
+    unsigned char* ring = smem + 2 * p.npanels * kPanelBytes;  // [nstages][2 planes][act_stage]
+    unsigned long long* full_bar =
+        (unsigned long long*)(ring + (size_t)p.nstages * 2 * act_stage);
+    unsigned long long* empty_bar = full_bar + kConvMaxStages;
+    unsigned long long* tmem_full = empty_bar + kConvMaxStages;   // [2]
+    unsigned long long* tmem_empty = tmem_full + 2;               // [2]
+    unsigned long long* filt_bar = tmem_empty + 2;
+    unsigned* tmem_holder = (unsigned*)(filt_bar + 1);
     int* fail_flag = (int*)(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -237,8 +256,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
 
     if (threadIdx.x == 0) {
         prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapB0); prefetch_map(&mapB1);
-        for (int s = 0; s < kCS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+        for (int s = 0; s < kConvMaxStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 8); }
+        mbar_init(filt_bar, 1);
         *fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -250,6 +270,12 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
 
     if (warp == 0) {
         if (lane == 0) {
+            // the filter planes of this CTA's output channels: once, resident
+            mbar_expect_tx(filt_bar, 2 * p.npanels * kPanelBytes);
+            for (int j = 0; j < p.npanels; ++j) {
+                tma_load_2d(filt + j * kPanelBytes, &mapB0, j * kKBytes, ncol0, filt_bar);
+                tma_load_2d(filt + (p.npanels + j) * kPanelBytes, &mapB1, j * kKBytes, ncol0, filt_bar);
+            }
             int g = 0;
             bool ok = true;
             const long long t_start = clock64();
@@ -259,49 +285,17 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 const int pp = pq / p.Q, q = pq - pp * p.Q;
                 const int n0 = nb * 128;
                 const int h0 = pp * p.str_h - p.pad_h, w0 = q * p.str_w - p.pad_w;
-                for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
-                    const int s = g % kCS;
+                for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
+                    const int s = g % p.nstages;
                     const long long tw = clock64();
-                    if (g >= kCS && !mbar_wait(&empty_bar[s], ((g / kCS) - 1) & 1)) {
+                    if (g >= p.nstages && !mbar_wait(&empty_bar[s], ((g / p.nstages) - 1) & 1)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
                     t_wait += clock64() - tw;
-                    unsigned char* sa = smem + s * kStageBytes;
-                    if (MODE == MODE_FLEX16) {
-                        // units of `cu` channels; a 32-row MMA step takes 32/cu of them; the last
-                        // stage of a tile may be short
-                        const int ups = 128 / p.cu, per_step = 32 / p.cu;
-                        int nu = p.units - st * ups;
-                        if (nu > ups) nu = ups;
-                        const int loaded = ((nu + per_step - 1) / per_step) * per_step;
-                        const int ubytes = p.cu * 128;
-                        mbar_expect_tx(&full_bar[s], 2 * loaded * ubytes + 2 * kBPlane);
-                        for (int j = 0; j < loaded; ++j) {
-                            int u = st * ups + j;
-                            if (u >= p.units) u = 0;   // filler: its filter columns are zero
-                            const int tap = u / p.cchunks, cc = u - tap * p.cchunks;
-                            const int fr = tap / p.S, fs = tap - fr * p.S;
-                            const int h = h0 + fr * p.dil_h, w = w0 + fs * p.dil_w;
-                            tma_load_4d(sa + j * ubytes, &mapI0, n0, w, h, cc * p.cu, &full_bar[s]);
-                            tma_load_4d(sa + kPlaneBytes + j * ubytes, &mapI1, n0, w, h, cc * p.cu,
-                                        &full_bar[s]);
-                        }
-                    } else {
-                        mbar_expect_tx(&full_bar[s], kStageBytes);
-                        const int u = st;
-                        const int tap = u / p.cchunks, cc = u - tap * p.cchunks;
-                        const int fr = tap / p.S, fs = tap - fr * p.S;
-                        const int h = h0 + fr * p.dil_h, w = w0 + fs * p.dil_w;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            tma_load_4d(sa + j * 4096, &mapI0, n0 + j * 32, w, h, cc * 32, &full_bar[s]);
-                            tma_load_4d(sa + kPlaneBytes + j * 4096, &mapI1, n0 + j * 32, w, h,
-                                        cc * 32, &full_bar[s]);
-                        }
-                    }
-                    const int kx = st * (MODE == MODE_FLEX16 ? kKBytes : kKBytes / 4);
-                    tma_load_2d(sa + 2 * kPlaneBytes, &mapB0, kx, ncol0, &full_bar[s]);
-                    tma_load_2d(sa + 2 * kPlaneBytes + kBPlane, &mapB1, kx, ncol0, &full_bar[s]);
+                    unsigned char* sa = ring + (size_t)s * 2 * act_stage;
+                    mbar_expect_tx(&full_bar[s], 2 * p.box_bytes);
+                    tma_load_4d(sa, &mapI0, n0, w0, h0, cc * p.cu, &full_bar[s]);
+                    tma_load_4d(sa + act_stage, &mapI1, n0, w0, h0, cc * p.cu, &full_bar[s]);
                 }
             }
             if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) {
@@ -314,9 +308,10 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const unsigned mn = 1u << 15;
             const unsigned id_ss = make_idesc(2, 1, 1, BN) | mn, id_su = make_idesc(2, 1, 0, BN) | mn,
                            id_us = make_idesc(2, 0, 1, BN) | mn, id_uu = make_idesc(2, 0, 0, BN) | mn;
-            const unsigned id_tf = make_idesc(1, 2, 2, BN) | mn;
             int g = 0, ti = 0;
-            bool ok = true;
+            bool ok = mbar_wait(filt_bar, 0);
+            if (!ok) atomicExch(fail_flag, 1);
+            const int ksteps = p.kc_pad >> 5;
             const long long t_start = clock64();
             long long t_wait_e = 0, t_wait_f = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
@@ -328,44 +323,30 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 }
                 t_wait_e += clock64() - tw;
                 tc_fence_after();
-                for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
-                    const int s = g % kCS;
+                for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
+                    const int s = g % p.nstages;
                     const long long tw2 = clock64();
-                    if (!mbar_wait(&full_bar[s], (g / kCS) & 1)) {
+                    if (!mbar_wait(&full_bar[s], (g / p.nstages) & 1)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
                     t_wait_f += clock64() - tw2;
                     tc_fence_after();
-                    unsigned char* sa = smem + s * kStageBytes;
-                    int ksteps = 4;
-                    if (MODE == MODE_FLEX16) {
-                        const int ups = 128 / p.cu;
-                        int nu = p.units - st * ups;
-                        if (nu > ups) nu = ups;
-                        ksteps = (nu * p.cu + 31) / 32;
-                    }
+                    unsigned char* sa = ring + (size_t)s * 2 * act_stage;
                     for (int k = 0; k < ksteps; ++k) {
-                        const unsigned acc = (st > 0 || k > 0) ? 1u : 0u;
-                        const unsigned long long badv = (unsigned long long)((k * 32) >> 4);
-                        const unsigned long long dB0 = make_smem_desc(sa + 2 * kPlaneBytes) + badv;
+                        const unsigned acc = (cc > 0 || k > 0) ? 1u : 0u;
+                        const int koff = cc * p.kc_pad + 32 * k;          // byte column of the filter planes
+                        const int panel = koff >> 7;
+                        const unsigned long long badv = (unsigned long long)((koff & 127) >> 4);
+                        const unsigned long long dB0 = make_smem_desc(filt + panel * kPanelBytes) + badv;
                         const unsigned long long dB1 =
-                            make_smem_desc(sa + 2 * kPlaneBytes + kBPlane) + badv;
-                        if (MODE == MODE_FLEX16) {
-                            const unsigned long long dA0 = make_smem_desc_mn(sa + k * 4096, 0, 1024);
-                            const unsigned long long dA1 =
-                                make_smem_desc_mn(sa + kPlaneBytes + k * 4096, 0, 1024);
-                            tc_mma<MODE>(acc_base + 0, dA0, dB0, id_ss, acc);
-                            tc_mma<MODE>(acc_base + BN, dA0, dB1, id_su, acc);
-                            tc_mma<MODE>(acc_base + BN, dA1, dB0, id_us, 1u);
-                            tc_mma<MODE>(acc_base + 2 * BN, dA1, dB1, id_uu, acc);
-                        } else {
-                            const unsigned long long dA0 = make_smem_desc_mn(sa + k * 1024, 4096, 1024);
-                            const unsigned long long dA1 =
-                                make_smem_desc_mn(sa + kPlaneBytes + k * 1024, 4096, 1024);
-                            tc_mma<MODE>(acc_base, dA0, dB0, id_tf, acc);
-                            tc_mma<MODE>(acc_base, dA0, dB1, id_tf, 1u);
-                            tc_mma<MODE>(acc_base, dA1, dB0, id_tf, 1u);
-                        }
+                            make_smem_desc(filt + (p.npanels + panel) * kPanelBytes) + badv;
+                        const unsigned long long dA0 = make_smem_desc_mn(sa + k * 4096, 0, 1024);
+                        const unsigned long long dA1 =
+                            make_smem_desc_mn(sa + act_stage + k * 4096, 0, 1024);
+                        tc_mma<MODE_FLEX16>(acc_base + 0, dA0, dB0, id_ss, acc);
+                        tc_mma<MODE_FLEX16>(acc_base + BN, dA0, dB1, id_su, acc);
+                        tc_mma<MODE_FLEX16>(acc_base + BN, dA1, dB0, id_us, 1u);
+                        tc_mma<MODE_FLEX16>(acc_base + 2 * BN, dA1, dB1, id_uu, acc);
                     }
                     tc_commit(&empty_bar[s]);
                 }
@@ -376,15 +357,16 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             }
         }
     } else {
+        // epilogue warps 2..9: TMEM lane quarter = warp % 4; the two warps of a quarter split the
+        // output channels of the tile
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        constexpr int CW = BN >= 32 ? 16 : 8;                  // columns per tensor-memory load
         int stat = 0;
         unsigned long long pmax = 0;
-        int sh = 0;
-        if (MODE == MODE_FLEX16) {
-            const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
-                            (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
-            sh = -ilogbf(f);
-        }
+        const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
+                        (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
+        const int sh = -ilogbf(f);
         int ti = 0;
         bool ok = true;
         const long long t_start = clock64();
@@ -397,39 +379,32 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             tc_fence_after();
             const long long row = (long long)tile * 128 + quarter * 32 + lane;   // (pq*N + n)
             const unsigned lane_addr = tmem_base + buf * kAcc + ((unsigned)(quarter * 32) << 16);
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (MODE == MODE_FLEX16) {
-                    unsigned hh[16], xx[16], ll[16];
+            for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += CW) {
+                unsigned hh[CW], xx[CW], ll[CW];
+                if (CW == 16) {
                     tmem_ld16(lane_addr + c0, hh);
                     tmem_ld16(lane_addr + BN + c0, xx);
                     tmem_ld16(lane_addr + 2 * BN + c0, ll);
-                    tmem_ld_wait();
-                    if (!ok) continue;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int col = ncol0 + c0 + j;
-                        const long long v = ((long long)(int)hh[j] << 16) +
-                                            ((long long)(int)xx[j] << 8) + (long long)(int)ll[j];
-                        if (p.probe) {
-                            const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
-                            if (col < p.K) pmax = a > pmax ? a : pmax;
-                        } else if (col < p.K) {
-                            const int qv = rescale_i64(v, sh);
-                            const int a = qv < 0 ? -qv : qv;
-                            stat = a > stat ? a : stat;
-                            ((short*)p.O)[(long long)col * p.ldc + row] = (short)qv;
-                        }
-                    }
                 } else {
-                    unsigned acc[16];
-                    tmem_ld16(lane_addr + c0, acc);
-                    tmem_ld_wait();
-                    if (!ok) continue;
+                    tmem_ld8(lane_addr + c0, hh);
+                    tmem_ld8(lane_addr + BN + c0, xx);
+                    tmem_ld8(lane_addr + 2 * BN + c0, ll);
+                }
+                tmem_ld_wait();
+                if (!ok) continue;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int col = ncol0 + c0 + j;
-                        if (col < p.K)
-                            ((float*)p.O)[(long long)col * p.ldc + row] = __uint_as_float(acc[j]);
+                for (int j = 0; j < CW; ++j) {
+                    const int col = ncol0 + c0 + j;
+                    const long long v = ((long long)(int)hh[j] << 16) +
+                                        ((long long)(int)xx[j] << 8) + (long long)(int)ll[j];
+                    if (p.probe) {
+                        const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
+                        if (col < p.K) pmax = a > pmax ? a : pmax;
+                    } else if (col < p.K) {
+                        const int qv = rescale_i64(v, sh);
+                        const int a = qv < 0 ? -qv : qv;
+                        stat = a > stat ? a : stat;
+                        ((short*)p.O)[(long long)col * p.ldc + row] = (short)qv;
                     }
                 }
             }
@@ -441,20 +416,18 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64) {
             p.dbg[5] = clock64() - t_start; p.dbg[6] = t_wait; p.dbg[7] = ti;
         }
-        if (MODE == MODE_FLEX16) {
-            if (p.probe) {
-                for (int o = 16; o > 0; o >>= 1) {
-                    const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
-                    pmax = t > pmax ? t : pmax;
-                }
-                if (lane == 0 && pmax) atomicMax(p.probe_out, pmax);
-            } else {
-                for (int o = 16; o > 0; o >>= 1) {
-                    const int t = __shfl_xor_sync(0xffffffffu, stat, o);
-                    stat = t > stat ? t : stat;
-                }
-                if (lane == 0 && stat) atomicMax(p.stats + p.slotC, stat);
+        if (p.probe) {
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
+                pmax = t > pmax ? t : pmax;
             }
+            if (lane == 0 && pmax) atomicMax(p.probe_out, pmax);
+        } else {
+            for (int o = 16; o > 0; o >>= 1) {
+                const int t = __shfl_xor_sync(0xffffffffu, stat, o);
+                stat = t > stat ? t : stat;
+            }
+            if (lane == 0 && stat) atomicMax(p.stats + p.slotC, stat);
         }
     }
     tc_fence_before();
@@ -510,134 +483,155 @@ split_same_layout_kernel(const T* __restrict__ src, long long n, void* __restric
     }
 }
 
-// filters C,R,S,K -> planes [k_out][columns] with columns ordered (tap, channel block, channel)
+// filters C,R,S,K -> planes [k_out][columns]; the columns of chunk cc start at cc*kc_pad and run
+// over (channel within the chunk, r, s), zero in the padding and for channels beyond C
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
-filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cu, int cchunks, int units,
+filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cu, int cchunks, int kc_pad,
                      int rows_p, int kp, void* __restrict__ plane0, void* __restrict__ plane1) {
     const long long total = (long long)rows_p * kp;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int row = (int)(i / kp), kc = (int)(i - (long long)row * kp);
-        const int u = kc / cu, cl = kc - u * cu;
-        const int tap = u / cchunks, cc = u - tap * cchunks;
-        const int c = cc * cu + cl;
+        const int cc = kc / kc_pad, within = kc - cc * kc_pad;
         T v = 0;
-        if (u < units && c < C && row < K) v = F[((long long)c * RS + tap) * K + row];
+        if (cc < cchunks && within < cu * RS && row < K) {
+            const int cl = within / RS, tap = within - cl * RS;
+            const int c = cc * cu + cl;
+            if (c < C) v = F[((long long)c * RS + tap) * K + row];
+        }
         if (MODE == MODE_FLEX16) {
             const int m = (int)v;
             const int lo = m & 0xff;
             ((signed char*)plane0)[i] = (signed char)((m - lo) >> 8);
             ((unsigned char*)plane1)[i] = (unsigned char)lo;
         } else {
-            const float a = (float)v;
-            unsigned hb;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(a));
-            const float hi = __uint_as_float(hb);
+            float hi, lo;
+            tf32_split((float)v, hi, lo);
             ((float*)plane0)[i] = hi;
-            ((float*)plane1)[i] = a - hi;
+            ((float*)plane1)[i] = lo;
         }
     }
 }
 
-int make_map_4d(CUtensorMap* map, void* base, const ConvGeom& g, int esize, int cu) {
+// int8 plane in C,H,W,N layout; box = [cu][R][S][128 images]
+int make_map_4d(CUtensorMap* map, void* base, const ConvGeom& g, int cu) {
     cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.C};
-    cuuint64_t strides[3] = {(cuuint64_t)g.N * esize, (cuuint64_t)g.W * g.N * esize,
-                             (cuuint64_t)g.H * g.W * g.N * esize};
-    cuuint32_t box[4] = {(cuuint32_t)(kKBytes / esize), 1, 1, (cuuint32_t)cu};
+    cuuint64_t strides[3] = {(cuuint64_t)g.N, (cuuint64_t)g.W * g.N, (cuuint64_t)g.H * g.W * g.N};
+    cuuint32_t box[4] = {(cuuint32_t)kKBytes, (cuuint32_t)g.S, (cuuint32_t)g.R, (cuuint32_t)cu};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = g_encode(map, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
-                          4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return b2::fail(B2_ERR_CUDA, "cuTensorMapEncodeTiled (4-d) failed (%d)", (int)r);
     return B2_OK;
 }
 
 struct ImplicitShape {
-    int esize, bn, cu, cchunks, units, stages, kp, np;
+    int bn, cu, cchunks, kc_pad, npanels, kp, np, nstages, smem;
     size_t act_plane, filt_plane, bytes;
 };
 
-ImplicitShape implicit_shape(int mode, const ConvGeom& g) {
+ImplicitShape implicit_shape(const ConvGeom& g) {
     ImplicitShape s;
-    s.esize = mode == MODE_FLEX16 ? 1 : 4;
     s.bn = pick_bn(g.K);
-    s.cu = (mode == MODE_FLEX16 && g.C <= 16) ? 16 : 32;
+    const int RS = g.R * g.S;
+    // 16 channels per chunk for real windows (a 3x3 chunk is 144 rows = 18 KB per plane); a 1x1
+    // filter takes up to 128 channels per chunk
+    s.cu = RS > 1 ? 16 : (g.C >= 128 ? 128 : round_up(g.C, 32));
     s.cchunks = (g.C + s.cu - 1) / s.cu;
-    s.units = g.R * g.S * s.cchunks;
-    const int ups = mode == MODE_FLEX16 ? 128 / s.cu : 1;
-    s.stages = (s.units + ups - 1) / ups;
-    s.kp = s.stages * (kKBytes / s.esize);
+    s.kc_pad = round_up(s.cu * RS, 32);
+    s.kp = round_up(s.cchunks * s.kc_pad, kKBytes);
+    s.npanels = s.kp / kKBytes;
     s.np = round_up(g.K, s.bn);
-    s.act_plane = (((size_t)g.C * g.H * g.W * g.N * s.esize) + 1023) / 1024 * 1024;
-    s.filt_plane = (size_t)s.np * s.kp * s.esize;
+    const int filt_smem = 2 * s.npanels * s.bn * kKBytes;
+    const int stage = 2 * s.kc_pad * 128;
+    int nst = (kConvSmemMax - kConvSmemFixed - filt_smem) / stage;
+    if (nst > kConvMaxStages) nst = kConvMaxStages;
+    s.nstages = nst;
+    s.smem = kConvSmemFixed + filt_smem + (nst > 0 ? nst : 0) * stage;
+    s.act_plane = (((size_t)g.C * g.H * g.W * g.N) + 1023) / 1024 * 1024;
+    s.filt_plane = (size_t)s.np * s.kp;
     s.bytes = 2 * s.act_plane + 2 * s.filt_plane;
     return s;
 }
 
 // flex16 only: an MN-major tf32 operand needs the 32-byte-atom variant of the 128-byte swizzle
 // (both in the tensor map and in the matrix descriptor); with the plain 128-byte swizzle the
-// tensor core reads zeros.  fp32 convolutions therefore stay on the gather + K-major path.
+// tensor core reads zeros.  fp32 convolutions therefore stay on the gather + K-major path, and so
+// do dilated filters and windows too large for two stages of shared memory.
 bool implicit_ok(int mode, const ConvGeom& g) {
-    return mode == MODE_FLEX16 && g.N % 128 == 0 &&
-           (long long)g.P * g.Q * (g.N / 128) < (1LL << 30);
+    if (mode != MODE_FLEX16 || g.N % 128 != 0 || g.dil_h != 1 || g.dil_w != 1) return false;
+    if (g.R > 256 || g.S > 256 || (long long)g.P * g.Q * (g.N / 128) >= (1LL << 30)) return false;
+    return implicit_shape(g).nstages >= 2;
 }
 
-template <int MODE, int BN>
+template <int BN>
 int launch_implicit(const CUtensorMap& mI0, const CUtensorMap& mI1, const CUtensorMap& mB0,
-                    const CUtensorMap& mB1, const ConvTileParams& p, int ntiles_n, cudaStream_t st) {
+                    const CUtensorMap& mB1, const ConvTileParams& p, int ntiles_n, int smem,
+                    cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        B2_CUDA(cudaFuncSetAttribute(conv_implicit_kernel<MODE, BN>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     conv_smem_bytes(BN)));
+        B2_CUDA(cudaFuncSetAttribute(conv_implicit_kernel<BN>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmemMax));
         attr_set = true;
     }
     int ctas = p.num_tiles < 148 ? p.num_tiles : 148;
     dim3 grid(ctas, ntiles_n);
-    conv_implicit_kernel<MODE, BN><<<grid, kThreads, conv_smem_bytes(BN), st>>>(mI0, mI1, mB0, mB1, p);
+    conv_implicit_kernel<BN><<<grid, kConvThreads, smem, st>>>(mI0, mI1, mB0, mB1, p);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+// The three parts of an implicit-GEMM forward convolution: the two operand pre-passes (which a
+// caller can skip when it already holds the planes) and the tile kernel.
+template <typename T, int MODE>
+int implicit_split_activations(const T* I, const ConvGeom& g, const ImplicitShape& s, void* planes,
+                               cudaStream_t st) {
+    const long long n_act = (long long)g.C * g.H * g.W * g.N;
+    long long blocks = (n_act / 8 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    split_same_layout_kernel<T, MODE><<<(unsigned)blocks, 256, 0, st>>>(
+        I, n_act, planes, (unsigned char*)planes + s.act_plane);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }
 
 template <typename T, int MODE>
-int run_fprop_implicit(const T* I, const T* F, void* O, const ConvGeom& g,
-                       const b2_flex_scale* table, int slotI, int slotF, int slotO, int* stats,
-                       void* scratch, size_t scratch_bytes, unsigned long long* probe_out,
-                       int* status, int probe, cudaStream_t st) {
+int implicit_filter_planes(const T* F, const ConvGeom& g, const ImplicitShape& s, void* planes,
+                           cudaStream_t st) {
+    const long long n_f = (long long)s.np * s.kp;
+    long long fb = (n_f + 255) / 256;
+    if (fb > 148 * 8) fb = 148 * 8;
+    filter_planes_kernel<T, MODE><<<(unsigned)fb, 256, 0, st>>>(
+        F, g.C, g.R * g.S, g.K, s.cu, s.cchunks, s.kc_pad, s.np, s.kp, planes,
+        (unsigned char*)planes + s.filt_plane);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int implicit_tiles(const void* act_planes, const void* filt_planes, void* O, const ConvGeom& g,
+                   const ImplicitShape& s, const b2_flex_scale* table, int slotI, int slotF,
+                   int slotO, int* stats, unsigned long long* probe_out, int* status, int probe,
+                   cudaStream_t st) {
     int rc = get_encode();
     if (rc) return rc;
-    const ImplicitShape s = implicit_shape(MODE, g);
-    B2_REQUIRE(scratch && scratch_bytes >= s.bytes && ((uintptr_t)scratch & 1023) == 0,
-               "convolution needs %zu bytes of 1024-byte aligned scratch, got %zu", s.bytes,
-               scratch_bytes);
-    unsigned char* base = (unsigned char*)scratch;
-    void* A0 = base; void* A1 = base + s.act_plane;
-    void* B0 = base + 2 * s.act_plane; void* B1 = base + 2 * s.act_plane + s.filt_plane;
-    const long long n_act = (long long)g.C * g.H * g.W * g.N;
-    {
-        long long blocks = (n_act + 255) / 256;
-        if (blocks > 148 * 16) blocks = 148 * 16;
-        split_same_layout_kernel<T, MODE><<<(unsigned)blocks, 256, 0, st>>>(I, n_act, A0, A1);
-        const long long n_f = (long long)s.np * s.kp;
-        long long fb = (n_f + 255) / 256;
-        if (fb > 148 * 8) fb = 148 * 8;
-        filter_planes_kernel<T, MODE><<<(unsigned)fb, 256, 0, st>>>(F, g.C, g.R * g.S, g.K, s.cu,
-                                                                   s.cchunks, s.units, s.np, s.kp,
-                                                                   B0, B1);
-        B2_CUDA(cudaGetLastError());
-    }
+    B2_REQUIRE((((uintptr_t)act_planes | (uintptr_t)filt_planes) & 1023) == 0,
+               "operand planes must be 1024-byte aligned");
+    void* A0 = (void*)act_planes; void* A1 = (unsigned char*)act_planes + s.act_plane;
+    void* B0 = (void*)filt_planes; void* B1 = (unsigned char*)filt_planes + s.filt_plane;
     CUtensorMap mI0, mI1, mB0, mB1;
-    if ((rc = make_map_4d(&mI0, A0, g, s.esize, s.cu))) return rc;
-    if ((rc = make_map_4d(&mI1, A1, g, s.esize, s.cu))) return rc;
-    if ((rc = make_map(&mB0, B0, s.np, s.kp, s.esize, s.bn))) return rc;
-    if ((rc = make_map(&mB1, B1, s.np, s.kp, s.esize, s.bn))) return rc;
+    if ((rc = make_map_4d(&mI0, A0, g, s.cu))) return rc;
+    if ((rc = make_map_4d(&mI1, A1, g, s.cu))) return rc;
+    if ((rc = make_map(&mB0, B0, s.np, s.kp, 1, s.bn))) return rc;
+    if ((rc = make_map(&mB1, B1, s.np, s.kp, 1, s.bn))) return rc;
     ConvTileParams p;
-    p.P = g.P; p.Q = g.Q; p.N = g.N; p.K = g.K; p.S = g.S;
+    p.P = g.P; p.Q = g.Q; p.N = g.N; p.K = g.K;
     p.pad_h = g.pad_h; p.pad_w = g.pad_w; p.str_h = g.str_h; p.str_w = g.str_w;
-    p.dil_h = g.dil_h; p.dil_w = g.dil_w;
-    p.cu = s.cu; p.cchunks = s.cchunks; p.units = s.units; p.stages_per_tile = s.stages;
+    p.cu = s.cu; p.cchunks = s.cchunks; p.kc_pad = s.kc_pad;
+    p.box_bytes = s.cu * g.R * g.S * 128;
+    p.npanels = s.npanels; p.nstages = s.nstages;
     p.nblk = g.N / 128;
     p.num_tiles = g.P * g.Q * p.nblk;
     p.ldc = (long long)g.P * g.Q * g.N;
@@ -650,11 +644,28 @@ int run_fprop_implicit(const T* I, const T* F, void* O, const ConvGeom& g,
     }
     const int ntn = s.np / s.bn;
     switch (s.bn) {
-        case 16: return launch_implicit<MODE, 16>(mI0, mI1, mB0, mB1, p, ntn, st);
-        case 32: return launch_implicit<MODE, 32>(mI0, mI1, mB0, mB1, p, ntn, st);
-        case 64: return launch_implicit<MODE, 64>(mI0, mI1, mB0, mB1, p, ntn, st);
-        default: return launch_implicit<MODE, 128>(mI0, mI1, mB0, mB1, p, ntn, st);
+        case 16: return launch_implicit<16>(mI0, mI1, mB0, mB1, p, ntn, s.smem, st);
+        case 32: return launch_implicit<32>(mI0, mI1, mB0, mB1, p, ntn, s.smem, st);
+        case 64: return launch_implicit<64>(mI0, mI1, mB0, mB1, p, ntn, s.smem, st);
+        default: return launch_implicit<128>(mI0, mI1, mB0, mB1, p, ntn, s.smem, st);
     }
+}
+
+template <typename T, int MODE>
+int run_fprop_implicit(const T* I, const T* F, void* O, const ConvGeom& g,
+                       const b2_flex_scale* table, int slotI, int slotF, int slotO, int* stats,
+                       void* scratch, size_t scratch_bytes, unsigned long long* probe_out,
+                       int* status, int probe, cudaStream_t st) {
+    const ImplicitShape s = implicit_shape(g);
+    B2_REQUIRE(scratch && scratch_bytes >= s.bytes && ((uintptr_t)scratch & 1023) == 0,
+               "convolution needs %zu bytes of 1024-byte aligned scratch, got %zu", s.bytes,
+               scratch_bytes);
+    unsigned char* base = (unsigned char*)scratch;
+    int rc = implicit_split_activations<T, MODE>(I, g, s, base, st);
+    if (rc) return rc;
+    if ((rc = implicit_filter_planes<T, MODE>(F, g, s, base + 2 * s.act_plane, st))) return rc;
+    return implicit_tiles(base, base + 2 * s.act_plane, O, g, s, table, slotI, slotF, slotO, stats,
+                          probe_out, status, probe, st);
 }
 
 template <typename T, int MODE>
@@ -934,7 +945,7 @@ extern "C" int b2_conv_fprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, 
     const int mode = flex ? MODE_FLEX16 : MODE_F32X3;
     size_t need = shapes_for(mode, g.P * g.Q * g.N, g.K, g.C * g.R * g.S).bytes;
     if (implicit_ok(mode, g)) {
-        const size_t alt = implicit_shape(mode, g).bytes;
+        const size_t alt = implicit_shape(g).bytes;
         if (alt > need || !getenv("B2_CONV_IM2COL")) need = alt > need ? alt : need;
     }
     *bytes = need;
@@ -958,6 +969,60 @@ extern "C" int b2_conv_fprop_flex16(const int16_t* I, const int16_t* F, int16_t*
     return run_fprop<short, MODE_FLEX16>(I, F, O, d, table, slotI, slotF, slotO, stats, scratch,
                                          scratch_bytes, (unsigned long long*)probe_out, status,
                                          probe ? 1 : 0, (cudaStream_t)stream);
+}
+
+extern "C" int b2_conv_planes_info(const b2_conv_dims* d, int32_t* supported,
+                                   size_t* act_plane_bytes, size_t* filter_planes_bytes) {
+    ConvGeom g;
+    int rc = geom_from(d, &g);
+    if (rc) return rc;
+    B2_REQUIRE(supported && act_plane_bytes && filter_planes_bytes, "null argument");
+    *supported = implicit_ok(MODE_FLEX16, g) ? 1 : 0;
+    *act_plane_bytes = 0;
+    *filter_planes_bytes = 0;
+    if (*supported) {
+        const ImplicitShape s = implicit_shape(g);
+        *act_plane_bytes = s.act_plane;
+        *filter_planes_bytes = 2 * s.filt_plane;
+    }
+    return B2_OK;
+}
+
+extern "C" int b2_conv_split_activations(const int16_t* I, const b2_conv_dims* d, void* planes,
+                                         void* stream) {
+    ConvGeom g;
+    int rc = geom_from(d, &g);
+    if (rc) return rc;
+    B2_REQUIRE(I && planes && implicit_ok(MODE_FLEX16, g), "planes are not available for this convolution");
+    return implicit_split_activations<short, MODE_FLEX16>(I, g, implicit_shape(g), planes,
+                                                          (cudaStream_t)stream);
+}
+
+extern "C" int b2_conv_filter_planes(const int16_t* F, const b2_conv_dims* d, void* planes,
+                                     void* stream) {
+    ConvGeom g;
+    int rc = geom_from(d, &g);
+    if (rc) return rc;
+    B2_REQUIRE(F && planes && implicit_ok(MODE_FLEX16, g), "planes are not available for this convolution");
+    return implicit_filter_planes<short, MODE_FLEX16>(F, g, implicit_shape(g), planes,
+                                                      (cudaStream_t)stream);
+}
+
+extern "C" int b2_conv_fprop_flex16_planes(const void* act_planes, const void* filter_planes,
+                                           int16_t* O, const b2_conv_dims* d,
+                                           const b2_flex_scale* table, int32_t slotI, int32_t slotF,
+                                           int32_t slotO, int32_t* stats, uint64_t* probe_out,
+                                           int32_t* status, int32_t probe, void* stream) {
+    ConvGeom g;
+    int rc = geom_from(d, &g);
+    if (rc) return rc;
+    B2_REQUIRE(act_planes && filter_planes && O && implicit_ok(MODE_FLEX16, g),
+               "planes are not available for this convolution");
+    B2_REQUIRE(table && slotI >= 0 && slotF >= 0 && slotO >= 0, "flex conv needs the scale table");
+    B2_REQUIRE(probe ? probe_out != nullptr : stats != nullptr, "missing statistics destination");
+    return implicit_tiles(act_planes, filter_planes, O, g, implicit_shape(g), table, slotI, slotF,
+                          slotO, stats, (unsigned long long*)probe_out, status, probe ? 1 : 0,
+                          (cudaStream_t)stream);
 }
 
 extern "C" int b2_conv_bprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, size_t* bytes) {

@@ -37,6 +37,7 @@ struct EwArgs {
     void* out[B2_EW_MAX_OUT];
     long long out_sa[B2_EW_MAX_OUT], out_sb[B2_EW_MAX_OUT], out_sc[B2_EW_MAX_OUT];
     int out_slot[B2_EW_MAX_OUT];
+    long long out_plane[B2_EW_MAX_OUT];
     float consts[B2_EW_MAX_CONST];
     const b2_flex_scale* flex_table;
     int* flex_stats;
@@ -212,12 +213,16 @@ int emit_op(std::ostringstream& o, const b2_ew_op& op, int dst, bool fast) {
     return 0;
 }
 
-const char* ctype(int dtype) { return dtype == B2_FLEX16 ? "short" : "float"; }
+const char* ctype(int dtype) {
+    return dtype == B2_FLEX16 ? "short" : dtype == B2_FLEX16_PLANES ? "unsigned char" : "float";
+}
+// results may be flex16 stored as int16 or as the two byte planes the convolution kernels read
+inline bool is_flex(int dtype) { return dtype == B2_FLEX16 || dtype == B2_FLEX16_PLANES; }
 
 // Emits the per-element body: registers for inputs/constants, the op list.
 bool uses_flex(const b2_ew_program& p) {
     for (int i = 0; i < p.n_in; ++i) if (p.in[i].dtype == B2_FLEX16) return true;
-    for (int k = 0; k < p.n_out + p.n_red; ++k) if (p.out[k].t.dtype == B2_FLEX16) return true;
+    for (int k = 0; k < p.n_out + p.n_red; ++k) if (is_flex(p.out[k].t.dtype)) return true;
     return false;
 }
 
@@ -282,7 +287,8 @@ void emit_loads(std::ostringstream& o, const b2_ew_program& p, const Plan& pl,
 void emit_store(std::ostringstream& o, const b2_ew_program& p, const Plan& pl, int k, bool probe,
                 const std::string& ind) {
     const b2_ew_tensor& t = p.out[k].t;
-    const bool flex = t.dtype == B2_FLEX16;
+    const bool flex = is_flex(t.dtype);
+    const bool planes = t.dtype == B2_FLEX16_PLANES;
     if (probe) {
         if (flex)
             o << ind << "_Pragma(\"unroll\") for (int e = 0; e < V; ++e) stat" << k
@@ -302,7 +308,13 @@ void emit_store(std::ostringstream& o, const b2_ew_program& p, const Plan& pl, i
     o << ind << "{ int m[V];\n"
       << ind << "  _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { m[e] = b2_f32_to_i16(y" << k
       << "[e] * q" << k << ", fstat" << k << "); }\n";
-    if (pl.vec)
+    if (planes && pl.vec)
+        o << ind << "  b2_st" << pl.V << "_planes(o" << k << " + c, p.out_plane[" << k << "], m); }\n";
+    else if (planes)
+        o << ind << "  _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const b2_i64 at = (c + e) * p.out_sc["
+          << k << "]; o" << k << "[at] = (unsigned char)(m[e] >> 8); o" << k << "[p.out_plane[" << k
+          << "] + at] = (unsigned char)m[e]; } }\n";
+    else if (pl.vec)
         o << ind << "  b2_st" << pl.V << "_i16(o" << k << " + c, m); }\n";
     else
         o << ind << "  _Pragma(\"unroll\") for (int e = 0; e < V; ++e) o" << k
@@ -313,7 +325,7 @@ void emit_store(std::ostringstream& o, const b2_ew_program& p, const Plan& pl, i
 void emit_red_store(std::ostringstream& o, const b2_ew_program& p, int k, bool probe,
                     const std::string& val, const std::string& addr, const std::string& ind) {
     const b2_ew_tensor& t = p.out[k].t;
-    if (t.dtype == B2_FLEX16) {
+    if (is_flex(t.dtype)) {
         if (probe) {
             o << ind << "stat" << k << " = max(stat" << k << ", b2_absbits(" << val << "));\n";
         } else {
@@ -331,7 +343,7 @@ void emit_prologue(std::ostringstream& o, const b2_ew_program& p, bool probe) {
         if (p.in[i].dtype == B2_FLEX16)
             o << "    const float s" << i << " = p.flex_table[p.in_slot[" << i << "]].scale;\n";
     for (int k = 0; k < nres; ++k)
-        if (p.out[k].t.dtype == B2_FLEX16) {
+        if (is_flex(p.out[k].t.dtype)) {
             if (!probe)
                 o << "    const float q" << k << " = p.flex_table[p.out_slot[" << k
                   << "]].inv_scale;\n";
@@ -362,7 +374,7 @@ void emit_finalize(std::ostringstream& o, const b2_ew_program& p, bool probe) {
         }
         o << "    }\n";
         for (int k = p.n_out; k < nres; ++k)
-            if (p.out[k].t.dtype == B2_FLEX16)
+            if (is_flex(p.out[k].t.dtype))
                 o << "    b2_block_stat(max(stat" << k << ", b2_stat_to_int(fstat" << k
                   << ")), p.flex_stats + p.out_slot[" << k << "], reinterpret_cast<int*>(smem));\n";
         o << "}\n";
@@ -565,7 +577,7 @@ int generate(const b2_ew_program& p, const Plan& pl, bool probe, std::string* ou
     {
         const int nstat = split ? p.n_out : nres;
         for (int k = 0; k < nstat; ++k)
-            if (p.out[k].t.dtype == B2_FLEX16)
+            if (is_flex(p.out[k].t.dtype))
                 o << "    b2_block_stat(max(stat" << k << ", b2_stat_to_int(fstat" << k
                   << ")), p.flex_stats + p.out_slot[" << k << "], reinterpret_cast<int*>(smem));\n";
     }
@@ -741,7 +753,7 @@ int generate_staged(const b2_ew_program& p, const Plan& pl, bool probe, std::str
     {
         const int nstat = split ? p.n_out : nres;
         for (int k = 0; k < nstat; ++k)
-            if (p.out[k].t.dtype == B2_FLEX16)
+            if (is_flex(p.out[k].t.dtype))
                 o << "    b2_block_stat(max(stat" << k << ", b2_stat_to_int(fstat" << k
                   << ")), p.flex_stats + p.out_slot[" << k << "], reinterpret_cast<int*>(smem));\n";
     }
@@ -772,7 +784,7 @@ Plan make_plan(const b2_ew_program& p, bool want_vec) {
     Plan pl;
     bool any16 = false;
     for (int i = 0; i < p.n_in; ++i) any16 |= p.in[i].dtype == B2_FLEX16;
-    for (int k = 0; k < p.n_out; ++k) any16 |= p.out[k].t.dtype == B2_FLEX16;
+    for (int k = 0; k < p.n_out; ++k) any16 |= is_flex(p.out[k].t.dtype);
     pl.V = 1;
     pl.vec = false;
     if (want_vec) {
@@ -898,8 +910,10 @@ int validate(const b2_ew_program& p) {
     }
     for (int k = 0; k < p.n_out + p.n_red; ++k) {
         B2_REQUIRE(p.out[k].reg >= 0 && p.out[k].reg < nreg, "result %d reads an undefined register", k);
-        B2_REQUIRE(p.out[k].t.dtype == B2_F32 || p.out[k].t.dtype == B2_FLEX16, "bad result dtype");
-        if (p.out[k].t.dtype == B2_FLEX16)
+        B2_REQUIRE(p.out[k].t.dtype == B2_F32 || is_flex(p.out[k].t.dtype), "bad result dtype");
+        B2_REQUIRE(p.out[k].t.dtype != B2_FLEX16_PLANES || k < p.n_out,
+                   "byte planes are for elementwise results only");
+        if (is_flex(p.out[k].t.dtype))
             B2_REQUIRE(p.out[k].t.flex_slot >= 0, "flex result %d has no slot", k);
         if (k >= p.n_out)
             B2_REQUIRE(p.out[k].redop >= B2_RED_SUM && p.out[k].redop <= B2_RED_ARGMIN, "bad redop");
@@ -1023,7 +1037,7 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
     }
     for (int q = 0; q < nres; ++q) {
         B2_REQUIRE(out[q], "result %d is null", q);
-        any_flex |= p.out[q].t.dtype == B2_FLEX16;
+        any_flex |= is_flex(p.out[q].t.dtype);
         if (vec && q < p.n_out && !aligned16(out[q])) vec = 0;
     }
     if (any_flex) B2_REQUIRE(flex_table && flex_stats, "flex tensors need a scale table and stats");
@@ -1049,6 +1063,7 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
         a.out[q] = out[q];
         a.out_sa[q] = p.out[q].t.sa; a.out_sb[q] = p.out[q].t.sb; a.out_sc[q] = p.out[q].t.sc;
         a.out_slot[q] = p.out[q].t.flex_slot;
+        a.out_plane[q] = p.out[q].t.plane_bytes;
     }
     for (int i = 0; i < p.n_const; ++i) a.consts[i] = consts[i];
     a.flex_table = flex_table;
@@ -1136,7 +1151,7 @@ extern "C" int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* 
     }
     for (int q = 0; q < nres; ++q) {
         B2_REQUIRE(out[q], "result %d is null", q);
-        any_flex |= p.out[q].t.dtype == B2_FLEX16;
+        any_flex |= is_flex(p.out[q].t.dtype);
         if (vec && q < p.n_out && !aligned16(out[q])) vec = 0;
     }
     if (any_flex) B2_REQUIRE(flex_table && flex_stats, "flex tensors need a scale table and stats");
@@ -1168,6 +1183,7 @@ extern "C" int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* 
         a.out[q] = out[q];
         a.out_sa[q] = p.out[q].t.sa; a.out_sb[q] = p.out[q].t.sb; a.out_sc[q] = p.out[q].t.sc;
         a.out_slot[q] = p.out[q].t.flex_slot;
+        a.out_plane[q] = p.out[q].t.plane_bytes;
     }
     for (int i = 0; i < p.n_const; ++i) a.consts[i] = consts[i];
     a.flex_table = flex_table;

@@ -39,6 +39,7 @@ struct b2_ew_args {
     void* out[B2_EW_MAX_OUT];             // elementwise outputs first, then reduction outputs
     b2_i64 out_sa[B2_EW_MAX_OUT], out_sb[B2_EW_MAX_OUT], out_sc[B2_EW_MAX_OUT];
     int out_slot[B2_EW_MAX_OUT];
+    b2_i64 out_plane[B2_EW_MAX_OUT];      // byte-plane results: offset of the low plane from the high plane
     float consts[B2_EW_MAX_CONST];
     const b2_flex_scale* flex_table;      // device table, indexed by slot
     int* flex_stats;                      // device s32 per slot: max |mantissa| written
@@ -157,6 +158,22 @@ __device__ __forceinline__ void b2_st8_i16(short* p, const int* m) {
     t.z = b2_pack_i16x2(m[4], m[5]);
     t.w = b2_pack_i16x2(m[6], m[7]);
     __stcs(reinterpret_cast<int4*>(p), t);
+}
+// flex16 results stored as two byte planes (high bytes at p, low bytes `lo` bytes further): the
+// operand format of the convolution kernels, so that no separate split pass is needed
+__device__ __forceinline__ void b2_st8_planes(unsigned char* p, b2_i64 lo, const int* m) {
+    uint2 h, l;
+    const unsigned a = (unsigned)b2_pack_i16x2(m[0], m[1]), b = (unsigned)b2_pack_i16x2(m[2], m[3]);
+    const unsigned c = (unsigned)b2_pack_i16x2(m[4], m[5]), d = (unsigned)b2_pack_i16x2(m[6], m[7]);
+    h.x = __byte_perm(a, b, 0x7531); l.x = __byte_perm(a, b, 0x6420);
+    h.y = __byte_perm(c, d, 0x7531); l.y = __byte_perm(c, d, 0x6420);
+    __stcs(reinterpret_cast<uint2*>(p), h);
+    __stcs(reinterpret_cast<uint2*>(p + lo), l);
+}
+__device__ __forceinline__ void b2_st4_planes(unsigned char* p, b2_i64 lo, const int* m) {
+    const unsigned a = (unsigned)b2_pack_i16x2(m[0], m[1]), b = (unsigned)b2_pack_i16x2(m[2], m[3]);
+    __stcs(reinterpret_cast<unsigned*>(p), __byte_perm(a, b, 0x7531));
+    __stcs(reinterpret_cast<unsigned*>(p + lo), __byte_perm(a, b, 0x6420));
 }
 __device__ __forceinline__ void b2_st4_i16(short* p, const int* m) {
     int2 t;

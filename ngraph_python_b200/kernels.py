@@ -157,8 +157,68 @@ class ConvStep(_Step):
         self.out_views = [ov]
         self.flex = t.flex
         self.scratch_bytes = lib.conv_fprop_scratch_bytes(self.flex, d) + 1024
+        # flex16 with a batch that suits the implicit-GEMM kernel: the activations are read as
+        # two byte planes that their producer writes directly, and the filter planes are kept
+        # for as long as the filters do not change -- one launch per convolution
+        self.use_planes = False
+        self.filter_planes = None
+        self.filter_version = None
+        if self.flex:
+            ok, act_bytes, filt_bytes = lib.conv_planes_info(d)
+            if ok:
+                self.use_planes = True
+                self.filter_bytes = filt_bytes
+                iv.buffer.plane_bytes = act_bytes
+                iv.buffer.plane_steps = getattr(iv.buffer, "plane_steps", []) + [self]
+                self.launches = 1
+
+    def allocate(self, t):
+        if self.use_planes and self.filter_planes is None and not t.plan_only:
+            self.filter_planes = t.torch.zeros((self.filter_bytes + 1024,), dtype=t.torch.uint8,
+                                               device=t.device)
+            self.filter_ptr = self.filter_planes.data_ptr() + (-self.filter_planes.data_ptr()) % 1024
+
+    def refresh(self, t):
+        """Rebuilds the cached filter planes when the filters have changed since they were built
+        (called before every launch, and before every replay of a captured step list)."""
+        if not self.use_planes:
+            return
+        fv = self.in_views[1]
+        if fv.buffer.last_write_step < 0 and self.filter_version != fv.buffer.version:
+            lib.check(lib.raw().b2_conv_filter_planes(self._ptr(fv), C.byref(self.dims),
+                                                      self.filter_ptr, t.stream.cuda_stream))
+            t.kernel_launches += 1
+            self.filter_version = fv.buffer.version
+
+    def _launch_planes(self, t):
+        iv, fv = self.in_views
+        ov = self.out_views[0]
+        raw = lib.raw()
+        st = t.stream.cuda_stream
+        ibuf, fbuf = iv.buffer, fv.buffer
+        if not ibuf.planes_by_producer:
+            lib.check(raw.b2_conv_split_activations(self._ptr(iv), C.byref(self.dims),
+                                                    ibuf.planes_ptr, st))
+            t.kernel_launches += 1
+        if fbuf.last_write_step >= 0:
+            # filters written inside this computation: rebuilt on every call
+            lib.check(raw.b2_conv_filter_planes(self._ptr(fv), C.byref(self.dims), self.filter_ptr,
+                                                st))
+            t.kernel_launches += 1
+        else:
+            self.refresh(t)
+        slots = (t._slot_for_read(ibuf, self), t._slot_for_read(fbuf, self), ov.buffer.slot_write)
+
+        def call(probe):
+            lib.check(raw.b2_conv_fprop_flex16_planes(
+                ibuf.planes_ptr, self.filter_ptr, self._ptr(ov), C.byref(self.dims),
+                t._table.data_ptr(), slots[0], slots[1], slots[2], t._stats.data_ptr(),
+                t._probe64.data_ptr(), t._status.data_ptr(), probe, st))
+        self._flex_probe_then(t, ov.buffer, [ibuf, fbuf], call)
 
     def launch(self, t):
+        if self.use_planes:
+            return self._launch_planes(t)
         iv, fv = self.in_views
         ov = self.out_views[0]
         raw = lib.raw()

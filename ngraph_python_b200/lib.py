@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200ng.so")
 
 EW_MAX_IN, EW_MAX_OUT, EW_MAX_CONST, EW_MAX_OPS = 12, 6, 16, 96
-F32, FLEX16 = 0, 1
+F32, FLEX16, FLEX16_PLANES = 0, 1, 2
 REDUCE_NONE, REDUCE_C, REDUCE_B = 0, 1, 2
 
 OPCODES = {
@@ -29,7 +29,8 @@ class B200Error(RuntimeError):
 
 class EwTensor(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("flex_slot", C.c_int32),
-                ("sa", C.c_int64), ("sb", C.c_int64), ("sc", C.c_int64)]
+                ("sa", C.c_int64), ("sb", C.c_int64), ("sc", C.c_int64),
+                ("plane_bytes", C.c_int64)]
 
 
 class EwOp(C.Structure):
@@ -90,6 +91,12 @@ def _load():
         "b2_conv_fprop_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
         "b2_conv_fprop_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,
                                            vp, sz, vp, vp, i32, vp]),
+        "b2_conv_planes_info": (C.c_int, [C.POINTER(ConvDims), C.POINTER(i32), C.POINTER(sz),
+                                          C.POINTER(sz)]),
+        "b2_conv_split_activations": (C.c_int, [vp, C.POINTER(ConvDims), vp, vp]),
+        "b2_conv_filter_planes": (C.c_int, [vp, C.POINTER(ConvDims), vp, vp]),
+        "b2_conv_fprop_flex16_planes": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32,
+                                                  i32, vp, vp, vp, i32, vp]),
         "b2_conv_bprop_scratch_bytes": (C.c_int, [i32, C.POINTER(ConvDims), C.POINTER(sz)]),
         "b2_conv_bprop_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
         "b2_conv_bprop_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,
@@ -157,6 +164,7 @@ def make_program(dims, inputs, consts, ops, outs, reds, reduce_mode):
         t.dtype = d["dtype"]
         t.flex_slot = d.get("slot", -1)
         t.sa, t.sb, t.sc = [int(s) for s in d["strides"]]
+        t.plane_bytes = int(d.get("plane_bytes", 0))
     for i, d in enumerate(inputs):
         fill(p.inp[i], d)
     for i, (name, a, b) in enumerate(ops):
@@ -239,6 +247,13 @@ def conv_fprop_scratch_bytes(flex, dims):
     n = C.c_size_t()
     check(_lib.b2_conv_fprop_scratch_bytes(int(bool(flex)), C.byref(dims), C.byref(n)))
     return n.value
+
+
+def conv_planes_info(dims):
+    """(supported, bytes of one activation plane, bytes of both filter planes)."""
+    ok, a, f = C.c_int32(), C.c_size_t(), C.c_size_t()
+    check(_lib.b2_conv_planes_info(C.byref(dims), C.byref(ok), C.byref(a), C.byref(f)))
+    return bool(ok.value), a.value, f.value
 
 
 def conv_bprop_scratch_bytes(flex, dims):

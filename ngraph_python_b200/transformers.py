@@ -50,6 +50,12 @@ class Buffer(object):
         self.slot = -1              # flex table row of the data currently stored
         self.slot_write = -1        # row used by in-place writers (persistent tensors)
         self.init_array = None
+        # flex16 tensors read by the implicit-GEMM convolution also exist as two byte planes
+        self.plane_bytes = 0        # bytes of one plane (0: no planes wanted)
+        self.planes = None          # torch uint8 allocation holding both planes
+        self.planes_ptr = 0         # 1024-byte aligned start of the high plane
+        self.planes_by_producer = False   # the kernel that writes the tensor writes the planes
+        self.version = 0            # bumped whenever the contents change
         # planning state (per computation build)
         self.last_write_step = -1
         self.last_read_step = -1
@@ -110,6 +116,7 @@ class EwStep(object):
         self.kernel = None
         self.in_views = []
         self.out_views = []      # elementwise outputs then reduction outputs
+        self.out_targets = []    # (view, as byte planes?) per program result, in program order
         self.consts = []
         self.scratch = None
 
@@ -169,6 +176,9 @@ class Computation(object):
         for s in self.steps:
             planner.finalize_step(s)
         t._allocate()
+        for s in self.steps:
+            if hasattr(s, "allocate"):
+                s.allocate(t)
         self.launches_per_call = builtin_sum(s.launches for s in self.steps)
         self.written = planner.written_buffers
         self.param_buffers = [t._view_of(p).buffer for p in self.parameters]
@@ -229,7 +239,11 @@ class Computation(object):
         per_call = t.kernel_launches - before
         self._graph = graph
 
+        refreshable = [s for s in self.steps if hasattr(s, "refresh")]
+
         def replay():
+            for s in refreshable:
+                s.refresh(t)          # cached operand planes of tensors that changed since
             graph.replay()
             t.kernel_launches += per_call
         self.executor = replay
@@ -505,6 +519,23 @@ class _Planner(object):
             if b not in self.written_buffers:
                 self.written_buffers.append(b)
 
+    def _only_plane_readers(self, m):
+        """True when every reader of the value m is a convolution that takes it as byte planes
+        (then the int16 copy need not be written at all)."""
+        if m in self.returned:
+            return False
+        readers = self.consumers.get(m, ())
+        if not readers:
+            return False
+        buf = self.t._view_of(m).buffer
+        steps = getattr(buf, "plane_steps", ())
+        for c in readers:
+            if not isinstance(c, ConvolutionOp) or self._base_tensor(c.args[0])[0] is not m:
+                return False
+            if not any(st.op is c for st in steps):
+                return False
+        return True
+
     def _collect_outputs(self, step):
         """Which values of the group must be stored: those used by another step or returned."""
         g = step.group
@@ -612,6 +643,7 @@ class _Planner(object):
                 d["slot"] = v.buffer.slot_write if g.after_write.get(v.key()) else v.buffer.slot
             inputs.append(d)
         outs, reds = [], []
+        out_targets, red_targets = [], []
         for k, (m, v) in enumerate(zip(ew_outs + red_outs, out_views)):
             d = tdesc(v, abc[n_in + k])
             d["slot"] = t._write_slot(v.buffer) if v.buffer.flex else -1
@@ -629,16 +661,33 @@ class _Planner(object):
                     ops.append(("assign", d["reg"], None))
                     d["reg"] = n_in + n_const + len(ops) - 1
                     outs.append(d)
+                    out_targets.append((v, False))
                     continue
                 d["redop"] = m.redop
                 reds.append(d)
+                red_targets.append((v, False))
             else:
                 d["reg"] = reg[m]
-                outs.append(d)
+                buf = v.buffer
+                wants = (buf.flex and buf.plane_bytes > 0 and not isinstance(m, AssignOp) and
+                         v.is_dense() and len(outs) + len(red_outs) + 2 <= fusion.MAX_OUT)
+                if wants:
+                    # the convolutions that read this tensor take it as two byte planes: write
+                    # them here instead of running a split pass in front of every convolution
+                    pd = dict(d)
+                    pd["dtype"] = lib.FLEX16_PLANES
+                    pd["plane_bytes"] = buf.plane_bytes
+                    outs.append(pd)
+                    out_targets.append((v, True))
+                    buf.planes_by_producer = True
+                if not (wants and self._only_plane_readers(m)):
+                    outs.append(d)
+                    out_targets.append((v, False))
         prog = lib.make_program(dims, inputs, consts, ops, outs, reds, mode)
         step.kernel = lib.PlannedKernel(prog, self.t.flex) if self.t.plan_only else lib.EwKernel(prog)
         step.in_views = in_views
         step.out_views = out_views
+        step.out_targets = out_targets + red_targets
         step.consts = consts
         step.scratch_bytes = step.kernel.scratch_bytes
         t._need_scratch(step.scratch_bytes)
@@ -860,6 +909,11 @@ class B200Transformer(object):
             if b.tensor is None:
                 dt = torch.int16 if b.flex else torch.float32
                 b.tensor = torch.zeros((max(b.size, 1),), dtype=dt, device=self.device)
+        for op, b in self._buffers.items():
+            if b.plane_bytes > 0 and b.planes is None:
+                b.planes = torch.zeros((2 * b.plane_bytes + 1024,), dtype=torch.uint8,
+                                       device=self.device)
+                b.planes_ptr = b.planes.data_ptr() + (-b.planes.data_ptr()) % 1024
         if self._status is None:
             self._status = torch.zeros((1,), dtype=torch.int32, device=self.device)
             self._status_host = torch.zeros((1,), dtype=torch.int32).pin_memory()
@@ -889,6 +943,7 @@ class B200Transformer(object):
         FlexGPUDeviceTensor.__setitem__ (flexgputransform.py:183-208)."""
         torch = self.torch
         buf = view.buffer
+        buf.version += 1
         arr = np.asarray(value, dtype=np.float32)
         if arr.shape not in ((), view.axes.lengths) and arr.size != buf.size:
             raise ValueError("value shape %s does not match tensor axes %s" % (arr.shape, view.axes))
@@ -1024,6 +1079,8 @@ class B200Transformer(object):
         if self.flex:
             self._stats_host.copy_(self._stats, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
+        for b in comp.written:
+            b.version += 1
         if int(self._status_host[0]) != 0:
             self._status.zero_()
             raise lib.B200Error("a device-side wait ran out during the computation")
@@ -1049,7 +1106,9 @@ class B200Transformer(object):
 
     def _launch_ew(self, step):
         ins = [v.buffer.ptr() + v.offset * (2 if v.buffer.flex else 4) for v in step.in_views]
-        outs = [v.buffer.ptr() + v.offset * (2 if v.buffer.flex else 4) for v in step.out_views]
+        outs = [v.buffer.planes_ptr if as_planes else
+                v.buffer.ptr() + v.offset * (2 if v.buffer.flex else 4)
+                for v, as_planes in step.out_targets]
         common = dict(consts=step.consts, scratch=self._scratch.data_ptr(),
                       scratch_bytes=self._scratch.numel(), status=self._status.data_ptr(),
                       stream=self.stream.cuda_stream)
