@@ -209,20 +209,12 @@ __device__ __forceinline__ unsigned long long make_smem_desc_mn(const void* p, u
     d |= (unsigned long long)2 << 61;
     return d;
 }
-// 8 consecutive 32-bit columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld8(unsigned taddr, unsigned* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7])
-        : "r"(taddr) : "memory");
-}
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
 }
 
 constexpr int kConvMaxStages = 8;
-constexpr int kConvThreads = 320;           // producer, MMA, eight epilogue warps
+constexpr int kConvThreads = 576;           // producer, MMA, sixteen epilogue warps
 constexpr int kConvSmemMax = 232448;        // 227 KB: the most one CTA can have
 constexpr int kConvSmemFixed = 1024 /*alignment*/ + 512 /*barriers*/;
 
@@ -235,19 +227,24 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int kPanelBytes = BN * kKBytes;
-    constexpr int kAcc = 3 * BN;                               // columns per accumulator set
-    constexpr int kNBuf = (2 * kAcc <= 512) ? 2 : 1;
-    constexpr int kCols = tmem_cols(MODE_FLEX16, BN) * kNBuf > 512 ? 512
-                                                                   : tmem_cols(MODE_FLEX16, BN) * kNBuf;
+    // four accumulators per tile (HH, ah*bl, al*bh, LL): the two cross products get one each so
+    // that no accumulator takes more than one dependent MMA per k-step -- at these small N a
+    // tile's time is the length of its longest chain of dependent MMAs, not their throughput
+    constexpr int kAcc = 4 * BN;                               // columns per accumulator set
+    constexpr int kNBuf = 512 / kAcc > 4 ? 4 : 512 / kAcc;     // accumulator sets: 4, 4, 2, 1
+    constexpr int kCols = kAcc * kNBuf;                        // 256 or 512
+    // sixteen epilogue warps = four per TMEM lane quarter; each accumulator set is drained by
+    // kEpiW of them per quarter, which split its columns
+    constexpr int kEpiW = 4 / kNBuf;
     const int act_stage = p.kc_pad * 128;                      // bytes per plane per stage
     unsigned char* filt = smem;                                // [2 planes][npanels][BN][128]
     unsigned char* ring = smem + 2 * p.npanels * kPanelBytes;  // [nstages][2 planes][act_stage]
     unsigned long long* full_bar =
         (unsigned long long*)(ring + (size_t)p.nstages * 2 * act_stage);
     unsigned long long* empty_bar = full_bar + kConvMaxStages;
-    unsigned long long* tmem_full = empty_bar + kConvMaxStages;   // [2]
-    unsigned long long* tmem_empty = tmem_full + 2;               // [2]
-    unsigned long long* filt_bar = tmem_empty + 2;
+    unsigned long long* tmem_full = empty_bar + kConvMaxStages;   // [4]
+    unsigned long long* tmem_empty = tmem_full + 4;               // [4]
+    unsigned long long* filt_bar = tmem_empty + 4;
     unsigned* tmem_holder = (unsigned*)(filt_bar + 1);
     int* fail_flag = (int*)(tmem_holder + 1);
 
@@ -257,7 +254,10 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     if (threadIdx.x == 0) {
         prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapB0); prefetch_map(&mapB1);
         for (int s = 0; s < kConvMaxStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 8); }
+        for (int b = 0; b < 4; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 4 * kEpiW);
+        }
         mbar_init(filt_bar, 1);
         *fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -276,7 +276,8 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 tma_load_2d(filt + j * kPanelBytes, &mapB0, j * kKBytes, ncol0, filt_bar);
                 tma_load_2d(filt + (p.npanels + j) * kPanelBytes, &mapB1, j * kKBytes, ncol0, filt_bar);
             }
-            int g = 0;
+            int s = 0;
+            unsigned empty_parity = 1;         // the first pass over the ring finds every stage free
             bool ok = true;
             const long long t_start = clock64();
             long long t_wait = 0;
@@ -285,10 +286,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 const int pp = pq / p.Q, q = pq - pp * p.Q;
                 const int n0 = nb * 128;
                 const int h0 = pp * p.str_h - p.pad_h, w0 = q * p.str_w - p.pad_w;
-                for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
-                    const int s = g % p.nstages;
+                for (int cc = 0; cc < p.cchunks; ++cc) {
                     const long long tw = clock64();
-                    if (g >= p.nstages && !mbar_wait(&empty_bar[s], ((g / p.nstages) - 1) & 1)) {
+                    if (!mbar_wait(&empty_bar[s], empty_parity)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
                     t_wait += clock64() - tw;
@@ -296,6 +296,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                     mbar_expect_tx(&full_bar[s], 2 * p.box_bytes);
                     tma_load_4d(sa, &mapI0, n0, w0, h0, cc * p.cu, &full_bar[s]);
                     tma_load_4d(sa + act_stage, &mapI1, n0, w0, h0, cc * p.cu, &full_bar[s]);
+                    if (++s == p.nstages) { s = 0; empty_parity ^= 1u; }
                 }
             }
             if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) {
@@ -308,10 +309,21 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const unsigned mn = 1u << 15;
             const unsigned id_ss = make_idesc(2, 1, 1, BN) | mn, id_su = make_idesc(2, 1, 0, BN) | mn,
                            id_us = make_idesc(2, 0, 1, BN) | mn, id_uu = make_idesc(2, 0, 0, BN) | mn;
-            int g = 0, ti = 0;
+            int ti = 0;
             bool ok = mbar_wait(filt_bar, 0);
             if (!ok) atomicExch(fail_flag, 1);
             const int ksteps = p.kc_pad >> 5;
+            // Matrix descriptors as (low word, constant high word): only the start address
+            // (bits 0-13, in 16-byte units) changes from one MMA to the next, so the loop keeps
+            // a few running integers instead of rebuilding 64-bit descriptors -- the issuing
+            // thread's own instruction latency is what bounds a tile at these small N.
+            const unsigned long long desc_hi = (unsigned long long)((1024u >> 4) | (1u << 14) | (2u << 29)) << 32;
+            const unsigned filt_lo = ((smem_u32(filt) >> 4) & 0x3FFF) | (1u << 16);     // K-major: LBO field 1
+            const unsigned filt_lo1 = filt_lo + (unsigned)((p.npanels * kPanelBytes) >> 4);
+            const unsigned ring_lo = (smem_u32(ring) >> 4) & 0x3FFF;                  // MN-major: LBO field 0
+            const unsigned stage_units = (unsigned)((2 * act_stage) >> 4), plane_units = (unsigned)(act_stage >> 4);
+            int s = 0;
+            unsigned full_parity = 0, stage_lo = ring_lo;
             const long long t_start = clock64();
             long long t_wait_e = 0, t_wait_f = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
@@ -323,32 +335,30 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 }
                 t_wait_e += clock64() - tw;
                 tc_fence_after();
-                for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
-                    const int s = g % p.nstages;
+                int idx = 0;                                   // 32-byte column block of the filter planes
+                for (int cc = 0; cc < p.cchunks; ++cc) {
                     const long long tw2 = clock64();
-                    if (!mbar_wait(&full_bar[s], (g / p.nstages) & 1)) {
+                    if (!mbar_wait(&full_bar[s], full_parity)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
                     t_wait_f += clock64() - tw2;
                     tc_fence_after();
-                    unsigned char* sa = ring + (size_t)s * 2 * act_stage;
-                    for (int k = 0; k < ksteps; ++k) {
+                    unsigned a_lo = stage_lo;
+                    for (int k = 0; k < ksteps; ++k, ++idx, a_lo += 256u) {
                         const unsigned acc = (cc > 0 || k > 0) ? 1u : 0u;
-                        const int koff = cc * p.kc_pad + 32 * k;          // byte column of the filter planes
-                        const int panel = koff >> 7;
-                        const unsigned long long badv = (unsigned long long)((koff & 127) >> 4);
-                        const unsigned long long dB0 = make_smem_desc(filt + panel * kPanelBytes) + badv;
-                        const unsigned long long dB1 =
-                            make_smem_desc(filt + (p.npanels + panel) * kPanelBytes) + badv;
-                        const unsigned long long dA0 = make_smem_desc_mn(sa + k * 4096, 0, 1024);
-                        const unsigned long long dA1 =
-                            make_smem_desc_mn(sa + act_stage + k * 4096, 0, 1024);
+                        const unsigned boff = (unsigned)(idx >> 2) * (unsigned)(kPanelBytes >> 4) + (unsigned)(idx & 3) * 2u;
+                        const unsigned long long dB0 = desc_hi | (filt_lo + boff);
+                        const unsigned long long dB1 = desc_hi | (filt_lo1 + boff);
+                        const unsigned long long dA0 = desc_hi | a_lo;
+                        const unsigned long long dA1 = desc_hi | (a_lo + plane_units);
                         tc_mma<MODE_FLEX16>(acc_base + 0, dA0, dB0, id_ss, acc);
                         tc_mma<MODE_FLEX16>(acc_base + BN, dA0, dB1, id_su, acc);
-                        tc_mma<MODE_FLEX16>(acc_base + BN, dA1, dB0, id_us, 1u);
-                        tc_mma<MODE_FLEX16>(acc_base + 2 * BN, dA1, dB1, id_uu, acc);
+                        tc_mma<MODE_FLEX16>(acc_base + 2 * BN, dA1, dB0, id_us, acc);
+                        tc_mma<MODE_FLEX16>(acc_base + 3 * BN, dA1, dB1, id_uu, acc);
                     }
                     tc_commit(&empty_bar[s]);
+                    stage_lo += stage_units;
+                    if (++s == p.nstages) { s = 0; full_parity ^= 1u; stage_lo = ring_lo; }
                 }
                 tc_commit(&tmem_full[buf]);
             }
@@ -357,11 +367,14 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             }
         }
     } else {
-        // epilogue warps 2..9: TMEM lane quarter = warp % 4; the two warps of a quarter split the
-        // output channels of the tile
+        // epilogue warps 2..17: TMEM lane quarter = warp % 4.  Accumulator set b is drained by the
+        // warps whose slot (0..3) falls into [b*kEpiW, (b+1)*kEpiW); they split its columns.
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
-        constexpr int CW = BN >= 32 ? 16 : 8;                  // columns per tensor-memory load
+        const int slot = (warp - 2) >> 2;
+        const int set = slot / kEpiW;
+        constexpr int CW = 16;                                 // columns per tensor-memory load
+        const int c_begin = (slot % kEpiW) * (BN / kEpiW);
+        const int c_end = c_begin + BN / kEpiW;
         int stat = 0;
         unsigned long long pmax = 0;
         const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
@@ -373,30 +386,27 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         long long t_wait = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++ti) {
             const int buf = ti % kNBuf;
+            if (buf != set) continue;
             const long long tw = clock64();
             if (ok && !mbar_wait(&tmem_full[buf], (ti / kNBuf) & 1)) { atomicExch(fail_flag, 1); ok = false; }
             t_wait += clock64() - tw;
             tc_fence_after();
             const long long row = (long long)tile * 128 + quarter * 32 + lane;   // (pq*N + n)
             const unsigned lane_addr = tmem_base + buf * kAcc + ((unsigned)(quarter * 32) << 16);
-            for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += CW) {
-                unsigned hh[CW], xx[CW], ll[CW];
-                if (CW == 16) {
-                    tmem_ld16(lane_addr + c0, hh);
-                    tmem_ld16(lane_addr + BN + c0, xx);
-                    tmem_ld16(lane_addr + 2 * BN + c0, ll);
-                } else {
-                    tmem_ld8(lane_addr + c0, hh);
-                    tmem_ld8(lane_addr + BN + c0, xx);
-                    tmem_ld8(lane_addr + 2 * BN + c0, ll);
-                }
+            for (int c0 = c_begin; c0 < c_end; c0 += CW) {
+                unsigned hh[CW], x1[CW], x2[CW], ll[CW];
+                tmem_ld16(lane_addr + c0, hh);
+                tmem_ld16(lane_addr + BN + c0, x1);
+                tmem_ld16(lane_addr + 2 * BN + c0, x2);
+                tmem_ld16(lane_addr + 3 * BN + c0, ll);
                 tmem_ld_wait();
                 if (!ok) continue;
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
                     const int col = ncol0 + c0 + j;
                     const long long v = ((long long)(int)hh[j] << 16) +
-                                        ((long long)(int)xx[j] << 8) + (long long)(int)ll[j];
+                                        (((long long)(int)x1[j] + (long long)(int)x2[j]) << 8) +
+                                        (long long)(int)ll[j];
                     if (p.probe) {
                         const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
                         if (col < p.K) pmax = a > pmax ? a : pmax;
