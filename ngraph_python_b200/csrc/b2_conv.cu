@@ -162,12 +162,24 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
 // those channels in a single copy, zero fill outside the image doing the padding.  It lands in
 // shared memory as an MN-major (images contiguous) 128-byte-swizzled operand whose K rows are in
 // (channel, r, s) order -- the natural order of the C,R,S,K filter tensor -- padded to a multiple
-// of 32 rows (one MMA step); the rows of the padding multiply filter columns that are zero.
-// The filter planes of the CTA's output channels are K-major, loaded ONCE per CTA and stay
-// resident in shared memory.  CTAs are persistent: each walks many tiles, the producer warp runs
-// ahead across tile boundaries through a ring of stages, and the accumulators are double-buffered
-// in tensor memory so that the epilogue of one tile (eight warps) overlaps the MMAs of the next.
-// The only pre-pass is an elementwise split of the activations into the two operand planes.
+// of 32 rows (one MMA step).
+//
+// At 16..64 output channels an MMA's time is the read of its A operand from shared memory (4 KB
+// per instruction whatever N is), so the four byte products are folded into TWO instructions per
+// k-step.  The filters' low plane is stored as the signed byte bl - 128, which makes both filter
+// planes signed and lets them lie behind one another as one operand of 2*bn rows:
+//     A_hi x [B_hi | B_lo'] -> HH | X            A_lo x [B_hi | B_lo'] -> X | LL
+// The bias costs 128 * (sum of the activations under the window); that sum comes out of the same
+// instructions through one extra filter column whose planes are (0, +1) on every K row: its X and
+// LL accumulators are sum(a_hi) and sum(a_lo).  Because that column is 1 on the padding rows too,
+// whatever bytes lie there cancel exactly (their true filter value is 0 = 256*0 + (-128) + 128).
+//
+// The filter planes of the CTA's output channels are loaded ONCE per CTA and stay resident in
+// shared memory.  CTAs are persistent: each walks many tiles, the producer warp runs ahead across
+// tile boundaries through a ring of stages, and up to four accumulator sets in tensor memory let
+// the epilogues of earlier tiles (sixteen warps) overlap the MMAs of later ones.
+// The only pre-pass is an elementwise split of the activations into the two operand planes, and a
+// fused elementwise kernel that produces the activations can write the planes itself.
 // ================================================================================================
 struct ConvTileParams {
     int P, Q, N, K;
@@ -178,6 +190,10 @@ struct ConvTileParams {
     int box_bytes;                // bytes one activation box delivers (cu*R*S*128)
     int npanels;                  // 128-byte K panels of the resident filter planes
     int nstages;                  // ring depth
+    int bn;                       // columns per accumulator: kt output channels + the sum column
+    int kt;                       // output channels per CTA column (blockIdx.y)
+    int nbuf;                     // accumulator sets in tensor memory: 1, 2 or 4
+    int tmem_cols;                // power of two >= 3*bn*nbuf
     int num_tiles, nblk;
     long long ldc;
     void* O;
@@ -198,19 +214,20 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
         : "memory");
 }
-// MN-major operand, 128-byte swizzle: 8-row K groups `sbo` bytes apart, MN atoms `lbo` bytes apart
-__device__ __forceinline__ unsigned long long make_smem_desc_mn(const void* p, unsigned lbo,
-                                                                unsigned sbo) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_u32(p) >> 4) & 0x3FFF);
-    d |= (unsigned long long)((lbo >> 4) & 0x3FFF) << 16;
-    d |= (unsigned long long)((sbo >> 4) & 0x3FFF) << 32;
-    d |= (unsigned long long)1 << 46;
-    d |= (unsigned long long)2 << 61;
-    return d;
+// one 32-bit column of this thread's TMEM lane
+__device__ __forceinline__ unsigned tmem_ld1(unsigned taddr) {
+    unsigned r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    return r;
 }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+}
+// instruction descriptor with a run-time N
+__device__ __forceinline__ unsigned make_idesc_n(unsigned dfmt, unsigned afmt, unsigned bfmt,
+                                                 unsigned n) {
+    return (dfmt << 4) | (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) |
+           ((unsigned)(kBlockM >> 4) << 24);
 }
 
 constexpr int kConvMaxStages = 8;
@@ -218,27 +235,18 @@ constexpr int kConvThreads = 576;           // producer, MMA, sixteen epilogue w
 constexpr int kConvSmemMax = 232448;        // 227 KB: the most one CTA can have
 constexpr int kConvSmemFixed = 1024 /*alignment*/ + 512 /*barriers*/;
 
-template <int BN>
 __global__ void __launch_bounds__(kConvThreads, 1)
 conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                      const __grid_constant__ CUtensorMap mapI1,
-                     const __grid_constant__ CUtensorMap mapB0,
-                     const __grid_constant__ CUtensorMap mapB1, const ConvTileParams p) {
+                     const __grid_constant__ CUtensorMap mapB, const ConvTileParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    constexpr int kPanelBytes = BN * kKBytes;
-    // four accumulators per tile (HH, ah*bl, al*bh, LL): the two cross products get one each so
-    // that no accumulator takes more than one dependent MMA per k-step -- at these small N a
-    // tile's time is the length of its longest chain of dependent MMAs, not their throughput
-    constexpr int kAcc = 4 * BN;                               // columns per accumulator set
-    constexpr int kNBuf = 512 / kAcc > 4 ? 4 : 512 / kAcc;     // accumulator sets: 4, 4, 2, 1
-    constexpr int kCols = kAcc * kNBuf;                        // 256 or 512
-    // sixteen epilogue warps = four per TMEM lane quarter; each accumulator set is drained by
-    // kEpiW of them per quarter, which split its columns
-    constexpr int kEpiW = 4 / kNBuf;
+    const int bn = p.bn;
+    const int panel_bytes = 2 * bn * kKBytes;                  // [B_hi rows | B_lo' rows] x 128 B
+    const int acc_cols = 3 * bn;                               // HH | X | LL
     const int act_stage = p.kc_pad * 128;                      // bytes per plane per stage
-    unsigned char* filt = smem;                                // [2 planes][npanels][BN][128]
-    unsigned char* ring = smem + 2 * p.npanels * kPanelBytes;  // [nstages][2 planes][act_stage]
+    unsigned char* filt = smem;                                // [npanels][2*bn][128]
+    unsigned char* ring = smem + p.npanels * panel_bytes;      // [nstages][2 planes][act_stage]
     unsigned long long* full_bar =
         (unsigned long long*)(ring + (size_t)p.nstages * 2 * act_stage);
     unsigned long long* empty_bar = full_bar + kConvMaxStages;
@@ -249,20 +257,20 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     int* fail_flag = (int*)(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ncol0 = blockIdx.y * BN;                        // first output channel of this CTA
+    const int epi_w = 4 / p.nbuf;              // epilogue warps per lane quarter and accumulator set
 
     if (threadIdx.x == 0) {
-        prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapB0); prefetch_map(&mapB1);
+        prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapB);
         for (int s = 0; s < kConvMaxStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 4; ++b) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 4 * kEpiW);
+            mbar_init(&tmem_empty[b], 4 * epi_w);
         }
         mbar_init(filt_bar, 1);
         *fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_holder, kCols);
+    if (warp == 1) tmem_alloc(tmem_holder, p.tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -271,11 +279,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     if (warp == 0) {
         if (lane == 0) {
             // the filter planes of this CTA's output channels: once, resident
-            mbar_expect_tx(filt_bar, 2 * p.npanels * kPanelBytes);
-            for (int j = 0; j < p.npanels; ++j) {
-                tma_load_2d(filt + j * kPanelBytes, &mapB0, j * kKBytes, ncol0, filt_bar);
-                tma_load_2d(filt + (p.npanels + j) * kPanelBytes, &mapB1, j * kKBytes, ncol0, filt_bar);
-            }
+            mbar_expect_tx(filt_bar, p.npanels * panel_bytes);
+            for (int j = 0; j < p.npanels; ++j)
+                tma_load_2d(filt + j * panel_bytes, &mapB, j * kKBytes, blockIdx.y * 2 * bn, filt_bar);
             int s = 0;
             unsigned empty_parity = 1;         // the first pass over the ring finds every stage free
             bool ok = true;
@@ -288,7 +294,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 const int h0 = pp * p.str_h - p.pad_h, w0 = q * p.str_w - p.pad_w;
                 for (int cc = 0; cc < p.cchunks; ++cc) {
                     const long long tw = clock64();
-                    if (!mbar_wait(&empty_bar[s], empty_parity)) {
+                    if (!mbar_wait_relaxed(&empty_bar[s], empty_parity)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
                     t_wait += clock64() - tw;
@@ -305,21 +311,21 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // bit 15: A is MN-major
+            // bit 15: A is MN-major.  A_hi is signed, A_lo unsigned, both filter planes signed.
             const unsigned mn = 1u << 15;
-            const unsigned id_ss = make_idesc(2, 1, 1, BN) | mn, id_su = make_idesc(2, 1, 0, BN) | mn,
-                           id_us = make_idesc(2, 0, 1, BN) | mn, id_uu = make_idesc(2, 0, 0, BN) | mn;
+            const unsigned id_s2 = make_idesc_n(2, 1, 1, 2 * bn) | mn, id_u2 = make_idesc_n(2, 0, 1, 2 * bn) | mn;
+            const unsigned id_s1 = make_idesc_n(2, 1, 1, bn) | mn, id_u1 = make_idesc_n(2, 0, 1, bn) | mn;
             int ti = 0;
             bool ok = mbar_wait(filt_bar, 0);
             if (!ok) atomicExch(fail_flag, 1);
             const int ksteps = p.kc_pad >> 5;
             // Matrix descriptors as (low word, constant high word): only the start address
             // (bits 0-13, in 16-byte units) changes from one MMA to the next, so the loop keeps
-            // a few running integers instead of rebuilding 64-bit descriptors -- the issuing
-            // thread's own instruction latency is what bounds a tile at these small N.
+            // a few running integers instead of rebuilding 64-bit descriptors.
             const unsigned long long desc_hi = (unsigned long long)((1024u >> 4) | (1u << 14) | (2u << 29)) << 32;
             const unsigned filt_lo = ((smem_u32(filt) >> 4) & 0x3FFF) | (1u << 16);     // K-major: LBO field 1
-            const unsigned filt_lo1 = filt_lo + (unsigned)((p.npanels * kPanelBytes) >> 4);
+            const unsigned lo_rows = (unsigned)((bn * kKBytes) >> 4);                   // B_lo' behind B_hi
+            const unsigned panel_units = (unsigned)(panel_bytes >> 4);
             const unsigned ring_lo = (smem_u32(ring) >> 4) & 0x3FFF;                  // MN-major: LBO field 0
             const unsigned stage_units = (unsigned)((2 * act_stage) >> 4), plane_units = (unsigned)(act_stage >> 4);
             int s = 0;
@@ -327,10 +333,10 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const long long t_start = clock64();
             long long t_wait_e = 0, t_wait_f = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
-                const int buf = ti % kNBuf;
-                const unsigned acc_base = tmem_base + buf * kAcc;
+                const int buf = ti % p.nbuf;
+                const unsigned acc_base = tmem_base + buf * acc_cols;
                 const long long tw = clock64();
-                if (ti >= kNBuf && !mbar_wait(&tmem_empty[buf], ((ti / kNBuf) - 1) & 1)) {
+                if (ti >= p.nbuf && !mbar_wait(&tmem_empty[buf], ((ti / p.nbuf) - 1) & 1)) {
                     atomicExch(fail_flag, 1); ok = false; break;
                 }
                 t_wait_e += clock64() - tw;
@@ -345,16 +351,21 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                     tc_fence_after();
                     unsigned a_lo = stage_lo;
                     for (int k = 0; k < ksteps; ++k, ++idx, a_lo += 256u) {
-                        const unsigned acc = (cc > 0 || k > 0) ? 1u : 0u;
-                        const unsigned boff = (unsigned)(idx >> 2) * (unsigned)(kPanelBytes >> 4) + (unsigned)(idx & 3) * 2u;
-                        const unsigned long long dB0 = desc_hi | (filt_lo + boff);
-                        const unsigned long long dB1 = desc_hi | (filt_lo1 + boff);
+                        const unsigned boff = (unsigned)(idx >> 2) * panel_units + (unsigned)(idx & 3) * 2u;
+                        const unsigned long long dB = desc_hi | (filt_lo + boff);
                         const unsigned long long dA0 = desc_hi | a_lo;
                         const unsigned long long dA1 = desc_hi | (a_lo + plane_units);
-                        tc_mma<MODE_FLEX16>(acc_base + 0, dA0, dB0, id_ss, acc);
-                        tc_mma<MODE_FLEX16>(acc_base + BN, dA0, dB1, id_su, acc);
-                        tc_mma<MODE_FLEX16>(acc_base + 2 * BN, dA1, dB0, id_us, acc);
-                        tc_mma<MODE_FLEX16>(acc_base + 3 * BN, dA1, dB1, id_uu, acc);
+                        if (idx > 0) {
+                            tc_mma<MODE_FLEX16>(acc_base, dA0, dB, id_s2, 1u);            // HH | X
+                            tc_mma<MODE_FLEX16>(acc_base + bn, dA1, dB, id_u2, 1u);       // X | LL
+                        } else {
+                            // first k-step of a tile: the accumulators start from different products
+                            const unsigned long long dBl = desc_hi | (filt_lo + boff + lo_rows);
+                            tc_mma<MODE_FLEX16>(acc_base, dA0, dB, id_s1, 0u);
+                            tc_mma<MODE_FLEX16>(acc_base + bn, dA0, dBl, id_s1, 0u);
+                            tc_mma<MODE_FLEX16>(acc_base + bn, dA1, dB, id_u1, 1u);
+                            tc_mma<MODE_FLEX16>(acc_base + 2 * bn, dA1, dBl, id_u1, 0u);
+                        }
                     }
                     tc_commit(&empty_bar[s]);
                     stage_lo += stage_units;
@@ -368,13 +379,14 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         }
     } else {
         // epilogue warps 2..17: TMEM lane quarter = warp % 4.  Accumulator set b is drained by the
-        // warps whose slot (0..3) falls into [b*kEpiW, (b+1)*kEpiW); they split its columns.
+        // warps whose slot (0..3) falls into [b*epi_w, (b+1)*epi_w); they take the 16-column
+        // chunks of its output channels in turn.
         const int quarter = warp & 3;
         const int slot = (warp - 2) >> 2;
-        const int set = slot / kEpiW;
-        constexpr int CW = 16;                                 // columns per tensor-memory load
-        const int c_begin = (slot % kEpiW) * (BN / kEpiW);
-        const int c_end = c_begin + BN / kEpiW;
+        const int set = slot / epi_w, part = slot % epi_w;
+        const int ncol0 = blockIdx.y * p.kt;                  // first output channel of this CTA
+        int kt = p.K - ncol0;                                  // output channels this CTA owns
+        if (kt > p.kt) kt = p.kt;
         int stat = 0;
         unsigned long long pmax = 0;
         const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
@@ -385,40 +397,43 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         const long long t_start = clock64();
         long long t_wait = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++ti) {
-            const int buf = ti % kNBuf;
+            const int buf = ti % p.nbuf;
             if (buf != set) continue;
             const long long tw = clock64();
-            if (ok && !mbar_wait(&tmem_full[buf], (ti / kNBuf) & 1)) { atomicExch(fail_flag, 1); ok = false; }
+            if (ok && !mbar_wait_relaxed(&tmem_full[buf], (ti / p.nbuf) & 1)) { atomicExch(fail_flag, 1); ok = false; }
             t_wait += clock64() - tw;
             tc_fence_after();
             const long long row = (long long)tile * 128 + quarter * 32 + lane;   // (pq*N + n)
-            const unsigned lane_addr = tmem_base + buf * kAcc + ((unsigned)(quarter * 32) << 16);
-            for (int c0 = c_begin; c0 < c_end; c0 += CW) {
-                unsigned hh[CW], x1[CW], x2[CW], ll[CW];
+            const unsigned lane_addr = tmem_base + buf * acc_cols + ((unsigned)(quarter * 32) << 16);
+            // 128 * (sum of this row's activations), from the extra column p.kt
+            const int s_hi = (int)tmem_ld1(lane_addr + bn + p.kt);
+            const int s_lo = (int)tmem_ld1(lane_addr + 2 * bn + p.kt);
+            tmem_ld_wait();
+            const long long fix = 128LL * (256LL * (long long)s_hi + (long long)s_lo);
+            for (int c0 = part * 16; c0 < kt; c0 += 16 * epi_w) {
+                unsigned hh[16], xx[16], ll[16];
                 tmem_ld16(lane_addr + c0, hh);
-                tmem_ld16(lane_addr + BN + c0, x1);
-                tmem_ld16(lane_addr + 2 * BN + c0, x2);
-                tmem_ld16(lane_addr + 3 * BN + c0, ll);
+                tmem_ld16(lane_addr + bn + c0, xx);
+                tmem_ld16(lane_addr + 2 * bn + c0, ll);
                 tmem_ld_wait();
                 if (!ok) continue;
 #pragma unroll
-                for (int j = 0; j < CW; ++j) {
-                    const int col = ncol0 + c0 + j;
-                    const long long v = ((long long)(int)hh[j] << 16) +
-                                        (((long long)(int)x1[j] + (long long)(int)x2[j]) << 8) +
-                                        (long long)(int)ll[j];
+                for (int j = 0; j < 16; ++j) {
+                    const int col = c0 + j;
+                    const long long v = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
+                                        (long long)(int)ll[j] + fix;
                     if (p.probe) {
                         const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
-                        if (col < p.K) pmax = a > pmax ? a : pmax;
-                    } else if (col < p.K) {
+                        if (col < kt) pmax = a > pmax ? a : pmax;
+                    } else if (col < kt) {
                         const int qv = rescale_i64(v, sh);
                         const int a = qv < 0 ? -qv : qv;
                         stat = a > stat ? a : stat;
-                        ((short*)p.O)[(long long)col * p.ldc + row] = (short)qv;
+                        ((short*)p.O)[(long long)(ncol0 + col) * p.ldc + row] = (short)qv;
                     }
                 }
             }
-            // this warp has read its part of the accumulator buffer
+            // this warp has read its part of the accumulator set
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
@@ -444,7 +459,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, kCols);
+        tmem_dealloc(tmem_base, p.tmem_cols);
     }
     if (threadIdx.x == 0 && *fail_flag && p.status) atomicExch(p.status, 1);
 }
@@ -493,34 +508,40 @@ split_same_layout_kernel(const T* __restrict__ src, long long n, void* __restric
     }
 }
 
-// filters C,R,S,K -> planes [k_out][columns]; the columns of chunk cc start at cc*kc_pad and run
-// over (channel within the chunk, r, s), zero in the padding and for channels beyond C
-template <typename T, int MODE>
+// filters C,R,S,K -> ONE array [ntn][2*bn rows][kp] for the implicit kernel: for every CTA column
+// the high bytes of its kt output channels (rows 0..bn-1) and, behind them, the low bytes minus
+// 128 as signed bytes (rows bn..2bn-1).  Row kt of either half is the sum column: 0 in the high
+// half, +1 in the low half, on every K position the MMAs touch.  The K positions of chunk cc start
+// at cc*kc_pad and run over (channel within the chunk, r, s); padding positions and channels
+// beyond C hold the filter value 0 (bytes 0 and -128).
+template <typename T>
 __global__ void __launch_bounds__(256)
 filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cu, int cchunks, int kc_pad,
-                     int rows_p, int kp, void* __restrict__ plane0, void* __restrict__ plane1) {
-    const long long total = (long long)rows_p * kp;
+                     int ntn, int bn, int kt, int kp, unsigned char* __restrict__ planes) {
+    const long long total = (long long)ntn * 2 * bn * kp;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
-        const int row = (int)(i / kp), kc = (int)(i - (long long)row * kp);
+        const int kc = (int)(i % kp);
+        const int r2 = (int)((i / kp) % (2 * bn)), tile = (int)(i / ((long long)kp * 2 * bn));
+        const bool low = r2 >= bn;
+        const int col = low ? r2 - bn : r2;
         const int cc = kc / kc_pad, within = kc - cc * kc_pad;
-        T v = 0;
-        if (cc < cchunks && within < cu * RS && row < K) {
+        int m = 0;                                           // the filter mantissa at this position
+        bool sum_col = false;
+        if (col == kt) {
+            sum_col = cc < cchunks;
+        } else if (col < kt && tile * kt + col < K && cc < cchunks && within < cu * RS) {
             const int cl = within / RS, tap = within - cl * RS;
             const int c = cc * cu + cl;
-            if (c < C) v = F[((long long)c * RS + tap) * K + row];
+            if (c < C) m = (int)F[((long long)c * RS + tap) * K + tile * kt + col];
         }
-        if (MODE == MODE_FLEX16) {
-            const int m = (int)v;
+        unsigned char v;
+        if (sum_col) v = low ? 1 : 0;
+        else {
             const int lo = m & 0xff;
-            ((signed char*)plane0)[i] = (signed char)((m - lo) >> 8);
-            ((unsigned char*)plane1)[i] = (unsigned char)lo;
-        } else {
-            float hi, lo;
-            tf32_split((float)v, hi, lo);
-            ((float*)plane0)[i] = hi;
-            ((float*)plane1)[i] = lo;
+            v = low ? (unsigned char)(lo ^ 0x80) : (unsigned char)(((m - lo) >> 8) & 0xff);
         }
+        planes[i] = v;
     }
 }
 
@@ -538,13 +559,21 @@ int make_map_4d(CUtensorMap* map, void* base, const ConvGeom& g, int cu) {
 }
 
 struct ImplicitShape {
-    int bn, cu, cchunks, kc_pad, npanels, kp, np, nstages, smem;
-    size_t act_plane, filt_plane, bytes;
+    int ntn, kt, bn, nbuf, tmem_cols, cu, cchunks, kc_pad, npanels, kp, nstages, smem;
+    size_t act_plane, filt_bytes, bytes;
 };
 
 ImplicitShape implicit_shape(const ConvGeom& g) {
     ImplicitShape s;
-    s.bn = pick_bn(g.K);
+    // output channels per CTA column: at most 127, so that with the sum column the two filter
+    // planes make one operand of at most 256 rows
+    s.ntn = (g.K + 126) / 127;
+    s.kt = (g.K + s.ntn - 1) / s.ntn;
+    s.bn = round_up(s.kt + 1, 16);
+    const int sets = 512 / (3 * s.bn);
+    s.nbuf = sets >= 4 ? 4 : sets >= 2 ? 2 : 1;
+    s.tmem_cols = 32;
+    while (s.tmem_cols < 3 * s.bn * s.nbuf) s.tmem_cols *= 2;
     const int RS = g.R * g.S;
     // 16 channels per chunk for real windows (a 3x3 chunk is 144 rows = 18 KB per plane); a 1x1
     // filter takes up to 128 channels per chunk
@@ -553,16 +582,15 @@ ImplicitShape implicit_shape(const ConvGeom& g) {
     s.kc_pad = round_up(s.cu * RS, 32);
     s.kp = round_up(s.cchunks * s.kc_pad, kKBytes);
     s.npanels = s.kp / kKBytes;
-    s.np = round_up(g.K, s.bn);
-    const int filt_smem = 2 * s.npanels * s.bn * kKBytes;
+    const int filt_smem = s.npanels * 2 * s.bn * kKBytes;
     const int stage = 2 * s.kc_pad * 128;
     int nst = (kConvSmemMax - kConvSmemFixed - filt_smem) / stage;
     if (nst > kConvMaxStages) nst = kConvMaxStages;
     s.nstages = nst;
     s.smem = kConvSmemFixed + filt_smem + (nst > 0 ? nst : 0) * stage;
     s.act_plane = (((size_t)g.C * g.H * g.W * g.N) + 1023) / 1024 * 1024;
-    s.filt_plane = (size_t)s.np * s.kp;
-    s.bytes = 2 * s.act_plane + 2 * s.filt_plane;
+    s.filt_bytes = (((size_t)s.ntn * 2 * s.bn * s.kp) + 1023) / 1024 * 1024;
+    s.bytes = 2 * s.act_plane + s.filt_bytes;
     return s;
 }
 
@@ -573,24 +601,9 @@ ImplicitShape implicit_shape(const ConvGeom& g) {
 bool implicit_ok(int mode, const ConvGeom& g) {
     if (mode != MODE_FLEX16 || g.N % 128 != 0 || g.dil_h != 1 || g.dil_w != 1) return false;
     if (g.R > 256 || g.S > 256 || (long long)g.P * g.Q * (g.N / 128) >= (1LL << 30)) return false;
+    // the exact int32 sums: |X| <= 2*128*255 per K row
+    if ((long long)g.C * g.R * g.S + 32 > 32768) return false;
     return implicit_shape(g).nstages >= 2;
-}
-
-template <int BN>
-int launch_implicit(const CUtensorMap& mI0, const CUtensorMap& mI1, const CUtensorMap& mB0,
-                    const CUtensorMap& mB1, const ConvTileParams& p, int ntiles_n, int smem,
-                    cudaStream_t st) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        B2_CUDA(cudaFuncSetAttribute(conv_implicit_kernel<BN>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmemMax));
-        attr_set = true;
-    }
-    int ctas = p.num_tiles < 148 ? p.num_tiles : 148;
-    dim3 grid(ctas, ntiles_n);
-    conv_implicit_kernel<BN><<<grid, kConvThreads, smem, st>>>(mI0, mI1, mB0, mB1, p);
-    B2_CUDA(cudaGetLastError());
-    return B2_OK;
 }
 
 // The three parts of an implicit-GEMM forward convolution: the two operand pre-passes (which a
@@ -611,12 +624,12 @@ int implicit_split_activations(const T* I, const ConvGeom& g, const ImplicitShap
 template <typename T, int MODE>
 int implicit_filter_planes(const T* F, const ConvGeom& g, const ImplicitShape& s, void* planes,
                            cudaStream_t st) {
-    const long long n_f = (long long)s.np * s.kp;
+    const long long n_f = (long long)s.ntn * 2 * s.bn * s.kp;
     long long fb = (n_f + 255) / 256;
     if (fb > 148 * 8) fb = 148 * 8;
-    filter_planes_kernel<T, MODE><<<(unsigned)fb, 256, 0, st>>>(
-        F, g.C, g.R * g.S, g.K, s.cu, s.cchunks, s.kc_pad, s.np, s.kp, planes,
-        (unsigned char*)planes + s.filt_plane);
+    filter_planes_kernel<T><<<(unsigned)fb, 256, 0, st>>>(F, g.C, g.R * g.S, g.K, s.cu, s.cchunks,
+                                                        s.kc_pad, s.ntn, s.bn, s.kt, s.kp,
+                                                        (unsigned char*)planes);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }
@@ -630,18 +643,17 @@ int implicit_tiles(const void* act_planes, const void* filt_planes, void* O, con
     B2_REQUIRE((((uintptr_t)act_planes | (uintptr_t)filt_planes) & 1023) == 0,
                "operand planes must be 1024-byte aligned");
     void* A0 = (void*)act_planes; void* A1 = (unsigned char*)act_planes + s.act_plane;
-    void* B0 = (void*)filt_planes; void* B1 = (unsigned char*)filt_planes + s.filt_plane;
-    CUtensorMap mI0, mI1, mB0, mB1;
+    CUtensorMap mI0, mI1, mB;
     if ((rc = make_map_4d(&mI0, A0, g, s.cu))) return rc;
     if ((rc = make_map_4d(&mI1, A1, g, s.cu))) return rc;
-    if ((rc = make_map(&mB0, B0, s.np, s.kp, 1, s.bn))) return rc;
-    if ((rc = make_map(&mB1, B1, s.np, s.kp, 1, s.bn))) return rc;
+    if ((rc = make_map(&mB, (void*)filt_planes, s.ntn * 2 * s.bn, s.kp, 1, 2 * s.bn))) return rc;
     ConvTileParams p;
     p.P = g.P; p.Q = g.Q; p.N = g.N; p.K = g.K;
     p.pad_h = g.pad_h; p.pad_w = g.pad_w; p.str_h = g.str_h; p.str_w = g.str_w;
     p.cu = s.cu; p.cchunks = s.cchunks; p.kc_pad = s.kc_pad;
     p.box_bytes = s.cu * g.R * g.S * 128;
     p.npanels = s.npanels; p.nstages = s.nstages;
+    p.bn = s.bn; p.kt = s.kt; p.nbuf = s.nbuf; p.tmem_cols = s.tmem_cols;
     p.nblk = g.N / 128;
     p.num_tiles = g.P * g.Q * p.nblk;
     p.ldc = (long long)g.P * g.Q * g.N;
@@ -652,13 +664,16 @@ int implicit_tiles(const void* act_planes, const void* filt_planes, void* O, con
         const char* e = getenv("B2_CONV_DBG");
         p.dbg = e ? (long long*)strtoull(e, nullptr, 0) : nullptr;
     }
-    const int ntn = s.np / s.bn;
-    switch (s.bn) {
-        case 16: return launch_implicit<16>(mI0, mI1, mB0, mB1, p, ntn, s.smem, st);
-        case 32: return launch_implicit<32>(mI0, mI1, mB0, mB1, p, ntn, s.smem, st);
-        case 64: return launch_implicit<64>(mI0, mI1, mB0, mB1, p, ntn, s.smem, st);
-        default: return launch_implicit<128>(mI0, mI1, mB0, mB1, p, ntn, s.smem, st);
+    static bool attr_set = false;
+    if (!attr_set) {
+        B2_CUDA(cudaFuncSetAttribute(conv_implicit_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmemMax));
+        attr_set = true;
     }
+    dim3 grid(p.num_tiles < 148 ? p.num_tiles : 148, s.ntn);
+    conv_implicit_kernel<<<grid, kConvThreads, s.smem, st>>>(mI0, mI1, mB, p);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
 }
 
 template <typename T, int MODE>
@@ -993,7 +1008,7 @@ extern "C" int b2_conv_planes_info(const b2_conv_dims* d, int32_t* supported,
     if (*supported) {
         const ImplicitShape s = implicit_shape(g);
         *act_plane_bytes = s.act_plane;
-        *filter_planes_bytes = 2 * s.filt_plane;
+        *filter_planes_bytes = s.filt_bytes;
     }
     return B2_OK;
 }

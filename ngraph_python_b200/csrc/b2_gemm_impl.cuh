@@ -98,6 +98,15 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// the same for warps that wait long and share an instruction scheduler with the MMA-issuing
+// thread: back off between polls so that the polling does not take its issue slots
+__device__ __forceinline__ bool mbar_wait_relaxed(unsigned long long* bar, unsigned parity) {
+    for (int i = 0; i < (1 << 20); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(64);
+    }
+    return false;
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
                                             unsigned long long* bar) {
     asm volatile(
