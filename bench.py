@@ -360,6 +360,149 @@ def resnet_cpu_baseline(budget_s=12.0, steps=None):
                       % (reps, n, cores), "ms_per_step": round(dt * 1e3, 2)}
 
 
+# ---- ResNet-20 data-parallel training step (global batch fixed, split over the GPUs) -----------
+TRAIN_PARAM_BYTES = 1084648 + 3200      # fp32 gradients exchanged per step (weights + biases)
+
+
+def run_resnet_train(args, rank, world, torch, dist, local):
+    """One step = forward, backward (bprop_conv / update_conv), bucketed gradient allreduce,
+    Kahan-momentum update of every parameter.  The graph is the hand-differentiated network of
+    tests/golden/cases.py (pinned there against the reference CPU transformer)."""
+    import ngraph_python_b200 as ng
+    from ngraph_python_b200.comm import TorchDistComm, SingleProcessComm
+    from tests.golden import cases
+    flex = args.workload == "resnet20_train_flex16"
+    gn = args.global_batch
+    if gn % world or (gn // world) % 128:
+        raise SystemExit("global batch must give every GPU a multiple of 128 images")
+    n = gn // world
+    comm = TorchDistComm() if dist is not None else SingleProcessComm()
+    t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex, comm=comm,
+                                             bucket_bytes=args.bucket_bytes)
+    outs, params, vals = cases.resnet_train_step(ng, global_n=gn, shard=(rank, world), hw=32,
+                                                 blocks=3, lr=0.002)
+    comp = t.computation(outs[:1], *params)
+    host = []
+    for v in vals:
+        pinned = torch.empty(v.shape, dtype=torch.float32).pin_memory()
+        pinned.numpy()[...] = v
+        host.append(pinned.numpy())
+    losses = [float(comp(*host)[0]) for _ in range(3)]
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_resident():
+        # inputs already on the device: exponent management, the step list, statistics read-back
+        t._begin_call(comp)
+        comp.executor()
+        t._end_call(comp)
+
+    launches0 = t.kernel_launches
+    for _ in range(args.warmup):
+        step_resident()
+    launches_per_step = (t.kernel_launches - launches0) // max(args.warmup, 1)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step_resident()
+    ev1.record(stream)
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    kinds = {}
+    passes = 3
+    for _ in range(passes):
+        t._begin_call(comp)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(comp.steps) + 1)]
+        evs[0].record(stream)
+        for i, s in enumerate(comp.steps):
+            t._launch_step(s)
+            evs[i + 1].record(stream)
+        t._end_call(comp)
+        for i, s in enumerate(comp.steps):
+            k = kinds.setdefault(s.kind, [0.0, 0])
+            k[0] += evs[i].elapsed_time(evs[i + 1])
+            k[1] += 1
+    e2e_steps = max(1, min(args.steps, args.e2e_steps * 2))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        last = comp(*host)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop()
+    if dist is not None:
+        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
+    if rank != 0:
+        return None
+    ms_step = dev_ms / args.steps
+    conv_ms = sum(kinds[k][0] for k in ("conv", "conv_bprop", "conv_update") if k in kinds) / passes
+    tpeak, which = tensor_peak()
+    tpeak = tpeak * 2 if flex else tpeak / 2
+    tops = 3 * RESNET_FLOP_PER_IMG * n * (4 if flex else 3) / (conv_ms * 1e-3) / 1e12
+    buckets = len(t._allreduce.plan.buckets) if t._allreduce is not None else 0
+    line = {
+        "metric": "ResNet-20 %s data-parallel training img/s" % ("flex16" if flex else "fp32"),
+        "value": round(gn / (ms_step * 1e-3), 1), "unit": "img/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "flex16 (i16 mantissas, int8 hi/lo tensor-core products, i32 accumulation)"
+                 if flex else "f32 (3xTF32 tensor-core products)",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "global_batch": gn, "batch_per_gpu": n,
+                   "image": [3, 32, 32], "layout": "C,H,W,N", "optimizer": "momentum 0.9 + Kahan",
+                   "parallelism": "dp%d" % world, "allreduce_buckets": buckets,
+                   "bucket_bytes": args.bucket_bytes, "steps_per_pass": len(comp.steps),
+                   "l2": "each step streams >126 MB of activations, gradients and operand planes"},
+        "clocks": clocks,
+        "e2e": {"value": round(gn / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "img/s",
+                "h2d_bytes_per_step": int(sum(h.nbytes for h in host)), "d2h_bytes_per_step": 4,
+                "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 3)},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "convolution fprop + bprop + update steps",
+                     "achieved": round(tops, 2), "peak": round(tpeak, 1),
+                     "unit": "TOPS (int8)" if flex else "TFLOP/s (tf32)",
+                     "frac": round(tops / tpeak, 4), "traffic": None,
+                     "peak_source": which + (" bf16 x 2 as int8 stand-in" if flex else
+                                             " bf16 / 2 as tf32 stand-in"),
+                     "ms": round(conv_ms, 4)},
+        "step_time_ms_by_kind": {k: round(v[0] / passes, 4) for k, v in kinds.items()},
+        "allreduce_algorithmic_bytes_per_gpu": int(2 * (world - 1) / world * TRAIN_PARAM_BYTES),
+        "loss_first_steps": [round(v, 5) for v in losses], "loss_last": round(float(last[0]), 5),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = train_cpu_baseline()
+    return line
+
+
+def train_cpu_baseline(steps=1):
+    """The same training graph evaluated with numpy (tests/mirror_interp.py over oracle/)."""
+    import ngraph_python_b200 as ng
+    from tests.golden import cases
+    from tests import mirror_interp
+    gn = 32
+    outs, params, vals = cases.resnet_train_step(ng, global_n=gn, hw=32, blocks=3, lr=0.002)
+    interp = mirror_interp.Interp()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        interp.run(outs[:1], dict(zip(params, vals)))
+    dt = (time.perf_counter() - t0) / steps
+    cores = os.cpu_count() or 1
+    return {"value": round(gn / dt, 2), "unit": "img/s", "cores": cores, "kind": "port",
+            "sample": "%d training step(s) on a %d-image batch, numpy restatement of every op "
+                      "(numpy BLAS threads = all %d cores)" % (steps, gn, cores),
+            "ms_per_step": round(dt * 1e3, 1)}
+
+
 def tensor_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -476,6 +619,11 @@ def run_b200(args, rank, world):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if args.workload.startswith("gemm"):
         line = run_gemm(args, rank, world, torch, dist, local)
+        if dist is not None:
+            dist.destroy_process_group()
+        return line
+    if args.workload.startswith("resnet20_train"):
+        line = run_resnet_train(args, rank, world, torch, dist, local)
         if dist is not None:
             dist.destroy_process_group()
         return line
@@ -649,6 +797,22 @@ def run_reference(args, rank, world):
                                            "Dot is np.dot), %d BLAS threads" % (n, cores)},
                 "e2e": {"value": v, "unit": "Tops/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    if args.workload.startswith("resnet20_train"):
+        flex = args.workload == "resnet20_train_flex16"
+        b = train_cpu_baseline(steps=max(1, min(args.steps, 3)))
+        return {
+            "impl": "reference",
+            "metric": "ResNet-20 %s data-parallel training img/s" % ("flex16" if flex else "fp32"),
+            "value": b["value"], "unit": "img/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": b["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (numpy)", "data": "synthetic",
+            "config": {"workload": args.workload, "global_batch": args.global_batch,
+                       "image": [3, 32, 32], "layout": "C,H,W,N"},
+            "cpu_baseline": b,
+            "e2e": {"value": b["value"], "unit": "img/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
     if args.workload.startswith("resnet20"):
         flex = args.workload == "resnet20_flex16"
         b = resnet_cpu_baseline(steps=max(1, args.steps))
@@ -694,7 +858,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="resnet20_flex16",
                     choices=["resnet20_flex16", "resnet20_fp32", "c2_flex16", "c2_fp32",
-                             "gemm_flex16", "gemm_fp32"])
+                             "gemm_flex16", "gemm_fp32", "resnet20_train_flex16",
+                             "resnet20_train_fp32"])
+    ap.add_argument("--global-batch", type=int, default=1024,
+                    help="images per training step over all GPUs (training workloads)")
+    ap.add_argument("--bucket-bytes", type=int, default=25 * 1024 * 1024,
+                    help="allreduce bucket size (training workloads)")
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the GEMM workloads")
     ap.add_argument("--batch", type=int, default=RESNET_N, help="images per GPU (ResNet-20)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])

@@ -216,22 +216,27 @@ int b2_conv_fprop_flex16(const int16_t* I, const int16_t* F, int16_t* O, const b
                          const b2_flex_scale* table, int32_t slotI, int32_t slotF, int32_t slotO,
                          int32_t* stats, void* scratch, size_t scratch_bytes, uint64_t* probe_out,
                          int32_t* status, int32_t probe, void* stream);
-/* The flex16 forward convolution in parts, for callers that keep operand planes around: the
- * tile kernel reads the activations and the filters as two byte planes each (high and low bytes
- * of the int16 mantissas; activations in C,H,W,N order with the low plane act_plane_bytes after
- * the high plane, both 1024-byte aligned).  A fused elementwise kernel can emit activation planes
- * directly (B2_FLEX16_PLANES) and the filter planes of constant weights can be built once, which
- * leaves ONE launch per convolution.  `supported` is 0 where the plane path does not apply (batch
- * not a multiple of 128, dilation, very large windows); use b2_conv_fprop_flex16 there.
- * No counterpart in the reference, whose kernels read int16 tensors directly. */
-int b2_conv_planes_info(const b2_conv_dims* d, int32_t* supported, size_t* act_plane_bytes,
-                        size_t* filter_planes_bytes);
-int b2_conv_split_activations(const int16_t* I, const b2_conv_dims* d, void* planes, void* stream);
-int b2_conv_filter_planes(const int16_t* F, const b2_conv_dims* d, void* planes, void* stream);
-int b2_conv_fprop_flex16_planes(const void* act_planes, const void* filter_planes, int16_t* O,
-                                const b2_conv_dims* d, const b2_flex_scale* table, int32_t slotI,
-                                int32_t slotF, int32_t slotO, int32_t* stats, uint64_t* probe_out,
-                                int32_t* status, int32_t probe, void* stream);
+/* The flex16 convolution in parts, for callers that keep operand planes around: the tile kernel
+ * reads its streamed tensor (pass 0: the activations I; pass 1, the input gradient of a
+ * unit-stride convolution: the error tensor E) and the filters as byte planes -- high and low
+ * bytes of the int16 mantissas, the streamed tensor in its own C,H,W,N (K,P,Q,N) order with the
+ * low plane act_plane_bytes after the high plane, 1024-byte aligned.  A fused elementwise kernel
+ * can emit such planes directly (B2_FLEX16_PLANES) and the filter planes of constant weights can
+ * be built once, which leaves ONE launch per convolution.  `supported` is 0 where the plane path
+ * does not apply (batch not a multiple of 128, dilation, very large windows; pass 1: strides);
+ * use b2_conv_fprop_flex16 / b2_conv_bprop_flex16 there.  `d` always describes the FORWARD
+ * convolution.  No counterpart in the reference, whose kernels read int16 tensors directly. */
+enum b2_conv_pass { B2_CONV_FPROP = 0, B2_CONV_BPROP = 1 };
+int b2_conv_planes_info(const b2_conv_dims* d, int32_t pass, int32_t* supported,
+                        size_t* act_plane_bytes, size_t* filter_planes_bytes);
+int b2_conv_split_activations(const int16_t* X, const b2_conv_dims* d, int32_t pass, void* planes,
+                              void* stream);
+int b2_conv_filter_planes(const int16_t* F, const b2_conv_dims* d, int32_t pass, void* planes,
+                          void* stream);
+int b2_conv_flex16_planes(int32_t pass, const void* act_planes, const void* filter_planes,
+                          int16_t* out, const b2_conv_dims* d, const b2_flex_scale* table,
+                          int32_t slotX, int32_t slotF, int32_t slotOut, int32_t* stats,
+                          uint64_t* probe_out, int32_t* status, int32_t probe, void* stream);
 /* The two training contractions of a convolution whose forward pass has the dimensions `d`
  * (d always describes the FORWARD convolution: I is C,D,H,W,N, F is C,T,R,S,K, E is K,M,P,Q,N).
  * Replace ConvBpropKernel / ConvUpdateKernel (ngraph/transformers/gpu/conv.py:121-312) and

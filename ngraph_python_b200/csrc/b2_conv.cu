@@ -517,7 +517,7 @@ split_same_layout_kernel(const T* __restrict__ src, long long n, void* __restric
 template <typename T>
 __global__ void __launch_bounds__(256)
 filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cu, int cchunks, int kc_pad,
-                     int ntn, int bn, int kt, int kp, unsigned char* __restrict__ planes) {
+                     int ntn, int bn, int kt, int kp, int bprop, unsigned char* __restrict__ planes) {
     const long long total = (long long)ntn * 2 * bn * kp;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -533,7 +533,11 @@ filter_planes_kernel(const T* __restrict__ F, int C, int RS, int K, int cu, int 
         } else if (col < kt && tile * kt + col < K && cc < cchunks && within < cu * RS) {
             const int cl = within / RS, tap = within - cl * RS;
             const int c = cc * cu + cl;
-            if (c < C) m = (int)F[((long long)c * RS + tap) * K + tile * kt + col];
+            // bprop: the filter tensor is that of the FORWARD convolution, [K outputs here = its
+            // input channels][R][S][C reduced here = its output channels], read flipped
+            if (c < C)
+                m = bprop ? (int)F[((long long)(tile * kt + col) * RS + (RS - 1 - tap)) * C + c]
+                          : (int)F[((long long)c * RS + tap) * K + tile * kt + col];
         }
         unsigned char v;
         if (sum_col) v = low ? 1 : 0;
@@ -606,6 +610,24 @@ bool implicit_ok(int mode, const ConvGeom& g) {
     return implicit_shape(g).nstages >= 2;
 }
 
+// The input gradient of a unit-stride convolution is itself a convolution: of the error tensor
+// (K channels, P x Q) with the filters flipped and transposed, padded by R-1-pad.  Returns false
+// where that does not hold (strides, dilation, padding larger than the window allows).
+bool bprop_as_fprop(const ConvGeom& f, ConvGeom* g) {
+    if (f.str_h != 1 || f.str_w != 1 || f.dil_h != 1 || f.dil_w != 1) return false;
+    if (f.pad_h > f.R - 1 || f.pad_w > f.S - 1) return false;
+    *g = f;
+    g->C = f.K; g->H = f.P; g->W = f.Q; g->K = f.C; g->P = f.H; g->Q = f.W;
+    g->pad_h = f.R - 1 - f.pad_h; g->pad_w = f.S - 1 - f.pad_w;
+    return true;
+}
+
+// geometry of the implicit kernel for a pass (0 forward, 1 input gradient); false if unsupported
+bool pass_geom(const ConvGeom& f, int pass, ConvGeom* g) {
+    if (pass == 0) { *g = f; return implicit_ok(MODE_FLEX16, f); }
+    return pass == 1 && bprop_as_fprop(f, g) && implicit_ok(MODE_FLEX16, *g);
+}
+
 // The three parts of an implicit-GEMM forward convolution: the two operand pre-passes (which a
 // caller can skip when it already holds the planes) and the tile kernel.
 template <typename T, int MODE>
@@ -623,12 +645,12 @@ int implicit_split_activations(const T* I, const ConvGeom& g, const ImplicitShap
 
 template <typename T, int MODE>
 int implicit_filter_planes(const T* F, const ConvGeom& g, const ImplicitShape& s, void* planes,
-                           cudaStream_t st) {
+                           cudaStream_t st, int bprop = 0) {
     const long long n_f = (long long)s.ntn * 2 * s.bn * s.kp;
     long long fb = (n_f + 255) / 256;
     if (fb > 148 * 8) fb = 148 * 8;
     filter_planes_kernel<T><<<(unsigned)fb, 256, 0, st>>>(F, g.C, g.R * g.S, g.K, s.cu, s.cchunks,
-                                                        s.kc_pad, s.ntn, s.bn, s.kt, s.kp,
+                                                        s.kc_pad, s.ntn, s.bn, s.kt, s.kp, bprop,
                                                         (unsigned char*)planes);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
@@ -863,6 +885,18 @@ int run_bprop(const T* E, const T* F, void* GI, const b2_conv_dims* d, const b2_
     int rc = geom_from(d, &g);
     if (rc) return rc;
     B2_REQUIRE(E && F && GI, "null tensor");
+    ConvGeom gb;
+    if (MODE == MODE_FLEX16 && pass_geom(g, 1, &gb) && !getenv("B2_CONV_IM2COL")) {
+        const ImplicitShape si = implicit_shape(gb);
+        B2_REQUIRE(scratch && scratch_bytes >= si.bytes && ((uintptr_t)scratch & 1023) == 0,
+                   "convolution bprop needs %zu bytes of 1024-byte aligned scratch, got %zu",
+                   si.bytes, scratch_bytes);
+        unsigned char* base = (unsigned char*)scratch;
+        if ((rc = implicit_split_activations<T, MODE>(E, gb, si, base, st))) return rc;
+        if ((rc = implicit_filter_planes<T, MODE>(F, gb, si, base + 2 * si.act_plane, st, 1))) return rc;
+        return implicit_tiles(base, base + 2 * si.act_plane, GI, gb, si, table, slotE, slotF, slotG,
+                              stats, probe_out, status, probe, st);
+    }
     const long long rows_ll = (long long)g.H * g.W * g.N;
     B2_REQUIRE(rows_ll < (1LL << 31) - 256 && (long long)g.K * g.P * g.Q * g.N < (1LL << 31),
                "tensor too large");
@@ -996,13 +1030,13 @@ extern "C" int b2_conv_fprop_flex16(const int16_t* I, const int16_t* F, int16_t*
                                          probe ? 1 : 0, (cudaStream_t)stream);
 }
 
-extern "C" int b2_conv_planes_info(const b2_conv_dims* d, int32_t* supported,
+extern "C" int b2_conv_planes_info(const b2_conv_dims* d, int32_t pass, int32_t* supported,
                                    size_t* act_plane_bytes, size_t* filter_planes_bytes) {
-    ConvGeom g;
-    int rc = geom_from(d, &g);
+    ConvGeom f, g;
+    int rc = geom_from(d, &f);
     if (rc) return rc;
     B2_REQUIRE(supported && act_plane_bytes && filter_planes_bytes, "null argument");
-    *supported = implicit_ok(MODE_FLEX16, g) ? 1 : 0;
+    *supported = pass_geom(f, pass, &g) ? 1 : 0;
     *act_plane_bytes = 0;
     *filter_planes_bytes = 0;
     if (*supported) {
@@ -1013,40 +1047,41 @@ extern "C" int b2_conv_planes_info(const b2_conv_dims* d, int32_t* supported,
     return B2_OK;
 }
 
-extern "C" int b2_conv_split_activations(const int16_t* I, const b2_conv_dims* d, void* planes,
-                                         void* stream) {
-    ConvGeom g;
-    int rc = geom_from(d, &g);
+extern "C" int b2_conv_split_activations(const int16_t* X, const b2_conv_dims* d, int32_t pass,
+                                         void* planes, void* stream) {
+    ConvGeom f, g;
+    int rc = geom_from(d, &f);
     if (rc) return rc;
-    B2_REQUIRE(I && planes && implicit_ok(MODE_FLEX16, g), "planes are not available for this convolution");
-    return implicit_split_activations<short, MODE_FLEX16>(I, g, implicit_shape(g), planes,
+    B2_REQUIRE(X && planes && pass_geom(f, pass, &g), "planes are not available for this convolution");
+    return implicit_split_activations<short, MODE_FLEX16>(X, g, implicit_shape(g), planes,
                                                           (cudaStream_t)stream);
 }
 
-extern "C" int b2_conv_filter_planes(const int16_t* F, const b2_conv_dims* d, void* planes,
-                                     void* stream) {
-    ConvGeom g;
-    int rc = geom_from(d, &g);
+extern "C" int b2_conv_filter_planes(const int16_t* F, const b2_conv_dims* d, int32_t pass,
+                                     void* planes, void* stream) {
+    ConvGeom f, g;
+    int rc = geom_from(d, &f);
     if (rc) return rc;
-    B2_REQUIRE(F && planes && implicit_ok(MODE_FLEX16, g), "planes are not available for this convolution");
+    B2_REQUIRE(F && planes && pass_geom(f, pass, &g), "planes are not available for this convolution");
     return implicit_filter_planes<short, MODE_FLEX16>(F, g, implicit_shape(g), planes,
-                                                      (cudaStream_t)stream);
+                                                      (cudaStream_t)stream, pass);
 }
 
-extern "C" int b2_conv_fprop_flex16_planes(const void* act_planes, const void* filter_planes,
-                                           int16_t* O, const b2_conv_dims* d,
-                                           const b2_flex_scale* table, int32_t slotI, int32_t slotF,
-                                           int32_t slotO, int32_t* stats, uint64_t* probe_out,
-                                           int32_t* status, int32_t probe, void* stream) {
-    ConvGeom g;
-    int rc = geom_from(d, &g);
+extern "C" int b2_conv_flex16_planes(int32_t pass, const void* act_planes,
+                                     const void* filter_planes, int16_t* out,
+                                     const b2_conv_dims* d, const b2_flex_scale* table,
+                                     int32_t slotX, int32_t slotF, int32_t slotOut, int32_t* stats,
+                                     uint64_t* probe_out, int32_t* status, int32_t probe,
+                                     void* stream) {
+    ConvGeom f, g;
+    int rc = geom_from(d, &f);
     if (rc) return rc;
-    B2_REQUIRE(act_planes && filter_planes && O && implicit_ok(MODE_FLEX16, g),
+    B2_REQUIRE(act_planes && filter_planes && out && pass_geom(f, pass, &g),
                "planes are not available for this convolution");
-    B2_REQUIRE(table && slotI >= 0 && slotF >= 0 && slotO >= 0, "flex conv needs the scale table");
+    B2_REQUIRE(table && slotX >= 0 && slotF >= 0 && slotOut >= 0, "flex conv needs the scale table");
     B2_REQUIRE(probe ? probe_out != nullptr : stats != nullptr, "missing statistics destination");
-    return implicit_tiles(act_planes, filter_planes, O, g, implicit_shape(g), table, slotI, slotF,
-                          slotO, stats, (unsigned long long*)probe_out, status, probe ? 1 : 0,
+    return implicit_tiles(act_planes, filter_planes, out, g, implicit_shape(g), table, slotX, slotF,
+                          slotOut, stats, (unsigned long long*)probe_out, status, probe ? 1 : 0,
                           (cudaStream_t)stream);
 }
 
@@ -1055,7 +1090,13 @@ extern "C" int b2_conv_bprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, 
     int rc = geom_from(d, &g);
     if (rc) return rc;
     B2_REQUIRE(bytes, "null argument");
-    *bytes = bprop_shape(flex ? MODE_FLEX16 : MODE_F32X3, g).bytes;
+    size_t need = bprop_shape(flex ? MODE_FLEX16 : MODE_F32X3, g).bytes;
+    ConvGeom gb;
+    if (flex && pass_geom(g, 1, &gb)) {
+        const size_t alt = implicit_shape(gb).bytes;
+        if (alt > need) need = alt;
+    }
+    *bytes = need;
     return B2_OK;
 }
 

@@ -63,6 +63,77 @@ class _Step(object):
         t.kernel_launches += self.launches
 
 
+class _PlaneUser(object):
+    """flex16 convolution steps that can run on the implicit-GEMM tile kernel: the streamed
+    tensor (activations for the forward pass, the error tensor for the input gradient) is read as
+    two byte planes which its producer writes directly, and the filter planes are kept for as long
+    as the filters do not change -- one launch per convolution."""
+    use_planes = False
+    filter_planes = None
+    filter_version = None
+
+    def _setup_planes(self, t, conv_pass, stream_arg, filter_arg):
+        if not self.flex:
+            return
+        ok, act_bytes, filt_bytes = lib.conv_planes_info(self.dims, conv_pass)
+        if not ok:
+            return
+        self.use_planes = True
+        self.conv_pass = conv_pass
+        self.plane_arg = stream_arg          # index of the streamed tensor in op.args / in_views
+        self.filter_arg = filter_arg
+        self.filter_bytes = filt_bytes
+        buf = self.in_views[stream_arg].buffer
+        buf.plane_bytes = act_bytes
+        buf.plane_steps = getattr(buf, "plane_steps", []) + [self]
+        self.launches = 1
+
+    def allocate(self, t):
+        if self.use_planes and self.filter_planes is None and not t.plan_only:
+            self.filter_planes = t.torch.zeros((self.filter_bytes + 1024,), dtype=t.torch.uint8,
+                                               device=t.device)
+            self.filter_ptr = self.filter_planes.data_ptr() + (-self.filter_planes.data_ptr()) % 1024
+
+    def _build_filter_planes(self, t):
+        fv = self.in_views[self.filter_arg]
+        lib.check(lib.raw().b2_conv_filter_planes(self._ptr(fv), C.byref(self.dims), self.conv_pass,
+                                                  self.filter_ptr, t.stream.cuda_stream))
+        t.kernel_launches += 1
+        self.filter_version = fv.buffer.version
+
+    def refresh(self, t):
+        """Rebuilds the cached filter planes when the filters have changed since they were built
+        (called before every launch, and before every replay of a captured step list)."""
+        if not self.use_planes:
+            return
+        fbuf = self.in_views[self.filter_arg].buffer
+        if fbuf.last_write_step < 0 and self.filter_version != fbuf.version:
+            self._build_filter_planes(t)
+
+    def _launch_planes(self, t):
+        xv, fv = self.in_views[self.plane_arg], self.in_views[self.filter_arg]
+        ov = self.out_views[0]
+        raw = lib.raw()
+        st = t.stream.cuda_stream
+        xbuf, fbuf = xv.buffer, fv.buffer
+        if not xbuf.planes_by_producer:
+            lib.check(raw.b2_conv_split_activations(self._ptr(xv), C.byref(self.dims),
+                                                    self.conv_pass, xbuf.planes_ptr, st))
+            t.kernel_launches += 1
+        if fbuf.last_write_step >= 0:
+            self._build_filter_planes(t)     # filters written inside this computation
+        else:
+            self.refresh(t)
+        slots = (t._slot_for_read(xbuf, self), t._slot_for_read(fbuf, self), ov.buffer.slot_write)
+
+        def call(probe):
+            lib.check(raw.b2_conv_flex16_planes(
+                self.conv_pass, xbuf.planes_ptr, self.filter_ptr, self._ptr(ov),
+                C.byref(self.dims), t._table.data_ptr(), slots[0], slots[1], slots[2],
+                t._stats.data_ptr(), t._probe64.data_ptr(), t._status.data_ptr(), probe, st))
+        self._flex_probe_then(t, ov.buffer, [xbuf, fbuf], call)
+
+
 class GemmStep(_Step):
     """C[M,N] = op(A)[M,K] * op(B)[K,N] for a DotOp."""
     kind = "gemm"
@@ -118,7 +189,7 @@ class GemmStep(_Step):
         self._flex_probe_then(t, ov.buffer, [xv.buffer, yv.buffer], call)
 
 
-class ConvStep(_Step):
+class ConvStep(_PlaneUser, _Step):
     """Convolution forward on C,D,H,W,N / C,T,R,S,K / K,M,P,Q,N tensors."""
     kind = "conv"
     launches = 3
@@ -157,64 +228,7 @@ class ConvStep(_Step):
         self.out_views = [ov]
         self.flex = t.flex
         self.scratch_bytes = lib.conv_fprop_scratch_bytes(self.flex, d) + 1024
-        # flex16 with a batch that suits the implicit-GEMM kernel: the activations are read as
-        # two byte planes that their producer writes directly, and the filter planes are kept
-        # for as long as the filters do not change -- one launch per convolution
-        self.use_planes = False
-        self.filter_planes = None
-        self.filter_version = None
-        if self.flex:
-            ok, act_bytes, filt_bytes = lib.conv_planes_info(d)
-            if ok:
-                self.use_planes = True
-                self.filter_bytes = filt_bytes
-                iv.buffer.plane_bytes = act_bytes
-                iv.buffer.plane_steps = getattr(iv.buffer, "plane_steps", []) + [self]
-                self.launches = 1
-
-    def allocate(self, t):
-        if self.use_planes and self.filter_planes is None and not t.plan_only:
-            self.filter_planes = t.torch.zeros((self.filter_bytes + 1024,), dtype=t.torch.uint8,
-                                               device=t.device)
-            self.filter_ptr = self.filter_planes.data_ptr() + (-self.filter_planes.data_ptr()) % 1024
-
-    def refresh(self, t):
-        """Rebuilds the cached filter planes when the filters have changed since they were built
-        (called before every launch, and before every replay of a captured step list)."""
-        if not self.use_planes:
-            return
-        fv = self.in_views[1]
-        if fv.buffer.last_write_step < 0 and self.filter_version != fv.buffer.version:
-            lib.check(lib.raw().b2_conv_filter_planes(self._ptr(fv), C.byref(self.dims),
-                                                      self.filter_ptr, t.stream.cuda_stream))
-            t.kernel_launches += 1
-            self.filter_version = fv.buffer.version
-
-    def _launch_planes(self, t):
-        iv, fv = self.in_views
-        ov = self.out_views[0]
-        raw = lib.raw()
-        st = t.stream.cuda_stream
-        ibuf, fbuf = iv.buffer, fv.buffer
-        if not ibuf.planes_by_producer:
-            lib.check(raw.b2_conv_split_activations(self._ptr(iv), C.byref(self.dims),
-                                                    ibuf.planes_ptr, st))
-            t.kernel_launches += 1
-        if fbuf.last_write_step >= 0:
-            # filters written inside this computation: rebuilt on every call
-            lib.check(raw.b2_conv_filter_planes(self._ptr(fv), C.byref(self.dims), self.filter_ptr,
-                                                st))
-            t.kernel_launches += 1
-        else:
-            self.refresh(t)
-        slots = (t._slot_for_read(ibuf, self), t._slot_for_read(fbuf, self), ov.buffer.slot_write)
-
-        def call(probe):
-            lib.check(raw.b2_conv_fprop_flex16_planes(
-                ibuf.planes_ptr, self.filter_ptr, self._ptr(ov), C.byref(self.dims),
-                t._table.data_ptr(), slots[0], slots[1], slots[2], t._stats.data_ptr(),
-                t._probe64.data_ptr(), t._status.data_ptr(), probe, st))
-        self._flex_probe_then(t, ov.buffer, [ibuf, fbuf], call)
+        self._setup_planes(t, lib.CONV_FPROP, 0, 1)
 
     def launch(self, t):
         if self.use_planes:
@@ -257,7 +271,7 @@ def _conv_dims_of(fprop, t):
     return d
 
 
-class _ConvGradStep(_Step):
+class _ConvGradStep(_PlaneUser, _Step):
     """Shared part of the two convolution gradients: two dense operands, one dense result, the
     forward convolution's dimensions."""
     launches = 3
@@ -286,8 +300,12 @@ class _ConvGradStep(_Step):
         sizer = lib.conv_bprop_scratch_bytes if self.what == "bprop" else \
             lib.conv_update_scratch_bytes
         self.scratch_bytes = sizer(self.flex, d) + 1024
+        if self.what == "bprop":
+            self._setup_planes(t, lib.CONV_BPROP, 0, 1)      # streamed: delta; filters: args[1]
 
     def launch(self, t):
+        if self.use_planes:
+            return self._launch_planes(t)
         av, bv = self.in_views           # (delta, filters) or (delta, inputs)
         ov = self.out_views[0]
         raw = lib.raw()

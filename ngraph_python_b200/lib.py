@@ -91,12 +91,12 @@ def _load():
         "b2_conv_fprop_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
         "b2_conv_fprop_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,
                                            vp, sz, vp, vp, i32, vp]),
-        "b2_conv_planes_info": (C.c_int, [C.POINTER(ConvDims), C.POINTER(i32), C.POINTER(sz),
+        "b2_conv_planes_info": (C.c_int, [C.POINTER(ConvDims), i32, C.POINTER(i32), C.POINTER(sz),
                                           C.POINTER(sz)]),
-        "b2_conv_split_activations": (C.c_int, [vp, C.POINTER(ConvDims), vp, vp]),
-        "b2_conv_filter_planes": (C.c_int, [vp, C.POINTER(ConvDims), vp, vp]),
-        "b2_conv_fprop_flex16_planes": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32,
-                                                  i32, vp, vp, vp, i32, vp]),
+        "b2_conv_split_activations": (C.c_int, [vp, C.POINTER(ConvDims), i32, vp, vp]),
+        "b2_conv_filter_planes": (C.c_int, [vp, C.POINTER(ConvDims), i32, vp, vp]),
+        "b2_conv_flex16_planes": (C.c_int, [i32, vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32,
+                                            i32, vp, vp, vp, i32, vp]),
         "b2_conv_bprop_scratch_bytes": (C.c_int, [i32, C.POINTER(ConvDims), C.POINTER(sz)]),
         "b2_conv_bprop_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
         "b2_conv_bprop_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,
@@ -249,10 +249,13 @@ def conv_fprop_scratch_bytes(flex, dims):
     return n.value
 
 
-def conv_planes_info(dims):
-    """(supported, bytes of one activation plane, bytes of both filter planes)."""
+CONV_FPROP, CONV_BPROP = 0, 1
+
+
+def conv_planes_info(dims, conv_pass=CONV_FPROP):
+    """(supported, bytes of one plane of the streamed tensor, bytes of the filter planes)."""
     ok, a, f = C.c_int32(), C.c_size_t(), C.c_size_t()
-    check(_lib.b2_conv_planes_info(C.byref(dims), C.byref(ok), C.byref(a), C.byref(f)))
+    check(_lib.b2_conv_planes_info(C.byref(dims), conv_pass, C.byref(ok), C.byref(a), C.byref(f)))
     return bool(ok.value), a.value, f.value
 
 

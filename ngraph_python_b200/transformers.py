@@ -530,10 +530,12 @@ class _Planner(object):
         buf = self.t._view_of(m).buffer
         steps = getattr(buf, "plane_steps", ())
         for c in readers:
-            if not isinstance(c, ConvolutionOp) or self._base_tensor(c.args[0])[0] is not m:
+            st = [x for x in steps if x.op is c]
+            if not st:
                 return False
-            if not any(st.op is c for st in steps):
-                return False
+            for i, a in enumerate(c.args):
+                if self._base_tensor(a)[0] is m and i != st[0].plane_arg:
+                    return False
         return True
 
     def _collect_outputs(self, step):

@@ -135,7 +135,12 @@ def test_pool_avg(flex):
 GRAD_SHAPES = [(16, 7, 7, 32, 8, 3, 3, 0, 1), (16, 9, 11, 32, 8, 3, 3, 1, 1), (3, 16, 16, 32, 16, 3, 3, 1, 1),
                (16, 16, 16, 64, 32, 3, 3, 1, 2), (32, 16, 16, 32, 64, 1, 1, 0, 2), (64, 8, 8, 32, 64, 3, 3, 1, 1),
                (5, 6, 5, 24, 10, 2, 3, 1, 1), (16, 12, 12, 256, 32, 3, 3, 1, 2), (16, 32, 32, 64, 16, 3, 3, 1, 1),
-               (4, 9, 7, 10, 6, 3, 3, 1, 2)]
+               (4, 9, 7, 10, 6, 3, 3, 1, 2),
+               # unit stride and a batch that is a multiple of 128: the input gradient runs on the
+               # implicit-GEMM kernel with flipped, transposed filters
+               (16, 8, 8, 128, 16, 3, 3, 1, 1), (32, 6, 6, 128, 64, 3, 3, 1, 1),
+               (16, 8, 8, 128, 32, 1, 1, 0, 1), (40, 5, 7, 128, 24, 3, 2, 1, 1),
+               (64, 6, 6, 256, 130, 3, 3, 1, 1)]
 
 
 def _run_grad(torch, lib, which, flex, first, second, out, d, table=None):
