@@ -265,6 +265,8 @@ class _Planner(object):
         self.group_of = {}        # EW/reduction op -> EwGroup
         self.consumers = collections.defaultdict(list)
         self.written_buffers = []
+        self.arg_override = {}     # op -> value args after register forwarding
+        self.last_assign = {}      # persistent tensor -> the AssignOp that last wrote all of it
 
     # -- helpers ------------------------------------------------------------------------------
     def _resolve(self, op):
@@ -291,6 +293,34 @@ class _Planner(object):
 
     def _new_step_index(self):
         return len(self.steps)
+
+    def _value_args(self, op):
+        """The arguments an elementwise op reads (an AssignOp: the assigned value), after the
+        planner's register forwarding: a persistent tensor that the same kernel has just assigned
+        is read from the register of that assignment instead of from memory."""
+        if op in self.arg_override:
+            return self.arg_override[op]
+        return [op.args[1]] if isinstance(op, AssignOp) else list(op.args)
+
+    def _forwarding(self, op, value_args):
+        """(overridden args, group) when every in-place-written persistent tensor that `op` reads
+        whole was last assigned by one and the same open kernel, else None."""
+        new_args, group = list(value_args), None
+        for i, a in enumerate(value_args):
+            base, chain = self._base_tensor(a)
+            if not isinstance(base, AssignableTensorOp) or base.is_scalar_constant:
+                continue
+            buf = self.t._buffer_of(base)
+            if buf.last_write_step < 0:
+                continue
+            asg = self.last_assign.get(base)
+            if chain or asg is None or self.group_of[asg].index != buf.last_write_step:
+                return None
+            if group is not None and self.group_of[asg] is not group:
+                return None
+            group = self.group_of[asg]
+            new_args[i] = asg
+        return (new_args, group) if group is not None else None
 
     # -- planning -----------------------------------------------------------------------------
     def plan(self, ordered, returns):
@@ -332,6 +362,22 @@ class _Planner(object):
         else:
             value_args = list(op.args)
             iter_axes = op.args[0].axes if is_red else op.axes
+        # (fp32 only: a flex16 reader must see the stored, quantised value -- the Kahan term of
+        # the optimizer exists to capture exactly that quantisation error)
+        fwd = self._forwarding(op, value_args) if (self.t.fuse and not self.t.flex) else None
+        if fwd is not None:
+            # try the kernel that made the in-place writes this op reads: its registers still
+            # hold the values, so the op can run there instead of in a later launch
+            self.arg_override[op] = fwd[0]
+            if self._place_ew_with(op, is_assign, is_red, iter_axes, fwd[0], only=fwd[1]):
+                return
+            del self.arg_override[op]
+        self._place_ew_with(op, is_assign, is_red, iter_axes, value_args, only=None)
+
+    def _place_ew_with(self, op, is_assign, is_red, iter_axes, value_args, only):
+        if is_assign:
+            target = op.args[0]
+            tbuf = self.t._buffer_of(target)
         lower = -1
         for a in value_args:
             base, chain = self._base_tensor(a)
@@ -356,6 +402,8 @@ class _Planner(object):
                 continue
             tried += 1
             cand = step.group
+            if only is not None and cand is not only:
+                continue
             if not self._can_join(cand, op, iter_axes, is_red):
                 continue
             if is_assign and tbuf.last_read_step == cand.index:
@@ -365,6 +413,8 @@ class _Planner(object):
                     continue
             group = cand
             break
+        if group is None and only is not None:
+            return False
         if group is None:
             group = fusion.EwGroup(self._new_step_index(), iter_axes)
             step = EwStep(group)
@@ -399,6 +449,9 @@ class _Planner(object):
                 b.last_read_step = max(b.last_read_step, group.index)
         if is_assign:
             tbuf.last_write_step = group.index
+            whole = self.t._view_of(target).is_dense()
+            self.last_assign[self._base_tensor(target)[0]] = op if whole else None
+        return True
 
     def _can_join(self, g, op, iter_axes, is_red):
         if g.iter_axes != iter_axes:
@@ -407,7 +460,7 @@ class _Planner(object):
             if g.red_axes is not None and g.red_axes != op.reduction_axes:
                 return False
         new_inputs = 0
-        for a in (op.args[1:] if isinstance(op, AssignOp) else op.args):
+        for a in self._value_args(op):
             base, chain = self._base_tensor(a)
             if g.has(base) and isinstance(base, ReductionOp):
                 return False     # needs a value that exists only after the whole reduction
@@ -418,7 +471,7 @@ class _Planner(object):
             return False
         # the iteration space must still fold onto the kernel's three axes
         views = list(g.ext_inputs)
-        for a in (op.args[1:] if isinstance(op, AssignOp) else op.args):
+        for a in self._value_args(op):
             base, chain = self._base_tensor(a)
             if self._is_scalar_const(base) or (g.has(base) and not chain):
                 continue
@@ -602,7 +655,7 @@ class _Planner(object):
         for m in g.members:
             if isinstance(m, ReductionOp):
                 continue
-            args = [m.args[1]] if isinstance(m, AssignOp) else list(m.args)
+            args = self._value_args(m)
             descs = []
             for a in args:
                 base, chain = self._base_tensor(a)

@@ -49,11 +49,14 @@ def test_softmax_splits_at_reductions():
 
 
 def test_inplace_update_stays_ordered():
-    t, comp = _plan("assign_sequence")
-    # step 0 updates w in place, step 1 reads the new w
+    # flex16: step 0 updates w in place, step 1 reads the new (stored, quantised) w
+    t, comp = _plan("assign_sequence", flex=True)
     assert len(comp.steps) == 2
     w_buf = comp.steps[0].out_views[0].buffer
     assert comp.steps[1].in_views[0].buffer is w_buf
+    # fp32: the reader takes the new value from the register of the assignment, same kernel
+    t, comp = _plan("assign_sequence", flex=False)
+    assert len(comp.steps) == 1
 
 
 def test_broadcast_by_axis_name():
