@@ -388,6 +388,10 @@ def run_resnet_train(args, rank, world, torch, dist, local):
         pinned.numpy()[...] = v
         host.append(pinned.numpy())
     losses = [float(comp(*host)[0]) for _ in range(3)]
+    graphed = False
+    if not args.no_graph and world == 1:
+        comp.capture()
+        graphed = True
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -462,6 +466,7 @@ def run_resnet_train(args, rank, world, torch, dist, local):
                    "image": [3, 32, 32], "layout": "C,H,W,N", "optimizer": "momentum 0.9 + Kahan",
                    "parallelism": "dp%d" % world, "allreduce_buckets": buckets,
                    "bucket_bytes": args.bucket_bytes, "steps_per_pass": len(comp.steps),
+                   "cuda_graph": graphed,
                    "l2": "each step streams >126 MB of activations, gradients and operand planes"},
         "clocks": clocks,
         "e2e": {"value": round(gn / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "img/s",

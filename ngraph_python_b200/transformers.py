@@ -222,11 +222,13 @@ class Computation(object):
         per call instead of one launch (plus tensor-map encoding) per kernel.  Call after the
         computation has run at least once, so that flex exponents exist and every kernel variant is
         compiled; flex scales live in a device table, so a replay picks up exponent changes.
-        Computations with collectives are not captured."""
+        A computation with allreduce steps is captured only when there is a single replica (the
+        exchange is the identity); with several replicas the step list runs launch by launch (a
+        recorded NCCL exchange did not complete when it was tried)."""
         t = self.transformer
         if self.steps is None or t.plan_only:
             raise lib.B200Error("run the computation once before capturing it")
-        if any(s.kind == "comm" for s in self.steps):
+        if any(s.kind == "comm" for s in self.steps) and t.comm.size > 1:
             raise lib.B200Error("computations with collectives are not captured")
         if t.flex and any(not b.entry.initialized for b in self.written):
             raise lib.B200Error("run the computation once before capturing it")
@@ -234,6 +236,8 @@ class Computation(object):
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = t.kernel_launches
+        if t._allreduce is not None:
+            t._allreduce.begin_call()
         with torch.cuda.graph(graph):
             self._run_steps()
         per_call = t.kernel_launches - before
