@@ -389,8 +389,8 @@ def run_resnet_train(args, rank, world, torch, dist, local):
         host.append(pinned.numpy())
     losses = [float(comp(*host)[0]) for _ in range(3)]
     graphed = False
-    if not args.no_graph and world == 1:
-        comp.capture()
+    if not args.no_graph:
+        comp.capture()          # graphs between the NCCL exchanges (one graph on a single GPU)
         graphed = True
     stream = torch.cuda.current_stream()
 

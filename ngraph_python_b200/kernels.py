@@ -412,6 +412,8 @@ class CommStep(_Step):
                 self._ptr(v), self.arena_buffer.ptr(), v.buffer.size, t._table.data_ptr(),
                 t._slot_for_read(v.buffer, self), t.stream.cuda_stream))
             t.kernel_launches += 1
+        if t._recording:
+            return          # a graph is being recorded: the exchange is issued between replays
         t._allreduce.produced(self.key)
         if self.closes_bucket is not None:
             t._allreduce.bucket_ready(self.closes_bucket)

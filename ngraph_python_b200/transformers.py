@@ -218,37 +218,82 @@ class Computation(object):
             t._launch_step(s)
 
     def capture(self):
-        """Records the step list into a CUDA graph and replays it from now on: one graph launch
-        per call instead of one launch (plus tensor-map encoding) per kernel.  Call after the
-        computation has run at least once, so that flex exponents exist and every kernel variant is
-        compiled; flex scales live in a device table, so a replay picks up exponent changes.
-        A computation with allreduce steps is captured only when there is a single replica (the
-        exchange is the identity); with several replicas the step list runs launch by launch (a
-        recorded NCCL exchange did not complete when it was tried)."""
+        """Records the step list into CUDA graphs and replays them from now on: one graph launch
+        instead of one launch (plus tensor-map encoding) per kernel.  Call after the computation
+        has run at least once, so that flex exponents exist and every kernel variant is compiled;
+        flex scales live in a device table, so a replay picks up exponent changes.
+        With several replicas the NCCL exchanges stay outside the graphs: the step list is cut
+        into segments at every point where a bucket is handed to NCCL or a reduced tensor is first
+        needed, each segment is one graph, and the collectives are issued between the replays
+        exactly where the step-by-step executor issues them."""
         t = self.transformer
         if self.steps is None or t.plan_only:
             raise lib.B200Error("run the computation once before capturing it")
-        if any(s.kind == "comm" for s in self.steps) and t.comm.size > 1:
-            raise lib.B200Error("computations with collectives are not captured")
         if t.flex and any(not b.entry.initialized for b in self.written):
             raise lib.B200Error("run the computation once before capturing it")
         torch = t.torch
+        refreshable = [s for s in self.steps if hasattr(s, "refresh")]
+        has_comm = any(s.kind == "comm" for s in self.steps) and t.comm.size > 1
+        # -- segments ---------------------------------------------------------------------------
+        segments, cur, made_here = [], None, set()
+
+        def close():
+            nonlocal cur, made_here
+            if cur is not None and cur["steps"]:
+                segments.append(cur)
+            cur, made_here = None, set()
+        for s in self.steps:
+            needs = []
+            if has_comm and s.kind != "comm":
+                needs = [v.buffer.comm_key for v in s.in_views
+                         if getattr(v.buffer, "comm_key", None) is not None]
+            if any(k in made_here for k in needs):
+                close()
+            if cur is None:
+                cur = {"steps": [], "wait": [], "comm": [], "graph": None}
+            cur["steps"].append(s)
+            for k in needs:
+                if k not in cur["wait"]:
+                    cur["wait"].append(k)
+            if has_comm and s.kind == "comm":
+                cur["comm"].append(s)
+                made_here.add(s.key)
+                if s.closes_bucket is not None:
+                    close()
+        close()
+        # -- record ------------------------------------------------------------------------------
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
         before = t.kernel_launches
         if t._allreduce is not None:
             t._allreduce.begin_call()
-        with torch.cuda.graph(graph):
-            self._run_steps()
+        t._recording = has_comm          # comm steps and waits: kernels only, no NCCL, no bookkeeping
+        try:
+            for seg in segments:
+                if all(s.launches == 0 for s in seg["steps"]):
+                    continue             # nothing to record (fp32 exchange markers)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for s in seg["steps"]:
+                        t._launch_step(s)
+                seg["graph"] = g
+        finally:
+            t._recording = False
         per_call = t.kernel_launches - before
-        self._graph = graph
-
-        refreshable = [s for s in self.steps if hasattr(s, "refresh")]
+        self._graphs = [seg["graph"] for seg in segments]
+        ar = t._allreduce
 
         def replay():
             for s in refreshable:
                 s.refresh(t)          # cached operand planes of tensors that changed since
-            graph.replay()
+            for seg in segments:
+                for k in seg["wait"]:
+                    ar.wait_for(k)
+                if seg["graph"] is not None:
+                    seg["graph"].replay()
+                for cs in seg["comm"]:
+                    ar.produced(cs.key)
+                    if cs.closes_bucket is not None:
+                        ar.bucket_ready(cs.closes_bucket)
             t.kernel_launches += per_call
         self.executor = replay
         return self
@@ -269,6 +314,7 @@ class _Planner(object):
         self.group_of = {}        # EW/reduction op -> EwGroup
         self.consumers = collections.defaultdict(list)
         self.written_buffers = []
+        self.deferred = []         # re-quantisations of reduced tensors, placed at first use
         self.arg_override = {}     # op -> value args after register forwarding
         self.last_assign = {}      # persistent tensor -> the AssignOp that last wrote all of it
 
@@ -345,6 +391,8 @@ class _Planner(object):
                 continue
             else:
                 self._place_other(op)
+        while self.deferred:                       # reduced tensors that are only returned
+            self._place_ew(self.deferred.pop(0))
         # replacements made while placing (allreduce) change what the returns resolve to
         self.returned = set(self._base_tensor(r)[0] for r in returns)
         # decide what each group materialises
@@ -358,6 +406,7 @@ class _Planner(object):
     def _place_ew(self, op):
         is_assign = isinstance(op, AssignOp)
         is_red = isinstance(op, ReductionOp)
+        self._place_deferred_for(op.args[1:] if is_assign else op.args)
         if is_assign:
             target = op.args[0]
             value_args = [op.args[1]]
@@ -540,10 +589,21 @@ class _Planner(object):
         self.producer[op] = index
         t._comm_steps.append(step)
         if t.flex:
-            self._place_ew(requant)
+            # placed when its first consumer is: a re-quantisation right here would need the
+            # reduced values at once and force one small exchange per tensor instead of one per
+            # bucket overlapped with the rest of back-propagation
+            self.deferred.append(requant)
+
+    def _place_deferred_for(self, args):
+        for a in args:
+            base, _ = self._base_tensor(a)
+            if base in self.deferred:
+                self.deferred.remove(base)
+                self._place_ew(base)
 
     def _place_other(self, op):
         """Dense contractions and pooling: one step each, never fused with neighbours."""
+        self._place_deferred_for(op.args)
         index = self._new_step_index()
         if isinstance(op, DotOp):
             step = kernels.GemmStep(index, op, self.t)
@@ -814,6 +874,7 @@ class B200Transformer(object):
         self._inputs_written = []
         self._comm_steps = []
         self._allreduce = None
+        self._recording = False     # a CUDA graph segment is being recorded
         self._buffers = collections.OrderedDict()   # op -> Buffer
         self._views = {}
         self.finalized = False
@@ -1153,7 +1214,7 @@ class B200Transformer(object):
 
     # ---- launching -------------------------------------------------------------------------------
     def _launch_step(self, step):
-        if self._allreduce is not None:
+        if self._allreduce is not None and not self._recording:
             for v in step.in_views:
                 key = getattr(v.buffer, "comm_key", None)
                 if key is not None and step.kind != "comm":

@@ -77,7 +77,7 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, world, port, flex, case, q):
+def _rank_main(rank, world, port, flex, case, capture, q):
     import torch
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -91,7 +91,10 @@ def _rank_main(rank, world, port, flex, case, q):
         t = ng.transformers.allocate_transformer("b200", device_id=rank, flex=flex,
                                                  comm=TorchDistComm(), bucket_bytes=8192)
         comp = t.computation(outs, *params)
-        results = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
+        results = [[np.array(r, copy=True) for r in comp(*vals)]]
+        if capture:
+            comp.capture()      # graphs between the NCCL exchanges; the second step replays them
+        results.append([np.array(r, copy=True) for r in comp(*vals)])
         q.put((rank, results))
         dist.barrier()
         t.close()
@@ -99,9 +102,10 @@ def _rank_main(rank, world, port, flex, case, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("capture", [False, True])
 @pytest.mark.parametrize("case", TRAIN_CASES)
 @pytest.mark.parametrize("flex", [False, True])
-def test_train_step_two_gpus(flex, case):
+def test_train_step_two_gpus(flex, case, capture):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -110,7 +114,7 @@ def test_train_step_two_gpus(flex, case):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, flex, case, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, flex, case, capture, q)) for r in range(2)]
     for p in procs:
         p.start()
     got = dict(q.get(timeout=300) for _ in range(2))
