@@ -767,7 +767,7 @@ class _Planner(object):
             d = tdesc(v, abc[n_in + k])
             d["slot"] = t._write_slot(v.buffer) if v.buffer.flex else -1
             if isinstance(m, ReductionOp):
-                src = m.args[0]
+                src = self._value_args(m)[0]
                 base, chain = self._base_tensor(src)
                 if g.has(base) and not chain:
                     d["reg"] = reg[base]

@@ -100,3 +100,16 @@ def test_resnet20_plan_shape():
     assert kinds.count("gemm") == 1
     # bias/ReLU/residual chains collapse: far fewer elementwise kernels than the 60+ ops
     assert kinds.count("ew") <= 26
+
+
+def test_reduction_of_a_tensor_assigned_in_the_same_kernel():
+    """fp32: a reduction that reads a persistent tensor right after its assignment takes the
+    assigned value from the kernel's registers (the GEMM bench graph has this shape)."""
+    A, B = ng.make_axis(6, name="A"), ng.make_axis(5, name="B")
+    x = ng.placeholder([A, B])
+    keep = ng.persistent_tensor([A, B])
+    out = ng.sequential([ng.assign(keep, x * 2.0), ng.max(keep, reduction_axes=[A])])
+    t = ng.transformers.allocate_transformer("b200", plan_only=True)
+    comp = t.computation(out, x)
+    t.initialize()
+    assert len(comp.steps) == 1

@@ -98,3 +98,17 @@ def test_captured_graph_matches_stepwise(flex):
     for a, b in zip(stepwise, replayed):
         for x, y in zip(a, b):
             assert np.array_equal(x, y)
+
+
+def test_reduction_reads_assignment_from_registers():
+    A, B = ng.make_axis(70, name="A"), ng.make_axis(33, name="B")
+    x = ng.placeholder([A, B])
+    keep = ng.persistent_tensor([A, B])
+    out = ng.sequential([ng.assign(keep, x * 2.0), ng.max(keep, reduction_axes=[A])])
+    t = ng.transformers.allocate_transformer("b200")
+    comp = t.computation([out, keep], x)
+    xv = np.random.RandomState(4).standard_normal((70, 33)).astype(np.float32)
+    got, kept = comp(xv)
+    np.testing.assert_allclose(got, (2 * xv).max(axis=0), rtol=1e-6)
+    np.testing.assert_allclose(kept, 2 * xv, rtol=1e-6)
+    t.close()
