@@ -231,7 +231,7 @@ __device__ __forceinline__ unsigned make_idesc_n(unsigned dfmt, unsigned afmt, u
 }
 
 constexpr int kConvMaxStages = 8;
-constexpr int kConvThreads = 576;           // producer, MMA, sixteen epilogue warps
+constexpr int kConvThreads = 608;           // producer, MMA, sixteen epilogue warps, second MMA warp
 constexpr int kConvSmemMax = 232448;        // 227 KB: the most one CTA can have
 constexpr int kConvSmemFixed = 1024 /*alignment*/ + 512 /*barriers*/;
 
@@ -309,15 +309,21 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 p.dbg[0] = clock64() - t_start; p.dbg[1] = t_wait;
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 18) {
+        // two MMA-issuing threads take alternate tiles (when there are accumulator sets for both):
+        // an MMA instruction costs its issuing thread about a hundred cycles whatever its N, and
+        // at 16..64 output channels that is what bounds a tile.  (Four issuers measured no better
+        // than two: the accumulator reads of the epilogue then queue behind the MMAs.)
+        const int mma_id = warp == 1 ? 0 : 1;
+        const int n_mma = p.nbuf >= 2 ? 2 : 1;
         if (lane == 0) {
             // bit 15: A is MN-major.  A_hi is signed, A_lo unsigned, both filter planes signed.
             const unsigned mn = 1u << 15;
             const unsigned id_s2 = make_idesc_n(2, 1, 1, 2 * bn) | mn, id_u2 = make_idesc_n(2, 0, 1, 2 * bn) | mn;
             const unsigned id_s1 = make_idesc_n(2, 1, 1, bn) | mn, id_u1 = make_idesc_n(2, 0, 1, bn) | mn;
             int ti = 0;
-            bool ok = mbar_wait(filt_bar, 0);
-            if (!ok) atomicExch(fail_flag, 1);
+            bool ok = mma_id < n_mma && mbar_wait(filt_bar, 0);
+            if (!ok && mma_id < n_mma) atomicExch(fail_flag, 1);
             const int ksteps = p.kc_pad >> 5;
             // Matrix descriptors as (low word, constant high word): only the start address
             // (bits 0-13, in 16-byte units) changes from one MMA to the next, so the loop keeps
@@ -331,8 +337,16 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             int s = 0;
             unsigned full_parity = 0, stage_lo = ring_lo;
             const long long t_start = clock64();
-            long long t_wait_e = 0, t_wait_f = 0;
+            long long t_wait_e = 0, t_wait_f = 0, t_mma = 0, t_commit = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
+                if (ti % n_mma != mma_id) {
+                    // the other issuing thread's tile: step over its stages
+                    for (int cc = 0; cc < p.cchunks; ++cc) {
+                        stage_lo += stage_units;
+                        if (++s == p.nstages) { s = 0; full_parity ^= 1u; stage_lo = ring_lo; }
+                    }
+                    continue;
+                }
                 const int buf = ti % p.nbuf;
                 const unsigned acc_base = tmem_base + buf * acc_cols;
                 const long long tw = clock64();
@@ -350,6 +364,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                     t_wait_f += clock64() - tw2;
                     tc_fence_after();
                     unsigned a_lo = stage_lo;
+                    const long long tm0 = clock64();
                     for (int k = 0; k < ksteps; ++k, ++idx, a_lo += 256u) {
                         const unsigned boff = (unsigned)(idx >> 2) * panel_units + (unsigned)(idx & 3) * 2u;
                         const unsigned long long dB = desc_hi | (filt_lo + boff);
@@ -367,14 +382,19 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                             tc_mma<MODE_FLEX16>(acc_base + 2 * bn, dA1, dBl, id_u1, 0u);
                         }
                     }
+                    const long long tm1 = clock64();
                     tc_commit(&empty_bar[s]);
                     stage_lo += stage_units;
                     if (++s == p.nstages) { s = 0; full_parity ^= 1u; stage_lo = ring_lo; }
+                    t_mma += tm1 - tm0; t_commit += clock64() - tm1;
                 }
+                const long long tc0 = clock64();
                 tc_commit(&tmem_full[buf]);
+                t_commit += clock64() - tc0;
             }
-            if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) {
+            if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && mma_id == 0) {
                 p.dbg[2] = clock64() - t_start; p.dbg[3] = t_wait_e; p.dbg[4] = t_wait_f;
+                p.dbg[8] = t_mma; p.dbg[9] = t_commit;
             }
         }
     } else {
@@ -392,6 +412,8 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
                         (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
         const int sh = -ilogbf(f);
+        const bool fast = sh >= 1 && sh <= 31;
+        const unsigned rmask = fast ? (1u << sh) - 1u : 0u, rhalf = fast ? 1u << (sh - 1) : 0u;
         int ti = 0;
         bool ok = true;
         const long long t_start = clock64();
@@ -417,8 +439,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 tmem_ld16(lane_addr + 2 * bn + c0, ll);
                 tmem_ld_wait();
                 if (!ok) continue;
+                short* out = (short*)p.O + (long long)(ncol0 + c0) * p.ldc + row;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < 16; ++j, out += p.ldc) {
                     const int col = c0 + j;
                     const long long v = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
                                         (long long)(int)ll[j] + fix;
@@ -426,10 +449,10 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                         const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
                         if (col < kt) pmax = a > pmax ? a : pmax;
                     } else if (col < kt) {
-                        const int qv = rescale_i64(v, sh);
+                        const int qv = fast ? rescale_i64_fast(v, sh, rmask, rhalf) : rescale_i64(v, sh);
                         const int a = qv < 0 ? -qv : qv;
                         stat = a > stat ? a : stat;
-                        ((short*)p.O)[(long long)(ncol0 + col) * p.ldc + row] = (short)qv;
+                        *out = (short)qv;
                     }
                 }
             }

@@ -219,6 +219,24 @@ __device__ __forceinline__ int rescale_i64(long long v, int sh) {
     return (int)q;
 }
 
+// The same for 1 <= sh <= 31 (every realistic exponent combination) in 32-bit pieces: the low
+// word of v >> sh by a funnel shift, the remainder by a mask, the tie rule from both, and the
+// saturation from whether the 64-bit quotient is the sign extension of its low word.
+// About a third of the instructions of the general form; callers test the range once per kernel.
+__device__ __forceinline__ int rescale_i64_fast(long long v, int sh, unsigned mask, unsigned half) {
+    const unsigned lo = (unsigned)v;
+    const int hi = (int)(v >> 32);
+    const unsigned q0lo = __funnelshift_r(lo, (unsigned)hi, sh);   // low word of floor(v / 2^sh)
+    const int q0hi = hi >> sh;
+    const unsigned rem = lo & mask;
+    const unsigned up = (rem > half || (rem == half && (q0lo & 1u))) ? 1u : 0u;
+    const unsigned qlo = q0lo + up;
+    const int qhi = q0hi + (qlo < up ? 1 : 0);
+    const int q32 = (int)qlo;
+    if (qhi != (q32 >> 31)) return qhi < 0 ? -32768 : 32767;
+    return q32 > 32767 ? 32767 : (q32 < -32768 ? -32768 : q32);
+}
+
 template <int MODE, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
@@ -345,6 +363,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
                             (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
             const int sh = -ilogbf(f);          // f = 2^-sh exactly
+            const bool fast = sh >= 1 && sh <= 31;
+            const unsigned rmask = fast ? (1u << sh) - 1u : 0u, rhalf = fast ? 1u << (sh - 1) : 0u;
             int stat = 0;
             unsigned long long pmax = 0;
             short* crow = (short*)p.C + (long long)row * p.ldc;
@@ -376,7 +396,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                         const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
                         pmax = a > pmax ? a : pmax;
                     } else {
-                        q[j] = rescale_i64(v, sh);
+                        q[j] = fast ? rescale_i64_fast(v, sh, rmask, rhalf) : rescale_i64(v, sh);
                         const int a = q[j] < 0 ? -q[j] : q[j];
                         stat = a > stat ? a : stat;
                     }
