@@ -340,8 +340,11 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             long long t_wait_e = 0, t_wait_f = 0, t_mma = 0, t_commit = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
                 if (ti % n_mma != mma_id) {
-                    // the other issuing thread's tile: step over its stages
-                    for (int cc = 0; cc < p.cchunks; ++cc) {
+                    // the other issuing thread's tile: step over its stages, but see each of them
+                    // filled -- a waiter that skipped a phase of a barrier could take the phase
+                    // before it (same parity) for the one it waits for
+                    for (int cc = 0; cc < p.cchunks && ok; ++cc) {
+                        if (!mbar_wait(&full_bar[s], full_parity)) { atomicExch(fail_flag, 1); ok = false; }
                         stage_lo += stage_units;
                         if (++s == p.nstages) { s = 0; full_parity ^= 1u; stage_lo = ring_lo; }
                     }

@@ -504,12 +504,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
 }
 
 // ---- split-K second stage ----------------------------------------------------------------------
-// Adds the slices of one output element in slice order (deterministic), then finishes it like the
-// tile kernel's epilogue: flex16 rescale + saturate + statistics (or the probe maximum), fp32 store.
+// Adds the slices of one output element in a fixed order (deterministic), then finishes it like
+// the tile kernel's epilogue: flex16 rescale + saturate + statistics (or the probe maximum), fp32
+// store.  A block of 8 warps owns 32 consecutive elements: warp w adds the slices w, w+8, ... of
+// its lane's element, the eight partial sums are combined in warp order through shared memory.
 template <int MODE>
 __global__ void __launch_bounds__(256)
 splitk_finish_kernel(const GemmParams p, int splits) {
+    __shared__ long long part64[8][32];
+    __shared__ float part32[8][32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const long long total = (long long)p.M * p.N;
+    const long long slice = (long long)p.Mp * p.Np;
     int stat = 0;
     unsigned long long pmax = 0;
     int sh = 0;
@@ -518,42 +524,61 @@ splitk_finish_kernel(const GemmParams p, int splits) {
                         (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
         sh = -ilogbf(f);
     }
-    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total;
-         i += (long long)gridDim.x * 256) {
-        const int row = (int)(i / p.N), col = (int)(i % p.N);
-        const long long src = (long long)row * p.Np + col, slice = (long long)p.Mp * p.Np;
-        const long long dst = p.c_colmajor ? (long long)col * p.ldc + row : (long long)row * p.ldc + col;
+    for (long long base = (long long)blockIdx.x * 32; base < total; base += (long long)gridDim.x * 32) {
+        const long long i = base + lane;
+        const bool live = i < total;
+        const int row = live ? (int)(i / p.N) : 0, col = live ? (int)(i % p.N) : 0;
+        const long long src = (long long)row * p.Np + col;
         if (MODE == MODE_FLEX16) {
             long long v = 0;
-            for (int z = 0; z < splits; ++z) v += ((const long long*)p.partial)[z * slice + src];
-            if (p.probe) {
-                const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
-                pmax = a > pmax ? a : pmax;
-            } else {
-                const int q = rescale_i64(v, sh);
-                const int a = q < 0 ? -q : q;
-                stat = a > stat ? a : stat;
-                ((short*)p.C)[dst] = (short)q;
-            }
+            if (live)
+                for (int z = w; z < splits; z += 8) v += ((const long long*)p.partial)[z * slice + src];
+            part64[w][lane] = v;
         } else {
             float v = 0.f;
-            for (int z = 0; z < splits; ++z) v += ((const float*)p.partial)[z * slice + src];
-            ((float*)p.C)[dst] = v;
+            if (live)
+                for (int z = w; z < splits; z += 8) v += ((const float*)p.partial)[z * slice + src];
+            part32[w][lane] = v;
         }
+        __syncthreads();
+        if (w == 0 && live) {
+            const long long dst = p.c_colmajor ? (long long)col * p.ldc + row
+                                               : (long long)row * p.ldc + col;
+            if (MODE == MODE_FLEX16) {
+                long long v = 0;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v += part64[k][lane];
+                if (p.probe) {
+                    const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
+                    pmax = a > pmax ? a : pmax;
+                } else {
+                    const int q = rescale_i64(v, sh);
+                    const int a = q < 0 ? -q : q;
+                    stat = a > stat ? a : stat;
+                    ((short*)p.C)[dst] = (short)q;
+                }
+            } else {
+                float v = 0.f;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v += part32[k][lane];
+                ((float*)p.C)[dst] = v;
+            }
+        }
+        __syncthreads();
     }
-    if (MODE == MODE_FLEX16) {
+    if (MODE == MODE_FLEX16 && w == 0) {
         if (p.probe) {
             for (int o = 16; o > 0; o >>= 1) {
                 const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
                 pmax = t > pmax ? t : pmax;
             }
-            if ((threadIdx.x & 31) == 0 && pmax) atomicMax(p.probe_out, pmax);
+            if (lane == 0 && pmax) atomicMax(p.probe_out, pmax);
         } else {
             for (int o = 16; o > 0; o >>= 1) {
                 const int t = __shfl_xor_sync(0xffffffffu, stat, o);
                 stat = t > stat ? t : stat;
             }
-            if ((threadIdx.x & 31) == 0 && stat) atomicMax(p.stats + p.slotC, stat);
+            if (lane == 0 && stat) atomicMax(p.stats + p.slotC, stat);
         }
     }
 }
@@ -924,8 +949,8 @@ int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStr
         default: rc = launch_tile<MODE, 128>(mA0, mA1, mB0, mB1, p, s, splits, st); break;
     }
     if (rc || !p.partial) return rc;
-    long long blocks = ((long long)p.M * p.N + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    long long blocks = ((long long)p.M * p.N + 31) / 32;
+    if (blocks > 148 * 16) blocks = 148 * 16;
     splitk_finish_kernel<MODE><<<(unsigned)blocks, 256, 0, st>>>(p, splits);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
