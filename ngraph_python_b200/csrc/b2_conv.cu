@@ -311,9 +311,10 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         }
     } else if (warp == 1 || warp == 18) {
         // two MMA-issuing threads take alternate tiles (when there are accumulator sets for both):
-        // an MMA instruction costs its issuing thread about a hundred cycles whatever its N, and
-        // at 16..64 output channels that is what bounds a tile.  (Four issuers measured no better
-        // than two: the accumulator reads of the epilogue then queue behind the MMAs.)
+        // an MMA instruction costs its issuing thread about a hundred cycles whatever its N and
+        // whatever the operand layout (a K-major, channel-innermost variant of this kernel was
+        // measured slower), and at 16..64 output channels that latency is what bounds a tile.
+        // Four issuers measured no better than two.
         const int mma_id = warp == 1 ? 0 : 1;
         const int n_mma = p.nbuf >= 2 ? 2 : 1;
         if (lane == 0) {
@@ -420,7 +421,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         int ti = 0;
         bool ok = true;
         const long long t_start = clock64();
-        long long t_wait = 0;
+        long long t_wait = 0, t_ld = 0, t_arr = 0, t_all = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++ti) {
             const int buf = ti % p.nbuf;
             if (buf != set) continue;
@@ -431,6 +432,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const long long row = (long long)tile * 128 + quarter * 32 + lane;   // (pq*N + n)
             const unsigned lane_addr = tmem_base + buf * acc_cols + ((unsigned)(quarter * 32) << 16);
             // 128 * (sum of this row's activations), from the extra column p.kt
+            const long long te0 = clock64();
             const int s_hi = (int)tmem_ld1(lane_addr + bn + p.kt);
             const int s_lo = (int)tmem_ld1(lane_addr + 2 * bn + p.kt);
             tmem_ld_wait();
@@ -441,31 +443,52 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 tmem_ld16(lane_addr + bn + c0, xx);
                 tmem_ld16(lane_addr + 2 * bn + c0, ll);
                 tmem_ld_wait();
+                t_ld += clock64() - te0;
                 if (!ok) continue;
                 short* out = (short*)p.O + (long long)(ncol0 + c0) * p.ldc + row;
+                long long v[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j, out += p.ldc) {
-                    const int col = c0 + j;
-                    const long long v = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
-                                        (long long)(int)ll[j] + fix;
-                    if (p.probe) {
-                        const unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
-                        if (col < kt) pmax = a > pmax ? a : pmax;
-                    } else if (col < kt) {
-                        const int qv = fast ? rescale_i64_fast(v, sh, rmask, rhalf) : rescale_i64(v, sh);
-                        const int a = qv < 0 ? -qv : qv;
+                for (int j = 0; j < 16; ++j)
+                    v[j] = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
+                           (long long)(int)ll[j] + fix;
+                if (p.probe) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const unsigned long long a = (unsigned long long)(v[j] < 0 ? -v[j] : v[j]);
+                        if (c0 + j < kt) pmax = a > pmax ? a : pmax;
+                    }
+                    continue;
+                }
+                // all sixteen values first, then the stores: independent chains for the scheduler
+                int q[16];
+                if (fast) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) q[j] = rescale_i64_fast(v[j], sh, rmask, rhalf);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) q[j] = rescale_i64(v[j], sh);
+                }
+                const int live = kt - c0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (j < live) {
+                        const int a = q[j] < 0 ? -q[j] : q[j];
                         stat = a > stat ? a : stat;
-                        *out = (short)qv;
+                        out[(long long)j * p.ldc] = (short)q[j];
                     }
                 }
             }
             // this warp has read its part of the accumulator set
+            const long long te1 = clock64();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            t_arr += clock64() - te1;
+            t_all += clock64() - te0;
         }
         if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64) {
             p.dbg[5] = clock64() - t_start; p.dbg[6] = t_wait; p.dbg[7] = ti;
+            p.dbg[10] = t_ld; p.dbg[11] = t_arr; p.dbg[12] = t_all;
         }
         if (p.probe) {
             for (int o = 16; o > 0; o >>= 1) {
