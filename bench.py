@@ -92,6 +92,17 @@ class ClockSampler(object):
         for line in self.proc.stdout:
             self.samples.append([c.strip() for c in line.split(",")])
 
+    def keep_loaded(self, load, sync, want=4, limit_s=4.0):
+        """The timed region of a short run can end before nvidia-smi has produced a sample: keep
+        the same workload running (untimed) until there are `want` samples under load."""
+        if self.proc is None:
+            return
+        t0 = time.perf_counter()
+        while len(self.samples) < want and time.perf_counter() - t0 < limit_s:
+            for _ in range(20):
+                load()
+            sync()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -270,6 +281,7 @@ def run_resnet(args, rank, world, torch, dist, local):
     ev1.record(stream)
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
+    sampler.keep_loaded(comp.executor, torch.cuda.synchronize)
     # per-kind device time: events between the steps of a few instrumented passes
     kinds = {}
     passes = 5
@@ -420,6 +432,7 @@ def run_resnet_train(args, rank, world, torch, dist, local):
     ev1.record(stream)
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
+    sampler.keep_loaded(step_resident, torch.cuda.synchronize)
     kinds = {}
     passes = 3
     for _ in range(passes):
@@ -560,6 +573,7 @@ def run_gemm(args, rank, world, torch, dist, local):
     ev1.record(stream)
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
+    sampler.keep_loaded(lambda: t._launch_step(gemm_step), torch.cuda.synchronize)
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     comp(*host)
     barrier()
@@ -674,6 +688,7 @@ def run_b200(args, rank, world):
     ev1.record(stream)
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
+    sampler.keep_loaded(comp.executor, torch.cuda.synchronize)
     # ---- end to end: host arrays in, results out ---------------------------------------------
     for _ in range(max(1, min(args.warmup, 2))):
         comp(*host)
