@@ -91,6 +91,8 @@ class FlexEntry(object):
         self.pending_dec = None
         self.history = deque(maxlen=HISTORY_LEN)
         self.overflows = 0
+        self._run_value = None      # last recorded maximum and how many times in a row it came
+        self._run_length = 0
 
     @property
     def scale(self):
@@ -123,15 +125,27 @@ class FlexEntry(object):
             return
         if maxabs_mantissa >= MANT_MAX:
             self.overflows += 1
+            self._run_length = 0
             self.history.append(2.0 * maxabs_mantissa * self.scale)
             self.pending_dec = DEC_MIN if self.dec - 2 < DEC_MIN else self.dec - 2
             return
-        self.history.append(maxabs_mantissa * self.scale)
-        n = len(self.history)
-        mean = math.fsum(self.history) / n
-        var = math.fsum((h - mean) ** 2 for h in self.history) / n
-        predicted = builtin_max(self.history) + HEADROOM_SIGMAS * math.sqrt(var)
-        self.pending_dec = largest_dec_holding(predicted)
+        value = maxabs_mantissa * self.scale
+        if value == self._run_value:
+            self._run_length += 1
+            if self._run_length > HISTORY_LEN:
+                # the window already holds nothing but this value: same mean, zero spread, same
+                # choice as after the previous write (steady state of an inference loop)
+                self.pending_dec = self._run_choice
+                return
+        else:
+            self._run_value, self._run_length = value, 1
+        self.history.append(value)
+        hist = list(self.history)
+        n = len(hist)
+        mean = math.fsum(hist) / n
+        var = math.fsum([(h - mean) ** 2 for h in hist]) / n
+        predicted = builtin_max(hist) + HEADROOM_SIGMAS * math.sqrt(var)
+        self.pending_dec = self._run_choice = largest_dec_holding(predicted)
 
 
 builtin_max = max

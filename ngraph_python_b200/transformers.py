@@ -1047,6 +1047,7 @@ class B200Transformer(object):
                 self._stats_host = torch.zeros((n,), dtype=torch.int32).pin_memory()
                 self._table_np = self._table_host.numpy()
                 self._dec_uploaded = {}
+                self._table_dirty = True
         for op, b in self._buffers.items():
             if b.init_array is not None and not getattr(b, "initialised", False):
                 b.initialised = True
@@ -1163,6 +1164,14 @@ class B200Transformer(object):
         self._table_np[slot, 1] = 2.0 ** dec
         self._table[slot].copy_(self._table_host[slot])
 
+    def _set_table_row_host(self, slot, dec):
+        """Updates the pinned copy of a table row; the device copy follows in one transfer."""
+        if self._dec_uploaded.get(slot) != dec:
+            self._dec_uploaded[slot] = dec
+            self._table_np[slot, 0] = math.ldexp(1.0, -dec)
+            self._table_np[slot, 1] = math.ldexp(1.0, dec)
+            self._table_dirty = True
+
     def _begin_call(self, comp):
         self._ensure_scratch()
         if self._allreduce is not None:
@@ -1171,25 +1180,32 @@ class B200Transformer(object):
             return
         self.flex_manager.autoflex_count += 1
         self._inputs_written = []
-        written = set(id(b) for b in comp.written)
-        written.update(id(b) for b in comp.param_buffers)
-        tab = self._table_np
-        for b in self._buffers.values():
+        # Only tensors this computation writes (or receives from the host) can adopt a new exponent
+        # here; every other tensor's table rows were brought up to date by the call that wrote it.
+        bufs = getattr(comp, "_flex_bufs", None)
+        if bufs is None:
+            seen, bufs = set(), []
+            for b in list(comp.written) + list(comp.param_buffers):
+                if id(b) in seen or b.entry is None or getattr(b, "shares_entry", False):
+                    continue
+                seen.add(id(b))
+                bufs.append(b)
+            comp._flex_bufs = bufs
+            for b in self._buffers.values():          # first call: every row the steps may read
+                if b.entry is not None and not getattr(b, "shares_entry", False) and id(b) not in seen:
+                    self._set_table_row_host(b.slot, b.entry.dec)
+                    self._set_table_row_host(b.slot_write, b.entry.dec)
+        for b in bufs:
             e = b.entry
-            if e is None or getattr(b, "shares_entry", False):
-                continue
             dec_stored = e.dec
             # tensors this call overwrites adopt the exponent chosen after their previous write
-            dec_w = e.begin_write() if (e.initialized and id(b) in written) else dec_stored
-            if self._dec_uploaded.get(b.slot_write) != dec_w:
-                self._dec_uploaded[b.slot_write] = dec_w
-                tab[b.slot_write, 0] = math.ldexp(1.0, -dec_w)
-                tab[b.slot_write, 1] = math.ldexp(1.0, dec_w)
-            if b.slot != b.slot_write and self._dec_uploaded.get(b.slot) != dec_stored:
-                self._dec_uploaded[b.slot] = dec_stored
-                tab[b.slot, 0] = math.ldexp(1.0, -dec_stored)
-                tab[b.slot, 1] = math.ldexp(1.0, dec_stored)
-        self._table.copy_(self._table_host, non_blocking=False)
+            dec_w = e.begin_write() if e.initialized else dec_stored
+            self._set_table_row_host(b.slot_write, dec_w)
+            if b.slot != b.slot_write:
+                self._set_table_row_host(b.slot, dec_stored)
+        if self._table_dirty:
+            self._table.copy_(self._table_host, non_blocking=True)
+            self._table_dirty = False
         self._stats.zero_()
 
     def _end_call(self, comp):
