@@ -237,6 +237,27 @@ int b2_conv_flex16_planes(int32_t pass, const void* act_planes, const void* filt
                           int16_t* out, const b2_conv_dims* d, const b2_flex_scale* table,
                           int32_t slotX, int32_t slotF, int32_t slotOut, int32_t* stats,
                           uint64_t* probe_out, int32_t* status, int32_t probe, void* stream);
+/* The same with the elementwise tail of a convolution layer folded into the tile kernel's
+ * epilogue: y = relu?(conv + bias[k] + residual) evaluated in fp32 from the exact integer sum,
+ * quantised ONCE with the output's exponent (slotOut), stored as int16 (write_int16) and / or as
+ * the byte planes the next convolution reads (out_planes, low plane plane_bytes further).  bias:
+ * int16 per output channel; residual: int16 tensor in the output's K,P,Q,N layout; NULL = absent.
+ * probe != 0 stores nothing and leaves the bit pattern of max |y| (fp32) in *probe_out.
+ * Replaces the bias / activation arguments the reference's convolution kernels carry
+ * (ConvFpropKernel bsum / relu flags, ngraph/transformers/gpu/conv.py:48-100) and the
+ * elementwise kernels it launches after them. */
+typedef struct b2_conv_epilogue {
+    const int16_t* bias;     int32_t slot_bias;
+    const int16_t* residual; int32_t slot_residual;
+    int32_t relu;
+    int32_t write_int16;
+    void* out_planes;        size_t plane_bytes;
+} b2_conv_epilogue;
+int b2_conv_flex16_planes_fused(int32_t pass, const void* act_planes, const void* filter_planes,
+                                int16_t* out, const b2_conv_dims* d, const b2_flex_scale* table,
+                                int32_t slotX, int32_t slotF, int32_t slotOut,
+                                const b2_conv_epilogue* epilogue, int32_t* stats,
+                                uint64_t* probe_out, int32_t* status, int32_t probe, void* stream);
 /* The two training contractions of a convolution whose forward pass has the dimensions `d`
  * (d always describes the FORWARD convolution: I is C,D,H,W,N, F is C,T,R,S,K, E is K,M,P,Q,N).
  * Replace ConvBpropKernel / ConvUpdateKernel (ngraph/transformers/gpu/conv.py:121-312) and

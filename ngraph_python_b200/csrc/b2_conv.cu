@@ -204,6 +204,15 @@ struct ConvTileParams {
     int* status;
     int probe;
     long long* dbg;      // optional per-role cycle counters of CTA 0 (profiling aid), else null
+    // fused epilogue (all optional): y = relu?(conv + bias[k] + residual) in fp32, quantised once
+    // with the output's exponent; stored as int16 and / or as the byte planes the next
+    // convolution reads
+    int fused;                    // 0: plain integer rescale of the convolution
+    const short* bias; int slot_bias;
+    const short* residual; int slot_res;      // same K,P,Q,N layout as the output
+    int relu;
+    int write_i16;
+    unsigned char* out_planes; long long out_plane_bytes;
 };
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1,
@@ -416,6 +425,11 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
                         (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
         const int sh = -ilogbf(f);
+        const float f_conv = p.table[p.slotA].scale * p.table[p.slotB].scale;
+        const float s_bias = p.bias ? p.table[p.slot_bias].scale : 0.0f;
+        const float s_res = p.residual ? p.table[p.slot_res].scale : 0.0f;
+        const float q_out = p.table[p.slotC].inv_scale;
+        float fmax_probe = 0.0f;
         const bool fast = sh >= 1 && sh <= 31;
         const unsigned rmask = fast ? (1u << sh) - 1u : 0u, rhalf = fast ? 1u << (sh - 1) : 0u;
         int ti = 0;
@@ -445,6 +459,39 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 tmem_ld_wait();
                 t_ld += clock64() - te0;
                 if (!ok) continue;
+                if (p.fused) {
+                    // fp32 epilogue: the exact integer sum scaled to a real value, bias and
+                    // residual added, ReLU, ONE quantisation with the output's exponent
+                    const long long base = (long long)(ncol0 + c0) * p.ldc + row;
+                    const int live = kt - c0;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j >= live) break;
+                        const long long vv = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
+                                             (long long)(int)ll[j] + fix;
+                        float y = __ll2float_rn(vv) * f_conv;
+                        if (p.bias) y += (float)p.bias[ncol0 + c0 + j] * s_bias;
+                        if (p.residual) y += (float)p.residual[base + (long long)j * p.ldc] * s_res;
+                        if (p.relu) y = fmaxf(y, 0.0f);
+                        if (p.probe) {
+                            fmax_probe = fmaxf(fmax_probe, fabsf(y));
+                            continue;
+                        }
+                        float t = y * q_out;
+                        t = (t != t) ? 0.0f : t;
+                        t = fminf(fmaxf(t, -32768.0f), 32767.0f);
+                        const int m = __float_as_int(t + 12582912.0f) - 0x4B400000;   // round to nearest even
+                        const int a = m < 0 ? -m : m;
+                        stat = a > stat ? a : stat;
+                        const long long at = base + (long long)j * p.ldc;
+                        if (p.write_i16) ((short*)p.O)[at] = (short)m;
+                        if (p.out_planes) {
+                            p.out_planes[at] = (unsigned char)(m >> 8);
+                            p.out_planes[p.out_plane_bytes + at] = (unsigned char)m;
+                        }
+                    }
+                    continue;
+                }
                 short* out = (short*)p.O + (long long)(ncol0 + c0) * p.ldc + row;
                 long long v[16];
 #pragma unroll
@@ -491,6 +538,8 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             p.dbg[10] = t_ld; p.dbg[11] = t_arr; p.dbg[12] = t_all;
         }
         if (p.probe) {
+            // fused: the bit pattern of max |y| (fp32); plain: max |integer sum|
+            if (p.fused) pmax = (unsigned long long)__float_as_uint(fmax_probe);
             for (int o = 16; o > 0; o >>= 1) {
                 const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
                 pmax = t > pmax ? t : pmax;
@@ -708,7 +757,7 @@ int implicit_filter_planes(const T* F, const ConvGeom& g, const ImplicitShape& s
 int implicit_tiles(const void* act_planes, const void* filt_planes, void* O, const ConvGeom& g,
                    const ImplicitShape& s, const b2_flex_scale* table, int slotI, int slotF,
                    int slotO, int* stats, unsigned long long* probe_out, int* status, int probe,
-                   cudaStream_t st) {
+                   cudaStream_t st, const b2_conv_epilogue* epi = nullptr) {
     int rc = get_encode();
     if (rc) return rc;
     B2_REQUIRE((((uintptr_t)act_planes | (uintptr_t)filt_planes) & 1023) == 0,
@@ -730,6 +779,21 @@ int implicit_tiles(const void* act_planes, const void* filt_planes, void* O, con
     p.ldc = (long long)g.P * g.Q * g.N;
     p.O = O; p.table = table; p.slotA = slotI; p.slotB = slotF; p.slotC = slotO;
     p.stats = stats; p.probe_out = probe_out; p.status = status; p.probe = probe;
+    p.fused = 0; p.bias = nullptr; p.residual = nullptr; p.slot_bias = p.slot_res = 0; p.relu = 0;
+    p.write_i16 = 1; p.out_planes = nullptr; p.out_plane_bytes = 0;
+    if (epi) {
+        B2_REQUIRE(!epi->bias || epi->slot_bias >= 0, "bias needs its scale slot");
+        B2_REQUIRE(!epi->residual || epi->slot_residual >= 0, "residual needs its scale slot");
+        B2_REQUIRE(epi->write_int16 || epi->out_planes, "the fused epilogue stores nothing");
+        B2_REQUIRE(!epi->out_planes || ((uintptr_t)epi->out_planes & 15) == 0, "planes alignment");
+        p.fused = 1;
+        p.bias = epi->bias; p.slot_bias = epi->slot_bias;
+        p.residual = epi->residual; p.slot_res = epi->slot_residual;
+        p.relu = epi->relu ? 1 : 0;
+        p.write_i16 = epi->write_int16 ? 1 : 0;
+        p.out_planes = (unsigned char*)epi->out_planes;
+        p.out_plane_bytes = (long long)epi->plane_bytes;
+    }
     {
         // profiling aid: B2_CONV_DBG=<device address> makes CTA 0 write 8 cycle counters there
         const char* e = getenv("B2_CONV_DBG");
@@ -1132,6 +1196,26 @@ extern "C" int b2_conv_flex16_planes(int32_t pass, const void* act_planes,
     return implicit_tiles(act_planes, filter_planes, out, g, implicit_shape(g), table, slotX, slotF,
                           slotOut, stats, (unsigned long long*)probe_out, status, probe ? 1 : 0,
                           (cudaStream_t)stream);
+}
+
+extern "C" int b2_conv_flex16_planes_fused(int32_t pass, const void* act_planes,
+                                           const void* filter_planes, int16_t* out,
+                                           const b2_conv_dims* d, const b2_flex_scale* table,
+                                           int32_t slotX, int32_t slotF, int32_t slotOut,
+                                           const b2_conv_epilogue* epilogue, int32_t* stats,
+                                           uint64_t* probe_out, int32_t* status, int32_t probe,
+                                           void* stream) {
+    ConvGeom f, g;
+    int rc = geom_from(d, &f);
+    if (rc) return rc;
+    B2_REQUIRE(act_planes && filter_planes && epilogue && pass_geom(f, pass, &g),
+               "planes are not available for this convolution");
+    B2_REQUIRE(out || !epilogue->write_int16, "missing output tensor");
+    B2_REQUIRE(table && slotX >= 0 && slotF >= 0 && slotOut >= 0, "flex conv needs the scale table");
+    B2_REQUIRE(probe ? probe_out != nullptr : stats != nullptr, "missing statistics destination");
+    return implicit_tiles(act_planes, filter_planes, out, g, implicit_shape(g), table, slotX, slotF,
+                          slotOut, stats, (unsigned long long*)probe_out, status, probe ? 1 : 0,
+                          (cudaStream_t)stream, epilogue);
 }
 
 extern "C" int b2_conv_bprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, size_t* bytes) {

@@ -41,6 +41,13 @@ class EwResult(C.Structure):
     _fields_ = [("reg", C.c_int32), ("redop", C.c_int32), ("t", EwTensor)]
 
 
+class ConvEpilogue(C.Structure):
+    _fields_ = [("bias", C.c_void_p), ("slot_bias", C.c_int32),
+                ("residual", C.c_void_p), ("slot_residual", C.c_int32),
+                ("relu", C.c_int32), ("write_int16", C.c_int32),
+                ("out_planes", C.c_void_p), ("plane_bytes", C.c_size_t)]
+
+
 class EwProgram(C.Structure):
     _fields_ = [("A", C.c_int64), ("B", C.c_int64), ("C", C.c_int64),
                 ("reduce_mode", C.c_int32),
@@ -97,6 +104,8 @@ def _load():
         "b2_conv_filter_planes": (C.c_int, [vp, C.POINTER(ConvDims), i32, vp, vp]),
         "b2_conv_flex16_planes": (C.c_int, [i32, vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32,
                                             i32, vp, vp, vp, i32, vp]),
+        "b2_conv_flex16_planes_fused": (C.c_int, [i32, vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32,
+                                                  i32, C.POINTER(ConvEpilogue), vp, vp, vp, i32, vp]),
         "b2_conv_bprop_scratch_bytes": (C.c_int, [i32, C.POINTER(ConvDims), C.POINTER(sz)]),
         "b2_conv_bprop_f32": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, sz, vp, vp]),
         "b2_conv_bprop_flex16": (C.c_int, [vp, vp, vp, C.POINTER(ConvDims), vp, i32, i32, i32, vp,

@@ -232,3 +232,73 @@ def test_conv_grad_flex16_exact(shape, small, which):
     got = out.cpu().numpy().astype(np.int64)
     assert np.array_equal(got, exp)
     assert stat == int(np.abs(got).max())
+
+
+@pytest.mark.parametrize("variant", ["bias_relu", "bias_res_relu_planes", "bias_only"])
+def test_conv_fused_epilogue(variant):
+    """Bias / residual / ReLU folded into the tile kernel's epilogue, with the result also emitted
+    as the byte planes the next convolution reads: one quantisation of the fp32 value."""
+    import torch
+    from ngraph_python_b200 import lib
+    shape = (16, 8, 8, 128, 32, 3, 3, 1, 1)
+    Cc, H, W, N, K, R, S, pad, stride = shape
+    d, P, Q = _dims(lib, *shape)
+    rng = np.random.RandomState(3)
+    I = rng.randint(-20000, 20000, (Cc, H, W, N)).astype(np.int16)
+    F = rng.randint(-20000, 20000, (Cc, R, S, K)).astype(np.int16)
+    B = rng.randint(-20000, 20000, (K,)).astype(np.int16)
+    Rz = rng.randint(-20000, 20000, (K, P, Q, N)).astype(np.int16)
+    dec_i, dec_f, dec_b, dec_r = 12, 15, 13, 10
+    exact = co.conv_fprop(I, F, (pad, pad), (stride, stride), dtype=np.int64)
+    y = exact.astype(np.float64) * 2.0 ** -(dec_i + dec_f)
+    y = y.astype(np.float32) + B.astype(np.float32)[:, None, None, None] * np.float32(2.0 ** -dec_b)
+    use_res = variant == "bias_res_relu_planes"
+    if use_res:
+        y = y + Rz.astype(np.float32) * np.float32(2.0 ** -dec_r)
+    if variant != "bias_only":
+        y = np.maximum(y, 0)
+    from oracle import flex_oracle as fx
+    dec_o = fx.fit_dec(float(np.abs(y).max()))
+    exp = fx.quantize(y, dec_o).astype(np.int64)
+    ok, act_bytes, filt_bytes = lib.conv_planes_info(d, lib.CONV_FPROP)
+    assert ok
+    dI, dF, dB, dR = [torch.from_numpy(a).cuda() for a in (I, F, B, Rz)]
+    keep_a, act = _scratch(torch, 2 * act_bytes)
+    keep_f, filt = _scratch(torch, filt_bytes)
+    out = torch.zeros((K, P, Q, N), dtype=torch.int16, device="cuda")
+    out_plane_bytes = (K * P * Q * N + 1023) // 1024 * 1024
+    keep_o, oplanes = _scratch(torch, 2 * out_plane_bytes)
+    table = torch.tensor([[2.0 ** -dd, 2.0 ** dd] for dd in (dec_i, dec_f, dec_o, dec_b, dec_r)],
+                         dtype=torch.float32, device="cuda")
+    stats = torch.zeros((5,), dtype=torch.int32, device="cuda")
+    probe = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    raw = lib.raw()
+    lib.check(raw.b2_conv_split_activations(dI.data_ptr(), C.byref(d), 0, act, 0))
+    lib.check(raw.b2_conv_filter_planes(dF.data_ptr(), C.byref(d), 0, filt, 0))
+    epi = lib.ConvEpilogue()
+    epi.bias, epi.slot_bias = dB.data_ptr(), 3
+    epi.residual, epi.slot_residual = (dR.data_ptr(), 4) if use_res else (None, -1)
+    epi.relu = int(variant != "bias_only")
+    epi.write_int16 = 1
+    epi.out_planes, epi.plane_bytes = (oplanes, out_plane_bytes) if use_res else (None, 0)
+    for pr in (1, 0):
+        lib.check(raw.b2_conv_flex16_planes_fused(0, act, filt, out.data_ptr(), C.byref(d),
+                                                  table.data_ptr(), 0, 1, 2, C.byref(epi),
+                                                  stats.data_ptr(), probe.data_ptr(),
+                                                  status.data_ptr(), pr, 0))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+    got_max = np.array([int(probe.item())], dtype=np.uint32).view(np.float32)[0]
+    assert abs(got_max - float(np.abs(y).max())) <= 1e-5 * float(np.abs(y).max())
+    got = out.cpu().numpy().astype(np.int64)
+    # the integer sum is converted to fp32 once (the oracle above goes through float64): one step
+    assert np.abs(got - exp).max() <= 1
+    assert (got != exp).mean() < 0.01
+    assert int(stats[2].item()) == int(np.abs(got).max())
+    if use_res:
+        pl = keep_o.cpu().numpy()
+        off = oplanes - keep_o.data_ptr()
+        hi = pl[off:off + got.size].view(np.int8).astype(np.int64).reshape(got.shape)
+        lo = pl[off + out_plane_bytes:off + out_plane_bytes + got.size].astype(np.int64).reshape(got.shape)
+        assert np.array_equal(256 * hi + lo, got)
