@@ -242,7 +242,7 @@ __device__ __forceinline__ unsigned make_idesc_n(unsigned dfmt, unsigned afmt, u
 constexpr int kConvMaxStages = 8;
 constexpr int kConvThreads = 608;           // producer, MMA, sixteen epilogue warps, second MMA warp
 constexpr int kConvSmemMax = 232448;        // 227 KB: the most one CTA can have
-constexpr int kConvSmemFixed = 1024 /*alignment*/ + 512 /*barriers*/;
+constexpr int kConvSmemFixed = 1024 /*alignment*/ + 1024 /*barriers, bias*/;
 
 __global__ void __launch_bounds__(kConvThreads, 1)
 conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
@@ -256,21 +256,28 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     const int act_stage = p.kc_pad * 128;                      // bytes per plane per stage
     unsigned char* filt = smem;                                // [npanels][2*bn][128]
     unsigned char* ring = smem + p.npanels * panel_bytes;      // [nstages][2 planes][act_stage]
+    // one set of "stage filled" barriers per MMA-issuing warp: a waiter must see every phase of
+    // a barrier in turn (a parity wait cannot tell phase n from phase n+2), and an issuer only
+    // ever looks at the stages of its own tiles
     unsigned long long* full_bar =
-        (unsigned long long*)(ring + (size_t)p.nstages * 2 * act_stage);
-    unsigned long long* empty_bar = full_bar + kConvMaxStages;
+        (unsigned long long*)(ring + (size_t)p.nstages * 2 * act_stage);   // [2][kConvMaxStages]
+    unsigned long long* empty_bar = full_bar + 2 * kConvMaxStages;
     unsigned long long* tmem_full = empty_bar + kConvMaxStages;   // [4]
     unsigned long long* tmem_empty = tmem_full + 4;               // [4]
     unsigned long long* filt_bar = tmem_empty + 4;
     unsigned* tmem_holder = (unsigned*)(filt_bar + 1);
     int* fail_flag = (int*)(tmem_holder + 1);
+    float* bias_s = (float*)(fail_flag + 2);                      // [bn] bias of this CTA's channels, real values
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epi_w = 4 / p.nbuf;              // epilogue warps per lane quarter and accumulator set
 
     if (threadIdx.x == 0) {
         prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapB);
-        for (int s = 0; s < kConvMaxStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < kConvMaxStages; ++s) {
+            mbar_init(&full_bar[s], 1); mbar_init(&full_bar[kConvMaxStages + s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
         for (int b = 0; b < 4; ++b) {
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], 4 * epi_w);
@@ -280,6 +287,11 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(tmem_holder, p.tmem_cols);
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + bn) {
+        const int col = blockIdx.y * p.kt + (threadIdx.x - 64);
+        bias_s[threadIdx.x - 64] = (p.fused && p.bias && (threadIdx.x - 64) < p.kt && col < p.K)
+                                       ? (float)p.bias[col] * p.table[p.slot_bias].scale : 0.0f;
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -291,12 +303,14 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             mbar_expect_tx(filt_bar, p.npanels * panel_bytes);
             for (int j = 0; j < p.npanels; ++j)
                 tma_load_2d(filt + j * panel_bytes, &mapB, j * kKBytes, blockIdx.y * 2 * bn, filt_bar);
-            int s = 0;
+            int s = 0, ti = 0;
+            const int n_mma = p.nbuf >= 2 ? 2 : 1;
             unsigned empty_parity = 1;         // the first pass over the ring finds every stage free
             bool ok = true;
             const long long t_start = clock64();
             long long t_wait = 0;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
+                unsigned long long* fb = full_bar + (ti % n_mma) * kConvMaxStages;   // its consumer's
                 const int pq = tile / p.nblk, nb = tile - pq * p.nblk;
                 const int pp = pq / p.Q, q = pq - pp * p.Q;
                 const int n0 = nb * 128;
@@ -308,9 +322,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                     }
                     t_wait += clock64() - tw;
                     unsigned char* sa = ring + (size_t)s * 2 * act_stage;
-                    mbar_expect_tx(&full_bar[s], 2 * p.box_bytes);
-                    tma_load_4d(sa, &mapI0, n0, w0, h0, cc * p.cu, &full_bar[s]);
-                    tma_load_4d(sa + act_stage, &mapI1, n0, w0, h0, cc * p.cu, &full_bar[s]);
+                    mbar_expect_tx(&fb[s], 2 * p.box_bytes);
+                    tma_load_4d(sa, &mapI0, n0, w0, h0, cc * p.cu, &fb[s]);
+                    tma_load_4d(sa + act_stage, &mapI1, n0, w0, h0, cc * p.cu, &fb[s]);
                     if (++s == p.nstages) { s = 0; empty_parity ^= 1u; }
                 }
             }
@@ -345,18 +359,17 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const unsigned ring_lo = (smem_u32(ring) >> 4) & 0x3FFF;                  // MN-major: LBO field 0
             const unsigned stage_units = (unsigned)((2 * act_stage) >> 4), plane_units = (unsigned)(act_stage >> 4);
             int s = 0;
-            unsigned full_parity = 0, stage_lo = ring_lo;
+            unsigned phase_bits = 0, stage_lo = ring_lo;       // bit s: parity of my next phase of stage s
+            unsigned long long* fb = full_bar + mma_id * kConvMaxStages;
             const long long t_start = clock64();
             long long t_wait_e = 0, t_wait_f = 0, t_mma = 0, t_commit = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++ti) {
                 if (ti % n_mma != mma_id) {
-                    // the other issuing thread's tile: step over its stages, but see each of them
-                    // filled -- a waiter that skipped a phase of a barrier could take the phase
-                    // before it (same parity) for the one it waits for
-                    for (int cc = 0; cc < p.cchunks && ok; ++cc) {
-                        if (!mbar_wait(&full_bar[s], full_parity)) { atomicExch(fail_flag, 1); ok = false; }
+                    // the other issuing thread's tile: step over its stages (their "filled"
+                    // barriers are the other thread's own)
+                    for (int cc = 0; cc < p.cchunks; ++cc) {
                         stage_lo += stage_units;
-                        if (++s == p.nstages) { s = 0; full_parity ^= 1u; stage_lo = ring_lo; }
+                        if (++s == p.nstages) { s = 0; stage_lo = ring_lo; }
                     }
                     continue;
                 }
@@ -371,9 +384,10 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 int idx = 0;                                   // 32-byte column block of the filter planes
                 for (int cc = 0; cc < p.cchunks; ++cc) {
                     const long long tw2 = clock64();
-                    if (!mbar_wait(&full_bar[s], full_parity)) {
+                    if (!mbar_wait(&fb[s], (phase_bits >> s) & 1u)) {
                         atomicExch(fail_flag, 1); ok = false; break;
                     }
+                    phase_bits ^= 1u << s;
                     t_wait_f += clock64() - tw2;
                     tc_fence_after();
                     unsigned a_lo = stage_lo;
@@ -398,7 +412,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                     const long long tm1 = clock64();
                     tc_commit(&empty_bar[s]);
                     stage_lo += stage_units;
-                    if (++s == p.nstages) { s = 0; full_parity ^= 1u; stage_lo = ring_lo; }
+                    if (++s == p.nstages) { s = 0; stage_lo = ring_lo; }
                     t_mma += tm1 - tm0; t_commit += clock64() - tm1;
                 }
                 const long long tc0 = clock64();
@@ -426,7 +440,6 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                         (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
         const int sh = -ilogbf(f);
         const float f_conv = p.table[p.slotA].scale * p.table[p.slotB].scale;
-        const float s_bias = p.bias ? p.table[p.slot_bias].scale : 0.0f;
         const float s_res = p.residual ? p.table[p.slot_res].scale : 0.0f;
         const float q_out = p.table[p.slotC].inv_scale;
         float fmax_probe = 0.0f;
@@ -461,33 +474,51 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 if (!ok) continue;
                 if (p.fused) {
                     // fp32 epilogue: the exact integer sum scaled to a real value, bias and
-                    // residual added, ReLU, ONE quantisation with the output's exponent
+                    // residual added, ReLU, ONE quantisation with the output's exponent.  Loads
+                    // first, then arithmetic, then stores: sixteen independent chains.
                     const long long base = (long long)(ncol0 + c0) * p.ldc + row;
                     const int live = kt - c0;
+                    float y[16];
+                    if (p.residual) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            y[j] = j < live ? (float)p.residual[base + (long long)j * p.ldc] * s_res : 0.0f;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) y[j] = 0.0f;
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        if (j >= live) break;
                         const long long vv = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
                                              (long long)(int)ll[j] + fix;
-                        float y = __ll2float_rn(vv) * f_conv;
-                        if (p.bias) y += (float)p.bias[ncol0 + c0 + j] * s_bias;
-                        if (p.residual) y += (float)p.residual[base + (long long)j * p.ldc] * s_res;
-                        if (p.relu) y = fmaxf(y, 0.0f);
-                        if (p.probe) {
-                            fmax_probe = fmaxf(fmax_probe, fabsf(y));
-                            continue;
-                        }
-                        float t = y * q_out;
+                        y[j] += __ll2float_rn(vv) * f_conv + bias_s[c0 + j];
+                        if (p.relu) y[j] = fmaxf(y[j], 0.0f);
+                    }
+                    if (p.probe) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < live) fmax_probe = fmaxf(fmax_probe, fabsf(y[j]));
+                        continue;
+                    }
+                    int m[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float t = y[j] * q_out;
                         t = (t != t) ? 0.0f : t;
                         t = fminf(fmaxf(t, -32768.0f), 32767.0f);
-                        const int m = __float_as_int(t + 12582912.0f) - 0x4B400000;   // round to nearest even
-                        const int a = m < 0 ? -m : m;
-                        stat = a > stat ? a : stat;
-                        const long long at = base + (long long)j * p.ldc;
-                        if (p.write_i16) ((short*)p.O)[at] = (short)m;
-                        if (p.out_planes) {
-                            p.out_planes[at] = (unsigned char)(m >> 8);
-                            p.out_planes[p.out_plane_bytes + at] = (unsigned char)m;
+                        m[j] = __float_as_int(t + 12582912.0f) - 0x4B400000;   // round to nearest even
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j < live) {
+                            const int a = m[j] < 0 ? -m[j] : m[j];
+                            stat = a > stat ? a : stat;
+                            const long long at = base + (long long)j * p.ldc;
+                            if (p.write_i16) ((short*)p.O)[at] = (short)m[j];
+                            if (p.out_planes) {
+                                p.out_planes[at] = (unsigned char)(m[j] >> 8);
+                                p.out_planes[p.out_plane_bytes + at] = (unsigned char)m[j];
+                            }
                         }
                     }
                     continue;

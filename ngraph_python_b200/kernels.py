@@ -55,7 +55,11 @@ class _Step(object):
             call(1)
             t.kernel_launches += self.launches
             imax = int(t._probe64.item())
-            real = float(imax) * in_bufs[0].entry.scale * in_bufs[1].entry.scale
+            if getattr(self, "probe_is_float", False):
+                # fused epilogue: the kernel leaves the bit pattern of max |fp32 result|
+                real = float(np.array([imax & 0xffffffff], dtype=np.uint32).view(np.float32)[0])
+            else:
+                real = float(imax) * in_bufs[0].entry.scale * in_bufs[1].entry.scale
             dec = e.initialize_from_range(real)
             t._set_table_row(out_buf.slot_write, dec)
             t._stats[out_buf.slot_write:out_buf.slot_write + 1].zero_()
@@ -125,13 +129,37 @@ class _PlaneUser(object):
         else:
             self.refresh(t)
         slots = (t._slot_for_read(xbuf, self), t._slot_for_read(fbuf, self), ov.buffer.slot_write)
+        epi = getattr(self, "epi", None)
+        if epi is None:
+            def call(probe):
+                lib.check(raw.b2_conv_flex16_planes(
+                    self.conv_pass, xbuf.planes_ptr, self.filter_ptr, self._ptr(ov),
+                    C.byref(self.dims), t._table.data_ptr(), slots[0], slots[1], slots[2],
+                    t._stats.data_ptr(), t._probe64.data_ptr(), t._status.data_ptr(), probe, st))
+            self._flex_probe_then(t, ov.buffer, [xbuf, fbuf], call)
+            return
+        ce = lib.ConvEpilogue()
+        extra = self.in_views[2:]
+        k = 0
+        ce.bias, ce.slot_bias, ce.residual, ce.slot_residual = None, -1, None, -1
+        if epi.get("bias") is not None:
+            ce.bias, ce.slot_bias = self._ptr(extra[k]), t._slot_for_read(extra[k].buffer, self)
+            k += 1
+        if epi.get("residual") is not None:
+            ce.residual = self._ptr(extra[k])
+            ce.slot_residual = t._slot_for_read(extra[k].buffer, self)
+        ce.relu = int(bool(epi.get("relu")))
+        obuf = ov.buffer
+        ce.write_int16 = int(self.write_int16 or obuf.plane_bytes == 0)
+        ce.out_planes, ce.plane_bytes = (obuf.planes_ptr, obuf.plane_bytes) if obuf.plane_bytes else (None, 0)
 
         def call(probe):
-            lib.check(raw.b2_conv_flex16_planes(
+            lib.check(raw.b2_conv_flex16_planes_fused(
                 self.conv_pass, xbuf.planes_ptr, self.filter_ptr, self._ptr(ov),
                 C.byref(self.dims), t._table.data_ptr(), slots[0], slots[1], slots[2],
-                t._stats.data_ptr(), t._probe64.data_ptr(), t._status.data_ptr(), probe, st))
-        self._flex_probe_then(t, ov.buffer, [xbuf, fbuf], call)
+                C.byref(ce), t._stats.data_ptr(), t._probe64.data_ptr(), t._status.data_ptr(),
+                probe, st))
+        self._flex_probe_then(t, obuf, [xbuf, fbuf], call)
 
 
 class GemmStep(_Step):
@@ -194,10 +222,17 @@ class ConvStep(_PlaneUser, _Step):
     kind = "conv"
     launches = 3
 
-    def __init__(self, index, op, t):
+    def __init__(self, index, op, t, epilogue=None):
+        """epilogue (flex16 implicit-GEMM path only): dict(out=<op whose tensor the step writes>,
+        bias=<op or None>, residual=<op or None>, relu=bool) -- the elementwise tail of the layer,
+        evaluated in the tile kernel's epilogue."""
         super(ConvStep, self).__init__(index, op)
         inputs, filters = op.args
-        iv, fv, ov = t._view_of(inputs), t._view_of(filters), t._view_of(op)
+        self.epi = epilogue
+        out_op = epilogue["out"] if epilogue else op
+        iv, fv, ov = t._view_of(inputs), t._view_of(filters), t._view_of(out_op)
+        if epilogue and not ov.is_dense():
+            raise ValueError("fused convolution output must be a dense tensor")
         for v, what in ((iv, "input"), (fv, "filter")):
             if not v.is_dense():
                 raise ValueError("Unhandled op: convolution %s must be a dense tensor" % what)
@@ -229,6 +264,17 @@ class ConvStep(_PlaneUser, _Step):
         self.flex = t.flex
         self.scratch_bytes = lib.conv_fprop_scratch_bytes(self.flex, d) + 1024
         self._setup_planes(t, lib.CONV_FPROP, 0, 1)
+        if epilogue:
+            if not self.use_planes:
+                raise ValueError("a fused convolution epilogue needs the implicit-GEMM path")
+            self.probe_is_float = True
+            self.write_int16 = True          # the planner clears it when only planes are read
+            for key in ("bias", "residual"):
+                if epilogue.get(key) is not None:
+                    v = t._view_of(epilogue[key])
+                    if not v.is_dense():
+                        raise ValueError("fused convolution %s must be a dense tensor" % key)
+                    self.in_views.append(v)
 
     def launch(self, t):
         if self.use_planes:

@@ -314,6 +314,8 @@ class _Planner(object):
         self.group_of = {}        # EW/reduction op -> EwGroup
         self.consumers = collections.defaultdict(list)
         self.written_buffers = []
+        self.conv_tails = {}       # ConvolutionOp -> dict(out, bias, residual, relu, ops)
+        self.conv_tail_of = {}     # absorbed elementwise op -> its ConvolutionOp
         self.deferred = []         # re-quantisations of reduced tensors, placed at first use
         self.arg_override = {}     # op -> value args after register forwarding
         self.last_assign = {}      # persistent tensor -> the AssignOp that last wrote all of it
@@ -382,7 +384,17 @@ class _Planner(object):
         for buf in self.t._buffers.values():
             buf.last_write_step = -1
             buf.last_read_step = -1
+        self._find_conv_tails(ordered)
         for op in ordered:
+            if op in self.conv_tail_of:
+                # part of a convolution layer's elementwise tail: the layer is placed, as one step,
+                # where its last op stands (every operand of the tail exists by then)
+                conv = self.conv_tail_of[op]
+                if self.conv_tails[conv]["out"] is op:
+                    self._place_other(conv)
+                continue
+            if isinstance(op, ConvolutionOp) and op in self.conv_tails:
+                continue
             if isinstance(op, (ElementWiseOp, ReductionOp, AssignOp)):
                 self._place_ew(op)
             elif isinstance(op, AllReduceOp):
@@ -594,6 +606,66 @@ class _Planner(object):
             # bucket overlapped with the rest of back-propagation
             self.deferred.append(requant)
 
+    def _find_conv_tails(self, ordered):
+        """flex16, implicit-GEMM convolutions: folds `+ bias[channel]`, `+ residual` and
+        `maximum(., 0)` that follow a convolution -- each the only reader of the value before it
+        -- into the convolution step (evaluated in the tile kernel's epilogue; the reference's
+        kernels carry bias / relu flags for the same purpose, ngraph/transformers/gpu/conv.py)."""
+        t = self.t
+        if not (t.flex and t.fuse and t.fuse_conv_tail):
+            return
+        for conv in ordered:
+            if not isinstance(conv, ConvolutionOp):
+                continue
+            try:
+                ok = lib.conv_planes_info(kernels._conv_dims_of(conv, t), lib.CONV_FPROP)[0]
+            except Exception:
+                ok = False
+            if not ok:
+                continue
+            info = dict(out=None, bias=None, residual=None, relu=False, ops=[])
+            cur = conv
+            chan = conv.axes[0].length
+            while True:
+                readers = [r for r in self.consumers.get(cur, ()) if not isinstance(r, ViewOp)]
+                if len(readers) != 1 or cur in self.returned:
+                    break
+                nxt = readers[0]
+                if not isinstance(nxt, ElementWiseOp) or len(nxt.args) != 2:
+                    break
+                if nxt in self.conv_tail_of:
+                    break        # the sum of two branches belongs to one of them only
+                mine = [i for i, a in enumerate(nxt.args) if self._base_tensor(a)[0] is cur]
+                if len(mine) != 1:
+                    break
+                other = nxt.args[1 - mine[0]]
+                obase, ochain = self._base_tensor(other)
+                if tuple(nxt.axes.lengths) != tuple(conv.axes.lengths):
+                    break
+                if nxt.opname == "add" and not info["relu"]:
+                    is_bias = (len(obase.axes) == 1 and obase.axes[0].length == chan and
+                               obase.axes[0] == nxt.axes[0] and not self._is_scalar_const(obase))
+                    same = (not ochain and tuple(obase.axes.lengths) == tuple(nxt.axes.lengths)
+                            and obase.axes == nxt.axes)
+                    if is_bias and info["bias"] is None and info["residual"] is None:
+                        info["bias"] = obase
+                    elif same and info["residual"] is None and not isinstance(obase, AssignableTensorOp):
+                        info["residual"] = obase
+                    else:
+                        break
+                elif nxt.opname == "maximum" and not info["relu"] and self._is_scalar_const(obase) \
+                        and float(np.asarray(obase.initial_value)) == 0.0:
+                    info["relu"] = True
+                else:
+                    break
+                info["ops"].append(nxt)
+                cur = nxt
+            if info["ops"]:
+                info["out"] = cur
+                self.conv_tails[conv] = info
+                for o in info["ops"]:
+                    self.conv_tail_of[o] = conv
+
     def _place_deferred_for(self, args):
         for a in args:
             base, _ = self._base_tensor(a)
@@ -603,12 +675,21 @@ class _Planner(object):
 
     def _place_other(self, op):
         """Dense contractions and pooling: one step each, never fused with neighbours."""
-        self._place_deferred_for(op.args)
+        tail = self.conv_tails.get(op) if isinstance(op, ConvolutionOp) else None
+        reads = list(op.args)
+        if tail:
+            reads += [x for x in (tail["bias"], tail["residual"]) if x is not None]
+        self._place_deferred_for(reads)
         index = self._new_step_index()
         if isinstance(op, DotOp):
             step = kernels.GemmStep(index, op, self.t)
         elif isinstance(op, ConvolutionOp):
-            step = kernels.ConvStep(index, op, self.t)
+            step = kernels.ConvStep(index, op, self.t, epilogue=tail)
+            if tail:
+                step.out_op = tail["out"]
+                self.producer[tail["out"]] = index
+                for o in tail["ops"]:
+                    self.producer[o] = index
         elif isinstance(op, bprop_conv):
             step = kernels.ConvBpropStep(index, op, self.t)
         elif isinstance(op, update_conv):
@@ -619,7 +700,7 @@ class _Planner(object):
             raise ValueError("Unhandled op: {}".format(op))
         # the step must come after everything its arguments depend on; steps are appended in
         # dependency order, so only in-place writes of persistent tensors need recording
-        for a in op.args:
+        for a in reads:
             base, _ = self._base_tensor(a)
             if base in self.group_of:
                 self.group_of[base].stored.add(base)
@@ -641,7 +722,7 @@ class _Planner(object):
         (then the int16 copy need not be written at all)."""
         if m in self.returned:
             return False
-        readers = self.consumers.get(m, ())
+        readers = [r for r in self.consumers.get(m, ()) if not isinstance(r, ViewOp)]
         if not readers:
             return False
         buf = self.t._view_of(m).buffer
@@ -685,6 +766,13 @@ class _Planner(object):
     def finalize_step(self, step):
         if step.kind == "ew":
             self._finalize_ew(step)
+        elif getattr(step, "epi", None):
+            # a fused convolution writes the byte planes of its result itself when the next
+            # convolution wants them, and the int16 tensor only if someone reads that
+            buf = step.out_views[0].buffer
+            if buf.plane_bytes > 0:
+                buf.planes_by_producer = True
+                step.write_int16 = not self._only_plane_readers(step.out_op)
 
     def _finalize_ew(self, step):
         t = self.t
@@ -863,6 +951,8 @@ class B200Transformer(object):
         # fuse=False launches one kernel per op, as the reference does; in flex mode that also
         # reproduces the reference's per-op re-quantisation of every intermediate tensor
         self.fuse = bool(fuse)
+        # fold bias / residual / ReLU after a convolution into the convolution step (flex16)
+        self.fuse_conv_tail = bool(kwargs.pop("fuse_conv_tail", True))
         self.flex = bool(flex)
         self.fixed_point = bool(fixed_point)
         self.flex_manager = flexmod.FlexManager(fixed_point=fixed_point, verbose=flex_verbose)

@@ -112,3 +112,30 @@ def test_reduction_reads_assignment_from_registers():
     np.testing.assert_allclose(got, (2 * xv).max(axis=0), rtol=1e-6)
     np.testing.assert_allclose(kept, 2 * xv, rtol=1e-6)
     t.close()
+
+
+def test_conv_tails_fused_into_the_convolution_step():
+    """Batch 128 takes the implicit-GEMM kernel, where `+ bias`, `+ residual` and ReLU after a
+    convolution run in its epilogue (one launch per layer).  The result must agree with the
+    unfused plan and with the numpy evaluation of the same graph, at flex16 tolerance."""
+    from tests.mirror_interp import Interp
+    res = {}
+    for tail in (True, False):
+        outs, params, vals = cases.resnet20(ng, n=128, hw=16, blocks=1)
+        t = ng.transformers.allocate_transformer("b200", flex=True, fuse_conv_tail=tail)
+        comp = t.computation(outs, *params)
+        res[tail] = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
+        kinds = [s.kind for s in comp.steps]
+        if tail:
+            assert kinds.count("ew") <= 4 and kinds.count("conv") == 10
+            assert all(getattr(s, "epi", None) for s in comp.steps if s.kind == "conv")
+        else:
+            assert kinds.count("ew") >= 10
+        t.close()
+    outs, params, vals = cases.resnet20(ng, n=128, hw=16, blocks=1)
+    exp = Interp().run(outs, dict(zip(params, vals)))
+    for rep in range(2):
+        for k in range(2):
+            atol, rtol = flex_tolerance(exp[k])
+            np.testing.assert_allclose(res[True][rep][k], exp[k], rtol=rtol, atol=4 * atol)
+            np.testing.assert_allclose(res[True][rep][k], res[False][rep][k], rtol=rtol, atol=4 * atol)
