@@ -229,6 +229,14 @@ __device__ __forceinline__ unsigned tmem_ld1(unsigned taddr) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
     return r;
 }
+// 8 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld8(unsigned taddr, unsigned* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
 }
@@ -464,6 +472,70 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const int s_lo = (int)tmem_ld1(lane_addr + 2 * bn + p.kt);
             tmem_ld_wait();
             const long long fix = 128LL * (256LL * (long long)s_hi + (long long)s_lo);
+            if (p.fused) {
+                // fp32 epilogue: the exact integer sum scaled to a real value, bias and residual
+                // added, ReLU, ONE quantisation with the output's exponent.  Eight columns at a
+                // time (the register budget of a 608-thread CTA), loads first, then arithmetic,
+                // then stores: eight independent chains.
+                for (int c0 = part * 16; c0 < kt; c0 += 16 * epi_w) {
+#pragma unroll
+                    for (int h8 = 0; h8 < 16; h8 += 8) {
+                        const int cc0 = c0 + h8;
+                        if (cc0 >= kt) break;
+                        unsigned hh[8], xx[8], ll[8];
+                        tmem_ld8(lane_addr + cc0, hh);
+                        tmem_ld8(lane_addr + bn + cc0, xx);
+                        tmem_ld8(lane_addr + 2 * bn + cc0, ll);
+                        const long long base = (long long)(ncol0 + cc0) * p.ldc + row;
+                        const int live = kt - cc0;
+                        float y[8];
+                        if (p.residual) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                y[j] = j < live ? (float)p.residual[base + (long long)j * p.ldc] * s_res : 0.0f;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) y[j] = 0.0f;
+                        }
+                        tmem_ld_wait();
+                        if (!ok) continue;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const long long vv = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
+                                                 (long long)(int)ll[j] + fix;
+                            y[j] += __ll2float_rn(vv) * f_conv + bias_s[cc0 + j];
+                            if (p.relu) y[j] = fmaxf(y[j], 0.0f);
+                        }
+                        if (p.probe) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (j < live) fmax_probe = fmaxf(fmax_probe, fabsf(y[j]));
+                            continue;
+                        }
+                        int m[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float t = y[j] * q_out;
+                            t = (t != t) ? 0.0f : t;
+                            t = fminf(fmaxf(t, -32768.0f), 32767.0f);
+                            m[j] = __float_as_int(t + 12582912.0f) - 0x4B400000;   // round to nearest even
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (j < live) {
+                                const int a = m[j] < 0 ? -m[j] : m[j];
+                                stat = a > stat ? a : stat;
+                                const long long at = base + (long long)j * p.ldc;
+                                if (p.write_i16) ((short*)p.O)[at] = (short)m[j];
+                                if (p.out_planes) {
+                                    p.out_planes[at] = (unsigned char)(m[j] >> 8);
+                                    p.out_planes[p.out_plane_bytes + at] = (unsigned char)m[j];
+                                }
+                            }
+                        }
+                    }
+                }
+            } else
             for (int c0 = part * 16; c0 < kt; c0 += 16 * epi_w) {
                 unsigned hh[16], xx[16], ll[16];
                 tmem_ld16(lane_addr + c0, hh);
@@ -472,57 +544,6 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 tmem_ld_wait();
                 t_ld += clock64() - te0;
                 if (!ok) continue;
-                if (p.fused) {
-                    // fp32 epilogue: the exact integer sum scaled to a real value, bias and
-                    // residual added, ReLU, ONE quantisation with the output's exponent.  Loads
-                    // first, then arithmetic, then stores: sixteen independent chains.
-                    const long long base = (long long)(ncol0 + c0) * p.ldc + row;
-                    const int live = kt - c0;
-                    float y[16];
-                    if (p.residual) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            y[j] = j < live ? (float)p.residual[base + (long long)j * p.ldc] * s_res : 0.0f;
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) y[j] = 0.0f;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const long long vv = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
-                                             (long long)(int)ll[j] + fix;
-                        y[j] += __ll2float_rn(vv) * f_conv + bias_s[c0 + j];
-                        if (p.relu) y[j] = fmaxf(y[j], 0.0f);
-                    }
-                    if (p.probe) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (j < live) fmax_probe = fmaxf(fmax_probe, fabsf(y[j]));
-                        continue;
-                    }
-                    int m[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float t = y[j] * q_out;
-                        t = (t != t) ? 0.0f : t;
-                        t = fminf(fmaxf(t, -32768.0f), 32767.0f);
-                        m[j] = __float_as_int(t + 12582912.0f) - 0x4B400000;   // round to nearest even
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (j < live) {
-                            const int a = m[j] < 0 ? -m[j] : m[j];
-                            stat = a > stat ? a : stat;
-                            const long long at = base + (long long)j * p.ldc;
-                            if (p.write_i16) ((short*)p.O)[at] = (short)m[j];
-                            if (p.out_planes) {
-                                p.out_planes[at] = (unsigned char)(m[j] >> 8);
-                                p.out_planes[p.out_plane_bytes + at] = (unsigned char)m[j];
-                            }
-                        }
-                    }
-                    continue;
-                }
                 short* out = (short*)p.O + (long long)(ncol0 + c0) * p.ldc + row;
                 long long v[16];
 #pragma unroll
