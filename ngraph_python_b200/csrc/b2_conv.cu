@@ -477,11 +477,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 // added, ReLU, ONE quantisation with the output's exponent.  Eight columns at a
                 // time (the register budget of a 608-thread CTA), loads first, then arithmetic,
                 // then stores: eight independent chains.
-                for (int c0 = part * 16; c0 < kt; c0 += 16 * epi_w) {
-#pragma unroll
-                    for (int h8 = 0; h8 < 16; h8 += 8) {
-                        const int cc0 = c0 + h8;
-                        if (cc0 >= kt) break;
+                {
+                    // the warps that share a lane quarter take the 8-column pieces in turn
+                    for (int cc0 = part * 8; cc0 < kt; cc0 += 8 * epi_w) {
                         unsigned hh[8], xx[8], ll[8];
                         tmem_ld8(lane_addr + cc0, hh);
                         tmem_ld8(lane_addr + bn + cc0, xx);
