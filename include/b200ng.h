@@ -238,7 +238,7 @@ int b2_conv_flex16_planes(int32_t pass, const void* act_planes, const void* filt
                           int32_t slotX, int32_t slotF, int32_t slotOut, int32_t* stats,
                           uint64_t* probe_out, int32_t* status, int32_t probe, void* stream);
 /* The same with the elementwise tail of a convolution layer folded into the tile kernel's
- * epilogue: y = relu?(conv + bias[k] + residual) evaluated in fp32 from the exact integer sum,
+ * epilogue: y = relu?(conv + bias[k] + residual) evaluated in fp32 from the exact integer sums,
  * quantised ONCE with the output's exponent (slotOut), stored as int16 (write_int16) and / or as
  * the byte planes the next convolution reads (out_planes, low plane plane_bytes further).  bias:
  * int16 per output channel; residual: int16 tensor in the output's K,P,Q,N layout; NULL = absent.

@@ -472,6 +472,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const int s_lo = (int)tmem_ld1(lane_addr + 2 * bn + p.kt);
             tmem_ld_wait();
             const long long fix = 128LL * (256LL * (long long)s_hi + (long long)s_lo);
+            const float fixf = (float)fix;
             if (p.fused) {
                 // fp32 epilogue: the exact integer sum scaled to a real value, bias and residual
                 // added, ReLU, ONE quantisation with the output's exponent.  Eight columns at a
@@ -499,9 +500,11 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                         if (!ok) continue;
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const long long vv = ((long long)(int)hh[j] << 16) + ((long long)(int)xx[j] << 8) +
-                                                 (long long)(int)ll[j] + fix;
-                            y[j] += __ll2float_rn(vv) * f_conv + bias_s[cc0 + j];
+                            // three exact-or-correctly-rounded conversions instead of a 64-bit sum:
+                            // the fp32 result is quantised to 16 bits right after
+                            const float acc = fmaf((float)(int)hh[j], 65536.0f,
+                                                   fmaf((float)(int)xx[j], 256.0f, (float)(int)ll[j] + fixf));
+                            y[j] += fmaf(acc, f_conv, bias_s[cc0 + j]);
                             if (p.relu) y[j] = fmaxf(y[j], 0.0f);
                         }
                         if (p.probe) {
