@@ -139,3 +139,40 @@ def test_conv_tails_fused_into_the_convolution_step():
             atol, rtol = flex_tolerance(exp[k])
             np.testing.assert_allclose(res[True][rep][k], exp[k], rtol=rtol, atol=4 * atol)
             np.testing.assert_allclose(res[True][rep][k], res[False][rep][k], rtol=rtol, atol=4 * atol)
+
+
+def test_cached_filter_planes_follow_the_filters():
+    """The convolution step keeps the byte planes of its filters until the filters change.  Another
+    computation of the same transformer overwrites the filters; the next call -- step by step and
+    as a replayed CUDA graph -- must see the new ones."""
+    from oracle import conv_oracle as co
+    Cc, K, H, W, N = 16, 16, 6, 6, 128
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    ax_i = [ax(Cc, "C"), ax(1, "D"), ax(H, "H"), ax(W, "W"), ax(N, "N")]
+    ax_f = [ax_i[0], ax(1, "T"), ax(3, "R"), ax(3, "S"), ax(K, "K")]
+    ax_o = [ax_f[4], ax(1, "M"), ax(H, "P"), ax(W, "Q"), ax_i[4]]
+    rng = np.random.RandomState(9)
+    f0 = (rng.standard_normal((Cc, 1, 3, 3, K)) * 0.2).astype(np.float32)
+    f1 = (rng.standard_normal((Cc, 1, 3, 3, K)) * 0.2).astype(np.float32)
+    xv = rng.standard_normal((Cc, 1, H, W, N)).astype(np.float32)
+    params = dict(pad_d=0, pad_h=1, pad_w=1, str_d=1, str_h=1, str_w=1, dil_d=1, dil_h=1, dil_w=1)
+    for graph in (False, True):
+        t = ng.transformers.allocate_transformer("b200", flex=True)
+        x = ng.placeholder(ax_i)
+        filt = ng.variable(ax_f, initial_value=f0)
+        newf = ng.placeholder(ax_f)
+        conv = t.computation(ng.convolution(params, x, filt, axes=ax_o), x)
+        setf = t.computation(ng.assign(filt, newf), newf)
+        a = np.array(conv(xv), copy=True)
+        conv(xv)
+        if graph:
+            conv.capture()
+            conv(xv)
+        setf(f1)
+        b = np.array(conv(xv), copy=True)
+        for got, f in ((a, f0), (b, f1)):
+            exp = co.conv_fprop(xv[:, 0], f[:, 0], (1, 1), (1, 1))
+            tol = float(np.abs(exp).max()) * 2.0 ** -12
+            assert np.abs(got[:, 0] - exp).max() <= 4 * tol
+        assert np.abs(a - b).max() > 0.1
+        t.close()
