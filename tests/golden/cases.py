@@ -287,7 +287,7 @@ def resnet8_small(ng):
     return resnet20(ng, n=32, hw=16, blocks=1)
 
 
-def mlp_train_step(ng, global_n=128, shard=None, dims=(64, 48, 32, 10), lr=0.05):
+def mlp_train_step(ng, global_n=128, shard=None, dims=(64, 48, 32, 10), lr=0.05, digest=False):
     """One data-parallel SGD step of a 3-layer MLP with softmax cross-entropy, gradients written
     out by hand (BASELINE configs 1 and 5 in miniature).  Every replica sees `shard = (rank,
     world)` of the global batch, scales its gradients by 1/global batch (the reference's optimizer
@@ -340,6 +340,10 @@ def mlp_train_step(ng, global_n=128, shard=None, dims=(64, 48, 32, 10), lr=0.05)
         updates.append(ng.assign(w, w - lr * allreduce(g)))
     step = ng.sequential(updates + [loss])
     outs = [step, W1, W2, W3, b3]
+    if digest:
+        # the biases of the first layers instead of their large weight matrices (their gradients
+        # pass through the same back-propagation; keeps the fixture small)
+        outs = [step, b1, b2, W3, b3]
     rng = _rng(3)
     xs = rng.uniform(0, 1, (Fd, global_n)).astype(np.float32)
     labels = np.eye(Yd, dtype=np.float32)[rng.randint(0, Yd, global_n)].T.copy()
@@ -501,8 +505,15 @@ def resnet_train_step(ng, global_n=32, shard=None, hw=16, widths=(16, 32, 64), b
     return outs, [x, t], [np.ascontiguousarray(xs[..., lo:hi]), np.ascontiguousarray(labels[:, lo:hi])]
 
 
+def mlp_c1_train_step(ng, shard=None):
+    """BASELINE config 1 at full size: 784-512-512-10, batch 128, one SGD step (lr 0.01)."""
+    return mlp_train_step(ng, global_n=128, shard=shard, dims=(784, 512, 512, 10), lr=0.01,
+                          digest=True)
+
+
 CASES = {
     "mlp_train_step": mlp_train_step,
+    "mlp_c1_train_step": mlp_c1_train_step,
     "resnet_train_step": resnet_train_step,
     "conv_basic": conv_basic,
     "conv_stride2_1x1": conv_stride2_1x1,
@@ -523,4 +534,5 @@ CASES = {
     "assign_sequence": assign_sequence,
 }
 # cases evaluated twice in a row (state carried by variables)
-REPEAT = {"assign_sequence": 2, "mlp_train_step": 2, "resnet_train_step": 2}
+REPEAT = {"assign_sequence": 2, "mlp_train_step": 2, "mlp_c1_train_step": 2,
+          "resnet_train_step": 2}

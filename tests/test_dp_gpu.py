@@ -24,7 +24,7 @@ def _check(results, fix, rtol=1e-4, atol=2e-5):
                                        err_msg="output %d call %d" % (k, rep))
 
 
-TRAIN_CASES = ["mlp_train_step", "resnet_train_step"]
+TRAIN_CASES = ["mlp_train_step", "mlp_c1_train_step", "resnet_train_step"]
 
 
 @pytest.mark.parametrize("case", TRAIN_CASES)
