@@ -307,10 +307,50 @@ def run_resnet(args, rank, world, torch, dist, local):
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop()
+    alone_ms = nocomm_ms = 0.0
+    exchanged = []
+    if dist is not None and t._allreduce is not None:
+        # How much of the exchange the step hides.  (1) what one step exchanges, (2) the same
+        # collectives alone, back to back, (3) the step with the collectives left out; exposed
+        # time = step - step without exchange.  Done last: (3) lets the replicas drift apart.
+        ar, real = t._allreduce, t._allreduce.comm
+
+        class Spy(object):
+            rank, size = real.rank, real.size
+
+            def all_reduce_async(self, flat, reduce_func="sum"):
+                exchanged.append(int(flat.numel()))
+                return real.all_reduce_async(flat, reduce_func)
+        ar.comm = Spy()
+        step_resident()
+        torch.cuda.synchronize()
+        per_step = list(exchanged)
+        bufs = [torch.zeros(c, dtype=torch.float32, device="cuda") for c in per_step]
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for timed in (False, True):
+            barrier()
+            a0.record(stream)
+            for _ in range(20 if timed else 3):
+                for b in bufs:
+                    dist.all_reduce(b)
+            a1.record(stream)
+            barrier()
+        alone_ms = a0.elapsed_time(a1) / 20
+        ar.comm = SingleProcessComm()
+        for timed in (False, True):
+            barrier()
+            a0.record(stream)
+            for _ in range(args.steps if timed else 3):
+                step_resident()
+            a1.record(stream)
+            barrier()
+        nocomm_ms = a0.elapsed_time(a1) / args.steps
+        ar.comm = real
+        exchanged = per_step
     if dist is not None:
-        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        tt = torch.tensor([dev_ms, e2e_ms, alone_ms, nocomm_ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
+        dev_ms, e2e_ms, alone_ms, nocomm_ms = [float(v) for v in tt.tolist()]
     if rank != 0:
         return None
     ms_step = dev_ms / args.steps
@@ -455,10 +495,50 @@ def run_resnet_train(args, rank, world, torch, dist, local):
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop()
+    alone_ms = nocomm_ms = 0.0
+    exchanged = []
+    if dist is not None and t._allreduce is not None:
+        # How much of the exchange the step hides.  (1) what one step exchanges, (2) the same
+        # collectives alone, back to back, (3) the step with the collectives left out; exposed
+        # time = step - step without exchange.  Done last: (3) lets the replicas drift apart.
+        ar, real = t._allreduce, t._allreduce.comm
+
+        class Spy(object):
+            rank, size = real.rank, real.size
+
+            def all_reduce_async(self, flat, reduce_func="sum"):
+                exchanged.append(int(flat.numel()))
+                return real.all_reduce_async(flat, reduce_func)
+        ar.comm = Spy()
+        step_resident()
+        torch.cuda.synchronize()
+        per_step = list(exchanged)
+        bufs = [torch.zeros(c, dtype=torch.float32, device="cuda") for c in per_step]
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for timed in (False, True):
+            barrier()
+            a0.record(stream)
+            for _ in range(20 if timed else 3):
+                for b in bufs:
+                    dist.all_reduce(b)
+            a1.record(stream)
+            barrier()
+        alone_ms = a0.elapsed_time(a1) / 20
+        ar.comm = SingleProcessComm()
+        for timed in (False, True):
+            barrier()
+            a0.record(stream)
+            for _ in range(args.steps if timed else 3):
+                step_resident()
+            a1.record(stream)
+            barrier()
+        nocomm_ms = a0.elapsed_time(a1) / args.steps
+        ar.comm = real
+        exchanged = per_step
     if dist is not None:
-        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        tt = torch.tensor([dev_ms, e2e_ms, alone_ms, nocomm_ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
+        dev_ms, e2e_ms, alone_ms, nocomm_ms = [float(v) for v in tt.tolist()]
     if rank != 0:
         return None
     ms_step = dev_ms / args.steps
@@ -497,6 +577,13 @@ def run_resnet_train(args, rank, world, torch, dist, local):
         "allreduce_algorithmic_bytes_per_gpu": int(2 * (world - 1) / world * TRAIN_PARAM_BYTES),
         "loss_first_steps": [round(v, 5) for v in losses], "loss_last": round(float(last[0]), 5),
     }
+    if exchanged:
+        exposed = max(0.0, ms_step - nocomm_ms)
+        line["allreduce"] = {
+            "collectives_per_step": len(exchanged), "bytes_per_step": int(4 * sum(exchanged)),
+            "alone_ms": round(alone_ms, 4), "step_without_exchange_ms": round(nocomm_ms, 4),
+            "exposed_ms": round(exposed, 4),
+            "overlap_frac": round(min(1.0, max(0.0, 1.0 - exposed / alone_ms)), 3) if alone_ms > 0 else None}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = train_cpu_baseline()
     return line
@@ -583,10 +670,50 @@ def run_gemm(args, rank, world, torch, dist, local):
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop()
+    alone_ms = nocomm_ms = 0.0
+    exchanged = []
+    if dist is not None and t._allreduce is not None:
+        # How much of the exchange the step hides.  (1) what one step exchanges, (2) the same
+        # collectives alone, back to back, (3) the step with the collectives left out; exposed
+        # time = step - step without exchange.  Done last: (3) lets the replicas drift apart.
+        ar, real = t._allreduce, t._allreduce.comm
+
+        class Spy(object):
+            rank, size = real.rank, real.size
+
+            def all_reduce_async(self, flat, reduce_func="sum"):
+                exchanged.append(int(flat.numel()))
+                return real.all_reduce_async(flat, reduce_func)
+        ar.comm = Spy()
+        step_resident()
+        torch.cuda.synchronize()
+        per_step = list(exchanged)
+        bufs = [torch.zeros(c, dtype=torch.float32, device="cuda") for c in per_step]
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for timed in (False, True):
+            barrier()
+            a0.record(stream)
+            for _ in range(20 if timed else 3):
+                for b in bufs:
+                    dist.all_reduce(b)
+            a1.record(stream)
+            barrier()
+        alone_ms = a0.elapsed_time(a1) / 20
+        ar.comm = SingleProcessComm()
+        for timed in (False, True):
+            barrier()
+            a0.record(stream)
+            for _ in range(args.steps if timed else 3):
+                step_resident()
+            a1.record(stream)
+            barrier()
+        nocomm_ms = a0.elapsed_time(a1) / args.steps
+        ar.comm = real
+        exchanged = per_step
     if dist is not None:
-        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        tt = torch.tensor([dev_ms, e2e_ms, alone_ms, nocomm_ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
+        dev_ms, e2e_ms, alone_ms, nocomm_ms = [float(v) for v in tt.tolist()]
     if rank != 0:
         return None
     ms_step = dev_ms / args.steps

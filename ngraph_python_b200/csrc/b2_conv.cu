@@ -298,7 +298,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     if (threadIdx.x >= 64 && threadIdx.x < 64 + bn) {
         const int col = blockIdx.y * p.kt + (threadIdx.x - 64);
         bias_s[threadIdx.x - 64] = (p.fused && p.bias && (threadIdx.x - 64) < p.kt && col < p.K)
-                                       ? (float)p.bias[col] * p.table[p.slot_bias].scale : 0.0f;
+                                       ? (float)p.bias[col] * p.table[p.slot_bias].scale *
+                                             (p.probe ? 1.0f : p.table[p.slotC].inv_scale)
+                                       : 0.0f;
     }
     tc_fence_before();
     __syncthreads();
@@ -447,10 +449,12 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
                         (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
         const int sh = -ilogbf(f);
-        const float f_conv = p.table[p.slotA].scale * p.table[p.slotB].scale;
-        const float s_res = p.residual ? p.table[p.slot_res].scale : 0.0f;
-        const float q_out = p.table[p.slotC].inv_scale;
-        float fmax_probe = 0.0f;
+        // fused epilogue: every term carries the output's 1/step (a power of two, so the scaled
+        // sum is the real-valued sum times that power, bit for bit); the probe keeps real values
+        const float q_out = p.probe ? 1.0f : p.table[p.slotC].inv_scale;
+        const float f_conv = p.table[p.slotA].scale * p.table[p.slotB].scale * q_out;
+        const float s_res = p.residual ? p.table[p.slot_res].scale * q_out : 0.0f;
+        float fmax_probe = 0.0f, fstat = 0.0f;
         const bool fast = sh >= 1 && sh <= 31;
         const unsigned rmask = fast ? (1u << sh) - 1u : 0u, rhalf = fast ? 1u << (sh - 1) : 0u;
         int ti = 0;
@@ -460,11 +464,20 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++ti) {
             const int buf = ti % p.nbuf;
             if (buf != set) continue;
+            const long long row = (long long)tile * 128 + quarter * 32 + lane;   // (pq*N + n)
+            // the residual of the first piece is fetched while the tile is still being multiplied
+            short rz[8];
+            if (p.fused && p.residual) {
+                const int cc0 = part * 8;
+                const long long base = (long long)(ncol0 + cc0) * p.ldc + row;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    rz[j] = cc0 + j < kt ? p.residual[base + (long long)j * p.ldc] : (short)0;
+            }
             const long long tw = clock64();
             if (ok && !mbar_wait_relaxed(&tmem_full[buf], (ti / p.nbuf) & 1)) { atomicExch(fail_flag, 1); ok = false; }
             t_wait += clock64() - tw;
             tc_fence_after();
-            const long long row = (long long)tile * 128 + quarter * 32 + lane;   // (pq*N + n)
             const unsigned lane_addr = tmem_base + buf * acc_cols + ((unsigned)(quarter * 32) << 16);
             // 128 * (sum of this row's activations), from the extra column p.kt
             const long long te0 = clock64();
@@ -490,8 +503,15 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                         float y[8];
                         if (p.residual) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                y[j] = j < live ? (float)p.residual[base + (long long)j * p.ldc] * s_res : 0.0f;
+                            for (int j = 0; j < 8; ++j) y[j] = (float)rz[j] * s_res;
+                            // and the next piece's, one piece ahead of its use
+                            const int nx = cc0 + 8 * epi_w;
+                            if (nx < kt) {
+                                const long long nbase = (long long)(ncol0 + nx) * p.ldc + row;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    rz[j] = nx + j < kt ? p.residual[nbase + (long long)j * p.ldc] : (short)0;
+                            }
                         } else {
 #pragma unroll
                             for (int j = 0; j < 8; ++j) y[j] = 0.0f;
@@ -505,7 +525,13 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                             const float acc = fmaf((float)(int)hh[j], 65536.0f,
                                                    fmaf((float)(int)xx[j], 256.0f, (float)(int)ll[j] + fixf));
                             y[j] += fmaf(acc, f_conv, bias_s[cc0 + j]);
-                            if (p.relu) y[j] = fmaxf(y[j], 0.0f);
+                        }
+                        if (p.relu) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) y[j] = fmaxf(y[j], 0.0f);      // also NaN -> 0
+                        } else if (!p.probe) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) y[j] = (y[j] != y[j]) ? 0.0f : fmaxf(y[j], -32768.0f);
                         }
                         if (p.probe) {
 #pragma unroll
@@ -513,24 +539,37 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                                 if (j < live) fmax_probe = fmaxf(fmax_probe, fabsf(y[j]));
                             continue;
                         }
+                        // y is already in units of the output's step (see f_conv): clamp, round to
+                        // nearest even by the magic-number add; the low 16 bits of the sum are the
+                        // mantissa, so the bytes are stored straight from it
                         int m[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            float t = y[j] * q_out;
-                            t = (t != t) ? 0.0f : t;
-                            t = fminf(fmaxf(t, -32768.0f), 32767.0f);
-                            m[j] = __float_as_int(t + 12582912.0f) - 0x4B400000;   // round to nearest even
+                            y[j] = fminf(y[j], 32767.0f);
+                            m[j] = __float_as_int(y[j] + 12582912.0f);
                         }
+                        if (live >= 8) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            if (j < live) {
-                                const int a = m[j] < 0 ? -m[j] : m[j];
-                                stat = a > stat ? a : stat;
+                            for (int j = 0; j < 8; ++j) {
+                                fstat = fmaxf(fstat, fabsf(y[j]));
                                 const long long at = base + (long long)j * p.ldc;
                                 if (p.write_i16) ((short*)p.O)[at] = (short)m[j];
                                 if (p.out_planes) {
                                     p.out_planes[at] = (unsigned char)(m[j] >> 8);
                                     p.out_planes[p.out_plane_bytes + at] = (unsigned char)m[j];
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                if (j < live) {
+                                    fstat = fmaxf(fstat, fabsf(y[j]));
+                                    const long long at = base + (long long)j * p.ldc;
+                                    if (p.write_i16) ((short*)p.O)[at] = (short)m[j];
+                                    if (p.out_planes) {
+                                        p.out_planes[at] = (unsigned char)(m[j] >> 8);
+                                        p.out_planes[p.out_plane_bytes + at] = (unsigned char)m[j];
+                                    }
                                 }
                             }
                         }
@@ -599,6 +638,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             }
             if (lane == 0 && pmax) atomicMax(p.probe_out, pmax);
         } else {
+            // fused epilogue: the largest |value| before rounding (rounding is monotonic)
+            const int fs = (int)rintf(fstat);
+            stat = fs > stat ? fs : stat;
             for (int o = 16; o > 0; o >>= 1) {
                 const int t = __shfl_xor_sync(0xffffffffu, stat, o);
                 stat = t > stat ? t : stat;
