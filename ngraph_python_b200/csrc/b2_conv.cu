@@ -36,6 +36,10 @@ namespace {
 
 struct ConvGeom {
     int C, H, W, N, K, R, S, P, Q, pad_h, pad_w, str_h, str_w, dil_h, dil_w;
+    // the streamed tensor of an implicit-GEMM pass may be a zero-dilated view of a smaller one
+    // (the input gradient of a strided convolution): element (h, w) is source (h/up_h, w/up_w)
+    // where both divide and the quotient is inside src_h x src_w, zero elsewhere
+    int up_h, up_w, src_h, src_w;
 };
 
 int geom_from(const b2_conv_dims* d, ConvGeom* g) {
@@ -48,6 +52,7 @@ int geom_from(const b2_conv_dims* d, ConvGeom* g) {
     g->C = d->C; g->H = d->H; g->W = d->W; g->N = d->N; g->K = d->K; g->R = d->R; g->S = d->S;
     g->P = d->P; g->Q = d->Q; g->pad_h = d->pad_h; g->pad_w = d->pad_w; g->str_h = d->str_h;
     g->str_w = d->str_w; g->dil_h = d->dil_h; g->dil_w = d->dil_w;
+    g->up_h = g->up_w = 1; g->src_h = g->H; g->src_w = g->W;
     return B2_OK;
 }
 
@@ -803,15 +808,22 @@ bool implicit_ok(int mode, const ConvGeom& g) {
     return implicit_shape(g).nstages >= 2;
 }
 
-// The input gradient of a unit-stride convolution is itself a convolution: of the error tensor
-// (K channels, P x Q) with the filters flipped and transposed, padded by R-1-pad.  Returns false
-// where that does not hold (strides, dilation, padding larger than the window allows).
+// The input gradient of a convolution is itself a unit-stride convolution: of the error tensor
+// (K channels, P x Q), with zeros put between its elements when the forward pass was strided,
+// with the filters flipped and transposed, padded by R-1-pad.  The dilated tensor is H+2pad-R+1
+// high (for unit stride that is P), so that the result is exactly H high.  Returns false where
+// this does not hold or does not pay (filter dilation, padding larger than the window allows,
+// strides whose zero-filling would multiply the work by more than four).
 bool bprop_as_fprop(const ConvGeom& f, ConvGeom* g) {
-    if (f.str_h != 1 || f.str_w != 1 || f.dil_h != 1 || f.dil_w != 1) return false;
+    if (f.dil_h != 1 || f.dil_w != 1 || f.str_h * f.str_w > 4) return false;
     if (f.pad_h > f.R - 1 || f.pad_w > f.S - 1) return false;
+    const int he = f.H + 2 * f.pad_h - f.R + 1, we = f.W + 2 * f.pad_w - f.S + 1;
+    if (he < (f.P - 1) * f.str_h + 1 || we < (f.Q - 1) * f.str_w + 1) return false;
     *g = f;
-    g->C = f.K; g->H = f.P; g->W = f.Q; g->K = f.C; g->P = f.H; g->Q = f.W;
+    g->C = f.K; g->H = he; g->W = we; g->K = f.C; g->P = f.H; g->Q = f.W;
     g->pad_h = f.R - 1 - f.pad_h; g->pad_w = f.S - 1 - f.pad_w;
+    g->str_h = g->str_w = 1;
+    g->up_h = f.str_h; g->up_w = f.str_w; g->src_h = f.P; g->src_w = f.Q;
     return true;
 }
 
@@ -823,6 +835,38 @@ bool pass_geom(const ConvGeom& f, int pass, ConvGeom* g) {
 
 // The three parts of an implicit-GEMM forward convolution: the two operand pre-passes (which a
 // caller can skip when it already holds the planes) and the tile kernel.
+// int16 tensor [C][src_h][src_w][N] -> the two byte planes of its zero-dilated form
+// [C][H][W][N]; eight images per thread (N is a multiple of 128 on this path).
+__global__ void __launch_bounds__(256)
+dilate_planes_kernel(const short* __restrict__ src, ConvGeom g, long long n8,
+                     void* __restrict__ plane0, void* __restrict__ plane1) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const int nv = g.N / 8;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n8; v += stride) {
+        const int n = (int)(v % nv);
+        long long r = v / nv;
+        const int w = (int)(r % g.W); r /= g.W;
+        const int h = (int)(r % g.H);
+        const int c = (int)(r / g.H);
+        const int sh = h / g.up_h, sw = w / g.up_w;
+        unsigned hi[2] = {0, 0}, lo[2] = {0, 0};
+        if (sh * g.up_h == h && sw * g.up_w == w && sh < g.src_h && sw < g.src_w) {
+            const long long at = (((long long)c * g.src_h + sh) * g.src_w + sw) * nv + n;
+            const int4 q = __ldcs(reinterpret_cast<const int4*>(src) + at);
+            const unsigned x[4] = {(unsigned)q.x, (unsigned)q.y, (unsigned)q.z, (unsigned)q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const unsigned l2 = __byte_perm(x[j], 0, 0x4420);   // low bytes of the two int16
+                const unsigned h2 = __byte_perm(x[j], 0, 0x4431);   // high bytes
+                lo[j >> 1] |= (l2 & 0xffffu) << (16 * (j & 1));
+                hi[j >> 1] |= (h2 & 0xffffu) << (16 * (j & 1));
+            }
+        }
+        reinterpret_cast<uint2*>(plane0)[v] = make_uint2(hi[0], hi[1]);
+        reinterpret_cast<uint2*>(plane1)[v] = make_uint2(lo[0], lo[1]);
+    }
+}
+
 template <typename T, int MODE>
 int implicit_split_activations(const T* I, const ConvGeom& g, const ImplicitShape& s, void* planes,
                                cudaStream_t st) {
@@ -830,6 +874,14 @@ int implicit_split_activations(const T* I, const ConvGeom& g, const ImplicitShap
     long long blocks = (n_act / 8 + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks < 1) blocks = 1;
+    if (g.up_h != 1 || g.up_w != 1 || g.src_h != g.H || g.src_w != g.W) {
+        B2_REQUIRE(MODE == MODE_FLEX16 && g.N % 8 == 0 && ((uintptr_t)I & 15) == 0,
+                   "the dilated planes need int16 data, 16-byte aligned, N a multiple of 8");
+        dilate_planes_kernel<<<(unsigned)blocks, 256, 0, st>>>(
+            (const short*)I, g, n_act / 8, planes, (unsigned char*)planes + s.act_plane);
+        B2_CUDA(cudaGetLastError());
+        return B2_OK;
+    }
     split_same_layout_kernel<T, MODE><<<(unsigned)blocks, 256, 0, st>>>(
         I, n_act, planes, (unsigned char*)planes + s.act_plane);
     B2_CUDA(cudaGetLastError());
@@ -901,6 +953,10 @@ int implicit_tiles(const void* act_planes, const void* filt_planes, void* O, con
         attr_set = true;
     }
     dim3 grid(p.num_tiles < 148 ? p.num_tiles : 148, s.ntn);
+    // a CTA with one or two tiles has no use for more accumulator sets than tiles: with fewer
+    // sets, more epilogue warps share the columns of each
+    const int per_cta = (p.num_tiles + (int)grid.x - 1) / (int)grid.x;
+    if (per_cta < p.nbuf) p.nbuf = per_cta >= 3 ? 4 : per_cta == 2 ? 2 : 1;
     conv_implicit_kernel<<<grid, kConvThreads, s.smem, st>>>(mI0, mI1, mB, p);
     B2_CUDA(cudaGetLastError());
     return B2_OK;

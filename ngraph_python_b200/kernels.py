@@ -87,6 +87,13 @@ class _PlaneUser(object):
         self.plane_arg = stream_arg          # index of the streamed tensor in op.args / in_views
         self.filter_arg = filter_arg
         self.filter_bytes = filt_bytes
+        # the input gradient of a strided convolution streams the error tensor with zeros between
+        # its elements: planes of its own, written by one extra launch of this step
+        self.own_plane_bytes = 0
+        if conv_pass == lib.CONV_BPROP and (self.dims.str_h > 1 or self.dims.str_w > 1):
+            self.own_plane_bytes = act_bytes
+            self.launches = 2
+            return
         buf = self.in_views[stream_arg].buffer
         buf.plane_bytes = act_bytes
         buf.plane_steps = getattr(buf, "plane_steps", []) + [self]
@@ -97,6 +104,10 @@ class _PlaneUser(object):
             self.filter_planes = t.torch.zeros((self.filter_bytes + 1024,), dtype=t.torch.uint8,
                                                device=t.device)
             self.filter_ptr = self.filter_planes.data_ptr() + (-self.filter_planes.data_ptr()) % 1024
+            if self.own_plane_bytes:
+                self.own_planes = t.torch.zeros((2 * self.own_plane_bytes + 1024,),
+                                                dtype=t.torch.uint8, device=t.device)
+                self.own_planes_ptr = self.own_planes.data_ptr() + (-self.own_planes.data_ptr()) % 1024
 
     def _build_filter_planes(self, t):
         fv = self.in_views[self.filter_arg]
@@ -120,9 +131,10 @@ class _PlaneUser(object):
         raw = lib.raw()
         st = t.stream.cuda_stream
         xbuf, fbuf = xv.buffer, fv.buffer
-        if not xbuf.planes_by_producer:
+        planes_ptr = self.own_planes_ptr if self.own_plane_bytes else xbuf.planes_ptr
+        if self.own_plane_bytes or not xbuf.planes_by_producer:
             lib.check(raw.b2_conv_split_activations(self._ptr(xv), C.byref(self.dims),
-                                                    self.conv_pass, xbuf.planes_ptr, st))
+                                                    self.conv_pass, planes_ptr, st))
             t.kernel_launches += 1
         if fbuf.last_write_step >= 0:
             self._build_filter_planes(t)     # filters written inside this computation
@@ -133,7 +145,7 @@ class _PlaneUser(object):
         if epi is None:
             def call(probe):
                 lib.check(raw.b2_conv_flex16_planes(
-                    self.conv_pass, xbuf.planes_ptr, self.filter_ptr, self._ptr(ov),
+                    self.conv_pass, planes_ptr, self.filter_ptr, self._ptr(ov),
                     C.byref(self.dims), t._table.data_ptr(), slots[0], slots[1], slots[2],
                     t._stats.data_ptr(), t._probe64.data_ptr(), t._status.data_ptr(), probe, st))
             self._flex_probe_then(t, ov.buffer, [xbuf, fbuf], call)
@@ -155,7 +167,7 @@ class _PlaneUser(object):
 
         def call(probe):
             lib.check(raw.b2_conv_flex16_planes_fused(
-                self.conv_pass, xbuf.planes_ptr, self.filter_ptr, self._ptr(ov),
+                self.conv_pass, planes_ptr, self.filter_ptr, self._ptr(ov),
                 C.byref(self.dims), t._table.data_ptr(), slots[0], slots[1], slots[2],
                 C.byref(ce), t._stats.data_ptr(), t._probe64.data_ptr(), t._status.data_ptr(),
                 probe, st))
