@@ -666,7 +666,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 split_same_layout_kernel(const T* __restrict__ src, long long n, void* __restrict__ plane0,
-                         void* __restrict__ plane1) {
+                         void* __restrict__ plane1, unsigned lo_xor = 0) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     if (MODE == MODE_FLEX16 && (n & 7) == 0 && (((uintptr_t)src | (uintptr_t)plane0 |
                                                   (uintptr_t)plane1) & 15) == 0) {
@@ -685,7 +685,7 @@ split_same_layout_kernel(const T* __restrict__ src, long long n, void* __restric
                 hi[j >> 1] |= (h2 & 0xffffu) << (16 * (j & 1));
             }
             reinterpret_cast<uint2*>(plane0)[v] = make_uint2(hi[0], hi[1]);
-            reinterpret_cast<uint2*>(plane1)[v] = make_uint2(lo[0], lo[1]);
+            reinterpret_cast<uint2*>(plane1)[v] = make_uint2(lo[0] ^ lo_xor, lo[1] ^ lo_xor);
         }
         return;
     }
@@ -1185,6 +1185,285 @@ int run_bprop(const T* E, const T* F, void* GI, const b2_conv_dims* d, const b2_
     return launch_on_planes<MODE>(base, s, p, st, t.splits, base + align1k(s.bytes));
 }
 
+// ---- filter gradient on the tile kernel's operands ------------------------------------------------
+// U[(c,r,s), k] = sum over (p,q,n) of I[c, p*str-pad+r, q*str-pad+s, n] * E[k, p, q, n].
+// One k-block = one output pixel x 128 images.  Its A operand is the very box the forward kernel
+// loads (rows (c,r,s) of one channel chunk, 128 images along the row: K-major here), its B operand
+// the rows k of the error tensor's planes at that pixel.  A CTA owns a channel chunk, a tile of
+// filters and a range of k-blocks; two threads issue the products of alternate k-blocks into
+// accumulators of their own ([HH | Ah*El'] and [Al*Eh | LL], El' = El - 128 with the row sums of A
+// taken from a constant extra row of B), and the CTA writes its exact int64 sums as one slice of
+// partial[slice][C*R*S][K], which splitk_finish_kernel adds up, rescales and stores.
+struct UpdTileParams {
+    int Q, nblk, nkb;              // k-block kb = (p*Q + q)*nblk + nb
+    int pad_h, pad_w, str_h, str_w;
+    int cu, rs, C, K;              // channels per chunk, R*S
+    int ntn, kt, bn;               // filter tiles: kt filters each, bn = round_up(kt + 1, 16) rows
+    int per;                       // k-blocks per slice (grid.x)
+    int nstages, tmem_cols;
+    unsigned box_a, box_b;         // bytes of one activation box, of one error box
+    long long* partial;
+    int* status;
+};
+
+constexpr int kUpdThreads = 256;
+constexpr int kUpdMaxStages = 6;
+constexpr int kUpdAPlane = 128 * kKBytes;          // 128 rows of 128 bytes
+constexpr int kUpdSmemFixed = 1024 + 512;
+
+__global__ void __launch_bounds__(kUpdThreads, 1)
+conv_update_kernel(const __grid_constant__ CUtensorMap mapI0, const __grid_constant__ CUtensorMap mapI1,
+                   const __grid_constant__ CUtensorMap mapE0, const __grid_constant__ CUtensorMap mapE1,
+                   const UpdTileParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* ring = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int bn = p.bn, kt = p.kt;
+    const int b_bytes = 2 * bn * kKBytes;                   // [E_hi rows | E_lo' rows]
+    const int stage = 2 * kUpdAPlane + b_bytes;
+    unsigned long long* full_bar = (unsigned long long*)(ring + (size_t)p.nstages * stage);   // [2][max]
+    unsigned long long* empty_bar = full_bar + 2 * kUpdMaxStages;
+    unsigned long long* tmem_full = empty_bar + kUpdMaxStages;                               // [2]
+    unsigned* tmem_holder = (unsigned*)(tmem_full + 2);
+    int* fail_flag = (int*)(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunk = blockIdx.y / p.ntn, ktile = blockIdx.y - chunk * p.ntn;
+    const int kb0 = blockIdx.x * p.per;
+    int mine = p.nkb - kb0;
+    if (mine > p.per) mine = p.per;
+
+    if (threadIdx.x == 0) {
+        prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapE0); prefetch_map(&mapE1);
+        for (int s = 0; s < kUpdMaxStages; ++s) {
+            mbar_init(&full_bar[s], 1); mbar_init(&full_bar[kUpdMaxStages + s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&tmem_full[0], 1); mbar_init(&tmem_full[1], 1);
+        *fail_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, p.tmem_cols);
+    {
+        // rows kt .. bn-1 of both parts of every stage's B tile are constants the loads never
+        // touch: zero, except row kt of the low part, which is all ones (the row-sum column)
+        const int rows = bn - kt, units = p.nstages * 2 * rows * 8;        // 16-byte units
+        for (int i = threadIdx.x; i < units; i += kUpdThreads) {
+            const int u = i & 7, r = (i >> 3) % rows, part = ((i >> 3) / rows) & 1;
+            const int st = (i >> 3) / (2 * rows);
+            const unsigned v = (part == 1 && r == 0) ? 0x01010101u : 0u;
+            uint4* dst = (uint4*)(ring + (size_t)st * stage + 2 * kUpdAPlane +
+                                  (size_t)(part * bn + kt + r) * kKBytes) + u;
+            *dst = make_uint4(v, v, v, v);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            unsigned empty_parity = 1;
+            for (int i = 0; i < mine; ++i) {
+                const int kb = kb0 + i;
+                const int pq = kb / p.nblk, nb = kb - pq * p.nblk;
+                const int pp = pq / p.Q, q = pq - pp * p.Q;
+                unsigned long long* fb = full_bar + (i & 1) * kUpdMaxStages;
+                if (!mbar_wait_relaxed(&empty_bar[s], empty_parity)) { atomicExch(fail_flag, 1); break; }
+                unsigned char* sa = ring + (size_t)s * stage;
+                mbar_expect_tx(&fb[s], 2 * p.box_a + 2 * p.box_b);
+                tma_load_4d(sa, &mapI0, nb * 128, q * p.str_w - p.pad_w, pp * p.str_h - p.pad_h,
+                            chunk * p.cu, &fb[s]);
+                tma_load_4d(sa + kUpdAPlane, &mapI1, nb * 128, q * p.str_w - p.pad_w,
+                            pp * p.str_h - p.pad_h, chunk * p.cu, &fb[s]);
+                tma_load_2d(sa + 2 * kUpdAPlane, &mapE0, kb * 128, ktile * kt, &fb[s]);
+                tma_load_2d(sa + 2 * kUpdAPlane + bn * kKBytes, &mapE1, kb * 128, ktile * kt, &fb[s]);
+                if (++s == p.nstages) { s = 0; empty_parity ^= 1u; }
+            }
+        }
+    } else if (warp == 1 || warp == 2) {
+        const int id = warp - 1;
+        if (lane == 0) {
+            const unsigned id_s = make_idesc_n(2, 1, 1, 2 * bn), id_u = make_idesc_n(2, 0, 1, 2 * bn);
+            const unsigned acc = tmem_base + id * 4 * bn;
+            unsigned long long* fb = full_bar + id * kUpdMaxStages;
+            unsigned phase_bits = 0, accumulate = 0;
+            bool ok = true;
+            for (int i = id; i < mine && ok; i += 2) {
+                const int s = i % p.nstages;
+                if (!mbar_wait(&fb[s], (phase_bits >> s) & 1u)) { atomicExch(fail_flag, 1); ok = false; break; }
+                phase_bits ^= 1u << s;
+                tc_fence_after();
+                unsigned char* sa = ring + (size_t)s * stage;
+                const unsigned long long dAh = make_smem_desc(sa), dAl = make_smem_desc(sa + kUpdAPlane);
+                const unsigned long long dB = make_smem_desc(sa + 2 * kUpdAPlane);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    tc_mma<MODE_FLEX16>(acc, dAh + 2 * k, dB + 2 * k, id_s, accumulate);            // HH | Ah*El'
+                    tc_mma<MODE_FLEX16>(acc + 2 * bn, dAl + 2 * k, dB + 2 * k, id_u, accumulate);   // Al*Eh | LL
+                    accumulate = 1;
+                }
+                tc_commit(&empty_bar[s]);
+            }
+            if (accumulate) tc_commit(&tmem_full[id]);
+            else mbar_arrive(&tmem_full[id]);          // no k-block of its own: nothing to wait for
+        }
+    } else if (warp >= 4) {
+        const int quarter = warp - 4;
+        const bool two = mine >= 2;                     // the second accumulator set holds sums
+        bool ok = mbar_wait_relaxed(&tmem_full[0], 0);
+        ok = mbar_wait_relaxed(&tmem_full[1], 0) && ok;
+        if (!ok) atomicExch(fail_flag, 1);
+        tc_fence_after();
+        const int row = quarter * 32 + lane;
+        const int cg = chunk * p.cu + row / p.rs;
+        const bool valid = ok && row < p.cu * p.rs && cg < p.C;
+        const unsigned a0 = tmem_base + ((unsigned)(quarter * 32) << 16), a1 = a0 + 4 * bn;
+        // (the loaded registers are only read after the wait)
+        const unsigned h0 = tmem_ld1(a0 + bn + kt), l0 = tmem_ld1(a0 + 3 * bn + kt);
+        unsigned h1 = 0, l1 = 0;
+        if (two) { h1 = tmem_ld1(a1 + bn + kt); l1 = tmem_ld1(a1 + 3 * bn + kt); }
+        tmem_ld_wait();
+        const long long s_hi = (long long)(int)h0 + (long long)(int)h1;
+        const long long s_lo = (long long)(int)l0 + (long long)(int)l1;
+        const long long fix = 128LL * (256LL * s_hi + s_lo);
+        long long* out = p.partial + ((long long)blockIdx.x * p.C * p.rs + (long long)chunk * p.cu * p.rs + row) * p.K +
+                         ktile * kt;
+        for (int c0 = 0; c0 < kt; c0 += 8) {
+            unsigned hh[8], x1[8], x2[8], ll[8];
+            tmem_ld8(a0 + c0, hh); tmem_ld8(a0 + bn + c0, x1);
+            tmem_ld8(a0 + 2 * bn + c0, x2); tmem_ld8(a0 + 3 * bn + c0, ll);
+            tmem_ld_wait();
+            long long v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                v[j] = ((long long)(int)hh[j] << 16) + (((long long)(int)x1[j] + (long long)(int)x2[j]) << 8) +
+                       (long long)(int)ll[j];
+            if (two) {
+                tmem_ld8(a1 + c0, hh); tmem_ld8(a1 + bn + c0, x1);
+                tmem_ld8(a1 + 2 * bn + c0, x2); tmem_ld8(a1 + 3 * bn + c0, ll);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    v[j] += ((long long)(int)hh[j] << 16) + (((long long)(int)x1[j] + (long long)(int)x2[j]) << 8) +
+                            (long long)(int)ll[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (valid && c0 + j < kt && ktile * kt + c0 + j < p.K) out[c0 + j] = v[j] + fix;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, p.tmem_cols);
+    }
+    if (threadIdx.x == 0 && *fail_flag && p.status) atomicExch(p.status, 1);
+}
+
+struct UpdShape {
+    bool ok;
+    int cu, cchunks, ntn, kt, bn, tmem_cols, nstages, smem, nkb, per, nsplit;
+    size_t act_plane, err_plane, partial_bytes, bytes;
+};
+
+UpdShape update_implicit_shape(int mode, const ConvGeom& g) {
+    UpdShape u;
+    u.ok = false;
+    const int rs = g.R * g.S;
+    const long long cols = (long long)g.P * g.Q * g.N;
+    if (mode != MODE_FLEX16 || g.N % 128 != 0 || g.dil_h != 1 || g.dil_w != 1 || rs > 128 ||
+        g.R > 256 || g.S > 256 || cols >= (1LL << 31) - 256 || getenv("B2_CONV_IM2COL"))
+        return u;
+    const int cu_max = 128 / rs;
+    u.cchunks = (g.C + cu_max - 1) / cu_max;
+    u.cu = (g.C + u.cchunks - 1) / u.cchunks;
+    u.ntn = (g.K + 62) / 63;                       // two accumulator sets of 4*bn columns in 512
+    u.kt = (g.K + u.ntn - 1) / u.ntn;
+    u.bn = round_up(u.kt + 1, 16);
+    u.tmem_cols = 32;
+    while (u.tmem_cols < 8 * u.bn) u.tmem_cols *= 2;
+    const int stage = 2 * kUpdAPlane + 2 * u.bn * kKBytes;
+    u.nstages = (kConvSmemMax - kUpdSmemFixed) / stage;
+    if (u.nstages > kUpdMaxStages) u.nstages = kUpdMaxStages;
+    if (u.nstages < 2) return u;
+    u.smem = kUpdSmemFixed + u.nstages * stage;
+    u.nkb = (int)(cols / 128);
+    int slices = 148 / (u.cchunks * u.ntn);
+    if (slices < 1) slices = 1;
+    u.per = (u.nkb + slices - 1) / slices;
+    if (u.per > 256) u.per = 256;                  // the int32 sums stay exact up to 32768 terms
+    u.nsplit = (u.nkb + u.per - 1) / u.per;
+    u.act_plane = (((size_t)g.C * g.H * g.W * g.N) + 1023) / 1024 * 1024;
+    u.err_plane = (((size_t)g.K * cols) + 1023) / 1024 * 1024;
+    u.partial_bytes = (size_t)u.nsplit * g.C * rs * g.K * sizeof(long long);
+    u.bytes = 2 * u.act_plane + 2 * u.err_plane + align1k(u.partial_bytes);
+    u.ok = true;
+    return u;
+}
+
+template <typename T, int MODE>
+int run_update_implicit(const T* I, const T* E, void* U, const ConvGeom& g, const UpdShape& u,
+                        const b2_flex_scale* table, int slotI, int slotE, int slotU, int* stats,
+                        void* scratch, size_t scratch_bytes, unsigned long long* probe_out,
+                        int* status, int probe, cudaStream_t st) {
+    int rc = get_encode();
+    if (rc) return rc;
+    B2_REQUIRE(scratch && scratch_bytes >= u.bytes && ((uintptr_t)scratch & 1023) == 0,
+               "convolution update needs %zu bytes of 1024-byte aligned scratch, got %zu", u.bytes,
+               scratch_bytes);
+    unsigned char* base = (unsigned char*)scratch;
+    unsigned char* eplanes = base + 2 * u.act_plane;
+    long long* partial = (long long*)(eplanes + 2 * u.err_plane);
+    const long long n_act = (long long)g.C * g.H * g.W * g.N, n_err = (long long)g.K * g.P * g.Q * g.N;
+    long long blocks = (n_act / 8 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    split_same_layout_kernel<T, MODE><<<(unsigned)(blocks < 1 ? 1 : blocks), 256, 0, st>>>(
+        I, n_act, base, base + u.act_plane, 0u);
+    blocks = (n_err / 8 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    // the error tensor's low plane as signed bytes (low - 128): both of its planes then make one
+    // signed operand
+    split_same_layout_kernel<T, MODE><<<(unsigned)(blocks < 1 ? 1 : blocks), 256, 0, st>>>(
+        E, n_err, eplanes, eplanes + u.err_plane, 0x80808080u);
+    B2_CUDA(cudaGetLastError());
+    CUtensorMap mI0, mI1, mE0, mE1;
+    if ((rc = make_map_4d(&mI0, base, g, u.cu))) return rc;
+    if ((rc = make_map_4d(&mI1, base + u.act_plane, g, u.cu))) return rc;
+    const int cols = g.P * g.Q * g.N;
+    if ((rc = make_map(&mE0, eplanes, g.K, cols, 1, u.kt))) return rc;
+    if ((rc = make_map(&mE1, eplanes + u.err_plane, g.K, cols, 1, u.kt))) return rc;
+    UpdTileParams p;
+    p.Q = g.Q; p.nblk = g.N / 128; p.nkb = u.nkb;
+    p.pad_h = g.pad_h; p.pad_w = g.pad_w; p.str_h = g.str_h; p.str_w = g.str_w;
+    p.cu = u.cu; p.rs = g.R * g.S; p.C = g.C; p.K = g.K;
+    p.ntn = u.ntn; p.kt = u.kt; p.bn = u.bn; p.per = u.per;
+    p.nstages = u.nstages; p.tmem_cols = u.tmem_cols;
+    p.box_a = (unsigned)(u.cu * g.R * g.S * kKBytes); p.box_b = (unsigned)(u.kt * kKBytes);
+    p.partial = partial; p.status = status;
+    static bool attr_set = false;
+    if (!attr_set) {
+        B2_CUDA(cudaFuncSetAttribute(conv_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kConvSmemMax));
+        attr_set = true;
+    }
+    dim3 grid(u.nsplit, u.cchunks * u.ntn);
+    conv_update_kernel<<<grid, kUpdThreads, u.smem, st>>>(mI0, mI1, mE0, mE1, p);
+    B2_CUDA(cudaGetLastError());
+    GemmParams gp;
+    const int rows = g.C * g.R * g.S;
+    fill_params(&gp, rows, g.K, g.K, U, 0, table, slotI, slotE, slotU, stats, probe_out, status, probe);
+    gp.partial = partial; gp.Mp = rows; gp.Np = g.K; gp.kb_per_split = u.per;
+    long long fb = ((long long)rows * g.K + 31) / 32;
+    if (fb > 148 * 16) fb = 148 * 16;
+    splitk_finish_kernel<MODE><<<(unsigned)fb, 256, 0, st>>>(gp, u.nsplit);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
 template <typename T, int MODE>
 int run_update(const T* I, const T* E, void* U, const b2_conv_dims* d, const b2_flex_scale* table,
                int slotI, int slotE, int slotU, int* stats, void* scratch, size_t scratch_bytes,
@@ -1193,6 +1472,12 @@ int run_update(const T* I, const T* E, void* U, const b2_conv_dims* d, const b2_
     int rc = geom_from(d, &g);
     if (rc) return rc;
     B2_REQUIRE(I && E && U, "null tensor");
+    {
+        const UpdShape u = update_implicit_shape(MODE, g);
+        if (u.ok)
+            return run_update_implicit<T, MODE>(I, E, U, g, u, table, slotI, slotE, slotU, stats,
+                                                scratch, scratch_bytes, probe_out, status, probe, st);
+    }
     const long long kg_ll = (long long)g.P * g.Q * g.N;
     B2_REQUIRE(kg_ll < (1LL << 31) - 256 && (long long)g.C * g.H * g.W * g.N < (1LL << 31),
                "tensor too large");
@@ -1408,7 +1693,8 @@ extern "C" int b2_conv_update_scratch_bytes(int32_t flex, const b2_conv_dims* d,
     int rc = geom_from(d, &g);
     if (rc) return rc;
     B2_REQUIRE(bytes, "null argument");
-    *bytes = update_shape(flex ? MODE_FLEX16 : MODE_F32X3, g).bytes;
+    const UpdShape u = update_implicit_shape(flex ? MODE_FLEX16 : MODE_F32X3, g);
+    *bytes = u.ok ? u.bytes : update_shape(flex ? MODE_FLEX16 : MODE_F32X3, g).bytes;
     return B2_OK;
 }
 

@@ -140,7 +140,9 @@ GRAD_SHAPES = [(16, 7, 7, 32, 8, 3, 3, 0, 1), (16, 9, 11, 32, 8, 3, 3, 1, 1), (3
                # implicit-GEMM kernel with flipped, transposed filters
                (16, 8, 8, 128, 16, 3, 3, 1, 1), (32, 6, 6, 128, 64, 3, 3, 1, 1),
                (16, 8, 8, 128, 32, 1, 1, 0, 1), (40, 5, 7, 128, 24, 3, 2, 1, 1),
-               (64, 6, 6, 256, 130, 3, 3, 1, 1)]
+               (64, 6, 6, 256, 130, 3, 3, 1, 1),
+               # many k-blocks per slice of the filter-gradient kernel, two issuing threads
+               (16, 32, 32, 256, 16, 3, 3, 1, 1), (3, 32, 32, 128, 16, 3, 3, 1, 1)]
 
 
 def _run_grad(torch, lib, which, flex, first, second, out, d, table=None):
