@@ -1512,34 +1512,53 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 pool_avg_kernel(const T* __restrict__ I, T* __restrict__ O, int C, int H, int W, int N, int P, int Q,
                 int R, int S, int pad_h, int pad_w, int str_h, int str_w, int* stats) {
+    // a block takes 32 consecutive results (consecutive images: coalesced); its eight warps each
+    // add every eighth element of the window, the eight partial sums are combined in warp order
+    __shared__ float part[8][32];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const long long total = (long long)C * P * Q * N;
+    const long long units = (total + 31) / 32;
     int stat = 0;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int n = (int)(i % N);
-        long long t = i / N;
-        const int q = (int)(t % Q); t /= Q;
-        const int p = (int)(t % P);
-        const int c = (int)(t / P);
-        const int h0 = max(p * str_h - pad_h, 0), h1 = min(p * str_h - pad_h + R, H);
-        const int w0 = max(q * str_w - pad_w, 0), w1 = min(q * str_w - pad_w + S, W);
+    for (long long u = blockIdx.x; u < units; u += gridDim.x) {
+        const long long i = u * 32 + tx;
+        const bool live = i < total;
         float acc = 0.0f;
-        for (int h = h0; h < h1; ++h)
-            for (int w = w0; w < w1; ++w)
+        int cnt = 1;
+        if (live) {
+            const int n = (int)(i % N);
+            long long t = i / N;
+            const int q = (int)(t % Q); t /= Q;
+            const int p = (int)(t % P);
+            const int c = (int)(t / P);
+            const int h0 = max(p * str_h - pad_h, 0), h1 = min(p * str_h - pad_h + R, H);
+            const int w0 = max(q * str_w - pad_w, 0), w1 = min(q * str_w - pad_w + S, W);
+            const int wlen = max(w1 - w0, 0), area = max(h1 - h0, 0) * wlen;
+            cnt = max(area, 1);
+            for (int e = ty; e < area; e += 8) {
+                const int h = h0 + e / wlen, w = w0 + e % wlen;
                 acc += (float)I[(((long long)c * H + h) * W + w) * N + n];
-        const int cnt = max((h1 - h0) * (w1 - w0), 1);
-        const float mean = acc / (float)cnt;
-        if (sizeof(T) == 2) {
-            const int m = __float2int_rn(mean);
-            stat = max(stat, m < 0 ? -m : m);
-            O[i] = (T)m;
-        } else {
-            O[i] = (T)mean;
+            }
         }
+        part[ty][tx] = acc;
+        __syncthreads();
+        if (ty == 0 && live) {
+            float sum = part[0][tx];
+#pragma unroll
+            for (int k = 1; k < 8; ++k) sum += part[k][tx];
+            const float mean = sum / (float)cnt;
+            if (sizeof(T) == 2) {
+                const int m = __float2int_rn(mean);
+                stat = max(stat, m < 0 ? -m : m);
+                O[i] = (T)m;
+            } else {
+                O[i] = (T)mean;
+            }
+        }
+        __syncthreads();
     }
-    if (sizeof(T) == 2 && stats) {
+    if (sizeof(T) == 2 && stats && ty == 0) {
         for (int o = 16; o > 0; o >>= 1) stat = max(stat, __shfl_xor_sync(0xffffffffu, stat, o));
-        if ((threadIdx.x & 31) == 0 && stat) atomicMax(stats, stat);
+        if (tx == 0 && stat) atomicMax(stats, stat);
     }
 }
 
@@ -1724,7 +1743,7 @@ extern "C" int b2_pool_avg_fprop(const void* I, void* O, int32_t flex, int32_t C
     B2_REQUIRE(I && O && C > 0 && H > 0 && W > 0 && N > 0 && P > 0 && Q > 0 && R > 0 && S > 0 &&
                str_h > 0 && str_w > 0, "bad pooling argument");
     const long long total = (long long)C * P * Q * N;
-    long long blocks = (total + 255) / 256;
+    long long blocks = (total + 31) / 32;            // 32 results per block
     if (blocks > 148 * 16) blocks = 148 * 16;
     cudaStream_t st = (cudaStream_t)stream;
     if (flex)

@@ -956,6 +956,57 @@ int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStr
     return B2_OK;
 }
 
+// A flex16 product far smaller than one wave of tensor-core tiles (the 10 x 64 x 256 classifier
+// of a small network): one thread per result, exact int64 sum, the tile kernel's rescale -- one
+// launch instead of the operand pre-passes and a mostly empty 128-row tile.
+__global__ void __launch_bounds__(256)
+small_gemm_flex16_kernel(const short* __restrict__ A, long long a_rs, long long a_cs,
+                         const short* __restrict__ B, long long b_ks, long long b_ns,
+                         short* __restrict__ C, long long ldc, int M, int N, int K,
+                         const b2_flex_scale* __restrict__ table, int slotA, int slotB, int slotC,
+                         int* stats, unsigned long long* probe_out, int probe) {
+    const float f = table[slotA].scale * table[slotB].scale * (probe ? 1.0f : table[slotC].inv_scale);
+    const int sh = -ilogbf(f);
+    int stat = 0;
+    unsigned long long pmax = 0;
+    const long long total = (long long)M * N;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int m = (int)(i / N), n = (int)(i - (long long)m * N);
+        const short* a = A + m * a_rs;
+        const short* b = B + n * b_ns;
+        long long acc = 0;
+#pragma unroll 4
+        for (int k = 0; k < K; ++k) acc += (long long)((int)a[k * a_cs] * (int)b[k * b_ks]);
+        if (probe) {
+            const unsigned long long v = (unsigned long long)(acc < 0 ? -acc : acc);
+            pmax = v > pmax ? v : pmax;
+        } else {
+            const int q = rescale_i64(acc, sh);
+            const int v = q < 0 ? -q : q;
+            stat = v > stat ? v : stat;
+            C[m * ldc + n] = (short)q;
+        }
+    }
+    if (probe) {
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long t = __shfl_xor_sync(0xffffffffu, pmax, o);
+            pmax = t > pmax ? t : pmax;
+        }
+        if ((threadIdx.x & 31) == 0 && pmax) atomicMax(probe_out, pmax);
+    } else {
+        for (int o = 16; o > 0; o >>= 1) {
+            const int t = __shfl_xor_sync(0xffffffffu, stat, o);
+            stat = t > stat ? t : stat;
+        }
+        if ((threadIdx.x & 31) == 0 && stat) atomicMax(stats + slotC, stat);
+    }
+}
+
+inline bool small_gemm(int mode, int M, int N, int K) {
+    return mode == MODE_FLEX16 && (long long)M * N <= 8192 && K <= 1024;
+}
+
 template <typename T, int MODE>
 int run_gemm(const T* A, long long a_rs, long long a_cs, const T* B, long long b_ks, long long b_ns,
              void* C, long long ldc, int M, int N, int K, const b2_flex_scale* table, int slotA,
@@ -964,6 +1015,14 @@ int run_gemm(const T* A, long long a_rs, long long a_cs, const T* B, long long b
     B2_REQUIRE(A && B && C && M > 0 && N > 0 && K > 0, "bad GEMM argument");
     B2_REQUIRE(a_rs == 1 || a_cs == 1, "A must be contiguous along M or K");
     B2_REQUIRE(b_ks == 1 || b_ns == 1, "B must be contiguous along K or N");
+    if (small_gemm(MODE, M, N, K)) {
+        const int blocks = (int)(((long long)M * N + 255) / 256);
+        small_gemm_flex16_kernel<<<blocks, 256, 0, st>>>(
+            (const short*)A, a_rs, a_cs, (const short*)B, b_ks, b_ns, (short*)C, ldc, M, N, K, table,
+            slotA, slotB, slotC, stats, probe_out, probe);
+        B2_CUDA(cudaGetLastError());
+        return B2_OK;
+    }
     const Shapes s = shapes_for(MODE, M, N, K);
     const int splits = pick_splits(MODE, s, false);     // > 1 only for flex16 with K > 32768
     const size_t need = gemm_scratch_need(MODE, s);

@@ -189,6 +189,8 @@ class GemmStep(_Step):
         if None in (am, ak, bk, bn):
             raise ValueError("Unhandled op: dot operands must be 2-d collapsible: {}".format(op))
         self.M, self.K, self.N = am[0], ak[0], bn[0]
+        if t.flex and self.M * self.N <= 8192 and self.K <= 1024:
+            self.launches = 1         # the library's one-launch form for very small products
         if bk[0] != self.K:
             raise ValueError("Unhandled op: reduction axes of the dot operands disagree")
         # extents of 1 carry no stride of their own: describe them as row-major
