@@ -253,7 +253,7 @@ __device__ __forceinline__ unsigned make_idesc_n(unsigned dfmt, unsigned afmt, u
 }
 
 constexpr int kConvMaxStages = 8;
-constexpr int kConvThreads = 608;           // producer, MMA, sixteen epilogue warps, second MMA warp
+constexpr int kConvThreads = 640;           // producer, MMA, sixteen epilogue warps, two more MMA warps
 constexpr int kConvSmemMax = 232448;        // 227 KB: the most one CTA can have
 constexpr int kConvSmemFixed = 1024 /*alignment*/ + 1024 /*barriers, bias*/;
 
@@ -273,8 +273,8 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     // a barrier in turn (a parity wait cannot tell phase n from phase n+2), and an issuer only
     // ever looks at the stages of its own tiles
     unsigned long long* full_bar =
-        (unsigned long long*)(ring + (size_t)p.nstages * 2 * act_stage);   // [2][kConvMaxStages]
-    unsigned long long* empty_bar = full_bar + 2 * kConvMaxStages;
+        (unsigned long long*)(ring + (size_t)p.nstages * 2 * act_stage);   // [4][kConvMaxStages]
+    unsigned long long* empty_bar = full_bar + 4 * kConvMaxStages;
     unsigned long long* tmem_full = empty_bar + kConvMaxStages;   // [4]
     unsigned long long* tmem_empty = tmem_full + 4;               // [4]
     unsigned long long* filt_bar = tmem_empty + 4;
@@ -288,7 +288,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
     if (threadIdx.x == 0) {
         prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapB);
         for (int s = 0; s < kConvMaxStages; ++s) {
-            mbar_init(&full_bar[s], 1); mbar_init(&full_bar[kConvMaxStages + s], 1);
+            for (int i = 0; i < 4; ++i) mbar_init(&full_bar[i * kConvMaxStages + s], 1);
             mbar_init(&empty_bar[s], 1);
         }
         for (int b = 0; b < 4; ++b) {
@@ -319,7 +319,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             for (int j = 0; j < p.npanels; ++j)
                 tma_load_2d(filt + j * panel_bytes, &mapB, j * kKBytes, blockIdx.y * 2 * bn, filt_bar);
             int s = 0, ti = 0;
-            const int n_mma = p.nbuf >= 2 ? 2 : 1;
+            const int n_mma = p.nbuf >= 4 ? 3 : p.nbuf >= 2 ? 2 : 1;
             unsigned empty_parity = 1;         // the first pass over the ring finds every stage free
             bool ok = true;
             const long long t_start = clock64();
@@ -347,14 +347,16 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 p.dbg[0] = clock64() - t_start; p.dbg[1] = t_wait;
             }
         }
-    } else if (warp == 1 || warp == 18) {
-        // two MMA-issuing threads take alternate tiles (when there are accumulator sets for both):
-        // an MMA instruction costs its issuing thread about a hundred cycles whatever its N and
-        // whatever the operand layout (a K-major, channel-innermost variant of this kernel was
-        // measured slower), and at 16..64 output channels that latency is what bounds a tile.
-        // Four issuers measured no better than two.
-        const int mma_id = warp == 1 ? 0 : 1;
-        const int n_mma = p.nbuf >= 2 ? 2 : 1;
+    } else if (warp == 1 || warp >= 18) {
+        // up to three MMA-issuing threads take the tiles in turn (when there are accumulator sets
+        // for them): an MMA instruction costs its issuing thread about a hundred cycles whatever
+        // its N and whatever the operand layout (a K-major, channel-innermost variant of this
+        // kernel was measured slower), and at 16..64 output channels that latency is what bounds
+        // a tile.  Three keep up with the operand fetch; a fourth would need a 21st warp, and at
+        // 672 threads the register file leaves the epilogue 80 registers (it spills and the
+        // kernel is slower than with two).
+        const int mma_id = warp == 1 ? 0 : warp - 17;
+        const int n_mma = p.nbuf >= 4 ? 3 : p.nbuf >= 2 ? 2 : 1;
         if (lane == 0) {
             // bit 15: A is MN-major.  A_hi is signed, A_lo unsigned, both filter planes signed.
             const unsigned mn = 1u << 15;
