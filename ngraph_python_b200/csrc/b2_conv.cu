@@ -197,7 +197,7 @@ struct ConvTileParams {
     int nstages;                  // ring depth
     int bn;                       // columns per accumulator: kt output channels + the sum column
     int kt;                       // output channels per CTA column (blockIdx.y)
-    int nbuf;                     // accumulator sets in tensor memory: 1, 2 or 4
+    int nbuf;                     // accumulator sets in tensor memory: 1, 2, 3 (or 4)
     int tmem_cols;                // power of two >= 3*bn*nbuf
     int num_tiles, nblk;
     long long ldc;
@@ -276,15 +276,21 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         (unsigned long long*)(ring + (size_t)p.nstages * 2 * act_stage);   // [4][kConvMaxStages]
     unsigned long long* empty_bar = full_bar + 4 * kConvMaxStages;
     unsigned long long* tmem_full = empty_bar + kConvMaxStages;   // [4]
-    unsigned long long* tmem_empty = tmem_full + 4;               // [4]
-    unsigned long long* filt_bar = tmem_empty + 4;
+    // "set drained" barriers, one per (issuing thread, set): the epilogue signals the thread that
+    // will fill the set next, so each thread meets every phase of its own barriers in turn
+    unsigned long long* tmem_empty = tmem_full + 4;               // [4 issuers][4 sets]
+    unsigned long long* filt_bar = tmem_empty + 16;
     unsigned* tmem_holder = (unsigned*)(filt_bar + 1);
     int* fail_flag = (int*)(tmem_holder + 1);
     float* bias_s = (float*)(fail_flag + 2);                      // [bn] bias of this CTA's channels, real values
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int epi_w = 4 / p.nbuf;              // epilogue warps per lane quarter and accumulator set
+    const int epi_w = p.nbuf == 3 ? 1 : 4 / p.nbuf;   // epilogue warps per lane quarter and accumulator set
 
+    // Programmatic dependent launch: the next kernel of the stream, if it was launched the same
+    // way, may take the SMs this grid leaves while its last CTAs still work, and do its set-up;
+    // it reads and writes global memory only after its own griddepcontrol.wait below.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         prefetch_map(&mapI0); prefetch_map(&mapI1); prefetch_map(&mapB);
         for (int s = 0; s < kConvMaxStages; ++s) {
@@ -293,13 +299,16 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         }
         for (int b = 0; b < 4; ++b) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 4 * epi_w);
+            for (int i = 0; i < 4; ++i) mbar_init(&tmem_empty[i * 4 + b], 4 * epi_w);
         }
         mbar_init(filt_bar, 1);
         *fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(tmem_holder, p.tmem_cols);
+    // everything before this line touches no global memory; everything after it sees the
+    // completed work of all earlier kernels of the stream
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x >= 64 && threadIdx.x < 64 + bn) {
         const int col = blockIdx.y * p.kt + (threadIdx.x - 64);
         bias_s[threadIdx.x - 64] = (p.fused && p.bias && (threadIdx.x - 64) < p.kt && col < p.K)
@@ -319,7 +328,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             for (int j = 0; j < p.npanels; ++j)
                 tma_load_2d(filt + j * panel_bytes, &mapB, j * kKBytes, blockIdx.y * 2 * bn, filt_bar);
             int s = 0, ti = 0;
-            const int n_mma = p.nbuf >= 4 ? 3 : p.nbuf >= 2 ? 2 : 1;
+            const int n_mma = p.nbuf >= 4 ? 3 : p.nbuf;
             unsigned empty_parity = 1;         // the first pass over the ring finds every stage free
             bool ok = true;
             const long long t_start = clock64();
@@ -356,7 +365,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         // 672 threads the register file leaves the epilogue 80 registers (it spills and the
         // kernel is slower than with two).
         const int mma_id = warp == 1 ? 0 : warp - 17;
-        const int n_mma = p.nbuf >= 4 ? 3 : p.nbuf >= 2 ? 2 : 1;
+        const int n_mma = p.nbuf >= 4 ? 3 : p.nbuf;
         if (lane == 0) {
             // bit 15: A is MN-major.  A_hi is signed, A_lo unsigned, both filter planes signed.
             const unsigned mn = 1u << 15;
@@ -377,6 +386,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const unsigned stage_units = (unsigned)((2 * act_stage) >> 4), plane_units = (unsigned)(act_stage >> 4);
             int s = 0;
             unsigned phase_bits = 0, stage_lo = ring_lo;       // bit s: parity of my next phase of stage s
+            unsigned empty_bits = 0;                           // bit b: the same for set b's "drained" barrier
             unsigned long long* fb = full_bar + mma_id * kConvMaxStages;
             const long long t_start = clock64();
             long long t_wait_e = 0, t_wait_f = 0, t_mma = 0, t_commit = 0;
@@ -393,8 +403,11 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
                 const int buf = ti % p.nbuf;
                 const unsigned acc_base = tmem_base + buf * acc_cols;
                 const long long tw = clock64();
-                if (ti >= p.nbuf && !mbar_wait(&tmem_empty[buf], ((ti / p.nbuf) - 1) & 1)) {
-                    atomicExch(fail_flag, 1); ok = false; break;
+                if (ti >= p.nbuf) {
+                    if (!mbar_wait(&tmem_empty[mma_id * 4 + buf], (empty_bits >> buf) & 1u)) {
+                        atomicExch(fail_flag, 1); ok = false; break;
+                    }
+                    empty_bits ^= 1u << buf;
                 }
                 t_wait_e += clock64() - tw;
                 tc_fence_after();
@@ -453,6 +466,8 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         if (kt > p.kt) kt = p.kt;
         int stat = 0;
         unsigned long long pmax = 0;
+        const int n_mma_e = p.nbuf >= 4 ? 3 : p.nbuf;          // issuing threads (as in their branch)
+        const int n_my = (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
                         (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
         const int sh = -ilogbf(f);
@@ -628,7 +643,9 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             const long long te1 = clock64();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            // tell the thread that fills this set next (tile ti + nbuf of this CTA, if there is one)
+            if (lane == 0 && ti + p.nbuf < n_my)
+                mbar_arrive(&tmem_empty[((ti + p.nbuf) % n_mma_e) * 4 + buf]);
             t_arr += clock64() - te1;
             t_all += clock64() - te0;
         }
@@ -775,7 +792,7 @@ ImplicitShape implicit_shape(const ConvGeom& g) {
     s.kt = (g.K + s.ntn - 1) / s.ntn;
     s.bn = round_up(s.kt + 1, 16);
     const int sets = 512 / (3 * s.bn);
-    s.nbuf = sets >= 4 ? 4 : sets >= 2 ? 2 : 1;
+    s.nbuf = sets >= 4 ? 4 : sets >= 3 ? 3 : sets >= 2 ? 2 : 1;
     s.tmem_cols = 32;
     while (s.tmem_cols < 3 * s.bn * s.nbuf) s.tmem_cols *= 2;
     const int RS = g.R * g.S;
@@ -958,9 +975,14 @@ int implicit_tiles(const void* act_planes, const void* filt_planes, void* O, con
     // a CTA with one or two tiles has no use for more accumulator sets than tiles: with fewer
     // sets, more epilogue warps share the columns of each
     const int per_cta = (p.num_tiles + (int)grid.x - 1) / (int)grid.x;
-    if (per_cta < p.nbuf) p.nbuf = per_cta >= 3 ? 4 : per_cta == 2 ? 2 : 1;
-    conv_implicit_kernel<<<grid, kConvThreads, s.smem, st>>>(mI0, mI1, mB, p);
-    B2_CUDA(cudaGetLastError());
+    if (per_cta < p.nbuf) p.nbuf = per_cta >= 4 ? 4 : per_cta == 3 ? 3 : per_cta == 2 ? 2 : 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kConvThreads); cfg.dynamicSmemBytes = s.smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = getenv("B2_CONV_NO_PDL") ? 0 : 1;
+    B2_CUDA(cudaLaunchKernelEx(&cfg, conv_implicit_kernel, mI0, mI1, mB, p));
     return B2_OK;
 }
 
