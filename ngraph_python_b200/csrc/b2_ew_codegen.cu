@@ -391,6 +391,10 @@ int generate(const b2_ew_program& p, const Plan& pl, bool probe, std::string* ou
       << pl.group << "\n#define NRED " << (p.n_red > 0 ? p.n_red : 1) << "\n";
     o << "extern \"C\" __global__ void __launch_bounds__(THREADS, " << pl.minb << ") b2_ew_main(const b2_ew_args p) {\n";
     o << "    __shared__ float smem[64];\n";
+    // programmatic dependent launch: nothing above this line touches global memory; the next
+    // kernel of the stream may be scheduled while this grid drains
+    o << "    asm volatile(\"griddepcontrol.wait;\" ::: \"memory\");\n"
+      << "    asm volatile(\"griddepcontrol.launch_dependents;\" ::: \"memory\");\n";
     emit_prologue(o, p, probe);
 
     if (p.reduce_mode != B2_REDUCE_B) {
@@ -615,6 +619,10 @@ int generate_staged(const b2_ew_program& p, const Plan& pl, bool probe, std::str
       << "    __shared__ float smem[64];\n"
       << "    __shared__ unsigned long long full_bar[STAGES];\n"
       << "    extern __shared__ __align__(128) unsigned char stage_mem[];\n";
+    // programmatic dependent launch: nothing above this line touches global memory; the next
+    // kernel of the stream may be scheduled while this grid drains
+    o << "    asm volatile(\"griddepcontrol.wait;\" ::: \"memory\");\n"
+      << "    asm volatile(\"griddepcontrol.launch_dependents;\" ::: \"memory\");\n";
     emit_prologue(o, p, probe);
     o << "    const int tid = threadIdx.x;\n"
       << "    const int rows = (int)(p.A * p.B), Bn = (int)p.B;\n"
@@ -1021,6 +1029,21 @@ extern "C" int b2_ew_launch_count(const b2_ew_kernel* k) {
     return k->plan[k->can_vec ? 1 : 0].nsplit > 1 ? 2 : 1;
 }
 
+namespace {
+// The main kernel waits for the stream's earlier work itself (griddepcontrol.wait, its first
+// statement), so it may be scheduled while the kernel before it drains.
+cudaError_t launch_main(const void* func, dim3 grid, void** params, size_t dyn, cudaStream_t st) {
+    static const bool plain = getenv("B2_EW_NO_PDL") != nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = dyn; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = plain ? 0 : 1;
+    return cudaLaunchKernelExC(&cfg, func, params);
+}
+}  // namespace
+
 extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const* out,
                             const float* consts, const b2_flex_scale* flex_table,
                             int32_t* flex_stats, void* scratch, size_t scratch_bytes,
@@ -1075,7 +1098,7 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
     Module* m = k->mod[vec][probe];
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t dyn = pl.staged ? (size_t)pl.stages * pl.stage_bytes : 0;
-    B2_CUDA(cudaLaunchKernel((const void*)m->main, pl.grid, dim3(kThreads), params, dyn, st));
+    B2_CUDA(launch_main((const void*)m->main, pl.grid, params, dyn, st));
     if (pl.nsplit > 1) {
         const long long rows = p.A * p.B;
         dim3 g((unsigned)((rows + kThreads - 1) / kThreads));
@@ -1194,7 +1217,7 @@ extern "C" int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* 
     void* params[] = {&a};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t dyn = pl.staged ? (size_t)pl.stages * pl.stage_bytes : 0;
-    B2_CUDA(cudaLaunchKernel((const void*)m->main, pl.grid, dim3(kThreads), params, dyn, st));
+    B2_CUDA(launch_main((const void*)m->main, pl.grid, params, dyn, st));
     if (pl.nsplit > 1) {
         const long long rows = p.A * p.B;
         dim3 g((unsigned)((rows + kThreads - 1) / kThreads));
