@@ -197,9 +197,12 @@ class Computation(object):
         if len(args) != len(self.parameters):
             raise ValueError("Computation was expecting %d arguments, but was called with %d" %
                              (len(self.parameters), len(args)))
+        views = [t._view_of(p) for p in self.parameters]
+        for v, value in zip(views, args):
+            t._stage(v, value)             # the input copies run while the host does the rest
         t._begin_call(self)
-        for p, value in zip(self.parameters, args):
-            t._host_to_device(t._view_of(p), value, in_call=True)
+        for v in views:
+            t._host_to_device(v, None, in_call=True, staged=True)
         self.executor()
         # results, flex statistics and the status word come back with asynchronous copies and
         # ONE stream synchronisation
@@ -1149,9 +1152,10 @@ class B200Transformer(object):
                                              dtype=self.torch.uint8, device=self.device)
 
     # ---- host <-> device -----------------------------------------------------------------------
-    def _host_to_device(self, view, value, init=False, in_call=False):
-        """DeviceTensor.__setitem__ (ngraph/transformers/gputransform.py:806-854); flex:
-        FlexGPUDeviceTensor.__setitem__ (flexgputransform.py:183-208)."""
+    def _stage(self, view, value):
+        """The copy half of a host write: the fp32 values go to the device (for a flex16 tensor
+        into its staging buffer).  Depends on nothing else of a call, so a computation starts
+        these copies before its exponent bookkeeping."""
         torch = self.torch
         buf = view.buffer
         buf.version += 1
@@ -1170,6 +1174,16 @@ class B200Transformer(object):
         if buf.staging is None:
             buf.staging = torch.empty((max(buf.size, 1),), dtype=torch.float32, device=self.device)
         buf.staging.copy_(src, non_blocking=async_ok)
+
+    def _host_to_device(self, view, value, init=False, in_call=False, staged=False):
+        """DeviceTensor.__setitem__ (ngraph/transformers/gputransform.py:806-854); flex:
+        FlexGPUDeviceTensor.__setitem__ (flexgputransform.py:183-208).  staged: _stage has
+        already copied the values."""
+        buf = view.buffer
+        if not staged:
+            self._stage(view, value)
+        if not buf.flex:
+            return
         e = buf.entry
         raw = lib.raw()
         if in_call and e.initialized:

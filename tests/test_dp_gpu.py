@@ -69,6 +69,30 @@ def test_train_step_single_gpu_flex16(case):
     t.close()
 
 
+def test_train_step_flex16_on_the_tile_kernels():
+    """Batch 128: forward convolutions, input gradients (strided ones through zero-dilated error
+    planes) and filter gradients all run on the tensor-core tile kernels.  Checked against the
+    numpy evaluation of the same graph (tests/mirror_interp.py over oracle/), at the flex
+    tolerance of the committed ResNet training fixture (which has batch 32 and so runs on the
+    gather + GEMM path)."""
+    from tests import mirror_interp
+    outs, params, vals = cases.resnet_train_step(ng, global_n=128, hw=16, blocks=1)
+    interp = mirror_interp.Interp()
+    expect = [interp.run(outs, dict(zip(params, vals))) for _ in range(2)]
+    t = ng.transformers.allocate_transformer("b200", flex=True)
+    comp = t.computation(outs, *params)
+    kinds = [s.kind for s in comp.steps]
+    assert kinds.count("conv_bprop") >= 3 and kinds.count("conv_update") >= 3
+    assert all(s.use_planes for s in comp.steps if s.kind in ("conv", "conv_bprop"))
+    fix = {}
+    for rep, res in enumerate(expect):
+        for k, v in enumerate(res):
+            fix["out%d_%d" % (rep, k)] = v
+    results = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(2)]
+    _check_flex(results, fix, "resnet_train_step")
+    t.close()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
