@@ -81,6 +81,7 @@ def test_train_step_flex16_on_the_tile_kernels():
     expect = [interp.run(outs, dict(zip(params, vals))) for _ in range(2)]
     t = ng.transformers.allocate_transformer("b200", flex=True)
     comp = t.computation(outs, *params)
+    t.initialize()
     kinds = [s.kind for s in comp.steps]
     assert kinds.count("conv_bprop") >= 3 and kinds.count("conv_update") >= 3
     assert all(s.use_planes for s in comp.steps if s.kind in ("conv", "conv_bprop"))
