@@ -60,7 +60,13 @@ enum b2_ew_opcode {
     B2_OP_SIN, B2_OP_COS,
     B2_OP_ADD = 32, B2_OP_SUB, B2_OP_MUL, B2_OP_DIV, B2_OP_INT_DIV, B2_OP_MOD, B2_OP_EQ,
     B2_OP_NE, B2_OP_LT, B2_OP_LE, B2_OP_GT, B2_OP_GE, B2_OP_POW, B2_OP_MINIMUM, B2_OP_MAXIMUM,
-    B2_OP_ONEHOT  /* (index along the reduction-free axis B) == x */
+    B2_OP_ONEHOT, /* (index along the reduction-free axis B) == x */
+    /* a: register, b: index k of an elementwise flex16 result of the same program.  The value
+     * register a has after being stored as result k and read back: mantissa(a) * scale_k.  Lets
+     * a kernel go on computing with a tensor it has just written, exactly as a later kernel would
+     * see it.  In a probe launch results whose exponent is still to be chosen (bit k of the
+     * launch's probe argument, counted from bit 1) pass through unchanged. */
+    B2_OP_REQUANT
 };
 
 /* reduction codes: float_ew2.py:70-90 */
@@ -123,6 +129,8 @@ int b2_ew_scratch_bytes(const b2_ew_kernel* k, size_t* bytes);
  * destinations.  `probe` != 0 runs the measuring variant used on a tensor's first write: nothing
  * is stored, and flex_stats[slot] receives the bit pattern of the largest |fp32 value| each
  * flex output would have been given (fmaxf order == integer order for non-negative floats).
+ * Bits 1.. of `probe` name the results whose exponent is still to be chosen (bit 1 = result 0):
+ * a B2_OP_REQUANT op that refers to such a result passes its value through unchanged.
  * `status` (device int32, may be NULL) is set to 1 if a bounded device-side wait ran out, in
  * which case the results of that launch are undefined.
  * replaces ElementWiseKernel.execute / bind_flex_scales (gputransform.py:277-345,

@@ -44,6 +44,7 @@ struct EwArgs {
     float* scratch;
     int* status;
     int nsplit;
+    unsigned fresh_mask;
 };
 
 // ---- NVRTC through dlopen (no link-time dependency: the library loads on machines without it) --
@@ -171,10 +172,17 @@ bool is_arg(int op) { return op == B2_RED_ARGMAX || op == B2_RED_ARGMIN; }
 
 std::string reg(int i) { return "r" + std::to_string(i); }
 
-int emit_op(std::ostringstream& o, const b2_ew_op& op, int dst, bool fast) {
+int emit_op(std::ostringstream& o, const b2_ew_op& op, int dst, bool fast, bool probe) {
     const std::string d = "const float " + reg(dst) + " = ";
     const std::string x = reg(op.a), y = reg(op.b);
     switch (op.opcode) {
+        case B2_OP_REQUANT: {
+            const std::string k = std::to_string(op.b);
+            const std::string rq = "b2_requant(" + x + ", rq" + k + ", rs" + k + ")";
+            if (probe) o << d << "((p.fresh_mask >> " << k << ") & 1u) ? " << x << " : " << rq << ";";
+            else o << d << rq << ";";
+            break;
+        }
         case B2_OP_ASSIGN: o << d << x << ";"; break;
         case B2_OP_NEG: o << d << "-" << x << ";"; break;
         case B2_OP_ABS: o << d << "fabsf(" << x << ");"; break;
@@ -226,7 +234,7 @@ bool uses_flex(const b2_ew_program& p) {
     return false;
 }
 
-int emit_body(std::ostringstream& o, const b2_ew_program& p, const Plan& pl) {
+int emit_body(std::ostringstream& o, const b2_ew_program& p, const Plan& pl, bool probe) {
     // flex16 programs use the cheaper transcendentals (see b2_ew_device.cuh); fp32 programs
     // keep CUDA libm, as the reference's generated code does.
     const bool fast = uses_flex(p);
@@ -242,7 +250,7 @@ int emit_body(std::ostringstream& o, const b2_ew_program& p, const Plan& pl) {
         o << "            const float " << reg(p.n_in + i) << " = k" << i << ";\n";
     for (int i = 0; i < p.n_ops; ++i) {
         o << "            ";
-        if (emit_op(o, p.ops[i], p.n_in + p.n_const + i, fast)) return -1;
+        if (emit_op(o, p.ops[i], p.n_in + p.n_const + i, fast, probe)) return -1;
     }
     return 0;
 }
@@ -351,6 +359,15 @@ void emit_prologue(std::ostringstream& o, const b2_ew_program& p, bool probe) {
         }
     for (int i = 0; i < p.n_const; ++i)
         o << "    const float k" << i << " = p.consts[" << i << "];\n";
+    // 1/step and step of the results that a requant op refers to
+    unsigned seen = 0;
+    for (int i = 0; i < p.n_ops; ++i)
+        if (p.ops[i].opcode == B2_OP_REQUANT && !((seen >> p.ops[i].b) & 1u)) {
+            const int k = p.ops[i].b;
+            seen |= 1u << k;
+            o << "    const float rq" << k << " = p.flex_table[p.out_slot[" << k << "]].inv_scale;\n"
+              << "    const float rs" << k << " = p.flex_table[p.out_slot[" << k << "]].scale;\n";
+        }
 }
 
 void emit_finalize(std::ostringstream& o, const b2_ew_program& p, bool probe) {
@@ -450,7 +467,7 @@ int generate(const b2_ew_program& p, const Plan& pl, bool probe, std::string* ou
         o << "            _Pragma(\"unroll\") for (int e = 0; e < V; ++e) {\n";
         {
             std::ostringstream body;
-            if (emit_body(body, p, pl)) return b2::fail(B2_ERR_INVALID, "unknown elementwise opcode");
+            if (emit_body(body, p, pl, probe)) return b2::fail(B2_ERR_INVALID, "unknown elementwise opcode");
             o << body.str();
         }
         for (int k = 0; k < p.n_out; ++k)
@@ -547,7 +564,7 @@ int generate(const b2_ew_program& p, const Plan& pl, bool probe, std::string* ou
         o << "            _Pragma(\"unroll\") for (int e = 0; e < V; ++e) {\n";
         {
             std::ostringstream body;
-            if (emit_body(body, p, pl)) return b2::fail(B2_ERR_INVALID, "unknown elementwise opcode");
+            if (emit_body(body, p, pl, probe)) return b2::fail(B2_ERR_INVALID, "unknown elementwise opcode");
             o << body.str();
         }
         for (int k = 0; k < p.n_out; ++k)
@@ -706,7 +723,7 @@ int generate_staged(const b2_ew_program& p, const Plan& pl, bool probe, std::str
     o << "            _Pragma(\"unroll\") for (int e = 0; e < V; ++e) {\n";
     {
         std::ostringstream body;
-        if (emit_body(body, p, pl)) return b2::fail(B2_ERR_INVALID, "unknown elementwise opcode");
+        if (emit_body(body, p, pl, probe)) return b2::fail(B2_ERR_INVALID, "unknown elementwise opcode");
         o << body.str();
     }
     for (int k = 0; k < p.n_out; ++k)
@@ -913,7 +930,10 @@ int validate(const b2_ew_program& p) {
     for (int i = 0; i < p.n_ops; ++i) {
         const int lim = p.n_in + p.n_const + i;
         B2_REQUIRE(p.ops[i].a >= 0 && p.ops[i].a < lim, "op %d reads an undefined register", i);
-        if (p.ops[i].opcode >= B2_OP_ADD && p.ops[i].opcode != B2_OP_ONEHOT)
+        if (p.ops[i].opcode == B2_OP_REQUANT)
+            B2_REQUIRE(p.ops[i].b >= 0 && p.ops[i].b < p.n_out && is_flex(p.out[p.ops[i].b].t.dtype),
+                       "op %d: requant needs an elementwise flex16 result of this program", i);
+        else if (p.ops[i].opcode >= B2_OP_ADD && p.ops[i].opcode != B2_OP_ONEHOT)
             B2_REQUIRE(p.ops[i].b >= 0 && p.ops[i].b < lim, "op %d reads an undefined register", i);
     }
     for (int k = 0; k < p.n_out + p.n_red; ++k) {
@@ -1065,6 +1085,7 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
     }
     if (any_flex) B2_REQUIRE(flex_table && flex_stats, "flex tensors need a scale table and stats");
     B2_REQUIRE(p.n_const == 0 || consts, "constants missing");
+    const unsigned fresh_mask = probe > 0 ? (unsigned)probe >> 1 : 0u;
     probe = probe ? 1 : 0;
     int rc = ensure_variant(k, vec, probe);
     if (rc) return rc;
@@ -1094,6 +1115,7 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
     a.scratch = static_cast<float*>(scratch);
     a.status = status;
     a.nsplit = pl.nsplit;
+    a.fresh_mask = fresh_mask;
     void* params[] = {&a};
     Module* m = k->mod[vec][probe];
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -1179,6 +1201,7 @@ extern "C" int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* 
     }
     if (any_flex) B2_REQUIRE(flex_table && flex_stats, "flex tensors need a scale table and stats");
     B2_REQUIRE(p.n_const == 0 || consts, "constants missing");
+    const unsigned fresh_mask = probe > 0 ? (unsigned)probe >> 1 : 0u;
     probe = probe ? 1 : 0;
     Module* m = k->mod[vec][probe];
     B2_REQUIRE(m != nullptr,
@@ -1214,6 +1237,7 @@ extern "C" int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* 
     a.scratch = static_cast<float*>(scratch);
     a.status = status;
     a.nsplit = pl.nsplit;
+    a.fresh_mask = fresh_mask;
     void* params[] = {&a};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t dyn = pl.staged ? (size_t)pl.stages * pl.stage_bytes : 0;

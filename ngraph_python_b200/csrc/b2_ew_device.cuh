@@ -46,6 +46,7 @@ struct b2_ew_args {
     float* scratch;                       // split reductions: [nsplit][rows][n_red] partials
     int* status;                          // optional: set to 1 if a bounded wait ran out
     int nsplit;
+    unsigned fresh_mask;                  // probe launches: results whose exponent is not chosen yet
 };
 
 // fp32 -> int16 with the semantics of cvt.rni.s16.f32 (round to nearest even, saturate to
@@ -61,6 +62,11 @@ __device__ __forceinline__ int b2_f32_to_i16(float v, float& stat) {
     return __float_as_int(v + 12582912.0f) - 0x4B400000;
 }
 __device__ __forceinline__ int b2_stat_to_int(float stat) { return (int)rintf(stat); }
+// the value a flex16 tensor holds after v was stored into it with 1/step q and step s
+__device__ __forceinline__ float b2_requant(float v, float q, float s) {
+    float unused = 0.0f;
+    return (float)b2_f32_to_i16(v * q, unused) * s;
+}
 
 // two int16 mantissas packed in one 32-bit word -> two fp32 values times `scale`, exact:
 // (m ^ 0x8000) placed under the exponent of 2^23 is the float 2^23 + m + 32768.

@@ -18,6 +18,7 @@ OPCODES = {
     "exp2": 8, "log2": 9, "sig": 10, "tanh": 11, "safelog": 12, "sgn": 13, "sin": 14, "cos": 15,
     "add": 32, "sub": 33, "mul": 34, "div": 35, "int_div": 36, "mod": 37, "eq": 38, "ne": 39,
     "lt": 40, "le": 41, "gt": 42, "ge": 43, "pow": 44, "minimum": 45, "maximum": 46, "onehot": 47,
+    "requant": 48,      # (register, index of a flex16 result): the value as stored and read back
 }
 UNARY_OPS = frozenset(k for k, v in OPCODES.items() if v < 32) | {"onehot"}
 REDOPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "argmax": 4, "argmin": 5}

@@ -430,9 +430,10 @@ class _Planner(object):
         else:
             value_args = list(op.args)
             iter_axes = op.args[0].axes if is_red else op.axes
-        # (fp32 only: a flex16 reader must see the stored, quantised value -- the Kahan term of
-        # the optimizer exists to capture exactly that quantisation error)
-        fwd = self._forwarding(op, value_args) if (self.t.fuse and not self.t.flex) else None
+        # (a flex16 reader must see the stored, quantised value -- the Kahan term of the optimizer
+        # exists to capture exactly that quantisation error: there the register is re-quantised
+        # with the exponent of the store, see _finalize_ew)
+        fwd = self._forwarding(op, value_args) if (self.t.fuse and self.t.forward_inplace) else None
         if fwd is not None:
             # try the kernel that made the in-place writes this op reads: its registers still
             # hold the values, so the op can run there instead of in a later launch
@@ -833,11 +834,20 @@ class _Planner(object):
             if d[0] == "i":
                 return d[1]
             return reg[d[1]]
+        # flex16: an assignment whose value a later op of this kernel reads from the register is
+        # followed by a requant op, so that the reader sees what the tensor now holds
+        read_back = set(d[1] for _, _, descs in pending for d in descs
+                        if d[0] == "r" and isinstance(d[1], AssignOp))
+        requants = []    # (position in ops, AssignOp): the result index is known further down
         for m, name, descs in pending:
             a = resolve(descs[0])
             b = resolve(descs[1]) if len(descs) > 1 else None
             ops.append((name, a, b))
             reg[m] = n_in + n_const + len(ops) - 1
+            if t.flex and m in read_back and t._view_of(m.args[0]).buffer.flex:
+                ops.append(("requant", reg[m], None))
+                requants.append((len(ops) - 1, m))
+                reg[m] = n_in + n_const + len(ops) - 1
 
         if t.flex:
             ops = _fuse_sigmoid(ops, n_in, consts)
@@ -854,6 +864,7 @@ class _Planner(object):
             inputs.append(d)
         outs, reds = [], []
         out_targets, red_targets = [], []
+        result_index = {}
         for k, (m, v) in enumerate(zip(ew_outs + red_outs, out_views)):
             d = tdesc(v, abc[n_in + k])
             d["slot"] = t._write_slot(v.buffer) if v.buffer.flex else -1
@@ -891,8 +902,22 @@ class _Planner(object):
                     out_targets.append((v, True))
                     buf.planes_by_producer = True
                 if not (wants and self._only_plane_readers(m)):
+                    result_index[m] = len(outs)
                     outs.append(d)
                     out_targets.append((v, False))
+        for at, m in requants:
+            ops[at] = ("requant", ops[at][1], result_index[m])
+        # which results' stored form each result depends on (through requant ops): a tensor that
+        # is written for the first time gets its exponent only after those it depends on
+        dep = {}
+        for i, (name, a, b) in enumerate(ops):
+            r = n_in + n_const + i
+            if name == "requant":
+                dep[r] = dep.get(a, 0) | (1 << b)
+            else:
+                dep[r] = dep.get(a, 0) | (dep.get(b, 0) if b is not None and name != "onehot" else 0)
+        step.requant_deps = [dep.get(d["reg"], 0) & ~(1 << k if k < len(outs) else 0)
+                             for k, d in enumerate(outs + reds)]
         prog = lib.make_program(dims, inputs, consts, ops, outs, reds, mode)
         step.kernel = lib.PlannedKernel(prog, self.t.flex) if self.t.plan_only else lib.EwKernel(prog)
         step.in_views = in_views
@@ -956,6 +981,9 @@ class B200Transformer(object):
         self.fuse = bool(fuse)
         # fold bias / residual / ReLU after a convolution into the convolution step (flex16)
         self.fuse_conv_tail = bool(kwargs.pop("fuse_conv_tail", True))
+        # let a kernel go on computing with a persistent tensor it has just assigned (the value
+        # is taken from the register; flex16: re-quantised as the store quantises it)
+        self.forward_inplace = bool(kwargs.pop("forward_inplace", True))
         self.flex = bool(flex)
         self.fixed_point = bool(fixed_point)
         self.flex_manager = flexmod.FlexManager(fixed_point=fixed_point, verbose=flex_verbose)
@@ -1355,21 +1383,33 @@ class B200Transformer(object):
         if self.flex:
             common.update(flex_table=self._table.data_ptr(), flex_stats=self._stats.data_ptr())
             fresh = [b for b in step.output_buffers() if not b.entry.initialized]
-            if fresh:
-                # first write of these tensors: measure the unsaturated range, then pick exponents.
-                # The measuring launch leaves float bits in the statistic of EVERY output of the
-                # kernel, so the statistics of the outputs that are not new are put back after it.
+            # First write of these tensors: measure the unsaturated range, then pick exponents.
+            # The measuring launch leaves float bits in the statistic of EVERY output of the
+            # kernel, so the statistics of the outputs that are not new are put back after it.
+            # A new tensor whose value depends on the STORED form of another new tensor of the
+            # same kernel (a requant op) is measured in a later round, once that exponent exists.
+            deps = getattr(step, "requant_deps", None) or [0] * len(step.out_targets)
+            while fresh:
                 saved = self._stats.clone()
-                step.kernel.launch(ins, outs, probe=True, **common)
+                # bit k: result k has no exponent yet (a requant op on it passes values through)
+                open_bits = sum(1 << k for k, (v, _) in enumerate(step.out_targets)
+                                if v.buffer in fresh)
+                step.kernel.launch(ins, outs, probe=1 | (open_bits << 1), **common)
                 self.kernel_launches += step.kernel.launches
                 self._stats_host.copy_(self._stats, non_blocking=False)
                 self._stats.copy_(saved)
                 bits = self._stats_host.numpy()
-                for b in fresh:
+                ready = [b for b in fresh
+                         if not any(v.buffer is b and (deps[k] & open_bits & ~(1 << k))
+                                    for k, (v, _) in enumerate(step.out_targets))]
+                if not ready:            # cannot happen (ops are ordered); do not loop for ever
+                    ready = list(fresh)
+                for b in ready:
                     maxabs = float(bits[b.slot_write:b.slot_write + 1].view(np.float32)[0])
                     dec = b.entry.initialize_from_range(maxabs)
                     self._set_table_row(b.slot_write, dec)
                     self._stats[b.slot_write:b.slot_write + 1].zero_()
+                fresh = [b for b in fresh if b not in ready]
         step.kernel.launch(ins, outs, **common)
         self.kernel_launches += step.kernel.launches
 

@@ -49,14 +49,22 @@ def test_softmax_splits_at_reductions():
 
 
 def test_inplace_update_stays_ordered():
-    # flex16: step 0 updates w in place, step 1 reads the new (stored, quantised) w
-    t, comp = _plan("assign_sequence", flex=True)
-    assert len(comp.steps) == 2
-    w_buf = comp.steps[0].out_views[0].buffer
-    assert comp.steps[1].in_views[0].buffer is w_buf
-    # fp32: the reader takes the new value from the register of the assignment, same kernel
+    """A reader of a tensor that the same kernel has just assigned takes the value from the
+    register of the assignment.  flex16: through a requant op that refers to the stored result,
+    so that it sees the quantised value a later kernel would load."""
     t, comp = _plan("assign_sequence", flex=False)
     assert len(comp.steps) == 1
+    prog = comp.steps[0].kernel.prog
+    assert all(prog.ops[i].opcode != lib.OPCODES["requant"] for i in range(prog.n_ops))
+    t, comp = _plan("assign_sequence", flex=True)
+    assert len(comp.steps) == 1
+    prog = comp.steps[0].kernel.prog
+    rq = [prog.ops[i] for i in range(prog.n_ops) if prog.ops[i].opcode == lib.OPCODES["requant"]]
+    assert len(rq) >= 1
+    for op in rq:
+        assert 0 <= op.b < prog.n_out and prog.out[op.b].t.dtype == lib.FLEX16
+    src = comp.steps[0].kernel.source()
+    assert "b2_requant(" in src
 
 
 def test_broadcast_by_axis_name():

@@ -176,3 +176,25 @@ def test_cached_filter_planes_follow_the_filters():
             assert np.abs(got[:, 0] - exp).max() <= 4 * tol
         assert np.abs(a - b).max() > 0.1
         t.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", ["assign_sequence", "mlp_train_step", "resnet_train_step"])
+def test_flex_register_forwarding_is_bit_exact(case):
+    """flex16: a kernel that goes on computing with a tensor it has just assigned reads the
+    register through a requant op -- the mantissa the store writes times the tensor's step -- so
+    the results are, bit for bit, those of separate kernels that reload the stored tensor."""
+    got = {}
+    for fw in (True, False):
+        outs, params, vals = cases.CASES[case](ng)
+        t = ng.transformers.allocate_transformer("b200", flex=True, forward_inplace=fw)
+        comp = t.computation(outs, *params)
+        got[fw] = [[np.array(r, copy=True) for r in comp(*vals)] for _ in range(3)]
+        got[fw].append(len(comp.steps))
+        t.close()
+    assert got[True][-1] <= got[False][-1]
+    if case != "mlp_train_step":                   # (plain SGD never reads a weight back)
+        assert got[True][-1] < got[False][-1]      # fewer kernels
+    for a, b in zip(got[True][:-1], got[False][:-1]):
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
