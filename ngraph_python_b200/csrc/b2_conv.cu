@@ -198,6 +198,7 @@ struct ConvTileParams {
     int bn;                       // columns per accumulator: kt output channels + the sum column
     int kt;                       // output channels per CTA column (blockIdx.y)
     int nbuf;                     // accumulator sets in tensor memory: 1, 2, 3 (or 4)
+    int n_mma;                    // MMA-issuing threads: 1..3, at most nbuf
     int tmem_cols;                // power of two >= 3*bn*nbuf
     int num_tiles, nblk;
     long long ldc;
@@ -328,7 +329,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
             for (int j = 0; j < p.npanels; ++j)
                 tma_load_2d(filt + j * panel_bytes, &mapB, j * kKBytes, blockIdx.y * 2 * bn, filt_bar);
             int s = 0, ti = 0;
-            const int n_mma = p.nbuf >= 4 ? 3 : p.nbuf;
+            const int n_mma = p.n_mma;
             unsigned empty_parity = 1;         // the first pass over the ring finds every stage free
             bool ok = true;
             const long long t_start = clock64();
@@ -365,7 +366,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         // 672 threads the register file leaves the epilogue 80 registers (it spills and the
         // kernel is slower than with two).
         const int mma_id = warp == 1 ? 0 : warp - 17;
-        const int n_mma = p.nbuf >= 4 ? 3 : p.nbuf;
+        const int n_mma = p.n_mma;
         if (lane == 0) {
             // bit 15: A is MN-major.  A_hi is signed, A_lo unsigned, both filter planes signed.
             const unsigned mn = 1u << 15;
@@ -466,7 +467,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap mapI0,
         if (kt > p.kt) kt = p.kt;
         int stat = 0;
         unsigned long long pmax = 0;
-        const int n_mma_e = p.nbuf >= 4 ? 3 : p.nbuf;          // issuing threads (as in their branch)
+        const int n_mma_e = p.n_mma;
         const int n_my = (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const float f = p.table[p.slotA].scale * p.table[p.slotB].scale *
                         (p.probe ? 1.0f : p.table[p.slotC].inv_scale);
@@ -976,6 +977,11 @@ int implicit_tiles(const void* act_planes, const void* filt_planes, void* O, con
     // sets, more epilogue warps share the columns of each
     const int per_cta = (p.num_tiles + (int)grid.x - 1) / (int)grid.x;
     if (per_cta < p.nbuf) p.nbuf = per_cta >= 4 ? 4 : per_cta == 3 ? 3 : per_cta == 2 ? 2 : 1;
+    p.n_mma = p.nbuf >= 3 ? 3 : p.nbuf;
+    if (const char* e = getenv("B2_CONV_ISSUERS")) {      // measurement aid: 1..3
+        const int want = atoi(e);
+        if (want >= 1 && want < p.n_mma) p.n_mma = want;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(kConvThreads); cfg.dynamicSmemBytes = s.smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
