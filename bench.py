@@ -11,7 +11,7 @@ Rank 0 prints ONE JSON line.  Workloads:
                         per GPU, He-initialised weights from seed 0, batch norm folded into
                         biases.  Metric: images per second.  Each GPU runs a full replica on its
                         own batch; nothing is exchanged.
-  gemm_flex16 / gemm_fp32  (BASELINE config 3) C = A.B with M = N = K = --size (default 8192);
+  gemm_flex16 / gemm_fp32  (benchmark configuration 3) C = A.B with M = N = K = --size (default 8192);
                         flex16: int16 mantissas uniform in [-32767, 32767], exponents -15 and -12,
                         C re-quantised with the exponent chosen from its measured range.
                         Metric: T(flex-)MAC-op/s = 2MNK / t; roofline on the tensor pipe.
@@ -144,7 +144,7 @@ def build_c2(ng, flex, rows, cols):
 
 
 # ---------------------------------------------------------------------------------------------
-# ResNet-20 (BASELINE config 4): described once as a layer list, built either as a graph for the
+# ResNet-20 (benchmark configuration 4): described once as a layer list, built either as a graph for the
 # b200 transformer or evaluated with the numpy restatement for the CPU baseline.
 RESNET_WIDTHS = (16, 32, 64)
 RESNET_N = 256

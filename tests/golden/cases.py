@@ -11,7 +11,7 @@ def _rng(seed):
 
 
 def c2_fused(ng, rows=24, cols=2048):
-    """BASELINE config 2: y = tanh(a*x+b)*sigmoid(c); sum and maxabs over axis 1."""
+    """benchmark configuration 2: y = tanh(a*x+b)*sigmoid(c); sum and maxabs over axis 1."""
     R = ng.make_axis(rows, name="R")
     C = ng.make_axis(cols, name="C")
     ph = [ng.placeholder([R, C]) for _ in range(4)]
@@ -200,7 +200,7 @@ def conv_grads_stride2(ng):
 
 
 def mlp_forward(ng):
-    """Forward pass of BASELINE config 1: 784 -> 512 ReLU -> 512 ReLU -> 10 softmax, batch 128."""
+    """Forward pass of benchmark configuration 1: 784 -> 512 ReLU -> 512 ReLU -> 10 softmax, batch 128."""
     r = _rng(0)
     N = ng.make_axis(128, name="N")
     F = ng.make_axis(784, name="F")
@@ -225,7 +225,7 @@ def mlp_forward(ng):
 
 
 def resnet20(ng, n=32, hw=32, widths=(16, 32, 64), blocks=3):
-    """ResNet-20 inference (BASELINE config 4): 3 stages of 3 basic blocks, 3x3 convolutions,
+    """ResNet-20 inference (benchmark configuration 4): 3 stages of 3 basic blocks, 3x3 convolutions,
     batch norm folded into per-channel biases, a 1x1 projection on the first block of every stage,
     8x8 average pool, 10-way linear, softmax.  22 convolutions, He-initialised from seed 0."""
     r = _rng(0)
@@ -289,7 +289,7 @@ def resnet8_small(ng):
 
 def mlp_train_step(ng, global_n=128, shard=None, dims=(64, 48, 32, 10), lr=0.05, digest=False):
     """One data-parallel SGD step of a 3-layer MLP with softmax cross-entropy, gradients written
-    out by hand (BASELINE configs 1 and 5 in miniature).  Every replica sees `shard = (rank,
+    out by hand (benchmark configurations 1 and 5 in miniature).  Every replica sees `shard = (rank,
     world)` of the global batch, scales its gradients by 1/global batch (the reference's optimizer
     divides by the global batch size, ngraph/frontends/neon/optimizer.py:177-198) and sum-allreduces
     them; with one replica the allreduce is the identity.  Returns the post-step weights and the
@@ -393,7 +393,7 @@ def momentum_update(ng, variable, grad, lr, momentum, wdecay=0.0):
 
 def resnet_train_step(ng, global_n=32, shard=None, hw=16, widths=(16, 32, 64), blocks=1, lr=0.1,
                       momentum=0.9):
-    """One data-parallel training step of the ResNet of resnet20() (BASELINE config 5): softmax
+    """One data-parallel training step of the ResNet of resnet20() (benchmark configuration 5): softmax
     cross-entropy, gradients written out with bprop_conv / update_conv, sum-allreduce of every
     gradient (already divided by the GLOBAL batch, as the reference's optimizer divides,
     ngraph/frontends/neon/optimizer.py:177-198), momentum SGD with Kahan summation.
@@ -506,7 +506,7 @@ def resnet_train_step(ng, global_n=32, shard=None, hw=16, widths=(16, 32, 64), b
 
 
 def mlp_c1_train_step(ng, shard=None):
-    """BASELINE config 1 at full size: 784-512-512-10, batch 128, one SGD step (lr 0.01)."""
+    """benchmark configuration 1 at full size: 784-512-512-10, batch 128, one SGD step (lr 0.01)."""
     return mlp_train_step(ng, global_n=128, shard=shard, dims=(784, 512, 512, 10), lr=0.01,
                           digest=True)
 
