@@ -52,3 +52,43 @@ def test_gradient_oracles_are_the_adjoints_of_fprop(shape):
     lhs = int((O * E).sum())
     assert lhs == int((I * gI).sum())
     assert lhs == int((F * U).sum())
+
+
+@pytest.mark.parametrize("shape", [(5, 9, 11, 3, 6, 3, 3, 1, 2), (4, 8, 8, 2, 7, 1, 1, 0, 2),
+                                   (3, 10, 7, 2, 5, 3, 2, 1, 2), (6, 7, 7, 2, 4, 3, 3, 1, 1),
+                                   (3, 12, 9, 2, 4, 3, 3, 0, 2), (2, 9, 9, 2, 3, 2, 2, 0, 1)])
+def test_input_gradient_is_a_unit_stride_convolution_of_the_dilated_error(shape):
+    """The identity the tile kernel uses for input gradients, on exact integers: put zeros
+    between the elements of E (a tensor H+2pad-R+1 high, E at the multiples of the stride), flip
+    and transpose the filters, pad by R-1-pad, convolve with unit stride."""
+    C, H, W, N, K, R, S, pad, stride = shape
+    P = (H + 2 * pad - R) // stride + 1
+    Q = (W + 2 * pad - S) // stride + 1
+    rng = np.random.RandomState(sum(shape))
+    E = rng.randint(-300, 300, (K, P, Q, N)).astype(np.int64)
+    F = rng.randint(-300, 300, (C, R, S, K)).astype(np.int64)
+    want = co.conv_bprop(E, F, (H, W), (pad, pad), (stride, stride), dtype=np.int64)
+    he, we = H + 2 * pad - R + 1, W + 2 * pad - S + 1
+    assert he >= (P - 1) * stride + 1 and we >= (Q - 1) * stride + 1
+    dil = np.zeros((K, he, we, N), np.int64)
+    dil[:, :(P - 1) * stride + 1:stride, :(Q - 1) * stride + 1:stride, :] = E
+    flipped = np.ascontiguousarray(F[:, ::-1, ::-1, :].transpose(3, 1, 2, 0))      # (K, R, S, C)
+    got = co.conv_fprop(dil, flipped, (R - 1 - pad, S - 1 - pad), (1, 1), dtype=np.int64)
+    assert got.shape == want.shape
+    assert np.array_equal(got, want)
+
+
+def test_folding_the_output_step_into_the_epilogue_is_exact():
+    """The fused convolution epilogue multiplies every term by the output's 1/step (a power of
+    two) instead of scaling the finished fp32 value: same bits, as long as nothing overflows or
+    goes subnormal."""
+    rng = np.random.RandomState(5)
+    acc = rng.randint(-2 ** 38, 2 ** 38, 20000).astype(np.float64).astype(np.float32)
+    bias = (rng.randint(-32768, 32768, 20000) * 2.0 ** -13).astype(np.float32)
+    res = (rng.randint(-32768, 32768, 20000) * 2.0 ** -10).astype(np.float32)
+    for dec_in, dec_out in ((27, 11), (20, 3), (30, 14), (12, -2)):
+        f = np.float32(2.0 ** -dec_in)
+        q = np.float32(2.0 ** dec_out)
+        plain = ((res + (acc * f + bias).astype(np.float32)).astype(np.float32) * q).astype(np.float32)
+        folded = (res * q + (acc * (f * q) + bias * q).astype(np.float32)).astype(np.float32)
+        assert np.array_equal(plain, folded)

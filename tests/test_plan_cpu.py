@@ -121,3 +121,31 @@ def test_reduction_of_a_tensor_assigned_in_the_same_kernel():
     comp = t.computation(out, x)
     t.initialize()
     assert len(comp.steps) == 1
+
+
+def test_plane_entry_points_describe_the_dilated_error_tensor():
+    """Host arithmetic of the C ABI (no device): the input gradient of a strided convolution
+    streams the error tensor zero-dilated to H+2pad-R+1 rows; strides whose zero filling would
+    multiply the work by more than four stay on the gather path."""
+    import ctypes as C
+
+    def dims(Cc, H, W, N, K, R, S, pad, stride):
+        d = lib.ConvDims()
+        P, Q = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
+        for k, v in dict(C=Cc, D=1, H=H, W=W, N=N, K=K, T=1, R=R, S=S, M=1, P=P, Q=Q, pad_d=0,
+                         pad_h=pad, pad_w=pad, str_d=1, str_h=stride, str_w=stride, dil_d=1,
+                         dil_h=1, dil_w=1).items():
+            setattr(d, k, v)
+        return d, P, Q
+    d, P, Q = dims(16, 32, 32, 128, 32, 3, 3, 1, 2)
+    ok, act, filt = lib.conv_planes_info(d, lib.CONV_BPROP)
+    assert ok and act == (32 * 32 * 32 * 128 + 1023) // 1024 * 1024      # K x (H+2-3+1)^2 x N
+    ok1, act1, _ = lib.conv_planes_info(dims(16, 32, 32, 128, 32, 3, 3, 1, 1)[0], lib.CONV_BPROP)
+    assert ok1 and act1 == act                                            # unit stride: K x P x Q x N
+    assert not lib.conv_planes_info(dims(16, 33, 33, 128, 32, 3, 3, 0, 3)[0], lib.CONV_BPROP)[0]
+    assert not lib.conv_planes_info(dims(16, 32, 32, 96, 32, 3, 3, 1, 2)[0], lib.CONV_BPROP)[0]
+    # filter gradient on the tile kernel: planes of both operands + int64 slices; far less than
+    # the unrolled input the gather path writes
+    small = lib.conv_update_scratch_bytes(True, dims(16, 32, 32, 128, 16, 3, 3, 1, 1)[0])
+    odd_batch = lib.conv_update_scratch_bytes(True, dims(16, 32, 32, 96, 16, 3, 3, 1, 1)[0])
+    assert small < odd_batch
