@@ -295,6 +295,12 @@ int b2_pool_avg_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H
                       int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S, int32_t pad_h,
                       int32_t pad_w, int32_t str_h, int32_t str_w, int32_t* stats_slot,
                       void* stream);
+/* Max pooling over the part of each window that lies inside the image (np.max of the same
+ * slices, ngraph/transformers/cpu/cpuengine.py:297-300); flex as for the average. */
+int b2_pool_max_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H, int32_t W,
+                      int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S, int32_t pad_h,
+                      int32_t pad_w, int32_t str_h, int32_t str_w, int32_t* stats_slot,
+                      void* stream);
 
 #ifdef __cplusplus
 }

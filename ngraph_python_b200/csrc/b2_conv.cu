@@ -1538,10 +1538,10 @@ int run_update(const T* I, const T* E, void* U, const b2_conv_dims* d, const b2_
 // np.mean of the clipped slice, ngraph/transformers/cpu/cpuengine.py:296-305).  flex16: the output
 // shares the input's exponent (ngraph/transformers/passes/flexpass.py:40-48), so mantissas are
 // averaged and rounded to nearest even.
-template <typename T>
+template <typename T, bool MAX>
 __global__ void __launch_bounds__(256)
-pool_avg_kernel(const T* __restrict__ I, T* __restrict__ O, int C, int H, int W, int N, int P, int Q,
-                int R, int S, int pad_h, int pad_w, int str_h, int str_w, int* stats) {
+pool_kernel(const T* __restrict__ I, T* __restrict__ O, int C, int H, int W, int N, int P, int Q,
+            int R, int S, int pad_h, int pad_w, int str_h, int str_w, int* stats) {
     // a block takes 32 consecutive results (consecutive images: coalesced); its eight warps each
     // add every eighth element of the window, the eight partial sums are combined in warp order
     __shared__ float part[8][32];
@@ -1552,7 +1552,7 @@ pool_avg_kernel(const T* __restrict__ I, T* __restrict__ O, int C, int H, int W,
     for (long long u = blockIdx.x; u < units; u += gridDim.x) {
         const long long i = u * 32 + tx;
         const bool live = i < total;
-        float acc = 0.0f;
+        float acc = MAX ? -INFINITY : 0.0f;
         int cnt = 1;
         if (live) {
             const int n = (int)(i % N);
@@ -1566,7 +1566,8 @@ pool_avg_kernel(const T* __restrict__ I, T* __restrict__ O, int C, int H, int W,
             cnt = max(area, 1);
             for (int e = ty; e < area; e += 8) {
                 const int h = h0 + e / wlen, w = w0 + e % wlen;
-                acc += (float)I[(((long long)c * H + h) * W + w) * N + n];
+                const float v = (float)I[(((long long)c * H + h) * W + w) * N + n];
+                acc = MAX ? fmaxf(acc, v) : acc + v;
             }
         }
         part[ty][tx] = acc;
@@ -1574,8 +1575,9 @@ pool_avg_kernel(const T* __restrict__ I, T* __restrict__ O, int C, int H, int W,
         if (ty == 0 && live) {
             float sum = part[0][tx];
 #pragma unroll
-            for (int k = 1; k < 8; ++k) sum += part[k][tx];
-            const float mean = sum / (float)cnt;
+            for (int k = 1; k < 8; ++k) sum = MAX ? fmaxf(sum, part[k][tx]) : sum + part[k][tx];
+            // (a window that lies entirely in the padding has no element: 0, as the mean gives)
+            const float mean = MAX ? (sum == -INFINITY ? 0.0f : sum) : sum / (float)cnt;
             if (sizeof(T) == 2) {
                 const int m = __float2int_rn(mean);
                 stat = max(stat, m < 0 ? -m : m);
@@ -1766,24 +1768,44 @@ extern "C" int b2_conv_update_flex16(const int16_t* I, const int16_t* E, int16_t
                                           probe ? 1 : 0, (cudaStream_t)stream);
 }
 
-extern "C" int b2_pool_avg_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H,
-                                 int32_t W, int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S,
-                                 int32_t pad_h, int32_t pad_w, int32_t str_h, int32_t str_w,
-                                 int32_t* stats_slot, void* stream) {
+namespace {
+int run_pool(bool is_max, const void* I, void* O, int32_t flex, int32_t C, int32_t H, int32_t W,
+             int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S, int32_t pad_h, int32_t pad_w,
+             int32_t str_h, int32_t str_w, int32_t* stats_slot, void* stream) {
     B2_REQUIRE(I && O && C > 0 && H > 0 && W > 0 && N > 0 && P > 0 && Q > 0 && R > 0 && S > 0 &&
                str_h > 0 && str_w > 0, "bad pooling argument");
     const long long total = (long long)C * P * Q * N;
     long long blocks = (total + 31) / 32;            // 32 results per block
     if (blocks > 148 * 16) blocks = 148 * 16;
     cudaStream_t st = (cudaStream_t)stream;
-    if (flex)
-        pool_avg_kernel<short><<<(unsigned)blocks, 256, 0, st>>>((const short*)I, (short*)O, C, H, W,
-                                                                N, P, Q, R, S, pad_h, pad_w, str_h,
-                                                                str_w, stats_slot);
-    else
-        pool_avg_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const float*)I, (float*)O, C, H, W,
-                                                                N, P, Q, R, S, pad_h, pad_w, str_h,
-                                                                str_w, nullptr);
+#define B2_POOL_LAUNCH(T, MAXV, STATS)                                                            \
+    pool_kernel<T, MAXV><<<(unsigned)blocks, 256, 0, st>>>((const T*)I, (T*)O, C, H, W, N, P, Q, R, \
+                                                          S, pad_h, pad_w, str_h, str_w, STATS)
+    if (flex) {
+        if (is_max) B2_POOL_LAUNCH(short, true, stats_slot);
+        else B2_POOL_LAUNCH(short, false, stats_slot);
+    } else {
+        if (is_max) B2_POOL_LAUNCH(float, true, nullptr);
+        else B2_POOL_LAUNCH(float, false, nullptr);
+    }
+#undef B2_POOL_LAUNCH
     B2_CUDA(cudaGetLastError());
     return B2_OK;
+}
+}  // namespace
+
+extern "C" int b2_pool_avg_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H,
+                                 int32_t W, int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S,
+                                 int32_t pad_h, int32_t pad_w, int32_t str_h, int32_t str_w,
+                                 int32_t* stats_slot, void* stream) {
+    return run_pool(false, I, O, flex, C, H, W, N, P, Q, R, S, pad_h, pad_w, str_h, str_w,
+                    stats_slot, stream);
+}
+
+extern "C" int b2_pool_max_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H,
+                                 int32_t W, int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S,
+                                 int32_t pad_h, int32_t pad_w, int32_t str_h, int32_t str_w,
+                                 int32_t* stats_slot, void* stream) {
+    return run_pool(true, I, O, flex, C, H, W, N, P, Q, R, S, pad_h, pad_w, str_h, str_w,
+                    stats_slot, stream);
 }

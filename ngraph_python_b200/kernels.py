@@ -406,7 +406,7 @@ class ConvUpdateStep(_ConvGradStep):
 
 
 class PoolStep(_Step):
-    """Average pooling forward; a flex output keeps its input's exponent
+    """Average or max pooling forward; a flex output keeps its input's exponent
     (ngraph/transformers/passes/flexpass.py:40-48)."""
     kind = "pool"
     launches = 1
@@ -414,8 +414,10 @@ class PoolStep(_Step):
     def __init__(self, index, op, t):
         super(PoolStep, self).__init__(index, op)
         pp = op.pool_params
-        if pp["op"] != "avg":
-            raise ValueError("Unhandled op: only average pooling is implemented: {}".format(op))
+        if pp["op"] not in ("avg", "max"):
+            raise ValueError("Unhandled op: only average and max pooling are implemented: {}"
+                             .format(op))
+        self.pool_op = pp["op"]
         iv = t._view_of(op.args[0])
         if not iv.is_dense():
             raise ValueError("Unhandled op: pooling input must be a dense tensor")
@@ -440,8 +442,9 @@ class PoolStep(_Step):
         stats = 0
         if self.flex:
             stats = t._stats.data_ptr() + 4 * (t._stats.numel() - 2)    # discarded
-        lib.check(lib.raw().b2_pool_avg_fprop(self._ptr(iv), self._ptr(ov), int(self.flex),
-                                              *(self.args + (stats, t.stream.cuda_stream))))
+        fn = lib.raw().b2_pool_max_fprop if self.pool_op == "max" else lib.raw().b2_pool_avg_fprop
+        lib.check(fn(self._ptr(iv), self._ptr(ov), int(self.flex),
+                     *(self.args + (stats, t.stream.cuda_stream))))
         t.kernel_launches += 1
 
 

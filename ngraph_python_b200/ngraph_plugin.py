@@ -88,6 +88,10 @@ class GraphTranslator(object):
             return self(op.value_tensor)
         if isinstance(op, ref.AssignOp):
             return b2.assign(self(op.args[0]), self(op.args[1]))
+        if isinstance(op, ref.TensorSizeOp):
+            # the number of elements along the reduction axes (what mean and variance divide by:
+            # ngraph/op_graph/op_graph.py:4012-4029); the reference folds it into a constant too
+            return b2.constant(float(op.reduction_axes.size))
         args = [self(a) for a in op.args]
         if name in _UNARY:
             return _UNARY[name](args[0])

@@ -481,6 +481,13 @@ def mean(x, reduction_axes=None, out_axes=None):
     return sum(x, reduction_axes=reduction_axes, out_axes=out_axes) / float(reduction_axes.size)
 
 
+def variance(x, out_axes=None, reduction_axes=None):
+    """ngraph/op_graph/op_graph.py:4007-4009: mean of the squared distance from the mean."""
+    x = as_op(x)
+    return mean(square(x - mean(x, reduction_axes=reduction_axes, out_axes=out_axes)),
+                reduction_axes=reduction_axes, out_axes=out_axes)
+
+
 def softmax(x, normalization_axes=None, **kw):
     """ngraph/op_graph/op_graph.py: SoftmaxOp -- exp(x - max) / sum(exp(x - max))."""
     x = as_op(x)

@@ -91,3 +91,21 @@ def pool_avg_fprop(I, window, pad=(0, 0), stride=(1, 1)):
             w0, w1 = max(q * sw - pw, 0), min(q * sw - pw + S, W)
             O[:, p, q, :] = I[:, h0:h1, w0:w1, :].reshape(C, -1, N).mean(axis=1)
     return O
+
+
+def pool_max_fprop(I, window, pad=(0, 0), stride=(1, 1)):
+    """I: (C, H, W, N) -> (C, P, Q, N): maximum over the part of each window inside the image
+    (np.max of the same slices as the mean, ngraph/transformers/cpu/cpuengine.py:297-300)."""
+    C, H, W, N = I.shape
+    R, S = window
+    ph, pw = pad
+    sh, sw = stride
+    P = (H + 2 * ph - R) // sh + 1
+    Q = (W + 2 * pw - S) // sw + 1
+    O = np.zeros((C, P, Q, N), dtype=I.dtype)
+    for p in range(P):
+        for q in range(Q):
+            h0, h1 = max(p * sh - ph, 0), min(p * sh - ph + R, H)
+            w0, w1 = max(q * sw - pw, 0), min(q * sw - pw + S, W)
+            O[:, p, q, :] = I[:, h0:h1, w0:w1, :].reshape(C, -1, N).max(axis=1)
+    return O

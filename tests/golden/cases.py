@@ -511,7 +511,51 @@ def mlp_c1_train_step(ng, shard=None):
                           digest=True)
 
 
+def batchnorm_train(ng, C=16, H=8, W=8, N=32, rho=0.9, eps=1e-3):
+    """BatchNormalization in training mode as the reference's layer composes it
+    (ngraph/frontends/neon/layer.py:1244-1256): batch mean and variance per channel, the running
+    statistics updated in place, the batch normalised with gamma and beta.  The value returned
+    also contains the inference formula evaluated on the running statistics AFTER their update,
+    so the in-place assignments are part of what is compared."""
+    r = _rng(21)
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    Cx = ax(C, "C")
+    x = ng.placeholder([Cx, ax(1, "D"), ax(H, "H"), ax(W, "W"), ax(N, "N")])
+    gamma = ng.variable([Cx], initial_value=r.uniform(0.5, 1.5, C).astype(np.float32))
+    beta = ng.variable([Cx], initial_value=r.uniform(-0.5, 0.5, C).astype(np.float32))
+    gmean = ng.persistent_tensor(axes=[Cx], initial_value=0.)
+    gvar = ng.persistent_tensor(axes=[Cx], initial_value=1.)
+    xmean = ng.mean(x, out_axes=[Cx])
+    xvar = ng.variance(x, out_axes=[Cx])
+    y_train = gamma * ((x - xmean) * ng.reciprocal(ng.sqrt(xvar + eps))) + beta
+    y_infer = gamma * ((x - gmean) * ng.reciprocal(ng.sqrt(gvar + eps))) + beta
+    out = ng.sequential([
+        ng.assign(gmean, gmean * rho + xmean * (1.0 - rho)),
+        ng.assign(gvar, gvar * rho + xvar * (1.0 - rho)),
+        y_train + 0.5 * y_infer,
+    ])
+    vals = [(_rng(22).standard_normal((C, 1, H, W, N)) * 1.7 + 0.4).astype(np.float32)]
+    return [out], [x], vals
+
+
+def pool_max(ng, C=12, H=9, W=11, N=32, R=3, S=3, pad=1, stride=2):
+    """Max pooling forward with padding and stride (the reference's PoolingOp, np.max over the
+    in-image part of each window, ngraph/transformers/cpu/cpuengine.py:286-300)."""
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    P = (H + 2 * pad - R) // stride + 1
+    Q = (W + 2 * pad - S) // stride + 1
+    Cx, D, Nx = ax(C, "C"), ax(1, "D"), ax(N, "N")
+    x = ng.placeholder([Cx, D, ax(H, "H"), ax(W, "W"), Nx])
+    pool = dict(op="max", J=1, T=1, R=R, S=S, pad_c=0, pad_d=0, pad_h=pad, pad_w=pad,
+                str_c=1, str_d=1, str_h=stride, str_w=stride)
+    out = ng.pooling(pool, x, axes=[Cx, D, ax(P, "P"), ax(Q, "Q"), Nx])
+    vals = [_rng(31).standard_normal((C, 1, H, W, N)).astype(np.float32)]
+    return [ng.tanh(out) + out], [x], vals
+
+
 CASES = {
+    "pool_max": pool_max,
+    "batchnorm_train": batchnorm_train,
     "mlp_train_step": mlp_train_step,
     "mlp_c1_train_step": mlp_c1_train_step,
     "resnet_train_step": resnet_train_step,
@@ -534,5 +578,5 @@ CASES = {
     "assign_sequence": assign_sequence,
 }
 # cases evaluated twice in a row (state carried by variables)
-REPEAT = {"assign_sequence": 2, "mlp_train_step": 2, "mlp_c1_train_step": 2,
+REPEAT = {"batchnorm_train": 2, "assign_sequence": 2, "mlp_train_step": 2, "mlp_c1_train_step": 2,
           "resnet_train_step": 2}

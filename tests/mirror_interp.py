@@ -94,8 +94,9 @@ class Interp(object):
         if isinstance(op, g.PoolingOp):
             i = self.eval(op.args[0])
             pp = op.pool_params
-            out = co.pool_avg_fprop(i[:, 0], (pp["R"], pp["S"]), (pp["pad_h"], pp["pad_w"]),
-                                    (pp["str_h"], pp["str_w"]))
+            fn = co.pool_max_fprop if pp["op"] == "max" else co.pool_avg_fprop
+            out = fn(i[:, 0], (pp["R"], pp["S"]), (pp["pad_h"], pp["pad_w"]),
+                     (pp["str_h"], pp["str_w"]))
             return out[:, None].reshape(op.axes.lengths)
         if isinstance(op, g.AllReduceOp):
             return self.eval(op.args[0])

@@ -129,6 +129,31 @@ def test_pool_avg(flex):
         np.testing.assert_allclose(out.cpu().numpy(), exp, rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("flex", [0, 1])
+def test_pool_max(flex):
+    """Max pooling with padding and stride: exact in both storage types (the maximum of stored
+    values; a flex16 result keeps the input's exponent)."""
+    import torch
+    from ngraph_python_b200 import lib
+    Cc, H, W, N, R, S, pad, stride = 12, 9, 11, 32, 3, 3, 1, 2
+    P, Q = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
+    rng = np.random.RandomState(6)
+    if flex:
+        x = rng.randint(-30000, 30000, (Cc, H, W, N)).astype(np.int16)
+    else:
+        x = rng.standard_normal((Cc, H, W, N)).astype(np.float32)
+    dx = torch.from_numpy(x).cuda()
+    out = torch.zeros((Cc, P, Q, N), dtype=dx.dtype, device="cuda")
+    stat = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    lib.check(lib.raw().b2_pool_max_fprop(dx.data_ptr(), out.data_ptr(), flex, Cc, H, W, N, P, Q,
+                                          R, S, pad, pad, stride, stride, stat.data_ptr(), 0))
+    torch.cuda.synchronize()
+    exp = co.pool_max_fprop(x, (R, S), (pad, pad), (stride, stride))
+    assert np.array_equal(out.cpu().numpy(), exp)
+    if flex:
+        assert int(stat.item()) == int(np.abs(exp.astype(np.int64)).max())
+
+
 # ---- the two training contractions ------------------------------------------------------------
 # shapes of ResNet-20's layers (scaled down in H, W, N) plus ragged ones; the update contraction of
 # the larger ones runs in several K slices

@@ -32,6 +32,10 @@ def test_pool_oracle():
     np.testing.assert_allclose(out[:, 0, 0, :], x.reshape(2, 16, 3).mean(axis=1))
     out = co.pool_avg_fprop(x, (2, 2), stride=(2, 2))
     np.testing.assert_allclose(out[1, 1, 0, 2], x[1, 2:4, 0:2, 2].mean())
+    out = co.pool_max_fprop(x, (3, 3), pad=(1, 1), stride=(2, 2))
+    assert out.shape == (2, 2, 2, 3)
+    assert out[1, 0, 0, 2] == x[1, 0:2, 0:2, 2].max()          # window clipped by the padding
+    assert out[0, 1, 1, 1] == x[0, 1:4, 1:4, 1].max()
 
 
 @pytest.mark.parametrize("shape", [(3, 7, 6, 4, 5, 3, 3, 1, 1), (4, 9, 8, 2, 6, 3, 2, 1, 2),
