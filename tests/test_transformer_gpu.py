@@ -55,9 +55,13 @@ def test_fusion_reduces_launches():
     assert unfused >= 10     # the reference's one-kernel-per-op count for this graph
 
 
+# (batchnorm_train is fp32 only: the reference's flex transformer does not run batch normalisation
+# either -- ngraph/frontends/neon/tests/test_batchnorm_layer.py:148,251 skip it -- and the running
+# statistics, which start at 0 and 1 and grow by a tenth of the batch value per call, overrun
+# the exponent autoflex picks from their history)
 FLEX_CASES = ["c2_fused", "ew_4d", "reduce_4d_axis1", "recip_add_sum", "broadcast_bias",
               "assign_sequence", "conv_basic", "conv_stride2_1x1", "conv_stride2_3x3", "conv_grads",
-              "conv_grads_stride2", "mlp_forward", "batchnorm_train", "pool_max",
+              "conv_grads_stride2", "mlp_forward", "pool_max",
               "resnet8_small", "resnet20"]
 
 
