@@ -301,6 +301,17 @@ int b2_pool_max_fprop(const void* I, void* O, int32_t flex, int32_t C, int32_t H
                       int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S, int32_t pad_h,
                       int32_t pad_w, int32_t str_h, int32_t str_w, int32_t* stats_slot,
                       void* stream);
+/* Gradient of pooling with respect to its input (BpropPoolOp; arithmetic and summation order of
+ * ngraph/transformers/cpu/cpuengine.py:306-336).  avg: every element of a window receives
+ * E / (elements of the window inside the image); max: the first maximum of the window (np.argmax
+ * order) receives E, found again from the pooled tensor I (unused, may be NULL, for avg).
+ * flex16: fp32 arithmetic, one quantisation with slotGI's exponent, statistic or probe (bit
+ * pattern of max |fp32 result| into *probe_out) as for the other flex16 entry points. */
+int b2_pool_bprop(const void* E, const void* I, void* GI, int32_t flex, int32_t is_max, int32_t C,
+                  int32_t H, int32_t W, int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S,
+                  int32_t pad_h, int32_t pad_w, int32_t str_h, int32_t str_w,
+                  const b2_flex_scale* table, int32_t slotE, int32_t slotGI, int32_t* stats,
+                  uint64_t* probe_out, int32_t probe, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1768,6 +1768,86 @@ extern "C" int b2_conv_update_flex16(const int16_t* I, const int16_t* E, int16_t
                                           probe ? 1 : 0, (cudaStream_t)stream);
 }
 
+// Gradient of pooling with respect to its input, gathered per input element (consecutive threads =
+// consecutive images): the windows (p, q) that contain (h, w) are visited in increasing (p, q) --
+// the order in which the reference's loop adds them (ngraph/transformers/cpu/cpuengine.py:316-336).
+// avg: E / (elements of the window inside the image); max: E where (h, w) is the FIRST maximum of
+// the window in row-major order (np.argmax).  flex16: fp32 arithmetic on scale_E * mantissa, one
+// quantisation with the result's exponent; probe: the bit pattern of max |fp32 result|.
+template <typename T, bool MAX>
+__global__ void __launch_bounds__(256)
+pool_bprop_kernel(const T* __restrict__ E, const T* __restrict__ I, T* __restrict__ GI, int C, int H,
+                  int W, int N, int P, int Q, int R, int S, int pad_h, int pad_w, int str_h,
+                  int str_w, const b2_flex_scale* __restrict__ table, int slotE, int slotG,
+                  int* stats, unsigned long long* probe_out, int probe) {
+    const long long total = (long long)C * H * W * N;
+    const bool flex = sizeof(T) == 2;
+    const float sE = flex ? table[slotE].scale : 1.0f;
+    const float qG = flex && !probe ? table[slotG].inv_scale : 1.0f;
+    float fstat = 0.0f, fmax = 0.0f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int n = (int)(i % N);
+        long long t = i / N;
+        const int w = (int)(t % W); t /= W;
+        const int h = (int)(t % H);
+        const int c = (int)(t / H);
+        // windows with p*str - pad <= h < p*str - pad + R
+        int p0 = h + pad_h - R + 1;
+        p0 = p0 <= 0 ? 0 : (p0 + str_h - 1) / str_h;
+        int p1 = (h + pad_h) / str_h;
+        if (p1 > P - 1) p1 = P - 1;
+        int q0 = w + pad_w - S + 1;
+        q0 = q0 <= 0 ? 0 : (q0 + str_w - 1) / str_w;
+        int q1 = (w + pad_w) / str_w;
+        if (q1 > Q - 1) q1 = Q - 1;
+        float acc = 0.0f;
+        for (int p = p0; p <= p1; ++p)
+            for (int q = q0; q <= q1; ++q) {
+                const int h0 = max(p * str_h - pad_h, 0), h1 = min(p * str_h - pad_h + R, H);
+                const int w0 = max(q * str_w - pad_w, 0), w1 = min(q * str_w - pad_w + S, W);
+                const float e = sE * (float)E[(((long long)c * P + p) * Q + q) * N + n];
+                if (MAX) {
+                    // is (h, w) the first maximum of the window?
+                    const T mine = I[i];
+                    bool first = true;
+                    for (int hh = h0; hh < h1 && first; ++hh)
+                        for (int ww = w0; ww < w1; ++ww) {
+                            const T v = I[(((long long)c * H + hh) * W + ww) * N + n];
+                            const bool before = hh < h || (hh == h && ww < w);
+                            if (v > mine || (before && v == mine)) { first = false; break; }
+                        }
+                    if (first) acc += e;
+                } else {
+                    const int cnt = (h1 - h0) * (w1 - w0);
+                    acc += e * (1.0f / (float)cnt);
+                }
+            }
+        if (!flex) {
+            GI[i] = (T)acc;
+        } else if (probe) {
+            fmax = fmaxf(fmax, fabsf(acc));
+        } else {
+            float v = acc * qG;
+            v = (v != v) ? 0.0f : v;
+            v = fminf(fmaxf(v, -32768.0f), 32767.0f);
+            fstat = fmaxf(fstat, fabsf(v));
+            GI[i] = (T)(__float_as_int(v + 12582912.0f) - 0x4B400000);
+        }
+    }
+    if (flex) {
+        if (probe) {
+            unsigned bits = __float_as_uint(fmax);
+            for (int o = 16; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+            if ((threadIdx.x & 31) == 0 && bits) atomicMax(probe_out, (unsigned long long)bits);
+        } else {
+            int stat = (int)rintf(fstat);
+            for (int o = 16; o > 0; o >>= 1) stat = max(stat, __shfl_xor_sync(0xffffffffu, stat, o));
+            if ((threadIdx.x & 31) == 0 && stat) atomicMax(stats + slotG, stat);
+        }
+    }
+}
+
 namespace {
 int run_pool(bool is_max, const void* I, void* O, int32_t flex, int32_t C, int32_t H, int32_t W,
              int32_t N, int32_t P, int32_t Q, int32_t R, int32_t S, int32_t pad_h, int32_t pad_w,
@@ -1808,4 +1888,38 @@ extern "C" int b2_pool_max_fprop(const void* I, void* O, int32_t flex, int32_t C
                                  int32_t* stats_slot, void* stream) {
     return run_pool(true, I, O, flex, C, H, W, N, P, Q, R, S, pad_h, pad_w, str_h, str_w,
                     stats_slot, stream);
+}
+
+extern "C" int b2_pool_bprop(const void* E, const void* I, void* GI, int32_t flex, int32_t is_max,
+                             int32_t C, int32_t H, int32_t W, int32_t N, int32_t P, int32_t Q,
+                             int32_t R, int32_t S, int32_t pad_h, int32_t pad_w, int32_t str_h,
+                             int32_t str_w, const b2_flex_scale* table, int32_t slotE,
+                             int32_t slotGI, int32_t* stats, uint64_t* probe_out, int32_t probe,
+                             void* stream) {
+    B2_REQUIRE(E && GI && C > 0 && H > 0 && W > 0 && N > 0 && P > 0 && Q > 0 && R > 0 && S > 0 &&
+               str_h > 0 && str_w > 0, "bad pooling argument");
+    B2_REQUIRE(!is_max || I, "the gradient of max pooling needs the pooled tensor");
+    if (flex) {
+        B2_REQUIRE(table && slotE >= 0 && slotGI >= 0, "flex pooling gradient needs the scale table");
+        B2_REQUIRE(probe ? probe_out != nullptr : stats != nullptr, "missing statistics destination");
+    }
+    const long long total = (long long)C * H * W * N;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned long long* po = (unsigned long long*)probe_out;
+#define B2_PB_LAUNCH(T, MAXV)                                                                       \
+    pool_bprop_kernel<T, MAXV><<<(unsigned)blocks, 256, 0, st>>>(                                  \
+        (const T*)E, (const T*)I, (T*)GI, C, H, W, N, P, Q, R, S, pad_h, pad_w, str_h, str_w, table, \
+        slotE, slotGI, stats, po, probe ? 1 : 0)
+    if (flex) {
+        if (is_max) B2_PB_LAUNCH(short, true);
+        else B2_PB_LAUNCH(short, false);
+    } else {
+        if (is_max) B2_PB_LAUNCH(float, true);
+        else B2_PB_LAUNCH(float, false);
+    }
+#undef B2_PB_LAUNCH
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
 }

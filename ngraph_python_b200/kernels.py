@@ -448,6 +448,54 @@ class PoolStep(_Step):
         t.kernel_launches += 1
 
 
+class PoolBpropStep(_Step):
+    """Gradient of average or max pooling with respect to the pooled tensor."""
+    kind = "pool_bprop"
+    launches = 1
+    probe_is_float = True
+
+    def __init__(self, index, op, t):
+        super(PoolBpropStep, self).__init__(index, op)
+        pp = op.pool_params
+        if pp["op"] not in ("avg", "max"):
+            raise ValueError("Unhandled op: only average and max pooling are implemented: {}"
+                             .format(op))
+        if int(pp.get("J", 1)) != 1 or int(pp.get("T", 1)) != 1:
+            raise ValueError("Unhandled op: pooling over channels or depth")
+        ev, iv, ov = t._view_of(op.args[0]), t._view_of(op.args[1]), t._view_of(op)
+        for v in (ev, iv):
+            if not v.is_dense():
+                raise ValueError("Unhandled op: pooling gradient operands must be dense tensors")
+        Cc, D, H, W, N = iv.axes.lengths
+        K, M, P, Q, N2 = ev.axes.lengths
+        self.is_max = int(pp["op"] == "max")
+        self.args = (Cc, H, W, N, P, Q, int(pp["R"]), int(pp["S"]), int(pp.get("pad_h", 0)),
+                     int(pp.get("pad_w", 0)), int(pp.get("str_h", 1)), int(pp.get("str_w", 1)))
+        self.in_views = [ev, iv]
+        self.out_views = [ov]
+        self.flex = t.flex
+
+    def launch(self, t):
+        ev, iv = self.in_views
+        ov = self.out_views[0]
+        raw = lib.raw()
+        st = t.stream.cuda_stream
+        if not self.flex:
+            lib.check(raw.b2_pool_bprop(self._ptr(ev), self._ptr(iv), self._ptr(ov), 0, self.is_max,
+                                        *(self.args + (None, -1, -1, None, None, 0, st))))
+            t.kernel_launches += 1
+            return
+        t._slot_for_read(iv.buffer, self)
+        slots = (t._slot_for_read(ev.buffer, self), ov.buffer.slot_write)
+
+        def call(probe):
+            lib.check(raw.b2_pool_bprop(self._ptr(ev), self._ptr(iv), self._ptr(ov), 1, self.is_max,
+                                        *(self.args + (t._table.data_ptr(), slots[0], slots[1],
+                                                       t._stats.data_ptr(), t._probe64.data_ptr(),
+                                                       probe, st))))
+        self._flex_probe_then(t, ov.buffer, [ev.buffer, iv.buffer], call)
+
+
 class CommStep(_Step):
     """One tensor's share of a bucketed allreduce (see comm.py).  The tensor lives inside the
     flat fp32 arena; when this step is the last of its bucket the collective for the whole bucket

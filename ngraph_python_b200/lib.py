@@ -119,6 +119,8 @@ def _load():
                                         i32, i32, i32, vp, vp]),
         "b2_pool_max_fprop": (C.c_int, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32,
                                         i32, i32, i32, vp, vp]),
+        "b2_pool_bprop": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32,
+                                    i32, i32, i32, i32, vp, i32, i32, vp, vp, i32, vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),

@@ -24,7 +24,7 @@ import ngraph.op_graph.op_graph as ref
 from ngraph.op_graph.convolution import ConvolutionOp as RefConvolutionOp
 from ngraph.op_graph.convolution import bprop_conv as ref_bprop_conv
 from ngraph.op_graph.convolution import update_conv as ref_update_conv
-from ngraph.op_graph.pooling import PoolingOp as RefPoolingOp
+from ngraph.op_graph.pooling import PoolingOp as RefPoolingOp, BpropPoolOp as RefBpropPoolOp
 from ngraph.transformers.base import Transformer
 
 from . import op_graph as b2
@@ -119,6 +119,9 @@ class GraphTranslator(object):
             return b2.update_conv(args[0], args[1], fprop.args[1], fprop)
         if isinstance(op, RefPoolingOp):
             return b2.pooling(dict(op.pool_params), args[0], self.axes(op.axes))
+        if isinstance(op, RefBpropPoolOp):            # args (delta,); the pooled tensor via fprop
+            fprop = self(op.fprop)
+            return b2.bprop_pool(args[0], fprop.args[0], fprop)
         if isinstance(op, ref.ContiguousOp):
             return b2.value_of(args[0])
         raise ValueError("Unhandled op: {}".format(op))

@@ -589,6 +589,29 @@ def pooling(pool_params, inputs, axes, **kw):
     return PoolingOp(pool_params, inputs, make_axes(axes), **kw)
 
 
+class BpropPoolOp(Op):
+    """Gradient of a PoolingOp with respect to its input (ngraph/op_graph/pooling.py:70-93):
+    args (delta C,M,P,Q,N ; the pooled tensor C,D,H,W,N), result on the pooled tensor's axes."""
+
+    def __init__(self, delta, inputs, fprop, **kw):
+        delta, inputs = as_op(delta), as_op(inputs)
+        if not isinstance(fprop, PoolingOp):
+            raise ValueError("bprop_pool needs the forward PoolingOp, got {}".format(fprop))
+        if delta.axes.lengths != fprop.axes.lengths:
+            raise ValueError("bprop_pool: delta has shape %s, the pooling result %s"
+                             % (delta.axes.lengths, fprop.axes.lengths))
+        super(BpropPoolOp, self).__init__((delta, inputs), inputs.axes, **kw)
+        self.fprop = fprop
+
+    @property
+    def pool_params(self):
+        return self.fprop.pool_params
+
+
+def bprop_pool(delta, inputs, fprop):
+    return BpropPoolOp(delta, inputs, fprop)
+
+
 # ---- communication ----------------------------------------------------------------------------
 class AllReduceOp(Op):
     """Sum (or mean) of a tensor over all data-parallel replicas; every replica gets the result

@@ -24,7 +24,8 @@ from . import lib
 from . import comm as commmod
 from .op_graph import (AllReduceOp, AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp,
                        ConvolutionOp, DotOp, bprop_conv, update_conv,
-                       ElementWiseOp, Op, PoolingOp, ReductionOp, ReorderAxes, SequentialOp,
+                       BpropPoolOp, ElementWiseOp, Op, PoolingOp, ReductionOp, ReorderAxes,
+                       SequentialOp,
                        ViewOp, as_op, make_axes)
 
 
@@ -700,6 +701,8 @@ class _Planner(object):
             step = kernels.ConvUpdateStep(index, op, self.t)
         elif isinstance(op, PoolingOp):
             step = kernels.PoolStep(index, op, self.t)
+        elif isinstance(op, BpropPoolOp):
+            step = kernels.PoolBpropStep(index, op, self.t)
         else:
             raise ValueError("Unhandled op: {}".format(op))
         # the step must come after everything its arguments depend on; steps are appended in

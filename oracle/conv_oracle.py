@@ -109,3 +109,32 @@ def pool_max_fprop(I, window, pad=(0, 0), stride=(1, 1)):
             w0, w1 = max(q * sw - pw, 0), min(q * sw - pw + S, W)
             O[:, p, q, :] = I[:, h0:h1, w0:w1, :].reshape(C, -1, N).max(axis=1)
     return O
+
+
+def pool_bprop(E, I, window, pad=(0, 0), stride=(1, 1), op="avg"):
+    """E: (C, P, Q, N), I: (C, H, W, N) -> gradient of the pooling with respect to I, windows
+    visited in (p, q) order as in ngraph/transformers/cpu/cpuengine.py:316-336.  avg: every
+    in-image element of a window gets E * (1 / their number); max: the first maximum (np.argmax
+    over the window in row-major order) gets E."""
+    C, H, W, N = I.shape
+    R, S = window
+    ph, pw = pad
+    sh, sw = stride
+    P = (H + 2 * ph - R) // sh + 1
+    Q = (W + 2 * pw - S) // sw + 1
+    assert E.shape == (C, P, Q, N)
+    G = np.zeros((C, H, W, N), dtype=np.float32)
+    cols = np.arange(N)
+    for p in range(P):
+        for q in range(Q):
+            h0, h1 = max(p * sh - ph, 0), min(p * sh - ph + R, H)
+            w0, w1 = max(q * sw - pw, 0), min(q * sw - pw + S, W)
+            for c in range(C):
+                patch = G[c, h0:h1, w0:w1, :].reshape(-1, N).copy()
+                if op == "max":
+                    arg = np.argmax(I[c, h0:h1, w0:w1, :].reshape(-1, N), axis=0)
+                    patch[arg, cols] += E[c, p, q, :]
+                else:
+                    patch += E[c, p, q, :] * np.float32(1.0 / patch.shape[0])
+                G[c, h0:h1, w0:w1, :] = patch.reshape(h1 - h0, w1 - w0, N)
+    return G

@@ -553,7 +553,40 @@ def pool_max(ng, C=12, H=9, W=11, N=32, R=3, S=3, pad=1, stride=2):
     return [ng.tanh(out) + out], [x], vals
 
 
+def _pool_grad_op(ng):
+    """bprop_pool: the reference keeps BpropPoolOp in ngraph.op_graph.pooling."""
+    if hasattr(ng, "bprop_pool"):
+        return ng.bprop_pool
+    from ngraph.op_graph.pooling import BpropPoolOp
+    return lambda delta, inputs, fprop: BpropPoolOp(delta, inputs, fprop)
+
+
+def pool_grads(ng, op="max", C=6, H=9, W=11, N=32, R=3, S=3, pad=1, stride=2):
+    """Pooling forward and its input gradient for a given error tensor, overlapping windows
+    (3x3, stride 2, padding 1): what the reference's autodiff emits for a pooling layer."""
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    P = (H + 2 * pad - R) // stride + 1
+    Q = (W + 2 * pad - S) // stride + 1
+    Cx, D, Nx = ax(C, "C"), ax(1, "D"), ax(N, "N")
+    x = ng.placeholder([Cx, D, ax(H, "H"), ax(W, "W"), Nx])
+    delta = ng.placeholder([Cx, D, ax(P, "P"), ax(Q, "Q"), Nx])
+    pool = dict(op=op, J=1, T=1, R=R, S=S, pad_c=0, pad_d=0, pad_h=pad, pad_w=pad,
+                str_c=1, str_d=1, str_h=stride, str_w=stride)
+    out = ng.pooling(pool, x, axes=delta.axes)
+    gi = _pool_grad_op(ng)(delta, x, out)
+    r = _rng(41)
+    vals = [r.standard_normal((C, 1, H, W, N)).astype(np.float32),
+            r.standard_normal((C, 1, P, Q, N)).astype(np.float32)]
+    return [out, gi], [x, delta], vals
+
+
+def pool_grads_avg(ng):
+    return pool_grads(ng, op="avg")
+
+
 CASES = {
+    "pool_grads": pool_grads,
+    "pool_grads_avg": pool_grads_avg,
     "pool_max": pool_max,
     "batchnorm_train": batchnorm_train,
     "mlp_train_step": mlp_train_step,

@@ -91,6 +91,12 @@ class Interp(object):
             out = co.conv_update(i[:, 0], e[:, 0], op.axes.lengths[2:4], (cp["pad_h"], cp["pad_w"]),
                                  (cp["str_h"], cp["str_w"]))
             return out[:, None].reshape(op.axes.lengths)
+        if isinstance(op, g.BpropPoolOp):
+            e, i = self.eval(op.args[0]), self.eval(op.args[1])
+            pp = op.pool_params
+            out = co.pool_bprop(e[:, 0], i[:, 0], (pp["R"], pp["S"]), (pp["pad_h"], pp["pad_w"]),
+                                (pp["str_h"], pp["str_w"]), pp["op"])
+            return out[:, None].reshape(op.axes.lengths)
         if isinstance(op, g.PoolingOp):
             i = self.eval(op.args[0])
             pp = op.pool_params

@@ -154,6 +154,57 @@ def test_pool_max(flex):
         assert int(stat.item()) == int(np.abs(exp.astype(np.int64)).max())
 
 
+@pytest.mark.parametrize("op", ["avg", "max"])
+@pytest.mark.parametrize("flex", [0, 1])
+def test_pool_bprop(flex, op):
+    """Gradient of pooling (overlapping windows, padding): fp32 equals the oracle's loop bit for
+    bit (same order of additions); flex16 is the fp32 value quantised once."""
+    import torch
+    from ngraph_python_b200 import lib
+    from oracle import flex_oracle as fx
+    Cc, H, W, N, R, S, pad, stride = 6, 9, 11, 32, 3, 3, 1, 2
+    P, Q = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
+    rng = np.random.RandomState(8)
+    if flex:
+        xi = rng.randint(-30000, 30000, (Cc, H, W, N)).astype(np.int16)
+        xi[:, 2:4, 3:6, :] = 777                      # ties: the first maximum must win
+        ei = rng.randint(-30000, 30000, (Cc, P, Q, N)).astype(np.int16)
+        dec_e = 12
+        x, e = xi.astype(np.float32), ei.astype(np.float32) * np.float32(2.0 ** -dec_e)
+    else:
+        x = rng.standard_normal((Cc, H, W, N)).astype(np.float32)
+        x[:, 2:4, 3:6, :] = 0.5
+        e = rng.standard_normal((Cc, P, Q, N)).astype(np.float32)
+        xi, ei = x, e
+    exp = co.pool_bprop(e, x, (R, S), (pad, pad), (stride, stride), op)
+    dx, de = torch.from_numpy(xi).cuda(), torch.from_numpy(ei).cuda()
+    out = torch.zeros((Cc, H, W, N), dtype=dx.dtype, device="cuda")
+    raw = lib.raw()
+    if not flex:
+        lib.check(raw.b2_pool_bprop(de.data_ptr(), dx.data_ptr(), out.data_ptr(), 0, int(op == "max"),
+                                    Cc, H, W, N, P, Q, R, S, pad, pad, stride, stride, None, -1, -1,
+                                    None, None, 0, 0))
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), exp)
+        return
+    dec_g = fx.fit_dec(float(np.abs(exp).max()))
+    table = torch.tensor([[2.0 ** -dec_e, 2.0 ** dec_e], [2.0 ** -dec_g, 2.0 ** dec_g]],
+                         dtype=torch.float32, device="cuda")
+    stats = torch.zeros((2,), dtype=torch.int32, device="cuda")
+    probe = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    for pr in (1, 0):
+        lib.check(raw.b2_pool_bprop(de.data_ptr(), dx.data_ptr(), out.data_ptr(), 1, int(op == "max"),
+                                    Cc, H, W, N, P, Q, R, S, pad, pad, stride, stride,
+                                    table.data_ptr(), 0, 1, stats.data_ptr(), probe.data_ptr(), pr, 0))
+    torch.cuda.synchronize()
+    got_max = np.array([int(probe.item())], dtype=np.uint32).view(np.float32)[0]
+    assert got_max == np.float32(np.abs(exp).max())
+    want = fx.quantize(exp, dec_g).astype(np.int64)
+    got = out.cpu().numpy().astype(np.int64)
+    assert np.array_equal(got, want)
+    assert int(stats[1].item()) == int(np.abs(got).max())
+
+
 # ---- the two training contractions ------------------------------------------------------------
 # shapes of ResNet-20's layers (scaled down in H, W, N) plus ragged ones; the update contraction of
 # the larger ones runs in several K slices

@@ -96,3 +96,22 @@ def test_folding_the_output_step_into_the_epilogue_is_exact():
         plain = ((res + (acc * f + bias).astype(np.float32)).astype(np.float32) * q).astype(np.float32)
         folded = (res * q + (acc * (f * q) + bias * q).astype(np.float32)).astype(np.float32)
         assert np.array_equal(plain, folded)
+
+
+@pytest.mark.parametrize("op", ["avg", "max"])
+def test_pool_gradient_oracle_is_the_adjoint(op):
+    """<pool(I + t d), E> differentiated at t = 0 equals <d, pool_bprop(E)> (max: away from
+    ties, where the pooling is differentiable)."""
+    rng = np.random.RandomState(4)
+    I = rng.standard_normal((3, 7, 8, 4)).astype(np.float64)
+    E = rng.standard_normal((3, 4, 4, 4)).astype(np.float64)
+    d = rng.standard_normal(I.shape)
+    ana = (co.pool_bprop(E.astype(np.float32), I.astype(np.float32), (3, 3), (1, 1), (2, 2), op)
+           .astype(np.float64) * d).sum()
+    if op == "avg":                     # linear: <pool(d), E> itself
+        num = (co.pool_avg_fprop(d.astype(np.float32), (3, 3), (1, 1), (2, 2)).astype(np.float64) * E).sum()
+    else:
+        eps = 1e-6
+        num = ((co.pool_max_fprop(I + eps * d, (3, 3), (1, 1), (2, 2)) -
+                co.pool_max_fprop(I - eps * d, (3, 3), (1, 1), (2, 2))) * E).sum() / (2 * eps)
+    assert abs(num - ana) <= 2e-3 * max(1.0, abs(ana))

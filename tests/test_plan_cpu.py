@@ -25,7 +25,8 @@ def test_every_case_plans_and_compiles(name, flex):
         if s.kind == "ew":
             assert "b2_ew_main" in s.kernel.source()
         else:
-            assert s.kind in ("gemm", "conv", "conv_bprop", "conv_update", "pool", "comm") and s.launches >= 0
+            assert s.kind in ("gemm", "conv", "conv_bprop", "conv_update", "pool", "pool_bprop",
+                              "comm") and s.launches >= 0
 
 
 def test_c2_is_one_kernel():
