@@ -313,6 +313,24 @@ int b2_pool_bprop(const void* E, const void* I, void* GI, int32_t flex, int32_t 
                   const b2_flex_scale* table, int32_t slotE, int32_t slotGI, int32_t* stats,
                   uint64_t* probe_out, int32_t probe, void* stream);
 
+/* Lookup table (embedding).  lut_axis 0: lut [V][F], out / delta [n_idx][F], dW [V][F];
+ * lut_axis 1: lut [F][V], out / delta [F][n_idx], dW [F][V].  Indices are values of the tensor
+ * idx (fp32, or flex16 mantissas with the scale of slot_idx), rounded to the nearest integer.
+ *   fprop:  out = lut.take(idx, axis)                (rows outside [0, V) read as zero);
+ *           flex16: mantissas are copied, the result carries the table's exponent
+ *   update: dW[w] = sum of the rows of delta whose index is w, in increasing position; the row
+ *           pad_idx (pass -1 for none) and rows never looked up are zero
+ * replaces LUTBpropKernel / fprop_lut / update_lut (ngraph/transformers/gpu/lut.py,
+ * ngraph/transformers/cpu/cpuengine.py:421-435).  flex16 update: fp32 sums, one quantisation with
+ * slot_dW's exponent, statistic or probe as for b2_pool_bprop. */
+int b2_lut_fprop(const void* lut, const void* idx, void* out, int32_t flex, int32_t lut_axis,
+                 int32_t V, int32_t F, int32_t n_idx, const b2_flex_scale* table,
+                 int32_t slot_idx, void* stream);
+int b2_lut_update(const void* delta, const void* idx, void* dW, int32_t flex, int32_t lut_axis,
+                  int32_t V, int32_t F, int32_t n_idx, int32_t pad_idx, const b2_flex_scale* table,
+                  int32_t slot_delta, int32_t slot_idx, int32_t slot_dW, int32_t* stats,
+                  uint64_t* probe_out, int32_t probe, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

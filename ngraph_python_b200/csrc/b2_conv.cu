@@ -1923,3 +1923,140 @@ extern "C" int b2_pool_bprop(const void* E, const void* I, void* GI, int32_t fle
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }
+
+// ---- lookup table (embedding) ----------------------------------------------------------------
+namespace {
+// index held as fp32, or as a flex16 mantissa with its tensor's scale
+template <typename T>
+__device__ __forceinline__ int lut_index(const T* idx, int i, float s) {
+    return (int)rintf(s * (float)idx[i]);
+}
+
+// out = lut.take(idx, axis): lut_axis 0: lut [V][F], out [n][F]; lut_axis 1: lut [F][V], out [F][n]
+template <typename T>
+__global__ void __launch_bounds__(256)
+lut_fprop_kernel(const T* __restrict__ lut, const T* __restrict__ idx, T* __restrict__ out,
+                 int lut_axis, int V, int F, int n, const b2_flex_scale* __restrict__ table,
+                 int slotI) {
+    const float s_idx = table ? table[slotI].scale : 1.0f;
+    const long long total = (long long)n * F;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (long long)gridDim.x * blockDim.x) {
+        const int i = lut_axis == 0 ? (int)(e / F) : (int)(e % n);
+        const int f = lut_axis == 0 ? (int)(e % F) : (int)(e / n);
+        const int w = lut_index(idx, i, s_idx);
+        T v = (T)0;
+        if (w >= 0 && w < V) v = lut_axis == 0 ? lut[(long long)w * F + f] : lut[(long long)f * V + w];
+        out[e] = v;
+    }
+}
+
+// dW[w] = sum of the rows of delta whose index is w, rows added in increasing position (the order
+// of np.sum over the group, ngraph/transformers/cpu/cpuengine.py:425-435); pad_idx stays zero.
+// One thread per element of dW; the indices are staged through shared memory 256 at a time.
+template <typename T>
+__global__ void __launch_bounds__(256)
+lut_update_kernel(const T* __restrict__ delta, const T* __restrict__ idx, T* __restrict__ dW,
+                  int lut_axis, int V, int F, int n, int pad_idx, const b2_flex_scale* table,
+                  int slotD, int slotI, int slotW, int* stats, unsigned long long* probe_out,
+                  int probe) {
+    __shared__ int widx[256];
+    const bool flex = sizeof(T) == 2;
+    const float sD = flex ? table[slotD].scale : 1.0f;
+    const float sI = flex ? table[slotI].scale : 1.0f;
+    const float qW = flex && !probe ? table[slotW].inv_scale : 1.0f;
+    const long long total = (long long)V * F;
+    const long long rounds = (total + (long long)gridDim.x * 256 - 1) / ((long long)gridDim.x * 256);
+    float fstat = 0.0f, fmax = 0.0f;
+    for (long long r = 0; r < rounds; ++r) {
+        const long long e = (r * gridDim.x + blockIdx.x) * 256 + threadIdx.x;
+        const bool live = e < total;
+        const int w = live ? (lut_axis == 0 ? (int)(e / F) : (int)(e % V)) : -1;
+        const int f = live ? (lut_axis == 0 ? (int)(e % F) : (int)(e / V)) : 0;
+        float acc = 0.0f;
+        for (int base = 0; base < n; base += 256) {
+            __syncthreads();
+            if (base + (int)threadIdx.x < n) widx[threadIdx.x] = lut_index(idx, base + threadIdx.x, sI);
+            __syncthreads();
+            const int m = min(256, n - base);
+            if (live && w != pad_idx)
+                for (int j = 0; j < m; ++j)
+                    if (widx[j] == w) {
+                        const int i = base + j;
+                        acc += sD * (float)(lut_axis == 0 ? delta[(long long)i * F + f]
+                                                          : delta[(long long)f * n + i]);
+                    }
+        }
+        if (!live) continue;
+        if (!flex) {
+            dW[e] = (T)acc;
+        } else if (probe) {
+            fmax = fmaxf(fmax, fabsf(acc));
+        } else {
+            float v = acc * qW;
+            v = (v != v) ? 0.0f : v;
+            v = fminf(fmaxf(v, -32768.0f), 32767.0f);
+            fstat = fmaxf(fstat, fabsf(v));
+            dW[e] = (T)(__float_as_int(v + 12582912.0f) - 0x4B400000);
+        }
+    }
+    if (flex) {
+        if (probe) {
+            unsigned bits = __float_as_uint(fmax);
+            for (int o = 16; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+            if ((threadIdx.x & 31) == 0 && bits) atomicMax(probe_out, (unsigned long long)bits);
+        } else {
+            int stat = (int)rintf(fstat);
+            for (int o = 16; o > 0; o >>= 1) stat = max(stat, __shfl_xor_sync(0xffffffffu, stat, o));
+            if ((threadIdx.x & 31) == 0 && stat) atomicMax(stats + slotW, stat);
+        }
+    }
+}
+}  // namespace
+
+extern "C" int b2_lut_fprop(const void* lut, const void* idx, void* out, int32_t flex,
+                            int32_t lut_axis, int32_t V, int32_t F, int32_t n_idx,
+                            const b2_flex_scale* table, int32_t slot_idx, void* stream) {
+    B2_REQUIRE(lut && idx && out && V > 0 && F > 0 && n_idx > 0 && (lut_axis == 0 || lut_axis == 1),
+               "bad lookup-table argument");
+    B2_REQUIRE(!flex || (table && slot_idx >= 0), "flex lookup needs the scale table");
+    long long blocks = ((long long)n_idx * F + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (flex)
+        lut_fprop_kernel<short><<<(unsigned)blocks, 256, 0, st>>>(
+            (const short*)lut, (const short*)idx, (short*)out, lut_axis, V, F, n_idx, table, slot_idx);
+    else
+        lut_fprop_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(
+            (const float*)lut, (const float*)idx, (float*)out, lut_axis, V, F, n_idx, nullptr, 0);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_lut_update(const void* delta, const void* idx, void* dW, int32_t flex,
+                             int32_t lut_axis, int32_t V, int32_t F, int32_t n_idx, int32_t pad_idx,
+                             const b2_flex_scale* table, int32_t slot_delta, int32_t slot_idx,
+                             int32_t slot_dW, int32_t* stats, uint64_t* probe_out, int32_t probe,
+                             void* stream) {
+    B2_REQUIRE(delta && idx && dW && V > 0 && F > 0 && n_idx > 0 && (lut_axis == 0 || lut_axis == 1),
+               "bad lookup-table argument");
+    if (flex) {
+        B2_REQUIRE(table && slot_delta >= 0 && slot_idx >= 0 && slot_dW >= 0,
+                   "flex lookup update needs the scale table");
+        B2_REQUIRE(probe ? probe_out != nullptr : stats != nullptr, "missing statistics destination");
+    }
+    long long blocks = ((long long)V * F + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned long long* po = (unsigned long long*)probe_out;
+    if (flex)
+        lut_update_kernel<short><<<(unsigned)blocks, 256, 0, st>>>(
+            (const short*)delta, (const short*)idx, (short*)dW, lut_axis, V, F, n_idx, pad_idx, table,
+            slot_delta, slot_idx, slot_dW, stats, po, probe ? 1 : 0);
+    else
+        lut_update_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(
+            (const float*)delta, (const float*)idx, (float*)dW, lut_axis, V, F, n_idx, pad_idx, nullptr,
+            0, 0, 0, nullptr, nullptr, 0);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}

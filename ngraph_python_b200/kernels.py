@@ -496,6 +496,82 @@ class PoolBpropStep(_Step):
         self._flex_probe_then(t, ov.buffer, [ev.buffer, iv.buffer], call)
 
 
+class LutStep(_Step):
+    """Embedding lookup; a flex output keeps the table's exponent (its mantissas are copied)."""
+    kind = "lut"
+    launches = 1
+
+    def __init__(self, index, op, t):
+        super(LutStep, self).__init__(index, op)
+        lv, xv, ov = t._view_of(op.args[0]), t._view_of(op.args[1]), t._view_of(op)
+        for v in (lv, xv):
+            if not v.is_dense():
+                raise ValueError("Unhandled op: lookup operands must be dense tensors")
+        self.lut_axis = op.lut_axis
+        self.V = lv.axes.lengths[op.lut_axis]
+        self.F = lv.axes.lengths[1 - op.lut_axis]
+        self.n = xv.axes.lengths[0]
+        if t.flex:
+            t._share_entry(ov.buffer, lv.buffer)
+        self.in_views = [lv, xv]
+        self.out_views = [ov]
+        self.flex = t.flex
+
+    def output_buffers(self):
+        return []          # no exponent of its own to manage
+
+    def launch(self, t):
+        lv, xv = self.in_views
+        ov = self.out_views[0]
+        table, slot = (t._table.data_ptr(), t._slot_for_read(xv.buffer, self)) if self.flex else (None, -1)
+        lib.check(lib.raw().b2_lut_fprop(self._ptr(lv), self._ptr(xv), self._ptr(ov), int(self.flex),
+                                         self.lut_axis, self.V, self.F, self.n, table, slot,
+                                         t.stream.cuda_stream))
+        t.kernel_launches += 1
+
+
+class LutUpdateStep(_Step):
+    """Gradient of an embedding table: rows of delta added up per looked-up index."""
+    kind = "lut_update"
+    launches = 1
+    probe_is_float = True
+
+    def __init__(self, index, op, t):
+        super(LutUpdateStep, self).__init__(index, op)
+        dv, xv, ov = t._view_of(op.args[0]), t._view_of(op.args[1]), t._view_of(op)
+        for v in (dv, xv):
+            if not v.is_dense():
+                raise ValueError("Unhandled op: lookup update operands must be dense tensors")
+        self.lut_axis = op.lut_axis
+        self.V = ov.axes.lengths[op.lut_axis]
+        self.F = ov.axes.lengths[1 - op.lut_axis]
+        self.n = xv.axes.lengths[0]
+        self.pad_idx = -1 if op.pad_idx is None else int(op.pad_idx)
+        self.in_views = [dv, xv]
+        self.out_views = [ov]
+        self.flex = t.flex
+
+    def launch(self, t):
+        dv, xv = self.in_views
+        ov = self.out_views[0]
+        raw = lib.raw()
+        st = t.stream.cuda_stream
+        head = (self._ptr(dv), self._ptr(xv), self._ptr(ov))
+        dims = (self.lut_axis, self.V, self.F, self.n, self.pad_idx)
+        if not self.flex:
+            lib.check(raw.b2_lut_update(*(head + (0,) + dims + (None, -1, -1, -1, None, None, 0, st))))
+            t.kernel_launches += 1
+            return
+        slots = (t._slot_for_read(dv.buffer, self), t._slot_for_read(xv.buffer, self),
+                 ov.buffer.slot_write)
+
+        def call(probe):
+            lib.check(raw.b2_lut_update(*(head + (1,) + dims + (
+                t._table.data_ptr(), slots[0], slots[1], slots[2], t._stats.data_ptr(),
+                t._probe64.data_ptr(), probe, st))))
+        self._flex_probe_then(t, ov.buffer, [dv.buffer, xv.buffer], call)
+
+
 class CommStep(_Step):
     """One tensor's share of a bucketed allreduce (see comm.py).  The tensor lives inside the
     flat fp32 arena; when this step is the last of its bucket the collective for the whole bucket

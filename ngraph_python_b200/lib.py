@@ -121,6 +121,9 @@ def _load():
                                         i32, i32, i32, vp, vp]),
         "b2_pool_bprop": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32,
                                     i32, i32, i32, i32, vp, i32, i32, vp, vp, i32, vp]),
+        "b2_lut_fprop": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]),
+        "b2_lut_update": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, i32,
+                                    vp, vp, i32, vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),

@@ -25,6 +25,7 @@ from ngraph.op_graph.convolution import ConvolutionOp as RefConvolutionOp
 from ngraph.op_graph.convolution import bprop_conv as ref_bprop_conv
 from ngraph.op_graph.convolution import update_conv as ref_update_conv
 from ngraph.op_graph.pooling import PoolingOp as RefPoolingOp, BpropPoolOp as RefBpropPoolOp
+from ngraph.op_graph.lookuptable import LookupTableOp as RefLookupTableOp, update_lut as ref_update_lut
 from ngraph.transformers.base import Transformer
 
 from . import op_graph as b2
@@ -122,6 +123,11 @@ class GraphTranslator(object):
         if isinstance(op, RefBpropPoolOp):            # args (delta,); the pooled tensor via fprop
             fprop = self(op.fprop)
             return b2.bprop_pool(args[0], fprop.args[0], fprop)
+        if isinstance(op, RefLookupTableOp):
+            return b2.lookuptable(args[0], args[1], self.axes(op.axes), pad_idx=op.pad_idx)
+        if isinstance(op, ref_update_lut):            # args (delta, idx); the table via fprop
+            fprop = self(op.fprop)
+            return b2.update_lut(args[0], fprop.args[0], args[1], fprop)
         if isinstance(op, ref.ContiguousOp):
             return b2.value_of(args[0])
         raise ValueError("Unhandled op: {}".format(op))

@@ -612,6 +612,61 @@ def bprop_pool(delta, inputs, fprop):
     return BpropPoolOp(delta, inputs, fprop)
 
 
+class LookupTableOp(Op):
+    """out = lut.take(idx, axis) (ngraph/op_graph/lookuptable.py:55-118): lut is 2-d, idx 1-d;
+    the output axes name the index axis in place of the lut axis that is looked up."""
+
+    def __init__(self, lut, idx, axes, update=True, pad_idx=None, **kw):
+        lut, idx = as_op(lut), as_op(idx)
+        axes = make_axes(axes)
+        if len(lut.axes) != 2:
+            raise ValueError("lookup table shape must be length 2, found {}".format(len(lut.axes)))
+        if len(idx.axes) != 1:
+            raise ValueError("index shape must be length 1, found {}".format(len(idx.axes)))
+        if not (lut.axes[0] in axes or lut.axes[1] in axes):
+            raise ValueError("Output axes must indicate which axis to do lookup.  None of the "
+                             "output axes is from lookup table.")
+        if idx.axes[0] not in axes:
+            raise ValueError("Output axes must index axes.")
+        self.lut_axis = 0 if lut.axes[1] in axes else 1
+        self.pad_idx = pad_idx
+        self.update = update
+        if axes[self.lut_axis] != idx.axes[0]:
+            raise ValueError("Cannot transpose lut axes implicitly")
+        super(LookupTableOp, self).__init__((lut, idx), axes, **kw)
+
+
+def lookuptable(lut, idx, axes, update=True, pad_idx=None, **kw):
+    return LookupTableOp(lut, idx, axes, update=True, pad_idx=pad_idx)
+
+
+class update_lut(Op):    # noqa: N801  (the reference's name)
+    """Gradient of the table: args (delta, idx), result on the table's axes
+    (ngraph/op_graph/lookuptable.py:160-175)."""
+
+    def __init__(self, delta, lut, idx, fprop, **kw):
+        delta, lut, idx = as_op(delta), as_op(lut), as_op(idx)
+        if not isinstance(fprop, LookupTableOp):
+            raise ValueError("update_lut needs the forward LookupTableOp, got {}".format(fprop))
+        if delta.axes.lengths != fprop.axes.lengths:
+            raise ValueError("update_lut: delta has shape %s, the lookup result %s"
+                             % (delta.axes.lengths, fprop.axes.lengths))
+        super(update_lut, self).__init__((delta, idx), lut.axes, **kw)
+        self.fprop = fprop
+
+    @property
+    def lut_axis(self):
+        return self.fprop.lut_axis
+
+    @property
+    def pad_idx(self):
+        return self.fprop.pad_idx
+
+
+def lookuptable_update(delta, lut, idx, fprop_op):
+    return update_lut(delta, lut, idx, fprop_op)
+
+
 # ---- communication ----------------------------------------------------------------------------
 class AllReduceOp(Op):
     """Sum (or mean) of a tensor over all data-parallel replicas; every replica gets the result

@@ -24,8 +24,8 @@ from . import lib
 from . import comm as commmod
 from .op_graph import (AllReduceOp, AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp,
                        ConvolutionOp, DotOp, bprop_conv, update_conv,
-                       BpropPoolOp, ElementWiseOp, Op, PoolingOp, ReductionOp, ReorderAxes,
-                       SequentialOp,
+                       BpropPoolOp, ElementWiseOp, LookupTableOp, Op, PoolingOp, ReductionOp,
+                       ReorderAxes, SequentialOp, update_lut,
                        ViewOp, as_op, make_axes)
 
 
@@ -703,6 +703,10 @@ class _Planner(object):
             step = kernels.PoolStep(index, op, self.t)
         elif isinstance(op, BpropPoolOp):
             step = kernels.PoolBpropStep(index, op, self.t)
+        elif isinstance(op, LookupTableOp):
+            step = kernels.LutStep(index, op, self.t)
+        elif isinstance(op, update_lut):
+            step = kernels.LutUpdateStep(index, op, self.t)
         else:
             raise ValueError("Unhandled op: {}".format(op))
         # the step must come after everything its arguments depend on; steps are appended in

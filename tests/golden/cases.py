@@ -584,7 +584,41 @@ def pool_grads_avg(ng):
     return pool_grads(ng, op="avg")
 
 
+def lut_embedding(ng, V=50, F=24, n=40, pad_idx=0, lut_axis=0):
+    """Embedding lookup and the gradient of the table for a given error tensor, with repeated
+    indices and a padding index (the reference's LookupTableOp / update_lut,
+    ngraph/op_graph/lookuptable.py; tests/transformer_dependent/test_lookuptable.py builds the
+    same pair)."""
+    ax = lambda k, nm: ng.make_axis(k, name=nm)   # noqa: E731
+    Vx, Fx, Nx = ax(V, "V"), ax(F, "F"), ax(n, "NI")
+    r = _rng(51)
+    lut_axes = [Vx, Fx] if lut_axis == 0 else [Fx, Vx]
+    out_axes = [Nx, Fx] if lut_axis == 0 else [Fx, Nx]
+    lut = ng.placeholder(lut_axes)
+    idx = ng.placeholder([Nx])
+    delta = ng.placeholder(out_axes)
+    out = ng.lookuptable(lut, idx, out_axes, pad_idx=pad_idx)
+    if hasattr(ng, "lookuptable_update"):
+        grad = ng.lookuptable_update(delta, lut, idx, out)
+    else:
+        from ngraph.op_graph.lookuptable import lookuptable_update
+        grad = lookuptable_update(delta, lut, idx, out)
+    idx_val = r.randint(0, V, n).astype(np.float32)
+    if pad_idx is not None:
+        idx_val[::7] = pad_idx
+    idx_val[3::5] = idx_val[3]                       # repeats
+    vals = [r.standard_normal([a.length for a in lut_axes]).astype(np.float32), idx_val,
+            r.standard_normal([a.length for a in out_axes]).astype(np.float32)]
+    return [out * 2.0, grad], [lut, idx, delta], vals
+
+
+def lut_embedding_axis1(ng):
+    return lut_embedding(ng, V=33, F=20, n=48, pad_idx=None, lut_axis=1)
+
+
 CASES = {
+    "lut_embedding": lut_embedding,
+    "lut_embedding_axis1": lut_embedding_axis1,
     "pool_grads": pool_grads,
     "pool_grads_avg": pool_grads_avg,
     "pool_max": pool_max,

@@ -7,6 +7,7 @@ import numpy as np
 
 from ngraph_python_b200 import op_graph as g
 from oracle import conv_oracle as co
+from oracle import lut_oracle as lo
 from oracle import ew_oracle as ew
 
 
@@ -91,6 +92,12 @@ class Interp(object):
             out = co.conv_update(i[:, 0], e[:, 0], op.axes.lengths[2:4], (cp["pad_h"], cp["pad_w"]),
                                  (cp["str_h"], cp["str_w"]))
             return out[:, None].reshape(op.axes.lengths)
+        if isinstance(op, g.LookupTableOp):
+            lut, idx = self.eval(op.args[0]), self.eval(op.args[1])
+            return lo.lut_fprop(lut, idx, op.lut_axis).reshape(op.axes.lengths)
+        if isinstance(op, g.update_lut):
+            delta, idx = self.eval(op.args[0]), self.eval(op.args[1])
+            return lo.lut_update(delta, idx, op.pad_idx, op.lut_axis, op.axes.lengths)
         if isinstance(op, g.BpropPoolOp):
             e, i = self.eval(op.args[0]), self.eval(op.args[1])
             pp = op.pool_params

@@ -205,6 +205,65 @@ def test_pool_bprop(flex, op):
     assert int(stats[1].item()) == int(np.abs(got).max())
 
 
+@pytest.mark.parametrize("axis", [0, 1])
+@pytest.mark.parametrize("flex", [0, 1])
+def test_lookup_table(flex, axis):
+    """Embedding lookup and table gradient against oracle/lut_oracle.py: repeated indices, a
+    padding index, indices never used.  fp32 equal bit for bit (same order of additions)."""
+    import torch
+    from ngraph_python_b200 import lib
+    from oracle import lut_oracle as lo
+    from oracle import flex_oracle as fx
+    V, F, n, pad_idx = 37, 24, 300, 5
+    rng = np.random.RandomState(13 + axis)
+    idx = rng.randint(0, V, n)
+    idx[::9] = pad_idx
+    idx[4::11] = idx[4]
+    tshape = (V, F) if axis == 0 else (F, V)
+    oshape = (n, F) if axis == 0 else (F, n)
+    raw = lib.raw()
+    if not flex:
+        lut = rng.standard_normal(tshape).astype(np.float32)
+        delta = rng.standard_normal(oshape).astype(np.float32)
+        d_lut, d_idx, d_delta = [torch.from_numpy(a).cuda() for a in (lut, idx.astype(np.float32), delta)]
+        out = torch.zeros(oshape, dtype=torch.float32, device="cuda")
+        dW = torch.full(tshape, 7.0, dtype=torch.float32, device="cuda")
+        lib.check(raw.b2_lut_fprop(d_lut.data_ptr(), d_idx.data_ptr(), out.data_ptr(), 0, axis, V, F,
+                                   n, None, -1, 0))
+        lib.check(raw.b2_lut_update(d_delta.data_ptr(), d_idx.data_ptr(), dW.data_ptr(), 0, axis, V,
+                                    F, n, pad_idx, None, -1, -1, -1, None, None, 0, 0))
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), lo.lut_fprop(lut, idx, axis))
+        assert np.array_equal(dW.cpu().numpy(), lo.lut_update(delta, idx, pad_idx, axis, tshape))
+        return
+    lut = rng.randint(-30000, 30000, tshape).astype(np.int16)
+    delta = rng.randint(-30000, 30000, oshape).astype(np.int16)
+    dec_d, dec_i = 11, 0
+    exp = lo.lut_update(delta.astype(np.float32) * np.float32(2.0 ** -dec_d), idx, pad_idx, axis, tshape)
+    dec_w = fx.fit_dec(float(np.abs(exp).max()))
+    d_lut, d_idx, d_delta = [torch.from_numpy(a).cuda() for a in (lut, idx.astype(np.int16), delta)]
+    out = torch.zeros(oshape, dtype=torch.int16, device="cuda")
+    dW = torch.full(tshape, 7, dtype=torch.int16, device="cuda")
+    table = torch.tensor([[2.0 ** -d, 2.0 ** d] for d in (dec_d, dec_i, dec_w)], dtype=torch.float32,
+                         device="cuda")
+    stats = torch.zeros((3,), dtype=torch.int32, device="cuda")
+    probe = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    lib.check(raw.b2_lut_fprop(d_lut.data_ptr(), d_idx.data_ptr(), out.data_ptr(), 1, axis, V, F, n,
+                               table.data_ptr(), 1, 0))
+    for pr in (1, 0):
+        lib.check(raw.b2_lut_update(d_delta.data_ptr(), d_idx.data_ptr(), dW.data_ptr(), 1, axis, V, F,
+                                    n, pad_idx, table.data_ptr(), 0, 1, 2, stats.data_ptr(),
+                                    probe.data_ptr(), pr, 0))
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), lo.lut_fprop(lut, idx, axis))
+    got_max = np.array([int(probe.item())], dtype=np.uint32).view(np.float32)[0]
+    assert got_max == np.float32(np.abs(exp).max())
+    want = fx.quantize(exp, dec_w).astype(np.int64)
+    got = dW.cpu().numpy().astype(np.int64)
+    assert np.array_equal(got, want)
+    assert int(stats[2].item()) == int(np.abs(got).max())
+
+
 # ---- the two training contractions ------------------------------------------------------------
 # shapes of ResNet-20's layers (scaled down in H, W, N) plus ragged ones; the update contraction of
 # the larger ones runs in several K slices

@@ -26,7 +26,7 @@ def test_every_case_plans_and_compiles(name, flex):
             assert "b2_ew_main" in s.kernel.source()
         else:
             assert s.kind in ("gemm", "conv", "conv_bprop", "conv_update", "pool", "pool_bprop",
-                              "comm") and s.launches >= 0
+                              "lut", "lut_update", "comm") and s.launches >= 0
 
 
 def test_c2_is_one_kernel():

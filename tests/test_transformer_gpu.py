@@ -62,6 +62,7 @@ def test_fusion_reduces_launches():
 FLEX_CASES = ["c2_fused", "ew_4d", "reduce_4d_axis1", "recip_add_sum", "broadcast_bias",
               "assign_sequence", "conv_basic", "conv_stride2_1x1", "conv_stride2_3x3", "conv_grads",
               "conv_grads_stride2", "mlp_forward", "pool_max", "pool_grads", "pool_grads_avg",
+              "lut_embedding", "lut_embedding_axis1",
               "resnet8_small", "resnet20"]
 
 
