@@ -209,7 +209,8 @@ def test_pool_bprop(flex, op):
 @pytest.mark.parametrize("flex", [0, 1])
 def test_lookup_table(flex, axis):
     """Embedding lookup and table gradient against oracle/lut_oracle.py: repeated indices, a
-    padding index, indices never used.  fp32 equal bit for bit (same order of additions)."""
+    padding index, indices never used.  fp32 with the table's rows looked up (axis 0): equal bit
+    for bit (same order of additions)."""
     import torch
     from ngraph_python_b200 import lib
     from oracle import lut_oracle as lo
@@ -234,7 +235,13 @@ def test_lookup_table(flex, axis):
                                     F, n, pad_idx, None, -1, -1, -1, None, None, 0, 0))
         torch.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy(), lo.lut_fprop(lut, idx, axis))
-        assert np.array_equal(dW.cpu().numpy(), lo.lut_update(delta, idx, pad_idx, axis, tshape))
+        want = lo.lut_update(delta, idx, pad_idx, axis, tshape)
+        if axis == 0:
+            assert np.array_equal(dW.cpu().numpy(), want)
+        else:
+            # along the contiguous axis numpy adds pairwise once a group has eight members; the
+            # kernel adds in position order: same sums up to fp32 rounding
+            np.testing.assert_allclose(dW.cpu().numpy(), want, rtol=2e-6, atol=2e-6)
         return
     lut = rng.randint(-30000, 30000, tshape).astype(np.int16)
     delta = rng.randint(-30000, 30000, oshape).astype(np.int16)
