@@ -52,6 +52,7 @@ class GraphTranslator(object):
 
     def __init__(self):
         self.memo = {}
+        self.bare = {}       # AssignableTensorOp -> its translation (shared with memo)
         self.axis_memo = {}
 
     def axis(self, a):
@@ -67,9 +68,36 @@ class GraphTranslator(object):
         op = op.forwarded
         if op in self.memo:
             return self.memo[op]
-        out = self._translate(op)
+        out = self.bare[op] if op in self.bare else self._translate(op)
+        if isinstance(op, ref.AssignableTensorOp):
+            self.bare[op] = out
+        # Order is part of the contract (Op.ordered_ops sorts over args and control_deps): an op
+        # that must run after others -- a TensorValueOp reading a tensor after the assignments
+        # that build it, as the adjoint of a slice does -- becomes the last op of a sequential.
+        deps = [d.forwarded for d in getattr(op, "control_deps", ())]
+        if deps and not isinstance(op, ref.ParallelOp):
+            out = b2.sequential([self(d) for d in deps] + [out])
         self.memo[op] = out
         return out
+
+    def _target(self, op):
+        """(translated assignment target without sequencing wrappers, ops that must run first)."""
+        op = op.forwarded
+        before = [self(d.forwarded) for d in getattr(op, "control_deps", ())]
+        if isinstance(op, ref.ValueOp):
+            t, b = self._target(op.value_tensor)
+            return t, before + b
+        if isinstance(op, ref.TensorSliceOp):
+            t, b = self._target(op.args[0])
+            return b2.tensor_slice(t, op.slices, self.axes(op.axes)), before + b
+        if isinstance(op, ref.AxesCastOp):
+            t, b = self._target(op.args[0])
+            return b2.cast_axes(t, self.axes(op.axes)), before + b
+        if isinstance(op, ref.AssignableTensorOp):
+            if op not in self.bare:
+                self.bare[op] = self._translate(op)
+            return self.bare[op], before
+        raise ValueError("Unhandled op: assignment to {}".format(op))
 
     def _translate(self, op):
         name = type(op).__name__
@@ -85,10 +113,18 @@ class GraphTranslator(object):
             return b2.AssignableTensorOp(self.axes(op.axes), init, **kw)
         if isinstance(op, ref.SequentialOp):
             return b2.sequential([self(o) for o in op.ops])
+        if isinstance(op, ref.ParallelOp):              # doall: any order will do; keep the given one
+            return b2.sequential([self(o) for o in op.control_deps])
         if isinstance(op, ref.ValueOp):                 # sigmoid, softmax, mean, ... expand
             return self(op.value_tensor)
         if isinstance(op, ref.AssignOp):
-            return b2.assign(self(op.args[0]), self(op.args[1]))
+            # the target is the tensor (or a view of it) itself; what its description must run
+            # after (a Fill of the same tensor, say) runs before the assignment
+            target, before = self._target(op.args[0])
+            assign = b2.assign(target, self(op.args[1]))
+            return b2.sequential(before + [assign]) if before else assign
+        if isinstance(op, ref.Fill):
+            return b2.assign(self(op.args[0]), b2.constant(float(op.scalar)))
         if isinstance(op, ref.TensorSizeOp):
             # the number of elements along the reduction axes (what mean and variance divide by:
             # ngraph/op_graph/op_graph.py:4012-4029); the reference folds it into a constant too
@@ -106,6 +142,13 @@ class GraphTranslator(object):
             return b2.broadcast(args[0], self.axes(op.axes))
         if isinstance(op, ref.ReorderAxes):
             return b2.axes_with_order(args[0], self.axes(op.axes))
+        if isinstance(op, ref.OneHotOp):
+            # (class axis) + x.axes; element = 1 where the class index equals x
+            classes = self.axes([op.axis])
+            iota = b2.constant(np.arange(classes[0].length, dtype=np.float32), axes=classes)
+            return b2.equal(iota, args[0])
+        if isinstance(op, ref.TensorSliceOp):
+            return b2.tensor_slice(args[0], op.slices, self.axes(op.axes))
         if isinstance(op, ref.AxesCastOp):
             return b2.cast_axes(args[0], self.axes(op.axes))
         if isinstance(op, ref.ExpandDims):

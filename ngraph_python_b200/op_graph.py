@@ -336,6 +336,53 @@ class AxesCastOp(ViewOp):
         super(AxesCastOp, self).__init__((x,), axes, **kw)
 
 
+class TensorSliceOp(ViewOp):
+    """A sliced view: one slice or int per axis of x; an int drops the axis
+    (ngraph/op_graph/op_graph.py:2067-2120).  Negative steps are not supported, as there."""
+
+    def __init__(self, x, slices, axes=None, **kw):
+        x = as_op(x)
+        slices = tuple(slices)
+        if len(slices) != len(x.axes):
+            raise ValueError("There should be one slice in slices for each dimension in input "
+                             "tensor.  Input tensor had {} dimensions, but slices has length {}."
+                             .format(len(x.axes), len(slices)))
+        kept, starts, steps = [], [], []
+        for axis, sl in zip(x.axes, slices):
+            if isinstance(sl, slice):
+                if sl.step is not None and sl.step < 0:
+                    raise ValueError("Negative slice steps are not supported.")
+                start, stop, step = sl.indices(axis.length)
+                n = -(-(stop - start) // step)        # (max / min are reductions in this module)
+                n = n if n > 0 else 0
+                kept.append(axis if (start, n, step) == (0, axis.length, 1)
+                            else make_axis(n, name=axis.name))
+                starts.append(start)
+                steps.append(step)
+            else:
+                idx = int(sl)
+                if idx < 0:
+                    idx += axis.length
+                if not 0 <= idx < axis.length:
+                    raise ValueError("index %d is out of range for axis %s" % (int(sl), axis))
+                starts.append(idx)
+                steps.append(None)          # the axis is dropped
+        if axes is None:
+            axes = kept
+        axes = make_axes(axes)
+        if axes.lengths != make_axes(kept).lengths:
+            raise ValueError("slice result has shape %s, the given axes %s"
+                             % (make_axes(kept).lengths, axes.lengths))
+        super(TensorSliceOp, self).__init__((x,), axes, **kw)
+        self.slices = slices
+        self.starts = tuple(starts)
+        self.steps = tuple(steps)
+
+
+def tensor_slice(x, slices, axes=None):
+    return TensorSliceOp(x, slices, axes)
+
+
 def cast_axes(tensor, axes):
     tensor = as_op(tensor)
     axes = make_axes(axes)
@@ -693,7 +740,10 @@ class AssignOp(Op):
 
     def __init__(self, tensor, val, **kw):
         tensor, val = as_op(tensor), as_op(val)
-        if not isinstance(tensor, AssignableTensorOp):
+        base = tensor
+        while isinstance(base, ViewOp):              # a view of an assignable tensor is assignable
+            base = base.args[0]
+        if not isinstance(base, AssignableTensorOp):
             raise ValueError("{} is not assignable.".format(tensor))
         if not val.axes.is_sub_set(tensor.axes):
             raise ValueError("cannot assign axes %s to a tensor with axes %s" %

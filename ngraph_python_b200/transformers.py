@@ -25,7 +25,7 @@ from . import comm as commmod
 from .op_graph import (AllReduceOp, AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp,
                        ConvolutionOp, DotOp, bprop_conv, update_conv,
                        BpropPoolOp, ElementWiseOp, LookupTableOp, Op, PoolingOp, ReductionOp,
-                       ReorderAxes, SequentialOp, update_lut,
+                       ReorderAxes, SequentialOp, TensorSliceOp, update_lut,
                        ViewOp, as_op, make_axes)
 
 
@@ -427,7 +427,7 @@ class _Planner(object):
             target = op.args[0]
             value_args = [op.args[1]]
             iter_axes = target.axes
-            tbuf = self.t._buffer_of(target)
+            tbuf = self.t._view_of(target).buffer
         else:
             value_args = list(op.args)
             iter_axes = op.args[0].axes if is_red else op.axes
@@ -447,7 +447,7 @@ class _Planner(object):
     def _place_ew_with(self, op, is_assign, is_red, iter_axes, value_args, only):
         if is_assign:
             target = op.args[0]
-            tbuf = self.t._buffer_of(target)
+            tbuf = self.t._view_of(target).buffer
         lower = -1
         for a in value_args:
             base, chain = self._base_tensor(a)
@@ -1096,6 +1096,11 @@ class B200Transformer(object):
         elif isinstance(op, AxesCastOp):
             src = self._view_of(op.args[0])
             v = View(src.buffer, op.axes, src.strides, src.offset)
+        elif isinstance(op, TensorSliceOp):
+            src = self._view_of(op.args[0])
+            offset = src.offset + sum(st * sr for st, sr in zip(op.starts, src.strides))
+            strides = [sr * step for sr, step in zip(src.strides, op.steps) if step is not None]
+            v = View(src.buffer, op.axes, strides, offset)
         elif isinstance(op, AssignOp):
             v = self._view_of(op.args[0])
         else:

@@ -616,7 +616,28 @@ def lut_embedding_axis1(ng):
     return lut_embedding(ng, V=33, F=20, n=48, pad_idx=None, lut_axis=1)
 
 
+def slice_views(ng):
+    """Sliced views read and written: a strided window of the input, an integer index that drops
+    an axis, and an assignment into a slice of a persistent tensor that is read back afterwards
+    (what the reference's adjoint of a slice does, ngraph/op_graph/op_graph.py: UnsliceOp)."""
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    A, B, Cx = ax(6, "A"), ax(10, "B"), ax(3, "C")
+    x = ng.placeholder([A, B, Cx])
+    temp = ng.persistent_tensor(axes=[A, B], initial_value=0.)
+    window = [slice(1, 5), slice(2, 7)]
+    plane = ng.tensor_slice(x, [slice(None), slice(None), 1])            # (A, B): axis C dropped
+    part = ng.tensor_slice(plane, window)                                # (4, 5) window
+    out = ng.sequential([
+        ng.assign(temp, plane * 0.25),
+        ng.assign(ng.tensor_slice(temp, window), ng.tanh(part) + 3.0),
+        temp * 2.0,
+    ])
+    vals = [_rng(61).standard_normal((6, 10, 3)).astype(np.float32)]
+    return [out, ng.sum(part, reduction_axes=[part.axes[1]])], [x], vals
+
+
 CASES = {
+    "slice_views": slice_views,
     "lut_embedding": lut_embedding,
     "lut_embedding_axis1": lut_embedding_axis1,
     "pool_grads": pool_grads,
@@ -645,5 +666,5 @@ CASES = {
     "assign_sequence": assign_sequence,
 }
 # cases evaluated twice in a row (state carried by variables)
-REPEAT = {"batchnorm_train": 2, "assign_sequence": 2, "mlp_train_step": 2, "mlp_c1_train_step": 2,
+REPEAT = {"slice_views": 2, "batchnorm_train": 2, "assign_sequence": 2, "mlp_train_step": 2, "mlp_c1_train_step": 2,
           "resnet_train_step": 2}

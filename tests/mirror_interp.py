@@ -45,7 +45,12 @@ class Interp(object):
             return self.state[op]
         if isinstance(op, g.AssignOp):
             tgt, val = op.args
-            self.state[tgt] = np.array(self._to(self.eval(val), val.axes, tgt.axes), copy=True)
+            new = np.array(self._to(self.eval(val), val.axes, tgt.axes), copy=True)
+            if isinstance(tgt, g.TensorSliceOp):          # assignment into a slice of a tensor
+                base = self.eval(tgt.args[0])             # the state array itself
+                base[tgt.slices] = new.reshape(base[tgt.slices].shape)
+            else:
+                self.state[tgt] = new
             return None
         if op in self.cache:
             return self.cache[op]
@@ -56,6 +61,8 @@ class Interp(object):
     def _compute(self, op):
         if isinstance(op, (g.BroadcastOp, g.ReorderAxes)):
             return self._to(self.eval(op.args[0]), op.args[0].axes, op.axes)
+        if isinstance(op, g.TensorSliceOp):
+            return np.asarray(self.eval(op.args[0]))[op.slices].reshape(op.axes.lengths)
         if isinstance(op, g.AxesCastOp):
             return self.eval(op.args[0]).reshape(op.axes.lengths)
         if isinstance(op, g.ElementWiseOp):

@@ -63,3 +63,51 @@ def test_translated_graph_matches_reference_cpu(name):
             atol = 2e-5 * max(1.0, float(np.max(np.abs(exp))))
             np.testing.assert_allclose(got.reshape(exp.shape), exp, rtol=2e-4, atol=atol,
                                        err_msg="%s output %d call %d" % (name, k, rep))
+
+
+def test_neon_model_with_reference_autodiff_and_optimizer():
+    """A small convolutional network built with the reference's neon frontend, differentiated by
+    the reference's autodiff and updated by its GradientDescentMomentum: the translated graph
+    (pooling and convolution gradients, slices and their adjoints, control dependencies, one-hot
+    targets) plans for the device, and evaluated with numpy it follows the reference CPU
+    transformer through three training steps."""
+    from ngraph.frontends.neon import (Sequential, Convolution, Pooling, Affine, Rectlin, Softmax,
+                                       GaussianInit, ConstantInit, GradientDescentMomentum, ax)
+    ax.N.length = 32
+    ax.Y.length = 10
+    C, D = rng.make_axis(3, name="C"), rng.make_axis(1, name="D")
+    H, W = rng.make_axis(16, name="H"), rng.make_axis(16, name="W")
+    x = rng.placeholder([C, D, H, W, ax.N])
+    t = rng.placeholder([ax.N])
+    init = GaussianInit(0., 0.1)
+    model = Sequential([
+        Convolution((3, 3, 8), filter_init=init, strides=1, padding=1, activation=Rectlin()),
+        Pooling((2, 2), strides=2, pool_type="max"),
+        Convolution((3, 3, 16), filter_init=init, strides=2, padding=1, activation=Rectlin()),
+        Pooling((2, 2), strides=2, pool_type="avg"),
+        Affine(weight_init=init, bias_init=ConstantInit(0.), activation=Softmax(), axes=(ax.Y,))])
+    loss = rng.cross_entropy_multi(model(x), rng.one_hot(t, axis=ax.Y))
+    updates = GradientDescentMomentum(0.1, 0.9)(loss)
+    train = rng.sequential([updates, rng.mean(loss, out_axes=[])])
+    for flex in (False, True):
+        tr = ngt.make_transformer_factory("b200", plan_only=True, flex=flex)()
+        comp = tr.computation(train, x, t)
+        tr.initialize()
+        kinds = [s.kind for s in comp.impl.steps]
+        assert kinds.count("conv") == 2 and kinds.count("conv_update") == 2
+        assert kinds.count("conv_bprop") == 1 and kinds.count("pool_bprop") == 2
+        assert kinds.count("gemm") == 3
+        tr.close()
+    rs = np.random.RandomState(3)
+    xv = rs.standard_normal((3, 1, 16, 16, 32)).astype(np.float32)
+    tv = rs.randint(0, 10, 32).astype(np.float32)
+    cpu = ngt.make_transformer_factory("cpu")()
+    cref = cpu.computation(train, x, t)
+    want = [float(cref(xv, tv)) for _ in range(3)]
+    cpu.close()
+    trn = plugin.GraphTranslator()
+    m_train, m_x, m_t = trn(train), trn(x), trn(t)
+    it = Interp()
+    got = [float(np.asarray(it.run([m_train], {m_x: xv, m_t: tv})[0])) for _ in range(3)]
+    assert want[2] < want[0]                      # it does train
+    np.testing.assert_allclose(got, want, rtol=2e-5)
