@@ -253,8 +253,8 @@ class ConvStep(_PlaneUser, _Step):
         cp = op.conv_params
         Cc, D, H, W, N = iv.axes.lengths
         C2, T, R, S, K = fv.axes.lengths
-        K2, M, P, Q, N2 = ov.axes.lengths
-        if K2 != K or N2 != N:
+        K2, M, P, Q, N2 = op.axes.lengths          # (the tail's tensor may lack the unit axes)
+        if K2 != K or N2 != N or ov.buffer.size != K2 * M * P * Q * N2:
             raise ValueError("convolution output axes do not match filter/input axes")
         d = lib.ConvDims()
         d.C, d.D, d.H, d.W, d.N = Cc, D, H, W, N

@@ -47,6 +47,14 @@ _REDUCE = {"Sum": b2.sum, "Prod": b2.prod, "Max": b2.max, "Min": b2.min, "Argmax
            "Argmin": b2.argmin}
 
 
+def _is_zero(op):
+    """A scalar constant 0 of the mirror graph (possibly broadcast)."""
+    while isinstance(op, b2.ViewOp):
+        op = op.args[0]
+    return (isinstance(op, b2.AssignableTensorOp) and getattr(op, "is_scalar_constant", False) and
+            float(np.asarray(op.initial_value)) == 0.0)
+
+
 class GraphTranslator(object):
     """reference Op -> ngraph_python_b200 Op, memoised."""
 
@@ -133,6 +141,15 @@ class GraphTranslator(object):
         if name in _UNARY:
             return _UNARY[name](args[0])
         if name in _BINARY:
+            # The reference's Rectlin is maximum(x, 0) + slope * minimum(x, 0) with slope 0 for a
+            # plain ReLU; its SimplePrune pass folds the dead half away
+            # (ngraph/transformers/passes/passes.py), and so does this translation.
+            if name == "Multiply" and (_is_zero(args[0]) or _is_zero(args[1])):
+                return b2.constant(0.0)
+            if name == "Add" and _is_zero(args[1]) and args[0].axes == self.axes(op.axes):
+                return args[0]
+            if name == "Add" and _is_zero(args[0]) and args[1].axes == self.axes(op.axes):
+                return args[1]
             return _BINARY[name](args[0], args[1])
         if name in _REDUCE:
             return _REDUCE[name](args[0], reduction_axes=self.axes(op.reduction_axes))

@@ -645,17 +645,25 @@ class _Planner(object):
                     break
                 other = nxt.args[1 - mine[0]]
                 obase, ochain = self._base_tensor(other)
-                if tuple(nxt.axes.lengths) != tuple(conv.axes.lengths):
+                # (same shape up to axes of length 1: the reference's layers drop the unit depth
+                # axis of the result with a slice before the activation)
+                if [n for n in nxt.axes.lengths if n != 1] != [n for n in conv.axes.lengths if n != 1]:
                     break
                 if nxt.opname == "add" and not info["relu"]:
                     is_bias = (len(obase.axes) == 1 and obase.axes[0].length == chan and
                                obase.axes[0] == nxt.axes[0] and not self._is_scalar_const(obase))
-                    same = (not ochain and tuple(obase.axes.lengths) == tuple(nxt.axes.lengths)
-                            and obase.axes == nxt.axes)
+                    if ochain:
+                        # a view of the other tensor that still walks it in memory order (the
+                        # reference's layers drop a unit axis with a slice)
+                        oview = t._view_of(self._resolve(other))
+                        same = oview.is_dense() and oview.axes == nxt.axes
+                    else:
+                        same = (tuple(obase.axes.lengths) == tuple(nxt.axes.lengths)
+                                and obase.axes == nxt.axes)
                     if is_bias and info["bias"] is None and info["residual"] is None:
                         info["bias"] = obase
                     elif same and info["residual"] is None and not isinstance(obase, AssignableTensorOp):
-                        info["residual"] = obase
+                        info["residual"] = other if ochain else obase
                     else:
                         break
                 elif nxt.opname == "maximum" and not info["relu"] and self._is_scalar_const(obase) \

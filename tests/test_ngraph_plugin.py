@@ -111,3 +111,64 @@ def test_neon_model_with_reference_autodiff_and_optimizer():
     got = [float(np.asarray(it.run([m_train], {m_x: xv, m_t: tv})[0])) for _ in range(3)]
     assert want[2] < want[0]                      # it does train
     np.testing.assert_allclose(got, want, rtol=2e-5)
+
+
+def _reference_resnet(train):
+    """The reference's own CIFAR-10 ResNet builder (examples/resnet/resnet.py: BuildResnet), 8
+    layers, without batch normalisation -- the network of the headline benchmark, built by the
+    reference's code rather than by this package's restatement of it."""
+    sys.path.insert(0, os.path.join(REF, "examples", "resnet"))
+    from resnet import BuildResnet
+    from ngraph.frontends.neon import ax, GradientDescentMomentum, Layer
+    n = 32 if train else 128         # (128 images: the convolutions can run on the tile kernel)
+    ax.N.length = n
+    ax.Y.length = 10
+    C, H, W = rng.make_axis(3, name="C"), rng.make_axis(32, name="H"), rng.make_axis(32, name="W")
+    x = rng.placeholder([C, H, W, ax.N])
+    t = rng.placeholder([ax.N])
+    np.random.seed(0)
+    model = BuildResnet('cifar10', 8, False, 1, batch_norm=False)
+    rs = np.random.RandomState(1)
+    xv = rs.uniform(0, 255, (3, 32, 32, n)).astype(np.float32)
+    tv = rs.randint(0, 10, n).astype(np.float32)
+    if not train:
+        with Layer.inference_mode_on():
+            return model(x), [x], [xv]
+    loss = rng.cross_entropy_multi(model(x), rng.one_hot(t, axis=ax.Y))
+    updates = GradientDescentMomentum(0.01, 0.9)(loss)
+    return rng.sequential([updates, rng.mean(loss, out_axes=[])]), [x, t], [xv, tv]
+
+
+@pytest.mark.parametrize("train", [False, True])
+def test_reference_resnet_builder(train):
+    """Inference: the layers' bias / ReLU / residual tails fold into the convolution steps in
+    flex16.  Training: every convolution gets its filter gradient, all but the first their input
+    gradient, from the ops the reference's autodiff created.  Both: the translated graph, evaluated
+    with numpy, agrees with the reference CPU transformer."""
+    out, params, vals = _reference_resnet(train)
+    for flex in (False, True):
+        tr = ngt.make_transformer_factory("b200", plan_only=True, flex=flex)()
+        comp = tr.computation(out, *params)
+        tr.initialize()
+        kinds = [s.kind for s in comp.impl.steps]
+        assert kinds.count("conv") == 10 and kinds.count("pool") == 1
+        if train:
+            assert kinds.count("conv_update") == 10 and kinds.count("conv_bprop") == 9
+            assert kinds.count("pool_bprop") == 1 and kinds.count("gemm") == 3
+        else:
+            assert kinds.count("gemm") == 1
+            if flex:
+                assert kinds.count("ew") <= 6          # tails folded into the convolutions
+        tr.close()
+    cpu = ngt.make_transformer_factory("cpu")()
+    cref = cpu.computation(out, *params)
+    reps = 3 if train else 1
+    want = [np.array(cref(*vals), copy=True) for _ in range(reps)]
+    cpu.close()
+    trn = plugin.GraphTranslator()
+    m_out = trn(out)
+    m_params = [trn(p) for p in params]
+    it = Interp()
+    got = [np.asarray(it.run([m_out], dict(zip(m_params, vals)))[0]) for _ in range(reps)]
+    for g_, w_ in zip(got, want):
+        np.testing.assert_allclose(g_, w_, rtol=2e-5, atol=2e-6)
