@@ -147,7 +147,7 @@ int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const* out, const
  * the variant must already exist (b2_ew_compile builds the one for 16-byte-aligned pointers,
  * probe == 0).  The first call on a device resolves the array's address -- make it before any
  * stream capture.  All calls share the array: launches that overlap on the GPU race. */
-#define B2_EW_BUILTIN_SCRATCH_BYTES (1 << 20)
+#define B2_EW_BUILTIN_SCRATCH_BYTES (16 * 1024)
 int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* in, void* const* out,
                                  const float* consts, const b2_flex_scale* flex_table,
                                  int32_t* flex_stats, int32_t* status, int probe, void* stream);

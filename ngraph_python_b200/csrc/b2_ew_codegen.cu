@@ -1142,7 +1142,7 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
 // gives them a fixed array that lives in the library's device image instead of a caller buffer.
 //
 // Limits and rules:
-//   * the array is B2_EW_BUILTIN_SCRATCH_BYTES (1 MiB) per device, held by every GPU that loads
+//   * the array is B2_EW_BUILTIN_SCRATCH_BYTES (16 KiB) per device, held by every GPU that loads
 //     the library until the process exits; a launch that needs more is refused with an error;
 //   * the first call on a device looks the array's device address up (cudaGetSymbolAddress, with
 //     that device current) and remembers it; make that first call outside any stream capture;

@@ -230,7 +230,7 @@ class EwKernel(object):
     def launch_builtin_scratch(self, in_ptrs, out_ptrs, consts=(), flex_table=0, flex_stats=0,
                                status=0, probe=False, stream=0):
         """Same launch through the entry point that allocates nothing: split reductions use the
-        1 MiB scratch array that lives inside the library instead of a caller buffer."""
+        16 KiB scratch array that lives inside the library instead of a caller buffer."""
         ins = (C.c_void_p * max(1, len(in_ptrs)))(*in_ptrs)
         outs = (C.c_void_p * max(1, len(out_ptrs)))(*out_ptrs)
         for i, c in enumerate(consts):

@@ -1,9 +1,10 @@
 """Generates tests/golden/fixtures/<case>.npz by running each case of cases.py on the
 reference's own CPU transformer.  Run in a container that has the reference tree:
 
-    python tests/golden/make_fixtures.py /path/to/ngraph-python
+    python tests/golden/make_fixtures.py [/path/to/ngraph-python] [case ...]
 
-The reference is imported unmodified through the small compatibility shims in ref_shims/.
+Without a path the tree named by B200NG_REFERENCE, else oracle/_ref/ (oracle/make_ref.py), is
+used.  The reference is imported unmodified through the compatibility shims of oracle/ref_shims/.
 """
 import os
 import sys
@@ -11,13 +12,15 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.join(HERE, "ref_shims"))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 
 def main(ref_root, only=None):
-    import ref_bootstrap
-    ref_bootstrap.install(ref_root)
+    from oracle import ref_env
+    if ref_root:
+        os.environ["B200NG_REFERENCE"] = ref_root
+    if ref_env.install() is None:
+        raise SystemExit("no reference tree: pass its path or run oracle/make_ref.py")
     import ngraph as ng
     import ngraph.transformers as ngt
     from tests.golden import cases
@@ -40,4 +43,6 @@ def main(ref_root, only=None):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", set(sys.argv[2:]))
+    argv = sys.argv[1:]
+    root = argv.pop(0) if argv and os.path.isdir(argv[0]) else None
+    main(root, set(argv))

@@ -108,13 +108,22 @@ def _free_port():
 
 
 def _rank_main(rank, world, port, flex, case, capture, q):
+    import datetime
+    import traceback
     import torch
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", rank))
+    # a rank that leaves early must not hold memory bound to an NVLink multicast object
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank),
+                                timeout=datetime.timedelta(seconds=60))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+        return
     try:
         from ngraph_python_b200.comm import TorchDistComm
         outs, params, vals = cases.CASES[case](ng, shard=(rank, world))
@@ -125,11 +134,18 @@ def _rank_main(rank, world, port, flex, case, capture, q):
         if capture:
             comp.capture()      # graphs between the NCCL exchanges; the second step replays them
         results.append([np.array(r, copy=True) for r in comp(*vals)])
-        q.put((rank, results))
+        q.put((rank, "ok", results))
         dist.barrier()
         t.close()
+    except Exception:
+        # the parent fails at once with this traceback and ends the other rank, which would
+        # otherwise sit in a collective until the process-group timeout
+        q.put((rank, "error", traceback.format_exc()))
     finally:
-        dist.destroy_process_group()
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
 
 
 @pytest.mark.parametrize("capture", [False, True])
@@ -147,10 +163,20 @@ def test_train_step_two_gpus(flex, case, capture):
     procs = [ctx.Process(target=_rank_main, args=(r, 2, port, flex, case, capture, q)) for r in range(2)]
     for p in procs:
         p.start()
-    got = dict(q.get(timeout=300) for _ in range(2))
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    got = {}
+    try:
+        for _ in range(2):
+            rank, state, payload = q.get(timeout=300)
+            assert state == "ok", "rank %d failed:\n%s" % (rank, payload)
+            got[rank] = payload
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=30)
     for rank in (0, 1):
         if flex:
             _check_flex(got[rank], fix, case)

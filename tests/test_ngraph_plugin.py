@@ -4,20 +4,18 @@ through ngraph.transformers.make_transformer_factory('b200'), are translated to 
 op surface and planned; the translated graphs are also evaluated with numpy and compared with
 the fixtures that the reference CPU transformer produced for the same graphs."""
 import os
-import sys
 
 import numpy as np
 import pytest
 
-REF = "/root/reference"
-if not os.path.isdir(os.path.join(REF, "ngraph")):
-    pytest.skip("reference tree not present", allow_module_level=True)
+from oracle import ref_env  # noqa: E402
+
+REF = ref_env.install()
+if REF is None:
+    pytest.skip("reference tree not present (oracle/make_ref.py makes oracle/_ref)",
+                allow_module_level=True)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.join(HERE, "golden", "ref_shims"))
-import ref_bootstrap  # noqa: E402
-
-ref_bootstrap.install(REF)
 import ngraph as rng  # noqa: E402
 import ngraph.transformers as ngt  # noqa: E402
 import ngraph_python_b200.ngraph_plugin as plugin  # noqa: E402,F401
@@ -117,7 +115,6 @@ def _reference_resnet(train):
     """The reference's own CIFAR-10 ResNet builder (examples/resnet/resnet.py: BuildResnet), 8
     layers, without batch normalisation -- the network of the headline benchmark, built by the
     reference's code rather than by this package's restatement of it."""
-    sys.path.insert(0, os.path.join(REF, "examples", "resnet"))
     from resnet import BuildResnet
     from ngraph.frontends.neon import ax, GradientDescentMomentum, Layer
     n = 32 if train else 128         # (128 images: the convolutions can run on the tile kernel)

@@ -3,7 +3,7 @@
 Some hosts of this library cannot call cudaMalloc when a kernel turns out to need scratch: a
 runtime that handed the whole device to its own arena at start-up, or a steady-state loop that
 must not hit cudaMalloc's device-wide synchronisation.  For them the split row reduction can take
-its partial-sum scratch from a 1 MiB array inside the library.  This test runs the same compiled
+its partial-sum scratch from a 16 KiB array inside the library.  This test runs the same compiled
 kernel through the ordinary entry point (caller-provided scratch) and through the no-allocation
 one, twice in a row with different data, and expects identical results: both run the same code,
 only the scratch pointer differs.  It is collected last so that a failure here cannot hide another
@@ -13,6 +13,7 @@ import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
+BUILTIN_BYTES = 16 * 1024        # B2_EW_BUILTIN_SCRATCH_BYTES of include/b200ng.h
 
 
 def _split_program(lib, rows, cols):
@@ -30,7 +31,7 @@ def test_builtin_scratch_matches_caller_scratch_twice():
     rows, cols = 3, 1 << 20
     k = lib.EwKernel(_split_program(lib, rows, cols))
     assert k.launches == 2 and k.scratch_bytes > 0, "the program must be a split reduction"
-    assert k.scratch_bytes <= (1 << 20)
+    assert k.scratch_bytes <= BUILTIN_BYTES
     scratch = torch.empty((k.scratch_bytes,), dtype=torch.uint8, device="cuda")
     rng = np.random.RandomState(11)
     for call in range(2):
@@ -55,7 +56,7 @@ def test_builtin_scratch_matches_caller_scratch_twice():
 def test_builtin_scratch_rejects_oversized_and_uncompiled():
     import torch
     from ngraph_python_b200 import lib
-    # 290 rows x 6 reductions x many splits needs more than 1 MiB of partials
+    # 290 rows shared by 3 CTAs each x 6 reductions: 20 880 bytes of partials, more than the array
     rows, cols = 290, 1 << 16
     ins = [dict(dtype=lib.F32, strides=(0, cols, 1))]
     reds = [dict(dtype=lib.F32, strides=(0, 1, 0), reg=0, redop=r)
@@ -63,9 +64,15 @@ def test_builtin_scratch_rejects_oversized_and_uncompiled():
     k = lib.EwKernel(lib.make_program((1, rows, cols), ins, [], [], [], reds, lib.REDUCE_C))
     x = torch.zeros((rows, cols), device="cuda")
     outs = [torch.zeros((rows,), device="cuda") for _ in reds]
-    if k.scratch_bytes > (1 << 20):
-        with pytest.raises(lib.B200Error, match="built-in scratch holds"):
-            k.launch_builtin_scratch([x.data_ptr()], [o.data_ptr() for o in outs])
+    assert k.launches == 2 and k.scratch_bytes > BUILTIN_BYTES, \
+        "the program must need more scratch than the library holds"
+    with pytest.raises(lib.B200Error, match="built-in scratch holds"):
+        k.launch_builtin_scratch([x.data_ptr()], [o.data_ptr() for o in outs])
+    # the ordinary entry point takes the same launch with a caller buffer
+    scratch = torch.empty((k.scratch_bytes,), dtype=torch.uint8, device="cuda")
+    k.launch([x.data_ptr()], [o.data_ptr() for o in outs], scratch=scratch.data_ptr(),
+             scratch_bytes=k.scratch_bytes)
+    torch.cuda.synchronize()
     # an unaligned pointer needs the scalar variant, which nothing has compiled yet
     k2 = lib.EwKernel(_split_program(lib, 2, 1 << 20))
     a = torch.zeros((2 * (1 << 20) + 1,), device="cuda")
