@@ -6,28 +6,40 @@
 One step = one pass of the workload's computation over one batch of seeded synthetic input.
 Rank 0 prints ONE JSON line.  Workloads:
 
-  resnet20_flex16 / resnet20_fp32 (default: resnet20_flex16)
-                        ResNet-20 inference, 3x32x32 images ~N(0,1) in C,H,W,N layout, batch 256
-                        per GPU, He-initialised weights from seed 0, batch norm folded into
-                        biases.  Metric: images per second.  Each GPU runs a full replica on its
-                        own batch; nothing is exchanged.
-  gemm_flex16 / gemm_fp32  (benchmark configuration 3) C = A.B with M = N = K = --size (default 8192);
-                        flex16: int16 mantissas uniform in [-32767, 32767], exponents -15 and -12,
-                        C re-quantised with the exponent chosen from its measured range.
+  resnet20_flex16 / resnet20_fp32 (default: resnet20_flex16; benchmark configuration 4)
+                        ResNet-20 inference, 3x32x32 images in C,H,W,N layout, batch 256 per GPU,
+                        He-initialised weights from seed 0, no batch norm.  Where the reference
+                        tree is at hand (B200NG_REFERENCE or oracle/_ref) the network is the
+                        reference's own builder (examples/resnet/resnet.py: BuildResnet('cifar10',
+                        20, False, 3, batch_norm=False)), built with the reference's `ngraph` and
+                        compiled by ngraph.transformers.make_transformer_factory('b200'); the first
+                        result is compared with the reference CPU transformer on the same graph and
+                        input before anything is timed.  Elsewhere this package's restatement of the
+                        network is used.  Metric: images per second.  Each GPU runs a full replica
+                        on its own batch; nothing is exchanged.
+  resnet20_train_flex16 / resnet20_train_fp32 (configuration 5)
+                        one data-parallel momentum-SGD step of the same network, global batch 1024
+                        split over the GPUs, bucketed NCCL gradient exchange.
+  gemm_flex16 / gemm_fp32  (configuration 3) C = A.B with M = N = K = --size (default 8192).
                         Metric: T(flex-)MAC-op/s = 2MNK / t; roofline on the tensor pipe.
-  c2_flex16 / c2_fp32   fused elementwise + reduction microbenchmark
-                        y = tanh(a*x+b)*sigmoid(c), s = sum(y, axis 1), m = max|y| over axis 1,
-                        x,a,b,c of shape (8192, 16384); y is stored (into a variable), s and m are
-                        returned.  Metric: algorithmic HBM GB/s of the fused kernel.
+  c2_flex16 / c2_fp32   (configuration 2) y = tanh(a*x+b)*sigmoid(c), s = sum(y, axis 1),
+                        m = max|y| over axis 1, x,a,b,c of shape (8192, 16384); y is stored.
+                        Metric: algorithmic HBM GB/s of the fused kernel.
 
-`value` is measured with the inputs already resident in HBM (CUDA events around K launches of the
-compiled computation); `e2e` goes through transformer.computation()(*host_arrays) with pinned
-host arrays, host->device copies and the device->host read of the results inside the timed
-region.  With --gpus N every rank runs its own replica of the workload (nothing is exchanged);
-the time is the max over ranks and `value` the sum of all ranks' work over that time.
+The default run carries the whole headline metric: after the ResNet-20 timed region it also runs
+configurations 2 and 3 (one GPU) and the training step of configuration 5 and reports them under
+`extras` (skip with --no-extras).
 
-`--impl reference` times the CPU restatement of the same path (oracle/, numpy, all host cores) on
-a bounded sample and prints the same line with "impl": "reference".
+`value` is measured with the inputs already resident in HBM: CUDA events around K steps, each
+step = the per-call exponent bookkeeping + the compiled step list (a CUDA graph) + the read-back
+of statistics and status; the loop is repeated --repeats times and the median taken.  `e2e` goes
+through computation(host_array) with pinned host arrays, host->device copies and the device->host
+read of the results inside the timed region.  With --gpus N every rank runs its own replica; the
+time is the max over ranks and `value` the sum of all ranks' work over that time.
+
+`--impl reference` times the reference's own CPU transformer (numpy engine, all host cores) on the
+same configuration and prints the same line with "impl": "reference"; without the reference tree
+it falls back to the numpy restatement under oracle/ and says so (`cpu_baseline.kind`).
 """
 import argparse
 import json
@@ -45,9 +57,23 @@ sys.path.insert(0, ROOT)
 
 C2_ROWS, C2_COLS = 8192, 16384
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+INT8_DATASHEET_TOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum per full-size launch, scaled from the ncu capture
 # of a quarter-size launch (2048 rows): see profiles/ew_c2_flex16.md and profiles/ew_c2_fp32.md
 NCU_TRAFFIC_BYTES = {"c2_flex16": 4 * (268457728 + 39549952), "c2_fp32": 4 * (536940544 + 107399680)}
+# the same two counters summed over the 22 convolution launches of one batch-256 flex16 pass
+# (profiles/conv_resnet20_flex16.md); None until a capture of the current kernel is on file
+NCU_CONV_TRAFFIC_BYTES = {"resnet20_flex16": None}
+
+RESNET_N = 256
+# algorithmic figures per 256-image batch: 21.03 GFLOP; minimal layer I/O of the 22 convolutions
+# (inputs 58 458 112 + outputs 55 574 528 + filters 270 512 elements)
+RESNET_FLOP_PER_IMG = 82.1e6
+RESNET_CONV_ELEMS_PER_256 = 58458112 + 55574528 + 270512
+TRAIN_PARAM_BYTES = 1084648      # fp32 gradients exchanged per step (no batch norm, no biases)
+CIFAR_MEAN = np.array([113.9, 123.0, 125.3], np.float32)
+CIFAR_STD = np.array([66.7, 62.1, 63.0], np.float32)
 
 
 def peaks():
@@ -57,6 +83,14 @@ def peaks():
             d = json.load(f)
         return float(d["hbm_gbs"]), "measured"
     return FALLBACK_HBM_GBS, "fallback"
+
+
+def tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    return FALLBACK_BF16_TFLOPS, "fallback"
 
 
 def c2_algorithmic_bytes(flex, rows=C2_ROWS, cols=C2_COLS):
@@ -128,30 +162,124 @@ class ClockSampler(object):
                 "samples": len(sm)}
 
 
-# ---------------------------------------------------------------------------------------------
-def build_c2(ng, flex, rows, cols):
-    R = ng.make_axis(rows, name="R")
-    C = ng.make_axis(cols, name="C")
-    ph = [ng.placeholder([R, C]) for _ in range(4)]
-    x, a, b, c = ph
-    y = ng.tanh(a * x + b) * ng.sigmoid(c)
-    yvar = ng.persistent_tensor([R, C])
-    s = ng.sum(y, reduction_axes=[C])
-    m = ng.max(ng.absolute(y), reduction_axes=[C])
-    # y is materialised on the device (assigned to a persistent tensor); s and m are returned
-    out = ng.sequential([ng.assign(yvar, y), s])
-    return [out, m], ph
+class Timer(object):
+    """CUDA-event timing of `repeats` loops of `steps` calls, barrier + synchronize on both sides
+    of every loop, max over ranks per loop."""
+
+    def __init__(self, torch, dist):
+        self.torch, self.dist = torch, dist
+        self.stream = torch.cuda.current_stream()
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def loops(self, fn, steps, repeats):
+        torch = self.torch
+        out = []
+        for _ in range(max(1, repeats)):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.barrier()
+            ev0.record(self.stream)
+            for _ in range(steps):
+                fn()
+            ev1.record(self.stream)
+            self.barrier()
+            out.append(ev0.elapsed_time(ev1))
+        if self.dist is not None:
+            tt = torch.tensor(out, dtype=torch.float64, device="cuda")
+            self.dist.all_reduce(tt, op=self.dist.ReduceOp.MAX)
+            out = [float(v) for v in tt.tolist()]
+        return out
+
+    def wall(self, fn, steps):
+        """Host wall-clock around `steps` blocking calls (the end-to-end figure), max over ranks."""
+        self.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()
+        self.torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3
+        if self.dist is not None:
+            tt = self.torch.tensor([ms], dtype=self.torch.float64, device="cuda")
+            self.dist.all_reduce(tt, op=self.dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        return ms
+
+
+def spread(loop_ms, steps):
+    per = sorted(v / steps for v in loop_ms)
+    return {"n": len(per), "median": round(statistics.median(per), 5), "min": round(per[0], 5),
+            "max": round(per[-1], 5)}
 
 
 # ---------------------------------------------------------------------------------------------
-# ResNet-20 (benchmark configuration 4): described once as a layer list, built either as a graph for the
-# b200 transformer or evaluated with the numpy restatement for the CPU baseline.
+# the reference front end (real `ngraph` ops + the plug-in), where a tree of it is at hand
+def reference_root():
+    for c in (os.environ.get("B200NG_REFERENCE"), os.path.join(ROOT, "oracle", "_ref")):
+        if c and os.path.isdir(os.path.join(c, "ngraph")):
+            return os.path.abspath(c)
+    return None
+
+
+_frontend = {}
+
+
+def reference_frontend():
+    """(ngraph module, ngraph.transformers module) with the b200 plug-in registered, or None."""
+    if "mods" in _frontend:
+        return _frontend["mods"]
+    root = reference_root()
+    mods = None
+    if root is not None:
+        from ngraph_python_b200 import ngraph_compat
+        ngraph_compat.install(root)
+        ex = os.path.join(root, "examples", "resnet")
+        if ex not in sys.path:
+            sys.path.insert(0, ex)
+        import contextlib
+        import io
+        with contextlib.redirect_stdout(io.StringIO()):      # "Could not load MKLDNN Engine ..."
+            import ngraph as rng
+            import ngraph.transformers as ngt
+            import ngraph_python_b200.ngraph_plugin  # noqa: F401
+        mods = (rng, ngt)
+    _frontend["mods"] = mods
+    return mods
+
+
+def reference_resnet20(rng, n, train=False, lr=0.1, momentum=0.9):
+    """examples/resnet/resnet.py:74-117 of the reference: CIFAR-10 ResNet-20 without batch norm.
+    Returns (result op, placeholders)."""
+    from resnet import BuildResnet
+    from ngraph.frontends.neon import ax, Layer, GradientDescentMomentum
+    ax.N.length = n
+    ax.Y.length = 10
+    C, H, W = rng.make_axis(3, name="C"), rng.make_axis(32, name="H"), rng.make_axis(32, name="W")
+    x = rng.placeholder([C, H, W, ax.N])
+    np.random.seed(0)
+    model = BuildResnet('cifar10', 20, False, 3, batch_norm=False)
+    if not train:
+        with Layer.inference_mode_on():
+            return model(x), [x]
+    t = rng.placeholder([ax.N])
+    loss = rng.cross_entropy_multi(model(x), rng.one_hot(t, axis=ax.Y))
+    updates = GradientDescentMomentum(lr, momentum)(loss)
+    return rng.sequential([updates, rng.mean(loss, out_axes=[])]), [x, t]
+
+
+def cifar_like(seed, n):
+    """Images whose preprocessed values (the reference network subtracts the CIFAR-10 channel
+    means and divides by the channel deviations first) are ~N(0,1): mean + std * N(0,1)."""
+    z = np.random.RandomState(seed).standard_normal((3, 32, 32, n)).astype(np.float32)
+    return z * CIFAR_STD[:, None, None, None] + CIFAR_MEAN[:, None, None, None]
+
+
+# ---------------------------------------------------------------------------------------------
+# this package's restatement of the network, used where the reference tree is absent
 RESNET_WIDTHS = (16, 32, 64)
-RESNET_N = 256
-# algorithmic figures per 256-image batch: 21.03 GFLOP; minimal layer I/O of the 22 convolutions
-# (inputs 58 458 112 + outputs 55 574 528 + filters 270 512 elements)
-RESNET_FLOP_PER_IMG = 82.1e6
-RESNET_CONV_ELEMS_PER_256 = 58458112 + 55574528 + 270512
 
 
 def resnet_weights(seed=0):
@@ -244,185 +372,102 @@ def resnet20_numpy(x, weights):
     return e / e.sum(axis=0)
 
 
+def flex_tolerance(desired):
+    """The reference's flex tolerance (ngraph/transformers/flexgputransform.py:80-103): atol =
+    8 steps of a flex16 tensor that just holds max|desired|, rtol 1e-2."""
+    m = float(np.max(np.abs(desired)))
+    dec = 15 - int(np.floor(np.log2(m))) - 1 if m > 0 else 8
+    while m * 2.0 ** dec > 32767:
+        dec -= 1
+    return 8 * 2.0 ** -dec, 1e-2
+
+
+def resnet_config(workload, n, world, frontend):
+    return {"workload": workload, "batch_per_gpu": n, "image": [3, 32, 32], "layout": "C,H,W,N",
+            "convolutions": 22, "network": frontend}
+
+
+class ResnetInference(object):
+    """The compiled ResNet-20 inference computation on one GPU, through whichever front end is
+    available.  `comp` is this package's Computation, `t` its B200Transformer."""
+
+    def __init__(self, torch, local, flex, n, seed):
+        self.flex, self.n = flex, n
+        fe = reference_frontend()
+        if fe is not None:
+            rng, ngt = fe
+            out, params = reference_resnet20(rng, n)
+            self.outer_t = ngt.make_transformer_factory("b200", device_id=local, flex=flex)()
+            self.call = self.outer_t.computation(out, *params)
+            self.t, self.comp = self.outer_t.impl, self.call.impl
+            self.frontend = "reference examples/resnet/resnet.py BuildResnet('cifar10', 20, " \
+                            "False, 3, batch_norm=False) via the ngraph plug-in"
+            self.graph = (out, params)
+            shape, data = (3, 32, 32, n), cifar_like(seed, n)
+        else:
+            import ngraph_python_b200 as ng
+            self.weights = resnet_weights(0)
+            self.outer_t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex)
+            outs, params = build_resnet20(ng, n, self.weights)
+            self.call = self.outer_t.computation(outs[0], *params)
+            self.t, self.comp = self.outer_t, self.call
+            self.frontend = "this package's restatement of ResNet-20 (reference tree absent)"
+            self.graph = None
+            shape = (3, 1, 32, 32, n)
+            data = np.random.RandomState(seed).standard_normal(shape).astype(np.float32)
+        self.pinned = torch.empty(shape, dtype=torch.float32).pin_memory()
+        self.host = self.pinned.numpy()
+        self.host[...] = data
+
+    def cpu_expectation(self):
+        """(expected softmax, what computed it) on the host cores, same graph and input."""
+        fe = reference_frontend()
+        if fe is not None and self.graph is not None:
+            _, ngt = fe
+            cpu = ngt.make_transformer_factory("cpu")()
+            want = np.array(cpu.computation(self.graph[0], *self.graph[1])(self.host), copy=True)
+            cpu.close()
+            return want, "reference CPUTransformer, same graph and input"
+        want = resnet20_numpy(self.host[:, 0], self.weights)
+        return want, "numpy restatement (oracle/conv_oracle.py), same weights and input"
+
+    def close(self):
+        self.outer_t.close()
+
+
+def check_parity(got, want, flex):
+    got = np.asarray(got, dtype=np.float64).reshape(want.shape)
+    err = float(np.max(np.abs(got - want)))
+    if flex:
+        atol, rtol = flex_tolerance(want)
+        atol *= 4          # the expectation is the fp32 result, not a flex evaluation
+    else:
+        atol, rtol = 1e-5, 1e-4
+    ok = bool(np.all(np.abs(got - want) <= atol + rtol * np.abs(want)))
+    agree = float((got.argmax(axis=0) == want.argmax(axis=0)).mean())
+    return {"ok": ok, "max_abs_err": err, "atol": atol, "rtol": rtol, "argmax_agreement": agree}
+
+
 def run_resnet(args, rank, world, torch, dist, local):
-    import ngraph_python_b200 as ng
     flex = args.workload == "resnet20_flex16"
     n = args.batch
-    weights = resnet_weights(0)
-    t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex)
-    outs, params = build_resnet20(ng, n, weights)
-    comp = t.computation(outs, *params)
-    pinned = torch.empty((3, 1, 32, 32, n), dtype=torch.float32).pin_memory()
-    host = pinned.numpy()
-    host[...] = np.random.RandomState(100 + rank).standard_normal(host.shape).astype(np.float32)
-    first = comp(host)[0]
-    comp(host)
+    net = ResnetInference(torch, local, flex, n, seed=100 + rank)
+    t, comp, host = net.t, net.comp, net.host
+    first = np.array(net.call(host), copy=True)
+    parity = None
+    if rank == 0:
+        want, how = net.cpu_expectation()
+        parity = check_parity(first, want, flex)
+        parity["against"] = how
+        if not parity["ok"]:
+            raise SystemExit("parity check failed before timing: %s" % json.dumps(parity))
+    net.call(host)
     if not args.no_graph:
         comp.capture()          # the step list becomes one CUDA graph launch
-    stream = torch.cuda.current_stream()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    launches0 = t.kernel_launches
-    for _ in range(args.warmup):
-        comp.executor()
-    launches_per_step = (t.kernel_launches - launches0) // max(args.warmup, 1)
-    sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(stream)
-    for _ in range(args.steps):
-        comp.executor()
-    ev1.record(stream)
-    barrier()
-    dev_ms = ev0.elapsed_time(ev1)
-    sampler.keep_loaded(comp.executor, torch.cuda.synchronize)
-    # per-kind device time: events between the steps of a few instrumented passes
-    kinds = {}
-    passes = 5
-    for _ in range(passes):
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(comp.steps) + 1)]
-        evs[0].record(stream)
-        for i, s in enumerate(comp.steps):
-            t._launch_step(s)
-            evs[i + 1].record(stream)
-        torch.cuda.synchronize()
-        for i, s in enumerate(comp.steps):
-            k = kinds.setdefault(s.kind, [0.0, 0])
-            k[0] += evs[i].elapsed_time(evs[i + 1])
-            k[1] += 1
-    # end to end
-    for _ in range(2):
-        comp(host)
-    e2e_steps = max(1, min(args.steps, args.e2e_steps * 4))
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        res = comp(host)
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
-    clocks = sampler.stop()
-    if dist is not None:
-        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
-    if rank != 0:
-        return None
-    ms_step = dev_ms / args.steps
-    peak, which = peaks()
-    item = 2 if flex else 4
-    # Time of all 22 convolutions of one pass.  Events between the steps need the step list
-    # launched one by one, where the host's launch rate, not the kernels, sets the pace; under
-    # graph replay (the timed region) the kernels run back to back.  So: the convolutions' share
-    # of the launch-by-launch pass, applied to the replayed pass.
-    eager_total = sum(v[0] for v in kinds.values()) / passes
-    conv_ms = kinds["conv"][0] / passes
-    conv_ms_source = "events between steps, launch by launch"
-    if not args.no_graph and eager_total > 0 and ms_step < eager_total:
-        conv_ms = ms_step * conv_ms / eager_total
-        conv_ms_source = "graph-replay pass x the convolutions' share of a launch-by-launch pass"
-    conv_bytes = RESNET_CONV_ELEMS_PER_256 * item * n / 256.0
-    conv_gbs = conv_bytes / (conv_ms * 1e-3) / 1e9
-    line = {
-        "metric": "ResNet-20 %s inference img/s" % ("flex16" if flex else "fp32"),
-        "value": round(world * n / (ms_step * 1e-3), 1), "unit": "img/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "flex16 (i16 mantissas, int8 hi/lo tensor-core products, i32 accumulation)"
-                 if flex else "f32 (3xTF32 tensor-core products)",
-        "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": n, "image": [3, 32, 32],
-                   "layout": "C,H,W,N", "convolutions": 22, "replicas": world,
-                   "l2": "L2 flushed by the run itself: each pass streams >126 MB of "
-                         "activations and operand planes",
-                   "steps_per_pass": len(comp.steps), "cuda_graph": not args.no_graph},
-        "clocks": clocks,
-        "e2e": {"value": round(world * n / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "img/s",
-                "h2d_bytes_per_step": int(host.nbytes), "d2h_bytes_per_step": int(10 * n * item),
-                "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 3)},
-        "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "convolution steps (gather/split + tcgen05 tile "
-                     "kernel), all 22 per pass", "achieved": round(conv_gbs, 1), "peak": peak,
-                     "unit": "GB/s", "frac": round(conv_gbs / peak, 4), "traffic": None,
-                     "peak_source": which, "algorithmic_bytes_per_launch": int(conv_bytes),
-                     "ms": round(conv_ms, 4), "ms_source": conv_ms_source},
-        "step_time_ms_by_kind": {k: round(v[0] / passes, 4) for k, v in kinds.items()},
-        "tensor_TOPS_algorithmic": round(RESNET_FLOP_PER_IMG * n * (4 if flex else 3)
-                                         / (conv_ms * 1e-3) / 1e12, 2),
-        "softmax_checksum": float(np.asarray(first).sum()),
-    }
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = resnet_cpu_baseline(budget_s=12.0)
-    return line
-
-
-def resnet_cpu_baseline(budget_s=12.0, steps=None):
-    cores = os.cpu_count() or 1
-    weights = resnet_weights(0)
-    n = 32
-    x = np.random.RandomState(100).standard_normal((3, 32, 32, n)).astype(np.float32)
-    resnet20_numpy(x, weights)
-    t0 = time.perf_counter()
-    resnet20_numpy(x, weights)
-    dt = time.perf_counter() - t0
-    reps = steps or int(max(1, min(50, budget_s / max(dt, 1e-3))))
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        resnet20_numpy(x, weights)
-    dt = (time.perf_counter() - t0) / reps
-    return {"value": round(n / dt, 1), "unit": "img/s", "cores": cores, "kind": "port",
-            "sample": "%d passes of a %d-image batch through the numpy restatement of the "
-                      "network (oracle/conv_oracle.py; numpy BLAS threads = all %d cores)"
-                      % (reps, n, cores), "ms_per_step": round(dt * 1e3, 2)}
-
-
-# ---- ResNet-20 data-parallel training step (global batch fixed, split over the GPUs) -----------
-TRAIN_PARAM_BYTES = 1084648 + 3200      # fp32 gradients exchanged per step (weights + biases)
-
-
-def run_resnet_train(args, rank, world, torch, dist, local):
-    """One step = forward, backward (bprop_conv / update_conv), bucketed gradient allreduce,
-    Kahan-momentum update of every parameter.  The graph is the hand-differentiated network of
-    tests/golden/cases.py (pinned there against the reference CPU transformer)."""
-    import ngraph_python_b200 as ng
-    from ngraph_python_b200.comm import TorchDistComm, SingleProcessComm
-    from tests.golden import cases
-    flex = args.workload == "resnet20_train_flex16"
-    gn = args.global_batch
-    if gn % world or (gn // world) % 128:
-        raise SystemExit("global batch must give every GPU a multiple of 128 images")
-    n = gn // world
-    comm = TorchDistComm() if dist is not None else SingleProcessComm()
-    t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex, comm=comm,
-                                             bucket_bytes=args.bucket_bytes)
-    outs, params, vals = cases.resnet_train_step(ng, global_n=gn, shard=(rank, world), hw=32,
-                                                 blocks=3, lr=0.002)
-    comp = t.computation(outs[:1], *params)
-    host = []
-    for v in vals:
-        pinned = torch.empty(v.shape, dtype=torch.float32).pin_memory()
-        pinned.numpy()[...] = v
-        host.append(pinned.numpy())
-    losses = [float(comp(*host)[0]) for _ in range(3)]
-    graphed = False
-    if not args.no_graph:
-        comp.capture()          # graphs between the NCCL exchanges (one graph on a single GPU)
-        graphed = True
-    stream = torch.cuda.current_stream()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    timer = Timer(torch, dist)
 
     def step_resident():
-        # inputs already on the device: exponent management, the step list, statistics read-back
+        # inputs already on the device: exponent bookkeeping, the step list, statistics read-back
         t._begin_call(comp)
         comp.executor()
         t._end_call(comp)
@@ -432,16 +477,210 @@ def run_resnet_train(args, rank, world, torch, dist, local):
         step_resident()
     launches_per_step = (t.kernel_launches - launches0) // max(args.warmup, 1)
     sampler = ClockSampler(local)
-    barrier()
+    timer.barrier()
     sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(stream)
-    for _ in range(args.steps):
-        step_resident()
-    ev1.record(stream)
-    barrier()
-    dev_ms = ev0.elapsed_time(ev1)
+    loop_ms = timer.loops(step_resident, args.steps, args.repeats)
     sampler.keep_loaded(step_resident, torch.cuda.synchronize)
+    replay_ms = timer.loops(comp.executor, args.steps, args.repeats)
+    # the 22 convolution launches alone, back to back, as a CUDA graph of their own: every tensor
+    # they read is still in place from the last pass
+    conv_steps = [s for s in comp.steps if s.kind == "conv"]
+
+    def convs_only():
+        for s in conv_steps:
+            t._launch_step(s)
+    conv_fn, conv_src = convs_only, "CUDA events around the 22 convolution steps launched one by one"
+    if not args.no_graph:
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            convs_only()
+        conv_fn = g.replay
+        conv_src = "CUDA events around a replayed graph of the 22 convolution steps alone"
+    conv_loops = timer.loops(conv_fn, args.steps, args.repeats)
+    # end to end
+    for _ in range(2):
+        net.call(host)
+    e2e_steps = max(1, min(args.steps, args.e2e_steps * 4))
+    e2e_ms = timer.wall(lambda: net.call(host), e2e_steps)
+    clocks = sampler.stop()
+    if rank != 0:
+        net.close()
+        return None
+    ms_step = statistics.median(loop_ms) / args.steps
+    replay_step = statistics.median(replay_ms) / args.steps
+    conv_ms = statistics.median(conv_loops) / args.steps
+    peak, which = peaks()
+    item = 2 if flex else 4
+    conv_bytes = RESNET_CONV_ELEMS_PER_256 * item * n / 256.0
+    conv_gbs = conv_bytes / (conv_ms * 1e-3) / 1e9
+    cfg = resnet_config(args.workload, n, world, net.frontend)
+    cfg.update({"replicas": world,
+                "l2": "L2 flushed by the run itself: each pass streams >126 MB of activations and "
+                      "operand planes",
+                "steps_per_pass": len(comp.steps), "cuda_graph": not args.no_graph,
+                "value_includes": "per-call exponent bookkeeping, graph replay, statistics and "
+                                  "status read-back with one stream synchronisation"})
+    traffic = NCU_CONV_TRAFFIC_BYTES.get(args.workload)
+    line = {
+        "metric": "ResNet-20 %s inference img/s" % ("flex16" if flex else "fp32"),
+        "value": round(world * n / (ms_step * 1e-3), 1), "unit": "img/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "flex16 (i16 mantissas, int8 hi/lo tensor-core products, i32 accumulation)"
+                 if flex else "f32 (3xTF32 tensor-core products)",
+        "data": "synthetic",
+        "config": cfg,
+        "clocks": clocks,
+        "repeats": spread(loop_ms, args.steps),
+        "graph_replay_only": {"ms_per_step": round(replay_step, 4),
+                              "img_s": round(world * n / (replay_step * 1e-3), 1),
+                              "what": "the captured step list alone, no exponent bookkeeping or "
+                                      "read-back between replays"},
+        "e2e": {"value": round(world * n / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "img/s",
+                "h2d_bytes_per_step": int(host.nbytes), "d2h_bytes_per_step": int(10 * n * item),
+                "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 3)},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "the 22 convolution steps of a pass (tcgen05 tile "
+                     "kernel with fused tails)" if flex else "the 22 convolution steps of a pass",
+                     "achieved": round(conv_gbs, 1), "peak": peak,
+                     "unit": "GB/s", "frac": round(conv_gbs / peak, 4),
+                     "traffic": int(traffic * n / 256.0) if traffic else None,
+                     "peak_source": which, "algorithmic_bytes_per_launch": int(conv_bytes),
+                     "launch": "one pass = 22 kernel launches", "ms": round(conv_ms, 4),
+                     "ms_source": conv_src},
+        "tensor_TOPS_algorithmic": round(RESNET_FLOP_PER_IMG * n * (4 if flex else 3)
+                                         / (conv_ms * 1e-3) / 1e12, 2),
+        "parity": parity,
+    }
+    net.close()
+    return line
+
+
+# ---- the reference arm of the ResNet-20 workloads ------------------------------------------------
+def resnet_cpu_reference(n, steps, warmup, budget_s=None):
+    """The reference CPU transformer on the same network and batch size (all host cores through
+    numpy's BLAS); without the reference tree, the numpy restatement on a 32-image sample."""
+    cores = os.cpu_count() or 1
+    fe = reference_frontend()
+    if fe is not None:
+        rng, ngt = fe
+        out, params = reference_resnet20(rng, n)
+        cpu = ngt.make_transformer_factory("cpu")()
+        comp = cpu.computation(out, *params)
+        x = cifar_like(100, n)
+        for _ in range(max(1, warmup)):
+            comp(x)
+        t0 = time.perf_counter()
+        comp(x)
+        one = time.perf_counter() - t0
+        reps = steps if budget_s is None else int(max(1, min(steps, budget_s / max(one, 1e-3))))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            comp(x)
+        dt = (time.perf_counter() - t0) / reps
+        cpu.close()
+        return {"value": round(n / dt, 1), "unit": "img/s", "cores": cores, "kind": "reference",
+                "sample": "%d passes of a %d-image batch through the reference's CPUTransformer "
+                          "(numpy engine; MKL-DNN absent), BuildResnet-20 without batch norm, "
+                          "numpy BLAS threads = all %d cores" % (reps, n, cores),
+                "ms_per_step": round(dt * 1e3, 2), "batch": n}
+    weights = resnet_weights(0)
+    n = 32
+    x = np.random.RandomState(100).standard_normal((3, 32, 32, n)).astype(np.float32)
+    resnet20_numpy(x, weights)
+    t0 = time.perf_counter()
+    resnet20_numpy(x, weights)
+    one = time.perf_counter() - t0
+    reps = steps if budget_s is None else int(max(1, min(steps, budget_s / max(one, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        resnet20_numpy(x, weights)
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": round(n / dt, 1), "unit": "img/s", "cores": cores, "kind": "port",
+            "sample": "%d passes of a %d-image batch through the numpy restatement of the "
+                      "network (oracle/conv_oracle.py; the reference tree is absent here; numpy "
+                      "BLAS threads = all %d cores)" % (reps, n, cores),
+            "ms_per_step": round(dt * 1e3, 2), "batch": n}
+
+
+# ---- ResNet-20 data-parallel training step (global batch fixed, split over the GPUs) -----------
+class ResnetTraining(object):
+    """One momentum-SGD step of ResNet-20 as a computation.  With the reference tree: the
+    reference's builder, cross_entropy_multi, autodiff and GradientDescentMomentum(0.1, 0.9)
+    through the plug-in (which places the gradient exchange where the reference's passes would,
+    from the gradients' reduce_func tags).  Without: this package's hand-differentiated graph."""
+
+    def __init__(self, torch, local, flex, global_n, rank, world, comm, bucket_bytes, lr):
+        n = global_n // world
+        fe = reference_frontend()
+        kw = dict(device_id=local, flex=flex, comm=comm)
+        if bucket_bytes:
+            kw["bucket_bytes"] = bucket_bytes
+        r = np.random.RandomState(3)
+        labels = r.randint(0, 10, global_n)
+        lo, hi = rank * n, (rank + 1) * n
+        if fe is not None:
+            rng, ngt = fe
+            out, params = reference_resnet20(rng, n, train=True, lr=lr)
+            self.outer_t = ngt.make_transformer_factory("b200", **kw)()
+            self.call = self.outer_t.computation(out, *params)
+            self.t, self.comp = self.outer_t.impl, self.call.impl
+            self.frontend = "reference BuildResnet-20 + cross_entropy_multi + autodiff + " \
+                            "GradientDescentMomentum via the ngraph plug-in"
+            vals = [cifar_like(7, global_n)[..., lo:hi], labels[lo:hi].astype(np.float32)]
+        else:
+            import ngraph_python_b200 as ng
+            from ngraph_python_b200 import configs
+            self.outer_t = ng.transformers.allocate_transformer("b200", **kw)
+            outs, params, vals = configs.resnet_train_step(ng, global_n=global_n,
+                                                           shard=(rank, world), hw=32, blocks=3,
+                                                           lr=lr)
+            self.call = self.outer_t.computation(outs[0], *params)
+            self.t, self.comp = self.outer_t, self.call
+            self.frontend = "this package's hand-differentiated ResNet-20 (reference tree absent)"
+        self.host = []
+        for v in vals:
+            pinned = torch.empty(v.shape, dtype=torch.float32).pin_memory()
+            pinned.numpy()[...] = v
+            self.host.append(pinned.numpy())
+
+    def close(self):
+        self.outer_t.close()
+
+
+def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats, with_e2e=True):
+    """Times one training step; returns the fields of a bench line (rank 0) or None."""
+    from ngraph_python_b200.comm import TorchDistComm, SingleProcessComm
+    gn = args.global_batch
+    if gn % world or (gn // world) % 128:
+        raise SystemExit("global batch must give every GPU a multiple of 128 images")
+    n = gn // world
+    comm = TorchDistComm() if dist is not None else SingleProcessComm()
+    job = ResnetTraining(torch, local, flex, gn, rank, world, comm, args.bucket_bytes, lr=0.002)
+    t, comp, host = job.t, job.comp, job.host
+    losses = [float(job.call(*host)) for _ in range(3)]
+    graphed = False
+    if not args.no_graph:
+        comp.capture()          # graphs between the NCCL exchanges (one graph on a single GPU)
+        graphed = True
+    timer = Timer(torch, dist)
+
+    def step_resident():
+        t._begin_call(comp)
+        comp.executor()
+        t._end_call(comp)
+
+    launches0 = t.kernel_launches
+    for _ in range(args.warmup):
+        step_resident()
+    launches_per_step = (t.kernel_launches - launches0) // max(args.warmup, 1)
+    sampler = ClockSampler(local)
+    timer.barrier()
+    sampler.start()
+    loop_ms = timer.loops(step_resident, steps, repeats)
+    sampler.keep_loaded(step_resident, torch.cuda.synchronize)
+    stream = timer.stream
     kinds = {}
     passes = 3
     for _ in range(passes):
@@ -456,13 +695,9 @@ def run_resnet_train(args, rank, world, torch, dist, local):
             k = kinds.setdefault(s.kind, [0.0, 0])
             k[0] += evs[i].elapsed_time(evs[i + 1])
             k[1] += 1
-    e2e_steps = max(1, min(args.steps, args.e2e_steps * 2))
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        last = comp(*host)
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
+    e2e_steps = max(1, min(steps, args.e2e_steps * 2))
+    e2e_ms = timer.wall(lambda: job.call(*host), e2e_steps) if with_e2e else None
+    last = float(job.call(*host))
     clocks = sampler.stop()
     alone_ms = nocomm_ms = 0.0
     exchanged = []
@@ -483,58 +718,47 @@ def run_resnet_train(args, rank, world, torch, dist, local):
         torch.cuda.synchronize()
         per_step = list(exchanged)
         bufs = [torch.zeros(c, dtype=torch.float32, device="cuda") for c in per_step]
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for timed in (False, True):
-            barrier()
-            a0.record(stream)
-            for _ in range(20 if timed else 3):
-                for b in bufs:
-                    dist.all_reduce(b)
-            a1.record(stream)
-            barrier()
-        alone_ms = a0.elapsed_time(a1) / 20
+
+        def collectives_alone():
+            for b in bufs:
+                dist.all_reduce(b)
+        timer.loops(collectives_alone, 3, 1)
+        alone_ms = statistics.median(timer.loops(collectives_alone, 20, 3)) / 20
         ar.comm = SingleProcessComm()
-        for timed in (False, True):
-            barrier()
-            a0.record(stream)
-            for _ in range(args.steps if timed else 3):
-                step_resident()
-            a1.record(stream)
-            barrier()
-        nocomm_ms = a0.elapsed_time(a1) / args.steps
+        timer.loops(step_resident, 3, 1)
+        nocomm_ms = statistics.median(timer.loops(step_resident, steps, repeats)) / steps
         ar.comm = real
         exchanged = per_step
-    if dist is not None:
-        tt = torch.tensor([dev_ms, e2e_ms, alone_ms, nocomm_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms, alone_ms, nocomm_ms = [float(v) for v in tt.tolist()]
+    buckets = len(t._allreduce.plan.buckets) if t._allreduce is not None else 0
+    n_steps = len(comp.steps)
+    frontend = job.frontend
+    job.close()
     if rank != 0:
         return None
-    ms_step = dev_ms / args.steps
+    ms_step = statistics.median(loop_ms) / steps
     conv_ms = sum(kinds[k][0] for k in ("conv", "conv_bprop", "conv_update") if k in kinds) / passes
     tpeak, which = tensor_peak()
     tpeak = tpeak * 2 if flex else tpeak / 2
     tops = 3 * RESNET_FLOP_PER_IMG * n * (4 if flex else 3) / (conv_ms * 1e-3) / 1e12
-    buckets = len(t._allreduce.plan.buckets) if t._allreduce is not None else 0
-    line = {
+    out = {
         "metric": "ResNet-20 %s data-parallel training img/s" % ("flex16" if flex else "fp32"),
         "value": round(gn / (ms_step * 1e-3), 1), "unit": "img/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+        "steps": steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "flex16 (i16 mantissas, int8 hi/lo tensor-core products, i32 accumulation)"
                  if flex else "f32 (3xTF32 tensor-core products)",
         "data": "synthetic",
-        "config": {"workload": args.workload, "global_batch": gn, "batch_per_gpu": n,
+        "config": {"workload": "resnet20_train_%s" % ("flex16" if flex else "fp32"),
+                   "global_batch": gn, "batch_per_gpu": n,
                    "image": [3, 32, 32], "layout": "C,H,W,N", "optimizer": "momentum 0.9 + Kahan",
+                   "network": frontend,
                    "parallelism": "dp%d" % world, "allreduce_buckets": buckets,
-                   "bucket_bytes": args.bucket_bytes, "steps_per_pass": len(comp.steps),
+                   "bucket_bytes": t.bucket_bytes, "steps_per_pass": n_steps,
                    "cuda_graph": graphed,
                    "l2": "each step streams >126 MB of activations, gradients and operand planes"},
         "clocks": clocks,
-        "e2e": {"value": round(gn / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "img/s",
-                "h2d_bytes_per_step": int(sum(h.nbytes for h in host)), "d2h_bytes_per_step": 4,
-                "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 3)},
-        "gpu_launches": launches_per_step * args.steps,
+        "repeats": spread(loop_ms, steps),
+        "gpu_launches": launches_per_step * steps,
         "roofline": {"bound": "tensor", "kernel": "convolution fprop + bprop + update steps",
                      "achieved": round(tops, 2), "peak": round(tpeak, 1),
                      "unit": "TOPS (int8)" if flex else "TFLOP/s (tf32)",
@@ -544,51 +768,100 @@ def run_resnet_train(args, rank, world, torch, dist, local):
                      "ms": round(conv_ms, 4)},
         "step_time_ms_by_kind": {k: round(v[0] / passes, 4) for k, v in kinds.items()},
         "allreduce_algorithmic_bytes_per_gpu": int(2 * (world - 1) / world * TRAIN_PARAM_BYTES),
-        "loss_first_steps": [round(v, 5) for v in losses], "loss_last": round(float(last[0]), 5),
+        "loss_first_steps": [round(v, 5) for v in losses], "loss_last": round(last, 5),
     }
+    if e2e_ms is not None:
+        out["e2e"] = {"value": round(gn / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "img/s",
+                      "h2d_bytes_per_step": int(sum(h.nbytes for h in host)),
+                      "d2h_bytes_per_step": 4, "steps": e2e_steps,
+                      "ms_per_step": round(e2e_ms / e2e_steps, 3)}
     if exchanged:
         exposed = max(0.0, ms_step - nocomm_ms)
-        line["allreduce"] = {
+        out["allreduce"] = {
             "collectives_per_step": len(exchanged), "bytes_per_step": int(4 * sum(exchanged)),
             "alone_ms": round(alone_ms, 4), "step_without_exchange_ms": round(nocomm_ms, 4),
             "exposed_ms": round(exposed, 4),
             "overlap_frac": round(min(1.0, max(0.0, 1.0 - exposed / alone_ms)), 3) if alone_ms > 0 else None}
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = train_cpu_baseline()
+    return out
+
+
+def run_resnet_train(args, rank, world, torch, dist, local):
+    flex = args.workload == "resnet20_train_flex16"
+    line = measure_training(args, rank, world, torch, dist, local, flex, args.steps, args.repeats)
+    if line is not None and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = train_cpu_reference(args.global_batch, steps=1)
     return line
 
 
-def train_cpu_baseline(steps=1):
-    """The same training graph evaluated with numpy (tests/mirror_interp.py over oracle/)."""
+def train_cpu_reference(global_n, steps=1):
+    """The reference CPU transformer on one training step of the global batch (hetr itself needs
+    mpirun / MLSL, which this image lacks: SURVEY of the reference's hetr path)."""
+    cores = os.cpu_count() or 1
+    fe = reference_frontend()
+    if fe is not None:
+        rng, ngt = fe
+        out, params = reference_resnet20(rng, global_n, train=True, lr=0.002)
+        cpu = ngt.make_transformer_factory("cpu")()
+        comp = cpu.computation(out, *params)
+        vals = [cifar_like(7, global_n),
+                np.random.RandomState(3).randint(0, 10, global_n).astype(np.float32)]
+        comp(*vals)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            comp(*vals)
+        dt = (time.perf_counter() - t0) / steps
+        cpu.close()
+        return {"value": round(global_n / dt, 2), "unit": "img/s", "cores": cores,
+                "kind": "reference",
+                "sample": "%d training step(s) of the global batch of %d images on the "
+                          "reference's CPUTransformer (numpy engine, numpy BLAS threads = all %d "
+                          "cores)" % (steps, global_n, cores),
+                "ms_per_step": round(dt * 1e3, 1)}
     import ngraph_python_b200 as ng
-    from tests.golden import cases
+    from ngraph_python_b200 import configs
     from tests import mirror_interp
     gn = 32
-    outs, params, vals = cases.resnet_train_step(ng, global_n=gn, hw=32, blocks=3, lr=0.002)
+    outs, params, vals = configs.resnet_train_step(ng, global_n=gn, hw=32, blocks=3, lr=0.002)
     interp = mirror_interp.Interp()
     t0 = time.perf_counter()
     for _ in range(steps):
         interp.run(outs[:1], dict(zip(params, vals)))
     dt = (time.perf_counter() - t0) / steps
-    cores = os.cpu_count() or 1
     return {"value": round(gn / dt, 2), "unit": "img/s", "cores": cores, "kind": "port",
             "sample": "%d training step(s) on a %d-image batch, numpy restatement of every op "
-                      "(numpy BLAS threads = all %d cores)" % (steps, gn, cores),
+                      "(reference tree absent; numpy BLAS threads = all %d cores)"
+                      % (steps, gn, cores),
             "ms_per_step": round(dt * 1e3, 1)}
 
 
-def tensor_peak():
-    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(p):
-        with open(p) as f:
-            return float(json.load(f)["bf16_tflops"]), "measured"
-    return 1590.0, "fallback"
+# ---- configuration 3: GEMM --------------------------------------------------------------------
+def int8_yardstick(torch, n=8192, reps=10):
+    """A library int8 GEMM (torch._int_mm -> cuBLASLt), used ONLY as the measured denominator of
+    the flex16 GEMM's roofline fraction: best of `reps`, TOPS (2 n^3 / t)."""
+    try:
+        a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device="cuda")
+        b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device="cuda")
+        for _ in range(3):
+            torch._int_mm(a, b)
+        best = None
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        del a, b
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:       # pragma: no cover  (yardstick only: absence changes no result)
+        return None
 
 
-def run_gemm(args, rank, world, torch, dist, local):
+def measure_gemm(args, rank, world, torch, dist, local, flex, size, steps, repeats,
+                 with_e2e=True):
     import ngraph_python_b200 as ng
-    flex = args.workload == "gemm_flex16"
-    n = args.size
+    n = size
     t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex)
     M, K, N = ng.make_axis(n, name="M"), ng.make_axis(n, name="K"), ng.make_axis(n, name="N")
     a, b = ng.placeholder([M, K]), ng.placeholder([K, N])
@@ -597,208 +870,179 @@ def run_gemm(args, rank, world, torch, dist, local):
     # C stays on the device (assigned to a persistent tensor); its column maxima are returned
     out = ng.sequential([ng.assign(cvar, c), ng.max(cvar, reduction_axes=[M])])
     comp = t.computation(out, a, b)
-    rng = np.random.RandomState(rank)
-    host = []
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(rank)
+    dev = []
     for scale in ((2.0 ** -15, 2.0 ** -12) if flex else (1.0, 1.0)):
-        pinned = torch.empty((n, n), dtype=torch.float32).pin_memory()
-        arr = pinned.numpy()
         if flex:
-            arr[...] = rng.randint(-32767, 32768, (n, n)).astype(np.float32) * scale
+            v = torch.randint(-32767, 32768, (n, n), device="cuda", generator=gen).float() * scale
         else:
-            arr[...] = rng.standard_normal((n, n)).astype(np.float32)
-        host.append(arr)
-    comp(*host)
-    comp(*host)
-    stream = torch.cuda.current_stream()
+            v = torch.randn((n, n), device="cuda", generator=gen)
+        dev.append(v)
+    comp(*dev)
+    comp(*dev)
     gemm_step = [s for s in comp.steps if s.kind == "gemm"][0]
-
-    def barrier():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    timer = Timer(torch, dist)
     for _ in range(args.warmup):
         t._launch_step(gemm_step)
     sampler = ClockSampler(local)
-    barrier()
+    timer.barrier()
     sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(stream)
-    for _ in range(args.steps):
-        t._launch_step(gemm_step)
-    ev1.record(stream)
-    barrier()
-    dev_ms = ev0.elapsed_time(ev1)
+    loop_ms = timer.loops(lambda: t._launch_step(gemm_step), steps, repeats)
     sampler.keep_loaded(lambda: t._launch_step(gemm_step), torch.cuda.synchronize)
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    comp(*host)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        res = comp(*host)
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
+    e2e = None
+    if with_e2e:
+        host = []
+        for v in dev:
+            pinned = torch.empty((n, n), dtype=torch.float32).pin_memory()
+            pinned.copy_(v)
+            host.append(pinned.numpy())
+        comp(*host)
+        e2e_steps = max(1, min(steps, args.e2e_steps))
+        e2e_ms = timer.wall(lambda: comp(*host), e2e_steps)
+        e2e = (e2e_ms, e2e_steps, int(sum(h.nbytes for h in host)))
     clocks = sampler.stop()
-    if dist is not None:
-        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
+    launches = gemm_step.launches
+    del dev
+    t.close()
+    yard = int8_yardstick(torch) if (flex and rank == 0) else None
+    torch.cuda.empty_cache()
     if rank != 0:
         return None
-    ms_step = dev_ms / args.steps
+    ms_step = statistics.median(loop_ms) / steps
     ops = 2.0 * n * n * n
     bf16, which = tensor_peak()
-    # flex16: four int8 products per MAC; int8 peak is not measured on this pool, 2 x the
-    # measured bf16 figure stands in for it (datasheet: 4500 TOPS)
+    # flex16: four int8 products per MAC
     tensor_ops = (4 if flex else 3) * ops
-    peak = (2 * bf16) if flex else bf16 / 2
     achieved = tensor_ops / (ms_step * 1e-3) / 1e12
+    if flex and yard:
+        peak, src = yard, "library int8 GEMM (torch._int_mm, %d^3, best of 10) measured in this run" % 8192
+    elif flex:
+        peak, src = 2 * bf16, which + " bf16 x2 as int8 stand-in"
+    else:
+        peak, src = bf16 / 2, which + " bf16 / 2 as tf32 stand-in"
     line = {
         "metric": "%s GEMM T%sMAC-op/s (2MNK/t), M=N=K=%d" % ("flex16" if flex else "fp32",
                                                               "flex-" if flex else "", n),
         "value": round(world * ops / (ms_step * 1e-3) / 1e12, 2), "unit": "Tops/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "n_gpus": world, "steps": steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None,
         "dtype": "flex16 (int8 hi/lo tensor-core products, i32 accumulation)" if flex
                  else "f32 (3xTF32)",
         "data": "synthetic",
-        "config": {"workload": args.workload, "M": n, "N": n, "K": n, "replicas": world,
+        "config": {"workload": "gemm_%s" % ("flex16" if flex else "fp32"), "M": n, "N": n, "K": n,
+                   "replicas": world,
                    "l2": "operand planes (%d MB) larger than L2" % (4 * n * n * (1 if flex else 4) >> 20)
                          if n >= 8192 else "operands fit in L2 at this size",
                    "includes": "operand split pre-pass + tensor-core kernel"},
         "clocks": clocks,
-        "e2e": {"value": round(world * ops / (e2e_ms / e2e_steps * 1e-3) / 1e12, 3),
-                "unit": "Tops/s", "h2d_bytes_per_step": int(sum(h.nbytes for h in host)),
-                "d2h_bytes_per_step": int(n * (2 if flex else 4)), "steps": e2e_steps,
-                "ms_per_step": round(e2e_ms / e2e_steps, 3)},
-        "gpu_launches": gemm_step.launches * args.steps,
+        "repeats": spread(loop_ms, steps),
+        "gpu_launches": launches * steps,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1),
                      "unit": "TOPS (int8)" if flex else "TFLOP/s (tf32)",
                      "frac": round(achieved / peak, 4), "traffic": None,
-                     "peak_source": which + (" bf16 x2 as int8 stand-in" if flex
-                                             else " bf16 / 2 as tf32 stand-in"),
-                     "algorithmic_ops_per_launch": tensor_ops},
+                     "peak_source": src, "algorithmic_ops_per_launch": tensor_ops},
     }
+    if flex:
+        line["roofline"]["frac_of_datasheet_4500_TOPS"] = round(achieved / INT8_DATASHEET_TOPS, 4)
+        line["roofline"]["frac_of_2x_measured_bf16"] = round(achieved / (2 * bf16), 4)
+    if e2e is not None:
+        e2e_ms, e2e_steps, nbytes = e2e
+        line["e2e"] = {"value": round(world * ops / (e2e_ms / e2e_steps * 1e-3) / 1e12, 3),
+                       "unit": "Tops/s", "h2d_bytes_per_step": nbytes,
+                       "d2h_bytes_per_step": int(n * (2 if flex else 4)), "steps": e2e_steps,
+                       "ms_per_step": round(e2e_ms / e2e_steps, 3)}
     return line
 
 
-def run_b200(args, rank, world):
-    import torch
+# ---- configuration 2: fused elementwise + reductions --------------------------------------------
+def build_c2(ng, rows, cols):
+    R = ng.make_axis(rows, name="R")
+    C = ng.make_axis(cols, name="C")
+    ph = [ng.placeholder([R, C]) for _ in range(4)]
+    x, a, b, c = ph
+    y = ng.tanh(a * x + b) * ng.sigmoid(c)
+    yvar = ng.persistent_tensor([R, C])
+    s = ng.sum(y, reduction_axes=[C])
+    m = ng.max(ng.absolute(y), reduction_axes=[C])
+    # y is materialised on the device (assigned to a persistent tensor); s and m are returned
+    out = ng.sequential([ng.assign(yvar, y), s])
+    return [out, m], ph
+
+
+def measure_c2(args, rank, world, torch, dist, local, flex, rows, steps, repeats, with_e2e=True):
     import ngraph_python_b200 as ng
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    if args.workload.startswith("gemm"):
-        line = run_gemm(args, rank, world, torch, dist, local)
-        if dist is not None:
-            dist.destroy_process_group()
-        return line
-    if args.workload.startswith("resnet20_train"):
-        line = run_resnet_train(args, rank, world, torch, dist, local)
-        if dist is not None:
-            dist.destroy_process_group()
-        return line
-    if args.workload.startswith("resnet20"):
-        line = run_resnet(args, rank, world, torch, dist, local)
-        if dist is not None:
-            dist.destroy_process_group()
-        return line
-    flex = args.workload == "c2_flex16"
-    rows, cols = args.rows, C2_COLS
+    cols = C2_COLS
     t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex)
-    outs, params = build_c2(ng, flex, rows, cols)
+    outs, params = build_c2(ng, rows, cols)
     comp = t.computation(outs, *params)
-    rng = np.random.RandomState(rank)
-    host = []
-    for _ in range(4):
-        pinned = torch.empty((rows, cols), dtype=torch.float32).pin_memory()
-        arr = pinned.numpy()
-        arr[...] = rng.standard_normal((rows, cols)).astype(np.float32)
-        host.append(arr)
-    comp(*host)            # compile, first-call exponent initialisation
-    comp(*host)
-    stream = torch.cuda.current_stream()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing: inputs in HBM, K launches of the compiled step --------------
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(rank)
+    dev = [torch.randn((rows, cols), device="cuda", generator=gen) for _ in range(4)]
+    comp(*dev)            # compile, first-call exponent initialisation
+    res = comp(*dev)
+    timer = Timer(torch, dist)
     launches0 = t.kernel_launches
     for _ in range(args.warmup):
         comp.executor()
     launches_per_step = (t.kernel_launches - launches0) // max(args.warmup, 1)
     sampler = ClockSampler(local)
-    barrier()
+    timer.barrier()
     sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(stream)
-    for _ in range(args.steps):
-        comp.executor()
-    ev1.record(stream)
-    barrier()
-    dev_ms = ev0.elapsed_time(ev1)
+    loop_ms = timer.loops(comp.executor, steps, repeats)
     sampler.keep_loaded(comp.executor, torch.cuda.synchronize)
-    # ---- end to end: host arrays in, results out ---------------------------------------------
-    for _ in range(max(1, min(args.warmup, 2))):
+    e2e = None
+    if with_e2e:
+        host = []
+        for v in dev:
+            pinned = torch.empty((rows, cols), dtype=torch.float32).pin_memory()
+            pinned.copy_(v)
+            host.append(pinned.numpy())
         comp(*host)
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        res = comp(*host)
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
+        e2e_steps = max(1, min(steps, args.e2e_steps))
+        e2e_ms = timer.wall(lambda: comp(*host), e2e_steps)
+        e2e = (e2e_ms, e2e_steps, int(sum(h.nbytes for h in host)))
     clocks = sampler.stop()
-    h2d = sum(h.nbytes for h in host)
     d2h = sum(np.asarray(r).size for r in res) * (2 if flex else 4)
-    if dist is not None:
-        tt = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = [float(v) for v in tt.tolist()]
+    del dev
+    t.close()
+    torch.cuda.empty_cache()
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
         return None
     alg = c2_algorithmic_bytes(flex, rows, cols)
-    ms_step = dev_ms / args.steps
+    ms_step = statistics.median(loop_ms) / steps
     gbs = world * alg / (ms_step * 1e-3) / 1e9
     peak, which = peaks()
     kernel_gbs = alg / (ms_step * 1e-3) / 1e9
-    traffic = NCU_TRAFFIC_BYTES.get(args.workload)
+    name = "c2_flex16" if flex else "c2_fp32"
+    traffic = NCU_TRAFFIC_BYTES.get(name)
     line = {
         "metric": "fused-EW HBM GB/s (y=tanh(a*x+b)*sigmoid(c), row sum and row maxabs)",
-        "value": round(gbs, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "value": round(gbs, 1), "unit": "GB/s", "n_gpus": world, "steps": steps,
         "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None,
         "dtype": "flex16 (i16 mantissa storage, f32 math)" if flex else "f32",
         "data": "synthetic",
-        "config": {"workload": args.workload, "shape": [rows, cols], "replicas": world,
+        "config": {"workload": name, "shape": [rows, cols], "replicas": world,
                    "l2": "inputs (%d MB) larger than L2" % (4 * rows * cols * (2 if flex else 4) >> 20),
                    "fused_ops": 11, "y_materialised": True},
         "clocks": clocks,
-        "e2e": {"value": round(world * alg / (e2e_ms / e2e_steps * 1e-3) / 1e9, 2), "unit": "GB/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                "ms_per_step": round(e2e_ms / e2e_steps, 3)},
-        "gpu_launches": launches_per_step * args.steps,
+        "repeats": spread(loop_ms, steps),
+        "gpu_launches": launches_per_step * steps,
         "roofline": {"bound": "hbm", "achieved": round(kernel_gbs, 1), "peak": peak,
-                     "unit": "GB/s", "frac": round(kernel_gbs / peak, 4), "traffic": traffic,
+                     "unit": "GB/s", "frac": round(kernel_gbs / peak, 4),
+                     "traffic": int(traffic * rows / C2_ROWS) if traffic else None,
                      "peak_source": which, "algorithmic_bytes_per_launch": alg},
     }
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
-    if dist is not None:
-        dist.destroy_process_group()
+    if e2e is not None:
+        e2e_ms, e2e_steps, nbytes = e2e
+        line["e2e"] = {"value": round(world * alg / (e2e_ms / e2e_steps * 1e-3) / 1e9, 2),
+                       "unit": "GB/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": d2h,
+                       "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 3)}
     return line
 
 
-# ---------------------------------------------------------------------------------------------
 def _c2_cpu_block(flex, vals):
     from oracle import ew_oracle as ew
     from oracle import flex_oracle as fx
@@ -815,99 +1059,182 @@ def _c2_cpu_block(flex, vals):
     return y, s, m
 
 
-def cpu_reference_run(workload, rows, steps, warmup):
-    """The CPU restatement of the workload on `rows` rows, row blocks spread over all cores."""
-    from concurrent.futures import ThreadPoolExecutor
+def c2_cpu_reference(workload, rows, steps, warmup):
+    """(GB/s, seconds per pass, cores, kind, what) for `rows` rows of configuration 2 on the host:
+    the reference CPU transformer on the same graph (fp32); flex16 has no CPU implementation in the
+    reference (its flex transformer is GPU-only), so the numpy restatement under oracle/ is timed."""
     flex = workload == "c2_flex16"
     cores = os.cpu_count() or 1
-    rng = np.random.RandomState(0)
-    vals = [rng.standard_normal((rows, C2_COLS)).astype(np.float32) for _ in range(4)]
-    blocks = np.array_split(np.arange(rows), min(cores, rows))
+    rng_ = np.random.RandomState(0)
+    vals = [rng_.standard_normal((rows, C2_COLS)).astype(np.float32) for _ in range(4)]
+    fe = reference_frontend()
+    if fe is not None and not flex:
+        rng, ngt = fe
+        outs, params = build_c2(rng, rows, C2_COLS)
+        cpu = ngt.make_transformer_factory("cpu")()
+        comp = cpu.computation(outs, *params)
 
-    def one():
-        with ThreadPoolExecutor(cores) as ex:
-            list(ex.map(lambda idx: _c2_cpu_block(flex, [v[idx] for v in vals]), blocks))
-    for _ in range(warmup):
+        def one():
+            comp(*vals)
+        kind = "reference"
+        what = "reference CPUTransformer on the same graph (one numpy pass per op)"
+    else:
+        from concurrent.futures import ThreadPoolExecutor
+        blocks = np.array_split(np.arange(rows), min(cores, rows))
+
+        def one():
+            with ThreadPoolExecutor(cores) as ex:
+                list(ex.map(lambda idx: _c2_cpu_block(flex, [v[idx] for v in vals]), blocks))
+        kind = "port"
+        what = "numpy restatement (oracle/), row blocks on %d threads" % cores
+    for _ in range(max(1, warmup)):
         one()
     t0 = time.perf_counter()
     for _ in range(steps):
         one()
     dt = (time.perf_counter() - t0) / steps
     alg = c2_algorithmic_bytes(flex, rows, C2_COLS)
-    return alg / dt / 1e9, dt, cores
+    return alg / dt / 1e9, dt, cores, kind, what
 
 
-def cpu_baseline(workload, budget_s=12.0):
+def c2_cpu_baseline(workload, budget_s=10.0):
     rows = 256
-    gbs, dt, cores = cpu_reference_run(workload, rows, steps=1, warmup=1)
+    gbs, dt, cores, kind, what = c2_cpu_reference(workload, rows, steps=1, warmup=1)
     steps = int(max(1, min(20, budget_s / max(dt, 1e-3))))
-    gbs, dt, cores = cpu_reference_run(workload, rows, steps=steps, warmup=0)
-    return {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": "%d of %d rows x %d cols, %d passes, numpy restatement (oracle/), "
-                      "row blocks on %d threads" % (rows, C2_ROWS, C2_COLS, steps, cores)}
+    gbs, dt, cores, kind, what = c2_cpu_reference(workload, rows, steps=steps, warmup=0)
+    return {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": "%d of %d rows x %d cols, %d passes, %s" % (rows, C2_ROWS, C2_COLS, steps, what)}
+
+
+# ---------------------------------------------------------------------------------------------
+def slim(line, keys=("metric", "value", "unit", "ms_per_step", "config", "roofline", "repeats",
+                     "gpu_launches", "allreduce", "step_time_ms_by_kind", "loss_first_steps",
+                     "loss_last", "clocks", "scaling")):
+    return {k: line[k] for k in keys if k in line} if line else None
+
+
+def run_b200(args, rank, world):
+    import torch
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    try:
+        w = args.workload
+        if w.startswith("gemm"):
+            return measure_gemm(args, rank, world, torch, dist, local, w == "gemm_flex16",
+                                args.size, args.steps, args.repeats)
+        if w.startswith("resnet20_train"):
+            return run_resnet_train(args, rank, world, torch, dist, local)
+        if w.startswith("c2"):
+            line = measure_c2(args, rank, world, torch, dist, local, w == "c2_flex16", args.rows,
+                              args.steps, args.repeats)
+            if line is not None and world == 1 and not args.no_cpu_baseline:
+                line["cpu_baseline"] = c2_cpu_baseline(w)
+            return line
+        line = run_resnet(args, rank, world, torch, dist, local)
+        torch.cuda.empty_cache()
+        if w == "resnet20_flex16" and not args.no_extras and args.batch == RESNET_N:
+            # the rest of the headline metric, in the same driver-run line
+            extras = {}
+            if world == 1:
+                extras["c2_flex16"] = slim(measure_c2(args, rank, world, torch, dist, local, True,
+                                                      C2_ROWS, 20, 3, with_e2e=False))
+                extras["c2_fp32"] = slim(measure_c2(args, rank, world, torch, dist, local, False,
+                                                    C2_ROWS, 20, 3, with_e2e=False))
+                extras["gemm_flex16_8192"] = slim(measure_gemm(args, rank, world, torch, dist,
+                                                               local, True, 8192, 10, 3,
+                                                               with_e2e=False))
+            extras["resnet20_train_flex16"] = slim(measure_training(
+                args, rank, world, torch, dist, local, True, 10, 3, with_e2e=False))
+            if line is not None:
+                line["extras"] = extras
+        if line is not None and world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = resnet_cpu_reference(args.batch, steps=10, warmup=1,
+                                                        budget_s=12.0)
+        return line
+    finally:
+        if dist is not None:
+            dist.destroy_process_group()
 
 
 def run_reference(args, rank, world):
+    """The reference's CPU implementation of the workload on the host cores (rank 0 only)."""
     if rank != 0:
         return None
-    if args.workload.startswith("gemm"):
+    cores = os.cpu_count() or 1
+    w = args.workload
+    zero_copy = {"h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    if w.startswith("gemm"):
         n = min(args.size, 2048)
-        rng = np.random.RandomState(0)
-        flex = args.workload == "gemm_flex16"
-        a = rng.randint(-32767, 32768, (n, n)).astype(np.float64 if flex else np.float32)
-        bm = rng.randint(-32767, 32768, (n, n)).astype(np.float64 if flex else np.float32)
-        a @ bm
+        flex = w == "gemm_flex16"
+        r = np.random.RandomState(0)
+        fe = reference_frontend()
+        av = r.randint(-32767, 32768, (n, n)).astype(np.float32)
+        bv = r.randint(-32767, 32768, (n, n)).astype(np.float32)
+        if fe is not None:
+            rng, ngt = fe
+            M, K, N = [rng.make_axis(n, name=nm) for nm in ("M", "K", "N")]
+            a, b = rng.placeholder([M, K]), rng.placeholder([K, N])
+            cpu = ngt.make_transformer_factory("cpu")()
+            comp = cpu.computation(rng.dot(a, b), a, b)
+            one, kind = (lambda: comp(av, bv)), "reference"
+            what = "reference CPUTransformer DotOp (np.dot, cpu/cpuengine.py:339-350)"
+        else:
+            one, kind, what = (lambda: av @ bv), "port", "numpy matmul"
+        one()
         t0 = time.perf_counter()
         for _ in range(max(1, args.steps)):
-            a @ bm
+            one()
         dt = (time.perf_counter() - t0) / max(1, args.steps)
         v = round(2.0 * n ** 3 / dt / 1e12, 4)
-        cores = os.cpu_count() or 1
-        return {"impl": "reference", "metric": "GEMM Tops/s (2MNK/t)", "value": v,
+        base = {"value": v, "unit": "Tops/s", "cores": cores, "kind": kind,
+                "sample": "%s, %d^3 (bounded from %d^3), %d BLAS threads" % (what, n, args.size, cores)}
+        return {"impl": "reference", "metric": "%s GEMM T%sMAC-op/s (2MNK/t), M=N=K=%d"
+                % ("flex16" if flex else "fp32", "flex-" if flex else "", args.size), "value": v,
                 "unit": "Tops/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f64 (exact for int16 products)" if flex else "f32",
-                "data": "synthetic", "config": {"workload": args.workload, "M": n, "N": n, "K": n},
-                "cpu_baseline": {"value": v, "unit": "Tops/s", "cores": cores, "kind": "port",
-                                 "sample": "numpy matmul %d^3 (the reference CPU transformer's "
-                                           "Dot is np.dot), %d BLAS threads" % (n, cores)},
-                "e2e": {"value": v, "unit": "Tops/s", "h2d_bytes_per_step": 0,
-                        "d2h_bytes_per_step": 0}, "gpu_launches": 0}
-    if args.workload.startswith("resnet20_train"):
-        flex = args.workload == "resnet20_train_flex16"
-        b = train_cpu_baseline(steps=max(1, min(args.steps, 3)))
+                "vs_baseline": None, "dtype": "f32 (numpy)", "data": "synthetic",
+                "config": {"workload": w, "M": args.size, "N": args.size, "K": args.size},
+                "cpu_baseline": base, "e2e": dict(value=v, unit="Tops/s", **zero_copy),
+                "gpu_launches": 0}
+    if w.startswith("resnet20_train"):
+        flex = w == "resnet20_train_flex16"
+        b = train_cpu_reference(args.global_batch, steps=max(1, min(args.steps, 3)))
         return {
             "impl": "reference",
             "metric": "ResNet-20 %s data-parallel training img/s" % ("flex16" if flex else "fp32"),
             "value": b["value"], "unit": "img/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": b["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32 (numpy)", "data": "synthetic",
-            "config": {"workload": args.workload, "global_batch": args.global_batch,
+            "config": {"workload": w, "global_batch": args.global_batch,
                        "image": [3, 32, 32], "layout": "C,H,W,N"},
-            "cpu_baseline": b,
-            "e2e": {"value": b["value"], "unit": "img/s", "h2d_bytes_per_step": 0,
-                    "d2h_bytes_per_step": 0},
+            "cpu_baseline": b, "e2e": dict(value=b["value"], unit="img/s", **zero_copy),
             "gpu_launches": 0,
         }
-    if args.workload.startswith("resnet20"):
-        flex = args.workload == "resnet20_flex16"
-        b = resnet_cpu_baseline(steps=max(1, args.steps))
+    if w.startswith("resnet20"):
+        flex = w == "resnet20_flex16"
+        b = resnet_cpu_reference(args.batch, steps=max(1, args.steps), warmup=max(1, args.warmup),
+                                 budget_s=120.0)
+        fe = reference_frontend()
+        frontend = ("reference examples/resnet/resnet.py BuildResnet('cifar10', 20, False, 3, "
+                    "batch_norm=False) via the ngraph plug-in") if fe is not None else \
+            "this package's restatement of ResNet-20 (reference tree absent)"
         return {
             "impl": "reference",
             "metric": "ResNet-20 %s inference img/s" % ("flex16" if flex else "fp32"),
             "value": b["value"], "unit": "img/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": b["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32 (numpy)", "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": RESNET_N, "image": [3, 32, 32],
-                       "layout": "C,H,W,N", "convolutions": 22, "replicas": world},
-            "cpu_baseline": b,
-            "e2e": {"value": b["value"], "unit": "img/s", "h2d_bytes_per_step": 0,
-                    "d2h_bytes_per_step": 0},
+            "config": resnet_config(w, b["batch"], world, frontend),
+            "cpu_baseline": b, "e2e": dict(value=b["value"], unit="img/s", **zero_copy),
             "gpu_launches": 0,
         }
     rows = 256
-    gbs, dt, cores = cpu_reference_run(args.workload, rows, max(1, args.steps), max(0, args.warmup))
-    flex = args.workload == "c2_flex16"
+    gbs, dt, cores, kind, what = c2_cpu_reference(w, rows, max(1, args.steps), max(0, args.warmup))
+    flex = w == "c2_flex16"
     return {
         "impl": "reference",
         "metric": "fused-EW HBM GB/s (y=tanh(a*x+b)*sigmoid(c), row sum and row maxabs)",
@@ -916,13 +1243,11 @@ def run_reference(args, rank, world):
         "scaling": "weak", "vs_baseline": None,
         "dtype": "flex16 (i16 mantissa storage, f32 math)" if flex else "f32",
         "data": "synthetic",
-        "config": {"workload": args.workload, "shape": [C2_ROWS, C2_COLS], "replicas": world},
-        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": "each step = %d of %d rows x %d cols through the numpy "
-                                   "restatement (oracle/), row blocks on %d threads"
-                                   % (rows, C2_ROWS, C2_COLS, cores)},
-        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0,
-                "d2h_bytes_per_step": 0},
+        "config": {"workload": w, "shape": [C2_ROWS, C2_COLS], "replicas": world},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
+                         "sample": "each step = %d of %d rows x %d cols, %s"
+                                   % (rows, C2_ROWS, C2_COLS, what)},
+        "e2e": dict(value=round(gbs, 3), unit="GB/s", **zero_copy),
         "gpu_launches": 0,
     }
 
@@ -932,14 +1257,16 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="the timed loop of --steps steps is run this many times; median reported")
     ap.add_argument("--workload", default="resnet20_flex16",
                     choices=["resnet20_flex16", "resnet20_fp32", "c2_flex16", "c2_fp32",
                              "gemm_flex16", "gemm_fp32", "resnet20_train_flex16",
                              "resnet20_train_fp32"])
     ap.add_argument("--global-batch", type=int, default=1024,
                     help="images per training step over all GPUs (training workloads)")
-    ap.add_argument("--bucket-bytes", type=int, default=25 * 1024 * 1024,
-                    help="allreduce bucket size (training workloads)")
+    ap.add_argument("--bucket-bytes", type=int, default=0,
+                    help="upper bound of an allreduce bucket (0: the library's default)")
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the GEMM workloads")
     ap.add_argument("--batch", type=int, default=RESNET_N, help="images per GPU (ResNet-20)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
@@ -947,6 +1274,8 @@ def main():
                     help="rows of the microbenchmark (smaller values are for profiler captures)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="default workload only: leave out configurations 2, 3 and 5")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch kernel by kernel instead of replaying a CUDA graph")
     args = ap.parse_args()

@@ -6,7 +6,7 @@ peer-to-peer memcpy into peer scratch, a float_accum kernel, an all-gather by pe
 three MPI barriers and host synchronisations, with no overlap with back-propagation.
 
 Here every tensor that goes through an allreduce lives inside one flat arena, cut into buckets of at
-most `bucket_bytes` (25 MB by default) in the order the tensors are produced.  When the last tensor
+most `bucket_bytes` (25 MB by default; at least four buckets per step) in the order the tensors are produced.  When the last tensor
 of a bucket has been produced, ONE collective is started for the whole bucket on the communication
 stream (torch.distributed: NCCL over NVLink/NVSwitch on GPUs, gloo in CPU tests); the compute
 stream only waits for it right before the first consumer of a reduced tensor, so the exchange
@@ -24,13 +24,20 @@ ALIGN_ELEMS = 64          # every tensor starts on a 256-byte boundary inside th
 class BucketPlan(object):
     """Assigns tensors (given in production order as (key, n_elements)) to arena offsets and
     buckets.  A tensor never straddles two buckets; a tensor larger than the limit gets a bucket
-    of its own."""
+    of its own.  `bucket_bytes` is the upper bound of a bucket; `min_buckets` > 1 lowers the limit
+    to an even share of the total, so that a small model (ResNet-20: 1.1 MB of gradients, far below
+    25 MB) still exchanges in several pieces, each started as its last gradient lands, instead
+    of in one piece after back-propagation has ended."""
 
-    def __init__(self, sizes, bucket_bytes=DEFAULT_BUCKET_BYTES, itemsize=4):
+    def __init__(self, sizes, bucket_bytes=DEFAULT_BUCKET_BYTES, itemsize=4, min_buckets=1):
         self.offsets = {}
         self.bucket_of = {}
         self.buckets = []          # (start_elem, end_elem, [keys])
+        sizes = list(sizes)
         limit = max(1, int(bucket_bytes) // itemsize)
+        if min_buckets > 1:
+            total = sum(-(-int(n) // ALIGN_ELEMS) * ALIGN_ELEMS for _, n in sizes)
+            limit = max(1, min(limit, -(-total // int(min_buckets))))
         cur_start, cur_end, cur_keys = 0, 0, []
         for key, n in sizes:
             n_pad = -(-int(n) // ALIGN_ELEMS) * ALIGN_ELEMS
@@ -162,7 +169,10 @@ class BucketedAllReduce(object):
         self.flush(index)
 
     def wait_for(self, key):
-        """Called before the first consumer of the reduced tensor `key`."""
+        """Called before the first consumer of the reduced tensor `key`.  A tensor that another
+        computation exchanged (and finished with) needs no waiting here."""
+        if key not in self.plan.bucket_of:
+            return
         b = self.plan.bucket_of[key]
         off = self.plan.offsets[key]
         if off >= self.launched_upto[b]:

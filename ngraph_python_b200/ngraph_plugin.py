@@ -55,13 +55,39 @@ def _is_zero(op):
             float(np.asarray(op.initial_value)) == 0.0)
 
 
-class GraphTranslator(object):
-    """reference Op -> ngraph_python_b200 Op, memoised."""
+def _reduce_tag(op):
+    """The reduce_func an op is tagged with (a ValueOp carries the tag of its value tensor)."""
+    op = op.forwarded
+    while True:
+        rf = op.metadata.get("reduce_func")
+        if rf:
+            return rf
+        if isinstance(op, ref.ValueOp):
+            op = op.value_tensor.forwarded
+            continue
+        return None
 
-    def __init__(self):
+
+class GraphTranslator(object):
+    """reference Op -> ngraph_python_b200 Op, memoised.
+
+    replicas > 1: the graph is one replica's share of a data-parallel job.  An exchange is placed
+    wherever the reference's communication pass would place one: between a tensor tagged with
+    `reduce_func` -- autodiff tags every gradient 'sum' (ngraph/op_graph/op_graph.py:4294-4297)
+    -- and a consumer without the tag (ngraph/factory/comm_node_factory.py:314-318,
+    ngraph/transformers/passes/hetrpasses.py:63-89).  shard_batch: every replica built its graph
+    on its own shard of the global batch, so the optimizer's `/ batch_size`
+    (ngraph/frontends/neon/optimizer.py:177-198) divides by the shard's size; the summed gradient
+    is then also divided by the number of replicas, which makes it the division by the global
+    batch size the reference performs."""
+
+    def __init__(self, replicas=1, shard_batch=True):
         self.memo = {}
         self.bare = {}       # AssignableTensorOp -> its translation (shared with memo)
         self.axis_memo = {}
+        self.replicas = int(replicas)
+        self.shard_batch = bool(shard_batch)
+        self.exchanges = {}  # tagged reference op -> its allreduce
 
     def axis(self, a):
         key = (a.name, a.length)
@@ -87,6 +113,19 @@ class GraphTranslator(object):
             out = b2.sequential([self(d) for d in deps] + [out])
         self.memo[op] = out
         return out
+
+    def _arg(self, consumer, a):
+        """Translation of argument `a` as `consumer` reads it: through an allreduce where the
+        reference's communication pass would put one."""
+        if self.replicas > 1 and "reduce_func" not in consumer.metadata:
+            rf = _reduce_tag(a)
+            if rf is not None:
+                key = a.forwarded
+                if key not in self.exchanges:
+                    func = "mean" if (rf == "sum" and self.shard_batch) else rf
+                    self.exchanges[key] = b2.allreduce(self(a), reduce_func=func)
+                return self.exchanges[key]
+        return self(a)
 
     def _target(self, op):
         """(translated assignment target without sequencing wrappers, ops that must run first)."""
@@ -129,7 +168,7 @@ class GraphTranslator(object):
             # the target is the tensor (or a view of it) itself; what its description must run
             # after (a Fill of the same tensor, say) runs before the assignment
             target, before = self._target(op.args[0])
-            assign = b2.assign(target, self(op.args[1]))
+            assign = b2.assign(target, self._arg(op, op.args[1]))
             return b2.sequential(before + [assign]) if before else assign
         if isinstance(op, ref.Fill):
             return b2.assign(self(op.args[0]), b2.constant(float(op.scalar)))
@@ -137,7 +176,7 @@ class GraphTranslator(object):
             # the number of elements along the reduction axes (what mean and variance divide by:
             # ngraph/op_graph/op_graph.py:4012-4029); the reference folds it into a constant too
             return b2.constant(float(op.reduction_axes.size))
-        args = [self(a) for a in op.args]
+        args = [self._arg(op, a) for a in op.args]
         if name in _UNARY:
             return _UNARY[name](args[0])
         if name in _BINARY:
@@ -145,7 +184,8 @@ class GraphTranslator(object):
             # plain ReLU; its SimplePrune pass folds the dead half away
             # (ngraph/transformers/passes/passes.py), and so does this translation.
             if name == "Multiply" and (_is_zero(args[0]) or _is_zero(args[1])):
-                return b2.constant(0.0)
+                zero = b2.constant(0.0)
+                return b2.broadcast(zero, self.axes(op.axes)) if len(op.axes) else zero
             if name == "Add" and _is_zero(args[1]) and args[0].axes == self.axes(op.axes):
                 return args[0]
             if name == "Add" and _is_zero(args[0]) and args[1].axes == self.axes(op.axes):
@@ -239,8 +279,9 @@ class B200NgraphTransformer(Transformer):
 
     def __init__(self, **kwargs):
         # the reference base class expects no unknown keyword arguments
+        shard_batch = kwargs.pop("shard_batch", True)
         self.impl = b2t.B200Transformer(**kwargs)
-        self.translator = GraphTranslator()
+        self.translator = GraphTranslator(replicas=self.impl.comm.size, shard_batch=shard_batch)
         self.computations = []
         self.finalized = False
 

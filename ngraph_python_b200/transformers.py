@@ -154,6 +154,8 @@ class Computation(object):
         self.steps = None
         self.executor = None
         self.launches_per_call = 0
+        self._comm_steps = []       # this computation's exchanges, in production order
+        self._allreduce = None      # their arena and bucket plan (one per computation)
 
     # ---- compile -------------------------------------------------------------------------
     def _ordered_ops(self):
@@ -176,7 +178,8 @@ class Computation(object):
         self.steps, self.return_views = planner.plan(self._ordered_ops(), self.returns)
         for s in self.steps:
             planner.finalize_step(s)
-        t._allocate()
+        self._comm_steps = planner.comm_steps
+        t._allocate(self)
         for s in self.steps:
             if hasattr(s, "allocate"):
                 s.allocate(t)
@@ -268,6 +271,7 @@ class Computation(object):
         # -- record ------------------------------------------------------------------------------
         torch.cuda.synchronize()
         before = t.kernel_launches
+        t._allreduce = self._allreduce
         if t._allreduce is not None:
             t._allreduce.begin_call()
         t._recording = has_comm          # comm steps and waits: kernels only, no NCCL, no bookkeeping
@@ -322,6 +326,7 @@ class _Planner(object):
         self.conv_tail_of = {}     # absorbed elementwise op -> its ConvolutionOp
         self.deferred = []         # re-quantisations of reduced tensors, placed at first use
         self.arg_override = {}     # op -> value args after register forwarding
+        self.comm_steps = []       # exchanges of this computation, in the order they are placed
         self.last_assign = {}      # persistent tensor -> the AssignOp that last wrote all of it
 
     # -- helpers ------------------------------------------------------------------------------
@@ -604,7 +609,7 @@ class _Planner(object):
         step.reduce_func = op.reduce_func
         self.steps.append(step)
         self.producer[op] = index
-        t._comm_steps.append(step)
+        self.comm_steps.append(step)
         if t.flex:
             # placed when its first consumer is: a re-quantisation right here would need the
             # reduced values at once and force one small exchange per tensor instead of one per
@@ -1005,11 +1010,11 @@ class B200Transformer(object):
         self.computations = []
         self.comm = kwargs.pop("comm", None) or commmod.SingleProcessComm()
         self.bucket_bytes = int(kwargs.pop("bucket_bytes", commmod.DEFAULT_BUCKET_BYTES))
+        self.min_buckets = int(kwargs.pop("min_buckets", 4))
         self._alias = {}
         self._pinned = {}
         self._inputs_written = []
-        self._comm_steps = []
-        self._allreduce = None
+        self._allreduce = None      # exchange state of the computation that ran last
         self._recording = False     # a CUDA graph segment is being recorded
         self._buffers = collections.OrderedDict()   # op -> Buffer
         self._views = {}
@@ -1145,16 +1150,16 @@ class B200Transformer(object):
         buf.slot_write = src.slot_write
         buf.shares_entry = True
 
-    def _allocate(self):
+    def _allocate(self, comp=None):
         if self.plan_only:
             return
         torch = self.torch
-        if self._comm_steps and self._allreduce is None:
-            # every tensor that is exchanged lives in one flat fp32 arena, bucketed in the order
-            # the tensors are produced
-            steps = sorted(self._comm_steps, key=lambda s: s.index)
+        if comp is not None and comp._comm_steps and comp._allreduce is None:
+            # every tensor this computation exchanges lives in one flat fp32 arena of its own,
+            # bucketed in the order the tensors are produced (step indices are per computation)
+            steps = sorted(comp._comm_steps, key=lambda s: s.index)
             plan = commmod.BucketPlan([(s.key, s.arena_buffer.size) for s in steps],
-                                      self.bucket_bytes)
+                                      self.bucket_bytes, min_buckets=self.min_buckets)
             arena = torch.zeros((max(plan.total, 1),), dtype=torch.float32, device=self.device)
             funcs = {}
             last_of_bucket = {}
@@ -1165,7 +1170,8 @@ class B200Transformer(object):
                 last_of_bucket[plan.bucket_of[s.key]] = s
             for b_index, s in last_of_bucket.items():
                 s.closes_bucket = b_index
-            self._allreduce = commmod.BucketedAllReduce(self.comm, plan, arena, funcs)
+            comp._allreduce = commmod.BucketedAllReduce(self.comm, plan, arena, funcs)
+            self._allreduce = comp._allreduce
         for op, b in self._buffers.items():
             if b.tensor is None:
                 dt = torch.int16 if b.flex else torch.float32
@@ -1207,11 +1213,33 @@ class B200Transformer(object):
         torch = self.torch
         buf = view.buffer
         buf.version += 1
-        arr = np.asarray(value, dtype=np.float32)
-        if arr.shape not in ((), view.axes.lengths) and arr.size != buf.size:
-            raise ValueError("value shape %s does not match tensor axes %s" % (arr.shape, view.axes))
         if not view.is_dense():
             raise ValueError("host writes need a dense tensor")
+        if isinstance(value, torch.Tensor) and value.is_cuda:
+            # a tensor that already lives on the device (the reference's DeviceTensor.__setitem__
+            # takes a GPUArray the same way, gputransform.py:806-854): device-to-device copy
+            if tuple(value.shape) != tuple(view.axes.lengths) and \
+                    tuple(value.shape) != (buf.size,):
+                raise ValueError("value shape %s does not match tensor axes %s"
+                                 % (tuple(value.shape), view.axes))
+            src = value.to(torch.float32).reshape(-1)
+            if not buf.flex:
+                buf.tensor.copy_(src, non_blocking=True)
+                return
+            if buf.staging is None:
+                buf.staging = torch.empty((max(buf.size, 1),), dtype=torch.float32,
+                                          device=self.device)
+            buf.staging.copy_(src, non_blocking=True)
+            return
+        arr = np.asarray(value, dtype=np.float32)
+        # a scalar broadcasts; otherwise the shape must be the tensor's, or flat with its size
+        # (a transposed or otherwise differently shaped array of the right size is an error, as
+        # it is for the reference's DeviceTensor.__setitem__)
+        if arr.shape not in ((), tuple(view.axes.lengths), (buf.size,)):
+            squeezed = tuple(n for n in arr.shape if n != 1)
+            if squeezed != tuple(n for n in view.axes.lengths if n != 1):
+                raise ValueError("value shape %s does not match tensor axes %s"
+                                 % (arr.shape, view.axes))
         arr = np.ascontiguousarray(np.broadcast_to(arr, view.axes.lengths)
                                    if arr.shape == () else arr.reshape(view.axes.lengths))
         src = torch.from_numpy(np.array(arr.reshape(-1), copy=not arr.flags.writeable))
@@ -1326,6 +1354,7 @@ class B200Transformer(object):
 
     def _begin_call(self, comp):
         self._ensure_scratch()
+        self._allreduce = comp._allreduce
         if self._allreduce is not None:
             self._allreduce.begin_call()
         if not self.flex:

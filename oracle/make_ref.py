@@ -11,7 +11,7 @@ git-ignored (no reference source enters the history) and is only ever imported, 
   oracle/_ref/third_party/            Python wrapper the CPU transformer's generated code imports
   oracle/_ref/SOURCE                  where it came from and when
 The third-party packages the reference imports and this image lacks are stood in for by the small
-shims of oracle/ref_shims/ (committed; own code) -- see oracle/ref_env.py, which activates both.
+modules of ngraph_python_b200/ngraph_compat/ (own code) -- see oracle/ref_env.py.
 """
 import os
 import shutil

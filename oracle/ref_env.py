@@ -4,14 +4,13 @@ Test infrastructure (used by tests/, by the fixture generator and by the CPU-ref
 bench.py; never by the package).  Search order:
   1. the directory named by the environment variable B200NG_REFERENCE,
   2. oracle/_ref/ (made by oracle/make_ref.py from a checkout of NervanaSystems/ngraph-python).
-`install()` activates the compatibility shims of oracle/ref_shims/ first (the unmodified reference
-was written for Python 2.7/3.5 and numpy 1.x), then puts the tree on sys.path.
+`install()` goes through ngraph_python_b200.ngraph_compat (the unmodified reference was written
+for Python 2.7/3.5 and numpy 1.x), which puts the tree on sys.path.
 """
 import os
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SHIMS = os.path.join(HERE, "ref_shims")
 
 
 def reference_root():
@@ -28,10 +27,11 @@ def install():
     root = reference_root()
     if root is None:
         return None
-    if SHIMS not in sys.path:
-        sys.path.insert(0, SHIMS)
-    import ref_bootstrap
-    ref_bootstrap.install(root)
+    repo = os.path.dirname(HERE)
+    if repo not in sys.path:
+        sys.path.insert(0, repo)
+    from ngraph_python_b200 import ngraph_compat
+    ngraph_compat.install(root)
     resnet_dir = os.path.join(root, "examples", "resnet")
     if os.path.isdir(resnet_dir) and resnet_dir not in sys.path:
         sys.path.insert(0, resnet_dir)

@@ -4,7 +4,7 @@ reference's own CPU transformer.  Run in a container that has the reference tree
     python tests/golden/make_fixtures.py [/path/to/ngraph-python] [case ...]
 
 Without a path the tree named by B200NG_REFERENCE, else oracle/_ref/ (oracle/make_ref.py), is
-used.  The reference is imported unmodified through the compatibility shims of oracle/ref_shims/.
+used.  The reference is imported unmodified (ngraph_python_b200/ngraph_compat supplies what it needs).
 """
 import os
 import sys

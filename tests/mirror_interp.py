@@ -12,9 +12,12 @@ from oracle import ew_oracle as ew
 
 
 class Interp(object):
-    def __init__(self):
+    def __init__(self, allreduce=None):
+        """allreduce(array, reduce_func) -> array: what an AllReduceOp does (identity when None,
+        i.e. one replica); a multi-process test passes a gloo collective here."""
         self.state = {}      # AssignableTensorOp -> ndarray (axes order of the op)
         self.cache = {}
+        self.allreduce = allreduce
 
     def _to(self, val, src_axes, dst_axes):
         """Re-lay `val` (axes src_axes) out over dst_axes (superset, any order), broadcasting."""
@@ -119,5 +122,9 @@ class Interp(object):
                      (pp["str_h"], pp["str_w"]))
             return out[:, None].reshape(op.axes.lengths)
         if isinstance(op, g.AllReduceOp):
-            return self.eval(op.args[0])
+            val = self.eval(op.args[0])
+            if self.allreduce is None:
+                return val
+            return np.asarray(self.allreduce(np.ascontiguousarray(val, dtype=np.float32),
+                                             op.reduce_func), dtype=np.float32)
         raise ValueError("Unhandled op: {}".format(op))

@@ -186,3 +186,29 @@ def test_train_step_two_gpus(flex, case, capture):
     for a, b in zip(got[0], got[1]):
         for x, y in zip(a, b):
             assert np.array_equal(x, y)
+
+
+@pytest.mark.parametrize("flex", [False, True])
+def test_two_exchanging_computations_on_one_transformer(flex):
+    """Every computation has its own exchange arena and bucket plan: a second computation with
+    allreduce ops on the same transformer runs, and calls of the two may alternate."""
+    A, B = ng.make_axis(40, name="A"), ng.make_axis(24, name="B")
+    x = ng.placeholder([A, B])
+    w = ng.variable([A], initial_value=np.zeros(40, np.float32))
+    v = ng.variable([B], initial_value=np.zeros(24, np.float32))
+    t = ng.transformers.allocate_transformer("b200", flex=flex, bucket_bytes=64)
+    g1 = ng.allreduce(ng.sum(x * 2.0, reduction_axes=[B]))
+    g2 = ng.allreduce(ng.sum(x * 3.0, reduction_axes=[A]))
+    g3 = ng.allreduce(ng.sum(x * x, reduction_axes=[A]))
+    c1 = t.computation(ng.sequential([ng.assign(w, w + g1), w]), x)
+    c2 = t.computation([ng.sequential([ng.assign(v, v + g2), v]), g3 * 1.0], x)
+    xv = np.random.RandomState(2).uniform(-1, 1, (40, 24)).astype(np.float32)
+    tol = dict(rtol=1e-2, atol=0.05) if flex else dict(rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(c1(xv), 2 * xv.sum(axis=1), **tol)
+    r2 = c2(xv)
+    np.testing.assert_allclose(r2[0], 3 * xv.sum(axis=0), **tol)
+    np.testing.assert_allclose(r2[1], (xv * xv).sum(axis=0), **tol)
+    np.testing.assert_allclose(c1(xv), 4 * xv.sum(axis=1), **tol)
+    assert c1._allreduce is not c2._allreduce and c2._allreduce is not None
+    assert len(c2._allreduce.plan.buckets) == 2
+    t.close()

@@ -169,3 +169,105 @@ def test_reference_resnet_builder(train):
     got = [np.asarray(it.run([m_out], dict(zip(m_params, vals)))[0]) for _ in range(reps)]
     for g_, w_ in zip(got, want):
         np.testing.assert_allclose(g_, w_, rtol=2e-5, atol=2e-6)
+
+
+# ---- automatic gradient exchange (two gloo ranks on CPU) -------------------------------------
+def _dp_model(n):
+    """A small convolutional classifier with the reference's autodiff and momentum optimizer,
+    built for a batch of n images; weights from the global numpy seed."""
+    from ngraph.frontends.neon import (Sequential, Convolution, Pooling, Affine, Rectlin, Softmax,
+                                       GaussianInit, ConstantInit, GradientDescentMomentum, ax)
+    ax.N.length = n
+    ax.Y.length = 10
+    C, D = rng.make_axis(3, name="C"), rng.make_axis(1, name="D")
+    H, W = rng.make_axis(8, name="H"), rng.make_axis(8, name="W")
+    x = rng.placeholder([C, D, H, W, ax.N])
+    t = rng.placeholder([ax.N])
+    np.random.seed(5)
+    init = GaussianInit(0., 0.1)
+    model = Sequential([
+        Convolution((3, 3, 8), filter_init=init, strides=1, padding=1, activation=Rectlin()),
+        Pooling((2, 2), strides=2, pool_type="avg"),
+        Affine(weight_init=init, bias_init=ConstantInit(0.), activation=Softmax(), axes=(ax.Y,))])
+    loss = rng.cross_entropy_multi(model(x), rng.one_hot(t, axis=ax.Y))
+    updates = GradientDescentMomentum(0.1, 0.9)(loss)
+    return rng.sequential([updates, rng.mean(loss, out_axes=[])]), x, t
+
+
+def _dp_data(global_n):
+    rs = np.random.RandomState(8)
+    return (rs.standard_normal((3, 1, 8, 8, global_n)).astype(np.float32),
+            rs.randint(0, 10, global_n).astype(np.float32))
+
+
+def _dp_rank(rank, world, port, global_n, steps, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n = global_n // world
+        train, x, t = _dp_model(n)
+        tr = plugin.GraphTranslator(replicas=world)
+        m_train, m_x, m_t = tr(train), tr(x), tr(t)
+
+        def allreduce(arr, func):
+            buf = torch.from_numpy(arr.copy())
+            dist.all_reduce(buf)
+            return buf.numpy() / (world if func == "mean" else 1)
+        it = Interp(allreduce=allreduce)
+        xv, tv = _dp_data(global_n)
+        lo, hi = rank * n, (rank + 1) * n
+        losses = [float(np.asarray(it.run([m_train], {m_x: xv[..., lo:hi], m_t: tv[lo:hi]})[0]))
+                  for _ in range(steps)]
+        q.put((rank, losses, len(tr.exchanges), sorted(set(e.reduce_func
+                                                           for e in tr.exchanges.values()))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gradient_exchange_is_inserted_from_reduce_func_tags():
+    """Two replicas, each with half of the batch, built from the reference's own autodiff and
+    optimizer with nothing written by hand: the translation puts one exchange on every gradient
+    (tagged reduce_func='sum' by the reference, op_graph.py:4294-4297) where the untagged
+    `/ batch_size` reads it, and the two replicas then train exactly like the reference CPU
+    transformer on the whole batch: the mean of their post-step losses follows its loss."""
+    import socket
+    import torch.multiprocessing as mp
+    global_n, steps, world = 16, 3, 2
+    train, x, t = _dp_model(global_n)
+    cpu = ngt.make_transformer_factory("cpu")()
+    cref = cpu.computation(train, x, t)
+    xv, tv = _dp_data(global_n)
+    want = [float(cref(xv, tv)) for _ in range(steps)]
+    cpu.close()
+    # one replica: nothing is inserted
+    solo = plugin.GraphTranslator()
+    solo(train)
+    assert not solo.exchanges
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_dp_rank, args=(r, world, port, global_n, steps, q))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        got = dict((r, (l_, n_, f_)) for r, l_, n_, f_ in (q.get(timeout=300) for _ in range(world)))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    for r in range(world):
+        assert got[r][1] == 3          # filters, linear weights, bias: one per trainable tensor
+        assert got[r][2] == ["mean"]   # sum over replicas, divided by their number (shards)
+    mean_loss = np.mean([got[r][0] for r in range(world)], axis=0)
+    np.testing.assert_allclose(mean_loss, want, rtol=2e-5)
+    assert want[-1] < want[0]
