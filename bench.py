@@ -72,6 +72,9 @@ RESNET_N = 256
 RESNET_FLOP_PER_IMG = 82.1e6
 RESNET_CONV_ELEMS_PER_256 = 58458112 + 55574528 + 270512
 TRAIN_PARAM_BYTES = 1084648      # fp32 gradients exchanged per step (no batch norm, no biases)
+REFERENCE_NETWORK = ("reference examples/resnet/resnet.py BuildResnet('cifar10', 20, False, 3, "
+                     "batch_norm=False), built with the reference's ngraph")
+OWN_NETWORK = "this package's restatement of ResNet-20 (reference tree absent)"
 CIFAR_MEAN = np.array([113.9, 123.0, 125.3], np.float32)
 CIFAR_STD = np.array([66.7, 62.1, 63.0], np.float32)
 
@@ -250,7 +253,7 @@ def reference_frontend():
     return mods
 
 
-def reference_resnet20(rng, n, train=False, lr=0.1, momentum=0.9):
+def reference_resnet20(rng, n, train=False, lr=0.1, momentum=0.9, features=False):
     """examples/resnet/resnet.py:74-117 of the reference: CIFAR-10 ResNet-20 without batch norm.
     Returns (result op, placeholders)."""
     from resnet import BuildResnet
@@ -263,7 +266,14 @@ def reference_resnet20(rng, n, train=False, lr=0.1, momentum=0.9):
     model = BuildResnet('cifar10', 20, False, 3, batch_norm=False)
     if not train:
         with Layer.inference_mode_on():
-            return model(x), [x]
+            out = model(x)
+            if features:
+                # the pooled features that feed the linear layer (same layers, same weights): the
+                # softmax of this network without batch norm is all but one-hot, the features
+                # are what a parity check can bite on
+                from ngraph.frontends.neon import Sequential
+                return out, [x], Sequential(model.layers[:-2])(x)
+            return out, [x]
     t = rng.placeholder([ax.N])
     loss = rng.cross_entropy_multi(model(x), rng.one_hot(t, axis=ax.Y))
     updates = GradientDescentMomentum(lr, momentum)(loss)
@@ -396,13 +406,13 @@ class ResnetInference(object):
         fe = reference_frontend()
         if fe is not None:
             rng, ngt = fe
-            out, params = reference_resnet20(rng, n)
+            out, params, feat = reference_resnet20(rng, n, features=True)
             self.outer_t = ngt.make_transformer_factory("b200", device_id=local, flex=flex)()
             self.call = self.outer_t.computation(out, *params)
+            self.check = self.outer_t.computation([out, feat], *params)
             self.t, self.comp = self.outer_t.impl, self.call.impl
-            self.frontend = "reference examples/resnet/resnet.py BuildResnet('cifar10', 20, " \
-                            "False, 3, batch_norm=False) via the ngraph plug-in"
-            self.graph = (out, params)
+            self.frontend = REFERENCE_NETWORK
+            self.graph = ([out, feat], params)
             shape, data = (3, 32, 32, n), cifar_like(seed, n)
         else:
             import ngraph_python_b200 as ng
@@ -410,8 +420,9 @@ class ResnetInference(object):
             self.outer_t = ng.transformers.allocate_transformer("b200", device_id=local, flex=flex)
             outs, params = build_resnet20(ng, n, self.weights)
             self.call = self.outer_t.computation(outs[0], *params)
+            self.check = self.outer_t.computation([outs[0]], *params)
             self.t, self.comp = self.outer_t, self.call
-            self.frontend = "this package's restatement of ResNet-20 (reference tree absent)"
+            self.frontend = OWN_NETWORK
             self.graph = None
             shape = (3, 1, 32, 32, n)
             data = np.random.RandomState(seed).standard_normal(shape).astype(np.float32)
@@ -420,15 +431,17 @@ class ResnetInference(object):
         self.host[...] = data
 
     def cpu_expectation(self):
-        """(expected softmax, what computed it) on the host cores, same graph and input."""
+        """(expected results, what computed them) on the host cores, same graph and input: the
+        softmax and, with the reference front end, the pooled features under it."""
         fe = reference_frontend()
         if fe is not None and self.graph is not None:
             _, ngt = fe
             cpu = ngt.make_transformer_factory("cpu")()
-            want = np.array(cpu.computation(self.graph[0], *self.graph[1])(self.host), copy=True)
+            res = cpu.computation(self.graph[0], *self.graph[1])(self.host)
+            want = [np.array(r, copy=True) for r in res]
             cpu.close()
             return want, "reference CPUTransformer, same graph and input"
-        want = resnet20_numpy(self.host[:, 0], self.weights)
+        want = [resnet20_numpy(self.host[:, 0], self.weights)]
         return want, "numpy restatement (oracle/conv_oracle.py), same weights and input"
 
     def close(self):
@@ -436,16 +449,24 @@ class ResnetInference(object):
 
 
 def check_parity(got, want, flex):
-    got = np.asarray(got, dtype=np.float64).reshape(want.shape)
-    err = float(np.max(np.abs(got - want)))
-    if flex:
-        atol, rtol = flex_tolerance(want)
-        atol *= 4          # the expectation is the fp32 result, not a flex evaluation
-    else:
-        atol, rtol = 1e-5, 1e-4
-    ok = bool(np.all(np.abs(got - want) <= atol + rtol * np.abs(want)))
-    agree = float((got.argmax(axis=0) == want.argmax(axis=0)).mean())
-    return {"ok": ok, "max_abs_err": err, "atol": atol, "rtol": rtol, "argmax_agreement": agree}
+    """got, want: lists [softmax (10, n), pooled features (64, ..., n) if available]."""
+    report = {"ok": True}
+    for name, g_, w_ in zip(("softmax", "pooled_features"), got, want):
+        w_ = np.asarray(w_, dtype=np.float64)
+        g_ = np.asarray(g_, dtype=np.float64).reshape(w_.shape)
+        if flex:
+            atol, rtol = flex_tolerance(w_)
+            atol *= 4          # the expectation is the fp32 result, not a flex evaluation
+        else:
+            atol, rtol = 1e-5 * max(1.0, float(np.max(np.abs(w_)))), 1e-4
+        ok = bool(np.all(np.abs(g_ - w_) <= atol + rtol * np.abs(w_)))
+        report[name] = {"ok": ok, "max_abs_err": float(np.max(np.abs(g_ - w_))),
+                        "max_abs_expected": float(np.max(np.abs(w_))), "atol": atol, "rtol": rtol}
+        report["ok"] = report["ok"] and ok
+    w0 = np.asarray(want[0])
+    report["argmax_agreement"] = float((np.asarray(got[0]).reshape(w0.shape).argmax(axis=0)
+                                        == w0.argmax(axis=0)).mean())
+    return report
 
 
 def run_resnet(args, rank, world, torch, dist, local):
@@ -453,7 +474,7 @@ def run_resnet(args, rank, world, torch, dist, local):
     n = args.batch
     net = ResnetInference(torch, local, flex, n, seed=100 + rank)
     t, comp, host = net.t, net.comp, net.host
-    first = np.array(net.call(host), copy=True)
+    first = [np.array(r, copy=True) for r in net.check(host)]
     parity = None
     if rank == 0:
         want, how = net.cpu_expectation()
@@ -516,6 +537,8 @@ def run_resnet(args, rank, world, torch, dist, local):
     conv_gbs = conv_bytes / (conv_ms * 1e-3) / 1e9
     cfg = resnet_config(args.workload, n, world, net.frontend)
     cfg.update({"replicas": world,
+                "transformer": "ngraph.transformers.make_transformer_factory('b200') (plug-in)"
+                               if net.graph is not None else "ngraph_python_b200.transformers",
                 "l2": "L2 flushed by the run itself: each pass streams >126 MB of activations and "
                       "operand planes",
                 "steps_per_pass": len(comp.steps), "cuda_graph": not args.no_graph,
@@ -657,7 +680,7 @@ def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats
         raise SystemExit("global batch must give every GPU a multiple of 128 images")
     n = gn // world
     comm = TorchDistComm() if dist is not None else SingleProcessComm()
-    job = ResnetTraining(torch, local, flex, gn, rank, world, comm, args.bucket_bytes, lr=0.002)
+    job = ResnetTraining(torch, local, flex, gn, rank, world, comm, args.bucket_bytes, lr=args.lr)
     t, comp, host = job.t, job.comp, job.host
     losses = [float(job.call(*host)) for _ in range(3)]
     graphed = False
@@ -750,7 +773,8 @@ def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats
         "data": "synthetic",
         "config": {"workload": "resnet20_train_%s" % ("flex16" if flex else "fp32"),
                    "global_batch": gn, "batch_per_gpu": n,
-                   "image": [3, 32, 32], "layout": "C,H,W,N", "optimizer": "momentum 0.9 + Kahan",
+                   "image": [3, 32, 32], "layout": "C,H,W,N",
+                   "optimizer": "momentum 0.9 + Kahan, lr %g" % args.lr,
                    "network": frontend,
                    "parallelism": "dp%d" % world, "allreduce_buckets": buckets,
                    "bucket_bytes": t.bucket_bytes, "steps_per_pass": n_steps,
@@ -789,18 +813,18 @@ def run_resnet_train(args, rank, world, torch, dist, local):
     flex = args.workload == "resnet20_train_flex16"
     line = measure_training(args, rank, world, torch, dist, local, flex, args.steps, args.repeats)
     if line is not None and world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = train_cpu_reference(args.global_batch, steps=1)
+        line["cpu_baseline"] = train_cpu_reference(args.global_batch, steps=1, lr=args.lr)
     return line
 
 
-def train_cpu_reference(global_n, steps=1):
+def train_cpu_reference(global_n, steps=1, lr=0.1):
     """The reference CPU transformer on one training step of the global batch (hetr itself needs
     mpirun / MLSL, which this image lacks: SURVEY of the reference's hetr path)."""
     cores = os.cpu_count() or 1
     fe = reference_frontend()
     if fe is not None:
         rng, ngt = fe
-        out, params = reference_resnet20(rng, global_n, train=True, lr=0.002)
+        out, params = reference_resnet20(rng, global_n, train=True, lr=lr)
         cpu = ngt.make_transformer_factory("cpu")()
         comp = cpu.computation(out, *params)
         vals = [cifar_like(7, global_n),
@@ -821,7 +845,7 @@ def train_cpu_reference(global_n, steps=1):
     from ngraph_python_b200 import configs
     from tests import mirror_interp
     gn = 32
-    outs, params, vals = configs.resnet_train_step(ng, global_n=gn, hw=32, blocks=3, lr=0.002)
+    outs, params, vals = configs.resnet_train_step(ng, global_n=gn, hw=32, blocks=3, lr=lr)
     interp = mirror_interp.Interp()
     t0 = time.perf_counter()
     for _ in range(steps):
@@ -1202,7 +1226,7 @@ def run_reference(args, rank, world):
                 "gpu_launches": 0}
     if w.startswith("resnet20_train"):
         flex = w == "resnet20_train_flex16"
-        b = train_cpu_reference(args.global_batch, steps=max(1, min(args.steps, 3)))
+        b = train_cpu_reference(args.global_batch, steps=max(1, min(args.steps, 3)), lr=args.lr)
         return {
             "impl": "reference",
             "metric": "ResNet-20 %s data-parallel training img/s" % ("flex16" if flex else "fp32"),
@@ -1219,9 +1243,7 @@ def run_reference(args, rank, world):
         b = resnet_cpu_reference(args.batch, steps=max(1, args.steps), warmup=max(1, args.warmup),
                                  budget_s=120.0)
         fe = reference_frontend()
-        frontend = ("reference examples/resnet/resnet.py BuildResnet('cifar10', 20, False, 3, "
-                    "batch_norm=False) via the ngraph plug-in") if fe is not None else \
-            "this package's restatement of ResNet-20 (reference tree absent)"
+        frontend = REFERENCE_NETWORK if fe is not None else OWN_NETWORK
         return {
             "impl": "reference",
             "metric": "ResNet-20 %s inference img/s" % ("flex16" if flex else "fp32"),
@@ -1276,16 +1298,22 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="default workload only: leave out configurations 2, 3 and 5")
+    ap.add_argument("--lr", type=float, default=0.1, help="learning rate (training workloads)")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch kernel by kernel instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
-        line = run_reference(args, rank, world)
-    else:
-        line = run_b200(args, rank, world)
+    # whatever the libraries print on the way goes to stderr: stdout carries the one JSON line
+    out, sys.stdout = sys.stdout, sys.stderr
+    try:
+        if args.impl == "reference":
+            line = run_reference(args, rank, world)
+        else:
+            line = run_b200(args, rank, world)
+    finally:
+        sys.stdout = out
     if line is not None:
         print(json.dumps(line))
         sys.stdout.flush()

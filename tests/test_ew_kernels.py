@@ -168,3 +168,75 @@ def test_host_quantize_roundtrip():
     bits = torch.zeros((1,), dtype=torch.int32, device="cuda")
     lib.check(lib.raw().b2_absmax_bits_f32(src.data_ptr(), x.size, bits.data_ptr(), 0))
     assert bits.cpu().numpy().view(np.float32)[0] == np.abs(x).max()
+
+
+@pytest.mark.parametrize("flex", [False, True])
+def test_c2_at_benchmark_size_on_sampled_rows(flex):
+    """Benchmark configuration 2 at its stated size, 8192 x 16384: the kernel runs over the whole
+    tensor, 64 sampled rows (the first, the last, and rows on either side of every 1024-row
+    boundary among them) are checked against the oracle with the bars of the small cases.
+    Inputs are drawn on the device; the flex16 run quantises them there with the library's own
+    host-write kernel, and the oracle gets the mantissas of the sampled rows."""
+    torch = _torch()
+    from ngraph_python_b200 import lib
+    rows, cols = 8192, 16384
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    dev32 = [torch.randn((rows, cols), device="cuda", generator=gen) for _ in range(4)]
+    rs = np.random.RandomState(5)
+    pick = sorted(set([0, rows - 1] + [b + d for b in range(1024, rows, 1024) for d in (-1, 0)] +
+                      list(rs.choice(rows, 48, replace=False))))[:64]
+    idx = torch.tensor(pick, device="cuda")
+    k = lib.EwKernel(c2_program(lib, rows, cols, flex))
+    scratch = torch.empty((max(k.scratch_bytes, 4),), dtype=torch.uint8, device="cuda")
+    dt = torch.int16 if flex else torch.float32
+    y = torch.empty((rows, cols), dtype=dt, device="cuda")
+    s = torch.empty((rows,), dtype=dt, device="cuda")
+    m = torch.empty((rows,), dtype=dt, device="cuda")
+    outs = [y.data_ptr(), s.data_ptr(), m.data_ptr()]
+    if not flex:
+        k.launch([d.data_ptr() for d in dev32], outs, scratch=scratch.data_ptr(),
+                 scratch_bytes=k.scratch_bytes)
+        torch.cuda.synchronize()
+        host = [d[idx].cpu().numpy() for d in dev32]
+        ey, es, em = c2_oracle(*host)
+        np.testing.assert_allclose(y[idx].cpu().numpy(), ey, rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(s[idx].cpu().numpy(), es, rtol=1e-4, atol=1e-5 * cols)
+        np.testing.assert_allclose(m[idx].cpu().numpy(), em, rtol=1e-4, atol=1e-5)
+        return
+    decs = [fx.fit_dec(float(d.abs().max().item())) for d in dev32]
+    out_decs = [14, 6, 14]          # |y| < 1; |row sum| stays far below 512; row max|y| < 1
+    table = np.zeros((7, 2), dtype=np.float32)
+    for i, d in enumerate(decs + out_decs):
+        table[i] = (2.0 ** -d, 2.0 ** d)
+    d_table = torch.from_numpy(table).cuda()
+    d_stats = torch.zeros((7,), dtype=torch.int32, device="cuda")
+    dev = []
+    for i, d32 in enumerate(dev32):
+        q = torch.empty((rows, cols), dtype=torch.int16, device="cuda")
+        lib.check(lib.raw().b2_flex_host_quantize(d32.data_ptr(), q.data_ptr(), rows * cols,
+                                                  d_table.data_ptr(), i, d_stats.data_ptr(), 0))
+        dev.append(q)
+    torch.cuda.synchronize()
+    # the device conversion is the oracle's host write, on the sampled rows
+    for i in range(4):
+        assert np.array_equal(dev[i][idx].cpu().numpy(),
+                              fx.host_to_mantissa(dev32[i][idx].cpu().numpy(), decs[i])[0])
+    del dev32
+    d_stats.zero_()
+    k.launch([d.data_ptr() for d in dev], outs, flex_table=d_table.data_ptr(),
+             flex_stats=d_stats.data_ptr(), scratch=scratch.data_ptr(),
+             scratch_bytes=k.scratch_bytes)
+    torch.cuda.synchronize()
+    vals = [fx.dequantize(d[idx].cpu().numpy(), dec) for d, dec in zip(dev, decs)]
+    ey, es, em = c2_oracle(*vals)
+    gy = y[idx].cpu().numpy()
+    diff = np.abs(gy.astype(np.int32) - fx.quantize(ey, out_decs[0]).astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 2e-3
+    gm = m[idx].cpu().numpy()
+    assert np.abs(gm.astype(np.int32) - fx.quantize(em, out_decs[2]).astype(np.int32)).max() <= 1
+    gs = s[idx].cpu().numpy().astype(np.float64) * 2.0 ** -out_decs[1]
+    np.testing.assert_allclose(gs, es, rtol=1e-3, atol=8 * 2.0 ** -out_decs[1] + 1e-4 * cols ** 0.5)
+    # the statistic covers the whole tensor: it is the maximum over everything that was stored
+    assert int(d_stats[4].item()) == int(y.to(torch.int32).abs().max().item())
+    assert int(d_stats[6].item()) == int(m.to(torch.int32).abs().max().item())

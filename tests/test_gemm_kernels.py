@@ -112,3 +112,111 @@ def test_gemm_flex16(M, N, K, layout):
         e2 = exact << (-sh2)
     e2 = np.clip(e2, -32768, 32767)
     assert np.array_equal(dC.cpu().numpy().astype(np.int64), e2)
+
+
+# ---- benchmark configuration 3 at its stated sizes ---------------------------------------------
+# int16 products summed over K <= 8192 stay below 2^45: a float64 BLAS product is an exact oracle.
+def _rne_shift(exact, sh):
+    if sh > 0:
+        half = 1 << (sh - 1)
+        out = (exact + half - 1 + ((exact >> sh) & 1)) >> sh
+    else:
+        out = exact << (-sh)
+    return np.clip(out, -32768, 32767)
+
+
+def _stored(X, transposed):
+    return np.ascontiguousarray(X.T) if transposed else X
+
+
+@pytest.mark.parametrize("n", [1024, 4096, 8192])
+def test_gemm_flex16_benchmark_sizes(n):
+    """M = N = K = n, mantissas uniform in [-32767, 32767], exponents -15 and -12 (benchmark
+    configuration 3), all three operand layouts, the output exponent chosen from the probe launch as the
+    transformer chooses it; then once more with an exponent six bits too fine, where most of
+    the output saturates.  1024 and 4096 are checked in full, 8192 on 48 sampled rows."""
+    import torch
+    from ngraph_python_b200 import lib
+    rng = np.random.RandomState(n)
+    A = rng.randint(-32767, 32768, (n, n)).astype(np.int16)
+    B = rng.randint(-32767, 32768, (n, n)).astype(np.int16)
+    rows = np.arange(n) if n <= 4096 else np.sort(rng.choice(n, 48, replace=False))
+    exact = np.rint(A[rows].astype(np.float64) @ B.astype(np.float64)).astype(np.int64)
+    dec_a, dec_b = 15, 12
+    nbytes = lib.gemm_scratch_bytes(True, n, n, n)
+    keep, sp = _scratch(torch, nbytes)
+    stats = torch.zeros((3,), dtype=torch.int32, device="cuda")
+    probe = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    dC = torch.zeros((n, n), dtype=torch.int16, device="cuda")
+    for layout in ("nn", "nt", "tn"):
+        dA = torch.from_numpy(_stored(A, layout == "tn")).cuda()
+        dB = torch.from_numpy(_stored(B, layout == "nt")).cuda()
+        a_str = (1, n) if layout == "tn" else (n, 1)
+        b_str = (1, n) if layout == "nt" else (n, 1)
+        table = torch.zeros((3, 2), dtype=torch.float32, device="cuda")
+        table[0, 0], table[0, 1] = 2.0 ** -dec_a, 2.0 ** dec_a
+        table[1, 0], table[1, 1] = 2.0 ** -dec_b, 2.0 ** dec_b
+
+        def call(probe_flag):
+            lib.check(lib.raw().b2_gemm_flex16(
+                dA.data_ptr(), a_str[0], a_str[1], dB.data_ptr(), b_str[0], b_str[1],
+                dC.data_ptr(), n, n, n, n, table.data_ptr(), 0, 1, 2, stats.data_ptr(), sp, nbytes,
+                probe.data_ptr(), status.data_ptr(), probe_flag, 0))
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+        probe.zero_()
+        call(1)
+        imax = int(probe.item())
+        if n <= 4096:
+            assert imax == int(np.abs(exact).max())
+        else:
+            assert imax >= int(np.abs(exact).max())
+        dec_c = fx.fit_dec(float(imax) * 2.0 ** -(dec_a + dec_b))
+        for extra in (0, 6):
+            d = dec_c + extra
+            table[2, 0], table[2, 1] = 2.0 ** -d, 2.0 ** d
+            stats.zero_()
+            call(0)
+            got = dC[torch.from_numpy(rows).cuda()].cpu().numpy().astype(np.int64)
+            expect = _rne_shift(exact, dec_a + dec_b - d)
+            assert np.array_equal(got, expect), (layout, extra)
+            if extra:
+                assert (np.abs(expect) >= 32767).mean() > 0.5      # it does saturate
+                assert int(stats[2].item()) == 32768 or int(stats[2].item()) == 32767
+            elif n <= 4096:
+                assert int(stats[2].item()) == int(np.abs(got).max())
+        del dA, dB
+
+
+@pytest.mark.parametrize("n", [1024, 4096, 8192])
+def test_gemm_f32_benchmark_sizes(n):
+    """The fp32 twin of benchmark configuration 3: A, B ~ N(0,1), all three layouts, against a
+    float64 product at rtol 1e-4 / atol 1e-5 * 4 sqrt(K) (a sum of K products of unit variance
+    has magnitude sqrt(K)).  8192 is checked on 48 sampled rows."""
+    import torch
+    from ngraph_python_b200 import lib
+    rng = np.random.RandomState(n + 1)
+    A = rng.standard_normal((n, n)).astype(np.float32)
+    B = rng.standard_normal((n, n)).astype(np.float32)
+    rows = np.arange(n) if n <= 4096 else np.sort(rng.choice(n, 48, replace=False))
+    expect = A[rows].astype(np.float64) @ B.astype(np.float64)
+    nbytes = lib.gemm_scratch_bytes(False, n, n, n)
+    keep, sp = _scratch(torch, nbytes)
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    dC = torch.zeros((n, n), dtype=torch.float32, device="cuda")
+    for layout in ("nn", "nt", "tn"):
+        dA = torch.from_numpy(_stored(A, layout == "tn")).cuda()
+        dB = torch.from_numpy(_stored(B, layout == "nt")).cuda()
+        a_str = (1, n) if layout == "tn" else (n, 1)
+        b_str = (1, n) if layout == "nt" else (n, 1)
+        dC.zero_()
+        lib.check(lib.raw().b2_gemm_f32(dA.data_ptr(), a_str[0], a_str[1], dB.data_ptr(), b_str[0],
+                                        b_str[1], dC.data_ptr(), n, n, n, n, sp, nbytes,
+                                        status.data_ptr(), 0))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        got = dC[torch.from_numpy(rows).cuda()].cpu().numpy()
+        np.testing.assert_allclose(got, expect, rtol=1e-4, atol=1e-5 * np.sqrt(n) * 4,
+                                   err_msg=layout)
+        del dA, dB
