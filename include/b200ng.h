@@ -313,6 +313,22 @@ int b2_pool_bprop(const void* E, const void* I, void* GI, int32_t flex, int32_t 
                   const b2_flex_scale* table, int32_t slotE, int32_t slotGI, int32_t* stats,
                   uint64_t* probe_out, int32_t probe, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * N-d strided copy / transpose between two tensors of the same extents.
+ * Replaces: DimShuffleKernel and the generated copy-transpose kernels (ngraph/transformers/gpu/
+ * tensor_ops.py:119-204, gpu/kernels/cuda/copy_transpose.py:78-282), which also implement AssignOp
+ * between differently laid-out tensors (gputransform.py:393-395) and non-contiguous host I/O
+ * (gputransform.py:873-909).  dst[sum_i idx_i * dst_strides[i]] = src[sum_i idx_i *
+ * src_strides[i]] for every index tuple below `shape`; strides are in elements and non-negative
+ * (a source stride of 0 broadcasts); the destination must not alias itself.  Where the axis that
+ * is contiguous in the source differs from the one contiguous in the destination the copy goes
+ * through 32 x 32 shared-memory tiles so that both sides move whole rows.
+ * ------------------------------------------------------------------------------------------ */
+#define B2_DIMSHUFFLE_MAX_RANK 8
+int b2_dimshuffle(const void* src, void* dst, int32_t elem_bytes, int32_t rank,
+                  const int64_t* shape, const int64_t* src_strides, const int64_t* dst_strides,
+                  void* stream);
+
 /* Lookup table (embedding).  lut_axis 0: lut [V][F], out / delta [n_idx][F], dW [V][F];
  * lut_axis 1: lut [F][V], out / delta [F][n_idx], dW [F][V].  Indices are values of the tensor
  * idx (fp32, or flex16 mantissas with the scale of slot_idx), rounded to the nearest integer.

@@ -7,7 +7,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200ng.so")
 
-SOURCES = ["b2_api.cu", "b2_ew_codegen.cu", "b2_flex.cu", "b2_gemm.cu", "b2_conv.cu"]
+SOURCES = ["b2_api.cu", "b2_ew_codegen.cu", "b2_flex.cu", "b2_gemm.cu", "b2_conv.cu",
+           "b2_dimshuffle.cu"]
 
 
 def _embed_device_header():

@@ -36,6 +36,9 @@ namespace {
 
 struct ConvGeom {
     int C, H, W, N, K, R, S, P, Q, pad_h, pad_w, str_h, str_w, dil_h, dil_w;
+    // depth (the reference's D / T / M axes): handled by the gather + GEMM path only; the tile
+    // kernels take convolutions with D = T = M = 1
+    int D, T, M, pad_d, str_d, dil_d;
     // the streamed tensor of an implicit-GEMM pass may be a zero-dilated view of a smaller one
     // (the input gradient of a strided convolution): element (h, w) is source (h/up_h, w/up_w)
     // where both divide and the quotient is inside src_h x src_w, zero elsewhere
@@ -44,19 +47,28 @@ struct ConvGeom {
 
 int geom_from(const b2_conv_dims* d, ConvGeom* g) {
     B2_REQUIRE(d, "null dims");
-    B2_REQUIRE(d->D == 1 && d->T == 1 && d->M == 1 && d->pad_d == 0 && d->str_d == 1,
-               "only 2-d convolutions (D = T = M = 1) are supported");
     B2_REQUIRE(d->C > 0 && d->H > 0 && d->W > 0 && d->N > 0 && d->K > 0 && d->R > 0 && d->S > 0 &&
-               d->P > 0 && d->Q > 0 && d->str_h > 0 && d->str_w > 0 && d->dil_h > 0 && d->dil_w > 0,
+               d->P > 0 && d->Q > 0 && d->str_h > 0 && d->str_w > 0 && d->dil_h > 0 && d->dil_w > 0 &&
+               d->D > 0 && d->T > 0 && d->M > 0 && d->str_d > 0 && d->dil_d > 0 && d->pad_d >= 0 &&
+               d->pad_h >= 0 && d->pad_w >= 0,
                "bad convolution dimensions");
+    B2_REQUIRE((long long)d->D * d->H * d->W < (1 << 24) && (long long)d->M * d->P * d->Q < (1 << 24),
+               "convolution extents too large");
     g->C = d->C; g->H = d->H; g->W = d->W; g->N = d->N; g->K = d->K; g->R = d->R; g->S = d->S;
     g->P = d->P; g->Q = d->Q; g->pad_h = d->pad_h; g->pad_w = d->pad_w; g->str_h = d->str_h;
     g->str_w = d->str_w; g->dil_h = d->dil_h; g->dil_w = d->dil_w;
     g->up_h = g->up_w = 1; g->src_h = g->H; g->src_w = g->W;
+    g->D = d->D; g->T = d->T; g->M = d->M; g->pad_d = d->pad_d; g->str_d = d->str_d;
+    g->dil_d = d->dil_d;
     return B2_OK;
 }
 
-// Gather + split.  Rows of the planes: r = (p*Q + q)*N + n ; columns: kidx = (c*R + r_)*S + s_.
+inline bool flat_depth(const ConvGeom& g) {
+    return g.D == 1 && g.T == 1 && g.M == 1 && g.pad_d == 0;
+}
+
+// Gather + split.  Rows of the planes: r = ((m*P + p)*Q + q)*N + n ; columns:
+// kidx = ((c*T + t)*R + r_)*S + s_.
 // A block owns 32 consecutive rows (32 images of one output pixel when N is a multiple of 32) and
 // walks the columns in chunks of 128 bytes of plane row.  Per chunk the tap decomposition of each
 // column is computed once into shared memory; loads run along n (contiguous in the input), the
@@ -69,25 +81,28 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
                      void* __restrict__ plane0, void* __restrict__ plane1) {
     constexpr int CK = MODE == MODE_FLEX16 ? 128 : 32;
     __shared__ T tile[CK][33];
-    __shared__ int tab_c[CK], tab_h[CK], tab_w[CK];
+    __shared__ int tab_c[CK], tab_h[CK], tab_w[CK], tab_d[CK];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int r0 = blockIdx.x * 32;
     const int r = r0 + tx;
     const bool rvalid = r < rows;
-    int n = 0, h0 = 0, w0 = 0;
+    int n = 0, h0 = 0, w0 = 0, d0 = 0;
     if (rvalid) {
         n = r % g.N;
         const int pq = r / g.N;
         if (BPROP) {
-            h0 = pq / g.W + g.pad_h;
-            w0 = pq % g.W + g.pad_w;
+            const int hw = pq % (g.H * g.W);
+            d0 = pq / (g.H * g.W) + g.pad_d;
+            h0 = hw / g.W + g.pad_h;
+            w0 = hw % g.W + g.pad_w;
         } else {
-            const int q = pq % g.Q, pp = pq / g.Q;
+            const int q = pq % g.Q, mp = pq / g.Q, pp = mp % g.P;
+            d0 = (mp / g.P) * g.str_d - g.pad_d;
             h0 = pp * g.str_h - g.pad_h;
             w0 = q * g.str_w - g.pad_w;
         }
     }
-    const int RS = g.R * g.S;
+    const int RS = g.R * g.S, TRS = g.T * RS;
     const int wr = threadIdx.x >> 3, vec = threadIdx.x & 7;
     const int orow = r0 + wr;
     for (int kc = 0; kc < kp; kc += CK) {
@@ -95,9 +110,11 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
         if (threadIdx.x < CK) {
             const int kidx = kc + threadIdx.x;
             if (kidx < kg) {
-                const int c = kidx / RS, rs = kidx - c * RS;
+                const int c = kidx / TRS, trs = kidx - c * TRS;
+                const int ft = trs / RS, rs = trs - ft * RS;
                 const int fr = rs / g.S, fs = rs - fr * g.S;
-                tab_c[threadIdx.x] = c * (BPROP ? g.P * g.Q : g.H * g.W) * g.N;
+                tab_c[threadIdx.x] = c * (BPROP ? g.M * g.P * g.Q : g.D * g.H * g.W) * g.N;
+                tab_d[threadIdx.x] = ft * g.dil_d;
                 tab_h[threadIdx.x] = fr * g.dil_h;
                 tab_w[threadIdx.x] = fs * g.dil_w;
             } else {
@@ -110,16 +127,17 @@ im2col_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
             const int tc = tab_c[i];
             if (tc >= 0 && rvalid) {
                 if (BPROP) {
-                    const int th = h0 - tab_h[i], tw = w0 - tab_w[i];
-                    if (th >= 0 && tw >= 0 && th % g.str_h == 0 && tw % g.str_w == 0) {
-                        const int pp = th / g.str_h, q = tw / g.str_w;
-                        if (pp < g.P && q < g.Q)
-                            v = I[(long long)tc + ((long long)pp * g.Q + q) * g.N + n];
+                    const int th = h0 - tab_h[i], tw = w0 - tab_w[i], td = d0 - tab_d[i];
+                    if (th >= 0 && tw >= 0 && td >= 0 && th % g.str_h == 0 && tw % g.str_w == 0 &&
+                        td % g.str_d == 0) {
+                        const int pp = th / g.str_h, q = tw / g.str_w, mm = td / g.str_d;
+                        if (pp < g.P && q < g.Q && mm < g.M)
+                            v = I[(long long)tc + (((long long)mm * g.P + pp) * g.Q + q) * g.N + n];
                     }
                 } else {
-                    const int h = h0 + tab_h[i], w = w0 + tab_w[i];
-                    if (h >= 0 && h < g.H && w >= 0 && w < g.W)
-                        v = I[(long long)tc + ((long long)h * g.W + w) * g.N + n];
+                    const int h = h0 + tab_h[i], w = w0 + tab_w[i], dd = d0 + tab_d[i];
+                    if (h >= 0 && h < g.H && w >= 0 && w < g.W && dd >= 0 && dd < g.D)
+                        v = I[(long long)tc + (((long long)dd * g.H + h) * g.W + w) * g.N + n];
                 }
             }
             tile[i][tx] = v;
@@ -822,6 +840,7 @@ ImplicitShape implicit_shape(const ConvGeom& g) {
 // do dilated filters and windows too large for two stages of shared memory.
 bool implicit_ok(int mode, const ConvGeom& g) {
     if (mode != MODE_FLEX16 || g.N % 128 != 0 || g.dil_h != 1 || g.dil_w != 1) return false;
+    if (!flat_depth(g)) return false;
     if (g.R > 256 || g.S > 256 || (long long)g.P * g.Q * (g.N / 128) >= (1LL << 30)) return false;
     // the exact int32 sums: |X| <= 2*128*255 per K row
     if ((long long)g.C * g.R * g.S + 32 > 32768) return false;
@@ -835,7 +854,7 @@ bool implicit_ok(int mode, const ConvGeom& g) {
 // this does not hold or does not pay (filter dilation, padding larger than the window allows,
 // strides whose zero-filling would multiply the work by more than four).
 bool bprop_as_fprop(const ConvGeom& f, ConvGeom* g) {
-    if (f.dil_h != 1 || f.dil_w != 1 || f.str_h * f.str_w > 4) return false;
+    if (f.dil_h != 1 || f.dil_w != 1 || f.str_h * f.str_w > 4 || !flat_depth(f)) return false;
     if (f.pad_h > f.R - 1 || f.pad_w > f.S - 1) return false;
     const int he = f.H + 2 * f.pad_h - f.R + 1, we = f.W + 2 * f.pad_w - f.S + 1;
     if (he < (f.P - 1) * f.str_h + 1 || we < (f.Q - 1) * f.str_w + 1) return false;
@@ -1020,10 +1039,11 @@ int run_fprop(const T* I, const T* F, void* O, const b2_conv_dims* d, const b2_f
     if (implicit_ok(MODE, g) && !getenv("B2_CONV_IM2COL"))
         return run_fprop_implicit<T, MODE>(I, F, O, g, table, slotI, slotF, slotO, stats, scratch,
                                            scratch_bytes, probe_out, status, probe, st);
-    const long long rows_ll = (long long)g.P * g.Q * g.N;
+    const long long rows_ll = (long long)g.M * g.P * g.Q * g.N;
     B2_REQUIRE(rows_ll < (1LL << 31) - 256, "too many output positions");
-    const int rows = (int)rows_ll, kg = g.C * g.R * g.S;
-    if (MODE == MODE_FLEX16) B2_REQUIRE(kg <= 32768, "flex16 convolution needs C*R*S <= 32768");
+    B2_REQUIRE((long long)g.C * g.T * g.R * g.S < (1LL << 24), "filter window too large");
+    const int rows = (int)rows_ll, kg = g.C * g.T * g.R * g.S;
+    if (MODE == MODE_FLEX16) B2_REQUIRE(kg <= 32768, "flex16 convolution needs C*T*R*S <= 32768");
     const Shapes s = shapes_for(MODE, rows, g.K, kg);
     B2_REQUIRE(scratch && scratch_bytes >= s.bytes && ((uintptr_t)scratch & 1023) == 0,
                "convolution needs %zu bytes of 1024-byte aligned scratch, got %zu", s.bytes,
@@ -1031,7 +1051,7 @@ int run_fprop(const T* I, const T* F, void* O, const b2_conv_dims* d, const b2_f
     unsigned char* base = (unsigned char*)scratch;
     const size_t a_plane = (size_t)s.Mp * s.Kp * s.esize, b_plane = (size_t)s.Np * s.Kp * s.esize;
     {
-        B2_REQUIRE((long long)g.C * g.H * g.W * g.N < (1LL << 31), "input tensor too large");
+        B2_REQUIRE((long long)g.C * g.D * g.H * g.W * g.N < (1LL << 31), "input tensor too large");
         im2col_planes_kernel<T, MODE, false><<<s.Mp / 32, 256, 0, st>>>(I, g, rows, kg, s.Mp, s.Kp,
                                                                 base, base + a_plane);
         // filters: element (n = k_out, k = kidx) = F[kidx * K + k_out]
@@ -1093,16 +1113,18 @@ update_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
 #pragma unroll
     for (int e = 0; e < kPer; ++e) v[e] = 0;
     if (m < rows && j0 < kg) {
-        const int RS = g.R * g.S;
-        const int c = m / RS, rs = m - c * RS, fr = rs / g.S, fs = rs - fr * g.S;
-        const T* plane = I + (long long)c * g.H * g.W * g.N;
+        const int RS = g.R * g.S, TRS = g.T * RS;
+        const int c = m / TRS, trs = m - c * TRS, ft = trs / RS, rs = trs - ft * RS;
+        const int fr = rs / g.S, fs = rs - fr * g.S;
+        const T* plane = I + (long long)c * g.D * g.H * g.W * g.N;
         const bool fast = (g.N % kPer == 0) && ((uintptr_t)I & 15) == 0;
         if (fast) {
-            const int n0 = j0 % g.N, pq = j0 / g.N, q = pq % g.Q, pp = pq / g.Q;
+            const int n0 = j0 % g.N, pq = j0 / g.N, q = pq % g.Q, mp = pq / g.Q, pp = mp % g.P;
+            const int dd = (mp / g.P) * g.str_d - g.pad_d + ft * g.dil_d;
             const int h = pp * g.str_h - g.pad_h + fr * g.dil_h;
             const int w = q * g.str_w - g.pad_w + fs * g.dil_w;
-            if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
-                const T* sp = plane + ((long long)h * g.W + w) * g.N + n0;
+            if (h >= 0 && h < g.H && w >= 0 && w < g.W && dd >= 0 && dd < g.D) {
+                const T* sp = plane + (((long long)dd * g.H + h) * g.W + w) * g.N + n0;
                 if (MODE == MODE_FLEX16) {
                     const int4 a = __ldg((const int4*)sp), b = __ldg((const int4*)sp + 1);
                     *(int4*)&v[0] = a;
@@ -1116,11 +1138,12 @@ update_planes_kernel(const T* __restrict__ I, ConvGeom g, int rows, int kg, int 
             for (int e = 0; e < kPer; ++e) {
                 const int j = j0 + e;
                 if (j >= kg) break;
-                const int n = j % g.N, pq = j / g.N, q = pq % g.Q, pp = pq / g.Q;
+                const int n = j % g.N, pq = j / g.N, q = pq % g.Q, mp = pq / g.Q, pp = mp % g.P;
+                const int dd = (mp / g.P) * g.str_d - g.pad_d + ft * g.dil_d;
                 const int h = pp * g.str_h - g.pad_h + fr * g.dil_h;
                 const int w = q * g.str_w - g.pad_w + fs * g.dil_w;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W)
-                    v[e] = plane[((long long)h * g.W + w) * g.N + n];
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W && dd >= 0 && dd < g.D)
+                    v[e] = plane[(((long long)dd * g.H + h) * g.W + w) * g.N + n];
             }
         }
     }
@@ -1157,7 +1180,7 @@ struct TrainShape { Shapes s; int splits; size_t bytes; };
 
 TrainShape bprop_shape(int mode, const ConvGeom& g) {
     TrainShape t;
-    t.s = shapes_for(mode, g.H * g.W * g.N, g.C, g.K * g.R * g.S);
+    t.s = shapes_for(mode, g.D * g.H * g.W * g.N, g.C, g.K * g.T * g.R * g.S);
     t.splits = pick_splits(mode, t.s, false);
     t.bytes = align1k(t.s.bytes) + splitk_bytes(mode, t.s, t.splits);
     return t;
@@ -1165,7 +1188,7 @@ TrainShape bprop_shape(int mode, const ConvGeom& g) {
 
 TrainShape update_shape(int mode, const ConvGeom& g) {
     TrainShape t;
-    t.s = shapes_for(mode, g.C * g.R * g.S, g.K, g.P * g.Q * g.N);
+    t.s = shapes_for(mode, g.C * g.T * g.R * g.S, g.K, g.M * g.P * g.Q * g.N);
     t.splits = pick_splits(mode, t.s, true);
     t.bytes = align1k(t.s.bytes) + splitk_bytes(mode, t.s, t.splits);
     return t;
@@ -1191,10 +1214,10 @@ int run_bprop(const T* E, const T* F, void* GI, const b2_conv_dims* d, const b2_
         return implicit_tiles(base, base + 2 * si.act_plane, GI, gb, si, table, slotE, slotF, slotG,
                               stats, probe_out, status, probe, st);
     }
-    const long long rows_ll = (long long)g.H * g.W * g.N;
-    B2_REQUIRE(rows_ll < (1LL << 31) - 256 && (long long)g.K * g.P * g.Q * g.N < (1LL << 31),
-               "tensor too large");
-    const int rows = (int)rows_ll, kg = g.K * g.R * g.S;
+    const long long rows_ll = (long long)g.D * g.H * g.W * g.N;
+    B2_REQUIRE(rows_ll < (1LL << 31) - 256 && (long long)g.K * g.M * g.P * g.Q * g.N < (1LL << 31) &&
+               (long long)g.K * g.T * g.R * g.S < (1LL << 24), "tensor too large");
+    const int rows = (int)rows_ll, kg = g.K * g.T * g.R * g.S;
     const TrainShape t = bprop_shape(MODE, g);
     const Shapes& s = t.s;
     B2_REQUIRE(scratch && scratch_bytes >= t.bytes && ((uintptr_t)scratch & 1023) == 0,
@@ -1207,7 +1230,7 @@ int run_bprop(const T* E, const T* F, void* GI, const b2_conv_dims* d, const b2_
     long long blocks = ((long long)s.Np * s.Kp + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     filter_bprop_planes_kernel<T, MODE><<<(unsigned)blocks, 256, 0, st>>>(
-        F, g.C, g.R * g.S, g.K, s.Np, s.Kp, base + 2 * a_plane, base + 2 * a_plane + b_plane);
+        F, g.C, g.T * g.R * g.S, g.K, s.Np, s.Kp, base + 2 * a_plane, base + 2 * a_plane + b_plane);
     B2_CUDA(cudaGetLastError());
     GemmParams p;
     fill_params(&p, rows, g.C, rows, GI, 1, table, slotE, slotF, slotG, stats, probe_out, status,
@@ -1406,6 +1429,7 @@ UpdShape update_implicit_shape(int mode, const ConvGeom& g) {
     const int rs = g.R * g.S;
     const long long cols = (long long)g.P * g.Q * g.N;
     if (mode != MODE_FLEX16 || g.N % 128 != 0 || g.dil_h != 1 || g.dil_w != 1 || rs > 128 ||
+        !flat_depth(g) ||
         g.R > 256 || g.S > 256 || cols >= (1LL << 31) - 256 || getenv("B2_CONV_IM2COL"))
         return u;
     const int cu_max = 128 / rs;
@@ -1508,10 +1532,10 @@ int run_update(const T* I, const T* E, void* U, const b2_conv_dims* d, const b2_
             return run_update_implicit<T, MODE>(I, E, U, g, u, table, slotI, slotE, slotU, stats,
                                                 scratch, scratch_bytes, probe_out, status, probe, st);
     }
-    const long long kg_ll = (long long)g.P * g.Q * g.N;
-    B2_REQUIRE(kg_ll < (1LL << 31) - 256 && (long long)g.C * g.H * g.W * g.N < (1LL << 31),
-               "tensor too large");
-    const int rows = g.C * g.R * g.S, kg = (int)kg_ll;
+    const long long kg_ll = (long long)g.M * g.P * g.Q * g.N;
+    B2_REQUIRE(kg_ll < (1LL << 31) - 256 && (long long)g.C * g.D * g.H * g.W * g.N < (1LL << 31) &&
+               (long long)g.C * g.T * g.R * g.S < (1LL << 24), "tensor too large");
+    const int rows = g.C * g.T * g.R * g.S, kg = (int)kg_ll;
     const TrainShape t = update_shape(MODE, g);
     const Shapes& s = t.s;
     B2_REQUIRE(scratch && scratch_bytes >= t.bytes && ((uintptr_t)scratch & 1023) == 0,
@@ -1602,7 +1626,7 @@ extern "C" int b2_conv_fprop_scratch_bytes(int32_t flex, const b2_conv_dims* d, 
     if (rc) return rc;
     B2_REQUIRE(bytes, "null argument");
     const int mode = flex ? MODE_FLEX16 : MODE_F32X3;
-    size_t need = shapes_for(mode, g.P * g.Q * g.N, g.K, g.C * g.R * g.S).bytes;
+    size_t need = shapes_for(mode, g.M * g.P * g.Q * g.N, g.K, g.C * g.T * g.R * g.S).bytes;
     if (implicit_ok(mode, g)) {
         const size_t alt = implicit_shape(g).bytes;
         if (alt > need || !getenv("B2_CONV_IM2COL")) need = alt > need ? alt : need;

@@ -266,7 +266,8 @@ class ConvStep(_PlaneUser, _Step):
             setattr(d, k, int(cp.get(k, 1)))
         # the output extents must be what the parameters imply (reference: output_dim,
         # ngraph/frontends/neon/utils.py / conv_utils.py)
-        for (x, f, pad, st, dil, o, nm) in ((H, R, d.pad_h, d.str_h, d.dil_h, P, "H"),
+        for (x, f, pad, st, dil, o, nm) in ((D, T, d.pad_d, d.str_d, d.dil_d, M, "D"),
+                                            (H, R, d.pad_h, d.str_h, d.dil_h, P, "H"),
                                             (W, S, d.pad_w, d.str_w, d.dil_w, Q, "W")):
             expect = (x + 2 * pad - dil * (f - 1) - 1) // st + 1
             if expect != o:
@@ -570,6 +571,39 @@ class LutUpdateStep(_Step):
                 t._table.data_ptr(), slots[0], slots[1], slots[2], t._stats.data_ptr(),
                 t._probe64.data_ptr(), probe, st))))
         self._flex_probe_then(t, ov.buffer, [dv.buffer, xv.buffer], call)
+
+
+class DimshuffleStep(_Step):
+    """A strided copy between two views with the same axes (DimShuffleKernel of the reference,
+    ngraph/transformers/gpu/tensor_ops.py:119-204; it also carries AssignOp between differently
+    laid-out tensors, gputransform.py:393-395).  A flex16 copy moves mantissas, so the destination
+    shares the source's exponent (the reference propagates the FlexEntry through a dimshuffle the
+    same way, ngraph/transformers/passes/flexpass.py:32-48)."""
+    kind = "dimshuffle"
+    launches = 1
+
+    def __init__(self, index, op, t, src_view, dst_view, axes):
+        super(DimshuffleStep, self).__init__(index, op)
+        self.in_views = [src_view]
+        self.out_views = [dst_view]
+        self.lengths = [a.length for a in axes]
+        self.src_strides = [src_view.stride_of(a) for a in axes]
+        self.dst_strides = [dst_view.stride_of(a) for a in axes]
+        if len(self.lengths) > 8:
+            raise ValueError("Unhandled op: dimshuffle of more than 8 axes")
+        if src_view.buffer.flex != dst_view.buffer.flex:
+            raise ValueError("dimshuffle between tensors of different storage types")
+        self.elem_bytes = 2 if src_view.buffer.flex else 4
+        self.owns_version = True
+
+    def output_buffers(self):
+        return []          # no exponent of its own to manage
+
+    def launch(self, t):
+        sv, dv = self.in_views[0], self.out_views[0]
+        lib.dimshuffle(self._ptr(sv), self._ptr(dv), self.elem_bytes, self.lengths,
+                       self.src_strides, self.dst_strides, t.stream.cuda_stream)
+        t.kernel_launches += 1
 
 
 class CommStep(_Step):

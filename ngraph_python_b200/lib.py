@@ -124,6 +124,8 @@ def _load():
         "b2_lut_fprop": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]),
         "b2_lut_update": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, i32,
                                     vp, vp, i32, vp]),
+        "b2_dimshuffle": (C.c_int, [vp, vp, i32, i32, C.POINTER(i64), C.POINTER(i64),
+                                    C.POINTER(i64), vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),
@@ -286,3 +288,11 @@ def conv_update_scratch_bytes(flex, dims):
     n = C.c_size_t()
     check(_lib.b2_conv_update_scratch_bytes(int(bool(flex)), C.byref(dims), C.byref(n)))
     return n.value
+
+
+def dimshuffle(src_ptr, dst_ptr, elem_bytes, shape, src_strides, dst_strides, stream=0):
+    """N-d strided copy (strides in elements)."""
+    n = len(shape)
+    arr = C.c_int64 * max(n, 1)
+    check(_lib.b2_dimshuffle(src_ptr, dst_ptr, elem_bytes, n, arr(*shape), arr(*src_strides),
+                             arr(*dst_strides), stream))

@@ -315,7 +315,12 @@ class B200NgraphTransformer(Transformer):
         pass
 
     def get_tensor_view_value(self, op, host_tensor=None):
-        raise NotImplementedError("read tensors through a computation")
+        """ngraph/transformers/base.py:546-558: the value a tensor of the graph holds now."""
+        return self.impl.get_tensor_view_value(self.translator(op.tensor), host_tensor)
+
+    def device_tensor(self, op):
+        """The device tensor of a reference op (get / slicing / assignment from the host)."""
+        return self.impl.device_tensor(self.translator(op.tensor))
 
     def host_to_device(self, computation, parameters, args):
         pass

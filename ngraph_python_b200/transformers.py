@@ -176,8 +176,10 @@ class Computation(object):
         t = self.transformer
         planner = _Planner(t, self)
         self.steps, self.return_views = planner.plan(self._ordered_ops(), self.returns)
+        final = []
         for s in self.steps:
-            planner.finalize_step(s)
+            final.extend(planner.finalize_step(s))     # (a step may bring copies that precede it)
+        self.steps = final
         self._comm_steps = planner.comm_steps
         t._allocate(self)
         for s in self.steps:
@@ -788,15 +790,54 @@ class _Planner(object):
 
     # -- program construction -------------------------------------------------------------------
     def finalize_step(self, step):
+        """Builds the step's program; returns the steps that take its place in the list."""
         if step.kind == "ew":
-            self._finalize_ew(step)
-        elif getattr(step, "epi", None):
+            return self._finalize_ew(step)
+        if getattr(step, "epi", None):
             # a fused convolution writes the byte planes of its result itself when the next
             # convolution wants them, and the int16 tensor only if someone reads that
             buf = step.out_views[0].buffer
             if buf.plane_bytes > 0:
                 buf.planes_by_producer = True
                 step.write_int16 = not self._only_plane_readers(step.out_op)
+        return [step]
+
+    def _pure_copy(self, step):
+        """(source view, destination view) when the kernel would do nothing but copy one tensor
+        into another -- value_of / a materialised reorder, or an fp32 AssignOp -- else None."""
+        g = step.group
+        if len(g.members) != 1 or len(step.out_ops) != 1 or len(g.ext_inputs) != 1:
+            return None
+        m = g.members[0]
+        if isinstance(m, AssignOp):
+            if self.t.flex:
+                return None      # the target has an exponent of its own: values are re-quantised
+            dst = self.t._view_of(m.args[0])
+        elif isinstance(m, ElementWiseOp) and m.opname == "assign":
+            dst = self.t._view_of(m)
+        else:
+            return None
+        args = self._value_args(m)
+        base, _ = self._base_tensor(args[0])
+        if self._is_scalar_const(base):
+            return None
+        src = g.ext_inputs[0]
+        if src.buffer.flex != dst.buffer.flex:
+            return None
+        if any(src.stride_of(a) == 0 and a.length != 1 for a in g.iter_axes):
+            return None          # a broadcasting fill: the elementwise kernel does that well
+        return src, dst
+
+    def _dense_copy_of(self, view, iter_axes, index):
+        """A dimshuffle step that lays `view` out dense in iteration order, and the new view."""
+        t = self.t
+        axes = [a for a in iter_axes if view.stride_of(a) != 0 or a.length == 1]
+        tmp = Buffer("dimshuffle_%d" % len(t._buffers), axes, view.buffer.flex)
+        if view.buffer.flex:
+            t._share_entry(tmp, view.buffer)
+        t._buffers[object()] = tmp
+        new_view = View.dense(tmp)
+        return kernels.DimshuffleStep(index, None, t, view, new_view, make_axes(axes)), new_view
 
     def _finalize_ew(self, step):
         t = self.t
@@ -805,15 +846,52 @@ class _Planner(object):
         red_axes = g.red_axes if g.red_axes is not None else Axes()
         lengths = list(iter_axes.lengths)
         reduced = [a in red_axes for a in iter_axes]
-        in_views = list(g.ext_inputs)
         ew_outs = [m for m in step.out_ops if not isinstance(m, ReductionOp)]
         red_outs = [m for m in step.out_ops if isinstance(m, ReductionOp)]
         out_views = []
         for m in ew_outs + red_outs:
             out_views.append(t._view_of(m.args[0]) if isinstance(m, AssignOp) else t._view_of(m))
-        strides_list = [[v.stride_of(a) for a in iter_axes] for v in in_views + out_views]
-        clen, cstr, cred = fusion.collapse_dims(lengths, strides_list, reduced)
-        dims, abc, mode = fusion.map_to_abc(clen, cstr, cred)
+        pre_steps = []
+        key_views = list(g.ext_inputs)      # what the ops' arguments resolve to (looked up by key)
+
+        def fold():
+            sl = [[v.stride_of(a) for a in iter_axes] for v in list(g.ext_inputs) + out_views]
+            clen, cstr, cred = fusion.collapse_dims(lengths, sl, reduced)
+            return (clen, cstr) + fusion.map_to_abc(clen, cstr, cred)
+        copy = self._pure_copy(step)
+        folded = None
+        try:
+            folded = fold()
+        except ValueError:
+            if copy is None:
+                # More non-mergeable axes than the kernel has: lay the inputs that are to blame
+                # out dense in iteration order first (the reference's layout pass inserts
+                # DimshuffleOps for the same purpose, ngraph/transformers/passes/layout.py:282-339)
+                for i, v in enumerate(list(g.ext_inputs)):
+                    own = [a for a in iter_axes if v.stride_of(a) != 0 or a.length == 1]
+                    expect, dense = 1, True
+                    for a in reversed(own):
+                        dense = dense and (a.length == 1 or v.stride_of(a) == expect)
+                        expect *= a.length
+                    if dense:
+                        continue
+                    pre, nv = self._dense_copy_of(v, iter_axes, step.index)
+                    g.after_write[nv.key()] = g.after_write.get(v.key(), False)
+                    g.ext_inputs[i] = nv
+                    pre_steps.append(pre)
+                folded = fold()                 # raises as before if that was not the obstacle
+        if copy is not None:
+            src, dst = copy
+            # a transposing copy (source not contiguous along the destination's fastest axis), or
+            # one over more axes than the elementwise kernel folds: the tiled copy kernel
+            transposing = folded is None or (len(folded[0]) >= 1 and folded[1][0][-1] != 1)
+            if folded is None or (transposing and src.buffer.size >= 1024):
+                m = g.members[0]
+                if t.flex:
+                    t._share_entry(dst.buffer, src.buffer)
+                return [kernels.DimshuffleStep(step.index, m, t, src, dst, iter_axes)]
+        clen, cstr, dims, abc, mode = folded
+        in_views = list(g.ext_inputs)
         # registers
         reg = {}
         consts = []
@@ -822,7 +900,7 @@ class _Planner(object):
         n_in = len(in_views)
 
         def input_index(view):
-            for i, w in enumerate(in_views):
+            for i, w in enumerate(key_views):
                 if w.key() == view.key():
                     return i
             raise KeyError(view)
@@ -949,6 +1027,7 @@ class _Planner(object):
         for v in out_views:
             if v.buffer not in self.written_buffers:
                 self.written_buffers.append(v.buffer)
+        return pre_steps + [step]
 
 
 def _fuse_sigmoid(ops, n_in, consts):
@@ -1299,12 +1378,29 @@ class B200Transformer(object):
         if view.is_dense():
             src = buf.tensor[:max(buf.size, 1)]
         else:
-            src = self.torch.as_strided(buf.tensor, view.axes.lengths, view.strides, view.offset)
+            src = self._contiguous_copy(view)
         if pinned is None:
             pinned = self.torch.empty(src.shape, dtype=src.dtype).pin_memory()
             self._pinned[key] = pinned
         pinned.copy_(src, non_blocking=True)
         return pinned, view
+
+    def _contiguous_copy(self, view):
+        """A dense device tensor holding the elements of a strided view (GPUDeviceTensor.
+        as_contiguous, ngraph/transformers/gputransform.py:873-892: the same copy kernel that
+        runs dimshuffles)."""
+        buf = view.buffer
+        lengths = list(view.axes.lengths)
+        out = self.torch.empty(lengths or [1], dtype=buf.tensor.dtype, device=self.device)
+        dense, acc = [], 1
+        for n in reversed(lengths):
+            dense.append(acc)
+            acc *= n
+        esize = 2 if buf.flex else 4
+        lib.dimshuffle(buf.ptr() + view.offset * esize, out.data_ptr(), esize, lengths,
+                       list(view.strides), list(reversed(dense)), self.stream.cuda_stream)
+        self.kernel_launches += 1
+        return out.reshape(lengths) if lengths else out.reshape(())
 
     def _finish_host(self, pending):
         """After the stream has been synchronised: a caller-owned array from the pinned copy
@@ -1329,13 +1425,81 @@ class B200Transformer(object):
         if view.is_dense():
             host = flat.cpu().numpy().reshape(view.axes.lengths)
         else:
-            t = self.torch.as_strided(flat, view.axes.lengths, view.strides, view.offset)
-            host = t.cpu().numpy()
+            host = self._contiguous_copy(view).cpu().numpy()
         if buf.flex:
             return host.astype(np.float64) * buf.entry.scale
         if host.shape == ():
             return host[()]
         return host
+
+    # ---- tensors outside computations ---------------------------------------------------------
+    def device_tensor(self, op):
+        """The DeviceTensor of an op's value (a variable, a placeholder, a result some
+        computation keeps).  The transformer must have been initialised."""
+        if self.plan_only:
+            raise lib.B200Error("a plan_only transformer holds no tensors")
+        if not self.finalized:
+            self.initialize()
+        v = self._view_of(as_op(op))
+        if v.buffer.tensor is None:
+            raise ValueError("no computation of this transformer uses %r" % (op,))
+        return DeviceTensor(self, v)
+
+    def get_tensor_view_value(self, op, host_tensor=None):
+        """ngraph/transformers/base.py:546-558."""
+        return self.device_tensor(op).get(host_tensor)
+
+    def _write_view(self, view, value):
+        """Host -> a (possibly strided) window of a tensor.  A dense whole-tensor write is the
+        ordinary host write; anything else goes through a contiguous device copy of the window
+        and the strided copy kernel (GPUDeviceTensor.from_other, gputransform.py:894-909)."""
+        torch = self.torch
+        buf = view.buffer
+        lengths = list(view.axes.lengths)
+        if view.is_dense():
+            self._host_to_device(view, value)
+            self.stream.synchronize()
+            return
+        arr = np.asarray(value, dtype=np.float32)
+        if arr.shape not in ((), (1,)) and tuple(n for n in arr.shape if n != 1) != \
+                tuple(n for n in lengths if n != 1):
+            raise ValueError("value shape %s does not match the window %s" % (arr.shape, lengths))
+        count = int(np.prod(lengths)) if lengths else 1
+        scalar = arr.size == 1
+        src = torch.from_numpy(np.ascontiguousarray(arr).reshape(-1).copy()).to(self.device)
+        esize = 4
+        if buf.flex:
+            # FlexGPUDeviceTensor.__setitem__: the entry sees the value before and the largest
+            # mantissa after; the tensor keeps its exponent (a first write picks one that fits)
+            e = buf.entry
+            if not e.initialized:
+                e.initialize_from_range(float(np.max(np.abs(arr))) if arr.size else 0.0,
+                                        from_host=True)
+            else:
+                e.begin_write()
+            self._set_table_row(buf.slot, e.dec)
+            self._set_table_row(buf.slot_write, e.dec)
+            self._stats[buf.slot:buf.slot + 1].zero_()
+            q = torch.empty((src.numel(),), dtype=torch.int16, device=self.device)
+            lib.check(lib.raw().b2_flex_host_quantize(src.data_ptr(), q.data_ptr(), src.numel(),
+                                                      self._table.data_ptr(), buf.slot,
+                                                      self._stats.data_ptr(),
+                                                      self.stream.cuda_stream))
+            self.kernel_launches += 1
+            src, esize = q, 2
+        dense, acc = [], 1
+        for n in reversed(lengths):
+            dense.append(acc)
+            acc *= n
+        src_strides = [0] * len(lengths) if scalar else list(reversed(dense))
+        if count:
+            lib.dimshuffle(src.data_ptr(), buf.ptr() + view.offset * esize, esize, lengths,
+                           src_strides, list(view.strides), self.stream.cuda_stream)
+            self.kernel_launches += 1
+        self.stream.synchronize()
+        buf.version += 1
+        if buf.flex:
+            buf.entry.end_write(int(self._stats[buf.slot].item()))
 
     # ---- flex bookkeeping ------------------------------------------------------------------------
     def _set_table_row(self, slot, dec):
@@ -1461,6 +1625,79 @@ class B200Transformer(object):
                 fresh = [b for b in fresh if b not in ready]
         step.kernel.launch(ins, outs, **common)
         self.kernel_launches += step.kernel.launches
+
+
+class DeviceTensor(object):
+    """A tensor (or a window of one) on the device, readable and writable from the host outside
+    any computation: GPUDeviceTensor.get / __getitem__ / __setitem__
+    (ngraph/transformers/gputransform.py:679-909) and, for flex16 storage, FlexGPUDeviceTensor
+    (ngraph/transformers/flexgputransform.py:160-208): values are read as mantissa * scale and
+    written as value / scale, clipped to the int16 range and truncated, with the tensor's
+    exponent entry told the largest magnitude written.
+
+        w = transformer.device_tensor(variable)
+        w.get()                      # numpy copy of the whole tensor
+        w[2:5, :, 0].get()           # a window: slices and integers per axis, Ellipsis
+        w[...] = array               # whole tensor; w[1:3] = 0.5 fills a window
+    """
+
+    def __init__(self, transformer, view):
+        self.transformer = transformer
+        self.view = view
+
+    @property
+    def shape(self):
+        return tuple(self.view.axes.lengths)
+
+    @property
+    def scale(self):
+        e = self.view.buffer.entry
+        return e.scale if e is not None else 1.0
+
+    def get(self, tensor=None):
+        host = self.transformer._device_to_host(self.view)
+        if tensor is None:
+            return host
+        tensor[...] = host
+        return tensor
+
+    def __getitem__(self, index):
+        if index is None or index is Ellipsis or index == ():
+            return self
+        if not isinstance(index, tuple):
+            index = (index,)
+        v = self.view
+        n = len(v.axes)
+        if Ellipsis in index:
+            k = index.index(Ellipsis)
+            fill = n - (len(index) - 1)
+            if fill < 0 or Ellipsis in index[k + 1:]:
+                raise IndexError("too many indices for a tensor of %d axes" % n)
+            index = index[:k] + (slice(None),) * fill + index[k + 1:]
+        if len(index) > n:
+            raise IndexError("too many indices for a tensor of %d axes" % n)
+        index = index + (slice(None),) * (n - len(index))
+        axes, strides, offset = [], [], v.offset
+        for a, st, ix in zip(v.axes, v.strides, index):
+            if isinstance(ix, slice):
+                start, stop, step = ix.indices(a.length)
+                if step <= 0:
+                    raise IndexError("slices of device tensors need a positive step")
+                count = max(0, -(-(stop - start) // step))
+                offset += start * st
+                axes.append(a if count == a.length else type(a)(count, a.name))
+                strides.append(st * step)
+            else:
+                i = int(ix)
+                if i < 0:
+                    i += a.length
+                if not 0 <= i < a.length:
+                    raise IndexError("index %d is out of bounds for axis %s" % (ix, a))
+                offset += i * st
+        return DeviceTensor(self.transformer, View(v.buffer, axes, strides, offset))
+
+    def __setitem__(self, key, value):
+        self.transformer._write_view(self.__getitem__(key).view, value)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -138,3 +138,74 @@ def pool_bprop(E, I, window, pad=(0, 0), stride=(1, 1), op="avg"):
                     patch += E[c, p, q, :] * np.float32(1.0 / patch.shape[0])
                 G[c, h0:h1, w0:w1, :] = patch.reshape(h1 - h0, w1 - w0, N)
     return G
+
+
+# ---- the same three contractions with the depth axes (D / T / M) and filter dilation ------------
+def _out_extent(x, f, pad, stride, dil):
+    return (x + 2 * pad - dil * (f - 1) - 1) // stride + 1
+
+
+def conv3d_fprop(I, F, pad=(0, 0, 0), stride=(1, 1, 1), dil=(1, 1, 1), dtype=np.float32):
+    """I: (C, D, H, W, N); F: (C, T, R, S, K) -> O: (K, M, P, Q, N); pad / stride / dil are
+    (depth, height, width).  The reference's loop (ngraph/transformers/cpu/cpuengine.py:234-254)
+    takes, for every output position, the dot of the clipped filter slice with the clipped input
+    slice; here every filter tap contributes one tensordot over channels."""
+    C, D, H, W, N = I.shape
+    C2, T, R, S, K = F.shape
+    assert C == C2
+    (pd, ph, pw), (sd, sh, sw), (dd, dh, dw) = pad, stride, dil
+    M, P, Q = _out_extent(D, T, pd, sd, dd), _out_extent(H, R, ph, sh, dh), _out_extent(W, S, pw, sw, dw)
+    # padded so that every tap's strided window exists in full
+    Ip = np.zeros((C, D + 2 * pd + sd, H + 2 * ph + sh, W + 2 * pw + sw, N), dtype=dtype)
+    Ip[:, pd:pd + D, ph:ph + H, pw:pw + W, :] = I
+    O = np.zeros((K, M, P, Q, N), dtype=dtype)
+    Ft = F.astype(dtype)
+    for t in range(T):
+        for r in range(R):
+            for s in range(S):
+                win = Ip[:, t * dd:t * dd + (M - 1) * sd + 1:sd, r * dh:r * dh + (P - 1) * sh + 1:sh,
+                         s * dw:s * dw + (Q - 1) * sw + 1:sw, :]
+                O += np.tensordot(Ft[:, t, r, s, :].T, win, axes=([1], [0]))
+    return O
+
+
+def conv3d_bprop(E, F, in_dhw, pad=(0, 0, 0), stride=(1, 1, 1), dil=(1, 1, 1), dtype=np.float32):
+    """E: (K, M, P, Q, N); F: (C, T, R, S, K) -> gI: (C, D, H, W, N): every tap scatters
+    F[:, t, r, s, :] . E onto the input positions it read (the reference states it as the
+    forward loop over flipped, transposed filters, cpuengine.py:256-271)."""
+    K, M, P, Q, N = E.shape
+    C, T, R, S, K2 = F.shape
+    assert K == K2
+    D, H, W = in_dhw
+    (pd, ph, pw), (sd, sh, sw), (dd, dh, dw) = pad, stride, dil
+    G = np.zeros((C, D + 2 * pd + T * dd + sd, H + 2 * ph + R * dh + sh, W + 2 * pw + S * dw + sw, N),
+                 dtype=dtype)
+    Ft, Et = F.astype(dtype), E.astype(dtype)
+    for t in range(T):
+        for r in range(R):
+            for s in range(S):
+                G[:, t * dd:t * dd + (M - 1) * sd + 1:sd, r * dh:r * dh + (P - 1) * sh + 1:sh,
+                  s * dw:s * dw + (Q - 1) * sw + 1:sw, :] += np.tensordot(
+                      Ft[:, t, r, s, :], Et, axes=([1], [0]))
+    return np.ascontiguousarray(G[:, pd:pd + D, ph:ph + H, pw:pw + W, :])
+
+
+def conv3d_update(I, E, filter_trs, pad=(0, 0, 0), stride=(1, 1, 1), dil=(1, 1, 1), dtype=np.float32):
+    """I: (C, D, H, W, N); E: (K, M, P, Q, N) -> U: (C, T, R, S, K) (cpuengine.py:395-418)."""
+    C, D, H, W, N = I.shape
+    K, M, P, Q, N2 = E.shape
+    assert N == N2
+    T, R, S = filter_trs
+    (pd, ph, pw), (sd, sh, sw), (dd, dh, dw) = pad, stride, dil
+    Ip = np.zeros((C, D + 2 * pd + T * dd + sd, H + 2 * ph + R * dh + sh, W + 2 * pw + S * dw + sw, N),
+                  dtype=dtype)
+    Ip[:, pd:pd + D, ph:ph + H, pw:pw + W, :] = I
+    Et = E.astype(dtype)
+    U = np.zeros((C, T, R, S, K), dtype=dtype)
+    for t in range(T):
+        for r in range(R):
+            for s in range(S):
+                win = Ip[:, t * dd:t * dd + (M - 1) * sd + 1:sd, r * dh:r * dh + (P - 1) * sh + 1:sh,
+                         s * dw:s * dw + (Q - 1) * sw + 1:sw, :]
+                U[:, t, r, s, :] = np.tensordot(win, Et, axes=([1, 2, 3, 4], [1, 2, 3, 4]))
+    return U

@@ -184,6 +184,32 @@ def conv_grads_stride2(ng):
     return conv_grads(ng, C=8, K=16, H=9, W=11, N=32, R=3, S=3, pad=1, stride=2)
 
 
+def conv3d_grads(ng, C=6, K=10, D=4, H=7, W=8, N=32, T=2, R=3, S=2, pad=(1, 2, 0), stride=(1, 2, 1),
+                 dil=(1, 1, 2)):
+    """A convolution with real depth axes (D, T, M > 1), asymmetric padding / stride and a dilated
+    width, forward and both gradients: the reference's kernels are C,D,H,W,N x C,T,R,S,K throughout
+    (ngraph/transformers/gpu/flex_conv.py:49-200), and its flex convolution test runs a depth-2
+    image (tests/flex_tests/test_flexconv.py:33).  pad / stride / dil are (depth, height, width)."""
+    ext = lambda x, f, p_, s_, d_: (x + 2 * p_ - d_ * (f - 1) - 1) // s_ + 1   # noqa: E731
+    M, P, Q = [ext(x, f, p_, s_, d_) for x, f, p_, s_, d_ in zip((D, H, W), (T, R, S), pad, stride, dil)]
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    ax_i = [ax(C, "C"), ax(D, "D"), ax(H, "H"), ax(W, "W"), ax(N, "N")]
+    ax_f = [ax_i[0], ax(T, "T"), ax(R, "R"), ax(S, "S"), ax(K, "K")]
+    ax_o = [ax_f[4], ax(M, "M"), ax(P, "P"), ax(Q, "Q"), ax_i[4]]
+    inputs, filters, delta = ng.placeholder(ax_i), ng.placeholder(ax_f), ng.placeholder(ax_o)
+    params = dict(pad_d=pad[0], pad_h=pad[1], pad_w=pad[2], str_d=stride[0], str_h=stride[1],
+                  str_w=stride[2], dil_d=dil[0], dil_h=dil[1], dil_w=dil[2])
+    bprop_conv, update_conv = _conv_grad_ops(ng)
+    out = ng.convolution(params, inputs, filters, axes=ax_o)
+    gi = bprop_conv(delta, inputs, filters, out)
+    gf = update_conv(delta, inputs, filters, out)
+    r = _rng(71)
+    vals = [r.standard_normal((C, D, H, W, N)).astype(np.float32),
+            (r.standard_normal((C, T, R, S, K)) * 0.3).astype(np.float32),
+            r.standard_normal((K, M, P, Q, N)).astype(np.float32)]
+    return [out, gi, gf], [inputs, filters, delta], vals
+
+
 def mlp_forward(ng):
     """Forward pass of benchmark configuration 1: 784 -> 512 ReLU -> 512 ReLU -> 10 softmax, batch 128."""
     r = _rng(0)
@@ -425,6 +451,7 @@ CASES = {
     "conv_stride2_3x3": conv_stride2_3x3,
     "conv_grads": conv_grads,
     "conv_grads_stride2": conv_grads_stride2,
+    "conv3d_grads": conv3d_grads,
     "mlp_forward": mlp_forward,
     "resnet20": resnet20,
     "resnet8_small": resnet8_small,

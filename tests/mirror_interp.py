@@ -84,24 +84,18 @@ class Interp(object):
             k = int(np.prod([a.length for a in red])) if red else 1
             out = xv.reshape(-1, k).astype(np.float64) @ yv.reshape(k, -1).astype(np.float64)
             return out.astype(np.float32).reshape(op.axes.lengths)
-        if isinstance(op, g.ConvolutionOp):
-            i, f = [self.eval(a) for a in op.args]
+        if isinstance(op, (g.ConvolutionOp, g.bprop_conv, g.update_conv)):
+            a, b = [self.eval(x) for x in op.args]
             cp = op.conv_params
-            out = co.conv_fprop(i[:, 0], f[:, 0], (cp["pad_h"], cp["pad_w"]),
-                                (cp["str_h"], cp["str_w"]))
-            return out[:, None].reshape(op.axes.lengths)
-        if isinstance(op, g.bprop_conv):
-            e, f = [self.eval(a) for a in op.args]
-            cp = op.conv_params
-            out = co.conv_bprop(e[:, 0], f[:, 0], op.axes.lengths[2:4], (cp["pad_h"], cp["pad_w"]),
-                                (cp["str_h"], cp["str_w"]))
-            return out[:, None].reshape(op.axes.lengths)
-        if isinstance(op, g.update_conv):
-            e, i = [self.eval(a) for a in op.args]
-            cp = op.conv_params
-            out = co.conv_update(i[:, 0], e[:, 0], op.axes.lengths[2:4], (cp["pad_h"], cp["pad_w"]),
-                                 (cp["str_h"], cp["str_w"]))
-            return out[:, None].reshape(op.axes.lengths)
+            geo = [tuple(int(cp.get(k + "_" + d, dflt)) for d in "dhw")
+                   for k, dflt in (("pad", 0), ("str", 1), ("dil", 1))]
+            if isinstance(op, g.ConvolutionOp):
+                out = co.conv3d_fprop(a, b, *geo)
+            elif isinstance(op, g.bprop_conv):            # args (delta, filters)
+                out = co.conv3d_bprop(a, b, op.axes.lengths[1:4], *geo)
+            else:                                         # args (delta, inputs)
+                out = co.conv3d_update(b, a, op.axes.lengths[1:4], *geo)
+            return out.reshape(op.axes.lengths)
         if isinstance(op, g.LookupTableOp):
             lut, idx = self.eval(op.args[0]), self.eval(op.args[1])
             return lo.lut_fprop(lut, idx, op.lut_axis).reshape(op.axes.lengths)

@@ -446,3 +446,131 @@ def test_conv_fused_epilogue(variant):
         hi = pl[off:off + got.size].view(np.int8).astype(np.int64).reshape(got.shape)
         lo = pl[off + out_plane_bytes:off + out_plane_bytes + got.size].astype(np.int64).reshape(got.shape)
         assert np.array_equal(256 * hi + lo, got)
+
+
+# ---- the reference's own flex convolution shape set, with its depth axes ------------------------
+# tests/flex_tests/test_flexconv.py:25-45: (H, W, D, R, S, T, (pad_h, pad_w, pad_d),
+# (str_h, str_w, str_d)); C = 16, N = 32, K = 8, integer data in [-4, 4), exact equality (:60-70).
+REF_FLEXCONV = [
+    (7, 7, 1, 3, 3, 1, (0, 0, 0), (1, 1, 1)), (5, 5, 1, 3, 3, 1, (1, 1, 1), (1, 1, 1)),
+    (10, 10, 1, 4, 4, 1, (3, 3, 3), (1, 1, 1)), (7, 7, 2, 3, 3, 2, (0, 0, 0), (1, 1, 1)),
+    (8, 8, 1, 4, 4, 1, (0, 0, 0), (2, 2, 2)), (10, 10, 1, 3, 3, 1, (1, 1, 1), (3, 3, 3)),
+    (7, 7, 1, 3, 3, 1, (1, 2, 3), (1, 1, 1)), (7, 7, 1, 3, 3, 1, (0, 3, 0), (1, 1, 1)),
+    (7, 7, 1, 3, 3, 1, (0, 0, 0), (3, 1, 1)), (7, 7, 1, 3, 3, 1, (0, 0, 0), (1, 2, 3)),
+]
+# its three "limitation" cases (:47-52: K not a multiple of 8, N not a multiple of 32, dilation)
+# are assertion failures of the reference's SASS kernels; here they are ordinary supported shapes
+# (H, W, D, R, S, T, pad, stride, K, N, dilation)
+REF_FLEXCONV_LIMITS = [(7, 7, 1, 3, 3, 1, (0, 0, 0), (1, 1, 1), 7, 32, 1),
+                       (7, 7, 1, 3, 3, 1, (0, 0, 0), (1, 1, 1), 8, 31, 1),
+                       (7, 7, 1, 3, 3, 1, (0, 0, 0), (1, 1, 1), 8, 32, 2),
+                       (9, 8, 3, 3, 2, 2, (2, 1, 1), (2, 1, 1), 12, 40, 2)]
+
+
+def _dims3(lib, Cc, N, K, H, W, D, R, S, T, pad, stride, dil=1):
+    ph, pw, pd = pad
+    sh, sw, sd = stride
+    d = lib.ConvDims()
+    d.C, d.D, d.H, d.W, d.N = Cc, D, H, W, N
+    d.K, d.T, d.R, d.S = K, T, R, S
+    d.M = (D + 2 * pd - dil * (T - 1) - 1) // sd + 1
+    d.P = (H + 2 * ph - dil * (R - 1) - 1) // sh + 1
+    d.Q = (W + 2 * pw - dil * (S - 1) - 1) // sw + 1
+    d.pad_d, d.pad_h, d.pad_w = pd, ph, pw
+    d.str_d, d.str_h, d.str_w = sd, sh, sw
+    d.dil_d = d.dil_h = d.dil_w = dil
+    return d
+
+
+def _flexconv_cases():
+    out = [(16, 32, 8) + s + (1,) for s in REF_FLEXCONV]
+    for (H, W, D, R, S, T, pad, stride, K, N, dil) in REF_FLEXCONV_LIMITS:
+        out.append((16, N, K, H, W, D, R, S, T, pad, stride, dil))
+    return out
+
+
+@pytest.mark.parametrize("flex", [True, False])
+@pytest.mark.parametrize("case", _flexconv_cases())
+def test_reference_flexconv_shapes_all_three_contractions(case, flex):
+    """Forward, input gradient and filter gradient on every shape of the reference's flex
+    convolution test (depth 2, 4x4 filters with padding 3, stride 3, asymmetric padding and
+    stride) and on its three limitation cases, through the C ABI: flex16 results are the exact
+    integer contractions (np.array_equal, as the reference asserts), fp32 within rtol 1e-4."""
+    import torch
+    from ngraph_python_b200 import lib
+    Cc, N, K, H, W, D, R, S, T, pad, stride, dil = case
+    d = _dims3(lib, Cc, N, K, H, W, D, R, S, T, pad, stride, dil)
+    rng = np.random.RandomState(abs(hash(case)) % (2 ** 31))
+    I = rng.randint(-4, 4, (Cc, D, H, W, N))
+    F = rng.randint(-4, 4, (Cc, T, R, S, K))
+    E = rng.randint(-4, 4, (K, d.M, d.P, d.Q, N))
+    p3, s3, d3 = (pad[2], pad[0], pad[1]), (stride[2], stride[0], stride[1]), (dil, dil, dil)
+    want = [co.conv3d_fprop(I, F, p3, s3, d3, np.int64),
+            co.conv3d_bprop(E, F, (D, H, W), p3, s3, d3, np.int64),
+            co.conv3d_update(I, E, (T, R, S), p3, s3, d3, np.int64)]
+    raw = lib.raw()
+    dt_np, dt_t = (np.int16, torch.int16) if flex else (np.float32, torch.float32)
+    dI, dF, dE = [torch.from_numpy(x.astype(dt_np)).cuda() for x in (I, F, E)]
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    table = torch.ones((3, 2), dtype=torch.float32, device="cuda")      # all exponents 0
+    stats = torch.zeros((3,), dtype=torch.int32, device="cuda")
+    probe = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    jobs = [("fprop", lib.conv_fprop_scratch_bytes, raw.b2_conv_fprop_flex16, raw.b2_conv_fprop_f32,
+             (dI, dF)),
+            ("bprop", lib.conv_bprop_scratch_bytes, raw.b2_conv_bprop_flex16, raw.b2_conv_bprop_f32,
+             (dE, dF)),
+            ("update", lib.conv_update_scratch_bytes, raw.b2_conv_update_flex16,
+             raw.b2_conv_update_f32, (dI, dE))]
+    for (name, sizer, f16, f32, (a, b)), exp in zip(jobs, want):
+        out = torch.zeros(exp.shape, dtype=dt_t, device="cuda")
+        nb = sizer(flex, d)
+        keep, sp = _scratch(torch, nb)
+        if flex:
+            assert int(np.abs(exp).max()) <= 32767
+            stats.zero_()
+            probe.zero_()
+            for pr in (1, 0):
+                lib.check(f16(a.data_ptr(), b.data_ptr(), out.data_ptr(), C.byref(d),
+                              table.data_ptr(), 0, 1, 2, stats.data_ptr(), sp, nb, probe.data_ptr(),
+                              status.data_ptr(), pr, 0))
+                torch.cuda.synchronize()
+                assert int(status.item()) == 0
+            assert int(probe.item()) == int(np.abs(exp).max()), name
+            assert np.array_equal(out.cpu().numpy().astype(np.int64), exp), name
+            assert int(stats[2].item()) == int(np.abs(exp).max()), name
+        else:
+            lib.check(f32(a.data_ptr(), b.data_ptr(), out.data_ptr(), C.byref(d), sp, nb,
+                          status.data_ptr(), 0))
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+            np.testing.assert_allclose(out.cpu().numpy(), exp, rtol=1e-4, atol=1e-3, err_msg=name)
+
+
+@pytest.mark.parametrize("flex", [True, False])
+@pytest.mark.parametrize("case", _flexconv_cases())
+def test_reference_flexconv_shapes_through_the_transformer(case, flex):
+    """The same set the way the reference runs it (ngraph/testing/flex_util.py:241-267,
+    execute_convolution): placeholders for image and filters, ng.convolution, one call of the
+    computation with integer data; the result must equal the numpy convolution exactly."""
+    import ngraph_python_b200 as ng
+    Cc, N, K, H, W, D, R, S, T, pad, stride, dil = case
+    ax = lambda n, nm: ng.make_axis(n, name=nm)   # noqa: E731
+    M = (D + 2 * pad[2] - dil * (T - 1) - 1) // stride[2] + 1
+    P = (H + 2 * pad[0] - dil * (R - 1) - 1) // stride[0] + 1
+    Q = (W + 2 * pad[1] - dil * (S - 1) - 1) // stride[1] + 1
+    ax_i = [ax(Cc, "C"), ax(D, "D"), ax(H, "H"), ax(W, "W"), ax(N, "N")]
+    ax_f = [ax_i[0], ax(T, "T"), ax(R, "R"), ax(S, "S"), ax(K, "K")]
+    ax_o = [ax_f[4], ax(M, "M"), ax(P, "P"), ax(Q, "Q"), ax_i[4]]
+    params = dict(pad_d=pad[2], pad_h=pad[0], pad_w=pad[1], str_d=stride[2], str_h=stride[0],
+                  str_w=stride[1], dil_d=dil, dil_h=dil, dil_w=dil)
+    rng = np.random.RandomState(3)
+    iv = rng.randint(-4, 4, [a.length for a in ax_i]).astype(np.float32)
+    fv = rng.randint(-4, 4, [a.length for a in ax_f]).astype(np.float32)
+    t = ng.transformers.allocate_transformer("b200", flex=flex)
+    inputs, filters = ng.placeholder(ax_i), ng.placeholder(ax_f)
+    comp = t.computation(ng.convolution(params, inputs, filters, axes=ax_o), inputs, filters)
+    got = comp(iv, fv)
+    t.close()
+    exp = co.conv3d_fprop(iv, fv, (pad[2], pad[0], pad[1]), (stride[2], stride[0], stride[1]),
+                          (dil, dil, dil), np.float64)
+    assert np.array_equal(np.asarray(got, dtype=np.float64), exp)

@@ -115,3 +115,30 @@ def test_pool_gradient_oracle_is_the_adjoint(op):
         num = ((co.pool_max_fprop(I + eps * d, (3, 3), (1, 1), (2, 2)) -
                 co.pool_max_fprop(I - eps * d, (3, 3), (1, 1), (2, 2))) * E).sum() / (2 * eps)
     assert abs(num - ana) <= 2e-3 * max(1.0, abs(ana))
+
+
+def test_depth_oracles_match_reference_cpu():
+    """The restatements with depth axes, asymmetric padding / stride and dilation against the
+    reference CPU transformer's forward result and both gradients (fixture conv3d_grads), and,
+    with D = T = M = 1, against the 2-d restatements."""
+    _, _, (I, F, E) = cases.CASES["conv3d_grads"](ng)
+    fix = np.load(os.path.join(FIX, "conv3d_grads.npz"))
+    geo = ((1, 2, 0), (1, 2, 1), (1, 1, 2))
+    np.testing.assert_allclose(co.conv3d_fprop(I, F, *geo), fix["out0_0"], rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(co.conv3d_bprop(E, F, I.shape[1:4], *geo), fix["out0_1"], rtol=1e-4,
+                               atol=1e-4)
+    np.testing.assert_allclose(co.conv3d_update(I, E, F.shape[1:4], *geo), fix["out0_2"], rtol=1e-4,
+                               atol=2e-3)
+    rng = np.random.RandomState(3)
+    I2 = rng.randint(-9, 10, (4, 9, 8, 2)).astype(np.int64)
+    F2 = rng.randint(-9, 10, (4, 3, 2, 6)).astype(np.int64)
+    O2 = co.conv_fprop(I2, F2, (1, 1), (2, 1), dtype=np.int64)
+    assert np.array_equal(co.conv3d_fprop(I2[:, None], F2[:, None], (0, 1, 1), (1, 2, 1),
+                                          dtype=np.int64)[:, 0], O2)
+    E2 = rng.randint(-9, 10, O2.shape).astype(np.int64)
+    assert np.array_equal(co.conv3d_bprop(E2[:, None], F2[:, None], (1, 9, 8), (0, 1, 1), (1, 2, 1),
+                                          dtype=np.int64)[:, 0],
+                          co.conv_bprop(E2, F2, (9, 8), (1, 1), (2, 1), dtype=np.int64))
+    assert np.array_equal(co.conv3d_update(I2[:, None], E2[:, None], (1, 3, 2), (0, 1, 1), (1, 2, 1),
+                                           dtype=np.int64)[:, 0],
+                          co.conv_update(I2, E2, (3, 2), (1, 1), (2, 1), dtype=np.int64))

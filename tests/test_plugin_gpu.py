@@ -118,7 +118,7 @@ def test_reference_resnet20_batch_256(flex):
     comp = t.computation(out, x)
     got = [[np.array(r, copy=True) for r in comp(xv)] for _ in range(2)]
     convs = [s for s in comp.impl.steps if s.kind == "conv"]
-    assert len(convs) == 22
+    assert len(convs) == 44        # the network twice: once under the softmax, once for the features
     if flex:
         assert all(s.use_planes for s in convs)
         assert all(s.epi for s in convs if s.dims.R == 3)

@@ -203,3 +203,46 @@ def test_flex_register_forwarding_is_bit_exact(case):
     for a, b in zip(got[True][:-1], got[False][:-1]):
         for x, y in zip(a, b):
             assert np.array_equal(x, y)
+
+
+@pytest.mark.parametrize("flex", [False, True])
+def test_device_tensor_get_slice_and_assign(flex):
+    """Tensors read and written from the host outside any computation: whole tensor, windows
+    (slices, integers, Ellipsis, steps), scalar fills -- GPUDeviceTensor.get / __getitem__ /
+    __setitem__ of the reference (ngraph/transformers/gputransform.py:679-909); flex16 values go
+    through value / scale, clip, truncate (flexgputransform.py:183-208)."""
+    A, B, C = ng.make_axis(12, name="A"), ng.make_axis(9, name="B"), ng.make_axis(20, name="C")
+    rng = np.random.RandomState(5)
+    w0 = rng.uniform(-2, 2, (12, 9, 20)).astype(np.float32)
+    w = ng.variable([A, B, C], initial_value=w0)
+    x = ng.placeholder([A, B, C])
+    t = ng.transformers.allocate_transformer("b200", flex=flex)
+    comp = t.computation(w + x, x)
+    t.initialize()
+    dt = t.device_tensor(w)
+    assert dt.shape == (12, 9, 20)
+    step = dt.scale if flex else 0.0
+    ref = w0.copy()
+    if flex:
+        ref = np.trunc(ref / step) * step          # the host write truncates
+    np.testing.assert_allclose(dt.get(), ref, rtol=0, atol=1e-7)
+    np.testing.assert_allclose(dt[2:5, :, 3].get(), ref[2:5, :, 3], rtol=0, atol=1e-7)
+    np.testing.assert_allclose(dt[..., 1:20:3].get(), ref[..., 1:20:3], rtol=0, atol=1e-7)
+    np.testing.assert_allclose(dt[-1].get(), ref[-1], rtol=0, atol=1e-7)
+    new = rng.uniform(-1, 1, (3, 9)).astype(np.float32)
+    dt[2:5, :, 3] = new
+    dt[0, 1:4] = 0.5
+    ref[2:5, :, 3] = np.trunc(new / step) * step if flex else new
+    ref[0, 1:4] = 0.5
+    np.testing.assert_allclose(t.get_tensor_view_value(w), ref, rtol=0, atol=1e-7)
+    # and the computation sees what was written
+    xv = np.zeros((12, 9, 20), np.float32)
+    np.testing.assert_allclose(comp(xv), ref, rtol=0, atol=2 * step + 1e-7)
+    dt[...] = w0 * 0.5
+    got = dt.get()
+    np.testing.assert_allclose(got, w0 * 0.5, rtol=0, atol=step + 1e-7)
+    with pytest.raises(IndexError):
+        dt[0, 0, 0, 0]
+    with pytest.raises(ValueError):
+        dt[2:5, :, 3] = np.zeros((9, 3), np.float32)
+    t.close()
