@@ -329,6 +329,21 @@ int b2_dimshuffle(const void* src, void* dst, int32_t elem_bytes, int32_t rank,
                   const int64_t* shape, const int64_t* src_strides, const int64_t* dst_strides,
                   void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Random fill: out[i] ~ U[a, b) (B2_RNG_UNIFORM: a = low, b = high) or N(a, b) (B2_RNG_NORMAL:
+ * a = loc, b = scale), n elements, fp32 or flex16 (quantised with slot's exponent; statistic or
+ * probe -- bit pattern of max |fp32 value| into *probe_out -- as for b2_pool_bprop).
+ * Replaces RngFillKernel / FlexRngFillKernel (ngraph/transformers/gpu/tensor_ops.py:621-661,
+ * 713-740).  Counter-based generator (Philox-4x32-10): (seed, offset) determines the tensor.
+ * device_counter (may be NULL): a 64-bit device word added to `offset` and advanced by one after
+ * a storing launch, so that launches replayed from a CUDA graph still draw fresh numbers.
+ * ------------------------------------------------------------------------------------------ */
+enum b2_rng_distribution { B2_RNG_UNIFORM = 0, B2_RNG_NORMAL = 1 };
+int b2_rng_fill(void* out, int32_t flex, int64_t n, int32_t distribution, float a, float b,
+                uint64_t seed, uint64_t offset, uint64_t* device_counter,
+                const b2_flex_scale* table, int32_t slot, int32_t* stats, uint64_t* probe_out,
+                int32_t probe, void* stream);
+
 /* Lookup table (embedding).  lut_axis 0: lut [V][F], out / delta [n_idx][F], dW [V][F];
  * lut_axis 1: lut [F][V], out / delta [F][n_idx], dW [F][V].  Indices are values of the tensor
  * idx (fp32, or flex16 mantissas with the scale of slot_idx), rounded to the nearest integer.

@@ -573,6 +573,53 @@ class LutUpdateStep(_Step):
         self._flex_probe_then(t, ov.buffer, [dv.buffer, xv.buffer], call)
 
 
+class RngStep(_Step):
+    """Random fill (RngFillKernel / FlexRngFillKernel, ngraph/transformers/gpu/tensor_ops.py:
+    621-661, 713-740).  The stream of numbers is fixed by the transformer's seed and the position
+    of the op in its graph; a device-side counter moves it on after every execution, also under
+    CUDA-graph replay."""
+    kind = "rng"
+    launches = 2           # the fill and the advance of its counter
+    probe_is_float = True
+
+    def __init__(self, index, op, t):
+        super(RngStep, self).__init__(index, op)
+        ov = t._view_of(op)
+        self.out_views = [ov]
+        self.in_views = []
+        self.flex = t.flex
+        p = op.params
+        if op.distribution == "uniform":
+            self.dist, self.a, self.b = lib.RNG_UNIFORM, float(p["low"]), float(p["high"])
+        else:
+            self.dist, self.a, self.b = lib.RNG_NORMAL, float(p["loc"]), float(p["scale"])
+        self.seed = int(t.rng_seed)
+        self.stream_id = t._next_rng_stream()
+        self.counter = None
+
+    def allocate(self, t):
+        if self.counter is None and not t.plan_only:
+            self.counter = t.torch.zeros((1,), dtype=t.torch.int64, device=t.device)
+
+    def launch(self, t):
+        ov = self.out_views[0]
+        raw = lib.raw()
+        st = t.stream.cuda_stream
+        offset = self.stream_id << 40           # streams of different ops never meet
+        head = (self._ptr(ov), int(self.flex), ov.buffer.size, self.dist, self.a, self.b, self.seed,
+                offset, self.counter.data_ptr())
+        if not self.flex:
+            lib.check(raw.b2_rng_fill(*(head + (None, -1, None, None, 0, st))))
+            t.kernel_launches += self.launches
+            return
+        slot = ov.buffer.slot_write
+
+        def call(probe):
+            lib.check(raw.b2_rng_fill(*(head + (t._table.data_ptr(), slot, t._stats.data_ptr(),
+                                                t._probe64.data_ptr(), probe, st))))
+        self._flex_probe_then(t, ov.buffer, [], call)
+
+
 class DimshuffleStep(_Step):
     """A strided copy between two views with the same axes (DimShuffleKernel of the reference,
     ngraph/transformers/gpu/tensor_ops.py:119-204; it also carries AssignOp between differently

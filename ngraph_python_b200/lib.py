@@ -126,6 +126,8 @@ def _load():
                                     vp, vp, i32, vp]),
         "b2_dimshuffle": (C.c_int, [vp, vp, i32, i32, C.POINTER(i64), C.POINTER(i64),
                                     C.POINTER(i64), vp]),
+        "b2_rng_fill": (C.c_int, [vp, i32, i64, i32, C.c_float, C.c_float, C.c_uint64, C.c_uint64,
+                                  vp, vp, i32, vp, vp, i32, vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),
@@ -269,6 +271,7 @@ def conv_fprop_scratch_bytes(flex, dims):
 
 
 CONV_FPROP, CONV_BPROP = 0, 1
+RNG_UNIFORM, RNG_NORMAL = 0, 1
 
 
 def conv_planes_info(dims, conv_pass=CONV_FPROP):

@@ -228,6 +228,8 @@ class GraphTranslator(object):
         if isinstance(op, ref_update_lut):            # args (delta, idx); the table via fprop
             fprop = self(op.fprop)
             return b2.update_lut(args[0], fprop.args[0], args[1], fprop)
+        if isinstance(op, ref.RngOp):
+            return b2.RngOp(op.distribution, op.params, args[0])
         if isinstance(op, ref.ContiguousOp):
             return b2.value_of(args[0])
         raise ValueError("Unhandled op: {}".format(op))

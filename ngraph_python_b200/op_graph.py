@@ -729,6 +729,28 @@ class AllReduceOp(Op):
         self.reduce_func = reduce_func
 
 
+class RngOp(Op):
+    """A tensor with the axes of x, filled with fresh random numbers on every execution
+    (ngraph/op_graph/op_graph.py:2786-2870; x only supplies the axes, as in the reference's
+    kernels, ngraph/transformers/gpu/tensor_ops.py:621-661)."""
+
+    def __init__(self, distribution, params, x, **kw):
+        if distribution not in ("uniform", "normal"):
+            raise ValueError("unsupported distribution: {}".format(distribution))
+        x = as_op(x)
+        self.distribution = distribution
+        self.params = dict(params)
+        super(RngOp, self).__init__((x,), x.axes, **kw)
+
+
+def uniform(x, low=0.0, high=1.0):
+    return RngOp("uniform", dict(low=low, high=high), x)
+
+
+def normal(x, loc=0.0, scale=1.0):
+    return RngOp("normal", dict(loc=loc, scale=scale), x)
+
+
 def allreduce(x, reduce_func="sum"):
     return AllReduceOp(x, reduce_func)
 

@@ -24,7 +24,7 @@ from . import lib
 from . import comm as commmod
 from .op_graph import (AllReduceOp, AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp,
                        ConvolutionOp, DotOp, bprop_conv, update_conv,
-                       BpropPoolOp, ElementWiseOp, LookupTableOp, Op, PoolingOp, ReductionOp,
+                       BpropPoolOp, ElementWiseOp, LookupTableOp, Op, PoolingOp, ReductionOp, RngOp,
                        ReorderAxes, SequentialOp, TensorSliceOp, update_lut,
                        ViewOp, as_op, make_axes)
 
@@ -722,6 +722,9 @@ class _Planner(object):
             step = kernels.LutStep(index, op, self.t)
         elif isinstance(op, update_lut):
             step = kernels.LutUpdateStep(index, op, self.t)
+        elif isinstance(op, RngOp):
+            step = kernels.RngStep(index, op, self.t)
+            reads = []                 # the argument only supplies the axes
         else:
             raise ValueError("Unhandled op: {}".format(op))
         # the step must come after everything its arguments depend on; steps are appended in
@@ -1090,6 +1093,9 @@ class B200Transformer(object):
         self.comm = kwargs.pop("comm", None) or commmod.SingleProcessComm()
         self.bucket_bytes = int(kwargs.pop("bucket_bytes", commmod.DEFAULT_BUCKET_BYTES))
         self.min_buckets = int(kwargs.pop("min_buckets", 4))
+        # random fills: the seed fixes every stream of numbers this transformer draws
+        self.rng_seed = int(kwargs.pop("rng_seed", 0))
+        self._rng_streams = 0
         self._alias = {}
         self._pinned = {}
         self._inputs_written = []
@@ -1206,6 +1212,10 @@ class B200Transformer(object):
         if buf.persistent:
             return buf.slot_write
         return buf.slot
+
+    def _next_rng_stream(self):
+        self._rng_streams += 1
+        return self._rng_streams
 
     def _need_scratch(self, nbytes):
         self._scratch_bytes = max(self._scratch_bytes, int(nbytes))
@@ -1469,14 +1479,14 @@ class B200Transformer(object):
         src = torch.from_numpy(np.ascontiguousarray(arr).reshape(-1).copy()).to(self.device)
         esize = 4
         if buf.flex:
-            # FlexGPUDeviceTensor.__setitem__: the entry sees the value before and the largest
-            # mantissa after; the tensor keeps its exponent (a first write picks one that fits)
+            # FlexGPUDeviceTensor.__setitem__ (value / scale, clip, truncate)
+            # A window keeps the exponent the rest of the tensor is stored with (adopting a new
+            # one here would re-scale every mantissa that is not rewritten); values beyond its
+            # range saturate, as FlexGPUDeviceTensor.__setitem__ clips them.
             e = buf.entry
             if not e.initialized:
                 e.initialize_from_range(float(np.max(np.abs(arr))) if arr.size else 0.0,
                                         from_host=True)
-            else:
-                e.begin_write()
             self._set_table_row(buf.slot, e.dec)
             self._set_table_row(buf.slot_write, e.dec)
             self._stats[buf.slot:buf.slot + 1].zero_()
@@ -1498,8 +1508,6 @@ class B200Transformer(object):
             self.kernel_launches += 1
         self.stream.synchronize()
         buf.version += 1
-        if buf.flex:
-            buf.entry.end_write(int(self._stats[buf.slot].item()))
 
     # ---- flex bookkeeping ------------------------------------------------------------------------
     def _set_table_row(self, slot, dec):
