@@ -336,6 +336,29 @@ class AxesCastOp(ViewOp):
         super(AxesCastOp, self).__init__((x,), axes, **kw)
 
 
+class ReshapeOp(ViewOp):
+    """The same elements in the same order under other axes: neighbouring axes merged into one or
+    one axis split into several (the reference's Flatten / Unflatten,
+    ngraph/op_graph/op_graph.py:2221-2294, whose FlattenedAxis has the product of its members'
+    lengths).  No data moves; the argument's storage must allow it (a dense tensor always does)."""
+
+    def __init__(self, x, axes, **kw):
+        x = as_op(x)
+        axes = make_axes(axes)
+        if x.axes.size != axes.size:
+            raise ValueError("reshape from {} to {} changes the number of elements"
+                             .format(x.axes, axes))
+        super(ReshapeOp, self).__init__((x,), axes, **kw)
+
+
+def reshape(x, axes):
+    x = as_op(x)
+    axes = make_axes(axes)
+    if x.axes == axes:
+        return x
+    return ReshapeOp(x, axes)
+
+
 class TensorSliceOp(ViewOp):
     """A sliced view: one slice or int per axis of x; an int drops the axis
     (ngraph/op_graph/op_graph.py:2067-2120).  Negative steps are not supported, as there."""

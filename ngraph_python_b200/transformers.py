@@ -25,7 +25,7 @@ from . import comm as commmod
 from .op_graph import (AllReduceOp, AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp,
                        ConvolutionOp, DotOp, bprop_conv, update_conv,
                        BpropPoolOp, ElementWiseOp, LookupTableOp, Op, PoolingOp, ReductionOp, RngOp,
-                       ReorderAxes, SequentialOp, TensorSliceOp, update_lut,
+                       ReorderAxes, ReshapeOp, SequentialOp, TensorSliceOp, update_lut,
                        ViewOp, as_op, make_axes)
 
 
@@ -181,13 +181,14 @@ class Computation(object):
             final.extend(planner.finalize_step(s))     # (a step may bring copies that precede it)
         self.steps = final
         self._comm_steps = planner.comm_steps
+        # (a parameter the results do not depend on still gets its tensor: callers pass a value)
+        self.param_buffers = [t._view_of(p).buffer for p in self.parameters]
         t._allocate(self)
         for s in self.steps:
             if hasattr(s, "allocate"):
                 s.allocate(t)
         self.launches_per_call = builtin_sum(s.launches for s in self.steps)
         self.written = planner.written_buffers
-        self.param_buffers = [t._view_of(p).buffer for p in self.parameters]
         self.executor = self._run_steps
 
     # ---- run -----------------------------------------------------------------------------
@@ -700,6 +701,59 @@ class _Planner(object):
         if tail:
             reads += [x for x in (tail["bias"], tail["residual"]) if x is not None]
         self._place_deferred_for(reads)
+        # Operands these kernels cannot take as they lie (a sliced or reordered view where a dense
+        # tensor is needed; a dot operand that does not fold to two dimensions) are first copied
+        # into dense temporaries by the strided copy kernel -- what the reference's layout pass
+        # does with DimshuffleOps (ngraph/transformers/passes/layout.py:282-339).  The copies
+        # stand in for the operands' views only while this step is built.
+        saved = {}
+        try:
+            if isinstance(op, DotOp):
+                try:
+                    kernels.GemmStep(self._new_step_index(), op, self.t)
+                except ValueError:
+                    x, y = op.args
+                    red = [a for a in x.axes if a in op.reduction_axes]
+                    self._densify(x, list(op.x_out_axes) + red, saved)
+                    self._densify(y, red + list(op.y_out_axes), saved)
+            elif isinstance(op, (ConvolutionOp, bprop_conv, update_conv, PoolingOp, BpropPoolOp,
+                                 LookupTableOp, update_lut)):
+                for a in op.args:
+                    if not self.t._view_of(a).is_dense():
+                        self._densify(a, list(self.t._view_of(a).axes), saved)
+            step = self._make_other_step(op, tail)
+        finally:
+            for key, old in saved.items():
+                if old is None:
+                    self.t._views.pop(key, None)
+                else:
+                    self.t._views[key] = old
+        index = step.index
+        self._register_other(op, step, reads, tail)
+
+    def _densify(self, arg, axes, saved):
+        """Appends a copy step that lays `arg` out dense over `axes` and makes the copy stand in
+        for the argument's view until the caller restores `saved`."""
+        t = self.t
+        key = arg
+        while isinstance(key, SequentialOp) or key in t._alias:
+            key = key.value_tensor if isinstance(key, SequentialOp) else t._alias[key]
+        view = t._view_of(key)
+        pre, nv = self._dense_copy_of(view, make_axes(axes), self._new_step_index(), expand=True)
+        base, _ = self._base_tensor(arg)
+        if base in self.group_of:
+            self.group_of[base].stored.add(base)
+        if isinstance(base, AssignableTensorOp) and not base.is_scalar_constant:
+            b = t._buffer_of(base)
+            b.last_read_step = max(b.last_read_step, pre.index)
+            if t.flex and b.last_write_step >= 0:
+                nv.buffer.slot = b.slot_write      # the copy carries what the in-place write stored
+        self.steps.append(pre)
+        if key not in saved:
+            saved[key] = t._views.get(key)
+        t._views[key] = nv
+
+    def _make_other_step(self, op, tail):
         index = self._new_step_index()
         if isinstance(op, DotOp):
             step = kernels.GemmStep(index, op, self.t)
@@ -724,9 +778,14 @@ class _Planner(object):
             step = kernels.LutUpdateStep(index, op, self.t)
         elif isinstance(op, RngOp):
             step = kernels.RngStep(index, op, self.t)
-            reads = []                 # the argument only supplies the axes
         else:
             raise ValueError("Unhandled op: {}".format(op))
+        return step
+
+    def _register_other(self, op, step, reads, tail):
+        index = step.index
+        if isinstance(op, RngOp):
+            reads = []                 # the argument only supplies the axes
         # the step must come after everything its arguments depend on; steps are appended in
         # dependency order, so only in-place writes of persistent tensors need recording
         for a in reads:
@@ -831,10 +890,11 @@ class _Planner(object):
             return None          # a broadcasting fill: the elementwise kernel does that well
         return src, dst
 
-    def _dense_copy_of(self, view, iter_axes, index):
-        """A dimshuffle step that lays `view` out dense in iteration order, and the new view."""
+    def _dense_copy_of(self, view, iter_axes, index, expand=False):
+        """A dimshuffle step that lays `view` out dense in iteration order, and the new view.
+        expand: axes the view only broadcasts along are written out too."""
         t = self.t
-        axes = [a for a in iter_axes if view.stride_of(a) != 0 or a.length == 1]
+        axes = [a for a in iter_axes if expand or view.stride_of(a) != 0 or a.length == 1]
         tmp = Buffer("dimshuffle_%d" % len(t._buffers), axes, view.buffer.flex)
         if view.buffer.flex:
             t._share_entry(tmp, view.buffer)
@@ -859,7 +919,8 @@ class _Planner(object):
 
         def fold():
             sl = [[v.stride_of(a) for a in iter_axes] for v in list(g.ext_inputs) + out_views]
-            clen, cstr, cred = fusion.collapse_dims(lengths, sl, reduced)
+            red = [a in red_axes for a in iter_axes]
+            clen, cstr, cred = fusion.collapse_dims(list(iter_axes.lengths), sl, red)
             return (clen, cstr) + fusion.map_to_abc(clen, cstr, cred)
         copy = self._pure_copy(step)
         folded = None
@@ -867,9 +928,14 @@ class _Planner(object):
             folded = fold()
         except ValueError:
             if copy is None:
-                # More non-mergeable axes than the kernel has: lay the inputs that are to blame
-                # out dense in iteration order first (the reference's layout pass inserts
-                # DimshuffleOps for the same purpose, ngraph/transformers/passes/layout.py:282-339)
+                # More non-mergeable axes than the kernel has, or reduced axes that do not lie
+                # together: walk the kept axes first and the reduced ones last, and lay the
+                # inputs that are to blame out dense in that order first (the reference's layout
+                # pass inserts DimshuffleOps for the same purpose,
+                # ngraph/transformers/passes/layout.py:282-339)
+                if any(reduced):
+                    iter_axes = make_axes([a for a in iter_axes if a not in red_axes] +
+                                          [a for a in iter_axes if a in red_axes])
                 for i, v in enumerate(list(g.ext_inputs)):
                     own = [a for a in iter_axes if v.stride_of(a) != 0 or a.length == 1]
                     expect, dense = 1, True
@@ -911,6 +977,13 @@ class _Planner(object):
         pending = []     # (dst op, opname, [arg descriptors])
         for m in g.members:
             if isinstance(m, ReductionOp):
+                # a reduction of a broadcast scalar constant reads the constant's register
+                base, _ = self._base_tensor(self._value_args(m)[0])
+                if self._is_scalar_const(base):
+                    val = float(np.asarray(base.initial_value))
+                    if val not in const_reg:
+                        const_reg[val] = len(consts)
+                        consts.append(val)
                 continue
             args = self._value_args(m)
             descs = []
@@ -974,6 +1047,8 @@ class _Planner(object):
                 base, chain = self._base_tensor(src)
                 if g.has(base) and not chain:
                     d["reg"] = reg[base]
+                elif self._is_scalar_const(base):
+                    d["reg"] = n_in + const_reg[float(np.asarray(base.initial_value))]
                 else:
                     d["reg"] = input_index(t._view_of(self._resolve(src)))
                 if mode == lib.REDUCE_NONE:
@@ -1031,6 +1106,53 @@ class _Planner(object):
             if v.buffer not in self.written_buffers:
                 self.written_buffers.append(v.buffer)
         return pre_steps + [step]
+
+
+def _reshape_strides(old_shape, old_strides, new_shape):
+    """Element strides under which `new_shape` walks the same elements in the same order as
+    (old_shape, old_strides), or None when that needs a copy.  Axes of extent 1 are free; a
+    group of old axes can be re-cut only where it is contiguous within itself."""
+    olds = [(n, st) for n, st in zip(old_shape, old_strides) if n != 1]
+    out = []
+    oi = 0
+    ni = 0
+    news = list(new_shape)
+    while ni < len(news):
+        if news[ni] == 1:
+            out.append(0)
+            ni += 1
+            continue
+        if oi >= len(olds):
+            return None
+        # grow a group of old axes and a group of new axes until their sizes agree
+        o_size, n_size = olds[oi][0], news[ni]
+        o_end, n_end = oi + 1, ni + 1
+        while o_size != n_size:
+            if o_size < n_size:
+                if o_end >= len(olds):
+                    return None
+                o_size *= olds[o_end][0]
+                o_end += 1
+            else:
+                while n_end < len(news) and news[n_end] == 1:
+                    n_end += 1
+                if n_end >= len(news):
+                    return None
+                n_size *= news[n_end]
+                n_end += 1
+        # the old group must be contiguous within itself
+        for k in range(oi, o_end - 1):
+            if olds[k][1] != olds[k + 1][1] * olds[k + 1][0]:
+                return None
+        st = olds[o_end - 1][1]
+        part = []
+        for k in range(n_end - 1, ni - 1, -1):
+            part.append(0 if news[k] == 1 else st)
+            if news[k] != 1:
+                st *= news[k]
+        out.extend(reversed(part))
+        oi, ni = o_end, n_end
+    return out if oi == len(olds) else None
 
 
 def _fuse_sigmoid(ops, n_in, consts):
@@ -1194,6 +1316,14 @@ class B200Transformer(object):
         elif isinstance(op, AxesCastOp):
             src = self._view_of(op.args[0])
             v = View(src.buffer, op.axes, src.strides, src.offset)
+        elif isinstance(op, ReshapeOp):
+            src = self._view_of(op.args[0])
+            strides = _reshape_strides(list(src.axes.lengths), list(src.strides),
+                                       list(op.axes.lengths))
+            if strides is None:
+                raise ValueError("Unhandled op: {} needs a copy of its argument first "
+                                 "(its elements do not lie in one regular pattern)".format(op))
+            v = View(src.buffer, op.axes, strides, src.offset)
         elif isinstance(op, TensorSliceOp):
             src = self._view_of(op.args[0])
             offset = src.offset + sum(st * sr for st, sr in zip(op.starts, src.strides))

@@ -66,8 +66,8 @@ class Interp(object):
             return self._to(self.eval(op.args[0]), op.args[0].axes, op.axes)
         if isinstance(op, g.TensorSliceOp):
             return np.asarray(self.eval(op.args[0]))[op.slices].reshape(op.axes.lengths)
-        if isinstance(op, g.AxesCastOp):
-            return self.eval(op.args[0]).reshape(op.axes.lengths)
+        if isinstance(op, (g.AxesCastOp, g.ReshapeOp)):
+            return np.ascontiguousarray(self.eval(op.args[0])).reshape(op.axes.lengths)
         if isinstance(op, g.ElementWiseOp):
             args = [self._to(self.eval(a), a.axes, op.axes) for a in op.args]
             return ew.apply(op.opname, *args).astype(np.float32)
