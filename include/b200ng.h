@@ -362,6 +362,19 @@ int b2_lut_update(const void* delta, const void* idx, void* dW, int32_t flex, in
                   int32_t slot_delta, int32_t slot_idx, int32_t slot_dW, int32_t* stats,
                   uint64_t* probe_out, int32_t probe, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Self-test of the bounded-wait path.  Every device-side wait of the tile kernels gives up after
+ * a fixed number of polls, sets the caller's status word to 1 (the launching entry point's
+ * `status` argument; the host then reports B2_ERR_TIMEOUT-class failure for that call) and lets
+ * the kernel finish normally, tensor memory freed.  This entry point runs that path on purpose: a
+ * one-block kernel waits, with the kernels' own wait routine, `poll_limit` polls (1..65536) on a
+ * barrier nothing completes, then sets *status = 1, writes the polls it waited to *polls_waited
+ * (may be NULL), frees its tensor memory and returns.  Harmless: no fault, no trap, the context
+ * stays usable.  No counterpart in the reference (its kernels have no device-side waits).
+ * ------------------------------------------------------------------------------------------ */
+int b2_selftest_bounded_wait(int32_t poll_limit, int32_t* status, int32_t* polls_waited,
+                             void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,3 +31,45 @@ extern "C" int b2_gemm_flex16(const int16_t* A, int64_t a_row_stride, int64_t a_
                                         scratch_bytes, (unsigned long long*)probe_out, status,
                                         probe ? 1 : 0, (cudaStream_t)stream);
 }
+
+// ---- self-test of the bounded-wait path ----------------------------------------------------------
+// Every device-side wait of the tile kernels (on an mbarrier that a TMA copy, an MMA commit or
+// another warp completes) gives up after a fixed number of polls, sets the caller's status word
+// and lets the kernel finish normally -- tensor memory freed, nothing left spinning.  This kernel
+// runs exactly that path on purpose and harmlessly: it waits, with the kernels' own wait routine,
+// on a barrier that nothing will ever complete, for `poll_limit` polls, then reports and cleans up
+// as the tile kernels do.  No fault, no trap, no endless loop: the context stays usable.
+namespace {
+__global__ void __launch_bounds__(64)
+bounded_wait_selftest_kernel(int poll_limit, int* status, int* waited_out) {
+    __shared__ unsigned long long bar;
+    __shared__ unsigned holder;
+    __shared__ int failed;
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);                    // one arrival expected; nobody arrives
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(&holder, 32);    // held across the wait, like the tile kernels
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (threadIdx.x == 32 && !mbar_wait_limit(&bar, 0, poll_limit)) atomicExch(&failed, 1);
+    __syncthreads();
+    if (threadIdx.x == 0 && failed) {
+        if (status) atomicExch(status, 1);
+        if (waited_out) *waited_out = poll_limit;
+    }
+    if (warp == 0) tmem_dealloc(holder, 32);
+}
+}  // namespace
+
+extern "C" int b2_selftest_bounded_wait(int32_t poll_limit, int32_t* status, int32_t* polls_waited,
+                                        void* stream) {
+    B2_REQUIRE(poll_limit > 0 && poll_limit <= (1 << 16), "poll limit must be in 1..65536");
+    B2_REQUIRE(status, "null status word");
+    bounded_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(poll_limit, status, polls_waited);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}

@@ -92,11 +92,15 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// bounded wait: gives up after ~1M polls (each poll suspends up to a hardware time limit)
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    for (int i = 0; i < (1 << 20); ++i)
+// bounded wait: gives up after `limit` polls (each poll suspends up to a hardware time limit)
+__device__ __forceinline__ bool mbar_wait_limit(unsigned long long* bar, unsigned parity, int limit) {
+    for (int i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
+}
+constexpr int kWaitPolls = 1 << 20;     // what every wait of the kernels allows itself
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    return mbar_wait_limit(bar, parity, kWaitPolls);
 }
 // the same for warps that wait long and share an instruction scheduler with the MMA-issuing
 // thread: back off between polls so that the polling does not take its issue slots

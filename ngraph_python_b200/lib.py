@@ -128,6 +128,7 @@ def _load():
                                     C.POINTER(i64), vp]),
         "b2_rng_fill": (C.c_int, [vp, i32, i64, i32, C.c_float, C.c_float, C.c_uint64, C.c_uint64,
                                   vp, vp, i32, vp, vp, i32, vp]),
+        "b2_selftest_bounded_wait": (C.c_int, [i32, vp, vp, vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),

@@ -22,6 +22,7 @@ from . import fusion
 from . import kernels
 from . import lib
 from . import comm as commmod
+from . import tracing
 from .op_graph import (AllReduceOp, AssignableTensorOp, AssignOp, Axes, AxesCastOp, BroadcastOp,
                        ConvolutionOp, DotOp, bprop_conv, update_conv,
                        BpropPoolOp, ElementWiseOp, LookupTableOp, Op, PoolingOp, ReductionOp, RngOp,
@@ -210,11 +211,17 @@ class Computation(object):
         t._begin_call(self)
         for v in views:
             t._host_to_device(v, None, in_call=True, staged=True)
-        self.executor()
+        traced = None
+        if t.tracer is not None:
+            traced = self._run_steps_traced()
+        else:
+            self.executor()
         # results, flex statistics and the status word come back with asynchronous copies and
         # ONE stream synchronisation
         pending = [t._device_to_host_async(v) for v in self.return_views]
         t._end_call(self)
+        if traced is not None:
+            t._collect_trace(self, traced)
         results = [t._finish_host(p) for p in pending]
         if self.returns_kind is Op:
             return results[0]
@@ -226,6 +233,19 @@ class Computation(object):
         t = self.transformer
         for s in self.steps:
             t._launch_step(s)
+
+    def _run_steps_traced(self):
+        """The step list launched one by one, every step between two CUDA events."""
+        t = self.transformer
+        Event = t.torch.cuda.Event
+        pairs = []
+        for s in self.steps:
+            e0, e1 = Event(enable_timing=True), Event(enable_timing=True)
+            e0.record(t.stream)
+            t._launch_step(s)
+            e1.record(t.stream)
+            pairs.append((s, e0, e1))
+        return pairs
 
     def capture(self):
         """Records the step list into CUDA graphs and replays them from now on: one graph launch
@@ -278,6 +298,7 @@ class Computation(object):
         if t._allreduce is not None:
             t._allreduce.begin_call()
         t._recording = has_comm          # comm steps and waits: kernels only, no NCCL, no bookkeeping
+        io_in_graph = False
         try:
             for seg in segments:
                 if all(s.launches == 0 for s in seg["steps"]):
@@ -286,6 +307,15 @@ class Computation(object):
                 with torch.cuda.graph(g):
                     for s in seg["steps"]:
                         t._launch_step(s)
+                    if seg is segments[-1]:
+                        # the call's read-back rides in the graph: status word and flex
+                        # statistics to pinned host memory, then the statistics cleared for the
+                        # next call -- one graph launch and one synchronisation per call
+                        t._status_host.copy_(t._status, non_blocking=True)
+                        if t.flex:
+                            t._stats_host.copy_(t._stats, non_blocking=True)
+                            t._stats.zero_()
+                        io_in_graph = True
                 seg["graph"] = g
         finally:
             t._recording = False
@@ -306,6 +336,9 @@ class Computation(object):
                     if cs.closes_bucket is not None:
                         ar.bucket_ready(cs.closes_bucket)
             t.kernel_launches += per_call
+            if io_in_graph:
+                t._io_done = True
+                t._stats_clean = t.flex
         self.executor = replay
         return self
 
@@ -387,7 +420,95 @@ class _Planner(object):
         return (new_args, group) if group is not None else None
 
     # -- planning -----------------------------------------------------------------------------
+    def _relu_masks_from_activations(self, ordered, returns):
+        """`greater(x, 0)` -- the mask autodiff puts on the gradient of maximum(x, 0) -- reads the
+        activation maximum(x, 0) instead of the pre-activation x where both exist: x > 0 exactly
+        when max(x, 0) > 0, also for quantised values.  The pre-activation then has one reader
+        left, so a convolution's ReLU (and the residual sum before it) folds into the
+        convolution's epilogue in training as it does in inference, and x is never stored."""
+        t = self.t
+        if not (t.fuse and t.fuse_conv_tail):
+            return ordered
+
+        def is_zero(a):
+            base, _ = self._base_tensor(a)
+            return self._is_scalar_const(base) and float(np.asarray(base.initial_value)) == 0.0
+        def key_of(a):
+            base, _ = self._base_tensor(a)
+            if isinstance(base, AssignableTensorOp):
+                return None
+            return t._view_of(self._resolve(a)).key()
+        relu_of = {}
+        for op in ordered:
+            if isinstance(op, ElementWiseOp) and op.opname == "maximum" and len(op.args) == 2:
+                for i in (0, 1):
+                    if is_zero(op.args[1 - i]) and key_of(op.args[i]) is not None:
+                        relu_of.setdefault((key_of(op.args[i]), op.args[i].axes), op)
+        if not relu_of:
+            return ordered
+        out = []
+        for op in ordered:
+            new = None
+            if isinstance(op, ElementWiseOp) and op.opname == "gt" and len(op.args) == 2 and \
+                    is_zero(op.args[1]):
+                act = relu_of.get((key_of(op.args[0]), op.args[0].axes))
+                if act is not None and act.axes == op.args[0].axes:
+                    new = ElementWiseOp("gt", (act, op.args[1]))
+            if new is None:
+                out.append(op)
+            else:
+                t._alias[op] = new
+                out.append(new)
+        return out
+
+    def _sink_to_consumer(self, ordered, returns):
+        """Moves an elementwise op whose value has a single reader, itself elementwise over the
+        same axes, to just before that reader, so that the two share a kernel and the value is
+        never stored (the masks `x > 0` of back-propagation are the typical case: computed where
+        the reference's ordering puts them they would be written out and read back).  Only ops
+        over tensors that nothing overwrites are moved."""
+        if not self.t.fuse:
+            return ordered
+        returned = set(self._base_tensor(r)[0] for r in returns)
+        readers = collections.defaultdict(list)
+        for op in ordered:
+            for a in op.args:
+                readers[self._base_tensor(a)[0]].append(op)
+            if isinstance(op, SequentialOp):
+                for o in op.ops:
+                    readers[self._base_tensor(o)[0]].append(op)
+        held = collections.defaultdict(list)      # reader -> ops to emit right before it
+        for op in ordered:
+            if not isinstance(op, ElementWiseOp) or op in returned or op.opname == "assign":
+                continue
+            rs = readers.get(op, ())
+            if len(rs) != 1 or not isinstance(rs[0], ElementWiseOp) or rs[0].axes != op.axes:
+                continue
+            movable = True
+            for a in op.args:
+                base, _ = self._base_tensor(a)
+                if isinstance(base, AssignableTensorOp) and not base.is_scalar_constant and \
+                        not base.is_constant:
+                    movable = False
+            if movable:
+                held[rs[0]].append(op)
+        if not held:
+            return ordered
+        moved = set(o for ops in held.values() for o in ops)
+        out = []
+
+        def emit(op):
+            for o in held.get(op, ()):
+                emit(o)
+            out.append(op)
+        for op in ordered:
+            if op not in moved:
+                emit(op)
+        return out
+
     def plan(self, ordered, returns):
+        ordered = self._relu_masks_from_activations(ordered, returns)
+        ordered = self._sink_to_consumer(ordered, returns)
         for op in ordered:
             for a in op.args:
                 self.consumers[self._base_tensor(a)[0]].append(op)
@@ -640,7 +761,9 @@ class _Planner(object):
             cur = conv
             chan = conv.axes[0].length
             while True:
-                readers = [r for r in self.consumers.get(cur, ()) if not isinstance(r, ViewOp)]
+                # (a SequentialOp only orders: it reads nothing)
+                readers = [r for r in self.consumers.get(cur, ())
+                           if not isinstance(r, (ViewOp, SequentialOp))]
                 if len(readers) != 1 or cur in self.returned:
                     break
                 nxt = readers[0]
@@ -1223,6 +1346,10 @@ class B200Transformer(object):
         self._inputs_written = []
         self._allreduce = None      # exchange state of the computation that ran last
         self._recording = False     # a CUDA graph segment is being recorded
+        self.tracer = None
+        self._io_done = False       # the replayed graph has already queued the call's read-back
+        self._stats_clean = False   # ... and left the statistics array cleared
+        self._flex_epoch = 0        # moves whenever any exponent bookkeeping may have changed
         self._buffers = collections.OrderedDict()   # op -> Buffer
         self._views = {}
         self.finalized = False
@@ -1246,6 +1373,14 @@ class B200Transformer(object):
         self._status = None
         self._table = None
         self._stats = None
+        # TRACING=1: a Chrome-trace timeline of every launch (see tracing.py)
+        self.tracer = None
+        if tracing.is_tracing_enabled():
+            self.tracer = tracing.TraceEventTracker(
+                kwargs.pop("trace_name", "b200_trace_dev%d_%d" % (self.device_id, id(self) & 0xffff)))
+            self._trace_base = torch.cuda.Event(enable_timing=True)
+            self._trace_base.record(torch.cuda.current_stream(self.device))
+            self._trace_calls = 0
 
     @property
     def stream(self):
@@ -1275,10 +1410,23 @@ class B200Transformer(object):
         for c in self.computations:
             c.build()
 
+    def _collect_trace(self, comp, pairs):
+        """After the call's synchronisation: one 'X' event per step (device time, microseconds
+        since the transformer was made)."""
+        self._trace_calls += 1
+        for step, e0, e1 in pairs:
+            self.tracer.add_operation(
+                step.kind, tracing.step_name(step), self.device_id, 0,
+                round(self._trace_base.elapsed_time(e0) * 1e3, 3),
+                round(e0.elapsed_time(e1) * 1e3, 3),
+                {"call": self._trace_calls, "step": step.index, "launches": step.launches})
+
     def close(self):
         if self.closed:
             return
         self.closed = True
+        if getattr(self, "tracer", None) is not None and self.tracer.events:
+            self.tracer.serialize_to_file()
         self._buffers.clear()
         self._views.clear()
         self._scratch = self._table = self._stats = self._status = self._probe64 = None
@@ -1641,6 +1789,8 @@ class B200Transformer(object):
 
     # ---- flex bookkeeping ------------------------------------------------------------------------
     def _set_table_row(self, slot, dec):
+        self._flex_epoch += 1
+        self._stats_clean = False
         self._dec_uploaded[slot] = dec
         self._table_np[slot, 0] = 2.0 ** -dec
         self._table_np[slot, 1] = 2.0 ** dec
@@ -1649,6 +1799,7 @@ class B200Transformer(object):
     def _set_table_row_host(self, slot, dec):
         """Updates the pinned copy of a table row; the device copy follows in one transfer."""
         if self._dec_uploaded.get(slot) != dec:
+            self._flex_epoch += 1
             self._dec_uploaded[slot] = dec
             self._table_np[slot, 0] = math.ldexp(1.0, -dec)
             self._table_np[slot, 1] = math.ldexp(1.0, dec)
@@ -1663,6 +1814,16 @@ class B200Transformer(object):
             return
         self.flex_manager.autoflex_count += 1
         self._inputs_written = []
+        steady = getattr(comp, "_steady", None)
+        if steady is not None and steady[0] == self._flex_epoch and not self._table_dirty:
+            # Steady state: the previous call of this computation left every exponent where it
+            # was and nothing has touched the bookkeeping since, so no row of the table can move.
+            if self._stats_clean:
+                self._stats_clean = False
+            else:
+                self._stats.zero_()
+            return
+        comp._steady = None
         # Only tensors this computation writes (or receives from the host) can adopt a new exponent
         # here; every other tensor's table rows were brought up to date by the call that wrote it.
         bufs = getattr(comp, "_flex_bufs", None)
@@ -1689,14 +1850,20 @@ class B200Transformer(object):
         if self._table_dirty:
             self._table.copy_(self._table_host, non_blocking=True)
             self._table_dirty = False
-        self._stats.zero_()
+        if self._stats_clean:
+            self._stats_clean = False
+        else:
+            self._stats.zero_()
 
     def _end_call(self, comp):
         """One synchronisation per call: statistics and status come back together."""
         torch = self.torch
-        self._status_host.copy_(self._status, non_blocking=True)
-        if self.flex:
-            self._stats_host.copy_(self._stats, non_blocking=True)
+        if self._io_done:
+            self._io_done = False          # the replayed graph ended with these copies
+        else:
+            self._status_host.copy_(self._status, non_blocking=True)
+            if self.flex:
+                self._stats_host.copy_(self._stats, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         for b in comp.written:
             b.version += 1
@@ -1706,10 +1873,25 @@ class B200Transformer(object):
         if not self.flex:
             return
         stats = self._stats_host.numpy()
+        steady = getattr(comp, "_steady", None)
+        if steady is not None and steady[0] == self._flex_epoch and \
+                len(self._inputs_written) == steady[3] and np.array_equal(stats[steady[1]], steady[2]):
+            # the same maxima as after the previous call, with every history window already full
+            # of them: every entry would make the choice it made before
+            return
+        self._flex_epoch += 1
         for b in self._inputs_written:
             b.entry.end_write(int(stats[b.slot]))
         for b in comp.written:
             b.entry.end_write(int(stats[b.slot_write]))
+        entries = [b.entry for b in self._inputs_written] + [b.entry for b in comp.written]
+        if all(e.fixed_point or (e._run_length > flexmod.HISTORY_LEN and
+                                 e.pending_dec in (None, e.dec)) for e in entries):
+            idx = np.array([b.slot for b in self._inputs_written] +
+                           [b.slot_write for b in comp.written], dtype=np.int64)
+            comp._steady = (self._flex_epoch, idx, stats[idx].copy(), len(self._inputs_written))
+        else:
+            comp._steady = None
 
     # ---- launching -------------------------------------------------------------------------------
     def _launch_step(self, step):

@@ -220,3 +220,37 @@ def test_gemm_f32_benchmark_sizes(n):
         np.testing.assert_allclose(got, expect, rtol=1e-4, atol=1e-5 * np.sqrt(n) * 4,
                                    err_msg=layout)
         del dA, dB
+
+
+def test_bounded_wait_runs_out_and_reports():
+    """A device-side wait that nothing completes gives up after its poll limit, sets the status
+    word and lets the kernel end normally (tensor memory freed): the library's self-test runs that
+    path with the tile kernels' own wait routine on a barrier nobody arrives at.  Afterwards the
+    context is as usable as before -- a GEMM on the same stream is exact -- and a transformer
+    turns a non-zero status word into an error for that call, then clears it."""
+    import torch
+    import ngraph_python_b200 as ng
+    from ngraph_python_b200 import lib
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    waited = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    lib.check(lib.raw().b2_selftest_bounded_wait(300, status.data_ptr(), waited.data_ptr(), 0))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1 and int(waited.item()) == 300
+    with pytest.raises(lib.B200Error, match="poll limit"):
+        lib.check(lib.raw().b2_selftest_bounded_wait(0, status.data_ptr(), None, 0))
+    # the tensor cores and tensor memory are as before
+    M_, K_, N_ = [ng.make_axis(n, name=nm) for n, nm in ((128, "M"), (256, "K"), (128, "N"))]
+    a, b = ng.placeholder([M_, K_]), ng.placeholder([K_, N_])
+    t = ng.transformers.allocate_transformer("b200")
+    comp = t.computation(ng.dot(a, b), a, b)
+    rng = np.random.RandomState(1)
+    av = rng.randint(-8, 8, (128, 256)).astype(np.float32)
+    bv = rng.randint(-8, 8, (256, 128)).astype(np.float32)
+    assert np.array_equal(comp(av, bv), av @ bv)
+    # what a computation does when one of its kernels reports a wait that ran out
+    lib.check(lib.raw().b2_selftest_bounded_wait(50, t._status.data_ptr(), None,
+                                                 t.stream.cuda_stream))
+    with pytest.raises(lib.B200Error, match="device-side wait ran out"):
+        comp(av, bv)
+    assert np.array_equal(comp(av, bv), av @ bv)       # the word was cleared; the next call is fine
+    t.close()

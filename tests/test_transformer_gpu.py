@@ -246,3 +246,31 @@ def test_device_tensor_get_slice_and_assign(flex):
     with pytest.raises(ValueError):
         dt[2:5, :, 3] = np.zeros((9, 3), np.float32)
     t.close()
+
+
+def test_tracing_writes_a_chrome_trace(tmp_path, monkeypatch):
+    """TRACING=1 (the reference's switch, ngraph/util/trace_events.py:21-23): every step of every
+    call becomes an 'X' event with a device timestamp and duration, written as Chrome-trace JSON
+    when the transformer closes; results are those of an untraced run."""
+    import json
+    outs, params, vals = cases.CASES["resnet8_small"](ng)
+    plain = ng.transformers.allocate_transformer("b200")
+    want = [np.array(r, copy=True) for r in plain.computation(outs, *params)(*vals)]
+    plain.close()
+    monkeypatch.setenv("TRACING", "1")
+    name = str(tmp_path / "trace")
+    outs, params, vals = cases.CASES["resnet8_small"](ng)
+    t = ng.transformers.allocate_transformer("b200", trace_name=name)
+    comp = t.computation(outs, *params)
+    for _ in range(2):
+        got = comp(*vals)
+    n_steps = len(comp.steps)
+    t.close()
+    for g_, w_ in zip(got, want):
+        assert np.array_equal(g_, w_)
+    trace = json.load(open(name + ".json"))["traceEvents"]
+    assert len(trace) == 2 * n_steps
+    assert all(e["ph"] == "X" and e["dur"] > 0 and e["ts"] >= 0 for e in trace)
+    assert {e["cat"] for e in trace} >= {"conv", "ew", "gemm"}
+    ts = [e["ts"] for e in trace]
+    assert ts == sorted(ts)
