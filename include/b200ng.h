@@ -173,6 +173,14 @@ int b2_flex_dequantize(const int16_t* src, float* dst, int64_t n, const b2_flex_
 /* *out = max(*out, bit pattern of max |src[i]|) (NaN counts as 0); used to pick a first exponent
  * for data arriving from the host. */
 int b2_absmax_bits_f32(const float* src, int64_t n, int32_t* out, void* stream);
+/* End of a call in one launch: host_stats[i] = stats[i], stats[i] = 0 for i < n, and
+ * *host_status = *status (both NULL to skip).  host_stats / host_status are pinned host memory
+ * that the device can address (cudaHostAlloc memory under unified addressing); the values are
+ * there once the stream has been synchronised.  Replaces the per-kernel synchronous statistics
+ * read of the reference's flex transformer (manage_after_computation after every kernel,
+ * ngraph/transformers/flexgputransform.py:347-371) by one read per call. */
+int b2_flex_publish(int32_t* stats, int32_t n, const int32_t* status, int32_t* host_stats,
+                    int32_t* host_status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Dense GEMM on tcgen05 tensor cores: C[M,N] = op(A)[M,K] * op(B)[K,N], C row-major (ldc).

@@ -81,6 +81,17 @@ class TorchDistComm(object):
         return _Pending(work, flat, self.size if reduce_func == "mean" else 1)
 
 
+    def all_gather_host(self, array, axis):
+        """Host arrays of all replicas joined along `axis` (every replica gets the whole)."""
+        import torch
+        t = torch.from_numpy(np.ascontiguousarray(array))
+        if self.dist.get_backend(self.group) == "nccl":
+            t = t.cuda()
+        parts = [torch.empty_like(t) for _ in range(self.size)]
+        self.dist.all_gather(parts, t, group=self.group)
+        return np.concatenate([p.cpu().numpy() for p in parts], axis=axis)
+
+
 class _Pending(object):
     def __init__(self, work, flat, divisor):
         self.work, self.flat, self.divisor = work, flat, divisor
@@ -111,6 +122,10 @@ class SingleProcessComm(object):
         if reduce_func not in ("sum", "mean"):
             raise ValueError("unsupported reduce_func %r" % (reduce_func,))
         return _Done()
+
+
+    def all_gather_host(self, array, axis):
+        return array
 
 
 class _Done(object):

@@ -132,6 +132,7 @@ def _load():
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),
+        "b2_flex_publish": (C.c_int, [vp, i32, vp, vp, vp, vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)

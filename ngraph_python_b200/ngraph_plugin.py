@@ -71,6 +71,24 @@ def _reduce_tag(op):
         return None
 
 
+def _find_parallel_axis(computation_op):
+    """The axis named by `parallel=` in the metadata of the graph's ops (hetr's device
+    annotation: `with ng.metadata(device='gpu', device_id=('0', '1'), parallel=ax.N)`), or None."""
+    seen, stack = set(), [computation_op]
+    while stack:
+        op = stack.pop()
+        if op in seen:
+            continue
+        seen.add(op)
+        axis = op.metadata.get("parallel") if hasattr(op, "metadata") else None
+        if axis is not None:
+            return axis
+        stack.extend(op.all_deps)
+        if isinstance(op, ref.ValueOp):
+            stack.append(op.value_tensor)
+    return None
+
+
 class GraphTranslator(object):
     """reference Op -> ngraph_python_b200 Op, memoised.
 
@@ -84,13 +102,37 @@ class GraphTranslator(object):
     is then also divided by the number of replicas, which makes it the division by the global
     batch size the reference performs."""
 
-    def __init__(self, replicas=1, shard_batch=True):
+    def __init__(self, replicas=1, shard_batch=True, parallel_axis=None, rank=0):
         self.memo = {}
         self.bare = {}       # AssignableTensorOp -> its translation (shared with memo)
         self.axis_memo = {}
         self.replicas = int(replicas)
         self.shard_batch = bool(shard_batch)
         self.exchanges = {}  # tagged reference op -> its allreduce
+        # hetr-style graphs: built on the GLOBAL batch under ng.metadata(device_id=(...),
+        # parallel=axis); every replica runs the same graph with that axis cut to its share
+        # (what hetr's DeviceAssignPass / scatter does, ngraph/transformers/passes/hetrpasses.py:
+        # 98-131, ngraph/op_graph/comm_nodes.py:180-215)
+        self.parallel_axis = parallel_axis
+        self.rank = int(rank)
+
+    def set_parallel_axis(self, axis):
+        if axis is None or self.replicas <= 1:
+            return
+        if self.parallel_axis is not None and (self.parallel_axis.name != axis.name or
+                                               self.parallel_axis.length != axis.length):
+            raise ValueError("computations of one transformer must agree on the parallel axis")
+        if axis.length % self.replicas:
+            raise ValueError("the parallel axis {} does not divide over {} replicas"
+                             .format(axis, self.replicas))
+        if self.parallel_axis is None and self.axis_memo:
+            raise ValueError("the parallel axis must be known before the first translation")
+        self.parallel_axis = axis
+        self.shard_batch = False     # the graph's batch size is the global one already
+
+    def is_parallel(self, a):
+        p = self.parallel_axis
+        return p is not None and a.name == p.name and a.length == p.length
 
     def axis(self, a):
         if getattr(a, "is_flattened", False):
@@ -99,9 +141,10 @@ class GraphTranslator(object):
             name = "flat(" + ",".join(self.axis(m).name for m in a.axes) + ")"
         else:
             name = a.name
+        length = a.length // self.replicas if self.is_parallel(a) else a.length
         key = (name, a.length)
         if key not in self.axis_memo:
-            self.axis_memo[key] = b2.make_axis(a.length, name=name)
+            self.axis_memo[key] = b2.make_axis(length, name=name)
         return self.axis_memo[key]
 
     def axes(self, axes):
@@ -166,6 +209,13 @@ class GraphTranslator(object):
                       is_placeholder=op.is_placeholder, name=op.name)
             if init is not None and not callable(init):
                 init = np.asarray(init, dtype=np.float32)
+                for pos, a in enumerate(op.axes):
+                    # a tensor initialised along the parallel axis: this replica's share of it
+                    if self.is_parallel(a) and init.ndim == len(op.axes) and \
+                            init.shape[pos] == a.length:
+                        share = a.length // self.replicas
+                        init = np.take(init, range(self.rank * share, (self.rank + 1) * share),
+                                       axis=pos)
             return b2.AssignableTensorOp(self.axes(op.axes), init, **kw)
         if isinstance(op, ref.SequentialOp):
             return b2.sequential([self(o) for o in op.ops])
@@ -273,6 +323,8 @@ class _PluginComputation(object):
         self.computation_op = computation_op
         tr = transformer.translator
         returns = computation_op.returns
+        if tr.replicas > 1:
+            tr.set_parallel_axis(_find_parallel_axis(computation_op))
         self.dict_keys = None
         if isinstance(returns, dict):
             self.dict_keys = list(returns.keys())
@@ -288,17 +340,56 @@ class _PluginComputation(object):
         params = [tr(p.tensor) for p in self.parameters]
         self.impl = transformer.impl.computation(outs, *params)
         self.returns = returns
+        # position of the parallel axis in every parameter that has it: the caller passes the
+        # global array, this replica takes its slice (hetr's scatter)
+        self.scatter = [next((i for i, a in enumerate(p.tensor.axes) if tr.is_parallel(a)), None)
+                        for p in self.parameters]
+
+    def _gather(self, res):
+        """Results that carry the parallel axis, put together from all replicas along it."""
+        tr = self.transformer.translator
+        comm = self.transformer.impl.comm
+        ops = _result_ops(self.returns)
+        single = isinstance(self.returns, ref.Op)
+        vals = [res] if single else list(res)
+        out = []
+        for op, v in zip(ops, vals):
+            pos = next((i for i, a in enumerate(op.axes) if tr.is_parallel(a)), None)
+            out.append(v if pos is None else comm.all_gather_host(np.asarray(v), pos))
+        return out[0] if single else tuple(out)
 
     def __call__(self, *args, **kwargs):
         feed = kwargs.pop("feed_dict", None)
         if feed is not None:
             args = [feed[p.tensor] if p.tensor in feed else feed[p] for p in self.parameters]
+        tr = self.transformer.translator
+        if tr.parallel_axis is not None:
+            rank, n = self.transformer.impl.comm.rank, tr.replicas
+            cut = []
+            for a, pos in zip(args, self.scatter):
+                if pos is not None and np.ndim(a) > pos and np.shape(a)[pos] == tr.parallel_axis.length:
+                    share = np.shape(a)[pos] // n
+                    index = [slice(None)] * np.ndim(a)
+                    index[pos] = slice(rank * share, (rank + 1) * share)
+                    a = np.ascontiguousarray(np.asarray(a)[tuple(index)])
+                cut.append(a)
+            args = cut
         res = self.impl(*args)
+        if tr.parallel_axis is not None and self.transformer.gather_results:
+            res = self._gather(res)
         if self.dict_keys is not None:
             return dict(zip(self.dict_keys, res))
         if isinstance(self.returns, ref.Op) or self.returns is None:
             return res
         return self.container(res) if self.container in (tuple, list) else tuple(res)
+
+
+def _result_ops(returns):
+    if isinstance(returns, dict):
+        return [returns[k] for k in returns]
+    if isinstance(returns, ref.Op):
+        return [returns]
+    return list(returns) if returns is not None else []
 
 
 class B200NgraphTransformer(Transformer):
@@ -311,12 +402,17 @@ class B200NgraphTransformer(Transformer):
     def __init__(self, **kwargs):
         # the reference base class expects no unknown keyword arguments
         shard_batch = kwargs.pop("shard_batch", True)
+        # hetr-style graphs only: results that carry the parallel axis come back whole on every
+        # replica (hetr gathers them to the host, ngraph/op_graph/comm_nodes.py: GatherRecvOp)
+        gather_results = kwargs.pop("gather_results", True)
         if os.environ.get("B200NG_PLAN_ONLY") == "1":
             # plan and compile only (no device needed): lets the reference's own tests exercise
             # translation and planning on a machine without a GPU; calls then raise
             kwargs.setdefault("plan_only", True)
         self.impl = b2t.B200Transformer(**kwargs)
-        self.translator = GraphTranslator(replicas=self.impl.comm.size, shard_batch=shard_batch)
+        self.translator = GraphTranslator(replicas=self.impl.comm.size, shard_batch=shard_batch,
+                                          rank=self.impl.comm.rank)
+        self.gather_results = bool(gather_results)
         self.computations = []
         self.finalized = False
         self._counts_as_flex = bool(self.impl.flex)

@@ -239,9 +239,19 @@ class AssignableTensorOp(Op):
         self.is_placeholder = is_placeholder
         if initial_value is not None and not callable(initial_value):
             initial_value = np.asarray(initial_value, dtype=np.float32)
-            if initial_value.shape not in ((), self.axes.lengths):
-                raise ValueError("initial value shape %s does not match axes %s" %
-                                 (initial_value.shape, self.axes))
+            lengths = tuple(self.axes.lengths)
+            if initial_value.shape not in ((), lengths):
+                # the same elements up to axes of length 1, or a value that numpy broadcasts to
+                # the axes (the reference hands initial values to numpy the same way)
+                if tuple(n for n in initial_value.shape if n != 1) == \
+                        tuple(n for n in lengths if n != 1):
+                    initial_value = initial_value.reshape(lengths)
+                else:
+                    try:
+                        initial_value = np.ascontiguousarray(np.broadcast_to(initial_value, lengths))
+                    except ValueError:
+                        raise ValueError("initial value shape %s does not match axes %s" %
+                                         (initial_value.shape, self.axes))
         self.initial_value = initial_value
 
     @property

@@ -311,10 +311,7 @@ class Computation(object):
                         # the call's read-back rides in the graph: status word and flex
                         # statistics to pinned host memory, then the statistics cleared for the
                         # next call -- one graph launch and one synchronisation per call
-                        t._status_host.copy_(t._status, non_blocking=True)
-                        if t.flex:
-                            t._stats_host.copy_(t._stats, non_blocking=True)
-                            t._stats.zero_()
+                        t._publish()
                         io_in_graph = True
                 seg["graph"] = g
         finally:
@@ -1855,15 +1852,24 @@ class B200Transformer(object):
         else:
             self._stats.zero_()
 
+    def _publish(self):
+        """Status word and flex statistics into pinned host memory, statistics cleared: one
+        small launch (lib: b2_flex_publish)."""
+        n = self._stats.numel() if self.flex else 0
+        lib.check(lib.raw().b2_flex_publish(
+            self._stats.data_ptr() if self.flex else None, n, self._status.data_ptr(),
+            self._stats_host.data_ptr() if self.flex else None, self._status_host.data_ptr(),
+            self.stream.cuda_stream))
+        self.kernel_launches += 1
+
     def _end_call(self, comp):
         """One synchronisation per call: statistics and status come back together."""
         torch = self.torch
         if self._io_done:
-            self._io_done = False          # the replayed graph ended with these copies
+            self._io_done = False          # the replayed graph ended with the read-back
         else:
-            self._status_host.copy_(self._status, non_blocking=True)
-            if self.flex:
-                self._stats_host.copy_(self._stats, non_blocking=True)
+            self._publish()
+            self._stats_clean = self.flex
         torch.cuda.current_stream(self.device).synchronize()
         for b in comp.written:
             b.version += 1

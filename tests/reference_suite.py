@@ -1,6 +1,7 @@
 """Runs the reference's own transformer-dependent tests against a transformer of choice.
 
-    python tests/reference_suite.py --transformer b200 [--report FILE] [-k expr] [pytest args]
+    python tests/reference_suite.py --transformer b200 [--report FILE] [--marker EXPR]
+                                    [directories of the reference tree] [-k expr] [pytest args]
 
 The tests are the reference's, untouched (tests/transformer_dependent, frontends/neon/tests and
 frontends/common/tests of the tree that oracle/ref_env.py finds); the marker expression is the one its
@@ -55,7 +56,7 @@ def pytest_runtest_logreport(report):
 def main(argv):
     if REF is None:
         sys.exit("no reference tree: run oracle/make_ref.py first")
-    transformer, report = "b200", None
+    transformer, report, marker_arg = "b200", None, None
     rest = []
     it = iter(argv)
     for a in it:
@@ -63,6 +64,8 @@ def main(argv):
             transformer = next(it)
         elif a == "--report":
             report = os.path.abspath(next(it))
+        elif a == "--marker":
+            marker_arg = next(it)
         else:
             rest.append(a)
     targets = [a for a in rest if not a.startswith("-") and os.path.exists(os.path.join(REF, a))]
@@ -70,6 +73,8 @@ def main(argv):
     if not targets:
         targets = [os.path.join("tests", "transformer_dependent")]
     marker = "transformer_dependent and not flex_only and not hetr_only and not hetr_gpu_only"
+    if marker_arg is not None:          # e.g. --marker "not hetr_only and not flex_only"
+        marker = marker_arg
     args = ["-p", "tests.reference_suite", "--rootdir", REF, "-c", os.path.join(REF, "pytest.ini"),
             "--transformer", transformer, "-m", marker, "-q", "-W", "ignore",
             "-o", "cache_dir=/tmp/b200ng_ref_suite_cache"] + rest + \

@@ -271,3 +271,99 @@ def test_gradient_exchange_is_inserted_from_reduce_func_tags():
     mean_loss = np.mean([got[r][0] for r in range(world)], axis=0)
     np.testing.assert_allclose(mean_loss, want, rtol=2e-5)
     assert want[-1] < want[0]
+
+
+def _hetr_style_model(global_n):
+    """The way hetr scripts annotate a data-parallel graph: built on the GLOBAL batch, everything
+    under ng.metadata(device_id=(...), parallel=ax.N)."""
+    from ngraph.frontends.neon import (Sequential, Affine, Rectlin, Softmax, GaussianInit,
+                                       ConstantInit, GradientDescentMomentum, ax)
+    ax.N.length = global_n
+    ax.Y.length = 10
+    F = rng.make_axis(24, name="F")
+    with rng.metadata(device="gpu", device_id=("0", "1"), parallel=ax.N):
+        x = rng.placeholder([F, ax.N])
+        t = rng.placeholder([ax.N])
+        np.random.seed(6)
+        init = GaussianInit(0., 0.2)
+        model = Sequential([
+            Affine(weight_init=init, bias_init=ConstantInit(0.), activation=Rectlin(), nout=16),
+            Affine(weight_init=init, bias_init=ConstantInit(0.), activation=Softmax(), axes=(ax.Y,))])
+        probs = model(x)
+        loss = rng.cross_entropy_multi(probs, rng.one_hot(t, axis=ax.Y))
+        updates = GradientDescentMomentum(0.1, 0.9)(loss)
+        train = rng.sequential([updates, probs])
+    return train, x, t
+
+
+def _hetr_rank(rank, world, port, global_n, steps, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        train, x, t = _hetr_style_model(global_n)
+        tr = plugin.GraphTranslator(replicas=world, rank=rank)
+        tr.set_parallel_axis(plugin._find_parallel_axis(rng.computation(train, x, t)))
+        m_train, m_x, m_t = tr(train), tr(x), tr(t)
+        assert m_x.axes.lengths == (24, global_n // world)
+
+        def allreduce(arr, func):
+            buf = torch.from_numpy(arr.copy())
+            dist.all_reduce(buf)
+            return buf.numpy() / (world if func == "mean" else 1)
+        it = Interp(allreduce=allreduce)
+        rs = np.random.RandomState(9)
+        xv = rs.standard_normal((24, global_n)).astype(np.float32)
+        tv = rs.randint(0, 10, global_n).astype(np.float32)
+        n = global_n // world
+        lo, hi = rank * n, (rank + 1) * n
+        outs = [np.asarray(it.run([m_train], {m_x: xv[:, lo:hi], m_t: tv[lo:hi]})[0])
+                for _ in range(steps)]
+        q.put((rank, outs, sorted(set(e.reduce_func for e in tr.exchanges.values()))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_hetr_style_graph_runs_as_shards():
+    """A graph annotated for hetr -- global batch, ng.metadata(device_id=(...), parallel=ax.N) --
+    is cut along the parallel axis per replica: placeholders shrink to the replica's share,
+    gradients are summed over the replicas (the optimizer already divides by the global batch)
+    and the replicas' outputs, put side by side, are the reference CPU transformer's on the whole
+    batch, step after step."""
+    import socket
+    import torch.multiprocessing as mp
+    global_n, steps, world = 16, 3, 2
+    train, x, t = _hetr_style_model(global_n)
+    assert plugin._find_parallel_axis(rng.computation(train, x, t)).length == global_n
+    cpu = ngt.make_transformer_factory("cpu")()
+    cref = cpu.computation(train, x, t)
+    rs = np.random.RandomState(9)
+    xv = rs.standard_normal((24, global_n)).astype(np.float32)
+    tv = rs.randint(0, 10, global_n).astype(np.float32)
+    want = [np.array(cref(xv, tv), copy=True) for _ in range(steps)]
+    cpu.close()
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_hetr_rank, args=(r, world, port, global_n, steps, q))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        got = dict((r, (o, f)) for r, o, f in (q.get(timeout=300) for _ in range(world)))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    assert got[0][1] == ["sum"] and got[1][1] == ["sum"]
+    for k in range(steps):
+        whole = np.concatenate([got[0][0][k], got[1][0][k]], axis=1)
+        np.testing.assert_allclose(whole, want[k], rtol=2e-5, atol=1e-6)
