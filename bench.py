@@ -674,12 +674,17 @@ class ResnetTraining(object):
 
 def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats, with_e2e=True):
     """Times one training step; returns the fields of a bench line (rank 0) or None."""
-    from ngraph_python_b200.comm import TorchDistComm, SingleProcessComm
+    from ngraph_python_b200.comm import NcclComm, TorchDistComm, SingleProcessComm
     gn = args.global_batch
     if gn % world or (gn // world) % 128:
         raise SystemExit("global batch must give every GPU a multiple of 128 images")
     n = gn // world
-    comm = TorchDistComm() if dist is not None else SingleProcessComm()
+    if dist is None:
+        comm = SingleProcessComm()
+    elif args.comm == "torch":
+        comm = TorchDistComm()
+    else:
+        comm = NcclComm.from_torch_distributed(local)     # the library's own b2_comm_* group
     job = ResnetTraining(torch, local, flex, gn, rank, world, comm, args.bucket_bytes, lr=args.lr)
     t, comp, host = job.t, job.comp, job.host
     losses = [float(job.call(*host)) for _ in range(3)]
@@ -736,6 +741,9 @@ def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats
             def all_reduce_async(self, flat, reduce_func="sum"):
                 exchanged.append(int(flat.numel()))
                 return real.all_reduce_async(flat, reduce_func)
+
+            def __getattr__(self, name):
+                return getattr(real, name)
         ar.comm = Spy()
         step_resident()
         torch.cuda.synchronize()
@@ -777,6 +785,7 @@ def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats
                    "optimizer": "momentum 0.9 + Kahan, lr %g" % args.lr,
                    "network": frontend,
                    "parallelism": "dp%d" % world, "allreduce_buckets": buckets,
+                   "exchange": type(comm).__name__,
                    "bucket_bytes": t.bucket_bytes, "steps_per_pass": n_steps,
                    "cuda_graph": graphed,
                    "l2": "each step streams >126 MB of activations, gradients and operand planes"},
@@ -1299,13 +1308,19 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="default workload only: leave out configurations 2, 3 and 5")
     ap.add_argument("--lr", type=float, default=0.1, help="learning rate (training workloads)")
+    ap.add_argument("--comm", default="b2", choices=["b2", "torch"],
+                    help="gradient exchange through the library's NCCL group or torch.distributed")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch kernel by kernel instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    # whatever the libraries print on the way goes to stderr: stdout carries the one JSON line
+    # whatever the libraries print on the way (NCCL writes its version to file descriptor 1) goes
+    # to stderr: stdout carries the one JSON line
+    sys.stdout.flush()
+    real_fd = os.dup(1)
+    os.dup2(2, 1)
     out, sys.stdout = sys.stdout, sys.stderr
     try:
         if args.impl == "reference":
@@ -1314,6 +1329,8 @@ def main():
             line = run_b200(args, rank, world)
     finally:
         sys.stdout = out
+        os.dup2(real_fd, 1)
+        os.close(real_fd)
     if line is not None:
         print(json.dumps(line))
         sys.stdout.flush()

@@ -371,6 +371,35 @@ int b2_lut_update(const void* delta, const void* idx, void* dW, int32_t flex, in
                   uint64_t* probe_out, int32_t probe, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Gradient allreduce over NCCL (NVLink / NVSwitch), one process per GPU.
+ * Replaces: CudaAllReduceKernel and its reduction kernel (ngraph/transformers/gpu/tensor_ops.py:
+ * 52-116, 416-618), which reduce one gradient tensor at a time with peer-to-peer copies, MPI
+ * barriers and host synchronisations.  The caller reduces a whole bucket of fp32 gradients in
+ * place, on the stream it names.  NCCL is loaded at run time (the copy already in the process if
+ * there is one); without it these entry points return B2_ERR_UNAVAILABLE and the rest of the
+ * library is unaffected.
+ *   b2_comm_unique_id   one replica makes the 128-byte identifier and hands it to the others
+ *                       (any channel: a file, a socket, torch.distributed's store)
+ *   b2_comm_init        every replica joins (collective: returns once all have called it)
+ *   b2_comm_allreduce_f32  buf[0..count) <- sum over replicas, / nranks when mean != 0; queued on
+ *                       `stream`, returns at once
+ *   b2_comm_poll_error  B2_OK, or B2_ERR_COMM once NCCL has reported an asynchronous failure (a
+ *                       replica that died, a link fault); never blocks
+ *   b2_comm_abort       ends the collectives in flight after a failure so that a stream
+ *                       synchronisation returns; the handle can then only be destroyed
+ * ------------------------------------------------------------------------------------------ */
+#define B2_COMM_ID_BYTES 128
+typedef struct b2_comm b2_comm;
+int b2_set_nccl_path(const char* path);
+int b2_comm_version(int32_t* version);
+int b2_comm_unique_id(void* id_out);
+int b2_comm_init(const void* id, int32_t rank, int32_t nranks, int32_t device, b2_comm** out);
+int b2_comm_allreduce_f32(b2_comm* comm, float* buf, int64_t count, int32_t mean, void* stream);
+int b2_comm_poll_error(b2_comm* comm);
+int b2_comm_abort(b2_comm* comm);
+int b2_comm_destroy(b2_comm* comm);
+
+/* ------------------------------------------------------------------------------------------
  * Self-test of the bounded-wait path.  Every device-side wait of the tile kernels gives up after
  * a fixed number of polls, sets the caller's status word to 1 (the launching entry point's
  * `status` argument; the host then reports B2_ERR_TIMEOUT-class failure for that call) and lets

@@ -8,7 +8,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200ng.so")
 
 SOURCES = ["b2_api.cu", "b2_ew_codegen.cu", "b2_flex.cu", "b2_gemm.cu", "b2_conv.cu",
-           "b2_dimshuffle.cu", "b2_rng.cu"]
+           "b2_dimshuffle.cu", "b2_rng.cu", "b2_comm.cu"]
 
 
 def _embed_device_header():

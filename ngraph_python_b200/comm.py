@@ -15,9 +15,20 @@ kernel (tensor_ops.py:95-108).
 
 One process per GPU; the process group is created by the caller (torchrun) and handed in.
 """
+import datetime
+import time
+
 import numpy as np
 
+
+class CommError(RuntimeError):
+    """A collective failed or did not finish within its time limit (B2_ERR_COMM of the C ABI's
+    error codes): a peer raised, left, or never joined.  The exchange state of the call is
+    undefined afterwards; the computation's weights have not been updated with a partial sum."""
+
+
 DEFAULT_BUCKET_BYTES = 25 * 1024 * 1024
+DEFAULT_TIMEOUT_S = 120.0
 ALIGN_ELEMS = 64          # every tensor starts on a 256-byte boundary inside the arena
 
 
@@ -56,7 +67,9 @@ class BucketPlan(object):
 class TorchDistComm(object):
     """Thin wrapper over an initialised torch.distributed process group."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, timeout_s=DEFAULT_TIMEOUT_S):
+        """timeout_s: how long a collective may take before the wait gives up with CommError
+        (a replica that raised or left never joins; without a limit the others wait for ever)."""
         import torch.distributed as dist
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised: launch one process per GPU "
@@ -65,6 +78,7 @@ class TorchDistComm(object):
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
+        self.timeout_s = float(timeout_s)
 
     def Get_rank(self):          # the reference passes an mpi4py-style comm (hetrtransform.py:38-57)
         return self.rank
@@ -78,7 +92,7 @@ class TorchDistComm(object):
             raise ValueError("unsupported reduce_func %r" % (reduce_func,))
         work = self.dist.all_reduce(flat, op=self.dist.ReduceOp.SUM, group=self.group,
                                     async_op=True)
-        return _Pending(work, flat, self.size if reduce_func == "mean" else 1)
+        return _Pending(work, flat, self.size if reduce_func == "mean" else 1, self.timeout_s)
 
 
     def all_gather_host(self, array, axis):
@@ -93,18 +107,139 @@ class TorchDistComm(object):
 
 
 class _Pending(object):
-    def __init__(self, work, flat, divisor):
+    def __init__(self, work, flat, divisor, timeout_s=DEFAULT_TIMEOUT_S):
         self.work, self.flat, self.divisor = work, flat, divisor
+        self.timeout_s = timeout_s
         self.done = False
 
+    def poll_error(self):
+        """Raises CommError if the collective has failed so far; True once it has completed."""
+        try:
+            finished = self.work.is_completed()
+            exc = self.work.exception() if finished else None
+        except RuntimeError as e:                     # the backend reports the failure by raising
+            raise CommError("collective failed: %s" % e)
+        if exc is not None:
+            raise CommError("collective failed: %s" % (exc,))
+        return finished
+
     def wait(self):
-        """Makes the current stream wait for the collective (does not block the host on GPUs)."""
+        """Makes the current stream wait for the collective (does not block the host on GPUs; on
+        CPU tensors the host waits, at most timeout_s)."""
         if self.done:
             return
-        self.work.wait()
+        try:
+            if self.flat.is_cuda:
+                # the device-side wait is queued; completion is checked, with the time limit, by
+                # BucketedAllReduce.finish before the call's stream synchronisation
+                self.work.wait()
+            else:
+                self.work.wait(datetime.timedelta(seconds=self.timeout_s))
+        except RuntimeError as e:
+            raise CommError("collective did not complete: %s" % e)
         if self.divisor != 1:
             self.flat.div_(self.divisor)
         self.done = True
+
+
+class NcclComm(object):
+    """The library's own communicator (C ABI: b2_comm_*): one NCCL communicator per process,
+    collectives on a communication stream of its own, ordered against the compute stream by
+    events, asynchronous NCCL errors polled instead of waited for.
+
+    The 128-byte identifier made by replica 0 has to reach the others once; `exchange` is any
+    callable (bytes or None) -> bytes that does that.  `from_torch_distributed` uses an already
+    initialised torch.distributed group (any backend) for it."""
+
+    def __init__(self, rank, size, device, exchange, timeout_s=DEFAULT_TIMEOUT_S):
+        import ctypes as C
+        import torch
+        from . import lib
+        self.lib, self.torch = lib, torch
+        self.rank, self.size, self.device = int(rank), int(size), int(device)
+        self.timeout_s = float(timeout_s)
+        raw = lib.raw()
+        ident = C.create_string_buffer(128)
+        if self.rank == 0:
+            lib.check(raw.b2_comm_unique_id(ident))
+        blob = exchange(bytes(ident.raw) if self.rank == 0 else None)
+        handle = C.c_void_p()
+        torch.cuda.set_device(self.device)
+        lib.check(raw.b2_comm_init(C.create_string_buffer(blob, 128), self.rank, self.size,
+                                   self.device, C.byref(handle)))
+        self.handle = handle
+        self.stream = torch.cuda.Stream(device=self.device)
+
+    @classmethod
+    def from_torch_distributed(cls, device, group=None, timeout_s=DEFAULT_TIMEOUT_S):
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+
+        def exchange(blob):
+            box = [blob]
+            dist.broadcast_object_list(box, src=0, group=group)
+            return box[0]
+        return cls(dist.get_rank(group), dist.get_world_size(group), device, exchange, timeout_s)
+
+    def Get_rank(self):
+        return self.rank
+
+    def Get_size(self):
+        return self.size
+
+    def all_reduce_async(self, flat, reduce_func="sum"):
+        if reduce_func not in ("sum", "mean"):
+            raise ValueError("unsupported reduce_func %r" % (reduce_func,))
+        torch = self.torch
+        cur = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        self.stream.wait_event(ready)          # the bucket's producers have run
+        rc = self.lib.raw().b2_comm_allreduce_f32(self.handle, flat.data_ptr(), flat.numel(),
+                                                  int(reduce_func == "mean"),
+                                                  self.stream.cuda_stream)
+        if rc < 0:
+            raise CommError(self.lib.raw().b2_last_error().decode(errors="replace"))
+        done = torch.cuda.Event()
+        done.record(self.stream)
+        return _NcclPending(self, done)
+
+    def poll_error(self):
+        rc = self.lib.raw().b2_comm_poll_error(self.handle)
+        if rc < 0:
+            raise CommError(self.lib.raw().b2_last_error().decode(errors="replace"))
+
+    def all_gather_host(self, array, axis):
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            raise RuntimeError("gathering results needs torch.distributed")
+        return TorchDistComm(timeout_s=self.timeout_s).all_gather_host(array, axis)
+
+    def abort(self):
+        self.lib.raw().b2_comm_abort(self.handle)
+
+    def close(self):
+        if self.handle is not None:
+            self.lib.raw().b2_comm_destroy(self.handle)
+            self.handle = None
+
+
+class _NcclPending(object):
+    def __init__(self, comm, done):
+        self.comm, self.done_event = comm, done
+        self.timeout_s = comm.timeout_s
+        self.waited = False
+
+    def wait(self):
+        """The current stream waits for the collective; the host does not."""
+        if not self.waited:
+            self.comm.torch.cuda.current_stream(self.comm.device).wait_event(self.done_event)
+            self.waited = True
+
+    def poll_error(self):
+        self.comm.poll_error()
+        return self.done_event.query()
 
 
 class SingleProcessComm(object):
@@ -182,6 +317,22 @@ class BucketedAllReduce(object):
     def bucket_ready(self, index):
         """All tensors of bucket `index` have been produced: exchange what is left of it."""
         self.flush(index)
+
+    def finish(self, timeout_s=None):
+        """Before the call's stream synchronisation: every collective started in this call must
+        complete within the time limit, else CommError (a synchronisation on a stream that waits
+        for a collective nobody else joins would never return)."""
+        handles = [h for bucket in self.pending for _, _, h in bucket if hasattr(h, "poll_error")]
+        if not handles:
+            return
+        limit = handles[0].timeout_s if timeout_s is None else timeout_s
+        deadline = time.monotonic() + limit
+        for h in handles:
+            while not h.poll_error():
+                if time.monotonic() > deadline:
+                    raise CommError("a collective did not complete within %.1f s: a replica "
+                                    "has failed or left" % limit)
+                time.sleep(0.0002)
 
     def wait_for(self, key):
         """Called before the first consumer of the reduced tensor `key`.  A tensor that another

@@ -129,6 +129,14 @@ def _load():
         "b2_rng_fill": (C.c_int, [vp, i32, i64, i32, C.c_float, C.c_float, C.c_uint64, C.c_uint64,
                                   vp, vp, i32, vp, vp, i32, vp]),
         "b2_selftest_bounded_wait": (C.c_int, [i32, vp, vp, vp]),
+        "b2_set_nccl_path": (C.c_int, [C.c_char_p]),
+        "b2_comm_version": (C.c_int, [C.POINTER(i32)]),
+        "b2_comm_unique_id": (C.c_int, [vp]),
+        "b2_comm_init": (C.c_int, [vp, i32, i32, i32, C.POINTER(vp)]),
+        "b2_comm_allreduce_f32": (C.c_int, [vp, vp, i64, i32, vp]),
+        "b2_comm_poll_error": (C.c_int, [vp]),
+        "b2_comm_abort": (C.c_int, [vp]),
+        "b2_comm_destroy": (C.c_int, [vp]),
         "b2_flex_host_quantize": (C.c_int, [vp, vp, i64, vp, i32, vp, vp]),
         "b2_flex_dequantize": (C.c_int, [vp, vp, i64, vp, i32, vp]),
         "b2_absmax_bits_f32": (C.c_int, [vp, i64, vp, vp]),
@@ -169,6 +177,22 @@ if not os.path.exists("/usr/local/cuda/lib64/libnvrtc.so.12"):
     _d = _find_nvrtc_dir()
     if _d:
         _lib.b2_set_nvrtc_path(_d.encode())
+
+
+def _find_nccl_dir():
+    try:
+        import nvidia.nccl as m  # wheel bundled with torch
+        d = os.path.join(list(m.__path__)[0], "lib")
+        if os.path.exists(os.path.join(d, "libnccl.so.2")):
+            return d
+    except Exception:
+        pass
+    return None
+
+
+_d = _find_nccl_dir()
+if _d:
+    _lib.b2_set_nccl_path(_d.encode())
 
 
 def make_program(dims, inputs, consts, ops, outs, reds, reduce_mode):

@@ -467,13 +467,14 @@ class _Planner(object):
         if not self.t.fuse:
             return ordered
         returned = set(self._base_tensor(r)[0] for r in returns)
+        # (a SequentialOp that merely lists an op orders it, it does not read it: the op may
+        # run later as long as what it reads cannot change, which is checked below)
         readers = collections.defaultdict(list)
         for op in ordered:
+            if isinstance(op, SequentialOp):
+                continue
             for a in op.args:
                 readers[self._base_tensor(a)[0]].append(op)
-            if isinstance(op, SequentialOp):
-                for o in op.ops:
-                    readers[self._base_tensor(o)[0]].append(op)
         held = collections.defaultdict(list)      # reader -> ops to emit right before it
         for op in ordered:
             if not isinstance(op, ElementWiseOp) or op in returned or op.opname == "assign":
@@ -689,7 +690,28 @@ class _Planner(object):
             return False
         if len(g.stored) + 1 > fusion.MAX_OUT - 1:      # one spare for a later outside consumer
             return False
+        if self._prospective_outputs(g, op) > fusion.MAX_OUT:
+            return False
         return True
+
+    def _prospective_outputs(self, g, op):
+        """How many values the kernel would have to store if `op` joined it now: assignments,
+        reductions, returned values, and values read outside the kernel (a reader that has not
+        been placed yet counts as outside, which errs on the safe side)."""
+        members = list(g.members) + [op]
+        inside = set(members)
+        count = 0
+        for m in members:
+            if isinstance(m, (AssignOp, ReductionOp)) or m in self.returned:
+                count += 1
+                continue
+            for c in self.consumers.get(m, ()):
+                direct = any(self._base_tensor(a)[0] is m and not self._base_tensor(a)[1]
+                             for a in c.args)
+                if c not in inside or not direct:
+                    count += 1
+                    break
+        return count
 
     def _place_allreduce(self, op):
         """fp32: the producer's buffer is placed in the communication arena and reduced in
@@ -1870,6 +1892,8 @@ class B200Transformer(object):
         else:
             self._publish()
             self._stats_clean = self.flex
+        if self._allreduce is not None and self.comm.size > 1:
+            self._allreduce.finish()        # CommError instead of an endless synchronisation
         torch.cuda.current_stream(self.device).synchronize()
         for b in comp.written:
             b.version += 1

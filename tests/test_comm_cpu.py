@@ -103,3 +103,56 @@ def test_single_process_comm_is_identity():
     assert torch.equal(x, torch.arange(8, dtype=torch.float32))
     with pytest.raises(ValueError):
         comm.all_reduce_async(x, "max")
+
+
+def _leaver(rank, world, port, out):
+    """Rank 1 leaves between two exchanges (on the host, with nothing in flight); rank 0's next
+    collective must end with CommError within its time limit instead of waiting for ever."""
+    import time
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    comm = C.TorchDistComm(timeout_s=3.0)
+    plan = C.BucketPlan([("g", 256)])
+    arena = torch.ones(plan.total, dtype=torch.float32)
+    ar = C.BucketedAllReduce(comm, plan, arena, {"g": "sum"})
+    ar.begin_call()
+    ar.produced("g")
+    ar.bucket_ready(0)
+    ar.wait_for("g")                       # first step: both ranks take part
+    ok_first = bool(torch.all(arena[:256] == 2.0))
+    if rank == 1:
+        out.put(("left", ok_first, 0.0))
+        return                             # leaves without a word (no destroy, no second step)
+    t0 = time.monotonic()
+    try:
+        ar.begin_call()
+        ar.produced("g")
+        ar.bucket_ready(0)
+        ar.wait_for("g")
+        ar.finish()
+        out.put(("no error", ok_first, time.monotonic() - t0))
+    except C.CommError as e:
+        out.put(("CommError", ok_first, time.monotonic() - t0))
+
+
+def test_a_replica_that_leaves_ends_the_exchange_with_an_error():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        got = [q.get(timeout=120) for _ in range(world)]
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
+    by = dict((g[0], g) for g in got)
+    assert "left" in by and by["left"][1]
+    assert "CommError" in by, got
+    assert by["CommError"][1] and by["CommError"][2] < 60.0

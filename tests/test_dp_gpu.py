@@ -107,7 +107,7 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, world, port, flex, case, capture, q):
+def _rank_main(rank, world, port, flex, case, capture, q, comm_kind="torch"):
     import datetime
     import traceback
     import torch
@@ -125,10 +125,11 @@ def _rank_main(rank, world, port, flex, case, capture, q):
         q.put((rank, "error", traceback.format_exc()))
         return
     try:
-        from ngraph_python_b200.comm import TorchDistComm
+        from ngraph_python_b200.comm import NcclComm, TorchDistComm
         outs, params, vals = cases.CASES[case](ng, shard=(rank, world))
+        comm = TorchDistComm() if comm_kind == "torch" else NcclComm.from_torch_distributed(rank)
         t = ng.transformers.allocate_transformer("b200", device_id=rank, flex=flex,
-                                                 comm=TorchDistComm(), bucket_bytes=8192)
+                                                 comm=comm, bucket_bytes=8192)
         comp = t.computation(outs, *params)
         results = [[np.array(r, copy=True) for r in comp(*vals)]]
         if capture:
@@ -152,6 +153,17 @@ def _rank_main(rank, world, port, flex, case, capture, q):
 @pytest.mark.parametrize("case", TRAIN_CASES)
 @pytest.mark.parametrize("flex", [False, True])
 def test_train_step_two_gpus(flex, case, capture):
+    _two_gpu_step(flex, case, capture, "torch")
+
+
+@pytest.mark.parametrize("capture", [False, True])
+@pytest.mark.parametrize("flex", [False, True])
+def test_train_step_two_gpus_through_the_library_comm(flex, capture):
+    """The same step with the gradient exchange on the C ABI's own NCCL group (b2_comm_*)."""
+    _two_gpu_step(flex, "resnet_train_step", capture, "b2")
+
+
+def _two_gpu_step(flex, case, capture, comm_kind):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -160,7 +172,8 @@ def test_train_step_two_gpus(flex, case, capture):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, flex, case, capture, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, flex, case, capture, q, comm_kind))
+             for r in range(2)]
     for p in procs:
         p.start()
     got = {}
