@@ -634,12 +634,15 @@ class ResnetTraining(object):
     through the plug-in (which places the gradient exchange where the reference's passes would,
     from the gradients' reduce_func tags).  Without: this package's hand-differentiated graph."""
 
-    def __init__(self, torch, local, flex, global_n, rank, world, comm, bucket_bytes, lr):
+    def __init__(self, torch, local, flex, global_n, rank, world, comm, bucket_bytes, lr,
+                 min_buckets=0):
         n = global_n // world
         fe = reference_frontend()
         kw = dict(device_id=local, flex=flex, comm=comm)
         if bucket_bytes:
             kw["bucket_bytes"] = bucket_bytes
+        if min_buckets:
+            kw["min_buckets"] = min_buckets
         r = np.random.RandomState(3)
         labels = r.randint(0, 10, global_n)
         lo, hi = rank * n, (rank + 1) * n
@@ -685,12 +688,14 @@ def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats
         comm = TorchDistComm()
     else:
         comm = NcclComm.from_torch_distributed(local)     # the library's own b2_comm_* group
-    job = ResnetTraining(torch, local, flex, gn, rank, world, comm, args.bucket_bytes, lr=args.lr)
+    job = ResnetTraining(torch, local, flex, gn, rank, world, comm, args.bucket_bytes, lr=args.lr,
+                         min_buckets=args.min_buckets)
     t, comp, host = job.t, job.comp, job.host
     losses = [float(job.call(*host)) for _ in range(3)]
     graphed = False
     if not args.no_graph:
-        comp.capture()          # graphs between the NCCL exchanges (one graph on a single GPU)
+        comp.capture()          # one graph per step, the NCCL exchanges inside it (--comm torch:
+                                # graphs between the exchanges)
         graphed = True
     timer = Timer(torch, dist)
 
@@ -734,32 +739,22 @@ def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats
         # collectives alone, back to back, (3) the step with the collectives left out; exposed
         # time = step - step without exchange.  Done last: (3) lets the replicas drift apart.
         ar, real = t._allreduce, t._allreduce.comm
-
-        class Spy(object):
-            rank, size = real.rank, real.size
-
-            def all_reduce_async(self, flat, reduce_func="sum"):
-                exchanged.append(int(flat.numel()))
-                return real.all_reduce_async(flat, reduce_func)
-
-            def __getattr__(self, name):
-                return getattr(real, name)
-        ar.comm = Spy()
         step_resident()
         torch.cuda.synchronize()
-        per_step = list(exchanged)
-        bufs = [torch.zeros(c, dtype=torch.float32, device="cuda") for c in per_step]
+        exchanged = [int(c) for c in ar.last_sizes]       # elements of every collective of a step
+        bufs = [torch.zeros(c, dtype=torch.float32, device="cuda") for c in exchanged]
 
         def collectives_alone():
             for b in bufs:
-                dist.all_reduce(b)
+                real.all_reduce_async(b, "mean").wait()
         timer.loops(collectives_alone, 3, 1)
         alone_ms = statistics.median(timer.loops(collectives_alone, 20, 3)) / 20
         ar.comm = SingleProcessComm()
+        if graphed:
+            comp.capture()                                 # the same step list without exchanges
         timer.loops(step_resident, 3, 1)
         nocomm_ms = statistics.median(timer.loops(step_resident, steps, repeats)) / steps
         ar.comm = real
-        exchanged = per_step
     buckets = len(t._allreduce.plan.buckets) if t._allreduce is not None else 0
     n_steps = len(comp.steps)
     frontend = job.frontend
@@ -1298,6 +1293,8 @@ def main():
                     help="images per training step over all GPUs (training workloads)")
     ap.add_argument("--bucket-bytes", type=int, default=0,
                     help="upper bound of an allreduce bucket (0: the library's default)")
+    ap.add_argument("--min-buckets", type=int, default=0,
+                    help="lower bound on the buckets of a step (0: the library's default, 4)")
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the GEMM workloads")
     ap.add_argument("--batch", type=int, default=RESNET_N, help="images per GPU (ResNet-20)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])

@@ -116,9 +116,18 @@ class _Pending(object):
         """Raises CommError if the collective has failed so far; True once it has completed."""
         try:
             finished = self.work.is_completed()
-            exc = self.work.exception() if finished else None
         except RuntimeError as e:                     # the backend reports the failure by raising
             raise CommError("collective failed: %s" % e)
+        exc = None
+        if finished:
+            try:
+                exc = self.work.exception()
+            except RuntimeError as e:
+                raise CommError("collective failed: %s" % e)
+            except TypeError:
+                # the NCCL backend's work object cannot hand its (empty) exception slot to
+                # Python; a failed NCCL collective raises from is_completed / wait instead
+                exc = None
         if exc is not None:
             raise CommError("collective failed: %s" % (exc,))
         return finished
@@ -150,6 +159,7 @@ class NcclComm(object):
     The 128-byte identifier made by replica 0 has to reach the others once; `exchange` is any
     callable (bytes or None) -> bytes that does that.  `from_torch_distributed` uses an already
     initialised torch.distributed group (any backend) for it."""
+    capturable = True      # its collectives may be recorded into a CUDA graph with the step list
 
     def __init__(self, rank, size, device, exchange, timeout_s=DEFAULT_TIMEOUT_S):
         import ctypes as C
@@ -288,9 +298,12 @@ class BucketedAllReduce(object):
                 nxt = plan.offsets[keys[i + 1]] if i + 1 < len(keys) else end
                 self.sizes[k] = nxt - plan.offsets[k]
         self.started = 0
+        self.last_sizes = []
         self.begin_call()
 
     def begin_call(self):
+        self._sizes_now = []
+        self.graph_handle = None
         self.pending = [[] for _ in self.plan.buckets]          # (start, end, handle)
         self.launched_upto = [b[0] for b in self.plan.buckets]
         self.produced_upto = [b[0] for b in self.plan.buckets]
@@ -311,6 +324,8 @@ class BucketedAllReduce(object):
             raise ValueError("tensors exchanged together must share a reduce_func")
         self.pending[b].append((start, end,
                                 self.comm.all_reduce_async(self.arena[start:end], funcs.pop())))
+        self._sizes_now.append(end - start)
+        self.last_sizes = self._sizes_now       # elements per collective of the last exchanging call
         self.launched_upto[b] = end
         self.started += 1
 
@@ -318,21 +333,38 @@ class BucketedAllReduce(object):
         """All tensors of bucket `index` have been produced: exchange what is left of it."""
         self.flush(index)
 
+    def join_all(self):
+        """The current stream waits for every collective started in this call (the end of a CUDA
+        graph recording: all forked streams have to be back)."""
+        for bucket in self.pending:
+            for _, _, handle in bucket:
+                handle.wait()
+
+    def graph_launched(self, stream):
+        """A replayed graph held this call's collectives: `finish` watches an event behind it."""
+        event = self.comm.torch.cuda.Event()
+        event.record(stream)
+        self.graph_handle = _NcclPending(self.comm, event)
+
     def finish(self, timeout_s=None):
         """Before the call's stream synchronisation: every collective started in this call must
         complete within the time limit, else CommError (a synchronisation on a stream that waits
         for a collective nobody else joins would never return)."""
         handles = [h for bucket in self.pending for _, _, h in bucket if hasattr(h, "poll_error")]
+        if self.graph_handle is not None:
+            handles.append(self.graph_handle)
         if not handles:
             return
         limit = handles[0].timeout_s if timeout_s is None else timeout_s
-        deadline = time.monotonic() + limit
+        start = time.monotonic()
         for h in handles:
             while not h.poll_error():
-                if time.monotonic() > deadline:
+                waited = time.monotonic() - start
+                if waited > limit:
                     raise CommError("a collective did not complete within %.1f s: a replica "
                                     "has failed or left" % limit)
-                time.sleep(0.0002)
+                if waited > 0.05:
+                    time.sleep(0.0005)      # a healthy step ends within the spinning phase
 
     def wait_for(self, key):
         """Called before the first consumer of the reduced tensor `key`.  A tensor that another

@@ -252,10 +252,14 @@ class Computation(object):
         instead of one launch (plus tensor-map encoding) per kernel.  Call after the computation
         has run at least once, so that flex exponents exist and every kernel variant is compiled;
         flex scales live in a device table, so a replay picks up exponent changes.
-        With several replicas the NCCL exchanges stay outside the graphs: the step list is cut
-        into segments at every point where a bucket is handed to NCCL or a reduced tensor is first
-        needed, each segment is one graph, and the collectives are issued between the replays
-        exactly where the step-by-step executor issues them."""
+        With several replicas and a communicator whose collectives can be recorded (the library's
+        own NCCL group) the exchanges are nodes of the same graph: the communication stream forks
+        from the recording stream where a bucket closes and joins it again before the bucket's
+        first reader, so a training step is still ONE graph launch.  With any other communicator
+        (torch.distributed) the exchanges stay outside: the step list is cut into segments at
+        every point where a bucket is handed over or a reduced tensor is first needed, each
+        segment is one graph, and the collectives are issued between the replays exactly where
+        the step-by-step executor issues them."""
         t = self.transformer
         if self.steps is None or t.plan_only:
             raise lib.B200Error("run the computation once before capturing it")
@@ -263,7 +267,11 @@ class Computation(object):
             raise lib.B200Error("run the computation once before capturing it")
         torch = t.torch
         refreshable = [s for s in self.steps if hasattr(s, "refresh")]
-        has_comm = any(s.kind == "comm" for s in self.steps) and t.comm.size > 1
+        ar = self._allreduce
+        has_comm = any(s.kind == "comm" for s in self.steps) and ar is not None and ar.comm.size > 1
+        in_graph = has_comm and getattr(ar.comm, "capturable", False)
+        if in_graph:
+            has_comm = False             # one segment; the comm steps issue their collectives
         # -- segments ---------------------------------------------------------------------------
         segments, cur, made_here = [], None, set()
 
@@ -307,6 +315,8 @@ class Computation(object):
                 with torch.cuda.graph(g):
                     for s in seg["steps"]:
                         t._launch_step(s)
+                    if in_graph:
+                        ar.join_all()    # every forked stream is back before the recording ends
                     if seg is segments[-1]:
                         # the call's read-back rides in the graph: status word and flex
                         # statistics to pinned host memory, then the statistics cleared for the
@@ -318,7 +328,6 @@ class Computation(object):
             t._recording = False
         per_call = t.kernel_launches - before
         self._graphs = [seg["graph"] for seg in segments]
-        ar = t._allreduce
 
         def replay():
             for s in refreshable:
@@ -332,6 +341,8 @@ class Computation(object):
                     ar.produced(cs.key)
                     if cs.closes_bucket is not None:
                         ar.bucket_ready(cs.closes_bucket)
+            if in_graph:
+                ar.graph_launched(t.stream)
             t.kernel_launches += per_call
             if io_in_graph:
                 t._io_done = True

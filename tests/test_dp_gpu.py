@@ -133,7 +133,10 @@ def _rank_main(rank, world, port, flex, case, capture, q, comm_kind="torch"):
         comp = t.computation(outs, *params)
         results = [[np.array(r, copy=True) for r in comp(*vals)]]
         if capture:
-            comp.capture()      # graphs between the NCCL exchanges; the second step replays them
+            comp.capture()      # the second step replays the recorded graph(s)
+            if comm_kind == "b2":
+                # the library's collectives are nodes of the one graph of the step
+                assert len([g for g in comp._graphs if g is not None]) == 1
         results.append([np.array(r, copy=True) for r in comp(*vals)])
         q.put((rank, "ok", results))
         dist.barrier()
