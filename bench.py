@@ -63,8 +63,10 @@ INT8_DATASHEET_TOPS = 4500.0
 # of a quarter-size launch (2048 rows): see profiles/ew_c2_flex16.md and profiles/ew_c2_fp32.md
 NCU_TRAFFIC_BYTES = {"c2_flex16": 4 * (268457728 + 39549952), "c2_fp32": 4 * (536940544 + 107399680)}
 # the same two counters summed over the 22 convolution launches of one batch-256 flex16 pass
-# (profiles/conv_resnet20_flex16.md); None until a capture of the current kernel is on file
-NCU_CONV_TRAFFIC_BYTES = {"resnet20_flex16": None}
+# (profiles/conv_resnet20_flex16.md).  ncu flushes the caches before every launch it measures, so
+# this counts as DRAM reads what the real sequence finds in L2, and no write reaches DRAM within
+# its launch: an upper bound on the reads of the timed pass, not its traffic to the byte.
+NCU_CONV_TRAFFIC_BYTES = {"resnet20_flex16": 154123008}
 
 RESNET_N = 256
 # algorithmic figures per 256-image batch: 21.03 GFLOP; minimal layer I/O of the 22 convolutions

@@ -1064,10 +1064,12 @@ cudaError_t launch_main(const void* func, dim3 grid, void** params, size_t dyn, 
 }
 }  // namespace
 
-extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const* out,
-                            const float* consts, const b2_flex_scale* flex_table,
-                            int32_t* flex_stats, void* scratch, size_t scratch_bytes,
-                            int32_t* status, int probe, void* stream) {
+// What both launch entry points share: argument checks and the choice between the vector and the
+// scalar variant (decided by the pointers' alignment), then the argument block and the launches.
+namespace {
+int check_launch(const b2_ew_kernel* k, const void* const* in, void* const* out,
+                 const float* consts, const b2_flex_scale* flex_table, const int32_t* flex_stats,
+                 int* vec_out) {
     B2_REQUIRE(k && (in || k->prog.n_in == 0) && out, "null argument");
     const b2_ew_program& p = k->prog;
     const int nres = p.n_out + p.n_red;
@@ -1085,16 +1087,24 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
     }
     if (any_flex) B2_REQUIRE(flex_table && flex_stats, "flex tensors need a scale table and stats");
     B2_REQUIRE(p.n_const == 0 || consts, "constants missing");
-    const unsigned fresh_mask = probe > 0 ? (unsigned)probe >> 1 : 0u;
-    probe = probe ? 1 : 0;
-    int rc = ensure_variant(k, vec, probe);
-    if (rc) return rc;
+    *vec_out = vec;
+    return B2_OK;
+}
+
+size_t scratch_need(const b2_ew_kernel* k, int vec) {
     const Plan& pl = k->plan[vec];
-    if (pl.nsplit > 1) {
-        const size_t need = (size_t)pl.nsplit * (size_t)(p.A * p.B) * (size_t)p.n_red * sizeof(float);
-        B2_REQUIRE(scratch && scratch_bytes >= need,
-                   "split reduction needs %zu bytes of scratch, got %zu", need, scratch_bytes);
-    }
+    const b2_ew_program& p = k->prog;
+    return pl.nsplit > 1
+        ? (size_t)pl.nsplit * (size_t)(p.A * p.B) * (size_t)p.n_red * sizeof(float) : 0;
+}
+
+int launch_variant(const b2_ew_kernel* k, int vec, const Module* m, const void* const* in,
+                   void* const* out, const float* consts, const b2_flex_scale* flex_table,
+                   int32_t* flex_stats, void* scratch, int32_t* status, unsigned fresh_mask,
+                   void* stream) {
+    const b2_ew_program& p = k->prog;
+    const Plan& pl = k->plan[vec];
+    const int nres = p.n_out + p.n_red;
     EwArgs a;
     memset(&a, 0, sizeof(a));
     a.A = p.A; a.B = p.B; a.C = p.C;
@@ -1117,7 +1127,6 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
     a.nsplit = pl.nsplit;
     a.fresh_mask = fresh_mask;
     void* params[] = {&a};
-    Module* m = k->mod[vec][probe];
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t dyn = pl.staged ? (size_t)pl.stages * pl.stage_bytes : 0;
     B2_CUDA(launch_main((const void*)m->main, pl.grid, params, dyn, st));
@@ -1127,6 +1136,25 @@ extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const*
         B2_CUDA(cudaLaunchKernel((const void*)m->finalize, g, dim3(kThreads), params, 0, st));
     }
     return B2_OK;
+}
+}  // namespace
+
+extern "C" int b2_ew_launch(b2_ew_kernel* k, const void* const* in, void* const* out,
+                            const float* consts, const b2_flex_scale* flex_table,
+                            int32_t* flex_stats, void* scratch, size_t scratch_bytes,
+                            int32_t* status, int probe, void* stream) {
+    int vec = 0;
+    int rc = check_launch(k, in, out, consts, flex_table, flex_stats, &vec);
+    if (rc) return rc;
+    const unsigned fresh_mask = probe > 0 ? (unsigned)probe >> 1 : 0u;
+    probe = probe ? 1 : 0;
+    rc = ensure_variant(k, vec, probe);
+    if (rc) return rc;
+    const size_t need = scratch_need(k, vec);
+    B2_REQUIRE(need == 0 || (scratch && scratch_bytes >= need),
+               "split reduction needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+    return launch_variant(k, vec, k->mod[vec][probe], in, out, consts, flex_table, flex_stats,
+                          scratch, status, fresh_mask, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1184,68 +1212,23 @@ extern "C" int b2_ew_launch_builtin_scratch(b2_ew_kernel* k, const void* const* 
                                             void* const* out, const float* consts,
                                             const b2_flex_scale* flex_table, int32_t* flex_stats,
                                             int32_t* status, int probe, void* stream) {
-    B2_REQUIRE(k && (in || k->prog.n_in == 0) && out, "null argument");
-    const b2_ew_program& p = k->prog;
-    const int nres = p.n_out + p.n_red;
-    bool any_flex = false;
-    int vec = k->can_vec ? 1 : 0;
-    for (int i = 0; i < p.n_in; ++i) {
-        B2_REQUIRE(in[i], "input %d is null", i);
-        any_flex |= p.in[i].dtype == B2_FLEX16;
-        if (vec && p.in[i].sc == 1 && !aligned16(in[i])) vec = 0;
-    }
-    for (int q = 0; q < nres; ++q) {
-        B2_REQUIRE(out[q], "result %d is null", q);
-        any_flex |= is_flex(p.out[q].t.dtype);
-        if (vec && q < p.n_out && !aligned16(out[q])) vec = 0;
-    }
-    if (any_flex) B2_REQUIRE(flex_table && flex_stats, "flex tensors need a scale table and stats");
-    B2_REQUIRE(p.n_const == 0 || consts, "constants missing");
+    int vec = 0;
+    int rc = check_launch(k, in, out, consts, flex_table, flex_stats, &vec);
+    if (rc) return rc;
     const unsigned fresh_mask = probe > 0 ? (unsigned)probe >> 1 : 0u;
     probe = probe ? 1 : 0;
-    Module* m = k->mod[vec][probe];
+    const Module* m = k->mod[vec][probe];
     B2_REQUIRE(m != nullptr,
                "this kernel variant (vector=%d, probe=%d) has not been compiled yet; the "
                "no-allocation launch never compiles or loads code -- run b2_ew_launch once with "
                "the same kind of pointers first", vec, probe);
-    const Plan& pl = k->plan[vec];
-    const size_t need = pl.nsplit > 1
-        ? (size_t)pl.nsplit * (size_t)(p.A * p.B) * (size_t)p.n_red * sizeof(float) : 0;
+    const size_t need = scratch_need(k, vec);
     B2_REQUIRE(need <= (size_t)B2_EW_BUILTIN_SCRATCH_BYTES,
                "this launch needs %zu bytes of scratch but the built-in scratch holds %zu; use "
                "b2_ew_launch with a caller buffer", need, (size_t)B2_EW_BUILTIN_SCRATCH_BYTES);
     void* scratch = nullptr;
-    int rc = builtin_scratch_for_current_device(&scratch);
+    rc = builtin_scratch_for_current_device(&scratch);
     if (rc) return rc;
-    EwArgs a;
-    memset(&a, 0, sizeof(a));
-    a.A = p.A; a.B = p.B; a.C = p.C;
-    for (int i = 0; i < p.n_in; ++i) {
-        a.in[i] = in[i];
-        a.in_sa[i] = p.in[i].sa; a.in_sb[i] = p.in[i].sb; a.in_sc[i] = p.in[i].sc;
-        a.in_slot[i] = p.in[i].flex_slot;
-    }
-    for (int q = 0; q < nres; ++q) {
-        a.out[q] = out[q];
-        a.out_sa[q] = p.out[q].t.sa; a.out_sb[q] = p.out[q].t.sb; a.out_sc[q] = p.out[q].t.sc;
-        a.out_slot[q] = p.out[q].t.flex_slot;
-        a.out_plane[q] = p.out[q].t.plane_bytes;
-    }
-    for (int i = 0; i < p.n_const; ++i) a.consts[i] = consts[i];
-    a.flex_table = flex_table;
-    a.flex_stats = flex_stats;
-    a.scratch = static_cast<float*>(scratch);
-    a.status = status;
-    a.nsplit = pl.nsplit;
-    a.fresh_mask = fresh_mask;
-    void* params[] = {&a};
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t dyn = pl.staged ? (size_t)pl.stages * pl.stage_bytes : 0;
-    B2_CUDA(launch_main((const void*)m->main, pl.grid, params, dyn, st));
-    if (pl.nsplit > 1) {
-        const long long rows = p.A * p.B;
-        dim3 g((unsigned)((rows + kThreads - 1) / kThreads));
-        B2_CUDA(cudaLaunchKernel((const void*)m->finalize, g, dim3(kThreads), params, 0, st));
-    }
-    return B2_OK;
+    return launch_variant(k, vec, m, in, out, consts, flex_table, flex_stats, scratch, status,
+                          fresh_mask, stream);
 }

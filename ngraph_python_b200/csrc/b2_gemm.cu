@@ -1,6 +1,16 @@
 // C-ABI entry points of the dense GEMM (the kernels and their launch helpers are in
 // b2_gemm_impl.cuh, which the convolution entry points share).
+#define B2_GEMM_OWNS_TILE_KERNEL
 #include "b2_gemm_impl.cuh"
+
+int b2_gemm_launch_on_planes(int mode, unsigned char* base, const void* shapes, const void* params,
+                             cudaStream_t st, int splits, void* workspace) {
+    const Shapes& s = *static_cast<const Shapes*>(shapes);
+    const GemmParams& p = *static_cast<const GemmParams*>(params);
+    return mode == MODE_FLEX16
+        ? launch_on_planes<MODE_FLEX16>(base, s, p, st, splits, workspace)
+        : launch_on_planes<MODE_F32X3>(base, s, p, st, splits, workspace);
+}
 
 extern "C" int b2_gemm_scratch_bytes(int32_t flex, int32_t M, int32_t N, int32_t K, size_t* bytes) {
     B2_REQUIRE(bytes && M > 0 && N > 0 && K > 0, "bad argument");

@@ -47,6 +47,14 @@
 
 #include "b2_common.h"
 
+// The tile kernel is compiled once, in the translation unit that defines B2_GEMM_OWNS_TILE_KERNEL
+// (b2_gemm.cu); every other includer reaches it through this function.  Shapes and GemmParams
+// live in this header's unnamed namespace -- each translation unit has its own, identical, type --
+// so they cross the boundary as untyped pointers.
+__attribute__((visibility("hidden")))
+int b2_gemm_launch_on_planes(int mode, unsigned char* base, const void* shapes, const void* params,
+                             cudaStream_t st, int splits, void* workspace);
+
 namespace {
 
 constexpr int kBlockM = 128;          // UMMA M; the N tile (16/32/64/128) is a template parameter
@@ -879,6 +887,7 @@ Shapes shapes_for(int mode, int M, int N, int K) {
     return s;
 }
 
+#ifdef B2_GEMM_OWNS_TILE_KERNEL
 template <int MODE, int BN>
 int launch_tile(const CUtensorMap& mA0, const CUtensorMap& mA1, const CUtensorMap& mB0,
                 const CUtensorMap& mB1, const GemmParams& p, const Shapes& s, int splits,
@@ -894,6 +903,8 @@ int launch_tile(const CUtensorMap& mA0, const CUtensorMap& mA1, const CUtensorMa
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }
+
+#endif
 
 // bytes of split-K workspace for `splits` slices (0 when the GEMM runs in one slice)
 inline size_t splitk_bytes(int mode, const Shapes& s, int splits) {
@@ -924,6 +935,7 @@ inline size_t gemm_scratch_need(int mode, const Shapes& s) {
 // Launches the tile kernel on operand planes that are already in scratch:
 // A planes at `base`, B planes behind them.  With splits > 1, `workspace` (splitk_bytes) receives
 // the slices and a finishing kernel writes C.
+#ifdef B2_GEMM_OWNS_TILE_KERNEL
 template <int MODE>
 int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStream_t st,
                      int splits = 1, void* workspace = nullptr) {
@@ -959,6 +971,13 @@ int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStr
     B2_CUDA(cudaGetLastError());
     return B2_OK;
 }
+#else
+template <int MODE>
+int launch_on_planes(unsigned char* base, const Shapes& s, GemmParams p, cudaStream_t st,
+                     int splits = 1, void* workspace = nullptr) {
+    return b2_gemm_launch_on_planes(MODE, base, &s, &p, st, splits, workspace);
+}
+#endif
 
 // A flex16 product far smaller than one wave of tensor-core tiles (the 10 x 64 x 256 classifier
 // of a small network): one thread per result, exact int64 sum, the tile kernel's rescale -- one

@@ -345,6 +345,11 @@ class _PluginComputation(object):
         self.scatter = [next((i for i, a in enumerate(p.tensor.axes) if tr.is_parallel(a)), None)
                         for p in self.parameters]
 
+    def capture(self):
+        """Replays the computation as one CUDA graph from now on (call it after a first run)."""
+        self.impl.capture()
+        return self
+
     def _gather(self, res):
         """Results that carry the parallel axis, put together from all replicas along it."""
         tr = self.transformer.translator
@@ -474,3 +479,27 @@ class B200NgraphTransformer(Transformer):
 
     def device_to_host(self, computation, op, tensor=None):
         pass
+
+
+class B200FlexNgraphTransformer(B200NgraphTransformer):
+    """`make_transformer_factory('b200flex')`: flex16 storage with the reference flex
+    transformer's own granularity -- every op's result is stored, and therefore quantised, as
+    FlexGPUTransformer does with one kernel per op (flexgputransform.py:67-103) -- so that the
+    reference's flex tests (tests/flex_tests, marker flex_only), whose expected values are exact
+    mantissa-level facts of that granularity, run against it unchanged.  'b200' with flex=True is
+    the same storage with fused kernels (intermediate values stay fp32)."""
+
+    transformer_name = "b200flex"
+    default_rtol = 1e-02
+
+    def __init__(self, fixed_point=False, flex_verbose=False, collect_flex_data=False, **kwargs):
+        kwargs.setdefault("flex", True)
+        kwargs.setdefault("fuse", False)
+        kwargs.update(fixed_point=fixed_point, flex_verbose=flex_verbose)
+        super(B200FlexNgraphTransformer, self).__init__(**kwargs)
+
+    @classmethod
+    def get_default_tolerance(cls, desired):
+        from . import flex as flexmod
+        scale = flexmod.flex16.get_scale(float(np.max(np.abs(desired))))
+        return scale * 8, 1e-2

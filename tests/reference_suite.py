@@ -30,9 +30,110 @@ if REF is not None:
     import ngraph_python_b200.ngraph_plugin  # noqa: E402,F401
 
 
+class _LegacyParam(object):
+    """A parameter value with a mark on it, written the way pytest 3 allowed --
+    `pytest.config.flex_disabled(value)` inside a parametrize list -- until the number of argument
+    names is known (one name: the value is the parameter; several: it is the tuple of them)."""
+
+    def __init__(self, value, mark):
+        self.value, self.mark = value, mark
+
+    def to_param(self, n_names):
+        if n_names == 1:
+            return pytest.param(self.value, marks=self.mark)
+        return pytest.param(*self.value, marks=self.mark)
+
+
+class _LegacyMark(object):
+    """The mark objects the reference's conftest hangs on `pytest.config` (flex_disabled,
+    argon_disabled, ...), usable in all the ways its tests use them: as a decorator, called with
+    keywords (`reason=`) to refine it, and called with a parameter value to mark that value."""
+
+    def __init__(self, decorator):
+        self.decorator = decorator
+
+    @property
+    def mark(self):
+        """What pytest reads when the object stands in a `pytestmark` list."""
+        return self.decorator.mark
+
+    def __call__(self, *args, **kwargs):
+        if len(args) == 1 and not kwargs and (isinstance(args[0], type) or
+                                              type(args[0]).__name__ == "function"):
+            return self.decorator(args[0])
+        if args:
+            deco = self.decorator.with_args(**kwargs) if kwargs else self.decorator
+            return _LegacyParam(args[-1], deco)
+        return _LegacyMark(self.decorator.with_args(**kwargs))
+
+    def __getattr__(self, name):
+        return getattr(self.decorator, name)
+
+
+def _legacy_parametrize():
+    from _pytest.python import Metafunc
+    if getattr(Metafunc.parametrize, "_b200ng_legacy", False):
+        return
+    plain = Metafunc.parametrize
+
+    def parametrize(self, argnames, argvalues, *args, **kwargs):
+        names = [n.strip() for n in argnames.split(",") if n.strip()] \
+            if isinstance(argnames, str) else list(argnames)
+        argvalues = [v.to_param(len(names)) if isinstance(v, _LegacyParam) else v
+                     for v in argvalues]
+        return plain(self, argnames, argvalues, *args, **kwargs)
+    parametrize._b200ng_legacy = True
+    Metafunc.parametrize = parametrize
+
+
+def _python3_helpers():
+    """ngraph/testing/flex_util.py:73-98 names test cases after `function.func_name`, which
+    Python 3 spells `__name__`."""
+    from types import FunctionType
+    import ngraph.testing.flex_util as flex_util
+    plain = flex_util.id_func
+    if getattr(plain, "_b200ng_py3", False):
+        return
+
+    def id_func(param):
+        if isinstance(param, FunctionType):
+            return param.__name__.title()
+        return plain(param)
+    id_func._b200ng_py3 = True
+    flex_util.id_func = id_func
+
+
+FLEX_TRANSFORMERS = ("flexgpu", "b200flex")
+
+
 @pytest.hookimpl(tryfirst=True)
 def pytest_configure(config):
     pytest.config = config           # what `pytest.config.getoption(...)` in the reference reads
+    _python3_helpers()
+
+
+def pytest_sessionstart(session):
+    config = session.config
+    # after the reference's conftest has made its marks (conftest.py:85-106): the same marks,
+    # usable under today's pytest, and counting this package's flex transformer as a flex one.
+    # Its known-failure marks are strict for its own transformer only: a case that works here
+    # shows up as xpassed instead of failing the run.
+    name = config.getvalue("transformer")
+    flex, argon = name in FLEX_TRANSFORMERS, name == "argon"
+    strict = name in ("flexgpu", "argon")
+    x = pytest.mark.xfail
+    config.flex_and_argon_disabled = _LegacyMark(
+        x(flex or argon, reason="Not supported by argon or flex backend", strict=strict))
+    config.argon_disabled = _LegacyMark(
+        x(argon, reason="Not supported by argon backend", strict=strict))
+    config.flex_disabled = _LegacyMark(x(flex, reason="Failing test for Flex", strict=strict))
+    config.hetr_and_cpu_enabled_only = _LegacyMark(
+        x(name not in ("hetr", "cpu"), reason="Only Hetr/CPU and CPU transformers supported",
+          strict=True))
+    config.flex_skip = _LegacyMark(pytest.mark.skipif(flex, reason="Randomly failing test for Flex"))
+    config.argon_skip = _LegacyMark(pytest.mark.skipif(argon, reason="argon"))
+    config.flex_skip_now = pytest.skip if flex else (lambda *a, **k: None)
+    _legacy_parametrize()
 
 
 _outcomes = {}

@@ -33,6 +33,23 @@ def test_registered_in_reference_registry():
     t.close()
 
 
+def test_flex_transformer_with_the_reference_granularity_is_registered():
+    """'b200flex' stands where the reference's 'flexgpu' stands: flex16 storage, every op's result
+    stored (one kernel per op), the flex transformer's tolerances and keyword arguments
+    (flexgputransform.py:67-103)."""
+    assert "b200flex" in ngt.transformer_choices()
+    t = ngt.make_transformer_factory("b200flex", plan_only=True, fixed_point=True)()
+    assert t.impl.flex and not t.impl.fuse and t.impl.fixed_point
+    atol, rtol = type(t).get_default_tolerance(np.array([100.0]))
+    assert rtol == 1e-2 and atol == 8 * 2.0 ** -8          # 100 needs dec 8: one step is 2^-8
+    A = rng.make_axis(4, name="A")
+    x = rng.placeholder([A])
+    comp = t.computation(rng.tanh(x) * 2.0 + x, x)
+    t.initialize()
+    assert len([s for s in comp.impl.steps if s.kind == "ew"]) == 3     # not fused into one
+    t.close()
+
+
 @pytest.mark.parametrize("flex", [False, True])
 @pytest.mark.parametrize("name", NAMES)
 def test_reference_graph_translates_and_plans(name, flex):
