@@ -42,6 +42,7 @@ same configuration and prints the same line with "impl": "reference"; without th
 it falls back to the numpy restatement under oracle/ and says so (`cpu_baseline.kind`).
 """
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -131,13 +132,23 @@ class ClockSampler(object):
         for line in self.proc.stdout:
             self.samples.append([c.strip() for c in line.split(",")])
 
-    def keep_loaded(self, load, sync, want=4, limit_s=4.0):
+    def keep_loaded(self, load, sync, want=4, limit_s=4.0, dist=None, torch=None):
         """The timed region of a short run can end before nvidia-smi has produced a sample: keep
-        the same workload running (untimed) until there are `want` samples under load."""
-        if self.proc is None:
-            return
+        the same workload running (untimed) until there are `want` samples under load.
+        When `load` holds collectives (a data-parallel training step) every replica has to run
+        it the same number of times -- a replica that stopped early would leave the others waiting
+        in an exchange for ever -- so with `dist` the replicas agree after every batch of calls
+        whether to go on (any of them still short of samples and within its time limit)."""
         t0 = time.perf_counter()
-        while len(self.samples) < want and time.perf_counter() - t0 < limit_s:
+        while True:
+            need = self.proc is not None and len(self.samples) < want and \
+                time.perf_counter() - t0 < limit_s
+            if dist is not None:
+                flag = torch.tensor([1.0 if need else 0.0], device="cuda")
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+                need = bool(flag.item() > 0)
+            if not need:
+                return
             for _ in range(20):
                 load()
             sync()
@@ -714,7 +725,8 @@ def measure_training(args, rank, world, torch, dist, local, flex, steps, repeats
     timer.barrier()
     sampler.start()
     loop_ms = timer.loops(step_resident, steps, repeats)
-    sampler.keep_loaded(step_resident, torch.cuda.synchronize)
+    # (the step exchanges gradients: the replicas must agree on how often they run it)
+    sampler.keep_loaded(step_resident, torch.cuda.synchronize, dist=dist, torch=torch)
     stream = timer.stream
     kinds = {}
     passes = 3
@@ -1150,7 +1162,9 @@ def run_b200(args, rank, world):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # (a replica that fails must not keep the others in a collective for the default 10 min)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=240))
     try:
         w = args.workload
         if w.startswith("gemm"):

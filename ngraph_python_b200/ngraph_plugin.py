@@ -329,8 +329,12 @@ class _PluginComputation(object):
         if isinstance(returns, dict):
             self.dict_keys = list(returns.keys())
             outs = [tr(returns[k]) for k in self.dict_keys]
+        elif isinstance(returns, collections.abc.Set) and not isinstance(returns, ref.Op) and \
+                type(returns).__name__ != "OrderedSet":
+            # an unordered set of ops comes back as a dict keyed by op (base.py:128-132)
+            self.dict_keys = list(returns)
+            outs = [tr(r) for r in self.dict_keys]
         elif isinstance(returns, collections.abc.Container) and not isinstance(returns, ref.Op):
-            self.container = type(returns)
             outs = [tr(r) for r in returns]
         elif returns is None:
             outs = None
@@ -386,7 +390,7 @@ class _PluginComputation(object):
             return dict(zip(self.dict_keys, res))
         if isinstance(self.returns, ref.Op) or self.returns is None:
             return res
-        return self.container(res) if self.container in (tuple, list) else tuple(res)
+        return tuple(res)       # any sequence of ops comes back as a tuple (base.py:123-127)
 
 
 def _result_ops(returns):

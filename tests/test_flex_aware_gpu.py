@@ -40,7 +40,9 @@ def _stored(t, comp):
     """{op: (view, mantissas, step)} for every op whose value a kernel of `comp` stored in a
     buffer of its own, plus the computation's inputs and variables."""
     from ngraph_python_b200.op_graph import AssignableTensorOp
-    written = set(id(b) for s in comp.steps for b in s.output_buffers())
+    # (out_views, not output_buffers(): a pooling result shares its input's exponent entry and is
+    # not listed as a separately managed buffer, but it is stored all the same)
+    written = set(id(v.buffer) for s in comp.steps for v in s.out_views)
     out = {}
     for op, view in t._views.items():
         buf = view.buffer
@@ -72,10 +74,10 @@ def _check(t, comp, min_checked):
     # of the others, not from what it stored of them: only tensors of OTHER kernels are given
     siblings = {}
     for s in comp.steps:
-        ids = set(id(b) for b in s.output_buffers())
+        ids = set(id(v.buffer) for v in s.out_views)
         for i in ids:
             siblings[i] = ids
-    checked, worst = 0, 0
+    checked, worst, failures = 0, 0, []
     for op, (view, mant, step, buf_id) in stored.items():
         if isinstance(op, AssignableTensorOp):
             continue
@@ -94,12 +96,16 @@ def _check(t, comp, min_checked):
         m_want = np.clip(np.rint(want / step), -32768, 32767).astype(np.int64)
         diff = np.abs(m_want - mant)
         worst = max(worst, int(diff.max()))
-        assert diff.max() <= 1, "%s: %d mantissas off by more than one step (max %d, step %g)" % (
-            op, int((diff > 1).sum()), int(diff.max()), step)
-        # and a one-step difference is rounding at a half step, not an offset: rare
-        assert (diff > 0).mean() < 0.02, "%s: %.1f %% of the mantissas differ" % (
-            op, 100.0 * (diff > 0).mean())
+        if diff.max() > 1:
+            failures.append("%s: %d of %d mantissas off by more than one step (max %d, step %g, "
+                            "largest mantissa %d)" % (op, int((diff > 1).sum()), diff.size,
+                                                      int(diff.max()), step, int(np.abs(mant).max())))
+        elif (diff > 0).mean() >= 0.05:
+            # a one-step difference is rounding at a half step, not an offset: rare
+            failures.append("%s: %.1f %% of the mantissas differ by a step (step %g)" % (
+                op, 100.0 * (diff > 0).mean(), step))
         checked += 1
+    assert not failures, "\n".join(failures)
     assert checked >= min_checked, "only %d stored tensors were checked" % checked
     return checked, worst
 
