@@ -132,7 +132,7 @@ class ClockSampler(object):
         for line in self.proc.stdout:
             self.samples.append([c.strip() for c in line.split(",")])
 
-    def keep_loaded(self, load, sync, want=4, limit_s=4.0, dist=None, torch=None):
+    def keep_loaded(self, load, sync, want=4, limit_s=4.0, dist=None, torch=None, device="cuda"):
         """The timed region of a short run can end before nvidia-smi has produced a sample: keep
         the same workload running (untimed) until there are `want` samples under load.
         When `load` holds collectives (a data-parallel training step) every replica has to run
@@ -144,7 +144,7 @@ class ClockSampler(object):
             need = self.proc is not None and len(self.samples) < want and \
                 time.perf_counter() - t0 < limit_s
             if dist is not None:
-                flag = torch.tensor([1.0 if need else 0.0], device="cuda")
+                flag = torch.tensor([1.0 if need else 0.0], device=device)
                 dist.all_reduce(flag, op=dist.ReduceOp.MAX)
                 need = bool(flag.item() > 0)
             if not need:

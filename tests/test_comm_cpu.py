@@ -156,3 +156,45 @@ def test_a_replica_that_leaves_ends_the_exchange_with_an_error():
     assert "left" in by and by["left"][1]
     assert "CommError" in by, got
     assert by["CommError"][1] and by["CommError"][2] < 60.0
+
+
+def _sampler_rank(rank, world, port, out):
+    """One replica of the benchmark's keep-the-GPU-loaded loop, with a load that exchanges."""
+    import datetime
+    import torch.distributed as dist
+    import bench
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=20))
+    sampler = bench.ClockSampler(0)
+    sampler.proc = object()                       # "nvidia-smi is running"
+    # replica 0 already has its samples; replica 1 gets them only after 40 calls
+    sampler.samples = [["0"]] * 4 if rank == 0 else []
+    calls = [0]
+
+    def load():
+        calls[0] += 1
+        dist.all_reduce(torch.ones(1))            # a step that holds a collective
+        if rank == 1 and calls[0] == 40:
+            sampler.samples.extend([["0"]] * 4)
+    sampler.keep_loaded(load, lambda: None, want=4, limit_s=30.0, dist=dist, torch=torch,
+                        device="cpu")
+    out.put((rank, calls[0]))
+    dist.destroy_process_group()
+
+
+def test_replicas_agree_on_how_long_the_benchmark_keeps_them_loaded():
+    """bench.py keeps a GPU busy until its clock sampler has samples.  When the workload holds a
+    collective every replica must run it equally often, whatever its own sampler says: a replica
+    that stopped on its own would leave the others waiting in an exchange for ever."""
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sampler_rank, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(out.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    assert got[0] == got[1] == 40
