@@ -594,7 +594,7 @@ def run_resnet(args, rank, world, torch, dist, local):
 
 
 # ---- the reference arm of the ResNet-20 workloads ------------------------------------------------
-def resnet_cpu_reference(n, steps, warmup, budget_s=None):
+def resnet_cpu_reference(n, steps, warmup, max_seconds=None):
     """The reference CPU transformer on the same network and batch size (all host cores through
     numpy's BLAS); without the reference tree, the numpy restatement on a 32-image sample."""
     cores = os.cpu_count() or 1
@@ -610,7 +610,7 @@ def resnet_cpu_reference(n, steps, warmup, budget_s=None):
         t0 = time.perf_counter()
         comp(x)
         one = time.perf_counter() - t0
-        reps = steps if budget_s is None else int(max(1, min(steps, budget_s / max(one, 1e-3))))
+        reps = steps if max_seconds is None else int(max(1, min(steps, max_seconds / max(one, 1e-3))))
         t0 = time.perf_counter()
         for _ in range(reps):
             comp(x)
@@ -628,7 +628,7 @@ def resnet_cpu_reference(n, steps, warmup, budget_s=None):
     t0 = time.perf_counter()
     resnet20_numpy(x, weights)
     one = time.perf_counter() - t0
-    reps = steps if budget_s is None else int(max(1, min(steps, budget_s / max(one, 1e-3))))
+    reps = steps if max_seconds is None else int(max(1, min(steps, max_seconds / max(one, 1e-3))))
     t0 = time.perf_counter()
     for _ in range(reps):
         resnet20_numpy(x, weights)
@@ -837,7 +837,7 @@ def run_resnet_train(args, rank, world, torch, dist, local):
 
 def train_cpu_reference(global_n, steps=1, lr=0.1):
     """The reference CPU transformer on one training step of the global batch (hetr itself needs
-    mpirun / MLSL, which this image lacks: SURVEY of the reference's hetr path)."""
+    mpirun / MLSL, which this image lacks)."""
     cores = os.cpu_count() or 1
     fe = reference_frontend()
     if fe is not None:
@@ -1139,10 +1139,10 @@ def c2_cpu_reference(workload, rows, steps, warmup):
     return alg / dt / 1e9, dt, cores, kind, what
 
 
-def c2_cpu_baseline(workload, budget_s=10.0):
+def c2_cpu_baseline(workload, max_seconds=10.0):
     rows = 256
     gbs, dt, cores, kind, what = c2_cpu_reference(workload, rows, steps=1, warmup=1)
-    steps = int(max(1, min(20, budget_s / max(dt, 1e-3))))
+    steps = int(max(1, min(20, max_seconds / max(dt, 1e-3))))
     gbs, dt, cores, kind, what = c2_cpu_reference(workload, rows, steps=steps, warmup=0)
     return {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
             "sample": "%d of %d rows x %d cols, %d passes, %s" % (rows, C2_ROWS, C2_COLS, steps, what)}
@@ -1197,7 +1197,7 @@ def run_b200(args, rank, world):
                 line["extras"] = extras
         if line is not None and world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = resnet_cpu_reference(args.batch, steps=10, warmup=1,
-                                                        budget_s=12.0)
+                                                        max_seconds=12.0)
         return line
     finally:
         if dist is not None:
@@ -1261,7 +1261,7 @@ def run_reference(args, rank, world):
     if w.startswith("resnet20"):
         flex = w == "resnet20_flex16"
         b = resnet_cpu_reference(args.batch, steps=max(1, args.steps), warmup=max(1, args.warmup),
-                                 budget_s=120.0)
+                                 max_seconds=120.0)
         fe = reference_frontend()
         frontend = REFERENCE_NETWORK if fe is not None else OWN_NETWORK
         return {

@@ -1590,7 +1590,7 @@ class B200Transformer(object):
                 self._table_host = torch.zeros((n, 2), dtype=torch.float32).pin_memory()
                 self._stats_host = torch.zeros((n,), dtype=torch.int32).pin_memory()
                 self._table_np = self._table_host.numpy()
-                self._dec_uploaded = {}
+                self._dec_uploaded = np.full((n,), -1, dtype=np.int64)   # exponent each row holds
                 self._table_dirty = True
         for op, b in self._buffers.items():
             if b.init_array is not None and not getattr(b, "initialised", False):
@@ -1828,11 +1828,22 @@ class B200Transformer(object):
 
     def _set_table_row_host(self, slot, dec):
         """Updates the pinned copy of a table row; the device copy follows in one transfer."""
-        if self._dec_uploaded.get(slot) != dec:
+        if self._dec_uploaded[slot] != dec:
             self._flex_epoch += 1
             self._dec_uploaded[slot] = dec
             self._table_np[slot, 0] = math.ldexp(1.0, -dec)
             self._table_np[slot, 1] = math.ldexp(1.0, dec)
+            self._table_dirty = True
+
+    def _set_table_rows_host(self, slots, decs):
+        """_set_table_row_host for arrays of rows and exponents."""
+        changed = self._dec_uploaded[slots] != decs
+        if changed.any():
+            rows, d = slots[changed], decs[changed]
+            self._flex_epoch += 1
+            self._dec_uploaded[rows] = d
+            self._table_np[rows, 0] = np.ldexp(1.0, (-d).astype(np.int32))
+            self._table_np[rows, 1] = np.ldexp(1.0, d.astype(np.int32))
             self._table_dirty = True
 
     def _begin_call(self, comp):
@@ -1840,8 +1851,13 @@ class B200Transformer(object):
         self._allreduce = comp._allreduce
         if self._allreduce is not None:
             self._allreduce.begin_call()
-        if not self.flex:
-            return
+        if self.flex:
+            self._begin_call_flex(comp)
+
+    def _begin_call_flex(self, comp):
+        """Exponent bookkeeping before a call (manage_before_computation of every tensor the call
+        writes, flexgputransform.py:347-358): host work only, plus the upload of the scale table
+        when a row changed."""
         self.flex_manager.autoflex_count += 1
         self._inputs_written = []
         steady = getattr(comp, "_steady", None)
@@ -1869,14 +1885,25 @@ class B200Transformer(object):
                 if b.entry is not None and not getattr(b, "shares_entry", False) and id(b) not in seen:
                     self._set_table_row_host(b.slot, b.entry.dec)
                     self._set_table_row_host(b.slot_write, b.entry.dec)
-        for b in bufs:
-            e = b.entry
-            dec_stored = e.dec
+        if bufs:
+            arrays = getattr(comp, "_flex_buf_arrays", None)
+            if arrays is None:
+                arrays = (np.array([b.entry.i for b in bufs], dtype=np.int64),
+                          np.array([b.slot_write for b in bufs], dtype=np.int64),
+                          np.array([b.slot for b in bufs], dtype=np.int64))
+                comp._flex_buf_arrays = arrays
+            ids, slot_w, slot_r = arrays
+            fm = self.flex_manager
+            dec_stored = fm.dec[ids].copy()
             # tensors this call overwrites adopt the exponent chosen after their previous write
-            dec_w = e.begin_write() if e.initialized else dec_stored
-            self._set_table_row_host(b.slot_write, dec_w)
-            if b.slot != b.slot_write:
-                self._set_table_row_host(b.slot, dec_stored)
+            dec_w = dec_stored.copy()
+            init = fm.initialized[ids]
+            if init.any():
+                dec_w[init] = fm.begin_write_batch(ids[init])
+            self._set_table_rows_host(slot_w, dec_w)
+            two = slot_r != slot_w
+            if two.any():
+                self._set_table_rows_host(slot_r[two], dec_stored[two])
         if self._table_dirty:
             self._table.copy_(self._table_host, non_blocking=True)
             self._table_dirty = False
@@ -1903,16 +1930,23 @@ class B200Transformer(object):
         else:
             self._publish()
             self._stats_clean = self.flex
-        if self._allreduce is not None and self.comm.size > 1:
+        exchanging = self._allreduce is not None and self.comm.size > 1
+        if exchanging:
             self._allreduce.finish()        # CommError instead of an endless synchronisation
         torch.cuda.current_stream(self.device).synchronize()
+        if exchanging:
+            self._allreduce.after_sync()
         for b in comp.written:
             b.version += 1
         if int(self._status_host[0]) != 0:
             self._status.zero_()
             raise lib.B200Error("a device-side wait ran out during the computation")
-        if not self.flex:
-            return
+        if self.flex:
+            self._end_call_flex(comp)
+
+    def _end_call_flex(self, comp):
+        """Exponent bookkeeping after a call (manage_after_computation, flexgputransform.py:
+        360-366) from the statistics the call left in pinned host memory."""
         stats = self._stats_host.numpy()
         steady = getattr(comp, "_steady", None)
         if steady is not None and steady[0] == self._flex_epoch and \
@@ -1921,15 +1955,25 @@ class B200Transformer(object):
             # of them: every entry would make the choice it made before
             return
         self._flex_epoch += 1
+        fm = self.flex_manager
         for b in self._inputs_written:
             b.entry.end_write(int(stats[b.slot]))
-        for b in comp.written:
-            b.entry.end_write(int(stats[b.slot_write]))
-        entries = [b.entry for b in self._inputs_written] + [b.entry for b in comp.written]
-        if all(e.fixed_point or (e._run_length > flexmod.HISTORY_LEN and
-                                 e.pending_dec in (None, e.dec)) for e in entries):
-            idx = np.array([b.slot for b in self._inputs_written] +
-                           [b.slot_write for b in comp.written], dtype=np.int64)
+        arrays = getattr(comp, "_flex_written_arrays", None)
+        if arrays is None:
+            ids = np.array([b.entry.i for b in comp.written], dtype=np.int64)
+            arrays = (ids, np.array([b.slot_write for b in comp.written], dtype=np.int64),
+                      len(set(ids.tolist())) == len(ids))
+            comp._flex_written_arrays = arrays
+        ids, slots, distinct = arrays
+        if distinct:
+            fm.end_write_batch(ids, stats[slots])      # all written tensors in a few array ops
+        else:
+            for b in comp.written:                     # an entry written twice: one at a time
+                b.entry.end_write(int(stats[b.slot_write]))
+        in_ids = np.array([b.entry.i for b in self._inputs_written], dtype=np.int64)
+        if fm.settled(ids) and fm.settled(in_ids):
+            idx = np.concatenate([np.array([b.slot for b in self._inputs_written], dtype=np.int64),
+                                  slots])
             comp._steady = (self._flex_epoch, idx, stats[idx].copy(), len(self._inputs_written))
         else:
             comp._steady = None

@@ -11,8 +11,8 @@ exposed the active configuration as `pytest.config`; this module is loaded as a 
 them and puts that attribute back.  It also imports the b200 plug-in first, so that 'b200' is
 among the `--transformer` choices the reference's conftest offers.
 
-Not collected by this repository's own test run: the outcome of the reference's suite on b200 is
-recorded in DESIGN.md, test by test where it fails.
+Not collected by this repository's own test run; tests/test_reference_suites_gpu.py runs it in a
+child process and holds the outcome to what the reference's own cpu transformer passes.
 """
 import os
 import sys

@@ -198,3 +198,52 @@ def test_replicas_agree_on_how_long_the_benchmark_keeps_them_loaded():
     for p in procs:
         p.join(timeout=30)
     assert got[0] == got[1] == 40
+
+
+def _bare_nccl_comm(timeout_s):
+    """An NcclComm without a library behind it: only the watchdog's own logic is exercised."""
+    import threading
+    c = object.__new__(C.NcclComm)
+    c.timeout_s, c.handle = timeout_s, object()
+    c._deadline, c._failed, c._stop, c._watcher = None, None, threading.Event(), None
+    c.aborted = []
+    c.abort = lambda: c.aborted.append(True)
+    return c
+
+
+def test_watchdog_ends_a_step_whose_collective_never_completes():
+    """The main thread synchronises; the watchdog aborts the communicator when the time limit
+    passes (which makes the kernels in flight return) and the call ends with CommError."""
+    import time
+    c = _bare_nccl_comm(0.1)
+    c.poll_error = lambda: None                      # NCCL reports nothing: a peer is just absent
+    c.watch()
+    time.sleep(0.4)                                  # "the synchronisation"
+    with pytest.raises(C.CommError, match="time limit"):
+        c.unwatch()
+    assert c.aborted == [True]
+    with pytest.raises(C.CommError):                 # the communicator stays failed
+        c.watch()
+    c._stop.set()
+
+
+def test_watchdog_reports_an_asynchronous_nccl_error_and_stays_quiet_otherwise():
+    import time
+    c = _bare_nccl_comm(30.0)
+    state = {"bad": False}
+
+    def poll():
+        if state["bad"]:
+            raise C.CommError("a collective failed asynchronously: remote process exited")
+    c.poll_error = poll
+    c.watch()
+    time.sleep(0.1)
+    c.unwatch()                                      # a healthy step: nothing raised, no abort
+    assert c.aborted == []
+    c.watch()
+    state["bad"] = True
+    time.sleep(0.2)
+    with pytest.raises(C.CommError, match="remote process exited"):
+        c.unwatch()
+    assert c.aborted == [True]
+    c._stop.set()
